@@ -1,0 +1,136 @@
+/*
+ * sirius_b200 — C ABI of the B200-native colocated training step.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status (SRT_OK == 0) and never
+ * throws. Device pointers are raw CUDA addresses; `stream` is a cudaStream_t passed as void*.
+ * On failure srt_last_error() returns a thread-local description.
+ *
+ * Citations are paths inside the Sirius reference tree (file:line). The reference has no
+ * arithmetic of its own: its training scripts call torchvision / HuggingFace modules
+ * (train/resnet152.py:84-91, train/swin_b.py:83-95), so the compute entry points below replace
+ * the PyTorch operator each one names; the runtime entry points replace the reference's C++.
+ *
+ * Tensor layouts: activations NHWC, filters KRSC, both densely packed. dtype SRT_F32 uses fp32
+ * operands and fp32 accumulation on the CUDA cores; SRT_BF16 uses bf16 operands with fp32
+ * accumulation on the tcgen05 tensor cores (accumulators in tensor memory).
+ */
+#ifndef SIRIUS_B200_H_
+#define SIRIUS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { SRT_OK = 0, SRT_ERR_INVALID = 1, SRT_ERR_CUDA = 2, SRT_ERR_UNSUPPORTED = 3,
+       SRT_ERR_NOMEM = 4, SRT_ERR_TIMEOUT = 5, SRT_ERR_STATE = 6 };
+enum { SRT_F32 = 0, SRT_BF16 = 1 };
+/* Which kernel family a convolution call uses. AUTO: tcgen05 for bf16, CUDA cores for fp32. */
+enum { SRT_IMPL_AUTO = 0, SRT_IMPL_SIMT = 1, SRT_IMPL_TCGEN05 = 2 };
+
+const char* srt_last_error(void);
+const char* srt_version(void);
+
+/* ---- convolution as implicit GEMM (replaces nn.Conv2d / nn.Linear inside model(images),
+ *      train/resnet152.py:86; backward from scaler.scale(loss).backward(), :89) ------------- */
+typedef struct srt_conv_desc {
+  int N, H, W, C;   /* input  NHWC (C % 8 == 0) */
+  int K, R, S;      /* filter KRSC              */
+  int stride, pad;
+  int P, Q;         /* output NPQK              */
+} srt_conv_desc;
+
+/* Fused epilogue of fprop/dgrad: y = acc (+ bias[k]) (+ addend[m][k]).  Null pointers disable a
+ * term. addend may alias y. */
+typedef struct srt_conv_epilogue {
+  const float* bias;     /* [K] fp32, or NULL            */
+  const void*  addend;   /* same shape/dtype as y, or NULL */
+} srt_conv_epilogue;
+
+/* y[N,P,Q,K] = conv(x[N,H,W,C], w[K,R,S,C]). */
+int srt_conv_fprop(const srt_conv_desc* d, int dtype, int impl, const void* x, const void* w,
+                   void* y, const srt_conv_epilogue* ep, void* stream);
+/* dx[N,H,W,C] = conv^T(dy[N,P,Q,K], wt[C,R,S,K]); wt comes from srt_conv_filter_transpose. */
+int srt_conv_dgrad(const srt_conv_desc* d, int dtype, int impl, const void* dy, const void* wt,
+                   void* dx, const srt_conv_epilogue* ep, void* stream);
+/* dw[K,R,S,C] (fp32, overwritten) = sum over N,P,Q of dy x x. `scratch` holds split partial
+ * sums; query its size with srt_conv_wgrad_scratch_bytes. */
+int srt_conv_wgrad(const srt_conv_desc* d, int dtype, int impl, const void* dy, const void* x,
+                   float* dw, void* scratch, size_t scratch_bytes, void* stream);
+size_t srt_conv_wgrad_scratch_bytes(const srt_conv_desc* d, int dtype, int impl);
+/* wt[C,R,S,K] = transpose of w[K,R,S,C] (same dtype). */
+int srt_conv_filter_transpose(const srt_conv_desc* d, int dtype, const void* w, void* wt,
+                              void* stream);
+
+/* ---- BatchNorm2d in training mode over NHWC rows (replaces nn.BatchNorm2d + ReLU + residual
+ *      add of torchvision Bottleneck, reached from train/resnet152.py:86,89) ---------------- */
+/* Per-channel batch statistics of z[rows][C]; updates running stats in place
+ * (momentum 0.1, unbiased running variance) and writes scale/shift so that
+ * bn(z) = z*scale + shift, plus mean and invstd for the backward pass.
+ * scratch: srt_bn_scratch_bytes(rows, C) bytes. */
+int srt_bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma,
+                 const float* beta, float eps, float momentum, float* running_mean,
+                 float* running_var, float* mean, float* invstd, float* scale, float* shift,
+                 void* scratch, size_t scratch_bytes, void* stream);
+size_t srt_bn_scratch_bytes(int64_t rows, int C);
+/* y = act(z*scale + shift (+ residual)); relu != 0 applies max(.,0). */
+int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
+                 const float* scale, const float* shift, int relu, void* stream);
+/* Backward of y = act(bn(z) (+ residual)). dy is the gradient w.r.t. y; y supplies the ReLU mask
+ * when relu != 0. Writes dz, dgamma, dbeta and, when dresidual != NULL, the masked gradient that
+ * flows to the residual branch. */
+int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
+                    const float* gamma, const float* mean, const float* invstd, int relu,
+                    void* dz, void* dresidual, float* dgamma, float* dbeta, void* scratch,
+                    size_t scratch_bytes, void* stream);
+
+/* ---- pooling (replaces nn.MaxPool2d(3,2,1) and nn.AdaptiveAvgPool2d(1) of torchvision
+ *      ResNet) ------------------------------------------------------------------------------- */
+int srt_maxpool3x3s2_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W,
+                         int C, void* stream);
+int srt_maxpool3x3s2_bwd(int dtype, const void* dy, const uint8_t* argmax, void* dx, int N, int H,
+                         int W, int C, void* stream);
+int srt_avgpool_fwd(int dtype, const void* x, void* y, int N, int HW, int C, void* stream);
+int srt_avgpool_bwd(int dtype, const void* dy, void* dx, int N, int HW, int C, void* stream);
+
+/* ---- loss (replaces nn.CrossEntropyLoss, train/resnet152.py:26,87, and the loss scaling of
+ *      MicroBatchManager.scale_loss, pytorch/torch_col/dynamic_batch.py:112-120) -------------- */
+/* loss_sum[0] += sum_i CE(logits[i], labels[i]) * grad_scale ; dlogits = (softmax - onehot) *
+ * grad_scale. With grad_scale = 1/global_batch the accumulated gradients equal the global mean. */
+int srt_softmax_ce(int dtype, const void* logits, const int64_t* labels, int B, int classes,
+                   float grad_scale, float* loss_sum, void* dlogits, void* stream);
+/* dbias[k] = sum over rows of dy[rows][K] (fp32 out). */
+int srt_colsum(int dtype, const void* dy, int64_t rows, int K, float* out, void* stream);
+
+/* ---- optimizer + gradient accumulation (replaces torch.optim.SGD, train/resnet152.py:27-28,
+ *      and GradAccumulator, pytorch/torch_col/accumulate.py:7-49) ----------------------------- */
+/* g += wd*p ; m = mu*m + g (m = g on the first step) ; p -= lr*m ; optional bf16 copy of p. */
+int srt_sgd_momentum(float* p, const float* g, float* m, void* p_bf16, int64_t n, float lr,
+                     float mu, float wd, int first_step, void* stream);
+/* AdamW with fp32 state; step counts from 1. */
+int srt_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, int64_t n, float lr,
+              float beta1, float beta2, float eps, float wd, int step, void* stream);
+/* acc += g ; g = 0  (GradAccumulator.accumulate). */
+int srt_grad_accumulate(float* acc, float* g, int64_t n, void* stream);
+
+/* ---- layout / dtype helpers ---------------------------------------------------------------- */
+/* NCHW fp32 (host convention of the reference's data path, pytorch/torch_col/dynamic_batch.py:
+ * 438-459) -> NHWC of `dtype` with channels zero-padded to Cpad. */
+int srt_nchw_to_nhwc(int dtype, const float* src, void* dst, int N, int C, int H, int W, int Cpad,
+                     void* stream);
+int srt_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
+int srt_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
+
+/* ---- SM partition seen by the kernels (replaces SMPartitioner::SetStreamTpcMask,
+ *      common/sm_partition.cu:316-336: the reference pokes a TPC mask into the driver's stream
+ *      struct; here every persistent kernel tests %smid against this mask and retires). ------- */
+/* mask[0..2]: bit i set = SM i is available to training kernels. */
+int srt_set_sm_mask(const uint64_t mask[3]);
+int srt_get_sm_mask(uint64_t mask[3]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIRIUS_B200_H_ */

@@ -1,0 +1,76 @@
+"""In-tree build of libsirius_b200.so (hand-written sm_100a kernels + C++ runtime).
+
+nvcc cross-compiles for sm_100a without a GPU. Objects are cached under sirius_b200/build/ and
+rebuilt when a source or header is newer.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+BUILD = PKG / "build"
+LIB = PKG / "libsirius_b200.so"
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",
+    "-Xptxas", "-v",
+]
+
+
+def _sources() -> list[Path]:
+    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cc")) + list((CSRC / "runtime").glob("*.cc")))
+
+
+def _headers() -> list[Path]:
+    root = PKG.parent / "include"
+    return (list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((CSRC / "runtime").glob("*.h"))
+            + list(root.glob("*.h")))
+
+
+def _compile(src: Path, obj: Path, verbose: bool) -> None:
+    cmd = [NVCC, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    log = BUILD / (obj.stem + ".ptxas.log")
+    log.write_text(res.stderr)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError(f"nvcc failed on {src.name}")
+    if verbose:
+        for line in res.stderr.splitlines():
+            if "warning" in line.lower():
+                print(line)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every source for sm_100a and link the shared library. Returns its path."""
+    BUILD.mkdir(exist_ok=True)
+    newest_hdr = max((h.stat().st_mtime for h in _headers()), default=0.0)
+    jobs, objs = [], []
+    for src in _sources():
+        obj = BUILD / (src.stem + ".o")
+        objs.append(obj)
+        stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, newest_hdr)
+        if stale:
+            jobs.append((src, obj))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(lambda j: _compile(j[0], j[1], verbose), jobs))
+    if jobs or not LIB.exists():
+        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-lpthread", "-lrt", "-ldl"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    p = build(force="--force" in sys.argv, verbose=True)
+    print(p)

@@ -1,0 +1,260 @@
+// extern "C" surface of the kernel library: argument checks, dtype / kernel-family dispatch.
+#include <stdarg.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "conv_geom.cuh"
+#include "ops.cuh"
+
+namespace srt {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static int cached[16] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static std::mutex g_mask_mu;
+static SmMask g_mask = {{~0ull, ~0ull, ~0ull}};
+SmMask current_sm_mask() {
+  std::lock_guard<std::mutex> lk(g_mask_mu);
+  return g_mask;
+}
+void set_current_sm_mask(const SmMask& m) {
+  std::lock_guard<std::mutex> lk(g_mask_mu);
+  g_mask = m;
+}
+
+int tc_status_fetch(int* out);
+void tc_set_force_gather(int v);
+
+static int check_desc(const srt_conv_desc& d) {
+  SRT_REQUIRE(d.N > 0 && d.H > 0 && d.W > 0 && d.C > 0 && d.K > 0 && d.R > 0 && d.S > 0 &&
+                  d.stride > 0 && d.pad >= 0,
+              "conv: non-positive extent");
+  SRT_REQUIRE(d.P == (d.H + 2 * d.pad - d.R) / d.stride + 1 &&
+                  d.Q == (d.W + 2 * d.pad - d.S) / d.stride + 1,
+              "conv: P/Q (%d,%d) inconsistent with H/W/pad/stride", d.P, d.Q);
+  SRT_REQUIRE(d.C % 8 == 0 && d.K % 8 == 0, "conv: C (%d) and K (%d) must be multiples of 8", d.C, d.K);
+  SRT_REQUIRE((long long)d.N * d.H * d.W * d.C < (1ll << 31) &&
+                  (long long)d.N * d.P * d.Q * d.K < (1ll << 31),
+              "conv: tensor exceeds 2^31 elements");
+  return SRT_OK;
+}
+
+static bool use_tc(int dtype, int impl) {
+  return dtype == SRT_BF16 && impl != SRT_IMPL_SIMT;
+}
+
+int conv_fprop(const srt_conv_desc& d, int dtype, int impl, const void* x, const void* w, void* y,
+               const srt_conv_epilogue* ep, cudaStream_t st) {
+  int rc = check_desc(d);
+  if (rc) return rc;
+  SRT_REQUIRE(!(dtype == SRT_F32 && impl == SRT_IMPL_TCGEN05), "conv: tcgen05 path is bf16 only");
+  GatherGeom g = make_fprop_geom(d);
+  if (use_tc(dtype, impl)) return conv_gather_gemm_tc(g, x, w, y, ep, st);
+  return conv_gather_gemm_simt(g, dtype, x, w, y, ep, st);
+}
+
+int conv_dgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* wt,
+               void* dx, const srt_conv_epilogue* ep, cudaStream_t st) {
+  int rc = check_desc(d);
+  if (rc) return rc;
+  SRT_REQUIRE(!(dtype == SRT_F32 && impl == SRT_IMPL_TCGEN05), "conv: tcgen05 path is bf16 only");
+  GatherGeom g = make_dgrad_geom(d);
+  if (use_tc(dtype, impl)) return conv_gather_gemm_tc(g, dy, wt, dx, ep, st);
+  return conv_gather_gemm_simt(g, dtype, dy, wt, dx, ep, st);
+}
+
+size_t conv_wgrad_scratch_bytes(const srt_conv_desc& d, int dtype, int impl) {
+  GatherGeom g = make_fprop_geom(d);
+  return use_tc(dtype, impl) ? conv_wgrad_tc_scratch_bytes(g) : conv_wgrad_simt_scratch_bytes(g);
+}
+
+int conv_wgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* x,
+               float* dw, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  int rc = check_desc(d);
+  if (rc) return rc;
+  SRT_REQUIRE(!(dtype == SRT_F32 && impl == SRT_IMPL_TCGEN05), "conv: tcgen05 path is bf16 only");
+  GatherGeom g = make_fprop_geom(d);
+  if (use_tc(dtype, impl)) return conv_wgrad_tc(g, dy, x, dw, scratch, scratch_bytes, st);
+  return conv_wgrad_simt(g, dtype, dy, x, dw, scratch, scratch_bytes, st);
+}
+
+}  // namespace srt
+
+using namespace srt;
+
+#define ST(s) ((cudaStream_t)(s))
+#define CHECK_DTYPE(dt) SRT_REQUIRE((dt) == SRT_F32 || (dt) == SRT_BF16, "unknown dtype %d", (int)(dt))
+
+extern "C" {
+
+const char* srt_last_error(void) { return g_err; }
+const char* srt_version(void) { return "sirius_b200 0.1 (sm_100a)"; }
+
+int srt_conv_fprop(const srt_conv_desc* d, int dtype, int impl, const void* x, const void* w,
+                   void* y, const srt_conv_epilogue* ep, void* stream) {
+  SRT_REQUIRE(d && x && w && y, "conv_fprop: null argument");
+  CHECK_DTYPE(dtype);
+  return conv_fprop(*d, dtype, impl, x, w, y, ep, ST(stream));
+}
+int srt_conv_dgrad(const srt_conv_desc* d, int dtype, int impl, const void* dy, const void* wt,
+                   void* dx, const srt_conv_epilogue* ep, void* stream) {
+  SRT_REQUIRE(d && dy && wt && dx, "conv_dgrad: null argument");
+  CHECK_DTYPE(dtype);
+  return conv_dgrad(*d, dtype, impl, dy, wt, dx, ep, ST(stream));
+}
+int srt_conv_wgrad(const srt_conv_desc* d, int dtype, int impl, const void* dy, const void* x,
+                   float* dw, void* scratch, size_t scratch_bytes, void* stream) {
+  SRT_REQUIRE(d && dy && x && dw, "conv_wgrad: null argument");
+  CHECK_DTYPE(dtype);
+  return conv_wgrad(*d, dtype, impl, dy, x, dw, scratch, scratch_bytes, ST(stream));
+}
+size_t srt_conv_wgrad_scratch_bytes(const srt_conv_desc* d, int dtype, int impl) {
+  if (!d) return 0;
+  return conv_wgrad_scratch_bytes(*d, dtype, impl);
+}
+int srt_conv_filter_transpose(const srt_conv_desc* d, int dtype, const void* w, void* wt,
+                              void* stream) {
+  SRT_REQUIRE(d && w && wt, "filter_transpose: null argument");
+  CHECK_DTYPE(dtype);
+  return filter_transpose(dtype, w, wt, d->K, d->R * d->S, d->C, ST(stream));
+}
+
+int srt_bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma,
+                 const float* beta, float eps, float momentum, float* running_mean,
+                 float* running_var, float* mean, float* invstd, float* scale, float* shift,
+                 void* scratch, size_t scratch_bytes, void* stream) {
+  SRT_REQUIRE(z && mean && invstd && scale && shift, "bn_stats: null argument");
+  CHECK_DTYPE(dtype);
+  return bn_stats(dtype, z, rows, C, gamma, beta, eps, momentum, running_mean, running_var, mean,
+                  invstd, scale, shift, scratch, scratch_bytes, ST(stream));
+}
+size_t srt_bn_scratch_bytes(int64_t rows, int C) { return bn_scratch_bytes(rows, C); }
+int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
+                 const float* scale, const float* shift, int relu, void* stream) {
+  SRT_REQUIRE(z && y && scale && shift, "bn_apply: null argument");
+  CHECK_DTYPE(dtype);
+  return bn_apply(dtype, z, residual, y, rows, C, scale, shift, relu, ST(stream));
+}
+int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
+                    const float* gamma, const float* mean, const float* invstd, int relu,
+                    void* dz, void* dresidual, float* dgamma, float* dbeta, void* scratch,
+                    size_t scratch_bytes, void* stream) {
+  SRT_REQUIRE(dy && z && mean && invstd && dz, "bn_backward: null argument");
+  CHECK_DTYPE(dtype);
+  return bn_backward(dtype, dy, y, z, rows, C, gamma, mean, invstd, relu, dz, dresidual, dgamma,
+                     dbeta, scratch, scratch_bytes, ST(stream));
+}
+
+int srt_maxpool3x3s2_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W,
+                         int C, void* stream) {
+  SRT_REQUIRE(x && y && argmax, "maxpool_fwd: null argument");
+  CHECK_DTYPE(dtype);
+  return maxpool_fwd(dtype, x, y, argmax, N, H, W, C, ST(stream));
+}
+int srt_maxpool3x3s2_bwd(int dtype, const void* dy, const uint8_t* argmax, void* dx, int N, int H,
+                         int W, int C, void* stream) {
+  SRT_REQUIRE(dy && dx && argmax, "maxpool_bwd: null argument");
+  CHECK_DTYPE(dtype);
+  return maxpool_bwd(dtype, dy, argmax, dx, N, H, W, C, ST(stream));
+}
+int srt_avgpool_fwd(int dtype, const void* x, void* y, int N, int HW, int C, void* stream) {
+  SRT_REQUIRE(x && y, "avgpool_fwd: null argument");
+  CHECK_DTYPE(dtype);
+  return avgpool_fwd(dtype, x, y, N, HW, C, ST(stream));
+}
+int srt_avgpool_bwd(int dtype, const void* dy, void* dx, int N, int HW, int C, void* stream) {
+  SRT_REQUIRE(dy && dx, "avgpool_bwd: null argument");
+  CHECK_DTYPE(dtype);
+  return avgpool_bwd(dtype, dy, dx, N, HW, C, ST(stream));
+}
+
+int srt_softmax_ce(int dtype, const void* logits, const int64_t* labels, int B, int classes,
+                   float grad_scale, float* row_loss, void* dlogits, void* stream) {
+  SRT_REQUIRE(logits && labels, "softmax_ce: null argument");
+  CHECK_DTYPE(dtype);
+  return softmax_ce(dtype, logits, labels, B, classes, grad_scale, row_loss, dlogits, ST(stream));
+}
+int srt_sum_f32(const float* v, int n, float* out, int accumulate, void* stream) {
+  SRT_REQUIRE(v && out && n >= 0, "sum_f32: bad argument");
+  return sum_f32(v, n, out, accumulate, ST(stream));
+}
+int srt_colsum(int dtype, const void* dy, int64_t rows, int K, float* out, void* stream) {
+  SRT_REQUIRE(dy && out, "colsum: null argument");
+  CHECK_DTYPE(dtype);
+  return colsum(dtype, dy, rows, K, out, ST(stream));
+}
+
+int srt_sgd_momentum(float* p, const float* g, float* m, void* p_bf16, int64_t n, float lr,
+                     float mu, float wd, int first_step, void* stream) {
+  SRT_REQUIRE(p && g && m && n >= 0, "sgd_momentum: bad argument");
+  return sgd_momentum(p, g, m, p_bf16, n, lr, mu, wd, first_step, ST(stream));
+}
+int srt_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, int64_t n, float lr,
+              float beta1, float beta2, float eps, float wd, int step, void* stream) {
+  SRT_REQUIRE(p && g && m && v && n >= 0, "adamw: bad argument");
+  return adamw(p, g, m, v, p_bf16, n, lr, beta1, beta2, eps, wd, step, ST(stream));
+}
+int srt_grad_accumulate(float* acc, float* g, int64_t n, void* stream) {
+  SRT_REQUIRE(acc && g && n >= 0, "grad_accumulate: bad argument");
+  return grad_accumulate(acc, g, n, ST(stream));
+}
+
+int srt_nchw_to_nhwc(int dtype, const float* src, void* dst, int N, int C, int H, int W, int Cpad,
+                     void* stream) {
+  SRT_REQUIRE(src && dst, "nchw_to_nhwc: null argument");
+  CHECK_DTYPE(dtype);
+  return nchw_to_nhwc(dtype, src, dst, N, C, H, W, Cpad, ST(stream));
+}
+int srt_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream) {
+  SRT_REQUIRE(src && dst && n >= 0, "cast: bad argument");
+  return cast_f32_to_bf16(src, dst, n, ST(stream));
+}
+int srt_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream) {
+  SRT_REQUIRE(src && dst && n >= 0, "cast: bad argument");
+  return cast_bf16_to_f32(src, dst, n, ST(stream));
+}
+
+int srt_set_sm_mask(const uint64_t mask[3]) {
+  SRT_REQUIRE(mask != nullptr, "set_sm_mask: null mask");
+  SRT_REQUIRE((mask[0] | mask[1] | mask[2]) != 0, "set_sm_mask: mask disables every SM");
+  SmMask m = {{mask[0], mask[1], mask[2]}};
+  set_current_sm_mask(m);
+  return SRT_OK;
+}
+int srt_get_sm_mask(uint64_t mask[3]) {
+  SRT_REQUIRE(mask != nullptr, "get_sm_mask: null mask");
+  SmMask m = current_sm_mask();
+  mask[0] = m.w[0]; mask[1] = m.w[1]; mask[2] = m.w[2];
+  return SRT_OK;
+}
+
+int srt_tc_status(int* status) {
+  SRT_REQUIRE(status != nullptr, "tc_status: null argument");
+  return tc_status_fetch(status);
+}
+int srt_debug_force_gather(int on) {
+  tc_set_force_gather(on);
+  return SRT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+// Shared device/host helpers for the sm_100a kernel library.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/sirius_b200.h"
+
+namespace srt {
+
+// Thread-local last-error text surfaced through srt_last_error().
+void set_error(const char* fmt, ...);
+
+#define SRT_CHECK_CUDA(expr)                                                        \
+  do {                                                                              \
+    cudaError_t _e = (expr);                                                        \
+    if (_e != cudaSuccess) {                                                        \
+      ::srt::set_error("%s:%d %s -> %s", __FILE__, __LINE__, #expr,                 \
+                       cudaGetErrorString(_e));                                     \
+      return SRT_ERR_CUDA;                                                          \
+    }                                                                               \
+  } while (0)
+
+#define SRT_REQUIRE(cond, ...)                                                      \
+  do {                                                                              \
+    if (!(cond)) {                                                                  \
+      ::srt::set_error(__VA_ARGS__);                                                \
+      return SRT_ERR_INVALID;                                                       \
+    }                                                                               \
+  } while (0)
+
+#define SRT_LAUNCH_CHECK()                                                          \
+  do {                                                                              \
+    cudaError_t _e = cudaGetLastError();                                            \
+    if (_e != cudaSuccess) {                                                        \
+      ::srt::set_error("%s:%d launch -> %s", __FILE__, __LINE__,                    \
+                       cudaGetErrorString(_e));                                     \
+      return SRT_ERR_CUDA;                                                          \
+    }                                                                               \
+  } while (0)
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
+
+int sm_count();  // SM count of the current device (cached)
+
+// ---- element type traits ---------------------------------------------------------------
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> {
+  static constexpr int kVec = 4;  // elements per 16-byte vector
+  __device__ static inline float to_f(float v) { return v; }
+  __device__ static inline float from_f(float v) { return v; }
+};
+template <> struct ElemTraits<__nv_bfloat16> {
+  static constexpr int kVec = 8;
+  __device__ static inline float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static inline __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// 16-byte vector of T, loaded/stored in one transaction and unpacked to floats.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  float4 raw;
+  __device__ inline void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+  __device__ inline void store(float* p) const { *reinterpret_cast<float4*>(p) = raw; }
+  __device__ inline void unpack(float (&f)[4]) const { f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w; }
+  __device__ inline void pack(const float (&f)[4]) { raw = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ inline void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ inline void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ inline void unpack(float (&f)[8]) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ inline void pack(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    raw = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// ---- allowed-SM mask ---------------------------------------------------------------------
+// Bit i set = SM i may run training CTAs. Passed by value to persistent kernels, which read
+// %smid and retire at once when their SM is not allowed.
+struct SmMask {
+  uint64_t w[3];
+};
+__device__ inline uint32_t smid() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+__device__ inline bool sm_allowed(const SmMask& m) {
+  uint32_t s = smid();
+  return (m.w[(s >> 6) % 3] >> (s & 63)) & 1ull;
+}
+SmMask current_sm_mask();          // process-wide mask (all ones by default)
+void set_current_sm_mask(const SmMask& m);
+
+}  // namespace srt

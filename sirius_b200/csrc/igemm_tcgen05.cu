@@ -1,0 +1,613 @@
+// bf16 implicit-GEMM convolution on the sm_100a tensor cores.
+//
+// Two warp-specialised kernels, both 192 threads per CTA and one 128-row output tile per CTA:
+//
+//   igemm_fwd_kernel   fprop and dgrad.  D[m][n] = sum_k A(m,k) B[n][k]
+//       A: 128 output positions x 64 reduction elements per stage, gathered from the NHWC source
+//          with 16-byte cp.async (zero-fill outside the image) straight into the 128-byte-swizzled
+//          K-major layout tcgen05.mma reads; for 1x1 stride-1 filters the tile is a plain matrix
+//          block and comes by TMA instead.
+//       B: BN filters x 64 reduction elements per stage by TMA (K-major, 128-byte swizzle).
+//   igemm_wgrad_kernel  filter gradient.  dW[k][j] = sum_pix dy[pix][k] X(pix,j)
+//       A: dy block, 64 pixels x 128 filters per stage by TMA (MN-major, two 64-wide boxes).
+//       B: 64 pixels x BN gathered input channels per stage by cp.async (MN-major).
+//       The pixel range is split across blockIdx.z; partial sums go to scratch and are reduced
+//       in a fixed order afterwards.
+//
+// Warp roles: warps 0-3 gather during the main loop and then run the epilogue (warp w owns TMEM
+// lanes 32w..32w+31), warp 4 lane 0 issues TMA, warp 5 allocates tensor memory and its lane 0
+// issues tcgen05.mma. A ring of NS shared-memory stages is handed over with mbarriers; the fp32
+// accumulator lives in BN columns of tensor memory. No cluster launch and no multicast: every
+// CTA loads its own tiles. Every wait is bounded and reports through a status word.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "conv_geom.cuh"
+#include "ptx.cuh"
+
+namespace srt {
+
+namespace {
+
+using namespace ptx;
+using bf16 = __nv_bfloat16;
+
+constexpr int BM = 128;       // output rows per CTA (= TMEM lanes)
+constexpr int BK = 64;        // reduction elements per stage (one 128-byte swizzle row of bf16)
+constexpr int NTHREADS = 192;
+constexpr int NPROD = 128;    // gather / epilogue threads
+constexpr int LAG = 2;        // cp.async groups kept in flight per producer thread
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+
+__device__ int g_tc_status;  // 0 = ok; otherwise the code of the first wait that gave up
+
+enum WaitCode { W_PROD_EMPTY = 1, W_TMA_EMPTY = 2, W_MMA_FULL = 3, W_EPI_TMEM = 4 };
+
+struct FwdParams {
+  GatherGeom g;
+  const bf16* src;
+  bf16* D;
+  const float* bias;
+  const bf16* addend;
+  int k_blocks;
+  int a_tma;
+  int* status;
+};
+
+struct WgradParams {
+  GatherGeom g;  // fprop geometry: rows = output pixels, gather from x
+  const bf16* x;
+  float* out;          // [splits][Kout][J] partials, or dW itself when splits == 1
+  int pix_per_split;   // multiple of 64
+  int* status;
+};
+
+struct SmemLayout {
+  uint8_t* a;
+  uint8_t* b;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* tmem_full;
+  uint32_t* tmem_ptr;
+};
+
+template <int NS, int B_STAGE_BYTES>
+__device__ __forceinline__ SmemLayout carve_smem(uint8_t* raw) {
+  SmemLayout s;
+  uint8_t* base = (uint8_t*)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
+  s.a = base;
+  s.b = base + NS * A_STAGE_BYTES;
+  uint8_t* tail = s.b + NS * B_STAGE_BYTES;
+  s.full = (uint64_t*)tail;
+  s.empty = s.full + NS;
+  s.tmem_full = s.empty + NS;
+  s.tmem_ptr = (uint32_t*)(s.tmem_full + 1);
+  return s;
+}
+
+template <int NS, int B_STAGE_BYTES>
+constexpr size_t smem_bytes() {
+  return 1024 + (size_t)NS * (A_STAGE_BYTES + B_STAGE_BYTES) + (2 * NS + 1) * 8 + 16;
+}
+
+// Issue the NI 16-byte copies of one stage for this producer thread, then hand over the stage
+// that was issued LAG iterations ago (its copies have landed once at most LAG groups are pending).
+template <int NS>
+__device__ __forceinline__ void producer_handover(int kb, uint64_t* full) {
+  cp_async_commit();
+  if (kb >= LAG) {
+    cp_async_wait<LAG>();
+    fence_proxy_async_smem();
+    mbar_arrive(smem_u32(&full[(kb - LAG) % NS]));
+  }
+}
+template <int NS>
+__device__ __forceinline__ void producer_drain(int issued, uint64_t* full) {
+  cp_async_wait<0>();
+  fence_proxy_async_smem();
+  for (int kb = issued > LAG ? issued - LAG : 0; kb < issued; ++kb)
+    mbar_arrive(smem_u32(&full[kb % NS]));
+}
+
+// ------------------------------------------------------------------------------------------
+template <int BN, int NS>
+__global__ void __launch_bounds__(NTHREADS)
+igemm_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_a) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout sm = carve_smem<NS, B_STAGE_BYTES>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const GatherGeom& g = p.g;
+  const int nkb = p.k_blocks;
+
+  if (tid == 0) {
+    const uint32_t full_count = p.a_tma ? 1u : (uint32_t)(NPROD + 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(smem_u32(&sm.full[s]), full_count);
+      mbar_init(smem_u32(&sm.empty[s]), 1);
+    }
+    mbar_init(smem_u32(sm.tmem_full), 1);
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmap_b);
+    if (p.a_tma) tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(sm.tmem_ptr), BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+
+  if (warp < 4) {
+    // ---------------- gather producers ----------------
+    if (!p.a_tma) {
+      const int j = tid & 7, r0 = tid >> 3;
+      const uint32_t swz = (uint32_t)((j ^ (r0 & 7)) << 4);
+      int pixb[8], ih0[8], iw0[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m0 + r0 + 16 * i;
+        if (m < g.M) {
+          RowCoord rc = decode_row(g, m);
+          pixb[i] = rc.n * g.src_h * g.src_w;
+          ih0[i] = g.dgrad ? rc.oh + g.pad : rc.oh * g.stride - g.pad;
+          iw0[i] = g.dgrad ? rc.ow + g.pad : rc.ow * g.stride - g.pad;
+        } else {
+          pixb[i] = 0;
+          ih0[i] = g.dgrad ? -(1 << 20) : -(1 << 20);
+          iw0[i] = 0;
+        }
+      }
+      int issued = 0;
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % NS;
+        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) { ok = false; break; }
+        const int kk = kb * BK + j * 8;
+        const bool k_ok = kk < g.Kg;
+        const int tap = kk / g.src_c, c = kk - tap * g.src_c;
+        const int r = tap / g.S, sf = tap - r * g.S;
+        const uint32_t dst0 = smem_u32(sm.a + s * A_STAGE_BYTES) + (uint32_t)r0 * 128u + swz;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          int ih, iw;
+          bool v = k_ok;
+          if (!g.dgrad) {
+            ih = ih0[i] + r;
+            iw = iw0[i] + sf;
+          } else {
+            const int th = ih0[i] - r, tw = iw0[i] - sf;
+            v = v && th >= 0 && tw >= 0;
+            if (g.stride > 1) {
+              v = v && (th % g.stride == 0) && (tw % g.stride == 0);
+              ih = th / g.stride;
+              iw = tw / g.stride;
+            } else {
+              ih = th;
+              iw = tw;
+            }
+          }
+          v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
+          const bf16* ptr = v ? p.src + ((size_t)(pixb[i] + ih * g.src_w + iw) * g.src_c + c) : p.src;
+          cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
+        }
+        producer_handover<NS>(kb, sm.full);
+        issued = kb + 1;
+      }
+      (void)ok;
+      producer_drain<NS>(issued, sm.full);
+    }
+    // ---------------- epilogue ----------------
+    const bool ready = mbar_wait(smem_u32(sm.tmem_full), 0u, p.status, W_EPI_TMEM);
+    tc_fence_after_sync();
+    const int m = m0 + warp * 32 + lane;
+#pragma unroll 1
+    for (int cb = 0; cb < BN / 32; ++cb) {
+      uint32_t acc[32];
+      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 32), acc);
+      tmem_ld_wait();
+      if (ready && m < g.M) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = n0 + cb * 32 + v * 8;
+          if (col < g.Nout) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
+            if (p.bias) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
+            }
+            const size_t o = (size_t)m * g.Nout + col;
+            if (p.addend) {
+              Vec16<bf16> av;
+              av.load(p.addend + o);
+              float af[8];
+              av.unpack(af);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] += af[e];
+            }
+            Vec16<bf16> ov;
+            ov.pack(f);
+            ov.store(p.D + o);
+          }
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)B_STAGE_BYTES + (p.a_tma ? (uint32_t)A_STAGE_BYTES : 0u);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % NS;
+        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
+        const uint32_t bar = smem_u32(&sm.full[s]);
+        mbar_arrive_expect_tx(bar, bytes);
+        tma_load_2d(smem_u32(sm.b + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
+        if (p.a_tma) tma_load_2d(smem_u32(sm.a + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
+      }
+    }
+  } else {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % NS;
+        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.full[s]), ph, p.status, W_MMA_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a0 = smem_u32(sm.a + s * A_STAGE_BYTES);
+        const uint32_t b0 = smem_u32(sm.b + s * B_STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t ad = make_smem_desc_sw128(a0 + k * 32, 0, 1024);
+          const uint64_t bd = make_smem_desc_sw128(b0 + k * 32, 0, 1024);
+          umma_bf16(tmem_base, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.empty[s]));
+      }
+      umma_commit(smem_u32(sm.tmem_full));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+template <int BN, int NS>
+__global__ void __launch_bounds__(NTHREADS)
+igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap_dy) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;  // BN/64 blocks of [64 pixels][128 bytes]
+  constexpr int CPR = BN / 8;                 // 16-byte chunks per pixel row
+  constexpr int RSTEP = NPROD / CPR;          // pixel rows covered per pass
+  constexpr int NI = BK / RSTEP;              // copies per thread per stage
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout sm = carve_smem<NS, B_STAGE_BYTES>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const GatherGeom& g = p.g;
+  const int Kout = g.Nout, J = g.Kg;
+  const int j0 = blockIdx.x * BN, ko0 = blockIdx.y * BM;
+  const int pbeg = blockIdx.z * p.pix_per_split;
+  const int pend = min(g.M, pbeg + p.pix_per_split);
+  const int nkb = (pend - pbeg + BK - 1) / BK;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(smem_u32(&sm.full[s]), (uint32_t)(NPROD + 1));
+      mbar_init(smem_u32(&sm.empty[s]), 1);
+    }
+    mbar_init(smem_u32(sm.tmem_full), 1);
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) tma_prefetch_desc(&tmap_dy);
+  if (warp == 5) {
+    tmem_alloc(smem_u32(sm.tmem_ptr), BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+
+  if (warp < 4) {
+    // ---------------- gather producers: x(pix, j) for 64 pixels x BN columns ----------------
+    const int cj = tid % CPR, r0 = tid / CPR;
+    const int jj = j0 + cj * 8;
+    const bool j_ok = jj < J;
+    const int tap = jj / g.src_c, c = jj - tap * g.src_c;
+    const int r = tap / g.S, sf = tap - r * g.S;
+    const int hw = g.out_h * g.out_w;
+    // destination of row r0 in block cj/8; later rows step RSTEP*128 bytes (RSTEP % 8 == 0)
+    const uint32_t dst_off = (uint32_t)(cj >> 3) * 8192u + (uint32_t)r0 * 128u +
+                             (uint32_t)(((cj & 7) ^ (r0 & 7)) << 4);
+    int issued = 0;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int s = kb % NS;
+      const uint32_t ph = (uint32_t)(kb / NS) & 1u;
+      if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) break;
+      const uint32_t dst0 = smem_u32(sm.b + s * B_STAGE_BYTES) + dst_off;
+      const int pix0 = pbeg + kb * BK + r0;
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {
+        const int pix = pix0 + i * RSTEP;
+        bool v = j_ok && pix < pend;
+        const int n = pix / hw;
+        const int rem = pix - n * hw;
+        const int oh = rem / g.out_w, ow = rem - oh * g.out_w;
+        const int ih = oh * g.stride - g.pad + r, iw = ow * g.stride - g.pad + sf;
+        v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
+        const bf16* ptr =
+            v ? p.x + (((size_t)n * g.src_h + ih) * g.src_w + iw) * g.src_c + c : p.x;
+        cp_async_16(dst0 + (uint32_t)i * (uint32_t)(RSTEP * 128), ptr, v ? 16u : 0u);
+      }
+      producer_handover<NS>(kb, sm.full);
+      issued = kb + 1;
+    }
+    producer_drain<NS>(issued, sm.full);
+
+    // ---------------- epilogue: fp32 partial tile ----------------
+    const bool ready = mbar_wait(smem_u32(sm.tmem_full), 0u, p.status, W_EPI_TMEM);
+    tc_fence_after_sync();
+    const int ko = ko0 + warp * 32 + lane;
+    float* out = p.out + (size_t)blockIdx.z * Kout * J;
+#pragma unroll 1
+    for (int cb = 0; cb < BN / 32; ++cb) {
+      uint32_t acc[32];
+      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 32), acc);
+      tmem_ld_wait();
+      if (ready && ko < Kout) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int col = j0 + cb * 32 + v * 4;
+          if (col < J) {
+            float4 o = make_float4(__uint_as_float(acc[v * 4]), __uint_as_float(acc[v * 4 + 1]),
+                                   __uint_as_float(acc[v * 4 + 2]), __uint_as_float(acc[v * 4 + 3]));
+            *reinterpret_cast<float4*>(out + (size_t)ko * J + col) = o;
+          }
+        }
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % NS;
+        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
+        const uint32_t bar = smem_u32(&sm.full[s]);
+        mbar_arrive_expect_tx(bar, (uint32_t)A_STAGE_BYTES);
+        const uint32_t dst = smem_u32(sm.a + s * A_STAGE_BYTES);
+        const int pix0 = pbeg + kb * BK;
+        tma_load_2d(dst, &tmap_dy, bar, ko0, pix0);
+        tma_load_2d(dst + 8192u, &tmap_dy, bar, ko0 + 64, pix0);
+      }
+    }
+  } else {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 1, 1);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % NS;
+        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.full[s]), ph, p.status, W_MMA_FULL)) break;
+        tc_fence_after_sync();
+        const uint32_t a0 = smem_u32(sm.a + s * A_STAGE_BYTES);
+        const uint32_t b0 = smem_u32(sm.b + s * B_STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          // 16 pixels = two groups of 8 K-rows (1024 bytes each); 64-wide M/N blocks 8192 apart
+          const uint64_t ad = make_smem_desc_sw128(a0 + k * 2048, 8192, 1024);
+          const uint64_t bd = make_smem_desc_sw128(b0 + k * 2048, 8192, 1024);
+          umma_bf16(tmem_base, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.empty[s]));
+      }
+      umma_commit(smem_u32(sm.tmem_full));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+// 2-D bf16 row-major matrix [rows][cols] (cols contiguous), box = 64 cols x box_rows, 128B swizzle.
+int make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return SRT_ERR_CUDA;
+  }
+  SRT_REQUIRE(((uintptr_t)base & 15) == 0 && (cols * 2) % 16 == 0,
+              "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SRT_ERR_CUDA;
+  }
+  return SRT_OK;
+}
+
+int* status_ptr() {
+  static int* ptr = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tc_status) == cudaSuccess) ptr = (int*)p;
+  });
+  return ptr;
+}
+
+template <int BN, int NS>
+int launch_fwd(const FwdParams& p, const CUtensorMap& tb, const CUtensorMap& ta, cudaStream_t st) {
+  constexpr size_t smem = smem_bytes<NS, BN * BK * 2>();
+  static bool configured = false;
+  if (!configured) {
+    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_fwd_kernel<BN, NS>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid(ceil_div(p.g.M, BM), ceil_div(p.g.Nout, BN));
+  igemm_fwd_kernel<BN, NS><<<grid, NTHREADS, smem, st>>>(p, tb, ta);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+template <int BN, int NS>
+int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, int splits, cudaStream_t st) {
+  constexpr size_t smem = smem_bytes<NS, BN * BK * 2>();
+  static bool configured = false;
+  if (!configured) {
+    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_wgrad_kernel<BN, NS>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid(ceil_div(p.g.Kg, BN), ceil_div(p.g.Nout, BM), splits);
+  igemm_wgrad_kernel<BN, NS><<<grid, NTHREADS, smem, st>>>(p, tdy);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+struct WgradPlan {
+  int bn, splits, pix_per_split;
+};
+
+WgradPlan plan_wgrad(const GatherGeom& g) {
+  WgradPlan w;
+  w.bn = g.Kg <= 64 ? 64 : 128;
+  const int tiles = ceil_div(g.Kg, w.bn) * ceil_div(g.Nout, BM);
+  int want = ceil_div(2 * sm_count(), tiles);
+  const int max_by_pix = ceil_div(g.M, 4 * BK);
+  int splits = want < max_by_pix ? want : max_by_pix;
+  if (splits < 1) splits = 1;
+  if (splits > 128) splits = 128;
+  w.pix_per_split = ceil_div(ceil_div(g.M, splits), BK) * BK;
+  w.splits = ceil_div(g.M, w.pix_per_split);
+  return w;
+}
+
+}  // namespace
+
+// Reads and clears the device status word of the tcgen05 kernels (synchronises the device).
+int tc_status_fetch(int* out) {
+  int* sp = status_ptr();
+  SRT_REQUIRE(sp != nullptr, "tcgen05 status word unavailable");
+  SRT_CHECK_CUDA(cudaDeviceSynchronize());
+  SRT_CHECK_CUDA(cudaMemcpy(out, sp, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*out != 0) {
+    int zero = 0;
+    SRT_CHECK_CUDA(cudaMemcpy(sp, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  }
+  return SRT_OK;
+}
+
+static int g_force_gather = 0;  // test hook: route 1x1 stride-1 problems through the gather path
+void tc_set_force_gather(int v) { g_force_gather = v; }
+
+int conv_gather_gemm_tc(const GatherGeom& g, const void* src, const void* Bm, void* D,
+                        const srt_conv_epilogue* ep, cudaStream_t st) {
+  SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
+              "tcgen05 conv: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
+  SRT_REQUIRE(((uintptr_t)src & 15) == 0 && ((uintptr_t)D & 15) == 0, "tcgen05 conv: unaligned tensor");
+  FwdParams p;
+  p.g = g;
+  p.src = (const bf16*)src;
+  p.D = (bf16*)D;
+  p.bias = ep ? ep->bias : nullptr;
+  p.addend = ep ? (const bf16*)ep->addend : nullptr;
+  p.k_blocks = ceil_div(g.Kg, BK);
+  p.status = status_ptr();
+  SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
+  const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
+  p.a_tma = (plain && !g_force_gather) ? 1 : 0;
+
+  const int bn = g.Nout <= 64 ? 64 : 128;
+  CUtensorMap tb, ta;
+  int rc = make_tmap_2d(&tb, Bm, (uint64_t)g.Nout, (uint64_t)g.Kg, (uint32_t)bn);
+  if (rc != SRT_OK) return rc;
+  if (p.a_tma) {
+    rc = make_tmap_2d(&ta, src, (uint64_t)g.M, (uint64_t)g.Kg, (uint32_t)BM);
+    if (rc != SRT_OK) return rc;
+  } else {
+    ta = tb;
+  }
+  if (bn == 64) return launch_fwd<64, 4>(p, tb, ta, st);
+  return launch_fwd<128, 3>(p, tb, ta, st);
+}
+
+size_t conv_wgrad_tc_scratch_bytes(const GatherGeom& g) {
+  WgradPlan w = plan_wgrad(g);
+  return w.splits > 1 ? (size_t)w.splits * g.Nout * g.Kg * sizeof(float) : 0;
+}
+
+int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st) {
+  SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
+              "tcgen05 wgrad: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
+  WgradPlan w = plan_wgrad(g);
+  const size_t need = conv_wgrad_tc_scratch_bytes(g);
+  SRT_REQUIRE(scratch_bytes >= need && (need == 0 || scratch != nullptr),
+              "tcgen05 wgrad: scratch too small (%zu < %zu)", scratch_bytes, need);
+  WgradParams p;
+  p.g = g;
+  p.x = (const bf16*)x;
+  p.out = w.splits > 1 ? (float*)scratch : dw;
+  p.pix_per_split = w.pix_per_split;
+  p.status = status_ptr();
+  SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
+  CUtensorMap tdy;
+  int rc = make_tmap_2d(&tdy, dy, (uint64_t)g.M, (uint64_t)g.Nout, 64);
+  if (rc != SRT_OK) return rc;
+  rc = w.bn == 64 ? launch_wgrad<64, 4>(p, tdy, w.splits, st)
+                  : launch_wgrad<128, 4>(p, tdy, w.splits, st);
+  if (rc != SRT_OK) return rc;
+  if (w.splits > 1) return launch_split_reduce(p.out, dw, (long long)g.Nout * g.Kg, w.splits, st);
+  return SRT_OK;
+}
+
+}  // namespace srt

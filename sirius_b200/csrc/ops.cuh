@@ -1,0 +1,49 @@
+// Internal C++ declarations of the kernel launchers (one per C-ABI compute entry point).
+#pragma once
+#include "common.cuh"
+#include "conv_geom.cuh"
+
+namespace srt {
+
+size_t bn_scratch_bytes(int64_t rows, int C);
+int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, const float* beta,
+             float eps, float momentum, float* rm, float* rv, float* mean, float* invstd,
+             float* scale, float* shift, void* scratch, size_t scratch_bytes, cudaStream_t st);
+int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
+             const float* scale, const float* shift, int relu, cudaStream_t st);
+int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
+                const float* gamma, const float* mean, const float* invstd, int relu, void* dz,
+                void* dres, float* dgamma, float* dbeta, void* scratch, size_t scratch_bytes,
+                cudaStream_t st);
+
+int maxpool_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W, int C,
+                cudaStream_t st);
+int maxpool_bwd(int dtype, const void* dy, const uint8_t* argmax, void* dx, int N, int H, int W,
+                int C, cudaStream_t st);
+int avgpool_fwd(int dtype, const void* x, void* y, int N, int HW, int C, cudaStream_t st);
+int avgpool_bwd(int dtype, const void* dy, void* dx, int N, int HW, int C, cudaStream_t st);
+int softmax_ce(int dtype, const void* logits, const int64_t* labels, int B, int classes,
+               float grad_scale, float* row_loss, void* dlogits, cudaStream_t st);
+int sum_f32(const float* v, int n, float* out, int accumulate, cudaStream_t st);
+int colsum(int dtype, const void* dy, int64_t rows, int K, float* out, cudaStream_t st);
+int sgd_momentum(float* p, const float* g, float* m, void* pb, int64_t n, float lr, float mu,
+                 float wd, int first_step, cudaStream_t st);
+int adamw(float* p, const float* g, float* m, float* v, void* pb, int64_t n, float lr, float b1,
+          float b2, float eps, float wd, int step, cudaStream_t st);
+int grad_accumulate(float* acc, float* g, int64_t n, cudaStream_t st);
+int nchw_to_nhwc(int dtype, const float* src, void* dst, int N, int C, int H, int W, int Cpad,
+                 cudaStream_t st);
+int cast_f32_to_bf16(const float* s, void* d, int64_t n, cudaStream_t st);
+int cast_bf16_to_f32(const void* s, float* d, int64_t n, cudaStream_t st);
+int filter_transpose(int dtype, const void* w, void* wt, int K, int RS, int C, cudaStream_t st);
+
+// Convolution front ends: validate, pick the kernel family, launch.
+int conv_fprop(const srt_conv_desc& d, int dtype, int impl, const void* x, const void* w, void* y,
+               const srt_conv_epilogue* ep, cudaStream_t st);
+int conv_dgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* wt,
+               void* dx, const srt_conv_epilogue* ep, cudaStream_t st);
+int conv_wgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* x,
+               float* dw, void* scratch, size_t scratch_bytes, cudaStream_t st);
+size_t conv_wgrad_scratch_bytes(const srt_conv_desc& d, int dtype, int impl);
+
+}  // namespace srt

@@ -1,0 +1,259 @@
+"""Per-operator parity on the GPU: every kernel family, called through the C ABI, against the
+PyTorch CPU fp32 operator the reference's training scripts execute (train/resnet152.py:86-89).
+
+fp32 kernels: tight tolerance. bf16 kernels: inputs are rounded to bf16 first so the only
+differences are accumulation order and the final rounding to bf16.
+"""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+from sirius_b200 import ops
+from sirius_b200._lib import IMPL_SIMT, IMPL_TCGEN05, IMPL_AUTO, lib
+
+DEV = "cuda:0"
+
+# (name, N, H, W, C, K, R, S, stride, pad)
+CONV_CASES = [
+    ("1x1_s1_c256_k64", 2, 14, 14, 256, 64, 1, 1, 1, 0),
+    ("1x1_s1_c64_k256", 3, 14, 14, 64, 256, 1, 1, 1, 0),
+    ("3x3_s1_c64_k64", 2, 14, 14, 64, 64, 3, 3, 1, 1),
+    ("3x3_s1_c128_k128", 2, 14, 14, 128, 128, 3, 3, 1, 1),
+    ("3x3_s2_c128_k128", 2, 28, 28, 128, 128, 3, 3, 2, 1),
+    ("1x1_s2_c256_k512", 2, 28, 28, 256, 512, 1, 1, 2, 0),
+    ("7x7_s2_c8_k64_stem", 2, 64, 64, 8, 64, 7, 7, 2, 3),
+    ("fc_2048_1000", 64, 1, 1, 2048, 1000, 1, 1, 1, 0),
+    ("tail_7x7_c512_k512", 1, 7, 7, 512, 512, 3, 3, 1, 1),
+    ("odd_c24_k40", 2, 9, 11, 24, 40, 3, 3, 1, 1),
+]
+IDS = [c[0] for c in CONV_CASES]
+
+
+def _mk(case, dtype, seed=0):
+    _, N, H, W, C, K, R, S, stride, pad = case
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(N, H, W, C, generator=g)
+    w = torch.randn(K, R, S, C, generator=g) * (1.0 / (R * S * C) ** 0.5)
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    dy = torch.randn(N, P, Q, K, generator=g)
+    if dtype == torch.bfloat16:
+        x, w, dy = (t.to(torch.bfloat16).float() for t in (x, w, dy))
+    return x, w, dy
+
+
+def _ref(x, w, dy, stride, pad):
+    xn = x.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    wn = w.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    y = F.conv2d(xn, wn, stride=stride, padding=pad)
+    y.backward(dy.permute(0, 3, 1, 2).contiguous())
+    return (y.detach().permute(0, 2, 3, 1).contiguous(),
+            xn.grad.permute(0, 2, 3, 1).contiguous(),
+            wn.grad.permute(0, 2, 3, 1).contiguous())
+
+
+def _err(a, b):
+    return ((a.float().cpu() - b).abs().max() / (b.abs().max() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
+def test_conv_fp32_simt(case):
+    stride, pad = case[8], case[9]
+    x, w, dy = _mk(case, torch.float32)
+    y_ref, dx_ref, dw_ref = _ref(x, w, dy, stride, pad)
+    xd, wd, dyd = x.to(DEV), w.to(DEV), dy.to(DEV)
+    y = ops.conv_fprop(xd, wd, stride, pad)
+    dx = ops.conv_dgrad(dyd, ops.filter_transpose(wd), x.shape, stride, pad)
+    dw = ops.conv_wgrad(dyd, xd, case[6], case[7], stride, pad)
+    torch.cuda.synchronize()
+    assert _err(y, y_ref) < 2e-5
+    assert _err(dx, dx_ref) < 2e-5
+    assert _err(dw, dw_ref) < 2e-5
+
+
+@pytest.mark.parametrize("impl", [IMPL_SIMT, IMPL_TCGEN05], ids=["simt", "tcgen05"])
+@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
+def test_conv_bf16(case, impl):
+    stride, pad = case[8], case[9]
+    x, w, dy = _mk(case, torch.bfloat16)
+    y_ref, dx_ref, dw_ref = _ref(x, w, dy, stride, pad)
+    bf = torch.bfloat16
+    xd, wd, dyd = x.to(DEV, bf), w.to(DEV, bf), dy.to(DEV, bf)
+    y = ops.conv_fprop(xd, wd, stride, pad, impl=impl)
+    dx = ops.conv_dgrad(dyd, ops.filter_transpose(wd), x.shape, stride, pad, impl=impl)
+    dw = ops.conv_wgrad(dyd, xd, case[6], case[7], stride, pad, impl=impl)
+    torch.cuda.synchronize()
+    assert ops.tc_status() == 0
+    errs = (_err(y, y_ref), _err(dx, dx_ref), _err(dw, dw_ref))
+    print(case[0], "impl", impl, "rel-max errors y/dx/dw:", errs)
+    assert errs[0] < 1e-2 and errs[1] < 1e-2
+    assert errs[2] < 2e-3  # fp32 output
+
+
+def test_conv_tcgen05_gather_equals_tma():
+    """1x1 stride-1 problems take the TMA path for A; the gather path must agree bit for bit."""
+    case = CONV_CASES[0]
+    x, w, dy = _mk(case, torch.bfloat16)
+    bf = torch.bfloat16
+    xd, wd = x.to(DEV, bf), w.to(DEV, bf)
+    y_tma = ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05)
+    lib().srt_debug_force_gather(1)
+    try:
+        y_g = ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05)
+    finally:
+        lib().srt_debug_force_gather(0)
+    torch.cuda.synchronize()
+    assert ops.tc_status() == 0
+    assert torch.equal(y_tma, y_g)
+
+
+def test_conv_epilogue_bias_addend():
+    case = ("fc", 8, 1, 1, 256, 40, 1, 1, 1, 0)
+    for dtype, impl, tol in ((torch.float32, IMPL_AUTO, 2e-5), (torch.bfloat16, IMPL_TCGEN05, 1e-2)):
+        x, w, _ = _mk(case, dtype)
+        g = torch.Generator().manual_seed(5)
+        bias = torch.randn(40, generator=g)
+        add = torch.randn(8, 1, 1, 40, generator=g)
+        if dtype == torch.bfloat16:
+            add = add.to(dtype).float()
+        ref = (x.reshape(8, 256) @ w.reshape(40, 256).t() + bias).reshape(8, 1, 1, 40) + add
+        y = ops.conv_fprop(x.to(DEV, dtype), w.to(DEV, dtype), 1, 0, bias=bias.to(DEV),
+                           addend=add.to(DEV, dtype), impl=impl)
+        torch.cuda.synchronize()
+        assert _err(y, ref) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 14, 14, 64), (3, 7, 7, 2048), (2, 5, 5, 24)], ids=str)
+def test_batchnorm_fwd_bwd(dtype, shape):
+    g = torch.Generator().manual_seed(1)
+    C = shape[-1]
+    z = torch.randn(shape, generator=g) * 2 + 0.5
+    res = torch.randn(shape, generator=g)
+    dy = torch.randn(shape, generator=g)
+    gamma = torch.rand(C, generator=g) + 0.5
+    beta = torch.randn(C, generator=g)
+    if dtype == torch.bfloat16:
+        z, res, dy = (t.to(dtype).float() for t in (z, res, dy))
+    rm, rv = torch.zeros(C), torch.ones(C)
+    zn = z.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    resn = res.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    gp, bp = gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True)
+    rm_ref, rv_ref = rm.clone(), rv.clone()
+    out = F.relu(F.batch_norm(zn, rm_ref, rv_ref, gp, bp, True, 0.1, 1e-5) + resn)
+    out.backward(dy.permute(0, 3, 1, 2).contiguous())
+    y_ref = out.detach().permute(0, 2, 3, 1)
+    dz_ref = zn.grad.permute(0, 2, 3, 1)
+    dres_ref = resn.grad.permute(0, 2, 3, 1)
+
+    zd, resd, dyd = z.to(DEV, dtype), res.to(DEV, dtype), dy.to(DEV, dtype)
+    gd, bd, rmd, rvd = gamma.to(DEV), beta.to(DEV), rm.to(DEV), rv.to(DEV)
+    mean, invstd, scale, shift = ops.bn_stats(zd, gd, bd, rmd, rvd)
+    y = ops.bn_apply(zd, scale, shift, residual=resd, relu=True)
+    dz, dres, dgamma, dbeta = ops.bn_backward(dyd, y, zd, gd, mean, invstd, relu=True, want_dresidual=True)
+    torch.cuda.synchronize()
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    assert _err(rmd, rm_ref) < 1e-5 and _err(rvd, rv_ref) < 1e-5
+    assert _err(y, y_ref) < tol
+    if dtype == torch.float32:
+        assert _err(dz, dz_ref) < 1e-4
+        assert _err(dres, dres_ref) < 1e-6
+        assert _err(dgamma, gp.grad) < 1e-5 and _err(dbeta, bp.grad) < 1e-5
+    else:
+        # the ReLU mask comes from the bf16-rounded y; elements that round to 0 may flip, so
+        # compare the bulk statistics rather than every element
+        assert (dz.float().cpu() - dz_ref).abs().mean() / dz_ref.abs().mean() < 2e-2
+        assert _err(dgamma, gp.grad) < 2e-2 and _err(dbeta, bp.grad) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_pools(dtype):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 13, 16, 16, generator=g).clamp_min(0)  # zeros create ties like post-ReLU data
+    if dtype == torch.bfloat16:
+        x = x.to(dtype).float()
+    xn = x.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    y_ref = F.max_pool2d(xn, 3, 2, 1)
+    dy = torch.randn(y_ref.shape, generator=g)
+    if dtype == torch.bfloat16:
+        dy = dy.to(dtype).float()
+    y_ref.backward(dy)
+    xd = x.to(DEV, dtype)
+    y, arg = ops.maxpool_fwd(xd)
+    dx = ops.maxpool_bwd(dy.permute(0, 2, 3, 1).contiguous().to(DEV, dtype), arg, x.shape)
+    torch.cuda.synchronize()
+    assert torch.equal(y.float().cpu(), y_ref.detach().permute(0, 2, 3, 1))
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    assert _err(dx, xn.grad.permute(0, 2, 3, 1)) < tol
+
+    a = torch.randn(3, 7, 7, 64, generator=g)
+    if dtype == torch.bfloat16:
+        a = a.to(dtype).float()
+    ya = ops.avgpool_fwd(a.to(DEV, dtype))
+    da = ops.avgpool_bwd(ya, 49)
+    torch.cuda.synchronize()
+    assert _err(ya, a.mean(dim=(1, 2))) < (1e-6 if dtype == torch.float32 else 1e-2)
+    assert _err(da.reshape(3, 7, 7, 64), (ya.float().cpu() / 49)[:, None, None, :].expand(3, 7, 7, 64)) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_softmax_ce_and_colsum(dtype):
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(16, 1000, generator=g) * 3
+    if dtype == torch.bfloat16:
+        logits = logits.to(dtype).float()
+    labels = torch.randint(0, 1000, (16,), generator=g)
+    lr = logits.clone().requires_grad_(True)
+    loss = F.cross_entropy(lr, labels)
+    loss.backward()
+    row_loss, dlogits = ops.softmax_ce(logits.to(DEV, dtype), labels.to(DEV), 1.0 / 16)
+    cs = ops.colsum(dlogits)
+    torch.cuda.synchronize()
+    assert abs(row_loss.sum().item() - loss.item()) < 1e-5 * max(1, abs(loss.item()))
+    assert _err(dlogits, lr.grad) < (1e-6 if dtype == torch.float32 else 1e-2)
+    assert _err(cs, dlogits.float().cpu().sum(0)) < 1e-5
+
+
+def test_optimizers_match_torch():
+    g = torch.Generator().manual_seed(4)
+    n = 100003
+    p0 = torch.randn(n, generator=g)
+    grads = [torch.randn(n, generator=g) for _ in range(3)]
+    pr = p0.clone().requires_grad_(True)
+    opt = torch.optim.SGD([pr], lr=0.1, momentum=0.9, weight_decay=1e-4)
+    pd, md = p0.to(DEV), torch.zeros(n, device=DEV)
+    pb = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+    for i, gr in enumerate(grads):
+        pr.grad = gr.clone()
+        opt.step()
+        ops.sgd_momentum(pd, gr.to(DEV), md, 0.1, 0.9, 1e-4, i == 0, p_bf16=pb)
+    torch.cuda.synchronize()
+    assert _err(pd, pr.detach()) < 1e-6
+    assert torch.equal(pb.cpu(), pd.cpu().to(torch.bfloat16))
+
+    pr = p0.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([pr], lr=1e-3)
+    pd, md, vd = p0.to(DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    for i, gr in enumerate(grads):
+        pr.grad = gr.clone()
+        opt.step()
+        ops.adamw(pd, gr.to(DEV), md, vd, 1e-3, 0.9, 0.999, 1e-8, 0.01, i + 1)
+    torch.cuda.synchronize()
+    assert _err(pd, pr.detach()) < 1e-5
+
+    acc, gg = torch.zeros(n, device=DEV), grads[0].to(DEV)
+    ops.grad_accumulate(acc, gg)
+    torch.cuda.synchronize()
+    assert torch.equal(acc.cpu(), grads[0]) and gg.abs().max().item() == 0.0
+
+
+def test_nchw_to_nhwc():
+    g = torch.Generator().manual_seed(6)
+    src = torch.randn(2, 3, 9, 7, generator=g)
+    out = ops.nchw_to_nhwc(src.to(DEV), torch.float32, 8)
+    torch.cuda.synchronize()
+    ref = torch.zeros(2, 9, 7, 8)
+    ref[..., :3] = src.permute(0, 2, 3, 1)
+    assert torch.equal(out.cpu(), ref)

@@ -97,10 +97,14 @@ int srt_avgpool_bwd(int dtype, const void* dy, void* dx, int N, int HW, int C, v
 
 /* ---- loss (replaces nn.CrossEntropyLoss, train/resnet152.py:26,87, and the loss scaling of
  *      MicroBatchManager.scale_loss, pytorch/torch_col/dynamic_batch.py:112-120) -------------- */
-/* loss_sum[0] += sum_i CE(logits[i], labels[i]) * grad_scale ; dlogits = (softmax - onehot) *
- * grad_scale. With grad_scale = 1/global_batch the accumulated gradients equal the global mean. */
+/* row_loss[i] = CE(logits[i], labels[i]) * grad_scale ; dlogits = (softmax - onehot) * grad_scale.
+ * With grad_scale = 1/global_batch the gradients of all micro-batches sum to the global mean.
+ * row_loss and dlogits may each be NULL. */
 int srt_softmax_ce(int dtype, const void* logits, const int64_t* labels, int B, int classes,
-                   float grad_scale, float* loss_sum, void* dlogits, void* stream);
+                   float grad_scale, float* row_loss, void* dlogits, void* stream);
+/* out[0] = (accumulate ? out[0] : 0) + sum(v[0..n)), summed in a fixed order (loss.item() of
+ * train/resnet152.py:88 reads this value). */
+int srt_sum_f32(const float* v, int n, float* out, int accumulate, void* stream);
 /* dbias[k] = sum over rows of dy[rows][K] (fp32 out). */
 int srt_colsum(int dtype, const void* dy, int64_t rows, int K, float* out, void* stream);
 
@@ -129,6 +133,67 @@ int srt_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
 /* mask[0..2]: bit i set = SM i is available to training kernels. */
 int srt_set_sm_mask(const uint64_t mask[3]);
 int srt_get_sm_mask(uint64_t mask[3]);
+
+/* ---- tcgen05 kernel status ------------------------------------------------------------------
+ * Every wait inside the tensor-core kernels is bounded; a wait that gives up records a non-zero
+ * code here instead of hanging the GPU. Synchronises the device, returns and clears the word. */
+int srt_tc_status(int* status);
+/* Test hook: route 1x1 stride-1 convolutions through the gather path instead of TMA for A. */
+int srt_debug_force_gather(int on);
+
+/* ---- training-step executor (replaces the body of the reference's training loop:
+ *      model(images) / criterion / backward / optimizer stage, train/resnet152.py:84-91, with
+ *      the micro-batch semantics of pytorch/torch_col/dynamic_batch.py:112-153 and
+ *      pytorch/torch_col/accumulate.py:7-49) ---------------------------------------------------- */
+typedef struct srt_step srt_step;
+
+typedef struct srt_resnet_config {
+  int layers[4];      /* bottleneck blocks per stage: {3,8,36,3} = ResNet-152, {3,4,6,3} = ResNet-50 */
+  int num_classes;    /* multiple of 8 */
+  int max_batch;      /* largest micro-batch; buffers are sized for it */
+  int image;          /* input height = width, multiple of 32 */
+  int dtype;          /* SRT_F32 or SRT_BF16 */
+  int impl;           /* SRT_IMPL_* for the convolutions */
+  float lr, momentum, weight_decay;   /* torch.optim.SGD(lr, momentum, weight_decay) */
+  float bn_eps, bn_momentum;          /* 1e-5, 0.1 */
+} srt_resnet_config;
+
+enum { SRT_PARAM_CONV = 0, SRT_PARAM_VECTOR = 1, SRT_PARAM_BUFFER = 2, SRT_PARAM_LINEAR = 3 };
+enum { SRT_GET_VALUE = 0, SRT_GET_GRAD = 1, SRT_GET_ACCUM = 2, SRT_GET_MOMENTUM = 3 };
+
+int srt_resnet_create(const srt_resnet_config* cfg, srt_step** out);
+int srt_step_destroy(srt_step* s);
+/* Parameter registry under torchvision state_dict names ("layer1.0.conv1.weight", ...). Shapes and
+ * host data use the torch layout ([K,C,R,S] for convolutions); the device keeps [K,R,S,C]. */
+int srt_step_num_params(srt_step* s);
+int srt_step_param_info(srt_step* s, int idx, char* name, int name_cap, int64_t shape[4], int* ndim,
+                        int* kind);
+int srt_step_set_param(srt_step* s, int idx, const float* host);
+int srt_step_get_param(srt_step* s, int idx, float* host, int which);
+/* Rebuild the derived copies (bf16 working weights, transposed filters) after set_param. */
+int srt_step_commit_params(srt_step* s);
+void* srt_step_stream(srt_step* s);
+/* Stage one micro-batch: NCHW fp32 images and int64 labels, from (pinned) host memory
+ * (DynamicBatchDataset._retrieve_batch, pytorch/torch_col/dynamic_batch.py:438-459) or from
+ * device memory. Asynchronous on the step's stream. */
+int srt_step_upload_batch(srt_step* s, const float* host_images, const int64_t* host_labels, int B);
+int srt_step_set_batch_device(srt_step* s, const float* dev_images, const int64_t* dev_labels, int B);
+/* Forward, loss and backward of one micro-batch of B samples out of a global batch; the loss is
+ * scaled by B/global_batch (MicroBatchManager.scale_loss). Gradients overwrite the gradient
+ * buffer. Asynchronous. */
+int srt_step_forward_backward(srt_step* s, int B, int global_batch);
+int srt_step_forward_only(srt_step* s, int B);
+/* accumulated += grad ; grad = 0  (GradAccumulator.accumulate). */
+int srt_step_accumulate(srt_step* s);
+/* SGD-momentum update from the accumulated gradients (or the last micro-batch's if none were
+ * accumulated), then refresh of the derived weight copies (GradAccumulator.step). */
+int srt_step_optimizer(srt_step* s);
+/* Scaled loss of the last micro-batch; synchronises the stream (loss.item()). */
+int srt_step_loss(srt_step* s, float* host_loss);
+int srt_step_logits(srt_step* s, float* host, int B);
+int srt_step_synchronize(srt_step* s);
+/* which = 0: parameter + optimizer-state bytes; 1: activation + gradient-buffer bytes. */
+int64_t srt_step_memory_bytes(srt_step* s, int which);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,607 @@
+// Training-step executor for torchvision-layout bottleneck ResNets (ResNet-50/101/152).
+//
+// One object owns every device buffer of the step (flat fp32 master parameters, gradients,
+// momentum, optional bf16 working copy, saved activations, gradient ping-pong buffers, scratch)
+// and replays the forward / backward / optimizer sequence as kernel launches on one stream.
+// It stands where the reference runs `model(images)`, `criterion`, `scaler.scale(loss).backward()`
+// and the optimizer stage of MicroBatchManager (train/resnet152.py:84-91,
+// pytorch/torch_col/dynamic_batch.py:112-153, pytorch/torch_col/accumulate.py:7-49).
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "ops.cuh"
+
+
+namespace srt {
+
+namespace {
+
+constexpr int kStemCpad = 8;  // RGB input is zero-padded to 8 channels (16-byte vectors)
+
+struct ParamRec {
+  std::string name;
+  int kind;          // SRT_PARAM_*
+  int64_t shape[4];  // torch layout
+  int ndim;
+  size_t off;        // element offset into the flat buffers (kind != BUFFER) or buffer arena
+  size_t count;      // internal element count (with channel padding)
+  int cpad;          // internal channels (conv weights)
+};
+
+struct ConvL {
+  int C, K, R, S, stride, pad;  // C = internal (padded) channels
+  int w;                        // param index
+  size_t wt_off;                // element offset of the transposed copy (dgrad operand)
+};
+struct BNL {
+  int C;
+  int gamma, beta, rmean, rvar;  // param indices
+  float *mean, *invstd, *scale, *shift;
+};
+struct Unit {
+  ConvL conv;
+  BNL bn;
+  int relu;
+  void* z;  // conv output (pre-BN)
+  void* y;  // post BN (+residual) (+ReLU)
+  int H, W, P, Q;  // input and output spatial size
+};
+struct Block {
+  Unit u1, u2, u3, ds;
+  bool has_ds;
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct Step {
+  srt_resnet_config cfg;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  size_t esz = 4;  // activation element size
+
+  std::vector<ParamRec> params;
+  size_t n_flat = 0;     // elements in P/G/M/ACC
+  size_t n_buf = 0;      // elements in BN running-stat arena
+  size_t n_wt = 0;       // elements in the transposed-filter arena
+  float *P = nullptr, *G = nullptr, *M = nullptr, *ACC = nullptr, *BUF = nullptr;
+  void* Pw = nullptr;    // working copy of P in the compute dtype (== P in fp32 mode)
+  void* WT = nullptr;    // transposed filters in the compute dtype
+  float* bn_vec = nullptr;
+
+  Unit stem;
+  std::vector<Block> blocks;
+  int fc_w = -1, fc_b = -1;
+  int feat_C = 0, final_HW = 0;
+
+  // activations
+  void *x0 = nullptr, *pool_y = nullptr, *avg = nullptr, *logits = nullptr, *dlogits = nullptr;
+  uint8_t* pool_arg = nullptr;
+  void* T[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  float *row_loss = nullptr, *loss_acc = nullptr;
+  float* stage_images = nullptr;   // device staging of the NCHW fp32 batch
+  int64_t* stage_labels = nullptr;
+  std::vector<void*> allocs;
+
+  int opt_steps = 0;
+  int accum_pending = 0;
+  size_t act_bytes = 0;
+
+  ~Step() {
+    for (void* p : allocs) cudaFree(p);
+    if (own_stream && stream) cudaStreamDestroy(stream);
+  }
+  int dalloc(void** out, size_t bytes, bool zero) {
+    bytes = align_up(bytes ? bytes : 256, 256);
+    SRT_CHECK_CUDA(cudaMalloc(out, bytes));
+    allocs.push_back(*out);
+    if (zero) SRT_CHECK_CUDA(cudaMemset(*out, 0, bytes));
+    return SRT_OK;
+  }
+  int add_param(const std::string& name, int kind, std::initializer_list<int64_t> shape, int cpad) {
+    ParamRec r;
+    r.name = name;
+    r.kind = kind;
+    r.ndim = (int)shape.size();
+    int i = 0;
+    size_t cnt = 1;
+    for (int64_t s : shape) { r.shape[i++] = s; cnt *= (size_t)s; }
+    for (; i < 4; ++i) r.shape[i] = 1;
+    r.cpad = cpad;
+    if (kind == SRT_PARAM_CONV) cnt = (size_t)r.shape[0] * r.shape[2] * r.shape[3] * cpad;
+    r.count = cnt;
+    if (kind == SRT_PARAM_BUFFER) { r.off = n_buf; n_buf += align_up(cnt, 64); }
+    else { r.off = n_flat; n_flat += align_up(cnt, 64); }
+    params.push_back(r);
+    return (int)params.size() - 1;
+  }
+  ConvL make_conv(const std::string& name, int Cin_real, int K, int R, int stride, int pad) {
+    ConvL c;
+    c.C = Cin_real < 8 ? kStemCpad : Cin_real;
+    c.K = K; c.R = R; c.S = R; c.stride = stride; c.pad = pad;
+    c.w = add_param(name + ".weight", SRT_PARAM_CONV, {K, Cin_real, R, R}, c.C);
+    c.wt_off = n_wt;
+    n_wt += align_up((size_t)K * R * R * c.C, 64);
+    return c;
+  }
+  BNL make_bn(const std::string& name, int C) {
+    BNL b;
+    b.C = C;
+    b.gamma = add_param(name + ".weight", SRT_PARAM_VECTOR, {C}, 0);
+    b.beta = add_param(name + ".bias", SRT_PARAM_VECTOR, {C}, 0);
+    b.rmean = add_param(name + ".running_mean", SRT_PARAM_BUFFER, {C}, 0);
+    b.rvar = add_param(name + ".running_var", SRT_PARAM_BUFFER, {C}, 0);
+    b.mean = b.invstd = b.scale = b.shift = nullptr;
+    return b;
+  }
+  float* pf(int idx) { return P + params[idx].off; }
+  float* gf(int idx) { return G + params[idx].off; }
+  float* bf_(int idx) { return BUF + params[idx].off; }
+  void* pw(int idx) { return (char*)Pw + params[idx].off * esz; }
+  void* wt(const ConvL& c) { return (char*)WT + c.wt_off * esz; }
+
+  int build();
+  int refresh_working_copies();
+  int forward(int B);
+  int backward(int B);
+};
+
+int Step::build() {
+  const int dtype = cfg.dtype;
+  esz = dtype == SRT_F32 ? 4 : 2;
+  const int B = cfg.max_batch, IMG = cfg.image;
+  SRT_REQUIRE(B > 0 && IMG >= 32 && IMG % 32 == 0, "resnet: max_batch > 0 and image a multiple of 32 required");
+
+  // ---- topology + parameter registry (torchvision names) ----
+  stem.conv = make_conv("conv1", 3, 64, 7, 2, 3);
+  stem.bn = make_bn("bn1", 64);
+  stem.relu = 1;
+  stem.H = stem.W = IMG;
+  stem.P = stem.Q = IMG / 2;
+  int H = IMG / 4, inC = 64;
+  const int widths[4] = {64, 128, 256, 512};
+  for (int l = 0; l < 4; ++l) {
+    for (int b = 0; b < cfg.layers[l]; ++b) {
+      const std::string pre = "layer" + std::to_string(l + 1) + "." + std::to_string(b);
+      const int width = widths[l], outC = width * 4;
+      const int stride = (b == 0 && l > 0) ? 2 : 1;
+      Block blk;
+      blk.u1.conv = make_conv(pre + ".conv1", inC, width, 1, 1, 0);
+      blk.u1.bn = make_bn(pre + ".bn1", width);
+      blk.u1.relu = 1; blk.u1.H = blk.u1.W = H; blk.u1.P = blk.u1.Q = H;
+      blk.u2.conv = make_conv(pre + ".conv2", width, width, 3, stride, 1);
+      blk.u2.bn = make_bn(pre + ".bn2", width);
+      blk.u2.relu = 1; blk.u2.H = blk.u2.W = H; blk.u2.P = blk.u2.Q = H / stride;
+      blk.u3.conv = make_conv(pre + ".conv3", width, outC, 1, 1, 0);
+      blk.u3.bn = make_bn(pre + ".bn3", outC);
+      blk.u3.relu = 1; blk.u3.H = blk.u3.W = H / stride; blk.u3.P = blk.u3.Q = H / stride;
+      blk.has_ds = (b == 0);
+      if (blk.has_ds) {
+        blk.ds.conv = make_conv(pre + ".downsample.0", inC, outC, 1, stride, 0);
+        blk.ds.bn = make_bn(pre + ".downsample.1", outC);
+        blk.ds.relu = 0; blk.ds.H = blk.ds.W = H; blk.ds.P = blk.ds.Q = H / stride;
+      }
+      blocks.push_back(blk);
+      inC = outC;
+      H /= stride;
+    }
+  }
+  feat_C = inC;
+  final_HW = H * H;
+  fc_w = add_param("fc.weight", SRT_PARAM_LINEAR, {cfg.num_classes, feat_C}, 0);
+  fc_b = add_param("fc.bias", SRT_PARAM_VECTOR, {cfg.num_classes}, 0);
+  const size_t fc_wt_off = n_wt;
+  n_wt += align_up((size_t)cfg.num_classes * feat_C, 64);
+  (void)fc_wt_off;
+  SRT_REQUIRE(cfg.num_classes % 8 == 0, "resnet: num_classes must be a multiple of 8");
+
+  // ---- device memory ----
+  int rc;
+  if ((rc = dalloc((void**)&P, n_flat * 4, true))) return rc;
+  if ((rc = dalloc((void**)&G, n_flat * 4, true))) return rc;
+  if ((rc = dalloc((void**)&M, n_flat * 4, true))) return rc;
+  if ((rc = dalloc((void**)&ACC, n_flat * 4, true))) return rc;
+  if ((rc = dalloc((void**)&BUF, n_buf * 4, true))) return rc;
+  if (dtype == SRT_F32) Pw = P;
+  else if ((rc = dalloc(&Pw, n_flat * 2, true))) return rc;
+  if ((rc = dalloc(&WT, n_wt * esz, true))) return rc;
+
+  size_t bn_elems = 0;
+  auto count_bn = [&](BNL& b) { bn_elems += 4 * align_up(b.C, 64); };
+  count_bn(stem.bn);
+  for (auto& k : blocks) { count_bn(k.u1.bn); count_bn(k.u2.bn); count_bn(k.u3.bn); if (k.has_ds) count_bn(k.ds.bn); }
+  if ((rc = dalloc((void**)&bn_vec, bn_elems * 4, true))) return rc;
+  float* cur = bn_vec;
+  auto place_bn = [&](BNL& b) {
+    const size_t a = align_up(b.C, 64);
+    b.mean = cur; b.invstd = cur + a; b.scale = cur + 2 * a; b.shift = cur + 3 * a;
+    cur += 4 * a;
+  };
+  place_bn(stem.bn);
+  for (auto& k : blocks) { place_bn(k.u1.bn); place_bn(k.u2.bn); place_bn(k.u3.bn); if (k.has_ds) place_bn(k.ds.bn); }
+
+  size_t max_act = 0, max_bn_scratch = 0, max_wg_scratch = 0;
+  auto alloc_unit = [&](Unit& u) -> int {
+    const size_t elems = (size_t)B * u.P * u.Q * u.conv.K;
+    if (elems > max_act) max_act = elems;
+    int r;
+    if ((r = dalloc(&u.z, elems * esz, false))) return r;
+    if ((r = dalloc(&u.y, elems * esz, false))) return r;
+    act_bytes += 2 * align_up(elems * esz, 256);
+    const size_t bs = bn_scratch_bytes((int64_t)B * u.P * u.Q, u.conv.K);
+    if (bs > max_bn_scratch) max_bn_scratch = bs;
+    srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
+    const size_t ws = conv_wgrad_scratch_bytes(d, dtype, cfg.impl);
+    if (ws > max_wg_scratch) max_wg_scratch = ws;
+    return SRT_OK;
+  };
+  if ((rc = alloc_unit(stem))) return rc;
+  for (auto& k : blocks) {
+    if ((rc = alloc_unit(k.u1))) return rc;
+    if ((rc = alloc_unit(k.u2))) return rc;
+    if ((rc = alloc_unit(k.u3))) return rc;
+    if (k.has_ds && (rc = alloc_unit(k.ds))) return rc;
+  }
+  {
+    srt_conv_desc d = {B, 1, 1, feat_C, cfg.num_classes, 1, 1, 1, 0, 1, 1};
+    const size_t ws = conv_wgrad_scratch_bytes(d, dtype, cfg.impl);
+    if (ws > max_wg_scratch) max_wg_scratch = ws;
+  }
+  const size_t x0_elems = (size_t)B * IMG * IMG * kStemCpad;
+  if (x0_elems > max_act) max_act = x0_elems;
+  if ((rc = dalloc(&x0, x0_elems * esz, false))) return rc;
+  const size_t pool_elems = (size_t)B * (IMG / 4) * (IMG / 4) * 64;
+  if ((rc = dalloc(&pool_y, pool_elems * esz, false))) return rc;
+  if ((rc = dalloc((void**)&pool_arg, pool_elems, false))) return rc;
+  if ((rc = dalloc(&avg, (size_t)B * feat_C * esz, false))) return rc;
+  if ((rc = dalloc(&logits, (size_t)B * cfg.num_classes * esz, false))) return rc;
+  if ((rc = dalloc(&dlogits, (size_t)B * cfg.num_classes * esz, false))) return rc;
+  for (int i = 0; i < 5; ++i)
+    if ((rc = dalloc(&T[i], max_act * esz, false))) return rc;
+  act_bytes += (x0_elems + 2 * pool_elems) * esz + 5 * max_act * esz;
+  scratch_bytes = max_bn_scratch > max_wg_scratch ? max_bn_scratch : max_wg_scratch;
+  if ((rc = dalloc(&scratch, scratch_bytes, false))) return rc;
+  if ((rc = dalloc((void**)&row_loss, (size_t)B * 4, true))) return rc;
+  if ((rc = dalloc((void**)&loss_acc, 256, true))) return rc;
+  if ((rc = dalloc((void**)&stage_images, (size_t)B * 3 * IMG * IMG * 4, false))) return rc;
+  if ((rc = dalloc((void**)&stage_labels, (size_t)B * 8, false))) return rc;
+
+  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  own_stream = true;
+
+  // BN defaults (weight 1, bias 0, running_var 1); conv/fc weights are set by the caller.
+  std::vector<float> ones;
+  for (auto& r : params) {
+    const bool bn_weight = r.kind == SRT_PARAM_VECTOR && r.name.size() > 7 &&
+                           r.name.compare(r.name.size() - 7, 7, ".weight") == 0;
+    const bool rvar = r.kind == SRT_PARAM_BUFFER && r.name.find("running_var") != std::string::npos;
+    if (bn_weight || rvar) {
+      ones.assign(r.count, 1.f);
+      float* dst = rvar ? BUF + r.off : P + r.off;
+      SRT_CHECK_CUDA(cudaMemcpy(dst, ones.data(), r.count * 4, cudaMemcpyHostToDevice));
+    }
+  }
+  return refresh_working_copies();
+}
+
+// bf16 working copy of the parameters (bf16 mode) and transposed filters for dgrad.
+int Step::refresh_working_copies() {
+  int rc;
+  if (cfg.dtype == SRT_BF16 && (rc = cast_f32_to_bf16(P, Pw, (int64_t)n_flat, stream))) return rc;
+  auto tr = [&](const ConvL& c) -> int {
+    return filter_transpose(cfg.dtype, pw(c.w), wt(c), c.K, c.R * c.S, c.C, stream);
+  };
+  if ((rc = tr(stem.conv))) return rc;
+  for (auto& k : blocks) {
+    if ((rc = tr(k.u1.conv))) return rc;
+    if ((rc = tr(k.u2.conv))) return rc;
+    if ((rc = tr(k.u3.conv))) return rc;
+    if (k.has_ds && (rc = tr(k.ds.conv))) return rc;
+  }
+  // fc: [classes][feat] -> [feat][classes], stored after the conv filters
+  const size_t fc_wt_off = n_wt - align_up((size_t)cfg.num_classes * feat_C, 64);
+  return filter_transpose(cfg.dtype, pw(fc_w), (char*)WT + fc_wt_off * esz, cfg.num_classes, 1, feat_C, stream);
+}
+
+int Step::forward(int B) {
+  const int dt = cfg.dtype, impl = cfg.impl;
+  int rc;
+  auto run_unit = [&](Unit& u, const void* in, const void* residual) -> int {
+    srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
+    int r;
+    if ((r = conv_fprop(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, stream))) return r;
+    const int64_t rows = (int64_t)B * u.P * u.Q;
+    if ((r = bn_stats(dt, u.z, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
+                      bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift,
+                      scratch, scratch_bytes, stream)))
+      return r;
+    return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream);
+  };
+  if ((rc = nchw_to_nhwc(dt, stage_images, x0, B, 3, cfg.image, cfg.image, kStemCpad, stream))) return rc;
+  if ((rc = run_unit(stem, x0, nullptr))) return rc;
+  if ((rc = maxpool_fwd(dt, stem.y, pool_y, pool_arg, B, stem.P, stem.Q, 64, stream))) return rc;
+  const void* x = pool_y;
+  for (auto& k : blocks) {
+    if ((rc = run_unit(k.u1, x, nullptr))) return rc;
+    if ((rc = run_unit(k.u2, k.u1.y, nullptr))) return rc;
+    const void* identity = x;
+    if (k.has_ds) {
+      if ((rc = run_unit(k.ds, x, nullptr))) return rc;
+      identity = k.ds.y;
+    }
+    if ((rc = run_unit(k.u3, k.u2.y, identity))) return rc;
+    x = k.u3.y;
+  }
+  if ((rc = avgpool_fwd(dt, x, avg, B, final_HW, feat_C, stream))) return rc;
+  srt_conv_desc fd = {B, 1, 1, feat_C, cfg.num_classes, 1, 1, 1, 0, 1, 1};
+  srt_conv_epilogue ep = {pf(fc_b), nullptr};
+  return conv_fprop(fd, dt, impl, avg, pw(fc_w), logits, &ep, stream);
+}
+
+int Step::backward(int B) {
+  const int dt = cfg.dtype, impl = cfg.impl;
+  int rc;
+  // fc
+  srt_conv_desc fd = {B, 1, 1, feat_C, cfg.num_classes, 1, 1, 1, 0, 1, 1};
+  if ((rc = conv_wgrad(fd, dt, impl, dlogits, avg, gf(fc_w), scratch, scratch_bytes, stream))) return rc;
+  if ((rc = colsum(dt, dlogits, B, cfg.num_classes, gf(fc_b), stream))) return rc;
+  const size_t fc_wt_off = n_wt - align_up((size_t)cfg.num_classes * feat_C, 64);
+  if ((rc = conv_dgrad(fd, dt, impl, dlogits, (char*)WT + fc_wt_off * esz, T[1], nullptr, stream))) return rc;
+  if ((rc = avgpool_bwd(dt, T[1], T[0], B, final_HW, feat_C, stream))) return rc;
+
+  // gradient through conv+BN(+ReLU): dy (w.r.t. u.y) -> dz in T[1], filter gradient into G
+  auto unit_bwd = [&](Unit& u, const void* dy, const void* in, void* dz, void* dres) -> int {
+    const int64_t rows = (int64_t)B * u.P * u.Q;
+    int r;
+    if ((r = bn_backward(dt, dy, u.y, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean, u.bn.invstd, u.relu, dz,
+                         dres, gf(u.bn.gamma), gf(u.bn.beta), scratch, scratch_bytes, stream)))
+      return r;
+    srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
+    return conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch, scratch_bytes, stream);
+  };
+  auto unit_dgrad = [&](Unit& u, const void* dz, void* dx, const void* addend) -> int {
+    srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
+    srt_conv_epilogue ep = {nullptr, addend};
+    return conv_dgrad(d, dt, impl, dz, wt(u.conv), dx, addend ? &ep : nullptr, stream);
+  };
+
+  for (int i = (int)blocks.size() - 1; i >= 0; --i) {
+    Block& k = blocks[i];
+    const void* x_in = i == 0 ? pool_y : blocks[i - 1].u3.y;
+    // T0 = dout. u3: dz3 -> T1, masked dout -> T2
+    if ((rc = unit_bwd(k.u3, T[0], k.u2.y, T[1], T[2]))) return rc;
+    if ((rc = unit_dgrad(k.u3, T[1], T[3], nullptr))) return rc;       // dy2 -> T3
+    if ((rc = unit_bwd(k.u2, T[3], k.u1.y, T[1], nullptr))) return rc;  // dz2 -> T1
+    if ((rc = unit_dgrad(k.u2, T[1], T[3], nullptr))) return rc;       // dy1 -> T3
+    if ((rc = unit_bwd(k.u1, T[3], x_in, T[1], nullptr))) return rc;    // dz1 -> T1
+    if (k.has_ds) {
+      if ((rc = unit_bwd(k.ds, T[2], x_in, T[3], nullptr))) return rc;   // dz_ds -> T3
+      if ((rc = unit_dgrad(k.ds, T[3], T[4], nullptr))) return rc;     // dx_ds -> T4
+      if ((rc = unit_dgrad(k.u1, T[1], T[4], T[4]))) return rc;        // dx = dgrad(dz1) + dx_ds
+    } else {
+      if ((rc = unit_dgrad(k.u1, T[1], T[4], T[2]))) return rc;        // dx = dgrad(dz1) + masked dout
+    }
+    void* t = T[0]; T[0] = T[4]; T[4] = t;
+  }
+  // stem
+  if ((rc = maxpool_bwd(dt, T[0], pool_arg, T[3], B, stem.P, stem.Q, 64, stream))) return rc;
+  return unit_bwd(stem, T[3], x0, T[1], nullptr);
+}
+
+}  // namespace srt
+
+using namespace srt;
+
+extern "C" {
+
+int srt_resnet_create(const srt_resnet_config* cfg, srt_step** out) {
+  SRT_REQUIRE(cfg && out, "resnet_create: null argument");
+  SRT_REQUIRE(cfg->dtype == SRT_F32 || cfg->dtype == SRT_BF16, "resnet_create: unknown dtype");
+  Step* s = new Step();
+  s->cfg = *cfg;
+  int rc = s->build();
+  if (rc == SRT_OK) rc = cudaStreamSynchronize(s->stream) == cudaSuccess ? SRT_OK : SRT_ERR_CUDA;
+  if (rc != SRT_OK) { delete s; return rc; }
+  *out = (srt_step*)s;
+  return SRT_OK;
+}
+
+int srt_step_destroy(srt_step* h) {
+  if (!h) return SRT_OK;
+  Step* s = (Step*)h;
+  cudaStreamSynchronize(s->stream);
+  delete s;
+  return SRT_OK;
+}
+
+int srt_step_num_params(srt_step* h) { return h ? (int)((Step*)h)->params.size() : -1; }
+
+int srt_step_param_info(srt_step* h, int idx, char* name, int name_cap, int64_t shape[4], int* ndim,
+                        int* kind) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && idx >= 0 && idx < (int)s->params.size(), "param_info: bad index");
+  const ParamRec& r = s->params[idx];
+  if (name && name_cap > 0) { strncpy(name, r.name.c_str(), name_cap - 1); name[name_cap - 1] = 0; }
+  if (shape) for (int i = 0; i < 4; ++i) shape[i] = r.shape[i];
+  if (ndim) *ndim = r.ndim;
+  if (kind) *kind = r.kind;
+  return SRT_OK;
+}
+
+// Host fp32 tensor in torch layout ([K,C,R,S] for conv) -> internal layout ([K,R,S,Cpad]).
+int srt_step_set_param(srt_step* h, int idx, const float* host) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && host && idx >= 0 && idx < (int)s->params.size(), "set_param: bad argument");
+  const ParamRec& r = s->params[idx];
+  float* dst = r.kind == SRT_PARAM_BUFFER ? s->BUF + r.off : s->P + r.off;
+  if (r.kind == SRT_PARAM_CONV) {
+    const int K = (int)r.shape[0], C = (int)r.shape[1], R = (int)r.shape[2], S = (int)r.shape[3];
+    std::vector<float> tmp((size_t)K * R * S * r.cpad, 0.f);
+    for (int k = 0; k < K; ++k)
+      for (int c = 0; c < C; ++c)
+        for (int a = 0; a < R; ++a)
+          for (int b = 0; b < S; ++b)
+            tmp[(((size_t)k * R + a) * S + b) * r.cpad + c] = host[(((size_t)k * C + c) * R + a) * S + b];
+    SRT_CHECK_CUDA(cudaMemcpy(dst, tmp.data(), tmp.size() * 4, cudaMemcpyHostToDevice));
+  } else {
+    SRT_CHECK_CUDA(cudaMemcpy(dst, host, r.count * 4, cudaMemcpyHostToDevice));
+  }
+  return SRT_OK;
+}
+
+int srt_step_get_param(srt_step* h, int idx, float* host, int which) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && host && idx >= 0 && idx < (int)s->params.size(), "get_param: bad argument");
+  const ParamRec& r = s->params[idx];
+  SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  const float* base = r.kind == SRT_PARAM_BUFFER ? s->BUF
+                      : which == SRT_GET_GRAD     ? s->G
+                      : which == SRT_GET_ACCUM    ? s->ACC
+                      : which == SRT_GET_MOMENTUM ? s->M
+                                                  : s->P;
+  const float* src = base + r.off;
+  if (r.kind == SRT_PARAM_CONV) {
+    const int K = (int)r.shape[0], C = (int)r.shape[1], R = (int)r.shape[2], S = (int)r.shape[3];
+    std::vector<float> tmp((size_t)K * R * S * r.cpad);
+    SRT_CHECK_CUDA(cudaMemcpy(tmp.data(), src, tmp.size() * 4, cudaMemcpyDeviceToHost));
+    for (int k = 0; k < K; ++k)
+      for (int c = 0; c < C; ++c)
+        for (int a = 0; a < R; ++a)
+          for (int b = 0; b < S; ++b)
+            host[(((size_t)k * C + c) * R + a) * S + b] = tmp[(((size_t)k * R + a) * S + b) * r.cpad + c];
+  } else {
+    SRT_CHECK_CUDA(cudaMemcpy(host, src, r.count * 4, cudaMemcpyDeviceToHost));
+  }
+  return SRT_OK;
+}
+
+int srt_step_commit_params(srt_step* h) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "commit_params: null handle");
+  int rc = s->refresh_working_copies();
+  if (rc) return rc;
+  SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  return SRT_OK;
+}
+
+void* srt_step_stream(srt_step* h) { return h ? (void*)((Step*)h)->stream : nullptr; }
+
+int srt_step_upload_batch(srt_step* h, const float* host_images, const int64_t* host_labels, int B) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && host_images && host_labels && B > 0 && B <= s->cfg.max_batch, "upload_batch: bad argument");
+  const size_t img = (size_t)B * 3 * s->cfg.image * s->cfg.image * 4;
+  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_images, host_images, img, cudaMemcpyHostToDevice, s->stream));
+  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_labels, host_labels, (size_t)B * 8, cudaMemcpyHostToDevice, s->stream));
+  return SRT_OK;
+}
+
+int srt_step_set_batch_device(srt_step* h, const float* dev_images, const int64_t* dev_labels, int B) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && dev_images && dev_labels && B > 0 && B <= s->cfg.max_batch, "set_batch_device: bad argument");
+  const size_t img = (size_t)B * 3 * s->cfg.image * s->cfg.image * 4;
+  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_images, dev_images, img, cudaMemcpyDeviceToDevice, s->stream));
+  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_labels, dev_labels, (size_t)B * 8, cudaMemcpyDeviceToDevice, s->stream));
+  return SRT_OK;
+}
+
+int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch && global_batch >= B, "forward_backward: bad batch sizes");
+  int rc = s->forward(B);
+  if (rc) return rc;
+  const float scale = 1.f / (float)global_batch;
+  if ((rc = softmax_ce(s->cfg.dtype, s->logits, s->stage_labels, B, s->cfg.num_classes, scale, s->row_loss,
+                       s->dlogits, s->stream)))
+    return rc;
+  if ((rc = sum_f32(s->row_loss, B, s->loss_acc, 0, s->stream))) return rc;
+  return s->backward(B);
+}
+
+int srt_step_forward_only(srt_step* h, int B) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_only: bad batch size");
+  return s->forward(B);
+}
+
+int srt_step_accumulate(srt_step* h) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "accumulate: null handle");
+  s->accum_pending++;
+  return grad_accumulate(s->ACC, s->G, (int64_t)s->n_flat, s->stream);
+}
+
+int srt_step_optimizer(srt_step* h) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "optimizer: null handle");
+  const float* grad = s->accum_pending > 0 ? s->ACC : s->G;
+  int rc = sgd_momentum(s->P, grad, s->M, s->cfg.dtype == SRT_BF16 ? s->Pw : nullptr, (int64_t)s->n_flat,
+                        s->cfg.lr, s->cfg.momentum, s->cfg.weight_decay, s->opt_steps == 0, s->stream);
+  if (rc) return rc;
+  if (s->accum_pending > 0) {
+    SRT_CHECK_CUDA(cudaMemsetAsync(s->ACC, 0, s->n_flat * 4, s->stream));
+    s->accum_pending = 0;
+  }
+  s->opt_steps++;
+  // transposed filters follow the updated parameters (the bf16 copy was written by the optimizer)
+  auto tr = [&](const ConvL& c) -> int {
+    return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, s->stream);
+  };
+  if ((rc = tr(s->stem.conv))) return rc;
+  for (auto& k : s->blocks) {
+    if ((rc = tr(k.u1.conv))) return rc;
+    if ((rc = tr(k.u2.conv))) return rc;
+    if ((rc = tr(k.u3.conv))) return rc;
+    if (k.has_ds && (rc = tr(k.ds.conv))) return rc;
+  }
+  const size_t fc_wt_off = s->n_wt - align_up((size_t)s->cfg.num_classes * s->feat_C, 64);
+  return filter_transpose(s->cfg.dtype, s->pw(s->fc_w), (char*)s->WT + fc_wt_off * s->esz, s->cfg.num_classes, 1,
+                          s->feat_C, s->stream);
+}
+
+int srt_step_loss(srt_step* h, float* host_loss) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && host_loss, "loss: null argument");
+  SRT_CHECK_CUDA(cudaMemcpyAsync(host_loss, s->loss_acc, 4, cudaMemcpyDeviceToHost, s->stream));
+  SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  return SRT_OK;
+}
+
+int srt_step_synchronize(srt_step* h) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "synchronize: null handle");
+  SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  return SRT_OK;
+}
+
+int srt_step_logits(srt_step* h, float* host, int B) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && host && B > 0 && B <= s->cfg.max_batch, "logits: bad argument");
+  const size_t n = (size_t)B * s->cfg.num_classes;
+  SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  if (s->cfg.dtype == SRT_F32) {
+    SRT_CHECK_CUDA(cudaMemcpy(host, s->logits, n * 4, cudaMemcpyDeviceToHost));
+  } else {
+    std::vector<uint16_t> tmp(n);
+    SRT_CHECK_CUDA(cudaMemcpy(tmp.data(), s->logits, n * 2, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n; ++i) {
+      uint32_t u = (uint32_t)tmp[i] << 16;
+      memcpy(&host[i], &u, 4);
+    }
+  }
+  return SRT_OK;
+}
+
+int64_t srt_step_memory_bytes(srt_step* h, int which) {
+  Step* s = (Step*)h;
+  if (!s) return -1;
+  if (which == 0) return (int64_t)(s->n_flat * 16 + s->n_buf * 4);  // parameters + optimizer state
+  return (int64_t)s->act_bytes;                                     // activations + gradient buffers
+}
+
+}  // extern "C"

@@ -1,0 +1,44 @@
+"""CPU suite: the oracle reproduces the committed golden fixtures (same build container), and the
+fixtures carry the fp64 anchor. Small cases only, so the suite stays fast."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import resnet_oracle as O
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.mark.parametrize("name", ["resnet14_small", "resnet50_small"])
+def test_oracle_reproduces_golden(name):
+    with open(os.path.join(GOLD, name + ".json")) as f:
+        g = json.load(f)
+    torch.set_num_threads(os.cpu_count() or 1)
+    model = O.build_model(g["arch"], g["seed"])
+    batches = O.make_batches(g["batch"], g["steps"], g["image"])
+    loss0, grads = O.first_step_gradients(model, batches[0])
+    losses = O.train_steps(model, batches)
+    assert loss0 == pytest.approx(g["fp32"]["loss0"], rel=1e-6)
+    # later steps inherit ReLU-flip noise from thread-count dependent reduction order
+    assert losses[0] == pytest.approx(g["fp32"]["losses"][0], rel=1e-6)
+    dig = O.summarize(O.state_arrays(model), samples=4)
+    for k, d in g["fp32"]["final"].items():
+        assert dig[k]["l2"] == pytest.approx(d["l2"], rel=5e-2, abs=1e-6), k
+    gd = O.summarize(grads, samples=4)
+    rels = [abs(gd[k]["l2"] - d["l2"]) / (d["l2"] + 1e-30) for k, d in g["fp32"]["grad0"].items()]
+    assert np.median(rels) < 5e-2
+
+
+def test_c1_fixture_is_complete():
+    with open(os.path.join(GOLD, "resnet152_c1.json")) as f:
+        g = json.load(f)
+    assert g["arch"] == "resnet152" and g["batch"] == 16 and g["image"] == 224 and g["steps"] == 3
+    for prec in ("fp32", "fp64"):
+        assert len(g[prec]["losses"]) == 3 and len(g[prec]["final"]) == len(g["fp64"]["final"])
+    # 155 conv + fc weights, 155 BN x (weight, bias, mean, var), fc bias
+    assert len(g["fp32"]["final"]) == 155 + 1 + 155 * 4 + 1
+    # the reference's fp32 path is measurably inexact: the fixture records by how much
+    assert abs(g["fp32"]["losses"][2] - g["fp64"]["losses"][2]) > 1e-2

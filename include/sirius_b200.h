@@ -78,13 +78,14 @@ size_t srt_bn_scratch_bytes(int64_t rows, int C);
 /* y = act(z*scale + shift (+ residual)); relu != 0 applies max(.,0). */
 int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
                  const float* scale, const float* shift, int relu, void* stream);
-/* Backward of y = act(bn(z) (+ residual)). dy is the gradient w.r.t. y; y supplies the ReLU mask
- * when relu != 0. Writes dz, dgamma, dbeta and, when dresidual != NULL, the masked gradient that
- * flows to the residual branch. */
+/* Backward of y = act(bn(z) (+ residual)). dy is the gradient w.r.t. y. When relu != 0 the mask
+ * comes from y; for units without a residual y may be NULL and the mask is recomputed from
+ * z*scale + shift (saves one tensor read). Writes dz, dgamma, dbeta and, when dresidual != NULL,
+ * the masked gradient that flows to the residual branch. */
 int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
-                    const float* gamma, const float* mean, const float* invstd, int relu,
-                    void* dz, void* dresidual, float* dgamma, float* dbeta, void* scratch,
-                    size_t scratch_bytes, void* stream);
+                    const float* gamma, const float* mean, const float* invstd, const float* scale,
+                    const float* shift, int relu, void* dz, void* dresidual, float* dgamma,
+                    float* dbeta, void* scratch, size_t scratch_bytes, void* stream);
 
 /* ---- pooling (replaces nn.MaxPool2d(3,2,1) and nn.AdaptiveAvgPool2d(1) of torchvision
  *      ResNet) ------------------------------------------------------------------------------- */
@@ -194,6 +195,19 @@ int srt_step_logits(srt_step* s, float* host, int B);
 int srt_step_synchronize(srt_step* s);
 /* which = 0: parameter + optimizer-state bytes; 1: activation + gradient-buffer bytes. */
 int64_t srt_step_memory_bytes(srt_step* s, int which);
+/* Flat fp32 gradient buffer (last micro-batch, or the accumulated one): the operand of the data-
+ * parallel gradient all-reduce (c10d Reducer buckets in pytorch/torch_col/csrc/dist_ext.cc:59-123). */
+int srt_step_grad_buffer(srt_step* s, int accumulated, void** ptr, int64_t* n);
+/* Per-category device timing: CUDA events on the step's stream around every launch while enabled
+ * (counterpart of the reference's EventManager records, pytorch/torch_col/util.py:113-178, at kernel
+ * granularity). work[] is algorithmic FLOPs (CONV, WGRAD) or bytes (others). */
+enum { SRT_PROF_CONV = 0, SRT_PROF_WGRAD = 1, SRT_PROF_NORM = 2, SRT_PROF_OTHER = 3, SRT_PROF_OPTIM = 4,
+       SRT_PROF_NCAT = 5 };
+int srt_step_profile(srt_step* s, int enable);
+int srt_step_profile_read(srt_step* s, double ms[SRT_PROF_NCAT], double work[SRT_PROF_NCAT],
+                          int64_t launches[SRT_PROF_NCAT]);
+/* Kernel launches issued by this library in this process so far. */
+int64_t srt_launch_count(void);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,7 @@
 // extern "C" surface of the kernel library: argument checks, dtype / kernel-family dispatch.
 #include <stdarg.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -17,6 +18,9 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {
   static int cached[16] = {0};
@@ -156,13 +160,13 @@ int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_
   return bn_apply(dtype, z, residual, y, rows, C, scale, shift, relu, ST(stream));
 }
 int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
-                    const float* gamma, const float* mean, const float* invstd, int relu,
-                    void* dz, void* dresidual, float* dgamma, float* dbeta, void* scratch,
-                    size_t scratch_bytes, void* stream) {
+                    const float* gamma, const float* mean, const float* invstd, const float* scale,
+                    const float* shift, int relu, void* dz, void* dresidual, float* dgamma,
+                    float* dbeta, void* scratch, size_t scratch_bytes, void* stream) {
   SRT_REQUIRE(dy && z && mean && invstd && dz, "bn_backward: null argument");
   CHECK_DTYPE(dtype);
-  return bn_backward(dtype, dy, y, z, rows, C, gamma, mean, invstd, relu, dz, dresidual, dgamma,
-                     dbeta, scratch, scratch_bytes, ST(stream));
+  return bn_backward(dtype, dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz, dresidual,
+                     dgamma, dbeta, scratch, scratch_bytes, ST(stream));
 }
 
 int srt_maxpool3x3s2_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W,
@@ -247,6 +251,8 @@ int srt_get_sm_mask(uint64_t mask[3]) {
   mask[0] = m.w[0]; mask[1] = m.w[1]; mask[2] = m.w[2];
   return SRT_OK;
 }
+
+int64_t srt_launch_count(void) { return (int64_t)g_launches.load(); }
 
 int srt_tc_status(int* status) {
   SRT_REQUIRE(status != nullptr, "tc_status: null argument");

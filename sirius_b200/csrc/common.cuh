@@ -31,8 +31,11 @@ void set_error(const char* fmt, ...);
     }                                                                               \
   } while (0)
 
+void count_launch();  // bumps the process-wide launch counter
+
 #define SRT_LAUNCH_CHECK()                                                          \
   do {                                                                              \
+    ::srt::count_launch();                                                          \
     cudaError_t _e = cudaGetLastError();                                            \
     if (_e != cudaSuccess) {                                                        \
       ::srt::set_error("%s:%d launch -> %s", __FILE__, __LINE__,                    \

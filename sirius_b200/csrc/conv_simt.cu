@@ -58,7 +58,7 @@ gather_gemm_simt(GatherGeom g, const T* __restrict__ src, const T* __restrict__ 
     float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
     if (kk < g.Kg) {
       const int tap = kk / g.src_c, c = kk - tap * g.src_c;
-      const long long off = gather_offset(g, rc, tap, c);
+      const long long off = m < g.M ? gather_offset(g, rc, tap, c) : -1;
       if (off >= 0) Ld4<T>::ld(src + off, a);
       if (nb_ok) Ld4<T>::ld(brow + kk, b);
     }

@@ -11,7 +11,8 @@ namespace srt {
 namespace {
 
 constexpr int NT = 256;
-constexpr int ROWS_PER_THREAD = 32;
+constexpr int ROWS_PER_THREAD = 8;   // loads in flight per thread
+constexpr int FIN_LANES = 32;        // slab lanes per channel in the finalize kernels
 
 struct RowMap {
   int CV;    // 16-byte vectors per row
@@ -37,26 +38,49 @@ inline RowMap make_row_map(int64_t rows, int C, int V) {
 // vector writes the slab partial as doubles: partial[(slab*C + c)*2 + {0,1}].
 template <int V>
 __device__ inline void block_reduce_store(const float (&a)[V], const float (&b)[V], const RowMap& m,
-                                          int tc, int rl, int cv, int C, double* partial) {
+                                          int C, double* partial) {
   __shared__ float sh_a[NT * V];
   __shared__ float sh_b[NT * V];
   const int t = threadIdx.x;
 #pragma unroll
   for (int v = 0; v < V; ++v) { sh_a[t * V + v] = a[v]; sh_b[t * V + v] = b[v]; }
   __syncthreads();
-  if (rl == 0 && cv < m.CV) {
-#pragma unroll
-    for (int v = 0; v < V; ++v) {
-      double sa = 0.0, sb = 0.0;
-      for (int r = 0; r < m.RL; ++r) {
-        sa += (double)sh_a[(r * m.TC + tc) * V + v];
-        sb += (double)sh_b[(r * m.TC + tc) * V + v];
-      }
-      const size_t o = ((size_t)blockIdx.x * C + (size_t)cv * V + v) * 2;
-      partial[o] = sa;
-      partial[o + 1] = sb;
+  // one thread per channel of this block's chunk; row lanes are summed in a fixed order
+  const int chunk = m.TC * V;
+  for (int ch = t; ch < chunk; ch += NT) {
+    const int c = blockIdx.y * chunk + ch;
+    if (c >= C) break;
+    double sa = 0.0, sb = 0.0;
+    for (int r = 0; r < m.RL; ++r) {
+      sa += (double)sh_a[r * chunk + ch];
+      sb += (double)sh_b[r * chunk + ch];
+    }
+    double2* out = reinterpret_cast<double2*>(partial) + (size_t)blockIdx.x * C + c;
+    *out = make_double2(sa, sb);
+  }
+}
+
+// Sum of the S slab partials of channel c: FIN_LANES lanes stride over the slabs, then a fixed-order
+// combine through shared memory. Call with blockDim = (32 channels, FIN_LANES).
+__device__ inline double2 reduce_partials(const double* __restrict__ partial, int S, int C, int c) {
+  __shared__ double2 sh[FIN_LANES][33];
+  double2 acc = make_double2(0.0, 0.0);
+  if (c < C) {
+    const double2* p = reinterpret_cast<const double2*>(partial);
+#pragma unroll 4
+    for (int i = threadIdx.y; i < S; i += FIN_LANES) {
+      const double2 v = p[(size_t)i * C + c];
+      acc.x += v.x;
+      acc.y += v.y;
     }
   }
+  sh[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  double2 tot = make_double2(0.0, 0.0);
+  if (threadIdx.y == 0) {
+    for (int l = 0; l < FIN_LANES; ++l) { tot.x += sh[l][threadIdx.x].x; tot.y += sh[l][threadIdx.x].y; }
+  }
+  return tot;
 }
 
 template <typename T>
@@ -70,34 +94,37 @@ bn_stats_partial(const T* __restrict__ z, int64_t rows, int C, RowMap m, double*
 #pragma unroll
   for (int v = 0; v < V; ++v) { s[v] = 0.f; q[v] = 0.f; }
   if (rl < m.RL && cv < m.CV) {
-    const int64_t r0 = (int64_t)blockIdx.x * m.slab;
-    const int64_t r1 = r0 + m.slab < rows ? r0 + m.slab : rows;
-    for (int64_t r = r0 + rl; r < r1; r += m.RL) {
-      Vec16<T> x;
-      x.load(z + r * C + (int64_t)cv * V);
-      float f[V];
-      x.unpack(f);
+    const int64_t r0 = (int64_t)blockIdx.x * m.slab + rl;
+    Vec16<T> x[ROWS_PER_THREAD];
 #pragma unroll
-      for (int v = 0; v < V; ++v) { s[v] += f[v]; q[v] = fmaf(f[v], f[v], q[v]); }
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      const int64_t r = r0 + (int64_t)i * m.RL;
+      if (r < rows) x[i].load(z + r * C + (int64_t)cv * V);
+    }
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      const int64_t r = r0 + (int64_t)i * m.RL;
+      if (r < rows) {
+        float f[V];
+        x[i].unpack(f);
+#pragma unroll
+        for (int v = 0; v < V; ++v) { s[v] += f[v]; q[v] = fmaf(f[v], f[v], q[v]); }
+      }
     }
   }
-  block_reduce_store<V>(s, q, m, tc, rl, cv, C, partial);
+  block_reduce_store<V>(s, q, m, C, partial);
 }
 
-__global__ void bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
-                                  const float* __restrict__ gamma, const float* __restrict__ beta,
-                                  float eps, float momentum, float* running_mean,
-                                  float* running_var, float* mean, float* invstd, float* scale,
-                                  float* shift) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0.0, q = 0.0;
-  for (int i = 0; i < S; ++i) {
-    s += partial[((size_t)i * C + c) * 2];
-    q += partial[((size_t)i * C + c) * 2 + 1];
-  }
-  const double mu = s / (double)rows;
-  double var = q / (double)rows - mu * mu;
+__global__ void __launch_bounds__(32 * FIN_LANES)
+bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
+                  const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                  float momentum, float* running_mean, float* running_var, float* mean, float* invstd,
+                  float* scale, float* shift) {
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const double2 tot = reduce_partials(partial, S, C, c);
+  if (threadIdx.y != 0 || c >= C) return;
+  const double mu = tot.x / (double)rows;
+  double var = tot.y / (double)rows - mu * mu;
   if (var < 0.0) var = 0.0;
   const float is = (float)(1.0 / sqrt(var + (double)eps));
   const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
@@ -113,34 +140,40 @@ __global__ void bn_stats_finalize(const double* __restrict__ partial, int S, int
   }
 }
 
-template <typename T>
+constexpr int UNR = 4;  // independent 16-byte vectors per thread in the elementwise kernels
+
+template <typename T, bool HAS_RES>
 __global__ void __launch_bounds__(NT)
-bn_apply_kernel(const T* __restrict__ z, const T* residual, T* y, int64_t nvec, int CV,
-                const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
+bn_apply_kernel(const T* __restrict__ z, const T* __restrict__ residual, T* __restrict__ y, int64_t nvec,
+                int CV, const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
   constexpr int V = Vec16<T>::N;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < nvec; i += stride) {
+  const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
+  Vec16<T> x[UNR], rv[UNR];
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const int64_t i = base + (int64_t)u * NT;
+    if (i < nvec) {
+      x[u].load(z + i * V);
+      if (HAS_RES) rv[u].load(residual + i * V);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const int64_t i = base + (int64_t)u * NT;
+    if (i >= nvec) continue;
     const int cv = (int)(i % CV);
-    Vec16<T> x;
-    x.load(z + i * V);
     float f[V];
-    x.unpack(f);
-    float sc[V], sh[V];
+    x[u].unpack(f);
 #pragma unroll
     for (int v = 0; v < V; v += 4) {
-      float4 a = *reinterpret_cast<const float4*>(scale + cv * V + v);
-      float4 b = *reinterpret_cast<const float4*>(shift + cv * V + v);
-      sc[v] = a.x; sc[v + 1] = a.y; sc[v + 2] = a.z; sc[v + 3] = a.w;
-      sh[v] = b.x; sh[v + 1] = b.y; sh[v + 2] = b.z; sh[v + 3] = b.w;
+      const float4 a = *reinterpret_cast<const float4*>(scale + cv * V + v);
+      const float4 b = *reinterpret_cast<const float4*>(shift + cv * V + v);
+      f[v] = fmaf(f[v], a.x, b.x); f[v + 1] = fmaf(f[v + 1], a.y, b.y);
+      f[v + 2] = fmaf(f[v + 2], a.z, b.z); f[v + 3] = fmaf(f[v + 3], a.w, b.w);
     }
-#pragma unroll
-    for (int v = 0; v < V; ++v) f[v] = fmaf(f[v], sc[v], sh[v]);
-    if (residual) {
-      Vec16<T> rv;
-      rv.load(residual + i * V);
+    if (HAS_RES) {
       float rf[V];
-      rv.unpack(rf);
+      rv[u].unpack(rf);
 #pragma unroll
       for (int v = 0; v < V; ++v) f[v] += rf[v];
     }
@@ -154,11 +187,32 @@ bn_apply_kernel(const T* __restrict__ z, const T* residual, T* y, int64_t nvec, 
   }
 }
 
+// ReLU mask of y = relu(z*scale + shift): taken from the stored y when given (residual units),
+// otherwise recomputed from z with the same fused multiply-add the forward pass used, which has
+// the same sign as the stored (rounded) y.
+template <typename T, int V>
+__device__ __forceinline__ void apply_relu_mask(float (&g)[V], const float (&x)[V], const T* y_ptr,
+                                                const float* __restrict__ scale,
+                                                const float* __restrict__ shift, int c0) {
+  if (y_ptr) {
+    Vec16<T> yv;
+    yv.load(y_ptr);
+    float yy[V];
+    yv.unpack(yy);
+#pragma unroll
+    for (int v = 0; v < V; ++v) g[v] = yy[v] > 0.f ? g[v] : 0.f;
+  } else {
+#pragma unroll
+    for (int v = 0; v < V; ++v) g[v] = fmaf(x[v], scale[c0 + v], shift[c0 + v]) > 0.f ? g[v] : 0.f;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(NT)
 bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z,
                int64_t rows, int C, RowMap m, const float* __restrict__ mean,
-               const float* __restrict__ invstd, int relu, double* partial) {
+               const float* __restrict__ invstd, const float* __restrict__ scale,
+               const float* __restrict__ shift, int relu, double* partial) {
   constexpr int V = Vec16<T>::N;
   const int t = threadIdx.x;
   const int tc = t % m.TC, rl = t / m.TC;
@@ -170,24 +224,25 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
     float mu[V], is[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) { mu[v] = mean[cv * V + v]; is[v] = invstd[cv * V + v]; }
-    const int64_t r0 = (int64_t)blockIdx.x * m.slab;
-    const int64_t r1 = r0 + m.slab < rows ? r0 + m.slab : rows;
-    for (int64_t r = r0 + rl; r < r1; r += m.RL) {
-      const int64_t o = r * C + (int64_t)cv * V;
-      Vec16<T> a, b;
-      a.load(dy + o);
-      b.load(z + o);
-      float g[V], x[V];
-      a.unpack(g);
-      b.unpack(x);
-      if (relu) {
-        Vec16<T> c;
-        c.load(y + o);
-        float yy[V];
-        c.unpack(yy);
+    const int64_t r0 = (int64_t)blockIdx.x * m.slab + rl;
+    Vec16<T> a[ROWS_PER_THREAD], b[ROWS_PER_THREAD];
 #pragma unroll
-        for (int v = 0; v < V; ++v) g[v] = yy[v] > 0.f ? g[v] : 0.f;
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      const int64_t r = r0 + (int64_t)i * m.RL;
+      if (r < rows) {
+        const int64_t o = r * C + (int64_t)cv * V;
+        a[i].load(dy + o);
+        b[i].load(z + o);
       }
+    }
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      const int64_t r = r0 + (int64_t)i * m.RL;
+      if (r >= rows) continue;
+      float g[V], x[V];
+      a[i].unpack(g);
+      b[i].unpack(x);
+      if (relu) apply_relu_mask<T, V>(g, x, y ? y + r * C + (int64_t)cv * V : nullptr, scale, shift, cv * V);
 #pragma unroll
       for (int v = 0; v < V; ++v) {
         sg[v] += g[v];
@@ -195,53 +250,49 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
       }
     }
   }
-  block_reduce_store<V>(sg, sgx, m, tc, rl, cv, C, partial);
+  block_reduce_store<V>(sg, sgx, m, C, partial);
 }
 
 // coef[c*4 + {0,1,2}] = gamma*invstd, dbeta/rows, dgamma/rows
-__global__ void bn_bwd_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
-                                const float* __restrict__ gamma, const float* __restrict__ invstd,
-                                float* dgamma, float* dbeta, float* coef) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0.0, q = 0.0;
-  for (int i = 0; i < S; ++i) {
-    s += partial[((size_t)i * C + c) * 2];
-    q += partial[((size_t)i * C + c) * 2 + 1];
-  }
-  if (dbeta) dbeta[c] = (float)s;
-  if (dgamma) dgamma[c] = (float)q;
+__global__ void __launch_bounds__(32 * FIN_LANES)
+bn_bwd_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
+                const float* __restrict__ gamma, const float* __restrict__ invstd, float* dgamma,
+                float* dbeta, float* coef) {
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const double2 tot = reduce_partials(partial, S, C, c);
+  if (threadIdx.y != 0 || c >= C) return;
+  if (dbeta) dbeta[c] = (float)tot.x;
+  if (dgamma) dgamma[c] = (float)tot.y;
   const float g = gamma ? gamma[c] : 1.f;
   coef[c * 4 + 0] = g * invstd[c];
-  coef[c * 4 + 1] = (float)(s / (double)rows);
-  coef[c * 4 + 2] = (float)(q / (double)rows);
+  coef[c * 4 + 1] = (float)(tot.x / (double)rows);
+  coef[c * 4 + 2] = (float)(tot.y / (double)rows);
   coef[c * 4 + 3] = 0.f;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(NT)
-bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z, T* dz,
-             T* dres, int64_t nvec, int CV, const float* __restrict__ mean,
-             const float* __restrict__ invstd, const float* __restrict__ coef, int relu) {
+bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z, T* __restrict__ dz,
+             T* __restrict__ dres, int64_t nvec, int CV, const float* __restrict__ mean,
+             const float* __restrict__ invstd, const float* __restrict__ coef,
+             const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
   constexpr int V = Vec16<T>::N;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < nvec; i += stride) {
-    const int cv = (int)(i % CV);
-    Vec16<T> a, b;
-    a.load(dy + i * V);
-    b.load(z + i * V);
-    float g[V], x[V];
-    a.unpack(g);
-    b.unpack(x);
-    if (relu) {
-      Vec16<T> c;
-      c.load(y + i * V);
-      float yy[V];
-      c.unpack(yy);
+  const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
+  Vec16<T> a[UNR], b[UNR];
 #pragma unroll
-      for (int v = 0; v < V; ++v) g[v] = yy[v] > 0.f ? g[v] : 0.f;
-    }
+  for (int u = 0; u < UNR; ++u) {
+    const int64_t i = base + (int64_t)u * NT;
+    if (i < nvec) { a[u].load(dy + i * V); b[u].load(z + i * V); }
+  }
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const int64_t i = base + (int64_t)u * NT;
+    if (i >= nvec) continue;
+    const int cv = (int)(i % CV);
+    float g[V], x[V];
+    a[u].unpack(g);
+    b[u].unpack(x);
+    if (relu) apply_relu_mask<T, V>(g, x, y ? y + i * V : nullptr, scale, shift, cv * V);
     if (dres) {
       Vec16<T> o;
       o.pack(g);
@@ -261,12 +312,10 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
   }
 }
 
-inline unsigned stream_grid(int64_t nvec) {
-  int64_t blocks = (nvec + NT - 1) / NT;
-  const int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
-  return (unsigned)blocks;
+inline unsigned unrolled_grid(int64_t nvec) {
+  const int64_t per_block = (int64_t)NT * UNR;
+  const int64_t blocks = (nvec + per_block - 1) / per_block;
+  return (unsigned)(blocks < 1 ? 1 : blocks);
 }
 
 }  // namespace
@@ -286,8 +335,8 @@ static int bn_stats_t(const void* z, int64_t rows, int C, const float* gamma, co
   double* partial = (double*)scratch;
   bn_stats_partial<T><<<dim3(m.S, m.GY), NT, 0, st>>>((const T*)z, rows, C, m, partial);
   SRT_LAUNCH_CHECK();
-  bn_stats_finalize<<<ceil_div(C, 128), 128, 0, st>>>(partial, m.S, C, rows, gamma, beta, eps,
-                                                     momentum, rm, rv, mean, invstd, scale, shift);
+  bn_stats_finalize<<<ceil_div(C, 32), dim3(32, FIN_LANES), 0, st>>>(
+      partial, m.S, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -304,58 +353,64 @@ int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, 
                                    scale, shift, scratch, st);
 }
 
+template <typename T>
+static void bn_apply_t(const void* z, const void* residual, void* y, int64_t rows, int C,
+                       const float* scale, const float* shift, int relu, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  const int64_t nvec = rows * C / V;
+  if (residual)
+    bn_apply_kernel<T, true><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)z, (const T*)residual, (T*)y,
+                                                               nvec, C / V, scale, shift, relu);
+  else
+    bn_apply_kernel<T, false><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)z, nullptr, (T*)y, nvec, C / V,
+                                                                scale, shift, relu);
+}
+
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
              const float* scale, const float* shift, int relu, cudaStream_t st) {
   SRT_REQUIRE(C % 8 == 0, "bn_apply: C (%d) must be a multiple of 8", C);
-  if (dtype == SRT_F32) {
-    const int64_t nvec = rows * C / 4;
-    bn_apply_kernel<float><<<stream_grid(nvec), NT, 0, st>>>(
-        (const float*)z, (const float*)residual, (float*)y, nvec, C / 4, scale, shift, relu);
-  } else {
-    const int64_t nvec = rows * C / 8;
-    bn_apply_kernel<__nv_bfloat16><<<stream_grid(nvec), NT, 0, st>>>(
-        (const __nv_bfloat16*)z, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, nvec, C / 8,
-        scale, shift, relu);
-  }
+  if (dtype == SRT_F32) bn_apply_t<float>(z, residual, y, rows, C, scale, shift, relu, st);
+  else bn_apply_t<__nv_bfloat16>(z, residual, y, rows, C, scale, shift, relu, st);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 
 template <typename T>
 static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t rows, int C,
-                         const float* gamma, const float* mean, const float* invstd, int relu,
-                         void* dz, void* dres, float* dgamma, float* dbeta, void* scratch,
-                         cudaStream_t st) {
+                         const float* gamma, const float* mean, const float* invstd,
+                         const float* scale, const float* shift, int relu, void* dz, void* dres,
+                         float* dgamma, float* dbeta, void* scratch, cudaStream_t st) {
   constexpr int V = Vec16<T>::N;
   RowMap m = make_row_map(rows, C, V);
   double* partial = (double*)scratch;
   float* coef = (float*)((char*)scratch + (size_t)m.S * C * 2 * sizeof(double));
   bn_bwd_partial<T><<<dim3(m.S, m.GY), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, rows, C,
-                                                    m, mean, invstd, relu, partial);
+                                                    m, mean, invstd, scale, shift, relu, partial);
   SRT_LAUNCH_CHECK();
-  bn_bwd_finalize<<<ceil_div(C, 128), 128, 0, st>>>(partial, m.S, C, rows, gamma, invstd, dgamma,
-                                                   dbeta, coef);
+  bn_bwd_finalize<<<ceil_div(C, 32), dim3(32, FIN_LANES), 0, st>>>(partial, m.S, C, rows, gamma, invstd,
+                                                                  dgamma, dbeta, coef);
   SRT_LAUNCH_CHECK();
   const int64_t nvec = rows * C / V;
-  bn_bwd_apply<T><<<stream_grid(nvec), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, (T*)dz,
-                                                    (T*)dres, nvec, C / V, mean, invstd, coef, relu);
+  bn_bwd_apply<T><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, (T*)dz,
+                                                      (T*)dres, nvec, C / V, mean, invstd, coef, scale,
+                                                      shift, relu);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 
 int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
-                const float* gamma, const float* mean, const float* invstd, int relu, void* dz,
-                void* dres, float* dgamma, float* dbeta, void* scratch, size_t scratch_bytes,
-                cudaStream_t st) {
+                const float* gamma, const float* mean, const float* invstd, const float* scale,
+                const float* shift, int relu, void* dz, void* dres, float* dgamma, float* dbeta,
+                void* scratch, size_t scratch_bytes, cudaStream_t st) {
   SRT_REQUIRE(C % 8 == 0 && rows > 0, "bn_backward: C (%d) must be a multiple of 8", C);
   SRT_REQUIRE(scratch && scratch_bytes >= bn_scratch_bytes(rows, C),
               "bn_backward: scratch too small");
-  SRT_REQUIRE(!relu || y, "bn_backward: relu mask needs y");
+  SRT_REQUIRE(!relu || y || (scale && shift), "bn_backward: the ReLU mask needs y or scale/shift");
   if (dtype == SRT_F32)
-    return bn_backward_t<float>(dy, y, z, rows, C, gamma, mean, invstd, relu, dz, dres, dgamma,
-                                dbeta, scratch, st);
-  return bn_backward_t<__nv_bfloat16>(dy, y, z, rows, C, gamma, mean, invstd, relu, dz, dres,
-                                      dgamma, dbeta, scratch, st);
+    return bn_backward_t<float>(dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz, dres,
+                                dgamma, dbeta, scratch, st);
+  return bn_backward_t<__nv_bfloat16>(dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz,
+                                      dres, dgamma, dbeta, scratch, st);
 }
 
 }  // namespace srt

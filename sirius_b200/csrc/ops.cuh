@@ -12,9 +12,9 @@ int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, 
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
              const float* scale, const float* shift, int relu, cudaStream_t st);
 int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
-                const float* gamma, const float* mean, const float* invstd, int relu, void* dz,
-                void* dres, float* dgamma, float* dbeta, void* scratch, size_t scratch_bytes,
-                cudaStream_t st);
+                const float* gamma, const float* mean, const float* invstd, const float* scale,
+                const float* shift, int relu, void* dz, void* dres, float* dgamma, float* dbeta,
+                void* scratch, size_t scratch_bytes, cudaStream_t st);
 
 int maxpool_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W, int C,
                 cudaStream_t st);

@@ -93,7 +93,44 @@ struct Step {
   int accum_pending = 0;
   size_t act_bytes = 0;
 
+  // Optional per-category device timing (CUDA events on the step's stream around each launch).
+  bool prof_on = false;
+  struct ProfRec { int cat; double work; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof_recs;
+  std::vector<cudaEvent_t> prof_pool;
+  double prof_ms[SRT_PROF_NCAT] = {0}, prof_work[SRT_PROF_NCAT] = {0};
+  long long prof_launches[SRT_PROF_NCAT] = {0};
+  template <class F>
+  int timed(int cat, double work, F&& f) {
+    if (!prof_on) return f();
+    auto get = [&]() {
+      cudaEvent_t e;
+      if (!prof_pool.empty()) { e = prof_pool.back(); prof_pool.pop_back(); }
+      else cudaEventCreate(&e);
+      return e;
+    };
+    ProfRec r{cat, work, get(), get()};
+    cudaEventRecord(r.a, stream);
+    const int rc = f();
+    cudaEventRecord(r.b, stream);
+    prof_recs.push_back(r);
+    return rc;
+  }
+  void prof_collect() {
+    cudaStreamSynchronize(stream);
+    for (auto& r : prof_recs) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+        prof_ms[r.cat] += ms; prof_work[r.cat] += r.work; prof_launches[r.cat]++;
+      }
+      prof_pool.push_back(r.a); prof_pool.push_back(r.b);
+    }
+    prof_recs.clear();
+  }
+
   ~Step() {
+    for (auto& r : prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (auto e : prof_pool) cudaEventDestroy(e);
     for (void* p : allocs) cudaFree(p);
     if (own_stream && stream) cudaStreamDestroy(stream);
   }
@@ -315,17 +352,28 @@ int Step::forward(int B) {
   auto run_unit = [&](Unit& u, const void* in, const void* residual) -> int {
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     int r;
-    if ((r = conv_fprop(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, stream))) return r;
     const int64_t rows = (int64_t)B * u.P * u.Q;
-    if ((r = bn_stats(dt, u.z, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
-                      bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift,
-                      scratch, scratch_bytes, stream)))
+    const double flops = 2.0 * rows * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
+    const double abytes = (double)rows * u.bn.C * esz;
+    if ((r = timed(SRT_PROF_CONV, flops, [&] { return conv_fprop(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, stream); })))
       return r;
-    return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream);
+    if ((r = timed(SRT_PROF_NORM, abytes, [&] {
+          return bn_stats(dt, u.z, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
+                          bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift,
+                          scratch, scratch_bytes, stream); })))
+      return r;
+    return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2), [&] {
+      return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream); });
   };
-  if ((rc = nchw_to_nhwc(dt, stage_images, x0, B, 3, cfg.image, cfg.image, kStemCpad, stream))) return rc;
+  const double img_px = (double)B * cfg.image * cfg.image;
+  if ((rc = timed(SRT_PROF_OTHER, img_px * (3 * 4 + kStemCpad * esz), [&] {
+        return nchw_to_nhwc(dt, stage_images, x0, B, 3, cfg.image, cfg.image, kStemCpad, stream); })))
+    return rc;
   if ((rc = run_unit(stem, x0, nullptr))) return rc;
-  if ((rc = maxpool_fwd(dt, stem.y, pool_y, pool_arg, B, stem.P, stem.Q, 64, stream))) return rc;
+  const double pool_in = (double)B * stem.P * stem.Q * 64 * esz;
+  if ((rc = timed(SRT_PROF_OTHER, pool_in * 1.25 + pool_in / 4 / esz, [&] {
+        return maxpool_fwd(dt, stem.y, pool_y, pool_arg, B, stem.P, stem.Q, 64, stream); })))
+    return rc;
   const void* x = pool_y;
   for (auto& k : blocks) {
     if ((rc = run_unit(k.u1, x, nullptr))) return rc;
@@ -338,10 +386,13 @@ int Step::forward(int B) {
     if ((rc = run_unit(k.u3, k.u2.y, identity))) return rc;
     x = k.u3.y;
   }
-  if ((rc = avgpool_fwd(dt, x, avg, B, final_HW, feat_C, stream))) return rc;
+  if ((rc = timed(SRT_PROF_OTHER, (double)B * (final_HW + 1) * feat_C * esz, [&] {
+        return avgpool_fwd(dt, x, avg, B, final_HW, feat_C, stream); })))
+    return rc;
   srt_conv_desc fd = {B, 1, 1, feat_C, cfg.num_classes, 1, 1, 1, 0, 1, 1};
   srt_conv_epilogue ep = {pf(fc_b), nullptr};
-  return conv_fprop(fd, dt, impl, avg, pw(fc_w), logits, &ep, stream);
+  return timed(SRT_PROF_CONV, 2.0 * B * feat_C * cfg.num_classes, [&] {
+    return conv_fprop(fd, dt, impl, avg, pw(fc_w), logits, &ep, stream); });
 }
 
 int Step::backward(int B) {
@@ -349,26 +400,45 @@ int Step::backward(int B) {
   int rc;
   // fc
   srt_conv_desc fd = {B, 1, 1, feat_C, cfg.num_classes, 1, 1, 1, 0, 1, 1};
-  if ((rc = conv_wgrad(fd, dt, impl, dlogits, avg, gf(fc_w), scratch, scratch_bytes, stream))) return rc;
-  if ((rc = colsum(dt, dlogits, B, cfg.num_classes, gf(fc_b), stream))) return rc;
+  const double fc_flops = 2.0 * B * feat_C * cfg.num_classes;
+  if ((rc = timed(SRT_PROF_WGRAD, fc_flops, [&] {
+        return conv_wgrad(fd, dt, impl, dlogits, avg, gf(fc_w), scratch, scratch_bytes, stream); })))
+    return rc;
+  if ((rc = timed(SRT_PROF_OTHER, (double)B * cfg.num_classes * esz, [&] {
+        return colsum(dt, dlogits, B, cfg.num_classes, gf(fc_b), stream); })))
+    return rc;
   const size_t fc_wt_off = n_wt - align_up((size_t)cfg.num_classes * feat_C, 64);
-  if ((rc = conv_dgrad(fd, dt, impl, dlogits, (char*)WT + fc_wt_off * esz, T[1], nullptr, stream))) return rc;
-  if ((rc = avgpool_bwd(dt, T[1], T[0], B, final_HW, feat_C, stream))) return rc;
+  if ((rc = timed(SRT_PROF_CONV, fc_flops, [&] {
+        return conv_dgrad(fd, dt, impl, dlogits, (char*)WT + fc_wt_off * esz, T[1], nullptr, stream); })))
+    return rc;
+  if ((rc = timed(SRT_PROF_OTHER, (double)B * (final_HW + 1) * feat_C * esz, [&] {
+        return avgpool_bwd(dt, T[1], T[0], B, final_HW, feat_C, stream); })))
+    return rc;
 
   // gradient through conv+BN(+ReLU): dy (w.r.t. u.y) -> dz in T[1], filter gradient into G
   auto unit_bwd = [&](Unit& u, const void* dy, const void* in, void* dz, void* dres) -> int {
     const int64_t rows = (int64_t)B * u.P * u.Q;
     int r;
-    if ((r = bn_backward(dt, dy, u.y, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean, u.bn.invstd, u.relu, dz,
-                         dres, gf(u.bn.gamma), gf(u.bn.beta), scratch, scratch_bytes, stream)))
+    // two passes over (dy, z[, y]) plus the dz (and masked-gradient) writes
+    const double abytes = (double)rows * u.bn.C * esz;
+    const double bn_bytes = abytes * ((dres ? 3 : 2) * 2 + 1 + (dres ? 1 : 0));
+    if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
+          // units without a residual recompute the ReLU mask from z instead of reading y
+          return bn_backward(dt, dy, dres ? u.y : nullptr, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean,
+                             u.bn.invstd, u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma),
+                             gf(u.bn.beta), scratch, scratch_bytes, stream); })))
       return r;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
-    return conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch, scratch_bytes, stream);
+    const double flops = 2.0 * rows * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
+    return timed(SRT_PROF_WGRAD, flops, [&] {
+      return conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch, scratch_bytes, stream); });
   };
   auto unit_dgrad = [&](Unit& u, const void* dz, void* dx, const void* addend) -> int {
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     srt_conv_epilogue ep = {nullptr, addend};
-    return conv_dgrad(d, dt, impl, dz, wt(u.conv), dx, addend ? &ep : nullptr, stream);
+    const double flops = 2.0 * B * u.P * u.Q * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
+    return timed(SRT_PROF_CONV, flops, [&] {
+      return conv_dgrad(d, dt, impl, dz, wt(u.conv), dx, addend ? &ep : nullptr, stream); });
   };
 
   for (int i = (int)blocks.size() - 1; i >= 0; --i) {
@@ -390,7 +460,10 @@ int Step::backward(int B) {
     void* t = T[0]; T[0] = T[4]; T[4] = t;
   }
   // stem
-  if ((rc = maxpool_bwd(dt, T[0], pool_arg, T[3], B, stem.P, stem.Q, 64, stream))) return rc;
+  const double pool_in = (double)B * stem.P * stem.Q * 64 * esz;
+  if ((rc = timed(SRT_PROF_OTHER, pool_in * 1.25 + pool_in / 4 / esz, [&] {
+        return maxpool_bwd(dt, T[0], pool_arg, T[3], B, stem.P, stem.Q, 64, stream); })))
+    return rc;
   return unit_bwd(stem, T[3], x0, T[1], nullptr);
 }
 
@@ -540,8 +613,10 @@ int srt_step_optimizer(srt_step* h) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s, "optimizer: null handle");
   const float* grad = s->accum_pending > 0 ? s->ACC : s->G;
-  int rc = sgd_momentum(s->P, grad, s->M, s->cfg.dtype == SRT_BF16 ? s->Pw : nullptr, (int64_t)s->n_flat,
-                        s->cfg.lr, s->cfg.momentum, s->cfg.weight_decay, s->opt_steps == 0, s->stream);
+  const bool bf = s->cfg.dtype == SRT_BF16;
+  int rc = s->timed(SRT_PROF_OPTIM, (double)s->n_flat * (bf ? 22 : 20), [&] {
+    return sgd_momentum(s->P, grad, s->M, bf ? s->Pw : nullptr, (int64_t)s->n_flat, s->cfg.lr, s->cfg.momentum,
+                        s->cfg.weight_decay, s->opt_steps == 0, s->stream); });
   if (rc) return rc;
   if (s->accum_pending > 0) {
     SRT_CHECK_CUDA(cudaMemsetAsync(s->ACC, 0, s->n_flat * 4, s->stream));
@@ -550,7 +625,8 @@ int srt_step_optimizer(srt_step* h) {
   s->opt_steps++;
   // transposed filters follow the updated parameters (the bf16 copy was written by the optimizer)
   auto tr = [&](const ConvL& c) -> int {
-    return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, s->stream);
+    return s->timed(SRT_PROF_OPTIM, 2.0 * c.K * c.R * c.S * c.C * s->esz, [&] {
+      return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, s->stream); });
   };
   if ((rc = tr(s->stem.conv))) return rc;
   for (auto& k : s->blocks) {
@@ -594,6 +670,36 @@ int srt_step_logits(srt_step* h, float* host, int B) {
       memcpy(&host[i], &u, 4);
     }
   }
+  return SRT_OK;
+}
+
+int srt_step_profile(srt_step* h, int enable) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "profile: null handle");
+  if (s->prof_on) s->prof_collect();
+  s->prof_on = enable != 0;
+  if (enable) {
+    for (int i = 0; i < SRT_PROF_NCAT; ++i) { s->prof_ms[i] = 0; s->prof_work[i] = 0; s->prof_launches[i] = 0; }
+  }
+  return SRT_OK;
+}
+
+int srt_step_profile_read(srt_step* h, double ms[SRT_PROF_NCAT], double work[SRT_PROF_NCAT],
+                          int64_t launches[SRT_PROF_NCAT]) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && ms && work && launches, "profile_read: null argument");
+  s->prof_collect();
+  for (int i = 0; i < SRT_PROF_NCAT; ++i) {
+    ms[i] = s->prof_ms[i]; work[i] = s->prof_work[i]; launches[i] = s->prof_launches[i];
+  }
+  return SRT_OK;
+}
+
+int srt_step_grad_buffer(srt_step* h, int accumulated, void** ptr, int64_t* n) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && ptr && n, "grad_buffer: null argument");
+  *ptr = accumulated ? (void*)s->ACC : (void*)s->G;
+  *n = (int64_t)s->n_flat;
   return SRT_OK;
 }
 

@@ -96,7 +96,7 @@ def bn_apply(z, scale, shift, residual=None, relu=True):
     return y
 
 
-def bn_backward(dy, y, z, gamma, mean, invstd, relu=True, want_dresidual=False):
+def bn_backward(dy, y, z, gamma, mean, invstd, relu=True, want_dresidual=False, scale=None, shift=None):
     Cc = z.shape[-1]
     rows = z.numel() // Cc
     dz = torch.empty_like(z)
@@ -105,7 +105,7 @@ def bn_backward(dy, y, z, gamma, mean, invstd, relu=True, want_dresidual=False):
     dbeta = torch.empty_like(dgamma)
     scratch, n = bn_scratch(rows, Cc, z.device)
     call("srt_bn_backward", _dt(z), _p(dy), _p(y), _p(z), rows, Cc, _p(gamma), _p(mean), _p(invstd),
-         int(relu), _p(dz), _p(dres), _p(dgamma), _p(dbeta), _p(scratch), n, _stream())
+         _p(scale), _p(shift), int(relu), _p(dz), _p(dres), _p(dgamma), _p(dbeta), _p(scratch), n, _stream())
     return dz, dres, dgamma, dbeta
 
 

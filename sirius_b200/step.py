@@ -37,7 +37,12 @@ register({
     "srt_step_logits": (None, [_vp, _vp, _i]),
     "srt_step_synchronize": (None, [_vp]),
     "srt_step_memory_bytes": (_i64, [_vp, _i]),
+    "srt_step_grad_buffer": (None, [_vp, _i, C.POINTER(_vp), C.POINTER(_i64)]),
+    "srt_step_profile": (None, [_vp, _i]),
+    "srt_step_profile_read": (None, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(_i64)]),
+    "srt_launch_count": (_i64, []),
 })
+PROF_CATS = ("conv_fprop_dgrad", "conv_wgrad", "batchnorm", "other", "optimizer")
 
 RESNET_LAYERS = {"resnet50": (3, 4, 6, 3), "resnet101": (3, 4, 23, 3), "resnet152": (3, 8, 36, 3)}
 GET_VALUE, GET_GRAD, GET_ACCUM, GET_MOMENTUM = 0, 1, 2, 3
@@ -157,6 +162,19 @@ class ResNetStep:
     def memory_bytes(self) -> tuple[int, int]:
         l = _lib.lib()
         return l.srt_step_memory_bytes(self._h, 0), l.srt_step_memory_bytes(self._h, 1)
+
+    def grad_buffer(self, accumulated=False) -> tuple[int, int]:
+        p, n = _vp(), _i64()
+        call("srt_step_grad_buffer", self._h, int(accumulated), C.byref(p), C.byref(n))
+        return p.value, n.value
+
+    def profile(self, enable: bool) -> None:
+        call("srt_step_profile", self._h, int(enable))
+
+    def profile_read(self) -> dict:
+        ms, work, n = (C.c_double * 5)(), (C.c_double * 5)(), (_i64 * 5)()
+        call("srt_step_profile_read", self._h, ms, work, n)
+        return {c: {"ms": ms[i], "work": work[i], "launches": n[i]} for i, c in enumerate(PROF_CATS)}
 
     def train_step(self, images, labels) -> float:
         """Whole-batch step through host buffers: H2D, forward, backward, SGD, loss readback."""

@@ -24,11 +24,11 @@ CASES = {
 }
 
 
-def run_precision(arch, batch, image, steps, double):
+def run_precision(arch, batch, image, steps, double, autocast=False):
     model = O.build_model(arch, 0, double=double)
     batches = O.make_batches(batch, steps, image, double=double)
-    loss0, grads = O.first_step_gradients(model, batches[0])
-    losses = O.train_steps(model, batches)
+    loss0, grads = O.first_step_gradients(model, batches[0], autocast_bf16=autocast)
+    losses = O.train_steps(model, batches, autocast_bf16=autocast)
     return {"loss0": loss0, "losses": losses, "grad0": O.summarize(grads, samples=4),
             "final": O.summarize(O.state_arrays(model), samples=4)}
 
@@ -39,10 +39,13 @@ def run(name):
     doc = {"case": name, "arch": arch, "batch": batch, "image": image, "steps": steps, "seed": 0,
            "torch": torch.__version__, "optimizer": {"lr": 0.1, "momentum": 0.9, "weight_decay": 1e-4},
            "fp32": run_precision(arch, batch, image, steps, False),
-           "fp64": run_precision(arch, batch, image, steps, True)}
+           "fp64": run_precision(arch, batch, image, steps, True),
+           # PyTorch's own reduced-precision path on the CPU: how far bf16 training drifts from exact
+           "bf16_autocast": run_precision(arch, batch, image, steps, False, autocast=True)}
     with open(os.path.join(HERE, name + ".json"), "w") as f:
         json.dump(doc, f)
-    print(name, "fp32 losses", doc["fp32"]["losses"], "fp64 losses", doc["fp64"]["losses"])
+    print(name, "fp32 losses", doc["fp32"]["losses"], "fp64 losses", doc["fp64"]["losses"],
+          "bf16 autocast losses", doc["bf16_autocast"]["losses"])
 
 
 if __name__ == "__main__":

@@ -169,6 +169,24 @@ def test_batchnorm_fwd_bwd(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_batchnorm_mask_recomputed_from_z_is_identical(dtype):
+    """Units without a residual skip reading y in the backward pass: the ReLU mask recomputed from
+    z*scale + shift must give bit-identical results to the mask read from the stored y."""
+    g = torch.Generator().manual_seed(7)
+    shape = (4, 9, 9, 128)
+    z = (torch.randn(shape, generator=g) * 2).to(DEV, dtype)
+    dy = torch.randn(shape, generator=g).to(DEV, dtype)
+    gamma = (torch.rand(128, generator=g) + 0.5).to(DEV)
+    beta = torch.randn(128, generator=g).to(DEV)
+    mean, invstd, scale, shift = ops.bn_stats(z, gamma, beta, None, None)
+    y = ops.bn_apply(z, scale, shift, relu=True)
+    a = ops.bn_backward(dy, y, z, gamma, mean, invstd, relu=True)
+    b = ops.bn_backward(dy, None, z, gamma, mean, invstd, relu=True, scale=scale, shift=shift)
+    torch.cuda.synchronize()
+    assert torch.equal(a[0], b[0]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_pools(dtype):
     g = torch.Generator().manual_seed(2)
     x = torch.randn(2, 13, 16, 16, generator=g).clamp_min(0)  # zeros create ties like post-ReLU data

@@ -12,7 +12,8 @@ namespace {
 
 constexpr int NT = 256;
 constexpr int ROWS_PER_THREAD = 8;   // loads in flight per thread
-constexpr int FIN_LANES = 32;        // slab lanes per channel in the finalize kernels
+constexpr int FIN_CH = 8;            // channels per finalize block (8 x 16 B = one 128-byte line)
+constexpr int FIN_LANES = 128;       // slab lanes per channel in the finalize kernels
 
 struct RowMap {
   int CV;    // 16-byte vectors per row
@@ -60,10 +61,10 @@ __device__ inline void block_reduce_store(const float (&a)[V], const float (&b)[
   }
 }
 
-// Sum of the S slab partials of channel c: FIN_LANES lanes stride over the slabs, then a fixed-order
-// combine through shared memory. Call with blockDim = (32 channels, FIN_LANES).
+// Sum of the S slab partials of channel c: FIN_LANES lanes stride over the slabs, then a fixed-shape
+// tree through shared memory (deterministic). Call with blockDim = (FIN_CH channels, FIN_LANES).
 __device__ inline double2 reduce_partials(const double* __restrict__ partial, int S, int C, int c) {
-  __shared__ double2 sh[FIN_LANES][33];
+  __shared__ double2 sh[FIN_LANES][FIN_CH];
   double2 acc = make_double2(0.0, 0.0);
   if (c < C) {
     const double2* p = reinterpret_cast<const double2*>(partial);
@@ -76,11 +77,18 @@ __device__ inline double2 reduce_partials(const double* __restrict__ partial, in
   }
   sh[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
-  double2 tot = make_double2(0.0, 0.0);
-  if (threadIdx.y == 0) {
-    for (int l = 0; l < FIN_LANES; ++l) { tot.x += sh[l][threadIdx.x].x; tot.y += sh[l][threadIdx.x].y; }
+#pragma unroll
+  for (int o = FIN_LANES / 2; o > 0; o >>= 1) {
+    if ((int)threadIdx.y < o) {
+      double2 a = sh[threadIdx.y][threadIdx.x];
+      const double2 b = sh[threadIdx.y + o][threadIdx.x];
+      a.x += b.x;
+      a.y += b.y;
+      sh[threadIdx.y][threadIdx.x] = a;
+    }
+    __syncthreads();
   }
-  return tot;
+  return sh[0][threadIdx.x];
 }
 
 template <typename T>
@@ -115,12 +123,12 @@ bn_stats_partial(const T* __restrict__ z, int64_t rows, int C, RowMap m, double*
   block_reduce_store<V>(s, q, m, C, partial);
 }
 
-__global__ void __launch_bounds__(32 * FIN_LANES)
+__global__ void __launch_bounds__(FIN_CH * FIN_LANES)
 bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
                   const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                   float momentum, float* running_mean, float* running_var, float* mean, float* invstd,
                   float* scale, float* shift) {
-  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int c = blockIdx.x * FIN_CH + threadIdx.x;
   const double2 tot = reduce_partials(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
   const double mu = tot.x / (double)rows;
@@ -203,7 +211,14 @@ __device__ __forceinline__ void apply_relu_mask(float (&g)[V], const float (&x)[
     for (int v = 0; v < V; ++v) g[v] = yy[v] > 0.f ? g[v] : 0.f;
   } else {
 #pragma unroll
-    for (int v = 0; v < V; ++v) g[v] = fmaf(x[v], scale[c0 + v], shift[c0 + v]) > 0.f ? g[v] : 0.f;
+    for (int v = 0; v < V; v += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(scale + c0 + v);
+      const float4 b = *reinterpret_cast<const float4*>(shift + c0 + v);
+      g[v] = fmaf(x[v], a.x, b.x) > 0.f ? g[v] : 0.f;
+      g[v + 1] = fmaf(x[v + 1], a.y, b.y) > 0.f ? g[v + 1] : 0.f;
+      g[v + 2] = fmaf(x[v + 2], a.z, b.z) > 0.f ? g[v + 2] : 0.f;
+      g[v + 3] = fmaf(x[v + 3], a.w, b.w) > 0.f ? g[v + 3] : 0.f;
+    }
   }
 }
 
@@ -253,28 +268,30 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
   block_reduce_store<V>(sg, sgx, m, C, partial);
 }
 
-// coef[c*4 + {0,1,2}] = gamma*invstd, dbeta/rows, dgamma/rows
-__global__ void __launch_bounds__(32 * FIN_LANES)
+__global__ void __launch_bounds__(FIN_CH * FIN_LANES)
 bn_bwd_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
                 const float* __restrict__ gamma, const float* __restrict__ invstd, float* dgamma,
                 float* dbeta, float* coef) {
-  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int c = blockIdx.x * FIN_CH + threadIdx.x;
   const double2 tot = reduce_partials(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
   if (dbeta) dbeta[c] = (float)tot.x;
   if (dgamma) dgamma[c] = (float)tot.y;
+  // dz = k0*(g - mean_g - xhat*mean_gx), xhat = (x - mean)*invstd, stored as three per-channel
+  // vectors so the elementwise pass reads them with 16-byte loads: dz = ka*g + kb*(x - mean) + kd
   const float g = gamma ? gamma[c] : 1.f;
-  coef[c * 4 + 0] = g * invstd[c];
-  coef[c * 4 + 1] = (float)(tot.x / (double)rows);
-  coef[c * 4 + 2] = (float)(tot.y / (double)rows);
-  coef[c * 4 + 3] = 0.f;
+  const float k0 = g * invstd[c];
+  const float mg = (float)(tot.x / (double)rows), mgx = (float)(tot.y / (double)rows);
+  coef[c] = k0;
+  coef[C + c] = -k0 * mgx * invstd[c];
+  coef[2 * C + c] = -k0 * mg;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(NT)
 bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z, T* __restrict__ dz,
-             T* __restrict__ dres, int64_t nvec, int CV, const float* __restrict__ mean,
-             const float* __restrict__ invstd, const float* __restrict__ coef,
+             T* __restrict__ dres, int64_t nvec, int CV, int C, const float* __restrict__ mean,
+             const float* __restrict__ coef,
              const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
   constexpr int V = Vec16<T>::N;
   const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
@@ -300,11 +317,16 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
     }
     float out[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
+    for (int v = 0; v < V; v += 4) {
       const int c = cv * V + v;
-      const float4 k = *reinterpret_cast<const float4*>(coef + c * 4);
-      const float xhat = (x[v] - mean[c]) * invstd[c];
-      out[v] = k.x * (g[v] - k.y - xhat * k.z);
+      const float4 ka = *reinterpret_cast<const float4*>(coef + c);
+      const float4 kb = *reinterpret_cast<const float4*>(coef + C + c);
+      const float4 kd = *reinterpret_cast<const float4*>(coef + 2 * C + c);
+      const float4 mu = *reinterpret_cast<const float4*>(mean + c);
+      out[v] = fmaf(ka.x, g[v], fmaf(kb.x, x[v] - mu.x, kd.x));
+      out[v + 1] = fmaf(ka.y, g[v + 1], fmaf(kb.y, x[v + 1] - mu.y, kd.y));
+      out[v + 2] = fmaf(ka.z, g[v + 2], fmaf(kb.z, x[v + 2] - mu.z, kd.z));
+      out[v + 3] = fmaf(ka.w, g[v + 3], fmaf(kb.w, x[v + 3] - mu.w, kd.w));
     }
     Vec16<T> o;
     o.pack(out);
@@ -335,7 +357,7 @@ static int bn_stats_t(const void* z, int64_t rows, int C, const float* gamma, co
   double* partial = (double*)scratch;
   bn_stats_partial<T><<<dim3(m.S, m.GY), NT, 0, st>>>((const T*)z, rows, C, m, partial);
   SRT_LAUNCH_CHECK();
-  bn_stats_finalize<<<ceil_div(C, 32), dim3(32, FIN_LANES), 0, st>>>(
+  bn_stats_finalize<<<ceil_div(C, FIN_CH), dim3(FIN_CH, FIN_LANES), 0, st>>>(
       partial, m.S, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -387,13 +409,13 @@ static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t r
   bn_bwd_partial<T><<<dim3(m.S, m.GY), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, rows, C,
                                                     m, mean, invstd, scale, shift, relu, partial);
   SRT_LAUNCH_CHECK();
-  bn_bwd_finalize<<<ceil_div(C, 32), dim3(32, FIN_LANES), 0, st>>>(partial, m.S, C, rows, gamma, invstd,
+  bn_bwd_finalize<<<ceil_div(C, FIN_CH), dim3(FIN_CH, FIN_LANES), 0, st>>>(partial, m.S, C, rows, gamma, invstd,
                                                                   dgamma, dbeta, coef);
   SRT_LAUNCH_CHECK();
   const int64_t nvec = rows * C / V;
   bn_bwd_apply<T><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, (T*)dz,
-                                                      (T*)dres, nvec, C / V, mean, invstd, coef, scale,
-                                                      shift, relu);
+                                                      (T*)dres, nvec, C / V, C, mean, coef, scale, shift,
+                                                      relu);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

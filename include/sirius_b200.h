@@ -141,6 +141,9 @@ int srt_get_sm_mask(uint64_t mask[3]);
 int srt_tc_status(int* status);
 /* Test hook: route 1x1 stride-1 convolutions through the gather path instead of TMA for A. */
 int srt_debug_force_gather(int on);
+/* Test hook: fprop/dgrad kernel variant (0 = persistent CTA per SM, 1 = one output tile per CTA)
+ * and tile width (0 = heuristic, else 64, 128 or 256 output channels per tile). */
+int srt_debug_fwd_variant(int variant, int bn);
 
 /* ---- training-step executor (replaces the body of the reference's training loop:
  *      model(images) / criterion / backward / optimizer stage, train/resnet152.py:84-91, with

@@ -1,5 +1,6 @@
 """Per-layer micro-benchmark of the convolution kernels on the ResNet-152 layer shapes.
 
+
     python -m sirius_b200.bench_ops [--batch 64] [--case NAME] [--pass fprop|dgrad|wgrad|all] [--iters 20]
 
 Each case is timed with CUDA events on the launching stream after warm-up; between timed launches a
@@ -33,6 +34,10 @@ CASES = {
     "l4_1x1_expand": (7, 7, 512, 2048, 1, 1, 0),
     "l3_3x3_s2": (28, 28, 256, 256, 3, 2, 1),
     "l3_ds_1x1_s2": (28, 28, 512, 1024, 1, 2, 0),
+    # synthetic shapes for pipeline studies: long reductions, one wave of tiles
+    "syn_1x1_k4096_n256": (14, 14, 4096, 256, 1, 1, 0),
+    "syn_1x1_k4096_n128": (14, 14, 4096, 128, 1, 1, 0),
+    "syn_1x1_k4096_n64": (14, 14, 4096, 64, 1, 1, 0),
 }
 
 
@@ -64,7 +69,9 @@ def run_case(name, batch, which, iters, flush):
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
-        total = 0.0
+        # enqueue every (flush, launch) pair before synchronising, so the host runs ahead of the GPU
+        # and the events bracket device time only
+        evs = []
         for _ in range(iters):
             if scrub is not None:
                 scrub.fill_(1)
@@ -72,8 +79,9 @@ def run_case(name, batch, which, iters, flush):
             e0.record()
             fn()
             e1.record()
-            e1.synchronize()
-            total += e0.elapsed_time(e1)
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        total = sum(a.elapsed_time(b) for a, b in evs)
         us = total / iters * 1e3
         rec = {"case": name, "pass": p, "batch": batch, "us": round(us, 2),
                "tflops": round(flops / us / 1e6, 1), "min_gbytes_per_s": round(io[p] / us / 1e3, 1),

@@ -48,6 +48,8 @@ void set_current_sm_mask(const SmMask& m) {
 
 int tc_status_fetch(int* out);
 void tc_set_force_gather(int v);
+void tc_set_fwd_variant(int variant, int bn);
+void tc_set_no_load(int v);
 
 static int check_desc(const srt_conv_desc& d) {
   SRT_REQUIRE(d.N > 0 && d.H > 0 && d.W > 0 && d.C > 0 && d.K > 0 && d.R > 0 && d.S > 0 &&
@@ -260,6 +262,16 @@ int srt_tc_status(int* status) {
 }
 int srt_debug_force_gather(int on) {
   tc_set_force_gather(on);
+  return SRT_OK;
+}
+int srt_debug_no_load(int on) {
+  tc_set_no_load(on);
+  return SRT_OK;
+}
+int srt_debug_fwd_variant(int variant, int bn) {
+  SRT_REQUIRE(variant == 0 || variant == 1, "fwd_variant: 0 (persistent) or 1 (tile per CTA)");
+  SRT_REQUIRE(bn == 0 || bn == 64 || bn == 128 || bn == 256, "fwd_variant: bn must be 0, 64, 128 or 256");
+  tc_set_fwd_variant(variant, bn);
   return SRT_OK;
 }
 

@@ -430,6 +430,295 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Persistent fprop/dgrad kernel: one CTA per SM walks the output tiles t = blockIdx.x, +gridDim.x,
+// ... (t = m_tile * n_tiles + n_tile). 320 threads:
+//   warp 0      TMA producer: B tile every stage, A tile too when it is a plain matrix block
+//   warp 1      tensor-memory allocation, tcgen05.mma issue (lane 0)
+//   warps 2-5   epilogue: TMEM -> registers -> (+bias, +addend) -> bf16 -> swizzled smem -> TMA store
+//   warps 6-9   A gather producers (cp.async), idle when A comes by TMA
+// The shared-memory stage ring runs across tile boundaries, and the accumulator is double-buffered
+// in tensor memory (2 x BN columns), so the loads of tile i+1 and the MMAs of tile i+1 overlap the
+// epilogue of tile i.
+constexpr int P_THREADS = 320;
+constexpr int OUT_SLAB_BYTES = BM * 128;  // 128 rows x 64 bf16
+
+struct PersistParams {
+  GatherGeom g;
+  const bf16* src;
+  const float* bias;
+  const bf16* addend;
+  int k_blocks;
+  int a_tma;
+  int m_tiles, n_tiles;
+  int no_load;  // timing experiment: hand stages over without loading them (results are garbage)
+  int* status;
+};
+
+enum WaitCode2 { W_MMA_TMEM_EMPTY = 5 };
+
+template <int BN, int NS>
+constexpr size_t persist_smem_bytes() {
+  return 1024 + (size_t)NS * (A_STAGE_BYTES + BN * BK * 2) + 2 * OUT_SLAB_BYTES + (2 * NS + 4) * 8 + 16;
+}
+
+template <int BN, int NS>
+__global__ void __launch_bounds__(P_THREADS, 1)
+igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_a,
+                     const __grid_constant__ CUtensorMap tmap_d) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  constexpr int PLAG = NS - 2;  // cp.async groups in flight per gather thread
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = base;
+  uint8_t* sB = sA + NS * A_STAGE_BYTES;
+  uint8_t* sOut = sB + NS * B_STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(sOut + 2 * OUT_SLAB_BYTES);
+  uint64_t* empty = full + NS;
+  uint64_t* tmem_full = empty + NS;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;  // [2]
+  uint32_t* tmem_ptr = (uint32_t*)(tmem_empty + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const GatherGeom& g = p.g;
+  const int nkb = p.k_blocks;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (tid == 0) {
+    const uint32_t full_count = p.a_tma ? 1u : (uint32_t)(NPROD + 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(smem_u32(&full[s]), full_count);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full[b]), 1);
+      mbar_init(smem_u32(&tmem_empty[b]), NPROD);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_d);
+    if (p.a_tma) tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr), 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)B_STAGE_BYTES + (p.a_tma ? (uint32_t)A_STAGE_BYTES : 0u);
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / p.n_tiles) * BM, n0 = (t % p.n_tiles) * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % NS;
+          const uint32_t ph = (uint32_t)(it / NS) & 1u;
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&full[s]);
+          if (p.no_load) { mbar_arrive(bar); continue; }
+          mbar_arrive_expect_tx(bar, bytes);
+          tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
+          if (p.a_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      int it = 0, tc = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tc) {
+        const int b = tc & 1;
+        const uint32_t aph = (uint32_t)(tc >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&tmem_empty[b]), aph ^ 1u, p.status, W_MMA_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_base + (uint32_t)(b * BN);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % NS;
+          const uint32_t ph = (uint32_t)(it / NS) & 1u;
+          if (!mbar_wait(smem_u32(&full[s]), ph, p.status, W_MMA_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a0 = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b0 = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc_sw128(a0 + k * 32, 0, 1024);
+            const uint64_t bd = make_smem_desc_sw128(b0 + k * 32, 0, 1024);
+            umma_bf16(acc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty[s]));
+        }
+        umma_commit(smem_u32(&tmem_full[b]));
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;          // row of the tile held by this thread
+    const int et = tid - 64;                // 0..127
+    const bool issuer = et == 0;
+    const uint32_t swz_row = (uint32_t)row * 128u;
+    int tc = 0, slab_count = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tc) {
+      const int m0 = (t / p.n_tiles) * BM, n0 = (t % p.n_tiles) * BN;
+      const int b = tc & 1;
+      if (ok) ok = mbar_wait(smem_u32(&tmem_full[b]), (uint32_t)(tc >> 1) & 1u, p.status, W_EPI_TMEM);
+      tc_fence_after_sync();
+      const int m = m0 + row;
+      constexpr int NSLAB = BN / 64;
+#pragma unroll 1
+      for (int c = 0; c < NSLAB; ++c) {
+        const int col0 = n0 + c * 64;
+        const bool live = col0 < g.Nout;  // uniform across the epilogue threads
+        const int buf = slab_count & 1;
+        uint8_t* stage = sOut + buf * OUT_SLAB_BYTES;
+        if (live) {
+          // the store that read this staging buffer two slabs ago must be done with it
+          if (issuer) bulk_wait_group_read<1>();
+          named_bar_sync(1, NPROD);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t acc[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c * 64 + h * 32), acc);
+          tmem_ld_wait();
+          if (c == NSLAB - 1 && h == 1) {
+            // last read of this accumulator: hand it back to the MMA warp
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&tmem_empty[b]));
+          }
+          if (!live) continue;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + h * 32 + v * 8;
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
+            if (col < g.Nout) {
+              if (p.bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
+              }
+              if (p.addend && m < g.M) {
+                Vec16<bf16> av;
+                av.load(p.addend + (size_t)m * g.Nout + col);
+                float af[8];
+                av.unpack(af);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] += af[e];
+              }
+            }
+            Vec16<bf16> ov;
+            ov.pack(f);
+            const int chunk = h * 4 + v;
+            *reinterpret_cast<uint4*>(stage + swz_row + (uint32_t)((chunk ^ (row & 7)) << 4)) = ov.raw;
+          }
+        }
+        if (live) {
+          fence_proxy_async_smem();
+          named_bar_sync(1, NPROD);
+          if (issuer) {
+            tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
+            bulk_commit_group();
+          }
+          ++slab_count;
+        }
+      }
+    }
+    if (issuer) bulk_wait_group<0>();
+  } else {
+    // ---------------- A gather producers ----------------
+    if (!p.a_tma) {
+      const int pt = tid - 192;  // 0..127
+      const int j = pt & 7, r0 = pt >> 3;
+      const uint32_t swz = (uint32_t)((j ^ (r0 & 7)) << 4);
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / p.n_tiles) * BM;
+        int pixb[8], ih0[8], iw0[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m0 + r0 + 16 * i;
+          if (m < g.M) {
+            RowCoord rc = decode_row(g, m);
+            pixb[i] = rc.n * g.src_h * g.src_w;
+            ih0[i] = g.dgrad ? rc.oh + g.pad : rc.oh * g.stride - g.pad;
+            iw0[i] = g.dgrad ? rc.ow + g.pad : rc.ow * g.stride - g.pad;
+          } else {
+            pixb[i] = 0;
+            ih0[i] = -(1 << 20);
+            iw0[i] = 0;
+          }
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % NS;
+          const uint32_t ph = (uint32_t)(it / NS) & 1u;
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) { ok = false; break; }
+          const int kk = kb * BK + j * 8;
+          const bool k_ok = kk < g.Kg;
+          const int tap = kk / g.src_c, c = kk - tap * g.src_c;
+          const int r = tap / g.S, sf = tap - r * g.S;
+          const uint32_t dst0 = smem_u32(sA + s * A_STAGE_BYTES) + (uint32_t)r0 * 128u + swz;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            int ih, iw;
+            bool v = k_ok;
+            if (!g.dgrad) {
+              ih = ih0[i] + r;
+              iw = iw0[i] + sf;
+            } else {
+              const int th = ih0[i] - r, tw = iw0[i] - sf;
+              v = v && th >= 0 && tw >= 0;
+              if (g.stride > 1) {
+                v = v && (th % g.stride == 0) && (tw % g.stride == 0);
+                ih = th / g.stride;
+                iw = tw / g.stride;
+              } else {
+                ih = th;
+                iw = tw;
+              }
+            }
+            v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
+            const bf16* ptr = v ? p.src + ((size_t)(pixb[i] + ih * g.src_w + iw) * g.src_c + c) : p.src;
+            if (!p.no_load) cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
+          }
+          cp_async_commit();
+          if (it >= PLAG) {
+            cp_async_wait<PLAG>();
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&full[(it - PLAG) % NS]));
+          }
+        }
+      }
+      // drain: every stage issued but not yet handed over
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      for (int k = it > PLAG ? it - PLAG : 0; k < it; ++k) mbar_arrive(smem_u32(&full[k % NS]));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -473,6 +762,11 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols
   return SRT_OK;
 }
 
+// Output matrix [rows][cols] bf16 for TMA stores: box = 64 cols x 128 rows, 128B swizzle.
+int make_tmap_store(CUtensorMap* tm, void* base, uint64_t rows, uint64_t cols) {
+  return make_tmap_2d(tm, base, rows, cols, 128);
+}
+
 int* status_ptr() {
   static int* ptr = nullptr;
   static std::once_flag once;
@@ -513,6 +807,40 @@ int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, int splits, cudaS
   return SRT_OK;
 }
 
+template <int BN, int NS>
+int launch_persistent(const PersistParams& p, const CUtensorMap& tb, const CUtensorMap& ta,
+                      const CUtensorMap& td, cudaStream_t st) {
+  constexpr size_t smem = persist_smem_bytes<BN, NS>();
+  static_assert(smem <= 232448, "persistent igemm: shared memory budget exceeded");
+  static bool configured = false;
+  if (!configured) {
+    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_fwd_persistent<BN, NS>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  igemm_fwd_persistent<BN, NS><<<grid, P_THREADS, smem, st>>>(p, tb, ta, td);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+// Tile width: fewest (waves x bytes staged per k-block), the quantity that bounds an L2-fed main loop.
+int pick_bn(int M, int N, int forced) {
+  if (forced == 64 || forced == 128 || forced == 256) return forced;
+  const int mt = ceil_div(M, BM), sms = sm_count();
+  int best = 64;
+  double best_cost = 1e30;
+  for (int bn : {64, 128, 256}) {
+    if (bn > 64 && bn / 2 >= N) continue;  // wider than the matrix: wasted columns
+    const int tiles = mt * ceil_div(N, bn);
+    const int waves = ceil_div(tiles, sms);
+    const double cost = (double)waves * (16.0 + bn / 8.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
 struct WgradPlan {
   int bn, splits, pix_per_split;
 };
@@ -548,12 +876,50 @@ int tc_status_fetch(int* out) {
 
 static int g_force_gather = 0;  // test hook: route 1x1 stride-1 problems through the gather path
 void tc_set_force_gather(int v) { g_force_gather = v; }
+static int g_fwd_variant = 0;   // 0: persistent kernel, 1: one tile per CTA (kept for comparison)
+static int g_force_bn = 0;      // 0: heuristic, else 64/128/256
+static int g_no_load = 0;       // timing experiment, see PersistParams::no_load
+void tc_set_no_load(int v) { g_no_load = v; }
+void tc_set_fwd_variant(int variant, int bn) { g_fwd_variant = variant; g_force_bn = bn; }
+
+static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, const void* Bm, void* D,
+                                          const srt_conv_epilogue* ep, cudaStream_t st) {
+  PersistParams p;
+  p.g = g;
+  p.src = (const bf16*)src;
+  p.bias = ep ? ep->bias : nullptr;
+  p.addend = ep ? (const bf16*)ep->addend : nullptr;
+  p.k_blocks = ceil_div(g.Kg, BK);
+  p.no_load = g_no_load;
+  p.status = status_ptr();
+  SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
+  const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
+  p.a_tma = (plain && !g_force_gather) ? 1 : 0;
+  const int bn = pick_bn(g.M, g.Nout, g_force_bn);
+  p.m_tiles = ceil_div(g.M, BM);
+  p.n_tiles = ceil_div(g.Nout, bn);
+  CUtensorMap tb, ta, td;
+  int rc = make_tmap_2d(&tb, Bm, (uint64_t)g.Nout, (uint64_t)g.Kg, (uint32_t)bn);
+  if (rc != SRT_OK) return rc;
+  if (p.a_tma) {
+    rc = make_tmap_2d(&ta, src, (uint64_t)g.M, (uint64_t)g.Kg, (uint32_t)BM);
+    if (rc != SRT_OK) return rc;
+  } else {
+    ta = tb;
+  }
+  rc = make_tmap_store(&td, D, (uint64_t)g.M, (uint64_t)g.Nout);
+  if (rc != SRT_OK) return rc;
+  if (bn == 64) return launch_persistent<64, 6>(p, tb, ta, td, st);
+  if (bn == 128) return launch_persistent<128, 5>(p, tb, ta, td, st);
+  return launch_persistent<256, 4>(p, tb, ta, td, st);
+}
 
 int conv_gather_gemm_tc(const GatherGeom& g, const void* src, const void* Bm, void* D,
                         const srt_conv_epilogue* ep, cudaStream_t st) {
   SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
               "tcgen05 conv: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
   SRT_REQUIRE(((uintptr_t)src & 15) == 0 && ((uintptr_t)D & 15) == 0, "tcgen05 conv: unaligned tensor");
+  if (g_fwd_variant == 0) return conv_gather_gemm_tc_persistent(g, src, Bm, D, ep, st);
   FwdParams p;
   p.g = g;
   p.src = (const bf16*)src;

@@ -73,9 +73,7 @@ def test_conv_fp32_simt(case):
     assert _err(dw, dw_ref) < 2e-5
 
 
-@pytest.mark.parametrize("impl", [IMPL_SIMT, IMPL_TCGEN05], ids=["simt", "tcgen05"])
-@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
-def test_conv_bf16(case, impl):
+def _run_bf16(case, impl):
     stride, pad = case[8], case[9]
     x, w, dy = _mk(case, torch.bfloat16)
     y_ref, dx_ref, dw_ref = _ref(x, w, dy, stride, pad)
@@ -90,6 +88,41 @@ def test_conv_bf16(case, impl):
     print(case[0], "impl", impl, "rel-max errors y/dx/dw:", errs)
     assert errs[0] < 1e-2 and errs[1] < 1e-2
     assert errs[2] < 2e-3  # fp32 output
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
+def test_conv_bf16_simt(case):
+    _run_bf16(case, IMPL_SIMT)
+
+
+# fprop/dgrad kernel variants: persistent CTA per SM (default) with the tile width chosen by the
+# heuristic or forced, and the one-tile-per-CTA kernel
+VARIANTS = {"persistent": (0, 0), "persistent_bn64": (0, 64), "persistent_bn128": (0, 128),
+            "persistent_bn256": (0, 256), "tile_per_cta": (1, 0)}
+
+
+@pytest.mark.parametrize("variant", list(VARIANTS), ids=list(VARIANTS))
+@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
+def test_conv_bf16_tcgen05(case, variant):
+    lib().srt_debug_fwd_variant(*VARIANTS[variant])
+    try:
+        _run_bf16(case, IMPL_TCGEN05)
+    finally:
+        lib().srt_debug_fwd_variant(0, 0)
+
+
+def test_conv_tcgen05_many_tiles_per_cta():
+    """More tiles than SMs with a short reduction: the persistent kernel's stage ring and the two
+    accumulator buffers wrap many times per CTA."""
+    case = ("many_tiles", 40, 28, 28, 64, 128, 1, 1, 1, 0)  # M = 31360 -> 245 row tiles
+    for bn in (64, 128):
+        lib().srt_debug_fwd_variant(0, bn)
+        try:
+            _run_bf16(case, IMPL_TCGEN05)
+        finally:
+            lib().srt_debug_fwd_variant(0, 0)
+    case = ("many_tiles_3x3", 24, 28, 28, 64, 64, 3, 3, 1, 1)  # gathered A, 147 row tiles
+    _run_bf16(case, IMPL_TCGEN05)
 
 
 def test_conv_tcgen05_gather_equals_tma():

@@ -29,6 +29,8 @@
 
 namespace srt {
 
+static int g_force_gather = 0;  // test hook: route plain-matrix operands through the gather path
+
 namespace {
 
 using namespace ptx;
@@ -44,6 +46,18 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 __device__ int g_tc_status;  // 0 = ok; otherwise the code of the first wait that gave up
 
 enum WaitCode { W_PROD_EMPTY = 1, W_TMA_EMPTY = 2, W_MMA_FULL = 3, W_EPI_TMEM = 4 };
+
+// n / d for 0 <= n < 2^31 with a precomputed multiplier and shift (d >= 1).
+__host__ inline void fastdiv_make(uint32_t d, uint32_t* mul, uint32_t* shr) {
+  uint32_t p = 0;
+  while ((1u << p) < d) ++p;
+  if (d == 1) { *mul = 0; *shr = 0; return; }
+  *mul = (uint32_t)((((uint64_t)1 << (31 + p)) + d - 1) / d);
+  *shr = p - 1;
+}
+__device__ __forceinline__ int fastdiv(int n, int d, uint32_t mul, uint32_t shr) {
+  return d == 1 ? n : (int)(__umulhi((uint32_t)n, mul) >> shr);
+}
 
 struct FwdParams {
   GatherGeom g;
@@ -61,6 +75,8 @@ struct WgradParams {
   const bf16* x;
   float* out;          // [splits][Kout][J] partials, or dW itself when splits == 1
   int pix_per_split;   // multiple of 64
+  int b_tma;           // 1x1 stride-1 filters: X is a plain [pixels][C] matrix and comes by TMA
+  uint32_t hw_mul, hw_shr, w_mul, w_shr;  // fast division by out_h*out_w and out_w
   int* status;
 };
 
@@ -293,7 +309,8 @@ igemm_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tmap_b,
 // ------------------------------------------------------------------------------------------
 template <int BN, int NS>
 __global__ void __launch_bounds__(NTHREADS)
-igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap_dy) {
+igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap_dy,
+                   const __grid_constant__ CUtensorMap tmap_x) {
   constexpr int B_STAGE_BYTES = BN * BK * 2;  // BN/64 blocks of [64 pixels][128 bytes]
   constexpr int CPR = BN / 8;                 // 16-byte chunks per pixel row
   constexpr int RSTEP = NPROD / CPR;          // pixel rows covered per pass
@@ -309,14 +326,18 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
   const int nkb = (pend - pbeg + BK - 1) / BK;
 
   if (tid == 0) {
+    const uint32_t full_count = p.b_tma ? 1u : (uint32_t)(NPROD + 1);
     for (int s = 0; s < NS; ++s) {
-      mbar_init(smem_u32(&sm.full[s]), (uint32_t)(NPROD + 1));
+      mbar_init(smem_u32(&sm.full[s]), full_count);
       mbar_init(smem_u32(&sm.empty[s]), 1);
     }
     mbar_init(smem_u32(sm.tmem_full), 1);
     mbar_fence_init();
   }
-  if (warp == 4 && lane == 0) tma_prefetch_desc(&tmap_dy);
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmap_dy);
+    if (p.b_tma) tma_prefetch_desc(&tmap_x);
+  }
   if (warp == 5) {
     tmem_alloc(smem_u32(sm.tmem_ptr), BN);
     tmem_relinquish();
@@ -328,6 +349,7 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
 
   if (warp < 4) {
     // ---------------- gather producers: x(pix, j) for 64 pixels x BN columns ----------------
+    if (!p.b_tma) {
     const int cj = tid % CPR, r0 = tid / CPR;
     const int jj = j0 + cj * 8;
     const bool j_ok = jj < J;
@@ -348,9 +370,9 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
       for (int i = 0; i < NI; ++i) {
         const int pix = pix0 + i * RSTEP;
         bool v = j_ok && pix < pend;
-        const int n = pix / hw;
+        const int n = fastdiv(pix, hw, p.hw_mul, p.hw_shr);
         const int rem = pix - n * hw;
-        const int oh = rem / g.out_w, ow = rem - oh * g.out_w;
+        const int oh = fastdiv(rem, g.out_w, p.w_mul, p.w_shr), ow = rem - oh * g.out_w;
         const int ih = oh * g.stride - g.pad + r, iw = ow * g.stride - g.pad + sf;
         v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
         const bf16* ptr =
@@ -361,6 +383,7 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
       issued = kb + 1;
     }
     producer_drain<NS>(issued, sm.full);
+    }
 
     // ---------------- epilogue: fp32 partial tile ----------------
     const bool ready = mbar_wait(smem_u32(sm.tmem_full), 0u, p.status, W_EPI_TMEM);
@@ -391,11 +414,17 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
         const uint32_t ph = (uint32_t)(kb / NS) & 1u;
         if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
         const uint32_t bar = smem_u32(&sm.full[s]);
-        mbar_arrive_expect_tx(bar, (uint32_t)A_STAGE_BYTES);
+        mbar_arrive_expect_tx(bar, (uint32_t)A_STAGE_BYTES + (p.b_tma ? (uint32_t)B_STAGE_BYTES : 0u));
         const uint32_t dst = smem_u32(sm.a + s * A_STAGE_BYTES);
         const int pix0 = pbeg + kb * BK;
         tma_load_2d(dst, &tmap_dy, bar, ko0, pix0);
         tma_load_2d(dst + 8192u, &tmap_dy, bar, ko0 + 64, pix0);
+        if (p.b_tma) {
+          const uint32_t dstb = smem_u32(sm.b + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int blk = 0; blk < BN / 64; ++blk)
+            tma_load_2d(dstb + (uint32_t)blk * 8192u, &tmap_x, bar, j0 + blk * 64, pix0);
+        }
       }
     }
   } else {
@@ -793,7 +822,8 @@ int launch_fwd(const FwdParams& p, const CUtensorMap& tb, const CUtensorMap& ta,
 }
 
 template <int BN, int NS>
-int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, int splits, cudaStream_t st) {
+int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, const CUtensorMap& tx, int splits,
+                 cudaStream_t st) {
   constexpr size_t smem = smem_bytes<NS, BN * BK * 2>();
   static bool configured = false;
   if (!configured) {
@@ -802,7 +832,7 @@ int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, int splits, cudaS
     configured = true;
   }
   dim3 grid(ceil_div(p.g.Kg, BN), ceil_div(p.g.Nout, BM), splits);
-  igemm_wgrad_kernel<BN, NS><<<grid, NTHREADS, smem, st>>>(p, tdy);
+  igemm_wgrad_kernel<BN, NS><<<grid, NTHREADS, smem, st>>>(p, tdy, tx);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -848,8 +878,9 @@ struct WgradPlan {
 WgradPlan plan_wgrad(const GatherGeom& g) {
   WgradPlan w;
   w.bn = g.Kg <= 64 ? 64 : 128;
+  // as many splits as fit the machine in one wave (two CTAs per SM), never less than 4 k-blocks each
   const int tiles = ceil_div(g.Kg, w.bn) * ceil_div(g.Nout, BM);
-  int want = ceil_div(2 * sm_count(), tiles);
+  int want = (2 * sm_count()) / tiles;
   const int max_by_pix = ceil_div(g.M, 4 * BK);
   int splits = want < max_by_pix ? want : max_by_pix;
   if (splits < 1) splits = 1;
@@ -874,7 +905,6 @@ int tc_status_fetch(int* out) {
   return SRT_OK;
 }
 
-static int g_force_gather = 0;  // test hook: route 1x1 stride-1 problems through the gather path
 void tc_set_force_gather(int v) { g_force_gather = v; }
 static int g_fwd_variant = 0;   // 0: persistent kernel, 1: one tile per CTA (kept for comparison)
 static int g_force_bn = 0;      // 0: heuristic, else 64/128/256
@@ -966,11 +996,21 @@ int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw,
   p.pix_per_split = w.pix_per_split;
   p.status = status_ptr();
   SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
-  CUtensorMap tdy;
+  fastdiv_make((uint32_t)(g.out_h * g.out_w), &p.hw_mul, &p.hw_shr);
+  fastdiv_make((uint32_t)g.out_w, &p.w_mul, &p.w_shr);
+  const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
+  p.b_tma = (plain && !g_force_gather) ? 1 : 0;
+  CUtensorMap tdy, tx;
   int rc = make_tmap_2d(&tdy, dy, (uint64_t)g.M, (uint64_t)g.Nout, 64);
   if (rc != SRT_OK) return rc;
-  rc = w.bn == 64 ? launch_wgrad<64, 4>(p, tdy, w.splits, st)
-                  : launch_wgrad<128, 4>(p, tdy, w.splits, st);
+  if (p.b_tma) {
+    rc = make_tmap_2d(&tx, x, (uint64_t)g.M, (uint64_t)g.src_c, 64);
+    if (rc != SRT_OK) return rc;
+  } else {
+    tx = tdy;
+  }
+  rc = w.bn == 64 ? launch_wgrad<64, 4>(p, tdy, tx, w.splits, st)
+                  : launch_wgrad<128, 4>(p, tdy, tx, w.splits, st);
   if (rc != SRT_OK) return rc;
   if (w.splits > 1) return launch_split_reduce(p.out, dw, (long long)g.Nout * g.Kg, w.splits, st);
   return SRT_OK;

@@ -131,15 +131,19 @@ def test_conv_tcgen05_gather_equals_tma():
     x, w, dy = _mk(case, torch.bfloat16)
     bf = torch.bfloat16
     xd, wd = x.to(DEV, bf), w.to(DEV, bf)
+    dyd = dy.to(DEV, bf)
     y_tma = ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05)
+    dw_tma = ops.conv_wgrad(dyd, xd, 1, 1, 1, 0, impl=IMPL_TCGEN05)
     lib().srt_debug_force_gather(1)
     try:
         y_g = ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05)
+        dw_g = ops.conv_wgrad(dyd, xd, 1, 1, 1, 0, impl=IMPL_TCGEN05)
     finally:
         lib().srt_debug_force_gather(0)
     torch.cuda.synchronize()
     assert ops.tc_status() == 0
     assert torch.equal(y_tma, y_g)
+    assert torch.equal(dw_tma, dw_g)
 
 
 def test_conv_epilogue_bias_addend():

@@ -75,6 +75,27 @@ int srt_bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gam
                  float* running_var, float* mean, float* invstd, float* scale, float* shift,
                  void* scratch, size_t scratch_bytes, void* stream);
 size_t srt_bn_scratch_bytes(int64_t rows, int C);
+/* srt_bn_stats without any allocation by anyone. This entry point has no counterpart in the
+ * reference. It exists for callers that cannot obtain scratch memory: a colocated trainer that is
+ * handing its memory pool over to the inference server has promised all free device memory to the
+ * other process, so a cudaMalloc at that moment fails or takes what the server was told it may use;
+ * and a control thread that must stay responsive cannot call cudaMalloc/cudaFree, which may
+ * synchronise the device. The slab partial sums go into a fixed 4 MiB array inside the library
+ * (every GPU that loads the library holds it until the process exits). The caller still passes
+ * the input and all outputs. Limits and rules:
+ *  - problems with srt_bn_scratch_bytes(rows, C) > SRT_BN_STATIC_SCRATCH_BYTES are rejected with
+ *    SRT_ERR_INVALID and a message; use srt_bn_stats for those;
+ *  - the first call on each device looks up the array's device address (with that device current);
+ *    make that first call before any stream capture is begun;
+ *  - all calls share the one array, which keeps whatever the previous call left in it (nothing in
+ *    it needs clearing: each call writes every partial before reading it), so two calls whose
+ *    kernels can overlap on the GPU (different streams, no ordering) race and must be serialised;
+ *  - it calls neither cudaMalloc nor cudaFree nor any allocating library routine. */
+#define SRT_BN_STATIC_SCRATCH_BYTES (4u << 20)
+int srt_bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
+                        const float* beta, float eps, float momentum, float* running_mean,
+                        float* running_var, float* mean, float* invstd, float* scale, float* shift,
+                        void* stream);
 /* y = act(z*scale + shift (+ residual)); relu != 0 applies max(.,0). */
 int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
                  const float* scale, const float* shift, int relu, void* stream);

@@ -47,6 +47,7 @@ _SIGNATURES = {
     "srt_conv_filter_transpose": (None, [_PD, _i, _vp, _vp, _vp]),
     "srt_bn_stats": (None, [_i, _vp, _i64, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "srt_bn_scratch_bytes": (_sz, [_i64, _i]),
+    "srt_bn_stats_static": (None, [_i, _vp, _i64, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "srt_bn_apply": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _i, _vp]),
     "srt_bn_backward": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "srt_maxpool3x3s2_fwd": (None, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -155,6 +155,15 @@ int srt_bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gam
                   invstd, scale, shift, scratch, scratch_bytes, ST(stream));
 }
 size_t srt_bn_scratch_bytes(int64_t rows, int C) { return bn_scratch_bytes(rows, C); }
+int srt_bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
+                        const float* beta, float eps, float momentum, float* running_mean,
+                        float* running_var, float* mean, float* invstd, float* scale, float* shift,
+                        void* stream) {
+  SRT_REQUIRE(z && mean && invstd && scale && shift, "bn_stats_static: null argument");
+  CHECK_DTYPE(dtype);
+  return bn_stats_static(dtype, z, rows, C, gamma, beta, eps, momentum, running_mean, running_var,
+                         mean, invstd, scale, shift, ST(stream));
+}
 int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
                  const float* scale, const float* shift, int relu, void* stream) {
   SRT_REQUIRE(z && y && scale && shift, "bn_apply: null argument");

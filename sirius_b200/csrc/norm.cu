@@ -4,6 +4,8 @@
 // contiguous one), fp32 per-thread accumulation over a short run of rows, double-precision
 // combination of the per-thread and per-slab partial sums in a fixed order (deterministic, and
 // accurate enough for the fp32 parity mode).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace srt {
@@ -386,6 +388,49 @@ static void bn_apply_t(const void* z, const void* residual, void* y, int64_t row
   else
     bn_apply_kernel<T, false><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)z, nullptr, (T*)y, nvec, C / V,
                                                                 scale, shift, relu);
+}
+
+// ---- allocation-free variant of bn_stats ----------------------------------------------------
+// The slab partial sums normally live in caller-provided scratch. Some callers cannot provide any:
+// a colocated trainer that is in the middle of handing its memory pool to the inference server has
+// promised every free byte of the device to the other process, so a cudaMalloc at that moment
+// either fails or takes memory the server was just told it may use; and a control thread that has
+// to stay responsive cannot afford cudaMalloc/cudaFree, which may synchronise the whole device.
+// For them the partials go into this fixed array, which is part of the library image: every GPU
+// that loads the library holds these 4 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_bn_static_scratch[SRT_BN_STATIC_SCRATCH_BYTES];
+
+// In host code `g_bn_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use is looked up once per device (with that device current) and cached.
+static std::mutex g_static_mu;
+static void* g_static_ptr[64] = {nullptr};
+
+int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
+                    const float* beta, float eps, float momentum, float* rm, float* rv, float* mean,
+                    float* invstd, float* scale, float* shift, cudaStream_t st) {
+  SRT_REQUIRE(C % 8 == 0 && rows > 0, "bn_stats_static: C (%d) must be a multiple of 8, rows > 0", C);
+  const size_t need = bn_scratch_bytes(rows, C);
+  SRT_REQUIRE(need <= (size_t)SRT_BN_STATIC_SCRATCH_BYTES,
+              "bn_stats_static: rows=%lld, C=%d needs %zu bytes of partial sums, the built-in scratch "
+              "holds %zu; use srt_bn_stats with caller-provided scratch",
+              (long long)rows, C, need, (size_t)SRT_BN_STATIC_SCRATCH_BYTES);
+  int dev = -1;
+  SRT_CHECK_CUDA(cudaGetDevice(&dev));
+  SRT_REQUIRE(dev >= 0 && dev < 64, "bn_stats_static: unsupported device ordinal %d", dev);
+  void* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      SRT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_bn_static_scratch));
+      g_static_ptr[dev] = p;
+    }
+    ptr = g_static_ptr[dev];
+  }
+  // Nothing in the array has to start at zero: every slab partial that the finalize kernel reads
+  // is written by the partial kernel of the same call first.
+  return bn_stats(dtype, z, rows, C, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift,
+                  ptr, (size_t)SRT_BN_STATIC_SCRATCH_BYTES, st);
 }
 
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,

@@ -9,6 +9,9 @@ size_t bn_scratch_bytes(int64_t rows, int C);
 int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, const float* beta,
              float eps, float momentum, float* rm, float* rv, float* mean, float* invstd,
              float* scale, float* shift, void* scratch, size_t scratch_bytes, cudaStream_t st);
+int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
+                    const float* beta, float eps, float momentum, float* rm, float* rv, float* mean,
+                    float* invstd, float* scale, float* shift, cudaStream_t st);
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
              const float* scale, const float* shift, int relu, cudaStream_t st);
 int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,

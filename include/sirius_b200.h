@@ -25,7 +25,7 @@ extern "C" {
 #endif
 
 enum { SRT_OK = 0, SRT_ERR_INVALID = 1, SRT_ERR_CUDA = 2, SRT_ERR_UNSUPPORTED = 3,
-       SRT_ERR_NOMEM = 4, SRT_ERR_TIMEOUT = 5, SRT_ERR_STATE = 6 };
+       SRT_ERR_NOMEM = 4, SRT_ERR_TIMEOUT = 5, SRT_ERR_STATE = 6, SRT_ERR_ABORTED = 7 };
 enum { SRT_F32 = 0, SRT_BF16 = 1 };
 /* Which kernel family a convolution call uses. AUTO: tcgen05 for bf16, CUDA cores for fp32. */
 enum { SRT_IMPL_AUTO = 0, SRT_IMPL_SIMT = 1, SRT_IMPL_TCGEN05 = 2 };
@@ -187,6 +187,22 @@ enum { SRT_PARAM_CONV = 0, SRT_PARAM_VECTOR = 1, SRT_PARAM_BUFFER = 2, SRT_PARAM
 enum { SRT_GET_VALUE = 0, SRT_GET_GRAD = 1, SRT_GET_ACCUM = 2, SRT_GET_MOMENTUM = 3 };
 
 int srt_resnet_create(const srt_resnet_config* cfg, srt_step** out);
+/* Same, with the releasable part of the step's memory (saved activations, gradient buffers, scratch)
+ * taken from the training allocator of `pool` (sirius_pool.h), as the reference routes every tensor
+ * of the step through CUDAColAllocator -> CUDAMemPool (torch_allocator_plugin.cc:108-139). */
+struct srt_pool;
+int srt_resnet_create_with_pool(const srt_resnet_config* cfg, struct srt_pool* pool, srt_step** out);
+/* Memory handover, training side (ColocateCtrl.adjust_l1, pytorch/torch_col/colocate_ctrl.py:413-445:
+ * release_interm_memory + MemoryPool.empty_cache): synchronises the stream, frees the activation set
+ * and returns the pages that became empty to the pool. *released_bytes = bytes of pages handed back
+ * (bytes freed when no pool is attached). The next forward re-allocates for its batch size. */
+int srt_step_release_activations(srt_step* s, size_t* released_bytes);
+int srt_step_reserve_activations(srt_step* s, int B);
+/* Kill batch (ColocateStub on kColocateAdjustL1, pytorch/torch_col/csrc/control_stub.cc:486-510; the
+ * reference drops the launches still queued in xsched): any thread may raise the flag; forward and
+ * backward test it between units and return SRT_ERR_ABORTED, and never run more than 8 units ahead of
+ * the GPU, so the stream drains within a bounded time. Clear the flag before the next micro-batch. */
+int srt_step_request_abort(srt_step* s, int on);
 int srt_step_destroy(srt_step* s);
 /* Parameter registry under torchvision state_dict names ("layer1.0.conv1.weight", ...). Shapes and
  * host data use the torch layout ([K,C,R,S] for convolutions); the device keeps [K,R,S,C]. */

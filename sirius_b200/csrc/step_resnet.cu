@@ -11,6 +11,9 @@
 #include <string>
 #include <vector>
 
+#include <atomic>
+
+#include "../../include/sirius_pool.h"
 #include "common.cuh"
 #include "ops.cuh"
 
@@ -93,6 +96,47 @@ struct Step {
   int accum_pending = 0;
   size_t act_bytes = 0;
 
+  // Releasable part of the step's memory: saved activations, gradient ping-pong buffers, scratch.
+  // Taken from the training allocator of a page pool when one is attached (so that releasing them
+  // and emptying the allocator's cache hands whole pages to the inference side), else cudaMalloc.
+  srt_pool* pool = nullptr;
+  int act_batch = 0;               // batch size the activation set is currently sized for (0 = released)
+  std::vector<void*> act_blocks;
+  // Kill-batch support: a flag any thread may raise; forward/backward look at it between units and
+  // keep at most kLaunchAhead units in flight, so an abort drains within a bounded time.
+  std::atomic<int> abort_flag{0};
+  static constexpr int kLaunchAhead = 8;
+  cudaEvent_t ahead_ev[kLaunchAhead] = {nullptr};
+  unsigned long long unit_seq = 0;
+
+  int aalloc(void** out, size_t bytes) {
+    bytes = bytes ? bytes : 256;
+    if (pool) {
+      int rc = srt_pool_alloc(pool, SRT_POOL_TRAIN, bytes, out);
+      if (rc) return rc;
+    } else {
+      SRT_CHECK_CUDA(cudaMalloc(out, (bytes + 255) / 256 * 256));
+    }
+    act_blocks.push_back(*out);
+    act_bytes += bytes;
+    return SRT_OK;
+  }
+  int alloc_activations(int B);
+  int release_activations(size_t* released_bytes);
+  // Called between units: abort check + bounded launch-ahead.
+  int checkpoint() {
+    if (abort_flag.load(std::memory_order_acquire)) {
+      set_error("step aborted between units (kill batch)");
+      return SRT_ERR_ABORTED;
+    }
+    const int slot = (int)(unit_seq % kLaunchAhead);
+    if (!ahead_ev[slot]) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ahead_ev[slot], cudaEventDisableTiming));
+    else if (unit_seq >= (unsigned long long)kLaunchAhead) SRT_CHECK_CUDA(cudaEventSynchronize(ahead_ev[slot]));
+    SRT_CHECK_CUDA(cudaEventRecord(ahead_ev[slot], stream));
+    ++unit_seq;
+    return SRT_OK;
+  }
+
   // Optional per-category device timing (CUDA events on the step's stream around each launch).
   bool prof_on = false;
   struct ProfRec { int cat; double work; cudaEvent_t a, b; };
@@ -131,6 +175,8 @@ struct Step {
   ~Step() {
     for (auto& r : prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
     for (auto e : prof_pool) cudaEventDestroy(e);
+    for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
+    release_activations(nullptr);
     for (void* p : allocs) cudaFree(p);
     if (own_stream && stream) cudaStreamDestroy(stream);
   }
@@ -263,14 +309,47 @@ int Step::build() {
   place_bn(stem.bn);
   for (auto& k : blocks) { place_bn(k.u1.bn); place_bn(k.u2.bn); place_bn(k.u3.bn); if (k.has_ds) place_bn(k.ds.bn); }
 
+  if ((rc = dalloc(&avg, (size_t)B * feat_C * esz, false))) return rc;
+  if ((rc = dalloc(&logits, (size_t)B * cfg.num_classes * esz, false))) return rc;
+  if ((rc = dalloc(&dlogits, (size_t)B * cfg.num_classes * esz, false))) return rc;
+  if ((rc = dalloc((void**)&row_loss, (size_t)B * 4, true))) return rc;
+  if ((rc = dalloc((void**)&loss_acc, 256, true))) return rc;
+  if ((rc = dalloc((void**)&stage_images, (size_t)B * 3 * IMG * IMG * 4, false))) return rc;
+  if ((rc = dalloc((void**)&stage_labels, (size_t)B * 8, false))) return rc;
+
+  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  own_stream = true;
+  if ((rc = alloc_activations(B))) return rc;
+
+  // BN defaults (weight 1, bias 0, running_var 1); conv/fc weights are set by the caller.
+  std::vector<float> ones;
+  for (auto& r : params) {
+    const bool bn_weight = r.kind == SRT_PARAM_VECTOR && r.name.size() > 7 &&
+                           r.name.compare(r.name.size() - 7, 7, ".weight") == 0;
+    const bool rvar = r.kind == SRT_PARAM_BUFFER && r.name.find("running_var") != std::string::npos;
+    if (bn_weight || rvar) {
+      ones.assign(r.count, 1.f);
+      float* dst = rvar ? BUF + r.off : P + r.off;
+      SRT_CHECK_CUDA(cudaMemcpy(dst, ones.data(), r.count * 4, cudaMemcpyHostToDevice));
+    }
+  }
+  return refresh_working_copies();
+}
+
+// Activation set for micro-batches of up to B samples.
+int Step::alloc_activations(int B) {
+  SRT_REQUIRE(B > 0 && B <= cfg.max_batch, "activations: batch %d outside 1..%d", B, cfg.max_batch);
+  if (act_batch == B) return SRT_OK;
+  int rc = release_activations(nullptr);
+  if (rc) return rc;
+  const int dtype = cfg.dtype, IMG = cfg.image;
   size_t max_act = 0, max_bn_scratch = 0, max_wg_scratch = 0;
   auto alloc_unit = [&](Unit& u) -> int {
     const size_t elems = (size_t)B * u.P * u.Q * u.conv.K;
     if (elems > max_act) max_act = elems;
     int r;
-    if ((r = dalloc(&u.z, elems * esz, false))) return r;
-    if ((r = dalloc(&u.y, elems * esz, false))) return r;
-    act_bytes += 2 * align_up(elems * esz, 256);
+    if ((r = aalloc(&u.z, elems * esz))) return r;
+    if ((r = aalloc(&u.y, elems * esz))) return r;
     const size_t bs = bn_scratch_bytes((int64_t)B * u.P * u.Q, u.conv.K);
     if (bs > max_bn_scratch) max_bn_scratch = bs;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
@@ -292,39 +371,41 @@ int Step::build() {
   }
   const size_t x0_elems = (size_t)B * IMG * IMG * kStemCpad;
   if (x0_elems > max_act) max_act = x0_elems;
-  if ((rc = dalloc(&x0, x0_elems * esz, false))) return rc;
+  if ((rc = aalloc(&x0, x0_elems * esz))) return rc;
   const size_t pool_elems = (size_t)B * (IMG / 4) * (IMG / 4) * 64;
-  if ((rc = dalloc(&pool_y, pool_elems * esz, false))) return rc;
-  if ((rc = dalloc((void**)&pool_arg, pool_elems, false))) return rc;
-  if ((rc = dalloc(&avg, (size_t)B * feat_C * esz, false))) return rc;
-  if ((rc = dalloc(&logits, (size_t)B * cfg.num_classes * esz, false))) return rc;
-  if ((rc = dalloc(&dlogits, (size_t)B * cfg.num_classes * esz, false))) return rc;
+  if ((rc = aalloc(&pool_y, pool_elems * esz))) return rc;
+  if ((rc = aalloc((void**)&pool_arg, pool_elems))) return rc;
   for (int i = 0; i < 5; ++i)
-    if ((rc = dalloc(&T[i], max_act * esz, false))) return rc;
-  act_bytes += (x0_elems + 2 * pool_elems) * esz + 5 * max_act * esz;
+    if ((rc = aalloc(&T[i], max_act * esz))) return rc;
   scratch_bytes = max_bn_scratch > max_wg_scratch ? max_bn_scratch : max_wg_scratch;
-  if ((rc = dalloc(&scratch, scratch_bytes, false))) return rc;
-  if ((rc = dalloc((void**)&row_loss, (size_t)B * 4, true))) return rc;
-  if ((rc = dalloc((void**)&loss_acc, 256, true))) return rc;
-  if ((rc = dalloc((void**)&stage_images, (size_t)B * 3 * IMG * IMG * 4, false))) return rc;
-  if ((rc = dalloc((void**)&stage_labels, (size_t)B * 8, false))) return rc;
+  if ((rc = aalloc(&scratch, scratch_bytes))) return rc;
+  act_batch = B;
+  return SRT_OK;
+}
 
-  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
-  own_stream = true;
-
-  // BN defaults (weight 1, bias 0, running_var 1); conv/fc weights are set by the caller.
-  std::vector<float> ones;
-  for (auto& r : params) {
-    const bool bn_weight = r.kind == SRT_PARAM_VECTOR && r.name.size() > 7 &&
-                           r.name.compare(r.name.size() - 7, 7, ".weight") == 0;
-    const bool rvar = r.kind == SRT_PARAM_BUFFER && r.name.find("running_var") != std::string::npos;
-    if (bn_weight || rvar) {
-      ones.assign(r.count, 1.f);
-      float* dst = rvar ? BUF + r.off : P + r.off;
-      SRT_CHECK_CUDA(cudaMemcpy(dst, ones.data(), r.count * 4, cudaMemcpyHostToDevice));
+// Frees the activation set; with a pool attached, also returns every page that became empty.
+int Step::release_activations(size_t* released_bytes) {
+  if (released_bytes) *released_bytes = 0;
+  if (act_blocks.empty()) { act_batch = 0; return SRT_OK; }
+  if (stream) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
+  for (void* p : act_blocks) {
+    if (pool) {
+      int rc = srt_pool_free(pool, SRT_POOL_TRAIN, p);
+      if (rc) return rc;
+    } else {
+      cudaFree(p);
     }
   }
-  return refresh_working_copies();
+  act_blocks.clear();
+  size_t freed = act_bytes;
+  act_bytes = 0;
+  act_batch = 0;
+  if (pool) {
+    int rc = srt_pool_empty_cache(pool, SRT_POOL_TRAIN, &freed);
+    if (rc) return rc;
+  }
+  if (released_bytes) *released_bytes = freed;
+  return SRT_OK;
 }
 
 // bf16 working copy of the parameters (bf16 mode) and transposed filters for dgrad.
@@ -350,6 +431,7 @@ int Step::forward(int B) {
   const int dt = cfg.dtype, impl = cfg.impl;
   int rc;
   auto run_unit = [&](Unit& u, const void* in, const void* residual) -> int {
+    if (int c = checkpoint()) return c;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     int r;
     const int64_t rows = (int64_t)B * u.P * u.Q;
@@ -417,6 +499,7 @@ int Step::backward(int B) {
 
   // gradient through conv+BN(+ReLU): dy (w.r.t. u.y) -> dz in T[1], filter gradient into G
   auto unit_bwd = [&](Unit& u, const void* dy, const void* in, void* dz, void* dres) -> int {
+    if (int c = checkpoint()) return c;
     const int64_t rows = (int64_t)B * u.P * u.Q;
     int r;
     // two passes over (dy, z[, y]) plus the dz (and masked-gradient) writes
@@ -474,10 +557,15 @@ using namespace srt;
 extern "C" {
 
 int srt_resnet_create(const srt_resnet_config* cfg, srt_step** out) {
+  return srt_resnet_create_with_pool(cfg, nullptr, out);
+}
+
+int srt_resnet_create_with_pool(const srt_resnet_config* cfg, srt_pool* pool, srt_step** out) {
   SRT_REQUIRE(cfg && out, "resnet_create: null argument");
   SRT_REQUIRE(cfg->dtype == SRT_F32 || cfg->dtype == SRT_BF16, "resnet_create: unknown dtype");
   Step* s = new Step();
   s->cfg = *cfg;
+  s->pool = pool;
   int rc = s->build();
   if (rc == SRT_OK) rc = cudaStreamSynchronize(s->stream) == cudaSuccess ? SRT_OK : SRT_ERR_CUDA;
   if (rc != SRT_OK) { delete s; return rc; }
@@ -586,7 +674,9 @@ int srt_step_set_batch_device(srt_step* h, const float* dev_images, const int64_
 int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch && global_batch >= B, "forward_backward: bad batch sizes");
-  int rc = s->forward(B);
+  int rc;
+  if (s->act_batch < B && (rc = s->alloc_activations(B))) return rc;  // regain after a release
+  rc = s->forward(B);
   if (rc) return rc;
   const float scale = 1.f / (float)global_batch;
   if ((rc = softmax_ce(s->cfg.dtype, s->logits, s->stage_labels, B, s->cfg.num_classes, scale, s->row_loss,
@@ -599,6 +689,7 @@ int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
 int srt_step_forward_only(srt_step* h, int B) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_only: bad batch size");
+  if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
   return s->forward(B);
 }
 
@@ -670,6 +761,25 @@ int srt_step_logits(srt_step* h, float* host, int B) {
       memcpy(&host[i], &u, 4);
     }
   }
+  return SRT_OK;
+}
+
+int srt_step_release_activations(srt_step* h, size_t* released_bytes) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "release_activations: null handle");
+  return s->release_activations(released_bytes);
+}
+
+int srt_step_reserve_activations(srt_step* h, int B) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "reserve_activations: null handle");
+  return s->alloc_activations(B);
+}
+
+int srt_step_request_abort(srt_step* h, int on) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "request_abort: null handle");
+  s->abort_flag.store(on ? 1 : 0, std::memory_order_release);
   return SRT_OK;
 }
 

@@ -7,6 +7,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 from . import _lib
+from . import _runtime  # noqa: F401  (registers the runtime entry points)
 from ._lib import IMPL_AUTO, SRT_BF16, SRT_F32, call, register
 
 
@@ -64,7 +65,7 @@ class ResNetStep:
     MicroBatchManager/GradAccumulator (pytorch/torch_col/dynamic_batch.py:112-153)."""
 
     def __init__(self, arch="resnet152", num_classes=1000, max_batch=16, image=224, dtype="bf16",
-                 impl=IMPL_AUTO, lr=0.1, momentum=0.9, weight_decay=1e-4, layers=None):
+                 impl=IMPL_AUTO, lr=0.1, momentum=0.9, weight_decay=1e-4, layers=None, pool=None):
         cfg = ResNetConfigC()
         lay = tuple(layers) if layers is not None else RESNET_LAYERS[arch]
         cfg.layers = (C.c_int * 4)(*lay)
@@ -76,7 +77,8 @@ class ResNetStep:
         self.cfg = cfg
         self.dtype = "f32" if cfg.dtype == SRT_F32 else "bf16"
         self._h = _vp()
-        call("srt_resnet_create", C.byref(cfg), C.byref(self._h))
+        self.pool = pool
+        call("srt_resnet_create_with_pool", C.byref(cfg), pool if pool else None, C.byref(self._h))
         self.params: dict[str, ParamInfo] = {}
         n = _lib.lib().srt_step_num_params(self._h)
         name = C.create_string_buffer(256)
@@ -175,6 +177,18 @@ class ResNetStep:
         ms, work, n = (C.c_double * 5)(), (C.c_double * 5)(), (_i64 * 5)()
         call("srt_step_profile_read", self._h, ms, work, n)
         return {c: {"ms": ms[i], "work": work[i], "launches": n[i]} for i, c in enumerate(PROF_CATS)}
+
+    def release_activations(self) -> int:
+        """Frees the activation set and returns emptied pages to the pool; bytes handed back."""
+        n = C.c_size_t()
+        call("srt_step_release_activations", self._h, C.byref(n))
+        return n.value
+
+    def reserve_activations(self, B: int) -> None:
+        call("srt_step_reserve_activations", self._h, B)
+
+    def request_abort(self, on: bool = True) -> None:
+        call("srt_step_request_abort", self._h, int(on))
 
     def train_step(self, images, labels) -> float:
         """Whole-batch step through host buffers: H2D, forward, backward, SGD, loss readback."""

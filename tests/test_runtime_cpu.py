@@ -1,0 +1,383 @@
+"""CPU suite of the host-side runtime: the shared-memory channel, SM-partition arithmetic, ledger,
+performance model, train adjuster and page pool, through the C ABI, against the Python restatement
+of the reference's logic (oracle/control_oracle.py)."""
+import ctypes as C
+import multiprocessing as mp
+import os
+import random
+import time
+import uuid
+
+import pytest
+
+from oracle import control_oracle as O
+from sirius_b200 import _lib, _runtime  # noqa: F401
+from sirius_b200._lib import call, SrtError
+from sirius_b200._runtime import AdjusterConfig, CtrlMsg, PoolConfig, TrainInfo
+from sirius_b200.torch_col import _C as TC
+from sirius_b200.torch_col._C import CtrlEvent, PyInfTraCommunicator
+
+
+def _name(tag):
+    return f"srt_test_{tag}_{os.getpid()}_{uuid.uuid4().hex[:8]}"
+
+
+# ---------------------------------------------------------------- inf_tra_comm
+def test_comm_queues_and_info_board():
+    nm = _name("comm")
+    srv = PyInfTraCommunicator(True, True, 2, nm)
+    cli = PyInfTraCommunicator(False, False, 2, nm)
+    try:
+        assert cli.timed_get(0, 0, 0) is None                       # TryGet on an empty queue
+        t0 = time.time()
+        assert cli.timed_get(50, 0, 1) is None                      # TimedGet times out
+        assert 0.04 < time.time() - t0 < 1.0
+        srv.put_all_inf2tra(CtrlEvent.kColocateAdjustL1, 7, [12, 34])  # PutAll, one message per rank
+        a, b = cli.timed_get(100, 0, 0), cli.timed_get(100, 0, 1)
+        assert (a.id, a.event, a.value) == (7, CtrlEvent.kColocateAdjustL1, 12)
+        assert (b.id, b.event, b.value) == (7, CtrlEvent.kColocateAdjustL1, 34)
+        for i in range(5):                                          # FIFO per queue
+            cli.put_tra2inf(CtrlEvent.kReportBatchSize, 0, i, 1)
+        got = [srv.timed_get_from_any(100, 1) for _ in range(5)]
+        assert [m.value for r, m in got] == list(range(5)) and all(r == 1 for r, _ in got)
+        assert srv.timed_get_from_any(20, 1) is None
+        # information board
+        cli.set_train_info(0, train_pid=os.getpid(), train_rank=0, train_world_size=2, init_batch_size=64,
+                           current_batch_size=64, target_batch_size=64, target_batch_size_unpublished=64,
+                           model_name="resnet152")
+        ti = srv.get_train_info(0)
+        assert ti.model_name == b"resnet152" and ti.init_batch_size == 64
+        srv.update_field(0, 6, 40)
+        assert cli.get_field(0, 6) == 40 and cli.get_field(0, 5) == 64
+        with pytest.raises(SrtError):                               # rank 1 never registered: invalid
+            cli.get_field(1, 5)
+        # TPC counters shared with the SM partitioner
+        assert srv.infer_tpc(0, 1, 27) == 27 and srv.infer_tpc(0, 1, 6) == 33
+        assert cli.infer_tpc(0, 2, 27) == 6 and cli.infer_tpc(0, 3) == 6
+    finally:
+        cli.close()
+        srv.close()
+
+
+def test_comm_open_without_server_fails_quickly():
+    with pytest.raises(SrtError):
+        PyInfTraCommunicator(False, False, 1, _name("absent"), timeout_ms=100)
+
+
+def _blocking_getter(nm, q):
+    c = PyInfTraCommunicator(False, False, 1, nm)
+    m = c.timed_get(5000, 0, 0)
+    q.put((m.id, int(m.event), m.value))
+    c.close()
+
+
+def test_comm_wakes_a_blocked_getter_in_another_process():
+    nm = _name("comm2")
+    srv = PyInfTraCommunicator(True, True, 1, nm)
+    q = mp.get_context("spawn").Queue()
+    p = mp.get_context("spawn").Process(target=_blocking_getter, args=(nm, q))
+    p.start()
+    time.sleep(0.3)
+    srv.put_inf2tra(CtrlEvent.kInferExit, 3, 9, 0)
+    assert q.get(timeout=10) == (3, int(CtrlEvent.kInferExit), 9)
+    p.join(10)
+    srv.close()
+
+
+# ---------------------------------------------------------------- SM partition
+def test_sm_partition_mask_matches_reference_arithmetic():
+    lib = _lib.lib()
+    rnd = random.Random(0)
+    for _ in range(2000):
+        gpu_tpc = rnd.choice([40, 54, 66, 74])
+        mn, mx = rnd.randint(1, 8), rnd.choice([gpu_tpc, gpu_tpc - 3, 200])
+        req = rnd.randint(0, 100)
+        want = O.train_avail_tpc_mask(req, gpu_tpc, mn, mx) & (2 ** 64 - 1)
+        if O.train_avail_tpc_mask(req, gpu_tpc, mn, mx) >= 2 ** 64:
+            want = 2 ** 64 - 1
+        assert lib.srt_smp_train_avail_tpc_mask(req, gpu_tpc, mn, mx) == want
+        assert lib.srt_smp_train_avail_tpc_num(req, gpu_tpc, mn, mx) == O.train_avail_tpc_num(req, gpu_tpc, mn, mx)
+    # wide mask on a 148-SM part: 27 TPCs requested -> SMs 0..53 leave training, 54..147 stay
+    m = (C.c_uint64 * 3)()
+    call("srt_smp_allowed_sm_mask", 27, 148, 5, 74, m)
+    bits = [(m[i >> 6] >> (i & 63)) & 1 for i in range(192)]
+    assert sum(bits) == 148 - 54 and bits[53] == 0 and bits[54] == 1 and bits[147] == 1 and bits[148] == 0
+
+
+# ---------------------------------------------------------------- ledger, single rank
+@pytest.fixture
+def dist1():
+    TC._Config.has_infer_server = False
+    os.environ["SIRIUS_B200_DIST_NAME"] = _name("dist")
+    os.environ.pop("COLTRAIN_HAS_INFER_SERVER", None)
+    TC.torch_col_init(0, 1)
+    yield TC.dist
+    TC.torch_col_shutdown()
+
+
+def test_ledger_single_rank_global_batches(dist1):
+    D = TC._DynamicBatchDistirbutor
+    dist1.init_dynamic_batch_distributor(100, 16, 40, False, "fix")
+    assert D.get_global_batch_size() == 40 and D.get_num_global_batch_per_epoch() == 3
+    assert D.next_epoch() == 0
+    seen = []
+    for gb, size in enumerate([40, 40, 20]):                  # last global batch is the remainder
+        D.next_global_batch()
+        assert D._info(3) == size and D._info(6, 0) == size
+        done = 0
+        while True:
+            want = D.query_next_batch_size(16)
+            rng, last = D.get_batch(want)
+            n = sum(j - i for i, j in rng)
+            assert n == want == min(16, size - done)
+            if gb == 0 and done == 16:                        # abort once: samples go back, come again
+                D.abort_batch(rng, last)
+                assert D._info(3) == size - done and D._info(4) == 0
+                rng2, last2 = D.get_batch(want)
+                assert rng2 == rng and last2 == last
+            done += n
+            seen += rng
+            D.finish_batch(rng, last)
+            if last:
+                break
+        assert done == size and D._info(5) == size and D.get_num_proced_global_batch() == gb + 1
+    covered = sorted(seen)
+    assert covered[0][0] == 0 and covered[-1][1] == 100
+    assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))   # every sample exactly once
+    with pytest.raises(SrtError):
+        D.finish_batch([(0, 5)], False)                                 # not in the processing set
+    assert D.next_epoch() == 1
+
+
+def test_perf_model_matches_reference_interpolation(dist1):
+    P = TC._PerfModel
+    ref = O.PerfModel()
+    assert P.get_thpt(8) == -1 and P.get_thpt(0) == 0
+    rnd = random.Random(1)
+    for _ in range(200):
+        bs, ms = rnd.choice([4, 8, 16, 24, 32, 64]), rnd.uniform(5, 80)
+        P.record_thpt(bs, ms)
+        ref.record(bs, ms)
+    for bs in range(-2, 100):
+        assert P.get_thpt(bs) == pytest.approx(ref.get(bs), rel=1e-12, abs=1e-12)
+
+
+# ---------------------------------------------------------------- ledger, two ranks
+def _ledger_worker(rank, dist_name, policy, q):
+    os.environ["SIRIUS_B200_DIST_NAME"] = dist_name
+    TC.torch_col_init(rank, 2)
+    D = TC._DynamicBatchDistirbutor
+    TC.dist.init_dynamic_batch_distributor(64, 8, 32, False, policy)
+    if rank == 0 and policy == "by_performance":
+        TC._PerfModel.record_thpt(8, 10.0)
+    TC.dist.wait_barrier()
+    D.next_epoch()
+    mine, votes = [], []
+    for gb in range(2):
+        D.next_global_batch()
+        share = D._info(6, rank)
+        while True:
+            rng, last = D.get_batch(D.query_next_batch_size(8))
+            mine += rng
+            if last:
+                votes.append(D.vote_finish_last_micro_batch())
+            D.finish_batch(rng, last)
+            if last:
+                break
+    TC.dist.wait_barrier()
+    if rank == 1:
+        TC.dist.send_msg(0, "hello from rank 1 " * 2000)          # longer than one mailbox slot
+    else:
+        assert TC.dist.recv_msg(1) == "hello from rank 1 " * 2000
+    q.put((rank, mine, votes, share))
+    TC.dist.wait_barrier()
+    TC.torch_col_shutdown()
+
+
+@pytest.mark.parametrize("policy", ["simple", "by_performance"])
+def test_ledger_two_ranks_split_every_global_batch(policy):
+    ctx = mp.get_context("spawn")
+    q, nm = ctx.Queue(), _name("dist2")
+    ps = [ctx.Process(target=_ledger_worker, args=(r, nm, policy, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    out = sorted(q.get(timeout=60) for _ in range(2))
+    for p in ps:
+        p.join(30)
+        assert p.exitcode == 0
+    ranges = sorted(out[0][1] + out[1][1])
+    assert ranges[0][0] == 0 and ranges[-1][1] == 64
+    assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    assert all(all(v) for _, _, v, _ in out)                          # both ranks voted "finish" each time
+    assert out[0][3] + out[1][3] == 32                                # shares of a global batch add up
+
+
+def test_distribute_batch_matches_reference_for_every_policy():
+    rnd = random.Random(2)
+    for _ in range(300):
+        n = rnd.randint(1, 8)
+        unproc = rnd.randint(n, 5000)
+        perf = [rnd.choice([0.0, rnd.uniform(0.1, 9.0)]) for _ in range(n)]
+        for pol in ("simple", "by_performance"):
+            got = O.distribute_batch(pol, unproc, perf, n)
+            assert sum(got) == unproc and (pol == "simple" or min(got) >= 1)
+
+
+# ---------------------------------------------------------------- train adjuster
+def _make_adjuster(world, targets, init_bs, cfg):
+    nm = _name("adj")
+    srv = PyInfTraCommunicator(True, True, world, nm)
+    for r in range(world):
+        srv.set_train_info(r, train_pid=1, train_rank=r, train_world_size=world, init_batch_size=init_bs,
+                           current_batch_size=targets[r], target_batch_size=targets[r],
+                           target_batch_size_unpublished=targets[r], model_name="resnet152")
+    h = C.c_void_p()
+    call("srt_adjuster_create", srv._h, C.byref(cfg), C.byref(h))
+    call("srt_adjuster_load_train_info", h)
+    return srv, h
+
+
+def test_train_adjuster_plans_match_reference_logic():
+    rnd = random.Random(3)
+    b, s = C.c_double(), C.c_double()
+    call("srt_adjuster_model_mem_param", b"gpt2", C.byref(b), C.byref(s))
+    assert (b.value, s.value) == O.MODEL_MEM_PARAM["gpt2"]
+    for trial in range(60):
+        world = rnd.choice([1, 2, 4])
+        init_bs = rnd.choice([32, 64, 128])
+        targets = [rnd.randint(0, init_bs)] * world if rnd.random() < 0.6 else [rnd.randint(0, init_bs) for _ in range(world)]
+        balance = rnd.random() < 0.5
+        cfg = AdjusterConfig(1150.0, 85.0, rnd.choice([0, 4]), int(balance), 1500.0, world, 1)
+        srv, h = _make_adjuster(world, targets, init_bs, cfg)
+        ref = O.TrainAdjuster(1150.0, 85.0, targets, init_bs, cfg.batch_size_limit, balance, 1500.0, world, True)
+        try:
+            for _ in range(6):
+                plan, n = (C.c_int * 8)(), C.c_int()
+                if rnd.random() < 0.6:
+                    dev, need = rnd.randrange(world), rnd.uniform(-100, 6000)
+                    avail = [rnd.uniform(0, 20000) for _ in range(world)]
+                    arr = (C.c_double * world)(*avail)
+                    call("srt_adjuster_infer_require_plan", h, dev, need, arr, plan, C.byref(n))
+                    want = ref.require(dev, need, avail)
+                else:
+                    av = [rnd.uniform(0, 20000) for _ in range(world)]
+                    fr = [rnd.uniform(0, 9000) for _ in range(world)]
+                    rs = [rnd.uniform(0, 2000) for _ in range(world)]
+                    call("srt_adjuster_infer_release_plan", h, (C.c_double * world)(*av), (C.c_double * world)(*fr),
+                         (C.c_double * world)(*rs), plan, C.byref(n))
+                    want = ref.release(av, fr, rs)
+                assert list(plan[:n.value]) == want, (trial, want, list(plan[:n.value]))
+                if want:                                                   # published to the information board
+                    assert [srv.get_field(r, 6) for r in range(world)] == want
+        finally:
+            call("srt_adjuster_destroy", h)
+            srv.close()
+
+
+# ---------------------------------------------------------------- page pool (host backend)
+def _pool(pool_mb=64, page_mb=2):
+    cfg = PoolConfig(0, 1, page_mb << 20, pool_mb << 20, 4, 1)
+    h = C.c_void_p()
+    call("srt_pool_create", C.byref(cfg), C.byref(h))
+    return h
+
+
+def _stat(h, which): return _lib.lib().srt_pool_stat(h, which)
+
+
+def test_pool_alloc_free_empty_cache_and_handover():
+    h = _pool()
+    try:
+        assert _stat(h, 4) == 32 and _stat(h, 5) == 64 << 20 and _stat(h, 6) == 2 << 20
+        ptrs = []
+        for nbytes in (3 << 20, 1 << 20, 5 << 20, 700, 2 << 20):
+            p = C.c_void_p()
+            call("srt_pool_alloc", h, 0, nbytes, C.byref(p))
+            C.memset(p.value, 0xAB, nbytes)                 # mapped and writable
+            ptrs.append(p)
+        used_pages = 32 - _stat(h, 4)
+        assert used_pages >= 6 and _stat(h, 3) == used_pages * (2 << 20)
+        assert _stat(h, 1) >= (3 + 1 + 5 + 2) << 20
+        # free the 5 MiB block: its wholly-free pages go back on empty_cache, partially used ones stay
+        call("srt_pool_free", h, 0, ptrs[2])
+        rel = C.c_size_t()
+        call("srt_pool_empty_cache", h, 0, C.byref(rel))
+        assert rel.value >= 2 << 20 and rel.value % (2 << 20) == 0
+        free_after = _stat(h, 4)
+        assert free_after == 32 - used_pages + rel.value // (2 << 20)
+        # the inference allocator can now take everything that is free, and not one page more
+        q = C.c_void_p()
+        call("srt_pool_alloc", h, 1, free_after * (2 << 20), C.byref(q))
+        assert _stat(h, 4) == 0 and _stat(h, 0) == free_after * (2 << 20)
+        with pytest.raises(SrtError):
+            call("srt_pool_alloc", h, 0, 8 << 20, C.byref(C.c_void_p()))
+        with pytest.raises(SrtError):
+            call("srt_pool_free", h, 0, ptrs[2])              # double free is an error, not a crash
+        call("srt_pool_free", h, 1, q)
+        call("srt_pool_empty_cache", h, 1, C.byref(rel))
+        assert rel.value == free_after * (2 << 20)
+        for i in (0, 1, 3, 4):
+            call("srt_pool_free", h, 0, ptrs[i])
+        call("srt_pool_empty_cache", h, 0, C.byref(rel))
+        assert _stat(h, 4) == 32 and _stat(h, 1) == 0 and _stat(h, 3) == 0
+        assert _stat(h, 7) == _stat(h, 8) > 0                 # every map has its unmap
+    finally:
+        call("srt_pool_destroy", h)
+
+
+def test_pool_oom_handler_gets_a_chance_to_release_memory():
+    h = _pool(pool_mb=16, page_mb=2)
+    held = C.c_void_p()
+    call("srt_pool_alloc", h, 0, 12 << 20, C.byref(held))
+    calls = []
+    FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_size_t)
+
+    def on_oom(user, kind, nbytes):   # what the trainer does on an L1 adjust: drop activations, empty the cache
+        calls.append((kind, nbytes))
+        call("srt_pool_free", h, 0, held)
+        call("srt_pool_empty_cache", h, 0, None)
+
+    cb = FN(on_oom)
+    call("srt_pool_set_oom_handler", h, C.cast(cb, C.c_void_p), None)
+    try:
+        p = C.c_void_p()
+        call("srt_pool_alloc", h, 1, 10 << 20, C.byref(p))   # inference needs more than is free
+        assert calls == [(1, 10 << 20)] and p.value
+    finally:
+        call("srt_pool_destroy", h)
+
+
+def test_pool_random_workload_keeps_invariants():
+    h = _pool(pool_mb=128, page_mb=2)
+    rnd = random.Random(4)
+    live = {}
+    try:
+        for it in range(3000):
+            if live and (rnd.random() < 0.45 or len(live) > 60):
+                k = rnd.choice(list(live))
+                kind, ptr, n, tag = live.pop(k)
+                assert C.string_at(ptr.value, 1)[0] == tag and C.string_at(ptr.value + n - 1, 1)[0] == tag
+                call("srt_pool_free", h, kind, ptr)
+            else:
+                kind, n = rnd.randint(0, 1), rnd.choice([512, 4096, 100000, 1 << 20, 3 << 20, 7 << 20])
+                p = C.c_void_p()
+                try:
+                    call("srt_pool_alloc", h, kind, n, C.byref(p))
+                except SrtError:
+                    call("srt_pool_empty_cache", h, 1 - kind, None)
+                    continue
+                tag = it % 251
+                C.memset(p.value, tag, n)
+                live[it] = (kind, p, n, tag)
+            if it % 97 == 0:
+                call("srt_pool_empty_cache", h, rnd.randint(0, 1), None)
+            mapped = (_stat(h, 3) + _stat(h, 0)) // (2 << 20)
+            assert mapped + _stat(h, 4) == 64                       # every page is FREE, TRAIN or INFER
+            assert _stat(h, 1) <= _stat(h, 3)
+        for kind, ptr, n, tag in live.values():
+            call("srt_pool_free", h, kind, ptr)
+        call("srt_pool_empty_cache", h, 0, None)
+        call("srt_pool_empty_cache", h, 1, None)
+        assert _stat(h, 4) == 64
+    finally:
+        call("srt_pool_destroy", h)

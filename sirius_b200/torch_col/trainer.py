@@ -64,7 +64,10 @@ class Trainer:
             try:
                 loss = self.iter_train_fn(batch)
             except (ColocateAdjustL1Exception, SwitchL1Exception, EngineColocateAdjustL1Exception) as exc:
-                if self._is_ddp_training() and batch.should_update_param():
+                # The reference votes "abort" only when the killed micro-batch is the syncing one; a rank
+                # already waiting in the finish vote would then never learn that its peer was killed on an
+                # earlier micro-batch, so here every kill in a multi-rank job casts the abort vote.
+                if self._is_ddp_training():
                     self.batch_manager.vote_abort_last_micro_batch()
                 self.handle_abort_batch(epoch_idx, batch_idx, batch, exc)
             else:

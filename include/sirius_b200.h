@@ -224,6 +224,9 @@ int srt_step_set_batch_device(srt_step* s, const float* dev_images, const int64_
  * buffer. Asynchronous. */
 int srt_step_forward_backward(srt_step* s, int B, int global_batch);
 int srt_step_forward_only(srt_step* s, int B);
+/* Inference-mode forward (BatchNorm uses its running statistics): the stand-in for the reference's
+ * TVM graph executor run, server/model_store/infer_model.cc:656-686. Logits via srt_step_logits. */
+int srt_step_forward_infer(srt_step* s, int B);
 /* accumulated += grad ; grad = 0  (GradAccumulator.accumulate). */
 int srt_step_accumulate(srt_step* s);
 /* SGD-momentum update from the accumulated gradients (or the last micro-batch's if none were

@@ -433,6 +433,24 @@ int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* 
                   ptr, (size_t)SRT_BN_STATIC_SCRATCH_BYTES, st);
 }
 
+__global__ void bn_eval_params_kernel(const float* __restrict__ gamma, const float* __restrict__ beta,
+                                      const float* __restrict__ rmean, const float* __restrict__ rvar,
+                                      float eps, int C, float* scale, float* shift) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float sc = (gamma ? gamma[c] : 1.f) * rsqrtf(rvar[c] + eps);
+  scale[c] = sc;
+  shift[c] = (beta ? beta[c] : 0.f) - rmean[c] * sc;
+}
+
+// scale/shift of inference-mode BatchNorm: y = (z - running_mean) / sqrt(running_var + eps) * g + b.
+int bn_eval_params(const float* gamma, const float* beta, const float* rmean, const float* rvar, float eps, int C,
+                   float* scale, float* shift, cudaStream_t st) {
+  bn_eval_params_kernel<<<ceil_div(C, 128), 128, 0, st>>>(gamma, beta, rmean, rvar, eps, C, scale, shift);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
              const float* scale, const float* shift, int relu, cudaStream_t st) {
   SRT_REQUIRE(C % 8 == 0, "bn_apply: C (%d) must be a multiple of 8", C);

@@ -9,6 +9,8 @@ size_t bn_scratch_bytes(int64_t rows, int C);
 int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, const float* beta,
              float eps, float momentum, float* rm, float* rv, float* mean, float* invstd,
              float* scale, float* shift, void* scratch, size_t scratch_bytes, cudaStream_t st);
+int bn_eval_params(const float* gamma, const float* beta, const float* rmean, const float* rvar, float eps, int C,
+                   float* scale, float* shift, cudaStream_t st);
 int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
                     const float* beta, float eps, float momentum, float* rm, float* rv, float* mean,
                     float* invstd, float* scale, float* shift, cudaStream_t st);

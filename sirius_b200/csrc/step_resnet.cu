@@ -93,6 +93,7 @@ struct Step {
   std::vector<void*> allocs;
 
   int opt_steps = 0;
+  bool eval_mode = false;  // forward with BatchNorm running statistics (the inference stand-in)
   int accum_pending = 0;
   size_t act_bytes = 0;
 
@@ -439,7 +440,12 @@ int Step::forward(int B) {
     const double abytes = (double)rows * u.bn.C * esz;
     if ((r = timed(SRT_PROF_CONV, flops, [&] { return conv_fprop(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, stream); })))
       return r;
-    if ((r = timed(SRT_PROF_NORM, abytes, [&] {
+    if (eval_mode) {
+      // inference: normalise with the running statistics (scale/shift prepared by bn_eval_params)
+      if ((r = bn_eval_params(pf(u.bn.gamma), pf(u.bn.beta), bf_(u.bn.rmean), bf_(u.bn.rvar), cfg.bn_eps, u.bn.C,
+                              u.bn.scale, u.bn.shift, stream)))
+        return r;
+    } else if ((r = timed(SRT_PROF_NORM, abytes, [&] {
           return bn_stats(dt, u.z, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
                           bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift,
                           scratch, scratch_bytes, stream); })))
@@ -691,6 +697,16 @@ int srt_step_forward_only(srt_step* h, int B) {
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_only: bad batch size");
   if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
   return s->forward(B);
+}
+
+int srt_step_forward_infer(srt_step* h, int B) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_infer: bad batch size");
+  if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
+  s->eval_mode = true;
+  const int rc = s->forward(B);
+  s->eval_mode = false;
+  return rc;
 }
 
 int srt_step_accumulate(srt_step* h) {

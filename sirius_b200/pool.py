@@ -1,0 +1,44 @@
+"""Python handle on the page pool (include/sirius_pool.h)."""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib, _runtime  # noqa: F401
+from ._lib import call
+from ._runtime import PoolConfig
+
+TRAIN, INFER = 0, 1
+STAT = {"infer_usage": 0, "train_usage": 1, "train_peak": 2, "train_all": 3, "free_pages": 4, "pool_nbytes": 5,
+        "page_nbytes": 6, "num_map": 7, "num_unmap": 8, "infer_allocated": 9}
+
+
+class PagePool:
+    """One pool of physical pages on a GPU with a training and an inference allocator
+    (colserve::sta::CUDAMemPool, common/cuda_allocator.h:61-150)."""
+
+    def __init__(self, pool_gb: float, device: int = 0, page_mb: int = 32, host_backend: bool = False):
+        cfg = PoolConfig(device, 1 if host_backend else 0, page_mb << 20, int(pool_gb * (1 << 30)), 0, 0)
+        self._h = C.c_void_p()
+        call("srt_pool_create", C.byref(cfg), C.byref(self._h))
+
+    @property
+    def handle(self): return self._h
+
+    def alloc(self, kind: int, nbytes: int) -> int:
+        p = C.c_void_p()
+        call("srt_pool_alloc", self._h, kind, nbytes, C.byref(p))
+        return p.value
+
+    def free(self, kind: int, ptr: int): call("srt_pool_free", self._h, kind, C.c_void_p(ptr))
+
+    def empty_cache(self, kind: int = TRAIN) -> int:
+        n = C.c_size_t()
+        call("srt_pool_empty_cache", self._h, kind, C.byref(n))
+        return n.value
+
+    def stat(self, name: str) -> int: return _lib.lib().srt_pool_stat(self._h, STAT[name])
+
+    def close(self):
+        if self._h:
+            call("srt_pool_destroy", self._h)
+            self._h = C.c_void_p()

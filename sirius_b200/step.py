@@ -32,6 +32,7 @@ register({
     "srt_step_set_batch_device": (None, [_vp, _vp, _vp, _i]),
     "srt_step_forward_backward": (None, [_vp, _i, _i]),
     "srt_step_forward_only": (None, [_vp, _i]),
+    "srt_step_forward_infer": (None, [_vp, _i]),
     "srt_step_accumulate": (None, [_vp]),
     "srt_step_optimizer": (None, [_vp]),
     "srt_step_loss": (None, [_vp, C.POINTER(C.c_float)]),
@@ -141,6 +142,9 @@ class ResNetStep:
 
     def forward_only(self, B: int) -> None:
         call("srt_step_forward_only", self._h, B)
+
+    def forward_infer(self, B: int) -> None:
+        call("srt_step_forward_infer", self._h, B)
 
     def accumulate(self) -> None:
         call("srt_step_accumulate", self._h)

@@ -1,0 +1,147 @@
+"""Colocation on the GPU: a pool-backed ResNet step is killed in mid-batch by an L1 adjust from the
+(debug) inference server, releases its activation pages, replies, and carries on; the freed pages are
+immediately usable by the inference allocator. Mirrors the reference's kill-vs-no-kill check
+(train/train_valiation.py:83-95): a run with a kill must reproduce the losses and weights of a run
+without one, because the killed micro-batch is redone from the same samples."""
+import os
+import time
+import uuid
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import resnet_oracle as O
+from sirius_b200 import ops
+from sirius_b200._lib import SrtError
+from sirius_b200.pool import INFER, TRAIN, PagePool
+from sirius_b200.step import ResNetStep
+
+ARCH, B, IMG = "resnet50", 16, 64
+
+
+def _batches(n):
+    return O.make_batches(B, n, IMG)
+
+
+def test_pool_backed_step_matches_cudamalloc_step_and_releases_pages():
+    pool = PagePool(2.0)
+    model = O.build_model(ARCH, 0)
+    ref = ResNetStep(layers=O.LAYERS[ARCH], max_batch=B, image=IMG, dtype="bf16")
+    stp = ResNetStep(layers=O.LAYERS[ARCH], max_batch=B, image=IMG, dtype="bf16", pool=pool.handle)
+    for s in (ref, stp):
+        s.load_state_dict(O.state_arrays(model))
+    batches = _batches(3)
+    l_ref = [ref.train_step(*b) for b in batches]
+    l_stp = [stp.train_step(*b) for b in batches[:2]]
+    # handover: everything the step took from the pool for activations comes back as whole pages
+    used = pool.stat("train_all")
+    assert used > 0 and pool.stat("free_pages") * pool.stat("page_nbytes") + used == pool.stat("pool_nbytes")
+    t0 = time.perf_counter()
+    released = stp.release_activations()
+    dt = time.perf_counter() - t0
+    assert released == used and pool.stat("train_all") == 0
+    print(f"released {released / 2**20:.0f} MiB in {dt * 1e3:.2f} ms = {dt * 1e3 / (released / 2**30):.2f} ms/GiB")
+    # the inference allocator can map all of it at once, and training cannot while it is held
+    p = pool.alloc(INFER, pool.stat("pool_nbytes"))
+    with pytest.raises(SrtError):
+        stp.reserve_activations(B)
+    pool.free(INFER, p)
+    pool.empty_cache(INFER)
+    # regain: the next step re-allocates and continues bit-exactly
+    l_stp.append(stp.train_step(*batches[2]))
+    assert l_stp == l_ref
+    for k in ("conv1.weight", "layer3.2.conv2.weight", "fc.weight"):
+        assert np.array_equal(stp.get(k), ref.get(k))
+    assert ops.tc_status() == 0
+    stp.close(); ref.close(); pool.close()
+
+
+def test_l1_adjust_kills_batch_releases_memory_and_training_reproduces_undisturbed_run():
+    from sirius_b200 import torch_col as tc
+    tag = f"{os.getpid()}_{uuid.uuid4().hex[:6]}"
+    os.environ.update({"COLTRAIN_MODE": "colocate-l1", "COLTRAIN_HOOK_MODE": "xsched-sync2", "COLTRAIN_USE_XSCHED": "1",
+                       "COLTRAIN_HAS_INFER_SERVER": "1", "COLTRAIN_USE_SHARED_TENSOR": "1",
+                       "SIRIUS_B200_COMM_NAME": f"srt_gpu_comm_{tag}", "SIRIUS_B200_DIST_NAME": f"srt_gpu_dist_{tag}"})
+    model = O.build_model(ARCH, 0)
+    DS, GBS, EPOCHS = 96, 32, 2
+
+    def run(inject):
+        srv = tc.DebugServer(1, os.environ["SIRIUS_B200_COMM_NAME"])
+        pool = PagePool(2.0)
+        tc.setup_colocate_training(0, 1, False, False)
+        step = ResNetStep(layers=O.LAYERS[ARCH], max_batch=B, image=IMG, dtype="bf16", pool=pool.handle)
+        step.load_state_dict(O.state_arrays(model))
+        tc.set_train_step(step)
+        tc.set_memory_pool(pool.handle)
+        ctrl = tc.create_colocate_ctrl(tc.get_colocate_train_mode(), tc.get_colocate_ctrl_hook_mode(), EPOCHS, B,
+                                       stub_poll_ms=5)
+        ds, mgr = tc.init_dynamic_batch(DS, tc.DatasetType.VISION, tc.VisionDatasetConfig((3, IMG, IMG), 1000), B,
+                                        global_batch_size=GBS, enable_grad_accumulate=True, checkpoint_micro_batch=True)
+        tc.init_train_info(B, B, "resnet152")
+        acc = tc.GradAccumulator(step)
+        losses, state = [], {"n": 0, "cid": None, "free_before": None}
+
+        def iter_train_fn(batch):
+            state["n"] += 1
+            step.upload_batch(batch["images"], batch["labels"])
+            if inject and state["n"] == 4 and state["cid"] is None:
+                state["free_before"] = pool.stat("free_pages")
+                state["cid"] = srv.colocate_l1([B])        # same target: the batch is redone as it was
+                time.sleep(0.05)                           # the control thread raises the kill flag
+            try:
+                step.forward_backward(len(batch), GBS)
+            except SrtError as e:
+                if "aborted" in str(e):
+                    raise tc.ColocateAdjustL1Exception("killed in the executor")
+                raise
+            ctrl.check_kill("after backward")
+            loss = step.loss()
+            mgr.optimizer_step(batch, step, grad_accumulator=acc)
+            losses.append(loss)
+            return loss
+
+        trainer = tc.Trainer(step, iter_train_fn)
+        ctrl.train_start()
+        for e in range(EPOCHS):
+            trainer.train_one_epoch(e)
+        ctrl.train_end()
+        step.synchronize()
+        out = {"losses": losses, "w": step.get("layer2.1.conv2.weight"), "killed": trainer.get_overall_stat().killed_batch,
+               "adjust": list(ctrl.adjust_log), "done": srv.events(tc.CtrlEvent.kColocateAdjustL1Done),
+               "cid": state["cid"], "free_before": state["free_before"], "page": pool.stat("page_nbytes")}
+        assert ops.tc_status() == 0
+        step.close()
+        tc.cleanup_colocate_training(False)
+        tc.set_train_step(None)
+        pool.close()
+        srv.close()
+        return out
+
+    quiet = run(False)
+    noisy = run(True)
+    assert quiet["killed"] == 0 and noisy["killed"] == 1
+    assert [m.id for _, m in noisy["done"]] == [noisy["cid"]]
+    rel_ms, cache_ms, reply_ms, released = noisy["adjust"][0]
+    assert released > 0 and released % noisy["page"] == 0
+    print(f"L1 adjust: release {rel_ms:.2f} ms, empty cache {cache_ms:.2f} ms, reply {reply_ms:.2f} ms, "
+          f"{released / 2**20:.0f} MiB handed over = {(rel_ms + cache_ms + reply_ms) / (released / 2**30):.2f} ms/GiB")
+    # the killed micro-batch was redone from the same samples: identical finished-batch losses and weights
+    assert noisy["losses"] == quiet["losses"]
+    assert np.array_equal(noisy["w"], quiet["w"])
+
+
+def test_inference_mode_forward_uses_running_statistics():
+    model = O.build_model("resnet14", 0)
+    (im, lb), = O.make_batches(4, 1, 64)
+    with torch.no_grad():
+        model.train(); model(im); model(im)        # move the running statistics away from their defaults
+        model.eval(); ref = model(im[:1]).numpy()
+    step = ResNetStep(layers=O.LAYERS["resnet14"], max_batch=4, image=64, dtype="f32")
+    step.load_state_dict(O.state_arrays(model))
+    step.upload_batch(im[:1].contiguous(), lb[:1].contiguous())
+    step.forward_infer(1)
+    got = step.logits(1)
+    assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()

@@ -26,6 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 ARCH, BATCH, IMAGE, CLASSES = "resnet152", 64, 224, 1000
+POOL_GB = 12.0            # COLTRAIN_SHARED_TENSOR_POOL_GB default of the reference (config.cc:57-69)
 FLOP_PER_SAMPLE = 68.85e9  # forward + backward, 2 FLOP per MAC (torch.utils.flop_counter on the CPU model)
 METRIC, UNIT = "train samples/s", "samples/s"
 WORKLOAD = "ResNet-152 train step (fwd+bwd+SGD-momentum), bf16, batch 64 per GPU, 3x224x224 N(0,1)"
@@ -123,9 +124,15 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a short collective timeout: a mismatch between ranks must fail in minutes, not hang the box
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=120))
 
-    step = ResNetStep(arch=ARCH, num_classes=CLASSES, max_batch=BATCH, image=IMAGE, dtype="bf16")
+    # activations come from the training allocator of a page pool (CUDA VMM), as in the colocated setup
+    from sirius_b200.pool import PagePool
+    pool = PagePool(POOL_GB, device=local)
+    step = ResNetStep(arch=ARCH, num_classes=CLASSES, max_batch=BATCH, image=IMAGE, dtype="bf16", pool=pool.handle)
     step.load_state_dict(seeded_state(ARCH))
     stream = torch.cuda.ExternalStream(step.stream)
 
@@ -212,6 +219,27 @@ def run_ours(args):
     from sirius_b200 import ops
     status = ops.tc_status()
 
+    # ---- memory handover: give the activation pages back to the pool, then regain them ----
+    handover = None
+    if rank == 0:
+        rel_ms, regain_ms, nbytes = [], [], 0
+        for _ in range(3):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            nbytes = step.release_activations()      # sync + free blocks + unmap empty pages
+            t1 = time.perf_counter()
+            step.reserve_activations(BATCH)          # map pages again for the same batch size
+            t2 = time.perf_counter()
+            rel_ms.append((t1 - t0) * 1e3)
+            regain_ms.append((t2 - t1) * 1e3)
+        torch.cuda.synchronize()
+        gib = nbytes / 2 ** 30
+        handover = {"released_gib": round(gib, 3), "release_ms": round(min(rel_ms), 3),
+                    "release_ms_per_gib": round(min(rel_ms) / gib, 3), "regain_ms": round(min(regain_ms), 3),
+                    "page_mib": pool.stat("page_nbytes") >> 20,
+                    "what": "srt_step_release_activations: stream sync, free of the activation set, cuMemUnmap of "
+                            "every emptied page (pages become FREE for the inference allocator)"}
+
     peaks = load_peaks()
     fam = {}
     for name, d in prof.items():
@@ -247,6 +275,7 @@ def run_ours(args):
         "kernel_families": fam,
         "model_flops_frac": round(value / world * FLOP_PER_SAMPLE / (peaks["tflops"] * 1e12), 4),
         "tc_status": status,
+        "handover": handover,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(sample_batch=16, steps=1, warmup=1)

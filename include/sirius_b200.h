@@ -192,6 +192,10 @@ int srt_resnet_create(const srt_resnet_config* cfg, srt_step** out);
  * of the step through CUDAColAllocator -> CUDAMemPool (torch_allocator_plugin.cc:108-139). */
 struct srt_pool;
 int srt_resnet_create_with_pool(const srt_resnet_config* cfg, struct srt_pool* pool, srt_step** out);
+/* Same, choosing the allocator of the pool: 0 = training (caching), 1 = inference (direct; what the
+ * stand-in inference worker uses, as the reference's server allocates with MemType::kInfer). */
+int srt_resnet_create_on_allocator(const srt_resnet_config* cfg, struct srt_pool* pool, int pool_kind,
+                                   srt_step** out);
 /* Memory handover, training side (ColocateCtrl.adjust_l1, pytorch/torch_col/colocate_ctrl.py:413-445:
  * release_interm_memory + MemoryPool.empty_cache): synchronises the stream, frees the activation set
  * and returns the pages that became empty to the pool. *released_bytes = bytes of pages handed back

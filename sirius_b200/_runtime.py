@@ -106,6 +106,7 @@ register({
     "srt_pool_stat": (_i64, [_vp, _i]),
     "srt_pool_set_oom_handler": (None, [_vp, _vp, _vp]),
     "srt_resnet_create_with_pool": (None, [_vp, _vp, C.POINTER(_vp)]),
+    "srt_resnet_create_on_allocator": (None, [_vp, _vp, _i, C.POINTER(_vp)]),
     "srt_step_release_activations": (None, [_vp, C.POINTER(_sz)]),
     "srt_step_reserve_activations": (None, [_vp, _i]),
     "srt_step_request_abort": (None, [_vp, _i]),

@@ -101,6 +101,7 @@ struct Step {
   // Taken from the training allocator of a page pool when one is attached (so that releasing them
   // and emptying the allocator's cache hands whole pages to the inference side), else cudaMalloc.
   srt_pool* pool = nullptr;
+  int pool_kind = SRT_POOL_TRAIN;  // which allocator of the pool serves this step (INFER for the stand-in worker)
   int act_batch = 0;               // batch size the activation set is currently sized for (0 = released)
   std::vector<void*> act_blocks;
   // Kill-batch support: a flag any thread may raise; forward/backward look at it between units and
@@ -113,7 +114,7 @@ struct Step {
   int aalloc(void** out, size_t bytes) {
     bytes = bytes ? bytes : 256;
     if (pool) {
-      int rc = srt_pool_alloc(pool, SRT_POOL_TRAIN, bytes, out);
+      int rc = srt_pool_alloc(pool, pool_kind, bytes, out);
       if (rc) return rc;
     } else {
       SRT_CHECK_CUDA(cudaMalloc(out, (bytes + 255) / 256 * 256));
@@ -318,7 +319,15 @@ int Step::build() {
   if ((rc = dalloc((void**)&stage_images, (size_t)B * 3 * IMG * IMG * 4, false))) return rc;
   if ((rc = dalloc((void**)&stage_labels, (size_t)B * 8, false))) return rc;
 
-  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  if (pool_kind == SRT_POOL_INFER) {
+    // the inference stand-in runs on the highest-priority stream so its blocks are scheduled ahead of
+    // training blocks whenever an SM frees a slot
+    int lo = 0, hi = 0;
+    SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    SRT_CHECK_CUDA(cudaStreamCreateWithPriority(&stream, cudaStreamNonBlocking, hi));
+  } else {
+    SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  }
   own_stream = true;
   if ((rc = alloc_activations(B))) return rc;
 
@@ -391,7 +400,7 @@ int Step::release_activations(size_t* released_bytes) {
   if (stream) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
   for (void* p : act_blocks) {
     if (pool) {
-      int rc = srt_pool_free(pool, SRT_POOL_TRAIN, p);
+      int rc = srt_pool_free(pool, pool_kind, p);
       if (rc) return rc;
     } else {
       cudaFree(p);
@@ -402,7 +411,7 @@ int Step::release_activations(size_t* released_bytes) {
   act_bytes = 0;
   act_batch = 0;
   if (pool) {
-    int rc = srt_pool_empty_cache(pool, SRT_POOL_TRAIN, &freed);
+    int rc = srt_pool_empty_cache(pool, pool_kind, &freed);
     if (rc) return rc;
   }
   if (released_bytes) *released_bytes = freed;
@@ -567,11 +576,17 @@ int srt_resnet_create(const srt_resnet_config* cfg, srt_step** out) {
 }
 
 int srt_resnet_create_with_pool(const srt_resnet_config* cfg, srt_pool* pool, srt_step** out) {
+  return srt_resnet_create_on_allocator(cfg, pool, SRT_POOL_TRAIN, out);
+}
+
+int srt_resnet_create_on_allocator(const srt_resnet_config* cfg, srt_pool* pool, int pool_kind, srt_step** out) {
   SRT_REQUIRE(cfg && out, "resnet_create: null argument");
+  SRT_REQUIRE(pool_kind == SRT_POOL_TRAIN || pool_kind == SRT_POOL_INFER, "resnet_create: unknown allocator %d", pool_kind);
   SRT_REQUIRE(cfg->dtype == SRT_F32 || cfg->dtype == SRT_BF16, "resnet_create: unknown dtype");
   Step* s = new Step();
   s->cfg = *cfg;
   s->pool = pool;
+  s->pool_kind = pool_kind;
   int rc = s->build();
   if (rc == SRT_OK) rc = cudaStreamSynchronize(s->stream) == cudaSuccess ? SRT_OK : SRT_ERR_CUDA;
   if (rc != SRT_OK) { delete s; return rc; }

@@ -66,7 +66,7 @@ class ResNetStep:
     MicroBatchManager/GradAccumulator (pytorch/torch_col/dynamic_batch.py:112-153)."""
 
     def __init__(self, arch="resnet152", num_classes=1000, max_batch=16, image=224, dtype="bf16",
-                 impl=IMPL_AUTO, lr=0.1, momentum=0.9, weight_decay=1e-4, layers=None, pool=None):
+                 impl=IMPL_AUTO, lr=0.1, momentum=0.9, weight_decay=1e-4, layers=None, pool=None, pool_kind=0):
         cfg = ResNetConfigC()
         lay = tuple(layers) if layers is not None else RESNET_LAYERS[arch]
         cfg.layers = (C.c_int * 4)(*lay)
@@ -79,7 +79,7 @@ class ResNetStep:
         self.dtype = "f32" if cfg.dtype == SRT_F32 else "bf16"
         self._h = _vp()
         self.pool = pool
-        call("srt_resnet_create_with_pool", C.byref(cfg), pool if pool else None, C.byref(self._h))
+        call("srt_resnet_create_on_allocator", C.byref(cfg), pool if pool else None, int(pool_kind), C.byref(self._h))
         self.params: dict[str, ParamInfo] = {}
         n = _lib.lib().srt_step_num_params(self._h)
         name = C.create_string_buffer(256)

@@ -73,7 +73,7 @@ class ColocateCtrl(CtrlBase):
         super().__init__(train_mode, hook_mode, num_epoch, batch_size)
         self._stub = _C.PyColocateStub(batch_size, poll_ms=stub_poll_ms)
         _C._last_colocate_stub = self._stub
-        self.adjust_log = []  # (release_ms, empty_cache_ms, reply_ms, released_bytes)
+        self.adjust_log = []  # (release_ms, empty_cache_ms, reply_ms, released_bytes, start time.time())
 
     def check_kill(self, where: str):
         """What the reference's forward/backward hooks do (colocate_ctrl.py:360-400)."""
@@ -125,7 +125,7 @@ class ColocateCtrl(CtrlBase):
             t2 = time.time()
             self._stub.adjust_l1_done()
             t3 = time.time()
-        self.adjust_log.append(((t1 - t0) * 1e3, (t2 - t1) * 1e3, (t3 - t2) * 1e3, released))
+        self.adjust_log.append(((t1 - t0) * 1e3, (t2 - t1) * 1e3, (t3 - t2) * 1e3, released, t0))
         if _C._Config.log_control_stub:
             print(f'[Rank {_C.get_train_rank()} | PID {os.getpid()}] [Adjust L1 {(t1-t0)*1e3:.1f} | {(t2-t1)*1e3:.1f}'
                   f' | {(t3-t2)*1e3:.1f} ms] target batch_size: {self.target_batch_size}, released {released >> 20} MiB',
@@ -136,7 +136,7 @@ class ColocateCtrl(CtrlBase):
         with EventManager.record_duration_event('adjust_l2'):
             released = int(MemoryPool.empty_cache() or 0)
             self._stub.adjust_l2_done()
-        self.adjust_log.append((0.0, (time.time() - t0) * 1e3, 0.0, released))
+        self.adjust_log.append((0.0, (time.time() - t0) * 1e3, 0.0, released, t0))
 
     def report_batch_size(self, batch_size): self._stub.report_batch_size(batch_size)
 

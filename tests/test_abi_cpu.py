@@ -1,0 +1,51 @@
+"""The C-ABI library loads without a GPU and exports every function the public headers declare."""
+import ctypes as C
+import pathlib
+import re
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+DECL = re.compile(r"^\s*(?:const\s+)?[A-Za-z_][\w\s\*]*?\b(srt_\w+)\s*\(", re.M)
+
+
+def header_functions():
+    names = {}
+    for h in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
+        text = re.sub(r"//[^\n]*", "", text)
+        text = re.sub(r"^\s*#[^\n]*(?:\\\n[^\n]*)*", "", text, flags=re.M)
+        for m in DECL.finditer(text):
+            line = text[text.rfind("\n", 0, m.start()) + 1:m.end()]
+            if "typedef" in line:
+                continue
+            names.setdefault(m.group(1), h.name)
+    return names
+
+
+def test_headers_declare_functions():
+    names = header_functions()
+    assert len(names) > 100, len(names)
+    for must in ("srt_conv_fprop", "srt_step_forward_backward", "srt_pool_alloc", "srt_comm_open", "srt_stub_create"):
+        assert must in names, must
+
+
+def test_library_exports_every_declared_function():
+    from sirius_b200 import _lib
+    lib = _lib.lib()
+    missing = [f"{n} ({h})" for n, h in header_functions().items() if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_every_declared_function_has_a_python_signature():
+    from sirius_b200 import _lib, _runtime, ops, pool, step  # noqa: F401  (each registers its signatures)
+    bound = set(_lib.declared_symbols())
+    unbound = sorted(set(header_functions()) - bound)
+    assert not unbound, unbound
+    extra = sorted(n for n in bound if n not in header_functions())
+    assert not extra, f"bound in Python but not declared in include/: {extra}"
+
+
+def test_error_string_and_version_calls_need_no_gpu():
+    from sirius_b200 import _lib
+    lib = _lib.lib()
+    lib.srt_last_error.restype = C.c_char_p
+    assert isinstance(lib.srt_last_error(), bytes)

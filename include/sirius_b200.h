@@ -202,6 +202,11 @@ int srt_resnet_create_on_allocator(const srt_resnet_config* cfg, struct srt_pool
  * (bytes freed when no pool is attached). The next forward re-allocates for its batch size. */
 int srt_step_release_activations(srt_step* s, size_t* released_bytes);
 int srt_step_reserve_activations(srt_step* s, int B);
+/* The same handover when the trainer already knows the batch size it continues with (the adjust command
+ * carries it): frees the set, places the set for micro-batches of B samples on pages that are still
+ * mapped, then returns only the pages that stayed empty. The outcome equals release + the re-allocation
+ * the reference's next iteration would do, but nothing is unmapped and mapped again. B == 0 releases all. */
+int srt_step_shrink_activations(srt_step* s, int B, size_t* released_bytes);
 /* Kill batch (ColocateStub on kColocateAdjustL1, pytorch/torch_col/csrc/control_stub.cc:486-510; the
  * reference drops the launches still queued in xsched): any thread may raise the flag; forward and
  * backward test it between units and return SRT_ERR_ABORTED, and never run more than 8 units ahead of

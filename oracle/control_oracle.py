@@ -3,7 +3,7 @@ INFRASTRUCTURE ONLY: never imported by the product.
 
 Each function follows the cited reference code literally (plain Python ints / floats), so the C++
 runtime can be compared with it on random inputs. The reference has no tests or golden vectors for
-these functions (SURVEY section 4), so parity here is "restatement vs. restatement by independent
+these functions, so parity here is "restatement vs. restatement by independent
 code paths", pinned on the reference's source text.
 """
 from __future__ import annotations

@@ -31,7 +31,8 @@ class StubConfig(C.Structure):
 
 class PoolConfig(C.Structure):
     _fields_ = [("device", _i), ("backend", _i), ("page_nbytes", _sz), ("pool_nbytes", _sz),
-                ("train_va_scale", _i), ("infer_va_scale", _i)]
+                ("train_va_scale", _i), ("infer_va_scale", _i),
+                ("unmap_on_release", _i)]
 
 
 _PM, _PT = C.POINTER(CtrlMsg), C.POINTER(TrainInfo)
@@ -108,6 +109,7 @@ register({
     "srt_resnet_create_with_pool": (None, [_vp, _vp, C.POINTER(_vp)]),
     "srt_resnet_create_on_allocator": (None, [_vp, _vp, _i, C.POINTER(_vp)]),
     "srt_step_release_activations": (None, [_vp, C.POINTER(_sz)]),
+    "srt_step_shrink_activations": (None, [_vp, C.c_int, C.POINTER(_sz)]),
     "srt_step_reserve_activations": (None, [_vp, _i]),
     "srt_step_request_abort": (None, [_vp, _i]),
 })

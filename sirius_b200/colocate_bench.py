@@ -1,7 +1,7 @@
 """Colocation experiment on one GPU: ResNet-152 training (torch_col Trainer, colocate-l1) next to a
 stand-in inference worker that serves batch-1 ResNet-152 requests arriving as a seeded Poisson process.
 
-    python -m sirius_b200.colocate_bench [--duration 10] [--rate 50] [--idle-ms 50]
+    python -m sirius_b200.colocate_bench [--duration 10] [--rate 50] [--idle-ms 500] [--burst-s 1] [--gap-s 1]
 
 The worker plays the inference server's part of the reference's protocol (server/model_store/
 infer_model.cc:394-523,656-686 and server/control/controller.cc:268-386): when a request finds the
@@ -13,7 +13,8 @@ so inference cannot run without a handover. Reports training samples/s over the 
 percentiles, and the handover latency (adjust sent -> done received) per GiB released.
 
 Arrivals stand in for the reference harness's trace generators (eval/runner/hyper_workload.py:350-373):
-exponential inter-arrival times from numpy's MT19937 seeded with 0; no trace file is replayed.
+exponential inter-arrival times from numpy's MT19937 seeded with 0, switched on and off in bursts so that
+the idle give-back and the next cold request both occur; no trace file is replayed.
 """
 from __future__ import annotations
 
@@ -28,7 +29,7 @@ import uuid
 import numpy as np
 
 
-def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="resnet152", seed=0, verbose=False):
+def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch=64, image=224, arch="resnet152", seed=0, verbose=False):
     import torch
     from . import torch_col as tc
     from ._lib import SrtError, call
@@ -72,6 +73,12 @@ def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="res
     step.load_state_dict(sd)
     if pool.stat("free_pages") >= infer_pages:
         raise RuntimeError("pool sizing: inference fits beside training without a handover")
+    # one release/regain cycle during set-up: the first unmap after the large frees above (probe step and
+    # probe pool) has been seen to take 0.1-2.4 s in the driver, later ones 17 ms
+    t0 = time.perf_counter()
+    step.release_activations()
+    setup_release_ms = (time.perf_counter() - t0) * 1e3
+    step.reserve_activations(batch)
     tc.set_train_step(step)
     tc.set_memory_pool(pool.handle)
     ctrl = tc.create_colocate_ctrl(tc.get_colocate_train_mode(), tc.get_colocate_ctrl_hook_mode(), 1, batch, stub_poll_ms=2)
@@ -89,6 +96,7 @@ def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="res
     stop = threading.Event()
     t_start = [None]
     lat_ms, handover, sent_at, kill_seen = [], [], [], []
+    phase = {"reserve": [], "serve": [], "give_back": []}
     gpu_tpc = torch.cuda.get_device_properties(0).multi_processor_count // 2
     infer_tpc = max(1, gpu_tpc * 27 // 40)   # the reference asks for 27 of a V100's 40 TPCs for resnet152
 
@@ -103,7 +111,9 @@ def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="res
         while not stop.is_set():
             now = time.perf_counter()
             if have_mem and now - last_done > idle_ms / 1e3 and t_next - now > 0:
+                t1 = time.perf_counter()
                 infer.release_activations()   # frees the blocks and unmaps the inference pages
+                phase["give_back"].append((time.perf_counter() - t1) * 1e3)
                 plan, n = (C.c_int * 8)(), C.c_int()
                 avail = (C.c_double * 1)(pool.stat("pool_nbytes") / 2 ** 20)
                 free = (C.c_double * 1)(pool.stat("free_pages") * page / 2 ** 20)
@@ -116,25 +126,30 @@ def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="res
                 continue
             t_arr = t_next
             t_next += rng.exponential(1.0 / rate)
+            if burst_s > 0 and (t_next - t_start[0] - 1.0) % (burst_s + gap_s) > burst_s:   # off period: next burst
+                t_next = t_start[0] + 1.0 + ((t_next - t_start[0] - 1.0) // (burst_s + gap_s) + 1) * (burst_s + gap_s)
             if not have_mem:
                 plan, n = (C.c_int * 8)(), C.c_int()
                 need_mb = (infer_pages + 1) * page / 2 ** 20
                 call("srt_adjuster_infer_require_plan", adj, 0, need_mb, None, plan, C.byref(n))
                 t0 = time.perf_counter()
                 sent_at.append(time.time())
-                free_before = pool.stat("free_pages")
                 cid = srv.colocate_l1([max(plan[0], 1)] if n.value else [batch])
                 srv.wait_adjust_done(cid, 30)
                 dt = time.perf_counter() - t0
-                handover.append((dt * 1e3, (pool.stat("free_pages") - free_before) * page))
+                handover.append(dt * 1e3)
+                t1 = time.perf_counter()
                 infer.reserve_activations(1)
+                phase["reserve"].append((time.perf_counter() - t1) * 1e3)
                 have_mem = True
+            t2 = time.perf_counter()
             srv.comm.infer_tpc(0, 1, infer_tpc)            # AddInferRequiredTpcNum
             infer.upload_batch(img, lab)
             infer.forward_infer(1)
             infer.synchronize()
             srv.comm.infer_tpc(0, 2, infer_tpc)            # DecInferRequiredTpcNum
             last_done = time.perf_counter()
+            phase["serve"].append((last_done - t2) * 1e3)
             lat_ms.append((last_done - t_arr) * 1e3)
 
     losses, finished = [], [0]
@@ -178,8 +193,11 @@ def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="res
     ctrl.train_end()
     stat = trainer.get_overall_stat()
     lat = np.sort(np.array(lat_ms)) if lat_ms else np.array([float("nan")])
-    ho_ms = np.array([h[0] for h in handover]) if handover else np.array([float("nan")])
-    ho_gib = np.array([h[1] / 2 ** 30 for h in handover]) if handover else np.array([float("nan")])
+    ho_ms = np.array(handover) if handover else np.array([float("nan")])
+    # bytes the trainer handed back at each adjust (its own count of unmapped pages)
+    rel = [a[3] / 2 ** 30 for a in ctrl.adjust_log][:len(handover)]
+    ho_gib = np.array(rel) if rel and len(rel) == len(handover) else np.full(len(ho_ms), float("nan"))
+    pct = lambda v, q: round(float(np.sort(np.array(v))[min(len(v) - 1, int(len(v) * q))]), 3) if v else None
     out = {
         "train_samples_per_s": round(finished[0] / window, 1), "window_s": round(window, 2),
         "requests": len(lat_ms), "request_rate_per_s": rate,
@@ -190,13 +208,16 @@ def run(duration_s=10.0, rate=50.0, idle_ms=50.0, batch=64, image=224, arch="res
         "handover_ms_median": round(float(np.median(ho_ms)), 3), "handover_ms_max": round(float(np.max(ho_ms)), 3),
         "handover_gib_median": round(float(np.median(ho_gib)), 3),
         "handover_ms_per_gib": round(float(np.median(ho_ms / np.maximum(ho_gib, 1e-9))), 3),
+        "worker_phase_ms": {k: {"p50": pct(v, 0.5), "p99": pct(v, 0.99), "max": pct(v, 1.0)} for k, v in phase.items()},
         "trainer_adjust_ms": [[round(x, 2) for x in a[:3]] for a in ctrl.adjust_log][:8],
         "kill_seen_after_ms": [round((k - s0) * 1e3, 2) for k, s0 in zip(kill_seen, sent_at)][:8],
         "adjust_start_after_ms": [round((a[4] - s0) * 1e3, 2) for a, s0 in zip(ctrl.adjust_log, sent_at)][:8],
+        "setup_release_ms": round(setup_release_ms, 2),
         "pool_gib": round(pool.stat("pool_nbytes") / 2 ** 30, 2), "train_activation_gib": round(train_bytes / 2 ** 30, 2),
         "infer_activation_mib": round(infer_bytes / 2 ** 20, 1), "idle_ms": idle_ms,
+        "arrivals": f"Poisson {rate}/s in bursts of {burst_s} s separated by {gap_s} s of silence, MT19937 seed {seed}",
         "policy": "handover when a request finds no inference memory; pages return to training after idle_ms "
-                  "without requests (a handover per request at 50 req/s would keep training permanently killed)",
+                  "without requests (server/config.cc:75 defaults to 3000 ms, eval/ablation.py:162 uses 500)",
         "sm_mask": "TPC counters and mask are exchanged as in the reference; kernels do not restrict themselves yet",
         "final_loss_finite": bool(np.isfinite(losses[-1])) if losses else None,
     }
@@ -214,10 +235,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--duration", type=float, default=10.0)
     ap.add_argument("--rate", type=float, default=50.0)
-    ap.add_argument("--idle-ms", type=float, default=50.0)
+    ap.add_argument("--idle-ms", type=float, default=500.0)
+    ap.add_argument("--burst-s", type=float, default=1.0)
+    ap.add_argument("--gap-s", type=float, default=1.0)
     ap.add_argument("--batch", type=int, default=64)
     a = ap.parse_args()
-    print(json.dumps(run(a.duration, a.rate, a.idle_ms, a.batch)), flush=True)
+    print(json.dumps(run(a.duration, a.rate, a.idle_ms, a.burst_s, a.gap_s, a.batch)), flush=True)
 
 
 if __name__ == "__main__":

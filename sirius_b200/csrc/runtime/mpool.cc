@@ -16,6 +16,9 @@
 
 #include <algorithm>
 #include <map>
+#include <atomic>
+#include <chrono>
+#include <thread>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -34,8 +37,12 @@ struct Backend {
   virtual int unreserve(uint64_t base, size_t bytes) = 0;
   virtual int create_page(size_t bytes, uint64_t* handle) = 0;
   virtual int release_page(uint64_t handle) = 0;
+  // map() backs one page slot; the range becomes usable only after allow() over it. allow() and unmap()
+  // take any run of whole, consecutively mapped slots, so a handover costs one driver call per run
+  // rather than one per page.
   virtual int map(uint64_t va, size_t bytes, uint64_t handle) = 0;
-  virtual int unmap(uint64_t va, size_t bytes) = 0;
+  virtual int allow(uint64_t va, size_t bytes) = 0;
+  virtual int unmap(uint64_t va, size_t bytes, size_t page_bytes) = 0;
 };
 
 #define DRV(name) ((decltype(&name))drv(#name))
@@ -101,16 +108,25 @@ struct CudaVmmBackend : Backend {
   }
   int map(uint64_t va, size_t bytes, uint64_t handle) override {
     CU_CALL(f_map((CUdeviceptr)va, bytes, 0, (CUmemGenericAllocationHandle)handle, 0));
+    return SRT_OK;
+  }
+  int allow(uint64_t va, size_t bytes) override {
     CUmemAccessDesc acc{};
     acc.location = prop.location;
     acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
     CU_CALL(f_access((CUdeviceptr)va, bytes, &acc, 1));
     return SRT_OK;
   }
-  int unmap(uint64_t va, size_t bytes) override {
-    CU_CALL(f_unmap((CUdeviceptr)va, bytes));
+  int unmap(uint64_t va, size_t bytes, size_t page_bytes) override {
+    // one call over the whole run; a driver that wants one call per mapping gets that instead
+    if (!per_page_unmap && bytes > page_bytes) {
+      if (f_unmap((CUdeviceptr)va, bytes) == CUDA_SUCCESS) return SRT_OK;
+      per_page_unmap = true;
+    }
+    for (size_t o = 0; o < bytes; o += page_bytes) CU_CALL(f_unmap((CUdeviceptr)(va + o), page_bytes));
     return SRT_OK;
   }
+  bool per_page_unmap = false;
 };
 
 // Host stand-in: a "page" is just a token; mapping makes the address range accessible.
@@ -130,7 +146,8 @@ struct HostBackend : Backend {
     if (mprotect((void*)(uintptr_t)va, bytes, PROT_READ | PROT_WRITE) != 0) { set_error("host backend: mprotect failed"); return SRT_ERR_STATE; }
     return SRT_OK;
   }
-  int unmap(uint64_t va, size_t bytes) override {
+  int allow(uint64_t, size_t) override { return SRT_OK; }
+  int unmap(uint64_t va, size_t bytes, size_t) override {
     madvise((void*)(uintptr_t)va, bytes, MADV_DONTNEED);
     mprotect((void*)(uintptr_t)va, bytes, PROT_NONE);
     return SRT_OK;
@@ -150,7 +167,10 @@ struct Allocator {
   Belong who = kTrain;
   uint64_t base = 0;
   size_t slots = 0;
-  std::vector<int> slot_page;            // -1 = unmapped, else index into pool->pages
+  std::vector<int> slot_page;            // -1 = not backed, else index into pool->pages (page owned by this allocator)
+  std::vector<int> kept_page;            // -1, or the page a not-backed slot is still mapped to (mapping kept after
+                                         // the page went back to the pool; reused without a driver call if the page
+                                         // is free when the slot is needed again)
   std::map<uint64_t, uint64_t> free_;    // offset -> length, coalesced
   std::map<uint64_t, uint64_t> live_;    // offset -> length of allocated blocks
   size_t allocated = 0, peak = 0, mapped_pages = 0;
@@ -159,6 +179,9 @@ struct Allocator {
 
 struct Pool {
   std::mutex mu;
+  // Inference goes first: a training call waits (bounded) while an inference call is queued for the
+  // lock, so the few pages of a cold request are not mapped behind the trainer's whole regain.
+  std::atomic<int> infer_waiting{0};
   Backend* be = nullptr;
   int device = 0;
   size_t page_bytes = 0, n_pages = 0;
@@ -168,12 +191,13 @@ struct Pool {
   Allocator train, infer;
   srt_pool_oom_fn oom = nullptr;
   void* oom_user = nullptr;
-  long long n_map = 0, n_unmap = 0;
+  long long n_map = 0, n_unmap = 0, n_reuse = 0;
+  bool unmap_on_release = false;
   ~Pool() {
     for (Allocator* a : {&train, &infer}) {
       if (!a->base) continue;
       for (size_t s = 0; s < a->slots; ++s)
-        if (a->slot_page[s] >= 0) be->unmap(a->base + s * page_bytes, page_bytes);
+        if (a->slot_page[s] >= 0 || a->kept_page[s] >= 0) be->unmap(a->base + s * page_bytes, page_bytes, page_bytes);
       be->unreserve(a->base, a->slots * page_bytes);
     }
     for (uint64_t h : pages) be->release_page(h);
@@ -202,18 +226,46 @@ int take_free_page(Pool& p, Belong who, int* page) {
 
 int map_slots(Pool& p, Allocator& a, uint64_t off, uint64_t len) {
   const size_t s0 = off / p.page_bytes, s1 = (off + len - 1) / p.page_bytes;
+  size_t run0 = 0, run_n = 0;  // run of freshly mapped slots waiting for access rights
+  auto flush = [&]() -> int {
+    if (!run_n) return SRT_OK;
+    int rc = p.be->allow(a.base + run0 * p.page_bytes, run_n * p.page_bytes);
+    run_n = 0;
+    return rc;
+  };
   for (size_t s = s0; s <= s1; ++s) {
-    if (a.slot_page[s] >= 0) continue;
+    if (a.slot_page[s] >= 0) { int rc = flush(); if (rc) return rc; continue; }
+    const int kept = a.kept_page[s];
+    if (kept >= 0 && p.belong[kept] == kFree) {
+      // the slot is still mapped to a page that is free again: take it back without touching the driver
+      p.belong[kept] = a.who;
+      p.free_pages--;
+      a.slot_page[s] = kept;
+      a.kept_page[s] = -1;
+      a.mapped_pages++;
+      p.n_reuse++;
+      int rc = flush();
+      if (rc) return rc;
+      continue;
+    }
     int page;
     int rc = take_free_page(p, a.who, &page);
-    if (rc) return rc;
+    if (rc) { flush(); return rc; }
+    if (kept >= 0) {  // mapped to a page that now serves someone else: drop that mapping first
+      int r2 = p.be->unmap(a.base + s * p.page_bytes, p.page_bytes, p.page_bytes);
+      if (r2) { p.belong[page] = kFree; p.free_pages++; flush(); return r2; }
+      a.kept_page[s] = -1;
+      p.n_unmap++;
+    }
     rc = p.be->map(a.base + s * p.page_bytes, p.page_bytes, p.pages[page]);
-    if (rc) { p.belong[page] = kFree; p.free_pages++; return rc; }
+    if (rc) { p.belong[page] = kFree; p.free_pages++; flush(); return rc; }
     a.slot_page[s] = page;
     a.mapped_pages++;
     p.n_map++;
+    if (!run_n) run0 = s;
+    run_n++;
   }
-  return SRT_OK;
+  return flush();
 }
 
 // Pages needed to back [off, off+len) that are not mapped yet.
@@ -275,18 +327,26 @@ int empty_cache_locked(Pool& p, Allocator& a, size_t* released_pages) {
   size_t n = 0;
   for (auto& fr : a.free_) {
     const uint64_t b = fr.first, e = fr.first + fr.second;
-    size_t s0 = (b + p.page_bytes - 1) / p.page_bytes;
+    const size_t s0 = (b + p.page_bytes - 1) / p.page_bytes;
     const size_t s1 = e / p.page_bytes;  // exclusive
-    for (size_t s = s0; s < s1; ++s) {
-      if (a.slot_page[s] < 0) continue;
-      int rc = p.be->unmap(a.base + s * p.page_bytes, p.page_bytes);
-      if (rc) return rc;
-      p.belong[a.slot_page[s]] = kFree;
-      p.free_pages++;
-      a.slot_page[s] = -1;
-      a.mapped_pages--;
-      p.n_unmap++;
-      ++n;
+    size_t s = s0;
+    while (s < s1) {
+      if (a.slot_page[s] < 0) { ++s; continue; }
+      size_t t = s;
+      while (t < s1 && a.slot_page[t] >= 0) ++t;  // [s, t): a run of backed slots inside free space
+      if (p.unmap_on_release) {
+        int rc = p.be->unmap(a.base + s * p.page_bytes, (t - s) * p.page_bytes, p.page_bytes);
+        if (rc) return rc;
+      }
+      for (; s < t; ++s) {
+        p.belong[a.slot_page[s]] = kFree;
+        p.free_pages++;
+        if (p.unmap_on_release) p.n_unmap++;
+        else a.kept_page[s] = a.slot_page[s];
+        a.slot_page[s] = -1;
+        a.mapped_pages--;
+        ++n;
+      }
     }
   }
   if (released_pages) *released_pages = n;
@@ -294,6 +354,24 @@ int empty_cache_locked(Pool& p, Allocator& a, size_t* released_pages) {
 }
 
 Allocator* pick(Pool* p, int kind) { return kind == SRT_POOL_INFER ? &p->infer : &p->train; }
+
+// Takes the pool lock with the inference-first rule. The wait of a training caller is bounded (50 ms)
+// so a stuck inference thread cannot stall training for good.
+struct PoolLock {
+  std::unique_lock<std::mutex> lk;
+  PoolLock(Pool* p, int kind) : lk(p->mu, std::defer_lock) {
+    if (kind == SRT_POOL_INFER) {
+      p->infer_waiting.fetch_add(1, std::memory_order_acq_rel);
+      lk.lock();
+      p->infer_waiting.fetch_sub(1, std::memory_order_acq_rel);
+    } else {
+      const auto give_up = std::chrono::steady_clock::now() + std::chrono::milliseconds(50);
+      while (p->infer_waiting.load(std::memory_order_acquire) > 0 && std::chrono::steady_clock::now() < give_up)
+        std::this_thread::yield();
+      lk.lock();
+    }
+  }
+};
 
 }  // namespace
 }  // namespace srt
@@ -307,6 +385,7 @@ int srt_pool_create(const srt_pool_config* cfg, srt_pool** out) {
   SRT_REQUIRE(cfg->pool_nbytes > 0, "pool_create: pool_nbytes must be positive");
   Pool* p = new Pool();
   p->device = cfg->device;
+  p->unmap_on_release = cfg->unmap_on_release != 0;
   if (cfg->backend == SRT_POOL_BACKEND_HOST) {
     p->be = new HostBackend();
   } else {
@@ -345,6 +424,7 @@ int srt_pool_create(const srt_pool_config* cfg, srt_pool** out) {
     rc = p->be->reserve(d.a->slots * page, &d.a->base);
     if (rc) { delete p; return rc; }
     d.a->slot_page.assign(d.a->slots, -1);
+    d.a->kept_page.assign(d.a->slots, -1);
     d.a->free_[0] = d.a->slots * page;
   }
   *out = (srt_pool*)p;
@@ -359,7 +439,8 @@ int srt_pool_destroy(srt_pool* h) {
 int srt_pool_alloc(srt_pool* h, int kind, size_t nbytes, void** out) {
   Pool* p = (Pool*)h;
   SRT_REQUIRE(p && out && nbytes > 0, "pool_alloc: bad argument");
-  std::unique_lock<std::mutex> lk(p->mu);
+  PoolLock guard(p, kind);
+  std::unique_lock<std::mutex>& lk = guard.lk;
   uint64_t ptr = 0;
   int rc = alloc_locked(*p, *pick(p, kind), nbytes, &ptr);
   if (rc == SRT_ERR_NOMEM && p->oom) {
@@ -380,14 +461,14 @@ int srt_pool_free(srt_pool* h, int kind, void* ptr) {
   Pool* p = (Pool*)h;
   SRT_REQUIRE(p, "pool_free: null pool");
   if (!ptr) return SRT_OK;
-  std::lock_guard<std::mutex> lk(p->mu);
+  PoolLock guard(p, kind);
   return free_locked(*p, *pick(p, kind), (uint64_t)(uintptr_t)ptr);
 }
 
 int srt_pool_empty_cache(srt_pool* h, int kind, size_t* released_bytes) {
   Pool* p = (Pool*)h;
   SRT_REQUIRE(p, "pool_empty_cache: null pool");
-  std::lock_guard<std::mutex> lk(p->mu);
+  PoolLock guard(p, kind);
   size_t n = 0;
   int rc = empty_cache_locked(*p, *pick(p, kind), &n);
   if (released_bytes) *released_bytes = n * p->page_bytes;
@@ -409,6 +490,7 @@ int64_t srt_pool_stat(srt_pool* h, int which) {
     case SRT_POOL_STAT_NUM_MAP: return (int64_t)p->n_map;
     case SRT_POOL_STAT_NUM_UNMAP: return (int64_t)p->n_unmap;
     case SRT_POOL_STAT_INFER_ALLOCATED: return (int64_t)p->infer.allocated;
+    case SRT_POOL_STAT_NUM_REUSE: return (int64_t)p->n_reuse;
     default: return -1;
   }
 }

@@ -9,6 +9,7 @@
 #include <string.h>
 
 #include <string>
+#include <chrono>
 #include <vector>
 
 #include <atomic>
@@ -124,7 +125,9 @@ struct Step {
     return SRT_OK;
   }
   int alloc_activations(int B);
+  int free_activation_blocks();
   int release_activations(size_t* released_bytes);
+  int shrink_activations(int B, size_t* released_bytes);
   // Called between units: abort check + bounded launch-ahead.
   int checkpoint() {
     if (abort_flag.load(std::memory_order_acquire)) {
@@ -350,7 +353,9 @@ int Step::build() {
 int Step::alloc_activations(int B) {
   SRT_REQUIRE(B > 0 && B <= cfg.max_batch, "activations: batch %d outside 1..%d", B, cfg.max_batch);
   if (act_batch == B) return SRT_OK;
-  int rc = release_activations(nullptr);
+  // the old set goes back to the allocator but its pages stay mapped: the new set lands on them again
+  // and only the difference is mapped (growing) or left for the next empty-cache (shrinking)
+  int rc = free_activation_blocks();
   if (rc) return rc;
   const int dtype = cfg.dtype, IMG = cfg.image;
   size_t max_act = 0, max_bn_scratch = 0, max_wg_scratch = 0;
@@ -393,11 +398,9 @@ int Step::alloc_activations(int B) {
   return SRT_OK;
 }
 
-// Frees the activation set; with a pool attached, also returns every page that became empty.
-int Step::release_activations(size_t* released_bytes) {
-  if (released_bytes) *released_bytes = 0;
-  if (act_blocks.empty()) { act_batch = 0; return SRT_OK; }
-  if (stream) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
+// Waits for the stream and hands every activation block back to its allocator (pages stay mapped).
+int Step::free_activation_blocks() {
+  if (stream && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
   for (void* p : act_blocks) {
     if (pool) {
       int rc = srt_pool_free(pool, pool_kind, p);
@@ -407,13 +410,66 @@ int Step::release_activations(size_t* released_bytes) {
     }
   }
   act_blocks.clear();
-  size_t freed = act_bytes;
   act_bytes = 0;
   act_batch = 0;
-  if (pool) {
-    int rc = srt_pool_empty_cache(pool, pool_kind, &freed);
-    if (rc) return rc;
+  return SRT_OK;
+}
+
+namespace {
+struct PhaseTrace {  // SIRIUS_B200_TRACE=1 prints the phases of a release to stderr
+  const char* what;
+  bool on;
+  std::chrono::steady_clock::time_point t[4];
+  int n = 0;
+  explicit PhaseTrace(const char* w) : what(w) {
+    static const bool env = getenv("SIRIUS_B200_TRACE") != nullptr;
+    on = env;
+    mark();
   }
+  void mark() { if (on && n < 4) t[n++] = std::chrono::steady_clock::now(); }
+  void print(size_t freed) {
+    if (!on) return;
+    mark();
+    auto ms = [&](int i) { return i + 1 < n ? std::chrono::duration<double, std::milli>(t[i + 1] - t[i]).count() : 0.0; };
+    fprintf(stderr, "[sirius_b200] %s: free %.2f ms, regain %.2f ms, unmap %.2f ms, %zu MiB returned\n", what, ms(0), ms(1),
+            ms(2), freed >> 20);
+  }
+};
+}  // namespace
+
+// Frees the activation set; with a pool attached, also returns every page that became empty.
+int Step::release_activations(size_t* released_bytes) {
+  if (released_bytes) *released_bytes = 0;
+  if (act_blocks.empty()) { act_batch = 0; return SRT_OK; }
+  PhaseTrace tr("release_activations");
+  size_t freed = act_bytes;
+  int rc = free_activation_blocks();
+  if (rc) return rc;
+  tr.mark();
+  tr.mark();
+  if (pool && (rc = srt_pool_empty_cache(pool, pool_kind, &freed))) return rc;
+  tr.print(freed);
+  if (released_bytes) *released_bytes = freed;
+  return SRT_OK;
+}
+
+// Shrinks the activation set to micro-batches of B samples and returns the pages this frees. The smaller
+// set is placed before anything is unmapped, so it reuses pages that are already mapped and the only
+// driver work is unmapping the difference. B == 0 is release_activations.
+int Step::shrink_activations(int B, size_t* released_bytes) {
+  if (released_bytes) *released_bytes = 0;
+  if (B <= 0) return release_activations(released_bytes);
+  SRT_REQUIRE(B <= cfg.max_batch, "shrink_activations: batch %d above max_batch %d", B, cfg.max_batch);
+  PhaseTrace tr("shrink_activations");
+  const size_t before = act_bytes;
+  int rc = free_activation_blocks();
+  if (rc) return rc;
+  tr.mark();
+  if ((rc = alloc_activations(B))) return rc;
+  tr.mark();
+  size_t freed = before > act_bytes ? before - act_bytes : 0;
+  if (pool && (rc = srt_pool_empty_cache(pool, pool_kind, &freed))) return rc;
+  tr.print(freed);
   if (released_bytes) *released_bytes = freed;
   return SRT_OK;
 }
@@ -793,6 +849,12 @@ int srt_step_logits(srt_step* h, float* host, int B) {
     }
   }
   return SRT_OK;
+}
+
+int srt_step_shrink_activations(srt_step* h, int B, size_t* released_bytes) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "shrink_activations: null handle");
+  return s->shrink_activations(B, released_bytes);
 }
 
 int srt_step_release_activations(srt_step* h, size_t* released_bytes) {

@@ -9,15 +9,17 @@ from ._runtime import PoolConfig
 
 TRAIN, INFER = 0, 1
 STAT = {"infer_usage": 0, "train_usage": 1, "train_peak": 2, "train_all": 3, "free_pages": 4, "pool_nbytes": 5,
-        "page_nbytes": 6, "num_map": 7, "num_unmap": 8, "infer_allocated": 9}
+        "page_nbytes": 6, "num_map": 7, "num_unmap": 8, "infer_allocated": 9, "num_reuse": 10}
 
 
 class PagePool:
     """One pool of physical pages on a GPU with a training and an inference allocator
     (colserve::sta::CUDAMemPool, common/cuda_allocator.h:61-150)."""
 
-    def __init__(self, pool_gb: float, device: int = 0, page_mb: int = 32, host_backend: bool = False):
-        cfg = PoolConfig(device, 1 if host_backend else 0, page_mb << 20, int(pool_gb * (1 << 30)), 0, 0)
+    def __init__(self, pool_gb: float, device: int = 0, page_mb: int = 32, host_backend: bool = False,
+                 unmap_on_release: bool = False):
+        cfg = PoolConfig(device, 1 if host_backend else 0, page_mb << 20, int(pool_gb * (1 << 30)), 0, 0,
+                         int(unmap_on_release))
         self._h = C.c_void_p()
         call("srt_pool_create", C.byref(cfg), C.byref(self._h))
 

@@ -76,6 +76,7 @@ class ResNetStep:
         cfg.lr, cfg.momentum, cfg.weight_decay = lr, momentum, weight_decay
         cfg.bn_eps, cfg.bn_momentum = 1e-5, 0.1
         self.cfg = cfg
+        self.max_batch = max_batch
         self.dtype = "f32" if cfg.dtype == SRT_F32 else "bf16"
         self._h = _vp()
         self.pool = pool
@@ -186,6 +187,12 @@ class ResNetStep:
         """Frees the activation set and returns emptied pages to the pool; bytes handed back."""
         n = C.c_size_t()
         call("srt_step_release_activations", self._h, C.byref(n))
+        return n.value
+
+    def shrink_activations(self, B: int) -> int:
+        """Keeps an activation set for micro-batches of B samples and hands the other pages back; bytes returned."""
+        n = C.c_size_t()
+        call("srt_step_shrink_activations", self._h, int(B), C.byref(n))
         return n.value
 
     def reserve_activations(self, B: int) -> None:

@@ -225,9 +225,13 @@ def cuda_memory_pool_free_train_local(device_id=0):
     return 0
 
 
-def release_interm_memory():
+def release_interm_memory(keep_batch: int = 0):
     """CUDAColAllocator::ReleaseIntermMemory (torch_allocator_plugin.cc:343-369): drop every tagged
-    intermediate tensor. The step object owns its activations, so this releases its activation set."""
+    intermediate tensor. The step object owns its activations, so this releases its activation set.
+    With keep_batch > 0 the step keeps a set for that micro-batch size on pages that are already mapped
+    and returns only the rest, which is what release + the next iteration's allocations amount to."""
+    if _step is not None and keep_batch > 0 and hasattr(_step, 'shrink_activations'):
+        return _step.shrink_activations(min(int(keep_batch), getattr(_step, 'max_batch', int(keep_batch))))
     if _step is not None and hasattr(_step, 'release_activations'):
         return _step.release_activations()
     return 0

@@ -73,6 +73,9 @@ class ColocateCtrl(CtrlBase):
         super().__init__(train_mode, hook_mode, num_epoch, batch_size)
         self._stub = _C.PyColocateStub(batch_size, poll_ms=stub_poll_ms)
         _C._last_colocate_stub = self._stub
+        # keep an activation set for the announced batch size through an L1 adjust instead of dropping
+        # everything and mapping it again at the next iteration (COLTRAIN_KEEP_TARGET_SET=0 restores that)
+        self.keep_target_set = os.environ.get('COLTRAIN_KEEP_TARGET_SET', '1') != '0'
         self.adjust_log = []  # (release_ms, empty_cache_ms, reply_ms, released_bytes, start time.time())
 
     def check_kill(self, where: str):
@@ -119,7 +122,7 @@ class ColocateCtrl(CtrlBase):
         """Release the activation set, return empty pages to the pool, reply (colocate_ctrl.py:413-445)."""
         t0 = time.time()
         with EventManager.record_duration_event('adjust_l1'):
-            released = _C.release_interm_memory()
+            released = _C.release_interm_memory(self.unpub_target_batch_size if self.keep_target_set else 0)
             t1 = time.time()
             released = max(int(released or 0), int(MemoryPool.empty_cache() or 0))
             t2 = time.time()

@@ -64,6 +64,7 @@ def test_l1_adjust_kills_batch_releases_memory_and_training_reproduces_undisturb
     tag = f"{os.getpid()}_{uuid.uuid4().hex[:6]}"
     os.environ.update({"COLTRAIN_MODE": "colocate-l1", "COLTRAIN_HOOK_MODE": "xsched-sync2", "COLTRAIN_USE_XSCHED": "1",
                        "COLTRAIN_HAS_INFER_SERVER": "1", "COLTRAIN_USE_SHARED_TENSOR": "1",
+                       "COLTRAIN_KEEP_TARGET_SET": "0",   # the adjust names the same batch size: release everything
                        "SIRIUS_B200_COMM_NAME": f"srt_gpu_comm_{tag}", "SIRIUS_B200_DIST_NAME": f"srt_gpu_dist_{tag}"})
     model = O.build_model(ARCH, 0)
     DS, GBS, EPOCHS = 96, 32, 2
@@ -124,13 +125,50 @@ def test_l1_adjust_kills_batch_releases_memory_and_training_reproduces_undisturb
     noisy = run(True)
     assert quiet["killed"] == 0 and noisy["killed"] == 1
     assert [m.id for _, m in noisy["done"]] == [noisy["cid"]]
-    rel_ms, cache_ms, reply_ms, released = noisy["adjust"][0]
+    rel_ms, cache_ms, reply_ms, released = noisy["adjust"][0][:4]
     assert released > 0 and released % noisy["page"] == 0
     print(f"L1 adjust: release {rel_ms:.2f} ms, empty cache {cache_ms:.2f} ms, reply {reply_ms:.2f} ms, "
           f"{released / 2**20:.0f} MiB handed over = {(rel_ms + cache_ms + reply_ms) / (released / 2**30):.2f} ms/GiB")
     # the killed micro-batch was redone from the same samples: identical finished-batch losses and weights
     assert noisy["losses"] == quiet["losses"]
     assert np.array_equal(noisy["w"], quiet["w"])
+
+
+@pytest.mark.parametrize("unmap_on_release", [False, True])
+def test_shrink_keeps_a_smaller_set_on_mapped_pages_and_regrow_maps_only_the_difference(unmap_on_release):
+    model = O.build_model(ARCH, 0)
+    batches = O.make_batches(B, 1, IMG)
+    pool = PagePool(2.0, unmap_on_release=unmap_on_release)
+    page = pool.stat("page_nbytes")
+    step = ResNetStep(layers=O.LAYERS[ARCH], max_batch=B, image=IMG, dtype="bf16", pool=pool.handle)
+    step.load_state_dict(O.state_arrays(model))
+    im, lb = batches[0]
+    step.upload_batch(im, lb); step.forward_backward(B, B); loss_full = step.loss()
+    mapped_full, maps0, unmaps0 = pool.stat("train_all"), pool.stat("num_map"), pool.stat("num_unmap")
+    released = step.shrink_activations(B // 2)
+    assert released > 0 and released % page == 0
+    assert pool.stat("num_map") == maps0                       # nothing was mapped to place the smaller set
+    assert pool.stat("num_unmap") - unmaps0 == (released // page if unmap_on_release else 0)
+    assert pool.stat("train_all") == mapped_full - released and pool.stat("free_pages") * page >= released
+    # the inference allocator can use what was handed over while training runs the smaller batch
+    q = pool.alloc(INFER, released)
+    torch.cuda.synchronize()
+    step.upload_batch(im[:B // 2].contiguous(), lb[:B // 2].contiguous())
+    step.forward_backward(B // 2, B // 2)
+    assert np.isfinite(step.loss()) and pool.stat("num_map") == maps0 + released // page
+    pool.free(INFER, q)
+    pool.empty_cache(INFER)
+    # growing back takes exactly the pages that were returned, and the full batch reproduces its loss
+    reuse0 = pool.stat("num_reuse")
+    step.upload_batch(im, lb); step.forward_backward(B, B)
+    if unmap_on_release:
+        assert pool.stat("num_map") - maps0 == 2 * (released // page)
+    else:
+        assert pool.stat("num_map") - maps0 == released // page and pool.stat("num_reuse") - reuse0 == released // page
+    assert pool.stat("train_all") == mapped_full
+    assert step.loss() == loss_full
+    assert ops.tc_status() == 0
+    step.close(); pool.close()
 
 
 def test_inference_mode_forward_uses_running_statistics():

@@ -275,8 +275,8 @@ def test_train_adjuster_plans_match_reference_logic():
 
 
 # ---------------------------------------------------------------- page pool (host backend)
-def _pool(pool_mb=64, page_mb=2):
-    cfg = PoolConfig(0, 1, page_mb << 20, pool_mb << 20, 4, 1)
+def _pool(pool_mb=64, page_mb=2, unmap_on_release=0):
+    cfg = PoolConfig(0, 1, page_mb << 20, pool_mb << 20, 4, 1, unmap_on_release)
     h = C.c_void_p()
     call("srt_pool_create", C.byref(cfg), C.byref(h))
     return h
@@ -285,8 +285,9 @@ def _pool(pool_mb=64, page_mb=2):
 def _stat(h, which): return _lib.lib().srt_pool_stat(h, which)
 
 
-def test_pool_alloc_free_empty_cache_and_handover():
-    h = _pool()
+@pytest.mark.parametrize("unmap_on_release", [0, 1])
+def test_pool_alloc_free_empty_cache_and_handover(unmap_on_release):
+    h = _pool(unmap_on_release=unmap_on_release)
     try:
         assert _stat(h, 4) == 32 and _stat(h, 5) == 64 << 20 and _stat(h, 6) == 2 << 20
         ptrs = []
@@ -320,7 +321,53 @@ def test_pool_alloc_free_empty_cache_and_handover():
             call("srt_pool_free", h, 0, ptrs[i])
         call("srt_pool_empty_cache", h, 0, C.byref(rel))
         assert _stat(h, 4) == 32 and _stat(h, 1) == 0 and _stat(h, 3) == 0
-        assert _stat(h, 7) == _stat(h, 8) > 0                 # every map has its unmap
+        if unmap_on_release:
+            assert _stat(h, 7) == _stat(h, 8) > 0             # every map has its unmap
+        else:
+            assert _stat(h, 7) > 0 and _stat(h, 8) <= _stat(h, 7)   # mappings are kept until a slot needs another page
+    finally:
+        call("srt_pool_destroy", h)
+
+
+def test_pool_keeps_mappings_so_a_repeated_handover_makes_no_driver_calls():
+    """Training and inference trade the same pages back and forth: after the first exchange the slots
+    take their kept pages back (num_reuse grows) and neither num_map nor num_unmap moves."""
+    page = 2 << 20
+    h = _pool(pool_mb=32, page_mb=2)                          # 16 pages
+    try:
+        def alloc(kind, n):
+            p = C.c_void_p()
+            call("srt_pool_alloc", h, kind, n, C.byref(p))
+            C.memset(p.value, kind + 1, n)
+            return p
+        rel = C.c_size_t()
+        big = alloc(0, 16 * page)                             # training owns the whole pool
+        counts = []
+        for cycle in range(4):
+            # handover: training shrinks to 12 pages, inference takes the 4 it gave up
+            call("srt_pool_free", h, 0, big)
+            small = alloc(0, 12 * page)
+            call("srt_pool_empty_cache", h, 0, C.byref(rel))
+            assert rel.value == 4 * page and _stat(h, 4) == 4
+            inf = alloc(1, 4 * page)
+            assert _stat(h, 4) == 0
+            # give-back: inference leaves, training grows to the whole pool again
+            call("srt_pool_free", h, 1, inf)
+            call("srt_pool_empty_cache", h, 1, C.byref(rel))
+            assert rel.value == 4 * page
+            call("srt_pool_free", h, 0, small)
+            big = alloc(0, 16 * page)
+            assert _stat(h, 4) == 0
+            counts.append((_stat(h, 7), _stat(h, 8), _stat(h, 10)))
+        assert counts[0][:2] == (20, 0)                       # 16 training maps + 4 inference maps, nothing unmapped
+        assert all(c[:2] == counts[0][:2] for c in counts[1:])
+        assert [c[2] for c in counts] == [4, 12, 20, 28]      # later exchanges are served by kept mappings alone
+        # a slot whose kept page serves someone else gets another page: that costs one unmap and one map
+        call("srt_pool_free", h, 0, big)
+        call("srt_pool_empty_cache", h, 0, C.byref(rel))
+        inf = alloc(1, 4 * page)                              # inference slots 0..3 take their kept pages (12..15) back
+        low = alloc(0, 16 * page - 4 * page)                  # training slots 0..11 take theirs
+        assert (_stat(h, 7), _stat(h, 8)) == counts[0][:2]
     finally:
         call("srt_pool_destroy", h)
 

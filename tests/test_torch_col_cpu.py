@@ -3,7 +3,7 @@ small torch model (gloo all-reduce of the accumulated gradients), while this pro
 inference server with DebugServer and injects an L1 adjust (kill batch, release, reply), then an
 InferExit that gives the batch size back. Checks what the reference's design promises: every sample of
 every epoch is trained exactly once, replies carry the command id, and the batch size follows the
-adjust. The reference tests this only by hand with the same DebugServer."""
+adjust. The reference tests this only by hand with the same DebugServer (torch_col/debug_server.py)."""
 import multiprocessing as mp
 import os
 import time

@@ -220,25 +220,39 @@ def run_ours(args):
     status = ops.tc_status()
 
     # ---- memory handover: give the activation pages back to the pool, then regain them ----
-    handover = None
-    if rank == 0:
+    def time_handover(st, pl):
         rel_ms, regain_ms, nbytes = [], [], 0
         for _ in range(3):
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            nbytes = step.release_activations()      # sync + free blocks + unmap empty pages
+            nbytes = st.release_activations()      # sync + free blocks + pages marked FREE (unmapped in mpool mode)
             t1 = time.perf_counter()
-            step.reserve_activations(BATCH)          # map pages again for the same batch size
+            st.reserve_activations(BATCH)          # pages taken again for the same batch size
             t2 = time.perf_counter()
             rel_ms.append((t1 - t0) * 1e3)
             regain_ms.append((t2 - t1) * 1e3)
         torch.cuda.synchronize()
         gib = nbytes / 2 ** 30
-        handover = {"released_gib": round(gib, 3), "release_ms": round(min(rel_ms), 3),
-                    "release_ms_per_gib": round(min(rel_ms) / gib, 3), "regain_ms": round(min(regain_ms), 3),
-                    "page_mib": pool.stat("page_nbytes") >> 20,
-                    "what": "srt_step_release_activations: stream sync, free of the activation set, cuMemUnmap of "
-                            "every emptied page (pages become FREE for the inference allocator)"}
+        return {"released_gib": round(gib, 3), "release_ms": round(min(rel_ms), 3),
+                "release_ms_median": round(sorted(rel_ms)[1], 3),
+                "release_ms_per_gib": round(min(rel_ms) / gib, 4), "regain_ms": round(min(regain_ms), 3),
+                "page_mib": pl.stat("page_nbytes") >> 20}
+
+    handover = None
+    if rank == 0:
+        handover = time_handover(step, pool)
+        handover["what"] = ("srt_step_release_activations: stream sync, free of the activation set, every emptied page "
+                            "marked FREE for the inference allocator; the pool keeps the old mapping of a released page "
+                            "and reuses it, so no driver call is made")
+    step.close()
+    pool.close()
+    if rank == 0 and world == 1:
+        # the same handover the way the reference's mpool does it: cuMemUnmap at release, cuMemMap at regain
+        pool2 = PagePool(POOL_GB, device=local, unmap_on_release=True)
+        step2 = ResNetStep(arch=ARCH, num_classes=CLASSES, max_batch=BATCH, image=IMAGE, dtype="bf16", pool=pool2.handle)
+        handover["unmap_on_release"] = time_handover(step2, pool2)
+        step2.close()
+        pool2.close()
 
     peaks = load_peaks()
     fam = {}
@@ -277,6 +291,10 @@ def run_ours(args):
         "tc_status": status,
         "handover": handover,
     }
+    if rank == 0 and world == 1 and args.colocate_seconds > 0:
+        # training next to a stand-in inference worker on the same GPU: request latency, handover latency
+        from sirius_b200 import colocate_bench
+        out["colocated"] = colocate_bench.run(duration_s=args.colocate_seconds)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(sample_batch=16, steps=1, warmup=1)
     if rank == 0:
@@ -326,6 +344,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--colocate-seconds", type=float, default=8.0,
+                    help="length of the colocated training+inference window at N=1 (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -155,6 +155,18 @@ int srt_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
 /* mask[0..2]: bit i set = SM i is available to training kernels. */
 int srt_set_sm_mask(const uint64_t mask[3]);
 int srt_get_sm_mask(uint64_t mask[3]);
+/* Enforcement of the mask (SMPartitioner::SetStreamTpcMask, common/sm_partition.cu:316-336, pokes the
+ * TPC mask into a private field of the stream). Here: CUDA green contexts. The SM resource of the device
+ * is split once into a ladder of groups (whole device minus 16, 32, ... SMs; the driver rounds to its
+ * granularity), each with a green context and a stream; kernels launched on such a stream run on the SMs
+ * of its group only. srt_smp_partition_levels lists the SM counts of the ladder (widest first, starting
+ * with the whole device); srt_smp_partition_stream returns the stream of the widest group with at most
+ * allowed_sms SMs (NULL = whole device: use your own stream). SRT_ERR_UNSUPPORTED without green contexts.
+ * The mask's population count is what is enforced; which SMs a group holds is the driver's choice. */
+int srt_smp_partition_levels(int device, int* sms, int cap, int* n);
+int srt_smp_partition_stream(int device, int allowed_sms, void** stream, int* sms);
+/* Test aid: ORs the %smid of every block of a probe grid launched on `stream` into three device words. */
+int srt_debug_smid_probe(void* device_mask3, void* stream);
 
 /* ---- tcgen05 kernel status ------------------------------------------------------------------
  * Every wait inside the tensor-core kernels is bounded; a wait that gives up records a non-zero
@@ -212,6 +224,13 @@ int srt_step_shrink_activations(srt_step* s, int B, size_t* released_bytes);
  * backward test it between units and return SRT_ERR_ABORTED, and never run more than 8 units ahead of
  * the GPU, so the stream drains within a bounded time. Clear the flag before the next micro-batch. */
 int srt_step_request_abort(srt_step* s, int on);
+/* The pre-launch hook of the reference (pytorch/torch_col/csrc/init.cc:43-71) sets the TPC mask before
+ * every kernel. With on != 0 the step does the equivalent between units: it reads the process-wide mask
+ * (srt_set_sm_mask), and continues on the partition stream of the widest group that fits the mask's SM
+ * count, ordered after its earlier work by an event; grids are sized for that width. srt_step_stream()
+ * then returns the stream in use at the time of the call. Off by default. */
+int srt_step_follow_sm_mask(srt_step* s, int on);
+int srt_step_current_sms(srt_step* s, int* sms);
 int srt_step_destroy(srt_step* s);
 /* Parameter registry under torchvision state_dict names ("layer1.0.conv1.weight", ...). Shapes and
  * host data use the torch layout ([K,C,R,S] for convolutions); the device keeps [K,R,S,C]. */

@@ -112,4 +112,9 @@ register({
     "srt_step_shrink_activations": (None, [_vp, C.c_int, C.POINTER(_sz)]),
     "srt_step_reserve_activations": (None, [_vp, _i]),
     "srt_step_request_abort": (None, [_vp, _i]),
+    "srt_step_follow_sm_mask": (None, [_vp, _i]),
+    "srt_step_current_sms": (None, [_vp, C.POINTER(_i)]),
+    "srt_smp_partition_levels": (None, [_i, C.POINTER(_i), _i, C.POINTER(_i)]),
+    "srt_smp_partition_stream": (None, [_i, _i, C.POINTER(_vp), C.POINTER(_i)]),
+    "srt_debug_smid_probe": (None, [_vp, _vp]),
 })

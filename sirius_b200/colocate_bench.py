@@ -29,7 +29,7 @@ import uuid
 import numpy as np
 
 
-def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch=64, image=224, arch="resnet152", seed=0, verbose=False):
+def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch=64, image=224, arch="resnet152", seed=0, per_arrival=False):
     import torch
     from . import torch_col as tc
     from ._lib import SrtError, call
@@ -73,11 +73,13 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
     step.load_state_dict(sd)
     if pool.stat("free_pages") >= infer_pages:
         raise RuntimeError("pool sizing: inference fits beside training without a handover")
-    # one release/regain cycle during set-up: the first unmap after the large frees above (probe step and
-    # probe pool) has been seen to take 0.1-2.4 s in the driver, later ones 17 ms
-    t0 = time.perf_counter()
-    step.release_activations()
-    setup_release_ms = (time.perf_counter() - t0) * 1e3
+    # warm-up exchange, as a deployment would do before taking traffic: training shrinks by the plan's
+    # batch delta, inference maps the pages it gives up, then both return to their starting state. From
+    # here on both sides find their slots still mapped to the pages they trade (no driver call).
+    delta = -(-((infer_pages + 1) * page) // (train_pages * page // batch))
+    step.shrink_activations(max(batch - delta, 1))
+    infer.reserve_activations(1)
+    infer.release_activations()
     step.reserve_activations(batch)
     tc.set_train_step(step)
     tc.set_memory_pool(pool.handle)
@@ -107,7 +109,7 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
         while t_start[0] is None and not stop.is_set():
             time.sleep(0.001)
         t_next = t_start[0] + 1.0             # let the first training steps pass
-        have_mem, last_done = False, 0.0
+        have_mem, last_done, target = False, 0.0, batch
         while not stop.is_set():
             now = time.perf_counter()
             if have_mem and now - last_done > idle_ms / 1e3 and t_next - now > 0:
@@ -128,20 +130,23 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
             t_next += rng.exponential(1.0 / rate)
             if burst_s > 0 and (t_next - t_start[0] - 1.0) % (burst_s + gap_s) > burst_s:   # off period: next burst
                 t_next = t_start[0] + 1.0 + ((t_next - t_start[0] - 1.0) // (burst_s + gap_s) + 1) * (burst_s + gap_s)
-            if not have_mem:
-                plan, n = (C.c_int * 8)(), C.c_int()
-                need_mb = (infer_pages + 1) * page / 2 ** 20
-                call("srt_adjuster_infer_require_plan", adj, 0, need_mb, None, plan, C.byref(n))
+            if not have_mem or per_arrival:
+                if not have_mem:
+                    plan, n = (C.c_int * 8)(), C.c_int()
+                    need_mb = (infer_pages + 1) * page / 2 ** 20
+                    call("srt_adjuster_infer_require_plan", adj, 0, need_mb, None, plan, C.byref(n))
+                    target = max(plan[0], 1) if n.value else batch
                 t0 = time.perf_counter()
                 sent_at.append(time.time())
-                cid = srv.colocate_l1([max(plan[0], 1)] if n.value else [batch])
+                cid = srv.colocate_l1([target])       # warm request in per-arrival mode: same target again
                 srv.wait_adjust_done(cid, 30)
                 dt = time.perf_counter() - t0
                 handover.append(dt * 1e3)
-                t1 = time.perf_counter()
-                infer.reserve_activations(1)
-                phase["reserve"].append((time.perf_counter() - t1) * 1e3)
-                have_mem = True
+                if not have_mem:
+                    t1 = time.perf_counter()
+                    infer.reserve_activations(1)
+                    phase["reserve"].append((time.perf_counter() - t1) * 1e3)
+                    have_mem = True
             t2 = time.perf_counter()
             srv.comm.infer_tpc(0, 1, infer_tpc)            # AddInferRequiredTpcNum
             infer.upload_batch(img, lab)
@@ -207,15 +212,16 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
         "handovers": len(handover), "killed_micro_batches": stat.killed_batch,
         "handover_ms_median": round(float(np.median(ho_ms)), 3), "handover_ms_max": round(float(np.max(ho_ms)), 3),
         "handover_gib_median": round(float(np.median(ho_gib)), 3),
-        "handover_ms_per_gib": round(float(np.median(ho_ms / np.maximum(ho_gib, 1e-9))), 3),
+        "handover_ms_per_gib": (round(float(np.median(ho_ms[ho_gib > 0] / ho_gib[ho_gib > 0])), 3)
+                                if np.any(ho_gib > 0) else None),
         "worker_phase_ms": {k: {"p50": pct(v, 0.5), "p99": pct(v, 0.99), "max": pct(v, 1.0)} for k, v in phase.items()},
         "trainer_adjust_ms": [[round(x, 2) for x in a[:3]] for a in ctrl.adjust_log][:8],
         "kill_seen_after_ms": [round((k - s0) * 1e3, 2) for k, s0 in zip(kill_seen, sent_at)][:8],
         "adjust_start_after_ms": [round((a[4] - s0) * 1e3, 2) for a, s0 in zip(ctrl.adjust_log, sent_at)][:8],
-        "setup_release_ms": round(setup_release_ms, 2),
         "pool_gib": round(pool.stat("pool_nbytes") / 2 ** 30, 2), "train_activation_gib": round(train_bytes / 2 ** 30, 2),
         "infer_activation_mib": round(infer_bytes / 2 ** 20, 1), "idle_ms": idle_ms,
         "arrivals": f"Poisson {rate}/s in bursts of {burst_s} s separated by {gap_s} s of silence, MT19937 seed {seed}",
+        "adjust": "one L1 adjust per arrival" if per_arrival else "one L1 adjust per cold request",
         "policy": "handover when a request finds no inference memory; pages return to training after idle_ms "
                   "without requests (server/config.cc:75 defaults to 3000 ms, eval/ablation.py:162 uses 500)",
         "sm_mask": "TPC counters and mask are exchanged as in the reference; kernels do not restrict themselves yet",
@@ -239,8 +245,9 @@ def main():
     ap.add_argument("--burst-s", type=float, default=1.0)
     ap.add_argument("--gap-s", type=float, default=1.0)
     ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--per-arrival", action="store_true", help="send an L1 adjust for every request, not only cold ones")
     a = ap.parse_args()
-    print(json.dumps(run(a.duration, a.rate, a.idle_ms, a.burst_s, a.gap_s, a.batch)), flush=True)
+    print(json.dumps(run(a.duration, a.rate, a.idle_ms, a.burst_s, a.gap_s, a.batch, per_arrival=a.per_arrival)), flush=True)
 
 
 if __name__ == "__main__":

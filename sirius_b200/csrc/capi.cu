@@ -32,7 +32,8 @@ int sm_count() {
       n = 148;
     cached[dev] = n;
   }
-  return cached[dev];
+  const int lim = sm_limit();
+  return lim > 0 && lim < cached[dev] ? lim : cached[dev];
 }
 
 static std::mutex g_mask_mu;

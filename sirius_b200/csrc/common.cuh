@@ -47,7 +47,11 @@ void count_launch();  // bumps the process-wide launch counter
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 
-int sm_count();  // SM count of the current device (cached)
+int sm_count();  // SM count kernels should size their grids for: the device's, or the calling thread's limit
+int sm_limit();                  // 0 = none
+void set_sm_limit(int n);        // per thread: a step that runs inside an SM partition sets its width
+// Stream of the widest green-context partition with at most `allowed` SMs (nullptr = whole device).
+int partition_stream(int device, int allowed, cudaStream_t* stream, int* sms);
 
 // ---- element type traits ---------------------------------------------------------------
 template <typename T> struct ElemTraits;

@@ -128,11 +128,55 @@ struct Step {
   int free_activation_blocks();
   int release_activations(size_t* released_bytes);
   int shrink_activations(int B, size_t* released_bytes);
+  // SM partition: when on, the step moves between green-context streams so that its kernels only run
+  // on as many SMs as the process-wide allowed-SM mask has bits (see sm_partition.cu).
+  bool follow_mask = false;
+  cudaStream_t home_stream = nullptr;  // the stream the step was created with (whole device)
+  int cur_sms = 0;                     // 0 = whole device
+  cudaEvent_t switch_ev = nullptr;
+  int follow_sm_mask() {
+    const SmMask m = current_sm_mask();
+    const int total = sm_count_device();
+    int allowed = 0;
+    for (int i = 0; i < total; ++i) allowed += (int)((m.w[i >> 6] >> (i & 63)) & 1ull);
+    cudaStream_t want = nullptr;
+    int sms = total;
+    int rc = partition_stream(cfg_device, allowed, &want, &sms);
+    if (rc) return rc;
+    if (!want) { want = home_stream; sms = 0; }
+    if (want == stream) return SRT_OK;
+    if (!switch_ev) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&switch_ev, cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventRecord(switch_ev, stream));   // the new stream continues after everything queued so far
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(want, switch_ev, 0));
+    stream = want;
+    cur_sms = sms;
+    return SRT_OK;
+  }
+  int cfg_device = 0;
+  static int sm_count_device() {
+    const int lim = sm_limit();
+    set_sm_limit(0);
+    const int n = sm_count();
+    set_sm_limit(lim);
+    return n;
+  }
+  // Grid sizing of the calling thread follows the partition while the step's entry points run.
+  struct SmScope {
+    int saved;
+    explicit SmScope(const Step* s) : saved(sm_limit()) { if (s->follow_mask) set_sm_limit(s->cur_sms); }
+    ~SmScope() { set_sm_limit(saved); }
+  };
+
   // Called between units: abort check + bounded launch-ahead.
   int checkpoint() {
     if (abort_flag.load(std::memory_order_acquire)) {
       set_error("step aborted between units (kill batch)");
       return SRT_ERR_ABORTED;
+    }
+    if (follow_mask) {
+      int rc = follow_sm_mask();
+      if (rc) return rc;
+      set_sm_limit(cur_sms);
     }
     const int slot = (int)(unit_seq % kLaunchAhead);
     if (!ahead_ev[slot]) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ahead_ev[slot], cudaEventDisableTiming));
@@ -183,7 +227,8 @@ struct Step {
     for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
     release_activations(nullptr);
     for (void* p : allocs) cudaFree(p);
-    if (own_stream && stream) cudaStreamDestroy(stream);
+    if (switch_ev) cudaEventDestroy(switch_ev);
+    if (own_stream && home_stream) cudaStreamDestroy(home_stream);  // partition streams belong to the ladder
   }
   int dalloc(void** out, size_t bytes, bool zero) {
     bytes = align_up(bytes ? bytes : 256, 256);
@@ -332,6 +377,8 @@ int Step::build() {
     SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   }
   own_stream = true;
+  home_stream = stream;
+  SRT_CHECK_CUDA(cudaGetDevice(&cfg_device));
   if ((rc = alloc_activations(B))) return rc;
 
   // BN defaults (weight 1, bias 0, running_var 1); conv/fc weights are set by the caller.
@@ -751,6 +798,7 @@ int srt_step_set_batch_device(srt_step* h, const float* dev_images, const int64_
 int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch && global_batch >= B, "forward_backward: bad batch sizes");
+  Step::SmScope sm_scope(s);
   int rc;
   if (s->act_batch < B && (rc = s->alloc_activations(B))) return rc;  // regain after a release
   rc = s->forward(B);
@@ -766,6 +814,7 @@ int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
 int srt_step_forward_only(srt_step* h, int B) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_only: bad batch size");
+  Step::SmScope sm_scope(s);
   if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
   return s->forward(B);
 }
@@ -773,6 +822,7 @@ int srt_step_forward_only(srt_step* h, int B) {
 int srt_step_forward_infer(srt_step* h, int B) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_infer: bad batch size");
+  Step::SmScope sm_scope(s);
   if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
   s->eval_mode = true;
   const int rc = s->forward(B);
@@ -783,6 +833,7 @@ int srt_step_forward_infer(srt_step* h, int B) {
 int srt_step_accumulate(srt_step* h) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s, "accumulate: null handle");
+  Step::SmScope sm_scope(s);
   s->accum_pending++;
   return grad_accumulate(s->ACC, s->G, (int64_t)s->n_flat, s->stream);
 }
@@ -790,6 +841,7 @@ int srt_step_accumulate(srt_step* h) {
 int srt_step_optimizer(srt_step* h) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s, "optimizer: null handle");
+  Step::SmScope sm_scope(s);
   const float* grad = s->accum_pending > 0 ? s->ACC : s->G;
   const bool bf = s->cfg.dtype == SRT_BF16;
   int rc = s->timed(SRT_PROF_OPTIM, (double)s->n_flat * (bf ? 22 : 20), [&] {
@@ -823,6 +875,35 @@ int srt_step_loss(srt_step* h, float* host_loss) {
   SRT_REQUIRE(s && host_loss, "loss: null argument");
   SRT_CHECK_CUDA(cudaMemcpyAsync(host_loss, s->loss_acc, 4, cudaMemcpyDeviceToHost, s->stream));
   SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  return SRT_OK;
+}
+
+int srt_step_follow_sm_mask(srt_step* h, int on) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "follow_sm_mask: null handle");
+  if (on) {
+    cudaStream_t st;
+    int sms;
+    int rc = partition_stream(s->cfg_device, 1 << 30, &st, &sms);  // builds the ladder; fails where green contexts are missing
+    if (rc) return rc;
+    s->follow_mask = true;
+    return SRT_OK;
+  }
+  s->follow_mask = false;
+  if (s->stream != s->home_stream) {
+    if (!s->switch_ev) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&s->switch_ev, cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventRecord(s->switch_ev, s->stream));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(s->home_stream, s->switch_ev, 0));
+    s->stream = s->home_stream;
+    s->cur_sms = 0;
+  }
+  return SRT_OK;
+}
+
+int srt_step_current_sms(srt_step* h, int* sms) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && sms, "current_sms: null argument");
+  *sms = s->cur_sms > 0 ? s->cur_sms : Step::sm_count_device();
   return SRT_OK;
 }
 

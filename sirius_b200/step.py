@@ -198,6 +198,15 @@ class ResNetStep:
     def reserve_activations(self, B: int) -> None:
         call("srt_step_reserve_activations", self._h, B)
 
+    def follow_sm_mask(self, on: bool = True) -> None:
+        """Run on the green-context partition that fits the process-wide allowed-SM mask (checked between units)."""
+        call("srt_step_follow_sm_mask", self._h, int(on))
+
+    def current_sms(self) -> int:
+        n = C.c_int()
+        call("srt_step_current_sms", self._h, C.byref(n))
+        return n.value
+
     def request_abort(self, on: bool = True) -> None:
         call("srt_step_request_abort", self._h, int(on))
 

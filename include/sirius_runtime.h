@@ -85,6 +85,13 @@ int srt_smp_train_avail_tpc_num(int infer_required_tpc, int gpu_tpc_num, int min
 int srt_smp_allowed_sm_mask(int infer_required_tpc, int gpu_sm_num, int min_train_tpc, int max_train_tpc,
                             uint64_t allowed_sm[3]);
 
+/* The pre-launch hook (pytorch/torch_col/csrc/init.cc:56-62): between units the step reads
+ * infer_required_tpc_num of `device` from the board, keeps srt_smp_train_avail_tpc_num() TPCs and moves to
+ * the green-context partition that fits (sirius_b200.h: srt_step_follow_sm_mask). comm == NULL turns it off.
+ * The comm handle must outlive the step or be detached first. */
+struct srt_step;
+int srt_step_follow_infer_tpc(struct srt_step* s, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc);
+
 /* ---- DistTrainSync, DynamicBatchDistirbutor, PerfModel ----------------------------------------
  * (pytorch/torch_col/csrc/dist_train_sync.{h,cc}, dynamic_batch.{h,cc}, perf_model.{h,cc}) */
 typedef struct srt_dist srt_dist;

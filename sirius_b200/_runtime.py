@@ -114,6 +114,7 @@ register({
     "srt_step_request_abort": (None, [_vp, _i]),
     "srt_step_follow_sm_mask": (None, [_vp, _i]),
     "srt_step_current_sms": (None, [_vp, C.POINTER(_i)]),
+    "srt_step_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i]),
     "srt_smp_partition_levels": (None, [_i, C.POINTER(_i), _i, C.POINTER(_i)]),
     "srt_smp_partition_stream": (None, [_i, _i, C.POINTER(_vp), C.POINTER(_i)]),
     "srt_debug_smid_probe": (None, [_vp, _vp]),

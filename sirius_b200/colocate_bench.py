@@ -29,7 +29,7 @@ import uuid
 import numpy as np
 
 
-def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch=64, image=224, arch="resnet152", seed=0, per_arrival=False):
+def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch=64, image=224, arch="resnet152", seed=0, per_arrival=False, sm_partition=True):
     import torch
     from . import torch_col as tc
     from ._lib import SrtError, call
@@ -158,13 +158,15 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
             lat_ms.append((last_done - t_arr) * 1e3)
 
     losses, finished = [], [0]
-    allowed = (C.c_uint64 * 3)()
+
+    # SM partition: between units the training step reads the inference side's required-TPC counter and
+    # moves to the green-context partition that leaves those TPCs alone (the reference's pre-launch hook)
+    if sm_partition:
+        step.follow_infer_tpc(srv.comm._h, 0, 5, gpu_tpc)
+    sms_seen = set()
 
     def iter_train_fn(b):
-        # SM partition: what the reference's launch pre-hook does per kernel, here once per micro-batch
-        req = srv.comm.infer_tpc(0, 3)
-        call("srt_smp_allowed_sm_mask", req, gpu_tpc * 2, 5, gpu_tpc, allowed)
-        call("srt_set_sm_mask", allowed)
+        sms_seen.add(step.current_sms())
         step.upload_batch(b["images"], b["labels"])
         try:
             step.forward_backward(len(b), batch)
@@ -224,10 +226,14 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
         "adjust": "one L1 adjust per arrival" if per_arrival else "one L1 adjust per cold request",
         "policy": "handover when a request finds no inference memory; pages return to training after idle_ms "
                   "without requests (server/config.cc:75 defaults to 3000 ms, eval/ablation.py:162 uses 500)",
-        "sm_mask": "TPC counters and mask are exchanged as in the reference; kernels do not restrict themselves yet",
+        "sm_partition": ({"infer_required_tpc": infer_tpc, "of_tpc": gpu_tpc, "train_sms_seen": sorted(sms_seen),
+                          "how": "green-context partition streams, switched between conv+BN units"}
+                         if sm_partition else "off"),
         "final_loss_finite": bool(np.isfinite(losses[-1])) if losses else None,
     }
     call("srt_adjuster_destroy", adj)
+    if sm_partition:
+        step.follow_infer_tpc(None)
     step.close()
     infer.close()
     tc.cleanup_colocate_training(False)
@@ -245,9 +251,10 @@ def main():
     ap.add_argument("--burst-s", type=float, default=1.0)
     ap.add_argument("--gap-s", type=float, default=1.0)
     ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--no-sm-partition", action="store_true")
     ap.add_argument("--per-arrival", action="store_true", help="send an L1 adjust for every request, not only cold ones")
     a = ap.parse_args()
-    print(json.dumps(run(a.duration, a.rate, a.idle_ms, a.burst_s, a.gap_s, a.batch, per_arrival=a.per_arrival)), flush=True)
+    print(json.dumps(run(a.duration, a.rate, a.idle_ms, a.burst_s, a.gap_s, a.batch, per_arrival=a.per_arrival, sm_partition=not a.no_sm_partition)), flush=True)
 
 
 if __name__ == "__main__":

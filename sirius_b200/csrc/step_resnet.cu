@@ -15,6 +15,7 @@
 #include <atomic>
 
 #include "../../include/sirius_pool.h"
+#include "../../include/sirius_runtime.h"
 #include "common.cuh"
 #include "ops.cuh"
 
@@ -134,11 +135,22 @@ struct Step {
   cudaStream_t home_stream = nullptr;  // the stream the step was created with (whole device)
   int cur_sms = 0;                     // 0 = whole device
   cudaEvent_t switch_ev = nullptr;
+  // Source of the allowed SM count: the inference side's required-TPC counter on the information
+  // board when one is attached (what the reference's pre-launch hook reads), else the process-wide mask.
+  srt_comm* tpc_comm = nullptr;
+  int tpc_device = 0, tpc_min_train = 1, tpc_max_train = 1 << 20;
   int follow_sm_mask() {
-    const SmMask m = current_sm_mask();
     const int total = sm_count_device();
     int allowed = 0;
-    for (int i = 0; i < total; ++i) allowed += (int)((m.w[i >> 6] >> (i & 63)) & 1ull);
+    if (tpc_comm) {
+      int req = 0;
+      int rc = srt_comm_infer_tpc(tpc_comm, tpc_device, 3, 0, &req);
+      if (rc) return rc;
+      allowed = 2 * srt_smp_train_avail_tpc_num(req, total / 2, tpc_min_train, tpc_max_train);
+    } else {
+      const SmMask m = current_sm_mask();
+      for (int i = 0; i < total; ++i) allowed += (int)((m.w[i >> 6] >> (i & 63)) & 1ull);
+    }
     cudaStream_t want = nullptr;
     int sms = total;
     int rc = partition_stream(cfg_device, allowed, &want, &sms);
@@ -898,6 +910,17 @@ int srt_step_follow_sm_mask(srt_step* h, int on) {
     s->cur_sms = 0;
   }
   return SRT_OK;
+}
+
+int srt_step_follow_infer_tpc(srt_step* h, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "follow_infer_tpc: null handle");
+  if (!comm) { s->tpc_comm = nullptr; return srt_step_follow_sm_mask(h, 0); }
+  s->tpc_comm = comm;
+  s->tpc_device = device;
+  s->tpc_min_train = min_train_tpc > 0 ? min_train_tpc : 1;
+  s->tpc_max_train = max_train_tpc > 0 ? max_train_tpc : 1 << 20;
+  return srt_step_follow_sm_mask(h, 1);
 }
 
 int srt_step_current_sms(srt_step* h, int* sms) {

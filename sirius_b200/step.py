@@ -202,6 +202,10 @@ class ResNetStep:
         """Run on the green-context partition that fits the process-wide allowed-SM mask (checked between units)."""
         call("srt_step_follow_sm_mask", self._h, int(on))
 
+    def follow_infer_tpc(self, comm_handle, device: int = 0, min_train_tpc: int = 5, max_train_tpc: int = 0) -> None:
+        """Follow the inference side's required-TPC counter on the information board (None detaches)."""
+        call("srt_step_follow_infer_tpc", self._h, comm_handle, device, min_train_tpc, max_train_tpc)
+
     def current_sms(self) -> int:
         n = C.c_int()
         call("srt_step_current_sms", self._h, C.byref(n))

@@ -230,6 +230,10 @@ int srt_step_request_abort(srt_step* s, int on);
  * count, ordered after its earlier work by an event; grids are sized for that width. srt_step_stream()
  * then returns the stream in use at the time of the call. Off by default. */
 int srt_step_follow_sm_mask(srt_step* s, int on);
+/* Backward runs the filter-gradient kernels on a second stream beside the data-gradient and BatchNorm
+ * kernels of the following units (on by default; the result is bit-identical either way). Off while the
+ * step follows an SM partition or is being profiled per kernel family. */
+int srt_step_overlap_wgrad(srt_step* s, int on);
 int srt_step_current_sms(srt_step* s, int* sms);
 int srt_step_destroy(srt_step* s);
 /* Parameter registry under torchvision state_dict names ("layer1.0.conv1.weight", ...). Shapes and

@@ -113,6 +113,7 @@ register({
     "srt_step_reserve_activations": (None, [_vp, _i]),
     "srt_step_request_abort": (None, [_vp, _i]),
     "srt_step_follow_sm_mask": (None, [_vp, _i]),
+    "srt_step_overlap_wgrad": (None, [_vp, _i]),
     "srt_step_current_sms": (None, [_vp, C.POINTER(_i)]),
     "srt_step_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i]),
     "srt_smp_partition_levels": (None, [_i, C.POINTER(_i), _i, C.POINTER(_i)]),

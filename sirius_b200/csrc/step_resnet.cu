@@ -86,9 +86,41 @@ struct Step {
   // activations
   void *x0 = nullptr, *pool_y = nullptr, *avg = nullptr, *logits = nullptr, *dlogits = nullptr;
   uint8_t* pool_arg = nullptr;
-  void* T[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* T[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  void* scratch_wg = nullptr;  // split partials of the filter-gradient kernels (they run beside BatchNorm)
+  size_t scratch_wg_bytes = 0;
+  // Backward overlap: the filter gradient of a unit depends only on (dz, saved input), not on anything
+  // later in the chain, so it runs on a second, lowest-priority stream beside the data gradient and the
+  // next BatchNorm backward and fills the SMs those leave idle. dz buffers alternate so that the next
+  // unit does not have to wait for the reader; a write to a buffer waits for its pending reader.
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaEvent_t ev_read[6] = {nullptr};
+  bool read_pending[6] = {false};  // indexed by position in T; only T[1], T[3], T[5] are ever read by the side
+                                   // stream, and those never take part in the T[0]/T[4] swap
+  bool side_dirty = false;         // side-stream work queued that the main stream has not waited for
+  bool wt_dirty = false;           // ... of which only filter transposes (the forward pass need not wait for those)
+  bool overlap_wgrad = true;
+  bool use_side() const { return side && overlap_wgrad && !follow_mask && !prof_on; }
+  int t_slot(const void* p) const { for (int i = 0; i < 6; ++i) if (T[i] == p) return i; return -1; }
+  int before_write(const void* buf) {   // main stream is about to overwrite buf
+    const int i = t_slot(buf);
+    if (i >= 0 && read_pending[i]) {
+      SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_read[i], 0));
+      read_pending[i] = false;
+    }
+    return SRT_OK;
+  }
+  int join_side() {                      // main stream continues after everything queued on the side stream
+    if (!side || !(side_dirty || wt_dirty)) return SRT_OK;
+    side_dirty = wt_dirty = false;
+    SRT_CHECK_CUDA(cudaEventRecord(ev_join, side));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
+    for (bool& b : read_pending) b = false;
+    return SRT_OK;
+  }
   float *row_loss = nullptr, *loss_acc = nullptr;
   float* stage_images = nullptr;   // device staging of the NCHW fp32 batch
   int64_t* stage_labels = nullptr;
@@ -240,6 +272,10 @@ struct Step {
     release_activations(nullptr);
     for (void* p : allocs) cudaFree(p);
     if (switch_ev) cudaEventDestroy(switch_ev);
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+    for (auto e : ev_read) if (e) cudaEventDestroy(e);
+    if (side) cudaStreamDestroy(side);
     if (own_stream && home_stream) cudaStreamDestroy(home_stream);  // partition streams belong to the ladder
   }
   int dalloc(void** out, size_t bytes, bool zero) {
@@ -390,6 +426,14 @@ int Step::build() {
   }
   own_stream = true;
   home_stream = stream;
+  if (pool_kind != SRT_POOL_INFER) {
+    int lo = 0, hi = 0;
+    SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    SRT_CHECK_CUDA(cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, lo));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+    for (auto& e : ev_read) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
   SRT_CHECK_CUDA(cudaGetDevice(&cfg_device));
   if ((rc = alloc_activations(B))) return rc;
 
@@ -449,10 +493,12 @@ int Step::alloc_activations(int B) {
   const size_t pool_elems = (size_t)B * (IMG / 4) * (IMG / 4) * 64;
   if ((rc = aalloc(&pool_y, pool_elems * esz))) return rc;
   if ((rc = aalloc((void**)&pool_arg, pool_elems))) return rc;
-  for (int i = 0; i < 5; ++i)
+  for (int i = 0; i < 6; ++i)
     if ((rc = aalloc(&T[i], max_act * esz))) return rc;
-  scratch_bytes = max_bn_scratch > max_wg_scratch ? max_bn_scratch : max_wg_scratch;
+  scratch_bytes = max_bn_scratch > max_wg_scratch ? max_bn_scratch : max_wg_scratch;  // the fc wgrad uses it too
   if ((rc = aalloc(&scratch, scratch_bytes))) return rc;
+  scratch_wg_bytes = max_wg_scratch;
+  if ((rc = aalloc(&scratch_wg, scratch_wg_bytes))) return rc;
   act_batch = B;
   return SRT_OK;
 }
@@ -460,6 +506,9 @@ int Step::alloc_activations(int B) {
 // Waits for the stream and hands every activation block back to its allocator (pages stay mapped).
 int Step::free_activation_blocks() {
   if (stream && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
+  if (side && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(side));  // an aborted backward never joined
+  for (bool& b : read_pending) b = false;
+  side_dirty = wt_dirty = false;
   for (void* p : act_blocks) {
     if (pool) {
       int rc = srt_pool_free(pool, pool_kind, p);
@@ -536,6 +585,7 @@ int Step::shrink_activations(int B, size_t* released_bytes) {
 // bf16 working copy of the parameters (bf16 mode) and transposed filters for dgrad.
 int Step::refresh_working_copies() {
   int rc;
+  if ((rc = join_side())) return rc;
   if (cfg.dtype == SRT_BF16 && (rc = cast_f32_to_bf16(P, Pw, (int64_t)n_flat, stream))) return rc;
   auto tr = [&](const ConvL& c) -> int {
     return filter_transpose(cfg.dtype, pw(c.w), wt(c), c.K, c.R * c.S, c.C, stream);
@@ -555,6 +605,7 @@ int Step::refresh_working_copies() {
 int Step::forward(int B) {
   const int dt = cfg.dtype, impl = cfg.impl;
   int rc;
+  if (side_dirty && (rc = join_side())) return rc;  // an aborted backward may have left filter-gradient kernels in flight
   auto run_unit = [&](Unit& u, const void* in, const void* residual) -> int {
     if (int c = checkpoint()) return c;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
@@ -610,6 +661,7 @@ int Step::forward(int B) {
 int Step::backward(int B) {
   const int dt = cfg.dtype, impl = cfg.impl;
   int rc;
+  if ((rc = join_side())) return rc;
   // fc
   srt_conv_desc fd = {B, 1, 1, feat_C, cfg.num_classes, 1, 1, 1, 0, 1, 1};
   const double fc_flops = 2.0 * B * feat_C * cfg.num_classes;
@@ -627,11 +679,14 @@ int Step::backward(int B) {
         return avgpool_bwd(dt, T[1], T[0], B, final_HW, feat_C, stream); })))
     return rc;
 
-  // gradient through conv+BN(+ReLU): dy (w.r.t. u.y) -> dz in T[1], filter gradient into G
+  // gradient through conv+BN(+ReLU): dy (w.r.t. u.y) -> dz, filter gradient into G
+  const bool fork = use_side();
   auto unit_bwd = [&](Unit& u, const void* dy, const void* in, void* dz, void* dres) -> int {
     if (int c = checkpoint()) return c;
     const int64_t rows = (int64_t)B * u.P * u.Q;
     int r;
+    if ((r = before_write(dz))) return r;
+    if (dres && (r = before_write(dres))) return r;
     // two passes over (dy, z[, y]) plus the dz (and masked-gradient) writes
     const double abytes = (double)rows * u.bn.C * esz;
     const double bn_bytes = abytes * ((dres ? 3 : 2) * 2 + 1 + (dres ? 1 : 0));
@@ -643,41 +698,60 @@ int Step::backward(int B) {
       return r;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     const double flops = 2.0 * rows * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
-    return timed(SRT_PROF_WGRAD, flops, [&] {
-      return conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch, scratch_bytes, stream); });
+    if (!fork)
+      return timed(SRT_PROF_WGRAD, flops, [&] {
+        return conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch_wg, scratch_wg_bytes, stream); });
+    SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+    side_dirty = true;
+    if ((r = conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch_wg, scratch_wg_bytes, side))) return r;
+    const int slot = t_slot(dz);
+    if (slot >= 0) {
+      SRT_CHECK_CUDA(cudaEventRecord(ev_read[slot], side));
+      read_pending[slot] = true;
+    }
+    return SRT_OK;
   };
   auto unit_dgrad = [&](Unit& u, const void* dz, void* dx, const void* addend) -> int {
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     srt_conv_epilogue ep = {nullptr, addend};
     const double flops = 2.0 * B * u.P * u.Q * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
+    if (int r = before_write(dx)) return r;
     return timed(SRT_PROF_CONV, flops, [&] {
       return conv_dgrad(d, dt, impl, dz, wt(u.conv), dx, addend ? &ep : nullptr, stream); });
   };
 
+  int flip = 0;
+  auto next_dz = [&]() -> void* { flip ^= 1; return flip ? T[1] : T[5]; };
   for (int i = (int)blocks.size() - 1; i >= 0; --i) {
     Block& k = blocks[i];
     const void* x_in = i == 0 ? pool_y : blocks[i - 1].u3.y;
-    // T0 = dout. u3: dz3 -> T1, masked dout -> T2
-    if ((rc = unit_bwd(k.u3, T[0], k.u2.y, T[1], T[2]))) return rc;
-    if ((rc = unit_dgrad(k.u3, T[1], T[3], nullptr))) return rc;       // dy2 -> T3
-    if ((rc = unit_bwd(k.u2, T[3], k.u1.y, T[1], nullptr))) return rc;  // dz2 -> T1
-    if ((rc = unit_dgrad(k.u2, T[1], T[3], nullptr))) return rc;       // dy1 -> T3
-    if ((rc = unit_bwd(k.u1, T[3], x_in, T[1], nullptr))) return rc;    // dz1 -> T1
+    // T0 = dout. u3: dz3 -> D, masked dout -> T2
+    void* D = next_dz();
+    if ((rc = unit_bwd(k.u3, T[0], k.u2.y, D, T[2]))) return rc;
+    if ((rc = unit_dgrad(k.u3, D, T[3], nullptr))) return rc;        // dy2 -> T3
+    D = next_dz();
+    if ((rc = unit_bwd(k.u2, T[3], k.u1.y, D, nullptr))) return rc;   // dz2 -> D
+    if ((rc = unit_dgrad(k.u2, D, T[3], nullptr))) return rc;        // dy1 -> T3
+    D = next_dz();
+    if ((rc = unit_bwd(k.u1, T[3], x_in, D, nullptr))) return rc;     // dz1 -> D
     if (k.has_ds) {
       if ((rc = unit_bwd(k.ds, T[2], x_in, T[3], nullptr))) return rc;   // dz_ds -> T3
       if ((rc = unit_dgrad(k.ds, T[3], T[4], nullptr))) return rc;     // dx_ds -> T4
-      if ((rc = unit_dgrad(k.u1, T[1], T[4], T[4]))) return rc;        // dx = dgrad(dz1) + dx_ds
+      if ((rc = unit_dgrad(k.u1, D, T[4], T[4]))) return rc;           // dx = dgrad(dz1) + dx_ds
     } else {
-      if ((rc = unit_dgrad(k.u1, T[1], T[4], T[2]))) return rc;        // dx = dgrad(dz1) + masked dout
+      if ((rc = unit_dgrad(k.u1, D, T[4], T[2]))) return rc;           // dx = dgrad(dz1) + masked dout
     }
     void* t = T[0]; T[0] = T[4]; T[4] = t;
   }
   // stem
   const double pool_in = (double)B * stem.P * stem.Q * 64 * esz;
+  if ((rc = before_write(T[3]))) return rc;
   if ((rc = timed(SRT_PROF_OTHER, pool_in * 1.25 + pool_in / 4 / esz, [&] {
         return maxpool_bwd(dt, T[0], pool_arg, T[3], B, stem.P, stem.Q, 64, stream); })))
     return rc;
-  return unit_bwd(stem, T[3], x0, T[1], nullptr);
+  if ((rc = unit_bwd(stem, T[3], x0, next_dz(), nullptr))) return rc;
+  return join_side();
 }
 
 }  // namespace srt
@@ -713,6 +787,7 @@ int srt_step_destroy(srt_step* h) {
   if (!h) return SRT_OK;
   Step* s = (Step*)h;
   cudaStreamSynchronize(s->stream);
+  if (s->side) cudaStreamSynchronize(s->side);
   delete s;
   return SRT_OK;
 }
@@ -854,6 +929,7 @@ int srt_step_optimizer(srt_step* h) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s, "optimizer: null handle");
   Step::SmScope sm_scope(s);
+  if (int jr = s->join_side()) return jr;  // the parameters' working copy must not change under a reader
   const float* grad = s->accum_pending > 0 ? s->ACC : s->G;
   const bool bf = s->cfg.dtype == SRT_BF16;
   int rc = s->timed(SRT_PROF_OPTIM, (double)s->n_flat * (bf ? 22 : 20), [&] {
@@ -865,8 +941,17 @@ int srt_step_optimizer(srt_step* h) {
     s->accum_pending = 0;
   }
   s->opt_steps++;
-  // transposed filters follow the updated parameters (the bf16 copy was written by the optimizer)
+  // transposed filters follow the updated parameters (the bf16 copy was written by the optimizer). Only
+  // the backward pass reads them, so they run on the side stream beside the next forward pass.
+  cudaStream_t ts = s->stream;
+  if (s->use_side()) {
+    SRT_CHECK_CUDA(cudaEventRecord(s->ev_fork, s->stream));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(s->side, s->ev_fork, 0));
+    s->wt_dirty = true;
+    ts = s->side;
+  }
   auto tr = [&](const ConvL& c) -> int {
+    if (ts != s->stream) return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, ts);
     return s->timed(SRT_PROF_OPTIM, 2.0 * c.K * c.R * c.S * c.C * s->esz, [&] {
       return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, s->stream); });
   };
@@ -879,7 +964,7 @@ int srt_step_optimizer(srt_step* h) {
   }
   const size_t fc_wt_off = s->n_wt - align_up((size_t)s->cfg.num_classes * s->feat_C, 64);
   return filter_transpose(s->cfg.dtype, s->pw(s->fc_w), (char*)s->WT + fc_wt_off * s->esz, s->cfg.num_classes, 1,
-                          s->feat_C, s->stream);
+                          s->feat_C, ts);
 }
 
 int srt_step_loss(srt_step* h, float* host_loss) {
@@ -923,6 +1008,15 @@ int srt_step_follow_infer_tpc(srt_step* h, srt_comm* comm, int device, int min_t
   return srt_step_follow_sm_mask(h, 1);
 }
 
+int srt_step_overlap_wgrad(srt_step* h, int on) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s, "overlap_wgrad: null handle");
+  int rc = s->join_side();
+  if (rc) return rc;
+  s->overlap_wgrad = on != 0;
+  return SRT_OK;
+}
+
 int srt_step_current_sms(srt_step* h, int* sms) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && sms, "current_sms: null argument");
@@ -934,6 +1028,7 @@ int srt_step_synchronize(srt_step* h) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s, "synchronize: null handle");
   SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  if (s->side) SRT_CHECK_CUDA(cudaStreamSynchronize(s->side));
   return SRT_OK;
 }
 

@@ -198,6 +198,9 @@ class ResNetStep:
     def reserve_activations(self, B: int) -> None:
         call("srt_step_reserve_activations", self._h, B)
 
+    def overlap_wgrad(self, on: bool = True) -> None:
+        call("srt_step_overlap_wgrad", self._h, int(on))
+
     def follow_sm_mask(self, on: bool = True) -> None:
         """Run on the green-context partition that fits the process-wide allowed-SM mask (checked between units)."""
         call("srt_step_follow_sm_mask", self._h, int(on))

@@ -2,6 +2,7 @@
 #include <stdarg.h>
 
 #include <atomic>
+#include <stdlib.h>
 #include <mutex>
 
 #include "common.cuh"
@@ -35,6 +36,16 @@ int sm_count() {
   const int lim = sm_limit();
   return lim > 0 && lim < cached[dev] ? lim : cached[dev];
 }
+
+static thread_local bool tl_pdl_on = true;
+void set_pdl_enabled(bool on) { tl_pdl_on = on; }
+int pdl_classes() {
+  static const int v = [] { const char* e = getenv("SIRIUS_B200_PDL"); return e ? atoi(e) : 7; }();
+  return tl_pdl_on ? v : 0;
+}
+static thread_local bool tl_pdl_big = true;
+bool pdl_big_kernels() { return tl_pdl_big; }
+void set_pdl_big_kernels(bool on) { tl_pdl_big = on; }
 
 static std::mutex g_mask_mu;
 static SmMask g_mask = {{~0ull, ~0ull, ~0ull}};

@@ -100,6 +100,56 @@ template <> struct Vec16<__nv_bfloat16> {
   }
 };
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Chains of short kernels on one stream lose a few microseconds at every boundary (launch latency and
+// the ramp of the next grid). A kernel launched with launch_pdl() may be scheduled while its
+// predecessor on the stream still runs; it must call pdl_enter() before it touches global memory:
+// that waits until the predecessor has completed and its writes are visible, then lets the kernel
+// after this one be scheduled in turn (one kernel deep, so waiting blocks never pile up on the SMs).
+// In a kernel launched the ordinary way both instructions do nothing.
+__device__ inline void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
+}
+// Which kernel classes launch early: bit 0 BatchNorm, bit 1 tensor-core GEMMs, bit 2 everything else.
+// SIRIUS_B200_PDL overrides the default at process start (a tuning aid).
+enum { PDL_NORM = 1, PDL_GEMM = 2, PDL_MISC = 4 };
+int pdl_classes();
+// Per thread: launches made while this is off are ordinary ones (used for work queued on a second stream,
+// where blocks that sit resident waiting for their predecessor take SM room from the main stream).
+void set_pdl_enabled(bool on);
+struct PdlOff {  // scope guard
+  bool off;
+  explicit PdlOff(bool o) : off(o) { if (off) set_pdl_enabled(false); }
+  ~PdlOff() { if (off) set_pdl_enabled(true); }
+};
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl_if(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = early ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  return launch_pdl_if((pdl_classes() & PDL_MISC) != 0, kernel, grid, block, smem, st, static_cast<Args&&>(args)...);
+}
+// Kernels that hold most of an SM's shared memory (the tensor-core GEMMs) should not sit resident waiting
+// for their predecessor while another stream could use that SM; the step executor turns early launch
+// of those off while it overlaps streams.
+bool pdl_big_kernels();
+void set_pdl_big_kernels(bool on);
+
+
 // ---- allowed-SM mask ---------------------------------------------------------------------
 // Bit i set = SM i may run training CTAs. Passed by value to persistent kernels, which read
 // %smid and retire at once when their SM is not allowed.

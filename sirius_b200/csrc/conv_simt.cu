@@ -164,6 +164,7 @@ wgrad_simt(GatherGeom g /* fprop geometry: rows = output pixels */, const T* __r
 
 __global__ void split_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                     long long n, int splits) {
+  pdl_enter();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
@@ -180,7 +181,7 @@ int launch_split_reduce(const float* partial, float* out, long long n, int split
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  split_reduce_kernel<<<(unsigned)blocks, threads, 0, st>>>(partial, out, n, splits);
+  launch_pdl(split_reduce_kernel, dim3((unsigned)blocks), dim3(threads), 0, st, partial, out, n, splits);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

@@ -21,6 +21,7 @@ template <typename T>
 __global__ void maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y,
                                    uint8_t* __restrict__ argmax, int N, int H, int W, int C, int P,
                                    int Q) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int CV = C / V;
   const int64_t total = (int64_t)N * P * Q * CV;
@@ -64,6 +65,7 @@ __global__ void maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y,
 template <typename T>
 __global__ void maxpool_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ argmax,
                                    T* __restrict__ dx, int N, int H, int W, int C, int P, int Q) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int CV = C / V;
   const int64_t total = (int64_t)N * H * W * CV;
@@ -109,6 +111,7 @@ __global__ void maxpool_bwd_kernel(const T* __restrict__ dy, const uint8_t* __re
 template <typename T>
 __global__ void avgpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int HW,
                                    int C) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int CV = C / V;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -137,6 +140,7 @@ __global__ void avgpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, i
 template <typename T>
 __global__ void avgpool_bwd_kernel(const T* __restrict__ dy, T* __restrict__ dx, int N, int HW,
                                    int C) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int CV = C / V;
   const int64_t total = (int64_t)N * HW * CV;
@@ -190,6 +194,7 @@ template <typename T>
 __global__ void softmax_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels,
                                   int classes, float grad_scale, float* __restrict__ row_loss,
                                   T* __restrict__ dlogits) {
+  pdl_enter();
   const int row = blockIdx.x;
   const T* l = logits + (size_t)row * classes;
   float mx = -INFINITY;
@@ -214,6 +219,7 @@ __global__ void softmax_ce_kernel(const T* __restrict__ logits, const int64_t* _
 
 // out[0] (+)= sum of v[0..n) in a fixed order (single block).
 __global__ void sum_f32_kernel(const float* __restrict__ v, int n, float* out, int accumulate) {
+  pdl_enter();
   __shared__ double sh[NT];
   double s = 0.0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)v[i];
@@ -229,6 +235,7 @@ __global__ void sum_f32_kernel(const float* __restrict__ v, int n, float* out, i
 // out[k] = sum_rows dy[r][k]; one thread per column chunk, two-stage through shared memory.
 template <typename T>
 __global__ void colsum_kernel(const T* __restrict__ dy, int64_t rows, int K, float* __restrict__ out) {
+  pdl_enter();
   // blockDim = (32 columns, 8 row lanes)
   __shared__ float sh[8][33];
   const int k = blockIdx.x * 32 + threadIdx.x;
@@ -250,6 +257,7 @@ __global__ void sgd_momentum_kernel(float* __restrict__ p, const float* __restri
                                     float* __restrict__ m, __nv_bfloat16* __restrict__ pb,
                                     int64_t n4, int64_t n, float lr, float mu, float wd,
                                     int first_step) {
+  pdl_enter();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n4; i += stride) {
@@ -291,6 +299,7 @@ __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
                              float* __restrict__ m, float* __restrict__ v,
                              __nv_bfloat16* __restrict__ pb, int64_t n, float lr, float b1, float b2,
                              float eps, float wd, float bc1, float bc2_sqrt) {
+  pdl_enter();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const float step_size = lr / bc1;
@@ -308,6 +317,7 @@ __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
 
 __global__ void grad_accumulate_kernel(float* __restrict__ acc, float* __restrict__ g, int64_t n4,
                                        int64_t n) {
+  pdl_enter();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n4; i += stride) {
@@ -325,6 +335,7 @@ __global__ void grad_accumulate_kernel(float* __restrict__ acc, float* __restric
 template <typename T>
 __global__ void nchw_to_nhwc_kernel(const float* __restrict__ src, T* __restrict__ dst, int N, int C,
                                     int H, int W, int Cpad) {
+  pdl_enter();
   const int64_t total = (int64_t)N * H * W * Cpad;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -341,12 +352,14 @@ __global__ void nchw_to_nhwc_kernel(const float* __restrict__ src, T* __restrict
 
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d,
                                      int64_t n) {
+  pdl_enter();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) d[i] = __float2bfloat16_rn(s[i]);
 }
 __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ d,
                                      int64_t n) {
+  pdl_enter();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) d[i] = __bfloat162float(s[i]);
@@ -356,6 +369,7 @@ __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ s, float*
 template <typename T>
 __global__ void filter_transpose_kernel(const T* __restrict__ w, T* __restrict__ wt, int K, int RS,
                                         int C) {
+  pdl_enter();
   __shared__ T tile[32][33];
   const int rs = blockIdx.z;
   const int c0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
@@ -382,7 +396,7 @@ int maxpool_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H
   const int P = (H + 2 - 3) / 2 + 1, Q = (W + 2 - 3) / 2 + 1;
   DISPATCH_T(dtype, {
     const int64_t total = (int64_t)N * P * Q * (C / Vec16<T>::N);
-    maxpool_fwd_kernel<T><<<stream_grid(total), NT, 0, st>>>((const T*)x, (T*)y, argmax, N, H, W, C, P, Q);
+    launch_pdl(maxpool_fwd_kernel<T>, dim3(stream_grid(total)), dim3(NT), 0, st, (const T*)x, (T*)y, argmax, N, H, W, C, P, Q);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -394,7 +408,7 @@ int maxpool_bwd(int dtype, const void* dy, const uint8_t* argmax, void* dx, int 
   const int P = (H + 2 - 3) / 2 + 1, Q = (W + 2 - 3) / 2 + 1;
   DISPATCH_T(dtype, {
     const int64_t total = (int64_t)N * H * W * (C / Vec16<T>::N);
-    maxpool_bwd_kernel<T><<<stream_grid(total), NT, 0, st>>>((const T*)dy, argmax, (T*)dx, N, H, W, C, P, Q);
+    launch_pdl(maxpool_bwd_kernel<T>, dim3(stream_grid(total)), dim3(NT), 0, st, (const T*)dy, argmax, (T*)dx, N, H, W, C, P, Q);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -404,7 +418,7 @@ int avgpool_fwd(int dtype, const void* x, void* y, int N, int HW, int C, cudaStr
   SRT_REQUIRE(C % 8 == 0, "avgpool: C (%d) must be a multiple of 8", C);
   DISPATCH_T(dtype, {
     const int64_t total = (int64_t)N * (C / Vec16<T>::N);
-    avgpool_fwd_kernel<T><<<(unsigned)((total + NT - 1) / NT), NT, 0, st>>>((const T*)x, (T*)y, N, HW, C);
+    launch_pdl(avgpool_fwd_kernel<T>, dim3((unsigned)((total + NT - 1) / NT)), dim3(NT), 0, st, (const T*)x, (T*)y, N, HW, C);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -414,7 +428,7 @@ int avgpool_bwd(int dtype, const void* dy, void* dx, int N, int HW, int C, cudaS
   SRT_REQUIRE(C % 8 == 0, "avgpool: C (%d) must be a multiple of 8", C);
   DISPATCH_T(dtype, {
     const int64_t total = (int64_t)N * HW * (C / Vec16<T>::N);
-    avgpool_bwd_kernel<T><<<stream_grid(total), NT, 0, st>>>((const T*)dy, (T*)dx, N, HW, C);
+    launch_pdl(avgpool_bwd_kernel<T>, dim3(stream_grid(total)), dim3(NT), 0, st, (const T*)dy, (T*)dx, N, HW, C);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -424,21 +438,21 @@ int softmax_ce(int dtype, const void* logits, const int64_t* labels, int B, int 
                float grad_scale, float* row_loss, void* dlogits, cudaStream_t st) {
   SRT_REQUIRE(B > 0 && classes > 0, "softmax_ce: empty input");
   DISPATCH_T(dtype, {
-    softmax_ce_kernel<T><<<B, NT, 0, st>>>((const T*)logits, labels, classes, grad_scale, row_loss, (T*)dlogits);
+    launch_pdl(softmax_ce_kernel<T>, dim3(B), dim3(NT), 0, st, (const T*)logits, labels, classes, grad_scale, row_loss, (T*)dlogits);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 
 int sum_f32(const float* v, int n, float* out, int accumulate, cudaStream_t st) {
-  sum_f32_kernel<<<1, NT, 0, st>>>(v, n, out, accumulate);
+  launch_pdl(sum_f32_kernel, dim3(1), dim3(NT), 0, st, v, n, out, accumulate);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 
 int colsum(int dtype, const void* dy, int64_t rows, int K, float* out, cudaStream_t st) {
   DISPATCH_T(dtype, {
-    colsum_kernel<T><<<ceil_div(K, 32), dim3(32, 8), 0, st>>>((const T*)dy, rows, K, out);
+    launch_pdl(colsum_kernel<T>, dim3(ceil_div(K, 32)), dim3(dim3(32, 8)), 0, st, (const T*)dy, rows, K, out);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -448,7 +462,7 @@ int sgd_momentum(float* p, const float* g, float* m, void* pb, int64_t n, float 
                  float wd, int first_step, cudaStream_t st) {
   if (n == 0) return SRT_OK;
   const int64_t n4 = n / 4;
-  sgd_momentum_kernel<<<stream_grid(n4 > 0 ? n4 : 1, 8), NT, 0, st>>>(
+  launch_pdl(sgd_momentum_kernel, dim3(stream_grid(n4 > 0 ? n4 : 1, 8)), dim3(NT), 0, st, 
       p, g, m, (__nv_bfloat16*)pb, n4, n, lr, mu, wd, first_step);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -460,7 +474,7 @@ int adamw(float* p, const float* g, float* m, float* v, void* pb, int64_t n, flo
   SRT_REQUIRE(step >= 1, "adamw: step counts from 1");
   const float bc1 = 1.f - powf(b1, (float)step);
   const float bc2 = 1.f - powf(b2, (float)step);
-  adamw_kernel<<<stream_grid(n, 8), NT, 0, st>>>(p, g, m, v, (__nv_bfloat16*)pb, n, lr, b1, b2, eps,
+  launch_pdl(adamw_kernel, dim3(stream_grid(n, 8)), dim3(NT), 0, st, p, g, m, v, (__nv_bfloat16*)pb, n, lr, b1, b2, eps,
                                                  wd, bc1, sqrtf(bc2));
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -469,7 +483,7 @@ int adamw(float* p, const float* g, float* m, float* v, void* pb, int64_t n, flo
 int grad_accumulate(float* acc, float* g, int64_t n, cudaStream_t st) {
   if (n == 0) return SRT_OK;
   const int64_t n4 = n / 4;
-  grad_accumulate_kernel<<<stream_grid(n4 > 0 ? n4 : 1, 8), NT, 0, st>>>(acc, g, n4, n);
+  launch_pdl(grad_accumulate_kernel, dim3(stream_grid(n4 > 0 ? n4 : 1, 8)), dim3(NT), 0, st, acc, g, n4, n);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -479,7 +493,7 @@ int nchw_to_nhwc(int dtype, const float* src, void* dst, int N, int C, int H, in
   SRT_REQUIRE(Cpad >= C, "nchw_to_nhwc: Cpad < C");
   const int64_t total = (int64_t)N * H * W * Cpad;
   DISPATCH_T(dtype, {
-    nchw_to_nhwc_kernel<T><<<stream_grid(total), NT, 0, st>>>(src, (T*)dst, N, C, H, W, Cpad);
+    launch_pdl(nchw_to_nhwc_kernel<T>, dim3(stream_grid(total)), dim3(NT), 0, st, src, (T*)dst, N, C, H, W, Cpad);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -487,13 +501,13 @@ int nchw_to_nhwc(int dtype, const float* src, void* dst, int N, int C, int H, in
 
 int cast_f32_to_bf16(const float* s, void* d, int64_t n, cudaStream_t st) {
   if (n == 0) return SRT_OK;
-  cast_f32_bf16_kernel<<<stream_grid(n), NT, 0, st>>>(s, (__nv_bfloat16*)d, n);
+  launch_pdl(cast_f32_bf16_kernel, dim3(stream_grid(n)), dim3(NT), 0, st, s, (__nv_bfloat16*)d, n);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 int cast_bf16_to_f32(const void* s, float* d, int64_t n, cudaStream_t st) {
   if (n == 0) return SRT_OK;
-  cast_bf16_f32_kernel<<<stream_grid(n), NT, 0, st>>>((const __nv_bfloat16*)s, d, n);
+  launch_pdl(cast_bf16_f32_kernel, dim3(stream_grid(n)), dim3(NT), 0, st, (const __nv_bfloat16*)s, d, n);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -501,7 +515,7 @@ int cast_bf16_to_f32(const void* s, float* d, int64_t n, cudaStream_t st) {
 int filter_transpose(int dtype, const void* w, void* wt, int K, int RS, int C, cudaStream_t st) {
   dim3 grid(ceil_div(C, 32), ceil_div(K, 32), RS);
   DISPATCH_T(dtype, {
-    filter_transpose_kernel<T><<<grid, dim3(32, 8), 0, st>>>((const T*)w, (T*)wt, K, RS, C);
+    launch_pdl(filter_transpose_kernel<T>, dim3(grid), dim3(dim3(32, 8)), 0, st, (const T*)w, (T*)wt, K, RS, C);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;

@@ -132,6 +132,7 @@ template <int BN, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 igemm_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a) {
+  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   extern __shared__ uint8_t smem_raw[];
   SmemLayout sm = carve_smem<NS, B_STAGE_BYTES>(smem_raw);
@@ -311,6 +312,7 @@ template <int BN, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap_dy,
                    const __grid_constant__ CUtensorMap tmap_x) {
+  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;  // BN/64 blocks of [64 pixels][128 bytes]
   constexpr int CPR = BN / 8;                 // 16-byte chunks per pixel row
   constexpr int RSTEP = NPROD / CPR;          // pixel rows covered per pass
@@ -497,6 +499,7 @@ __global__ void __launch_bounds__(P_THREADS, 1)
 igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_d) {
+  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int PLAG = NS - 2;  // cp.async groups in flight per gather thread
   extern __shared__ uint8_t smem_raw[];
@@ -816,7 +819,7 @@ int launch_fwd(const FwdParams& p, const CUtensorMap& tb, const CUtensorMap& ta,
     configured = true;
   }
   dim3 grid(ceil_div(p.g.M, BM), ceil_div(p.g.Nout, BN));
-  igemm_fwd_kernel<BN, NS><<<grid, NTHREADS, smem, st>>>(p, tb, ta);
+  launch_pdl_if(pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0, igemm_fwd_kernel<BN, NS>, dim3(grid), dim3(NTHREADS), smem, st, p, tb, ta);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -832,7 +835,7 @@ int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, const CUtensorMap
     configured = true;
   }
   dim3 grid(ceil_div(p.g.Kg, BN), ceil_div(p.g.Nout, BM), splits);
-  igemm_wgrad_kernel<BN, NS><<<grid, NTHREADS, smem, st>>>(p, tdy, tx);
+  launch_pdl_if(pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0, igemm_wgrad_kernel<BN, NS>, dim3(grid), dim3(NTHREADS), smem, st, p, tdy, tx);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -850,7 +853,7 @@ int launch_persistent(const PersistParams& p, const CUtensorMap& tb, const CUten
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  igemm_fwd_persistent<BN, NS><<<grid, P_THREADS, smem, st>>>(p, tb, ta, td);
+  launch_pdl_if(pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0, igemm_fwd_persistent<BN, NS>, dim3(grid), dim3(P_THREADS), smem, st, p, tb, ta, td);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

@@ -96,6 +96,7 @@ __device__ inline double2 reduce_partials(const double* __restrict__ partial, in
 template <typename T>
 __global__ void __launch_bounds__(NT)
 bn_stats_partial(const T* __restrict__ z, int64_t rows, int C, RowMap m, double* partial) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int t = threadIdx.x;
   const int tc = t % m.TC, rl = t / m.TC;
@@ -130,6 +131,7 @@ bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows
                   const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                   float momentum, float* running_mean, float* running_var, float* mean, float* invstd,
                   float* scale, float* shift) {
+  pdl_enter();
   const int c = blockIdx.x * FIN_CH + threadIdx.x;
   const double2 tot = reduce_partials(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
@@ -156,6 +158,7 @@ template <typename T, bool HAS_RES>
 __global__ void __launch_bounds__(NT)
 bn_apply_kernel(const T* __restrict__ z, const T* __restrict__ residual, T* __restrict__ y, int64_t nvec,
                 int CV, const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
   Vec16<T> x[UNR], rv[UNR];
@@ -230,6 +233,7 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
                int64_t rows, int C, RowMap m, const float* __restrict__ mean,
                const float* __restrict__ invstd, const float* __restrict__ scale,
                const float* __restrict__ shift, int relu, double* partial) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int t = threadIdx.x;
   const int tc = t % m.TC, rl = t / m.TC;
@@ -274,6 +278,7 @@ __global__ void __launch_bounds__(FIN_CH * FIN_LANES)
 bn_bwd_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
                 const float* __restrict__ gamma, const float* __restrict__ invstd, float* dgamma,
                 float* dbeta, float* coef) {
+  pdl_enter();
   const int c = blockIdx.x * FIN_CH + threadIdx.x;
   const double2 tot = reduce_partials(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
@@ -295,6 +300,7 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
              T* __restrict__ dres, int64_t nvec, int CV, int C, const float* __restrict__ mean,
              const float* __restrict__ coef,
              const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
+  pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
   Vec16<T> a[UNR], b[UNR];
@@ -357,9 +363,9 @@ static int bn_stats_t(const void* z, int64_t rows, int C, const float* gamma, co
                       float* scale, float* shift, void* scratch, cudaStream_t st) {
   RowMap m = make_row_map(rows, C, Vec16<T>::N);
   double* partial = (double*)scratch;
-  bn_stats_partial<T><<<dim3(m.S, m.GY), NT, 0, st>>>((const T*)z, rows, C, m, partial);
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_partial<T>, dim3(m.S, m.GY), dim3(NT), 0, st, (const T*)z, rows, C, m, partial);
   SRT_LAUNCH_CHECK();
-  bn_stats_finalize<<<ceil_div(C, FIN_CH), dim3(FIN_CH, FIN_LANES), 0, st>>>(
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st,
       partial, m.S, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -383,11 +389,11 @@ static void bn_apply_t(const void* z, const void* residual, void* y, int64_t row
   constexpr int V = Vec16<T>::N;
   const int64_t nvec = rows * C / V;
   if (residual)
-    bn_apply_kernel<T, true><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)z, (const T*)residual, (T*)y,
-                                                               nvec, C / V, scale, shift, relu);
+    launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_apply_kernel<T, true>, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)z,
+               (const T*)residual, (T*)y, nvec, C / V, scale, shift, relu);
   else
-    bn_apply_kernel<T, false><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)z, nullptr, (T*)y, nvec, C / V,
-                                                                scale, shift, relu);
+    launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_apply_kernel<T, false>, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)z,
+               (const T*)nullptr, (T*)y, nvec, C / V, scale, shift, relu);
 }
 
 // ---- allocation-free variant of bn_stats ----------------------------------------------------
@@ -469,16 +475,15 @@ static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t r
   RowMap m = make_row_map(rows, C, V);
   double* partial = (double*)scratch;
   float* coef = (float*)((char*)scratch + (size_t)m.S * C * 2 * sizeof(double));
-  bn_bwd_partial<T><<<dim3(m.S, m.GY), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, rows, C,
-                                                    m, mean, invstd, scale, shift, relu, partial);
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_bwd_partial<T>, dim3(m.S, m.GY), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z, rows, C,
+             m, mean, invstd, scale, shift, relu, partial);
   SRT_LAUNCH_CHECK();
-  bn_bwd_finalize<<<ceil_div(C, FIN_CH), dim3(FIN_CH, FIN_LANES), 0, st>>>(partial, m.S, C, rows, gamma, invstd,
-                                                                  dgamma, dbeta, coef);
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_bwd_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st, partial, m.S, C, rows,
+             gamma, invstd, dgamma, dbeta, coef);
   SRT_LAUNCH_CHECK();
   const int64_t nvec = rows * C / V;
-  bn_bwd_apply<T><<<unrolled_grid(nvec), NT, 0, st>>>((const T*)dy, (const T*)y, (const T*)z, (T*)dz,
-                                                      (T*)dres, nvec, C / V, C, mean, coef, scale, shift,
-                                                      relu);
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_bwd_apply<T>, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z,
+             (T*)dz, (T*)dres, nvec, C / V, C, mean, (const float*)coef, scale, shift, relu);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

@@ -207,8 +207,12 @@ struct Step {
   // Grid sizing of the calling thread follows the partition while the step's entry points run.
   struct SmScope {
     int saved;
-    explicit SmScope(const Step* s) : saved(sm_limit()) { if (s->follow_mask) set_sm_limit(s->cur_sms); }
-    ~SmScope() { set_sm_limit(saved); }
+    bool saved_pdl;
+    explicit SmScope(const Step* s) : saved(sm_limit()), saved_pdl(pdl_big_kernels()) {
+      if (s->follow_mask) set_sm_limit(s->cur_sms);
+      set_pdl_big_kernels(true);
+    }
+    ~SmScope() { set_sm_limit(saved); set_pdl_big_kernels(saved_pdl); }
   };
 
   // Called between units: abort check + bounded launch-ahead.
@@ -704,7 +708,11 @@ int Step::backward(int B) {
     SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
     SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
     side_dirty = true;
-    if ((r = conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch_wg, scratch_wg_bytes, side))) return r;
+    {
+      PdlOff no_early_launch(true);
+      r = conv_wgrad(d, dt, impl, dz, in, gf(u.conv.w), scratch_wg, scratch_wg_bytes, side);
+    }
+    if (r) return r;
     const int slot = t_slot(dz);
     if (slot >= 0) {
       SRT_CHECK_CUDA(cudaEventRecord(ev_read[slot], side));
@@ -950,6 +958,7 @@ int srt_step_optimizer(srt_step* h) {
     s->wt_dirty = true;
     ts = s->side;
   }
+  PdlOff no_early_launch(ts != s->stream);
   auto tr = [&](const ConvL& c) -> int {
     if (ts != s->stream) return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, ts);
     return s->timed(SRT_PROF_OPTIM, 2.0 * c.K * c.R * c.S * c.C * s->esz, [&] {

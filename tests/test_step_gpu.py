@@ -158,3 +158,39 @@ def test_resnet152_c1_against_golden(dtype):
         print("C1 torch bf16 autocast losses", ac["losses"])
         for a, bac, b64 in zip(losses, ac["losses"], g["fp64"]["losses"]):
             assert anchored_scalar(a, bac, b64, factor=1.5, floor=5e-2)
+
+
+def test_backward_overlap_is_bit_identical_and_repeatable():
+    """The filter-gradient kernels run on a second stream beside the rest of backward, the filter
+    transposes beside the next forward, and short kernels are launched early (programmatic dependent
+    launch). None of that may change a bit: several optimizer steps with the overlap on, on again, and
+    off give identical losses, weights and gradients."""
+    arch, batch, image, steps = "resnet50", 16, 128, 4
+    model = O.build_model(arch, 0)
+    (im, lb), = O.make_batches(batch, 1, image)
+    names = ("conv1.weight", "layer1.0.conv1.weight", "layer2.0.downsample.0.weight", "layer3.4.conv2.weight",
+             "layer4.2.conv3.weight", "layer3.5.bn2.weight", "fc.weight", "fc.bias")
+
+    def run(overlap):
+        step = ResNetStep(layers=O.LAYERS[arch], max_batch=batch, image=image, dtype="bf16")
+        step.load_state_dict(O.state_arrays(model))
+        step.overlap_wgrad(overlap)
+        step.upload_batch(im, lb)
+        losses = []
+        for _ in range(steps):
+            step.forward_backward(batch, batch)
+            step.optimizer_step()
+            losses.append(step.loss())
+        step.synchronize()
+        out = (losses, [step.get(n).copy() for n in names], [step.get(n, GET_GRAD).copy() for n in names])
+        step.close()
+        return out
+
+    ref = run(True)
+    assert all(np.isfinite(ref[0]))
+    for overlap in (True, False):
+        got = run(overlap)
+        assert got[0] == ref[0]
+        for a, b in zip(got[1] + got[2], ref[1] + ref[2]):
+            assert np.array_equal(a, b)
+    assert ops.tc_status() == 0

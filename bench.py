@@ -153,10 +153,22 @@ def run_ours(args):
         grad_t.zero_()
         torch.cuda.synchronize()
 
+    # Gradient exchange overlapped with backward: forward_backward returns once everything is enqueued
+    # (the GPU is then still early in backward), so the all-reduce of each bucket is enqueued right away on
+    # a communication stream that waits for that bucket's ready event; the optimizer waits for the last one.
+    comm_stream = torch.cuda.Stream() if world > 1 else None
+    buckets = step.grad_buckets() if world > 1 else []
+    done_ev = torch.cuda.Event() if world > 1 else None
+
     def allreduce():
-        if grad_t is not None:
-            with torch.cuda.stream(stream):
-                dist.all_reduce(grad_t)
+        if grad_t is None:
+            return
+        for b, (off, cnt) in enumerate(buckets):
+            step.wait_grad_bucket(b, comm_stream.cuda_stream)
+            with torch.cuda.stream(comm_stream):
+                dist.all_reduce(grad_t[off:off + cnt])
+        done_ev.record(comm_stream)
+        step.wait_event(done_ev.cuda_event)
 
     def step_resident(i):
         im, lb = dev[i % nbuf]

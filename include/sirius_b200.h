@@ -234,6 +234,17 @@ int srt_step_follow_sm_mask(srt_step* s, int on);
  * kernels of the following units (on by default; the result is bit-identical either way). Off while the
  * step follows an SM partition or is being profiled per kernel family. */
 int srt_step_overlap_wgrad(srt_step* s, int on);
+/* Data-parallel gradient exchange overlapped with backward (the c10d Reducer's buckets,
+ * pytorch/torch_col/csrc/dist_ext.{h,cc}): the flat gradient buffer (srt_step_grad_buffer) is cut at block
+ * boundaries into buckets of at least 25 MiB, numbered in the order backward completes them. After
+ * srt_step_forward_backward has returned (everything is enqueued, little has run), make the communication
+ * stream wait for bucket i with srt_step_wait_grad_bucket and enqueue the all-reduce of
+ * [offset, offset + count) floats on it; when all are enqueued, record an event on that stream and pass it to
+ * srt_step_wait_event so that the optimizer runs after the exchange. */
+int srt_step_num_grad_buckets(srt_step* s);
+int srt_step_grad_bucket(srt_step* s, int i, int64_t* offset, int64_t* count);
+int srt_step_wait_grad_bucket(srt_step* s, int i, void* stream);
+int srt_step_wait_event(srt_step* s, void* cuda_event);
 int srt_step_current_sms(srt_step* s, int* sms);
 int srt_step_destroy(srt_step* s);
 /* Parameter registry under torchvision state_dict names ("layer1.0.conv1.weight", ...). Shapes and

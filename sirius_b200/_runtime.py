@@ -114,6 +114,10 @@ register({
     "srt_step_request_abort": (None, [_vp, _i]),
     "srt_step_follow_sm_mask": (None, [_vp, _i]),
     "srt_step_overlap_wgrad": (None, [_vp, _i]),
+    "srt_step_num_grad_buckets": (_i, [_vp]),
+    "srt_step_grad_bucket": (None, [_vp, _i, C.POINTER(_i64), C.POINTER(_i64)]),
+    "srt_step_wait_grad_bucket": (None, [_vp, _i, _vp]),
+    "srt_step_wait_event": (None, [_vp, _vp]),
     "srt_step_current_sms": (None, [_vp, C.POINTER(_i)]),
     "srt_step_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i]),
     "srt_smp_partition_levels": (None, [_i, C.POINTER(_i), _i, C.POINTER(_i)]),

@@ -103,6 +103,12 @@ struct Step {
   bool side_dirty = false;         // side-stream work queued that the main stream has not waited for
   bool wt_dirty = false;           // ... of which only filter transposes (the forward pass need not wait for those)
   bool overlap_wgrad = true;
+  // Gradient buckets for the data-parallel all-reduce, in the order backward completes them (fc and the
+  // last blocks first). A bucket's event fires when every gradient in its range is final.
+  struct GradBucket { size_t off, count; int first_block; cudaEvent_t ev; };
+  std::vector<GradBucket> buckets;
+  int build_buckets(size_t bucket_elems);
+  int bucket_ready(int b, bool on_side);
   bool use_side() const { return side && overlap_wgrad && !follow_mask && !prof_on; }
   int t_slot(const void* p) const { for (int i = 0; i < 6; ++i) if (T[i] == p) return i; return -1; }
   int before_write(const void* buf) {   // main stream is about to overwrite buf
@@ -276,6 +282,7 @@ struct Step {
     release_activations(nullptr);
     for (void* p : allocs) cudaFree(p);
     if (switch_ev) cudaEventDestroy(switch_ev);
+    for (auto& b : buckets) if (b.ev) cudaEventDestroy(b.ev);
     if (ev_fork) cudaEventDestroy(ev_fork);
     if (ev_join) cudaEventDestroy(ev_join);
     for (auto e : ev_read) if (e) cudaEventDestroy(e);
@@ -453,7 +460,36 @@ int Step::build() {
       SRT_CHECK_CUDA(cudaMemcpy(dst, ones.data(), r.count * 4, cudaMemcpyHostToDevice));
     }
   }
+  if ((rc = build_buckets((size_t)25 << 18))) return rc;  // 25 MiB of fp32 gradients per bucket, as c10d's default
   return refresh_working_copies();
+}
+
+int Step::build_buckets(size_t bucket_elems) {
+  for (auto& b : buckets) if (b.ev) cudaEventDestroy(b.ev);
+  buckets.clear();
+  size_t end = n_flat;
+  for (int i = (int)blocks.size() - 1; i >= 0; --i) {
+    const size_t start = params[blocks[i].u1.conv.w].off;
+    if (end - start >= bucket_elems && i > 0) {
+      buckets.push_back({start, end - start, i, nullptr});
+      end = start;
+    }
+  }
+  buckets.push_back({0, end, -1, nullptr});  // the rest, stem included: ready when backward is
+  for (auto& b : buckets) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&b.ev, cudaEventDisableTiming));
+  return SRT_OK;
+}
+
+// Records bucket b's event behind the last kernel that writes into its range.
+int Step::bucket_ready(int b, bool on_side) {
+  if (on_side) {  // filter gradients come from the side stream, BatchNorm gradients from the main one
+    SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+    SRT_CHECK_CUDA(cudaEventRecord(buckets[b].ev, side));
+  } else {
+    SRT_CHECK_CUDA(cudaEventRecord(buckets[b].ev, stream));
+  }
+  return SRT_OK;
 }
 
 // Activation set for micro-batches of up to B samples.
@@ -729,7 +765,7 @@ int Step::backward(int B) {
       return conv_dgrad(d, dt, impl, dz, wt(u.conv), dx, addend ? &ep : nullptr, stream); });
   };
 
-  int flip = 0;
+  int flip = 0, next_bucket = 0;
   auto next_dz = [&]() -> void* { flip ^= 1; return flip ? T[1] : T[5]; };
   for (int i = (int)blocks.size() - 1; i >= 0; --i) {
     Block& k = blocks[i];
@@ -751,6 +787,10 @@ int Step::backward(int B) {
       if ((rc = unit_dgrad(k.u1, D, T[4], T[2]))) return rc;           // dx = dgrad(dz1) + masked dout
     }
     void* t = T[0]; T[0] = T[4]; T[4] = t;
+    if (next_bucket + 1 < (int)buckets.size() && buckets[next_bucket].first_block == i) {
+      if ((rc = bucket_ready(next_bucket, fork))) return rc;
+      ++next_bucket;
+    }
   }
   // stem
   const double pool_in = (double)B * stem.P * stem.Q * 64 * esz;
@@ -759,7 +799,8 @@ int Step::backward(int B) {
         return maxpool_bwd(dt, T[0], pool_arg, T[3], B, stem.P, stem.Q, 64, stream); })))
     return rc;
   if ((rc = unit_bwd(stem, T[3], x0, next_dz(), nullptr))) return rc;
-  return join_side();
+  if ((rc = join_side())) return rc;
+  return bucket_ready((int)buckets.size() - 1, false);
 }
 
 }  // namespace srt
@@ -1015,6 +1056,30 @@ int srt_step_follow_infer_tpc(srt_step* h, srt_comm* comm, int device, int min_t
   s->tpc_min_train = min_train_tpc > 0 ? min_train_tpc : 1;
   s->tpc_max_train = max_train_tpc > 0 ? max_train_tpc : 1 << 20;
   return srt_step_follow_sm_mask(h, 1);
+}
+
+int srt_step_num_grad_buckets(srt_step* h) { return h ? (int)((Step*)h)->buckets.size() : -1; }
+
+int srt_step_grad_bucket(srt_step* h, int i, int64_t* offset, int64_t* count) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && offset && count && i >= 0 && i < (int)s->buckets.size(), "grad_bucket: bad argument");
+  *offset = (int64_t)s->buckets[i].off;
+  *count = (int64_t)s->buckets[i].count;
+  return SRT_OK;
+}
+
+int srt_step_wait_grad_bucket(srt_step* h, int i, void* stream) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && i >= 0 && i < (int)s->buckets.size(), "wait_grad_bucket: bad argument");
+  SRT_CHECK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, s->buckets[i].ev, 0));
+  return SRT_OK;
+}
+
+int srt_step_wait_event(srt_step* h, void* event) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && event, "wait_event: null argument");
+  SRT_CHECK_CUDA(cudaStreamWaitEvent(s->stream, (cudaEvent_t)event, 0));
+  return SRT_OK;
 }
 
 int srt_step_overlap_wgrad(srt_step* h, int on) {

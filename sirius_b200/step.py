@@ -198,6 +198,21 @@ class ResNetStep:
     def reserve_activations(self, B: int) -> None:
         call("srt_step_reserve_activations", self._h, B)
 
+    def grad_buckets(self) -> list[tuple[int, int]]:
+        """(offset, count) in floats of each gradient bucket, in the order backward completes them."""
+        out = []
+        for i in range(_lib.lib().srt_step_num_grad_buckets(self._h)):
+            off, cnt = C.c_int64(), C.c_int64()
+            call("srt_step_grad_bucket", self._h, i, C.byref(off), C.byref(cnt))
+            out.append((off.value, cnt.value))
+        return out
+
+    def wait_grad_bucket(self, i: int, cuda_stream: int) -> None:
+        call("srt_step_wait_grad_bucket", self._h, i, C.c_void_p(cuda_stream))
+
+    def wait_event(self, cuda_event: int) -> None:
+        call("srt_step_wait_event", self._h, C.c_void_p(cuda_event))
+
     def overlap_wgrad(self, on: bool = True) -> None:
         call("srt_step_overlap_wgrad", self._h, int(on))
 

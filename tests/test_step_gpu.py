@@ -194,3 +194,43 @@ def test_backward_overlap_is_bit_identical_and_repeatable():
         for a, b in zip(got[1] + got[2], ref[1] + ref[2]):
             assert np.array_equal(a, b)
     assert ops.tc_status() == 0
+
+
+def test_gradient_buckets_tile_the_buffer_and_fire_when_final():
+    """The buckets cover the flat gradient buffer exactly once, last layers first, and a stream that waits
+    for a bucket's event sees that bucket's final values (it copies them while backward is still running)."""
+    arch, batch, image = "resnet50", 16, 128
+    model = O.build_model(arch, 0)
+    (im, lb), = O.make_batches(batch, 1, image)
+    step = ResNetStep(layers=O.LAYERS[arch], max_batch=batch, image=image, dtype="bf16")
+    step.load_state_dict(O.state_arrays(model))
+    ptr, n = step.grad_buffer()
+    buckets = step.grad_buckets()
+    assert len(buckets) >= 2
+    assert buckets[0][0] + buckets[0][1] == n and buckets[-1][0] == 0
+    for (o0, c0), (o1, c1) in zip(buckets, buckets[1:]):
+        assert o1 + c1 == o0 and c0 >= (25 << 18)
+
+    class Buf:
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+    grad = torch.as_tensor(Buf(), device="cuda:0")
+    comm = torch.cuda.Stream()
+    for _ in range(2):
+        step.upload_batch(im, lb)
+        grad.zero_()
+        torch.cuda.synchronize()
+        step.forward_backward(batch, batch)
+        copies = []
+        for b, (off, cnt) in enumerate(buckets):
+            step.wait_grad_bucket(b, comm.cuda_stream)
+            with torch.cuda.stream(comm):
+                copies.append(grad[off:off + cnt].clone())
+        done = torch.cuda.Event()
+        done.record(comm)
+        step.wait_event(done.cuda_event)
+        step.synchronize()
+        torch.cuda.synchronize()
+        for (off, cnt), c in zip(buckets, copies):
+            assert torch.equal(c, grad[off:off + cnt])
+        assert float(grad.abs().sum()) > 0
+    step.close()

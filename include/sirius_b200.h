@@ -295,6 +295,64 @@ int srt_step_profile_read(srt_step* s, double ms[SRT_PROF_NCAT], double work[SRT
 /* Kernel launches issued by this library in this process so far. */
 int64_t srt_launch_count(void);
 
+/* ---- transformer step (GPT-2 layout) ---------------------------------------------------------------
+ * The reference trains transformers.GPT2LMHeadModel with the same torch_col loop as the vision models
+ * (train/gpt2.py:26,90-97: loss = model(ids, labels=ids).loss; backward; optimizer.step). There is no
+ * reference C interface for the arithmetic (it is PyTorch's); these entry points are the compute boundary of
+ * this library for that model, shaped like the srt_step_* calls above. Parameters carry the names and
+ * shapes of the reference's state_dict (linear weights [in][out] as its Conv1D stores them). */
+typedef struct srt_gpt2 srt_gpt2;
+typedef struct srt_gpt2_config {
+  int n_layer, n_head, d_model, vocab, ctx; /* GPT-2 small: 12, 12, 768, 50257, 1024 */
+  int max_batch, seq;                       /* sequences per micro-batch, tokens per sequence (multiple of 8) */
+  float lr, beta1, beta2, eps, weight_decay; /* AdamW (torch.optim.AdamW semantics) */
+  float ln_eps;                             /* 1e-5 */
+} srt_gpt2_config;
+int srt_gpt2_create(const srt_gpt2_config* cfg, srt_gpt2** out);
+int srt_gpt2_destroy(srt_gpt2* g);
+int srt_gpt2_num_params(srt_gpt2* g);
+int srt_gpt2_param_info(srt_gpt2* g, int idx, char* name, int name_cap, int64_t shape[2], int* ndim);
+int srt_gpt2_set_param(srt_gpt2* g, int idx, const float* host);
+int srt_gpt2_get_param(srt_gpt2* g, int idx, float* host, int which /* SRT_GET_VALUE, _GRAD, _MOMENTUM */);
+int srt_gpt2_commit_params(srt_gpt2* g);                 /* after set_param: bf16 copies, transposes */
+/* ids: [B][seq] int32 host array; targets are the next token of the same sequence (labels = ids). */
+int srt_gpt2_upload_tokens(srt_gpt2* g, const int32_t* host_ids, int B);
+/* Forward, mean cross-entropy over the targets, backward. Gradients are scaled by B / global_batch
+ * (MicroBatchManager.scale_loss, pytorch/torch_col/dynamic_batch.py:112-120). */
+int srt_gpt2_forward_backward(srt_gpt2* g, int B, int global_batch);
+int srt_gpt2_forward_only(srt_gpt2* g, int B);
+int srt_gpt2_optimizer(srt_gpt2* g);
+int srt_gpt2_loss(srt_gpt2* g, float* host_loss);        /* synchronises; loss of the last micro-batch */
+int srt_gpt2_logits(srt_gpt2* g, float* host, int B);    /* [B*seq][vocab], after forward_only */
+int srt_gpt2_synchronize(srt_gpt2* g);
+void* srt_gpt2_stream(srt_gpt2* g);
+int64_t srt_gpt2_memory_bytes(srt_gpt2* g);
+int64_t srt_gpt2_num_elements(srt_gpt2* g);
+
+/* Single operators of the transformer step, for unit parity (bf16 device tensors, fp32 parameters). */
+typedef struct srt_bgemm_desc { /* D[z][m][n] = alpha * sum_k A[z][m][k] B[z][n][k]; z = (z1, z2); strides in elements */
+  int M, N, K, Z1, Z2;
+  long long lda, a_s1, a_s2, ldb, b_s1, b_s2, ldd, d_s1, d_s2;
+  float alpha;
+  int causal;   /* skip output tiles wholly above the diagonal */
+  int k_causal; /* 1: A is zero for k > m, 2: A is zero for k < m */
+} srt_bgemm_desc;
+int srt_bgemm(const srt_bgemm_desc* d, const void* A, const void* B, void* D, void* stream);
+int srt_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                      int64_t rows, int C, float eps, void* stream);
+size_t srt_layernorm_bwd_scratch_bytes(int C);
+int srt_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                      const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                      size_t scratch_bytes, void* stream);
+int srt_gelu_fwd(const void* x, void* y, int64_t n, void* stream);
+int srt_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, void* stream);
+int srt_causal_softmax_fwd(void* scores, int64_t Z, int S, void* stream);
+int srt_causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, void* stream);
+int srt_batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1,
+                          int Z2, void* stream);
+int srt_lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale,
+                         float* row_loss, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -296,4 +296,50 @@ int srt_debug_fwd_variant(int variant, int bn) {
   return SRT_OK;
 }
 
+int srt_bgemm(const srt_bgemm_desc* d, const void* A, const void* B, void* D, void* stream) {
+  SRT_REQUIRE(d && A && B && D, "bgemm: null argument");
+  BgemmDesc g = {d->M, d->N, d->K, d->Z1, d->Z2, d->lda, d->a_s1, d->a_s2, d->ldb, d->b_s1, d->b_s2,
+                 d->ldd, d->d_s1, d->d_s2, d->alpha, d->causal, d->k_causal};
+  return bgemm_bf16(g, A, B, D, (cudaStream_t)stream);
+}
+int srt_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                      int64_t rows, int C, float eps, void* stream) {
+  SRT_REQUIRE(x && gamma && beta && y && mean && rstd, "layernorm_fwd: null argument");
+  return layernorm_fwd(x, gamma, beta, y, mean, rstd, rows, C, eps, (cudaStream_t)stream);
+}
+size_t srt_layernorm_bwd_scratch_bytes(int C) { return layernorm_bwd_scratch_bytes(C); }
+int srt_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                      const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                      size_t scratch_bytes, void* stream) {
+  SRT_REQUIRE(dy && x && gamma && mean && rstd && dx && dgamma && dbeta, "layernorm_bwd: null argument");
+  return layernorm_bwd(dy, x, gamma, mean, rstd, addend, dx, dgamma, dbeta, rows, C, scratch, scratch_bytes,
+                       (cudaStream_t)stream);
+}
+int srt_gelu_fwd(const void* x, void* y, int64_t n, void* stream) {
+  SRT_REQUIRE(x && y, "gelu_fwd: null argument");
+  return gelu_fwd(x, y, n, (cudaStream_t)stream);
+}
+int srt_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, void* stream) {
+  SRT_REQUIRE(dy && x && dx, "gelu_bwd: null argument");
+  return gelu_bwd(dy, x, dx, n, (cudaStream_t)stream);
+}
+int srt_causal_softmax_fwd(void* scores, int64_t Z, int S, void* stream) {
+  SRT_REQUIRE(scores, "causal_softmax_fwd: null argument");
+  return causal_softmax_fwd(scores, Z, S, (cudaStream_t)stream);
+}
+int srt_causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, void* stream) {
+  SRT_REQUIRE(P && dP, "causal_softmax_bwd: null argument");
+  return causal_softmax_bwd(P, dP, Z, S, (cudaStream_t)stream);
+}
+int srt_batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1,
+                          int Z2, void* stream) {
+  SRT_REQUIRE(in && out, "batched_transpose: null argument");
+  return batched_transpose(in, out, R, C, ld_in, s1, s2, Z1, Z2, (cudaStream_t)stream);
+}
+int srt_lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale,
+                         float* row_loss, void* stream) {
+  SRT_REQUIRE(logits && labels && row_loss, "lm_cross_entropy: null argument");
+  return lm_cross_entropy(logits, labels, rows, V, ld, grad_scale, row_loss, (cudaStream_t)stream);
+}
+
 }  // extern "C"

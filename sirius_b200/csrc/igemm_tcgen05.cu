@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 #include "conv_geom.cuh"
+#include "ops.cuh"
 #include "ptx.cuh"
 
 namespace srt {
@@ -751,6 +752,138 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Batched GEMM for attention: D[z][m][n] = alpha * sum_k A[z][m][k] * B[z][n][k], bf16 in, fp32
+// accumulate, bf16 out. z = (z1, z2) with independent strides per operand, so the heads of a fused
+// [tokens][3*hidden] projection are addressed in place through 4-D tensor maps (k, row, z1, z2).
+// One 128 x BN tile per CTA; warps 0-3 epilogue, warp 4 TMA, warp 5 MMA. `causal` skips tiles that
+// lie wholly above the diagonal (n > m); `k_causal` trims the reduction range of a tile when the
+// A operand is known to be zero beyond (1: k > m) or before (2: k < m) the diagonal.
+struct BgemmParams {
+  bf16* D;
+  int M, N, k_blocks;
+  int Z1;
+  long long ldd, d_s1, d_s2;
+  float alpha;
+  int causal, k_causal;
+  int* status;
+};
+
+template <int BN, int NS>
+__global__ void __launch_bounds__(NTHREADS)
+bgemm_kernel(const BgemmParams p, const __grid_constant__ CUtensorMap tmap_a,
+             const __grid_constant__ CUtensorMap tmap_b) {
+  pdl_enter();
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  if (p.causal && n0 >= m0 + BM) return;  // wholly above the diagonal: never read by the consumer
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout sm = carve_smem<NS, B_STAGE_BYTES>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int z1 = blockIdx.z % p.Z1, z2 = blockIdx.z / p.Z1;
+  int kb0 = 0, kb1 = p.k_blocks;
+  if (p.k_causal == 1) { const int lim = (m0 + BM + BK - 1) / BK; kb1 = kb1 < lim ? kb1 : lim; }
+  if (p.k_causal == 2) kb0 = m0 / BK < kb1 ? m0 / BK : kb1;
+  const int nkb = kb1 - kb0;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(smem_u32(&sm.full[s]), 1);
+      mbar_init(smem_u32(&sm.empty[s]), 1);
+    }
+    mbar_init(smem_u32(sm.tmem_full), 1);
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(sm.tmem_ptr), BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+
+  if (warp < 4) {
+    bool ready = true;
+    if (nkb > 0) {
+      ready = mbar_wait(smem_u32(sm.tmem_full), 0u, p.status, W_EPI_TMEM);
+      tc_fence_after_sync();
+    }
+    const int m = m0 + warp * 32 + lane;
+    bf16* drow = p.D + (long long)z1 * p.d_s1 + (long long)z2 * p.d_s2 + (long long)m * p.ldd;
+#pragma unroll 1
+    for (int cb = 0; cb < BN / 32; ++cb) {
+      uint32_t acc[32];
+      if (nkb > 0) {
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 32), acc);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[e] = 0u;
+      }
+      if (ready && m < p.M) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = n0 + cb * 32 + v * 8;
+          if (col < p.N) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]) * p.alpha;
+            Vec16<bf16> ov;
+            ov.pack(f);
+            ov.store(drow + col);
+          }
+        }
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % NS;
+        const uint32_t ph = (uint32_t)(i / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
+        const uint32_t bar = smem_u32(&sm.full[s]);
+        mbar_arrive_expect_tx(bar, (uint32_t)(A_STAGE_BYTES + B_STAGE_BYTES));
+        tma_load_4d(smem_u32(sm.a + s * A_STAGE_BYTES), &tmap_a, bar, (kb0 + i) * BK, m0, z1, z2);
+        tma_load_4d(smem_u32(sm.b + s * B_STAGE_BYTES), &tmap_b, bar, (kb0 + i) * BK, n0, z1, z2);
+      }
+    }
+  } else {
+    if (lane == 0 && nkb > 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % NS;
+        const uint32_t ph = (uint32_t)(i / NS) & 1u;
+        if (!mbar_wait(smem_u32(&sm.full[s]), ph, p.status, W_MMA_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a0 = smem_u32(sm.a + s * A_STAGE_BYTES);
+        const uint32_t b0 = smem_u32(sm.b + s * B_STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t ad = make_smem_desc_sw128(a0 + k * 32, 0, 1024);
+          const uint64_t bd = make_smem_desc_sw128(b0 + k * 32, 0, 1024);
+          umma_bf16(tmem_base, ad, bd, idesc, (i | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.empty[s]));
+      }
+      umma_commit(smem_u32(sm.tmem_full));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -893,7 +1026,74 @@ WgradPlan plan_wgrad(const GatherGeom& g) {
   return w;
 }
 
+// 4-D bf16 operand (k contiguous, then rows, then two batch dimensions), box = 64 x box_rows x 1 x 1.
+int make_tmap_4d(CUtensorMap* tm, const void* base, uint64_t kdim, uint64_t rows, uint64_t z1, uint64_t z2,
+                 uint64_t ld, uint64_t s1, uint64_t s2, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return SRT_ERR_CUDA;
+  }
+  SRT_REQUIRE(((uintptr_t)base & 15) == 0 && ld % 8 == 0 && s1 % 8 == 0 && s2 % 8 == 0,
+              "batched GEMM operand: base and strides must be 16-byte multiples");
+  cuuint64_t dims[4] = {kdim, rows, z1, z2};
+  cuuint64_t strides[3] = {ld * 2, (z1 > 1 ? s1 : ld * rows) * 2, (z2 > 1 ? s2 : ld * rows) * 2};
+  cuuint32_t box[4] = {64, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (4-D) failed with CUresult %d", (int)r);
+    return SRT_ERR_CUDA;
+  }
+  return SRT_OK;
+}
+
+template <int BN, int NS>
+int launch_bgemm(const BgemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, int zs, cudaStream_t st) {
+  constexpr size_t smem = smem_bytes<NS, BN * BK * 2>();
+  static bool configured = false;
+  if (!configured) {
+    SRT_CHECK_CUDA(cudaFuncSetAttribute(bgemm_kernel<BN, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid(ceil_div(p.M, BM), ceil_div(p.N, BN), zs);
+  launch_pdl_if(pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0, bgemm_kernel<BN, NS>, grid, dim3(NTHREADS), smem, st,
+                p, ta, tb);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
 }  // namespace
+
+int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaStream_t st) {
+  SRT_REQUIRE(d.M > 0 && d.N > 0 && d.K > 0 && d.Z1 > 0 && d.Z2 > 0, "bgemm: empty problem");
+  SRT_REQUIRE(d.K % 8 == 0 && d.N % 8 == 0 && d.ldd % 8 == 0 && d.d_s1 % 8 == 0 && d.d_s2 % 8 == 0 &&
+                  ((uintptr_t)D & 15) == 0,
+              "bgemm: K, N and the output strides must be multiples of 8 elements");
+  SRT_REQUIRE((long long)d.Z1 * d.Z2 <= 65535, "bgemm: more than 65535 batch entries");
+  BgemmParams p;
+  p.D = (bf16*)D;
+  p.M = d.M; p.N = d.N; p.k_blocks = ceil_div(d.K, BK);
+  p.Z1 = d.Z1;
+  p.ldd = d.ldd; p.d_s1 = d.d_s1; p.d_s2 = d.d_s2;
+  p.alpha = d.alpha;
+  p.causal = d.causal; p.k_causal = d.k_causal;
+  p.status = status_ptr();
+  SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
+  const int bn = d.N <= 64 ? 64 : 128;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_4d(&ta, A, (uint64_t)d.K, (uint64_t)d.M, (uint64_t)d.Z1, (uint64_t)d.Z2, (uint64_t)d.lda,
+                        (uint64_t)d.a_s1, (uint64_t)d.a_s2, (uint32_t)BM);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tb, B, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)d.Z1, (uint64_t)d.Z2, (uint64_t)d.ldb,
+                    (uint64_t)d.b_s1, (uint64_t)d.b_s2, (uint32_t)bn);
+  if (rc) return rc;
+  if (bn == 64) return launch_bgemm<64, 4>(p, ta, tb, d.Z1 * d.Z2, st);
+  return launch_bgemm<128, 3>(p, ta, tb, d.Z1 * d.Z2, st);
+}
+
 
 // Reads and clears the device status word of the tcgen05 kernels (synchronises the device).
 int tc_status_fetch(int* out) {

@@ -51,4 +51,38 @@ int conv_wgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, cons
                float* dw, void* scratch, size_t scratch_bytes, cudaStream_t st);
 size_t conv_wgrad_scratch_bytes(const srt_conv_desc& d, int dtype, int impl);
 
+
+// ---- transformer step ---------------------------------------------------------------------------------
+// Batched GEMM D[z][m][n] = alpha * sum_k A[z][m][k] * B[z][n][k] (bf16, fp32 accumulate, tcgen05), z = (z1, z2)
+// with per-operand element strides; see igemm_tcgen05.cu.
+struct BgemmDesc {
+  int M, N, K, Z1, Z2;
+  long long lda, a_s1, a_s2;
+  long long ldb, b_s1, b_s2;
+  long long ldd, d_s1, d_s2;
+  float alpha;
+  int causal;    // skip output tiles wholly above the diagonal (n > m)
+  int k_causal;  // 0 none; 1: A is zero for k > m; 2: A is zero for k < m (trims the reduction range per tile)
+};
+int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaStream_t st);
+
+int layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                  int64_t rows, int C, float eps, cudaStream_t st);
+size_t layernorm_bwd_scratch_bytes(int C);
+int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                  const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st);
+int gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t st);
+int gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st);
+int causal_softmax_fwd(void* scores, int64_t Z, int S, cudaStream_t st);
+int causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, cudaStream_t st);
+int batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1, int Z2,
+                      cudaStream_t st);
+int embedding_fwd(const int32_t* ids, const float* wte, const float* wpe, void* x, int64_t tokens, int S, int C,
+                  cudaStream_t st);
+int embedding_bwd(const void* dx, const int32_t* ids, const int32_t* order, const int32_t* seg, int n_unique, float* dwte,
+                  float* dwpe, int B, int S, int C, cudaStream_t st);
+int lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale, float* row_loss,
+                     cudaStream_t st);
+
 }  // namespace srt

@@ -1,0 +1,561 @@
+// Row-wise and elementwise kernels of the decoder-only transformer step (GPT-2 layout): LayerNorm,
+// GELU (tanh form), causal softmax, token/position embedding, next-token cross-entropy, batched
+// transposes for the attention products. bf16 activations, fp32 arithmetic and parameters.
+//
+// All of them are HBM-bound streaming passes: 16-byte vector accesses along the contiguous axis, one
+// warp per row with shuffle reductions for the row-wise ones, fixed-order (deterministic) partial sums
+// for the column reductions.
+#include "common.cuh"
+#include "ops.cuh"
+
+namespace srt {
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int NT = 256;
+constexpr int WARPS = NT / 32;
+
+__device__ inline float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ inline float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- LayerNorm ------------------------------------------------------------------------------------
+// y = (x - mean) * rstd * gamma + beta over the last axis (C % 8 == 0); one warp per row.
+__global__ void __launch_bounds__(NT)
+layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t rows, int C,
+                     float eps) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bf16* xr = x + row * C;
+  const int nv = C / 8;
+  float s = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a;
+    a.load(xr + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += f[e];
+  }
+  const float mu = warp_sum(s) / (float)C;
+  float q = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a;
+    a.load(xr + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { const float d = f[e] - mu; q = fmaf(d, d, q); }
+  }
+  const float rs = rsqrtf(warp_sum(q) / (float)C + eps);
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+  bf16* yr = y + row * C;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a;
+    a.load(xr + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = (f[e] - mu) * rs * gamma[v * 8 + e] + beta[v * 8 + e];
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(yr + v * 8);
+  }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * gamma; plus an optional addend (the gradient
+// that reaches x through the residual connection). One warp per row.
+__global__ void __launch_bounds__(NT)
+layernorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ gamma,
+                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                        const bf16* __restrict__ addend, bf16* __restrict__ dx, int64_t rows, int C) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bf16 *dr = dy + row * C, *xr = x + row * C;
+  const float mu = mean[row], rs = rstd[row];
+  const int nv = C / 8;
+  float sg = 0.f, sgx = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a, b;
+    a.load(dr + v * 8);
+    b.load(xr + v * 8);
+    float g[8], f[8];
+    a.unpack(g);
+    b.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ge = g[e] * gamma[v * 8 + e];
+      sg += ge;
+      sgx = fmaf(ge, (f[e] - mu) * rs, sgx);
+    }
+  }
+  const float mg = warp_sum(sg) / (float)C, mgx = warp_sum(sgx) / (float)C;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a, b;
+    a.load(dr + v * 8);
+    b.load(xr + v * 8);
+    float g[8], f[8], r[8];
+    a.unpack(g);
+    b.unpack(f);
+    if (addend) {
+      Vec16<bf16> c;
+      c.load(addend + row * C + v * 8);
+      c.unpack(r);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float xh = (f[e] - mu) * rs;
+      r[e] += rs * (g[e] * gamma[v * 8 + e] - mg - xh * mgx);
+    }
+    Vec16<bf16> o;
+    o.pack(r);
+    o.store(dx + row * C + v * 8);
+  }
+}
+
+// Column partials of (dy * xhat, dy): block b walks rows b, b + G, ...; thread t owns columns t, t + NT, ...
+// partial[(b * 2 + {0,1}) * C + c]. A second kernel adds the G partials in order.
+constexpr int LN_MAXCOL = 8;  // columns per thread: C <= NT * LN_MAXCOL
+__global__ void __launch_bounds__(NT)
+layernorm_bwd_param_partial(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ mean,
+                            const float* __restrict__ rstd, int64_t rows, int C, float* __restrict__ partial) {
+  pdl_enter();
+  float ag[LN_MAXCOL], ab[LN_MAXCOL];
+#pragma unroll
+  for (int i = 0; i < LN_MAXCOL; ++i) { ag[i] = 0.f; ab[i] = 0.f; }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+    for (int i = 0; i < LN_MAXCOL; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < C) {
+        const float g = __bfloat162float(dy[r * C + c]);
+        const float xh = (__bfloat162float(x[r * C + c]) - mu) * rs;
+        ag[i] = fmaf(g, xh, ag[i]);
+        ab[i] += g;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < LN_MAXCOL; ++i) {
+    const int c = threadIdx.x + i * NT;
+    if (c < C) {
+      partial[((size_t)blockIdx.x * 2 + 0) * C + c] = ag[i];
+      partial[((size_t)blockIdx.x * 2 + 1) * C + c] = ab[i];
+    }
+  }
+}
+__global__ void __launch_bounds__(NT)
+layernorm_bwd_param_final(const float* __restrict__ partial, int G, int C, float* __restrict__ dgamma,
+                          float* __restrict__ dbeta) {
+  pdl_enter();
+  const int c = blockIdx.x * NT + threadIdx.x;
+  if (c >= C) return;
+  float sg = 0.f, sb = 0.f;
+  for (int b = 0; b < G; ++b) {
+    sg += partial[((size_t)b * 2 + 0) * C + c];
+    sb += partial[((size_t)b * 2 + 1) * C + c];
+  }
+  dgamma[c] = sg;
+  dbeta[c] = sb;
+}
+
+// ---- GELU, tanh form ("gelu_new") -------------------------------------------------------------------
+__device__ inline float gelu_f(float x) {
+  const float k = 0.7978845608028654f;  // sqrt(2/pi)
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ inline float gelu_grad_f(float x) {
+  const float k = 0.7978845608028654f;
+  const float u = k * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x * x);
+}
+__global__ void __launch_bounds__(NT)
+gelu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int64_t nvec) {
+  pdl_enter();
+  for (int64_t v = (int64_t)blockIdx.x * NT + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * NT) {
+    Vec16<bf16> a;
+    a.load(x + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = gelu_f(f[e]);
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(y + v * 8);
+  }
+}
+__global__ void __launch_bounds__(NT)
+gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, int64_t nvec) {
+  pdl_enter();
+  for (int64_t v = (int64_t)blockIdx.x * NT + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * NT) {
+    Vec16<bf16> a, b;
+    a.load(dy + v * 8);
+    b.load(x + v * 8);
+    float g[8], f[8];
+    a.unpack(g);
+    b.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] *= gelu_grad_f(f[e]);
+    Vec16<bf16> o;
+    o.pack(g);
+    o.store(dx + v * 8);
+  }
+}
+
+// ---- causal softmax over [Z][S][S] scores, in place ---------------------------------------------------
+// Row r keeps columns 0..r; the rest of the row is written as zero (the tiles above the diagonal were never
+// produced by the score GEMM, and the products that follow read whole rows). One warp per row.
+__global__ void __launch_bounds__(NT)
+causal_softmax_fwd_kernel(bf16* __restrict__ s, int64_t total_rows, int S) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= total_rows) return;
+  const int r = (int)(row % S);
+  bf16* p = s + row * S;
+  const int nv = S / 8, lastv = r / 8;  // vectors 0..lastv hold valid columns
+  float mx = -INFINITY;
+  for (int v = lane; v <= lastv; v += 32) {
+    Vec16<bf16> a;
+    a.load(p + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if (v * 8 + e <= r) mx = fmaxf(mx, f[e]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int v = lane; v <= lastv; v += 32) {
+    Vec16<bf16> a;
+    a.load(p + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if (v * 8 + e <= r) sum += __expf(f[e] - mx);
+  }
+  const float inv = 1.f / warp_sum(sum);
+  for (int v = lane; v < nv; v += 32) {
+    float f[8];
+    if (v <= lastv) {
+      Vec16<bf16> a;
+      a.load(p + v * 8);
+      a.unpack(f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = v * 8 + e <= r ? __expf(f[e] - mx) * inv : 0.f;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(p + v * 8);
+  }
+}
+// dS = P * (dP - sum_j P_j dP_j) on the valid part of each row, zero elsewhere; in place over dP.
+__global__ void __launch_bounds__(NT)
+causal_softmax_bwd_kernel(const bf16* __restrict__ P, bf16* __restrict__ dP, int64_t total_rows, int S) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= total_rows) return;
+  const int r = (int)(row % S);
+  const bf16* p = P + row * S;
+  bf16* d = dP + row * S;
+  const int nv = S / 8, lastv = r / 8;
+  float dot = 0.f;
+  for (int v = lane; v <= lastv; v += 32) {
+    Vec16<bf16> a, b;
+    a.load(p + v * 8);
+    b.load(d + v * 8);
+    float pf[8], df[8];
+    a.unpack(pf);
+    b.unpack(df);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if (v * 8 + e <= r) dot = fmaf(pf[e], df[e], dot);
+  }
+  dot = warp_sum(dot);
+  for (int v = lane; v < nv; v += 32) {
+    float o[8];
+    if (v <= lastv) {
+      Vec16<bf16> a, b;
+      a.load(p + v * 8);
+      b.load(d + v * 8);
+      float pf[8], df[8];
+      a.unpack(pf);
+      b.unpack(df);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = v * 8 + e <= r ? pf[e] * (df[e] - dot) : 0.f;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+    }
+    Vec16<bf16> w;
+    w.pack(o);
+    w.store(d + v * 8);
+  }
+}
+
+// ---- batched transpose: out[z][c][r] = in[z][r][c] ----------------------------------------------------
+// in: row stride ld_in, batch strides (s1 for z1, s2 for z2), z = z2 * Z1 + z1; out: contiguous [Z][C][R].
+__global__ void __launch_bounds__(256)
+transpose_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int R, int C, int64_t ld_in, int64_t s1,
+                 int64_t s2, int Z1) {
+  pdl_enter();
+  __shared__ bf16 tile[32][33];
+  const int z = blockIdx.z, z1 = z % Z1, z2 = z / Z1;
+  const bf16* src = in + (int64_t)z1 * s1 + (int64_t)z2 * s2;
+  bf16* dst = out + (int64_t)z * R * C;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + ty + i * 8, c = c0 + tx;
+    if (r < R && c < C) tile[ty + i * 8][tx] = src[(int64_t)r * ld_in + c];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty + i * 8, r = r0 + tx;
+    if (r < R && c < C) dst[(int64_t)c * R + r] = tile[tx][ty + i * 8];
+  }
+}
+
+// ---- embedding ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NT)
+embedding_fwd_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wte, const float* __restrict__ wpe,
+                     bf16* __restrict__ x, int64_t tokens, int S, int C) {
+  pdl_enter();
+  const int nv = C / 8;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < tokens * nv; i += (int64_t)gridDim.x * NT) {
+    const int64_t t = i / nv;
+    const int v = (int)(i - t * nv);
+    const float* a = wte + (int64_t)ids[t] * C + v * 8;
+    const float* b = wpe + (int64_t)(t % S) * C + v * 8;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = a[e] + b[e];
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(x + t * C + v * 8);
+  }
+}
+// Position table gradient: dwpe[s][c] = sum over the batch, in batch order.
+__global__ void __launch_bounds__(NT)
+embedding_bwd_pos_kernel(const bf16* __restrict__ dx, float* __restrict__ dwpe, int B, int S, int C) {
+  pdl_enter();
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < (int64_t)S * C; i += (int64_t)gridDim.x * NT) {
+    float acc = 0.f;
+    for (int b = 0; b < B; ++b) acc += __bfloat162float(dx[(int64_t)b * S * C + i]);
+    dwpe[i] = acc;
+  }
+}
+// Token table gradient, added to what the tied output projection left there. `order` lists the token
+// positions sorted by token id (ties by position), seg[u]..seg[u+1] is the run of the u-th distinct id:
+// one block per distinct id adds its occurrences in that fixed order (deterministic, no atomics).
+__global__ void __launch_bounds__(NT)
+embedding_bwd_tok_kernel(const bf16* __restrict__ dx, const int32_t* __restrict__ ids, const int32_t* __restrict__ order,
+                         const int32_t* __restrict__ seg, int n_unique, float* __restrict__ dwte, int C) {
+  pdl_enter();
+  const int u = blockIdx.x;
+  if (u >= n_unique) return;
+  const int a = seg[u], b = seg[u + 1];
+  const int64_t tok = ids[order[a]];
+  for (int c = threadIdx.x; c < C; c += NT) {
+    float acc = 0.f;
+    for (int j = a; j < b; ++j) acc += __bfloat162float(dx[(int64_t)order[j] * C + c]);
+    dwte[tok * C + c] += acc;
+  }
+}
+
+// ---- next-token cross-entropy -------------------------------------------------------------------------
+// logits [rows][ld] (V valid columns); label[row] < 0 = no target (the last position of each sequence).
+// row_loss[row] = -log softmax(logits)[label]; logits are overwritten with (softmax - onehot) * grad_scale,
+// zero in rows without a target and in the padding columns. One block per row.
+__global__ void __launch_bounds__(NT)
+lm_cross_entropy_kernel(bf16* __restrict__ logits, const int32_t* __restrict__ labels, int V, int ld, float grad_scale,
+                        float* __restrict__ row_loss) {
+  pdl_enter();
+  __shared__ float red[WARPS];
+  __shared__ float bcast;
+  const int64_t row = blockIdx.x;
+  bf16* z = logits + row * ld;
+  const int label = labels[row];
+  const int nv = ld / 8, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (label < 0) {
+    for (int v = threadIdx.x; v < nv; v += NT) *reinterpret_cast<uint4*>(z + v * 8) = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    return;
+  }
+  float mx = -INFINITY;
+  for (int v = threadIdx.x; v < nv; v += NT) {
+    Vec16<bf16> a;
+    a.load(z + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if (v * 8 + e < V) mx = fmaxf(mx, f[e]);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[w] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) { float m = red[0]; for (int i = 1; i < WARPS; ++i) m = fmaxf(m, red[i]); bcast = m; }
+  __syncthreads();
+  mx = bcast;
+  __syncthreads();
+  float sum = 0.f;
+  for (int v = threadIdx.x; v < nv; v += NT) {
+    Vec16<bf16> a;
+    a.load(z + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if (v * 8 + e < V) sum += __expf(f[e] - mx);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) red[w] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < WARPS; ++i) t += red[i]; bcast = t; }
+  __syncthreads();
+  const float total = bcast;
+  const float inv = 1.f / total;
+  if (threadIdx.x == 0) row_loss[row] = logf(total) + mx - __bfloat162float(z[label]);
+  __syncthreads();  // the label's logit is read before anyone overwrites it
+  for (int v = threadIdx.x; v < nv; v += NT) {
+    Vec16<bf16> a;
+    a.load(z + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = v * 8 + e;
+      f[e] = c < V ? (__expf(f[e] - mx) * inv - (c == label ? 1.f : 0.f)) * grad_scale : 0.f;
+    }
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(z + v * 8);
+  }
+}
+
+inline unsigned rows_grid(int64_t rows) { return (unsigned)((rows + WARPS - 1) / WARPS); }
+inline unsigned stream_blocks(int64_t work_items) {
+  int64_t b = (work_items + NT - 1) / NT;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  return (unsigned)(b < 1 ? 1 : b > cap ? cap : b);
+}
+
+}  // namespace
+
+int layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                  int64_t rows, int C, float eps, cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && C % 8 == 0, "layernorm: C (%d) must be a multiple of 8", C);
+  launch_pdl(layernorm_fwd_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)x, gamma, beta, (bf16*)y, mean,
+             rstd, rows, C, eps);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+size_t layernorm_bwd_scratch_bytes(int C) { return (size_t)sm_count() * 2 * 2 * C * sizeof(float) + 256; }
+
+int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                  const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && C % 8 == 0 && C <= NT * LN_MAXCOL, "layernorm_bwd: C (%d) must be a multiple of 8, at most %d",
+              C, NT * LN_MAXCOL);
+  int G = 2 * sm_count();
+  if ((int64_t)G > rows) G = (int)rows;
+  SRT_REQUIRE(scratch && scratch_bytes >= (size_t)G * 2 * C * sizeof(float), "layernorm_bwd: scratch too small");
+  launch_pdl(layernorm_bwd_dx_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, gamma,
+             mean, rstd, (const bf16*)addend, (bf16*)dx, rows, C);
+  SRT_LAUNCH_CHECK();
+  launch_pdl(layernorm_bwd_param_partial, dim3(G), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, mean, rstd, rows, C,
+             (float*)scratch);
+  SRT_LAUNCH_CHECK();
+  launch_pdl(layernorm_bwd_param_final, dim3(ceil_div(C, NT)), dim3(NT), 0, st, (const float*)scratch, G, C, dgamma,
+             dbeta);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t st) {
+  SRT_REQUIRE(n > 0 && n % 8 == 0, "gelu: element count must be a multiple of 8");
+  launch_pdl(gelu_fwd_kernel, dim3(stream_blocks(n / 8)), dim3(NT), 0, st, (const bf16*)x, (bf16*)y, n / 8);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st) {
+  SRT_REQUIRE(n > 0 && n % 8 == 0, "gelu: element count must be a multiple of 8");
+  launch_pdl(gelu_bwd_kernel, dim3(stream_blocks(n / 8)), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, (bf16*)dx,
+             n / 8);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int causal_softmax_fwd(void* scores, int64_t Z, int S, cudaStream_t st) {
+  SRT_REQUIRE(Z > 0 && S % 8 == 0, "causal_softmax: S (%d) must be a multiple of 8", S);
+  launch_pdl(causal_softmax_fwd_kernel, dim3(rows_grid(Z * S)), dim3(NT), 0, st, (bf16*)scores, Z * S, S);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, cudaStream_t st) {
+  SRT_REQUIRE(Z > 0 && S % 8 == 0, "causal_softmax: S (%d) must be a multiple of 8", S);
+  launch_pdl(causal_softmax_bwd_kernel, dim3(rows_grid(Z * S)), dim3(NT), 0, st, (const bf16*)P, (bf16*)dP, Z * S, S);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1, int Z2,
+                      cudaStream_t st) {
+  SRT_REQUIRE(R > 0 && C > 0 && Z1 > 0 && Z2 > 0 && (int64_t)Z1 * Z2 <= 65535, "transpose: bad shape");
+  launch_pdl(transpose_kernel, dim3(ceil_div(C, 32), ceil_div(R, 32), Z1 * Z2), dim3(256), 0, st, (const bf16*)in,
+             (bf16*)out, R, C, ld_in, s1, s2, Z1);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int embedding_fwd(const int32_t* ids, const float* wte, const float* wpe, void* x, int64_t tokens, int S, int C,
+                  cudaStream_t st) {
+  SRT_REQUIRE(tokens > 0 && C % 8 == 0, "embedding: C must be a multiple of 8");
+  launch_pdl(embedding_fwd_kernel, dim3(stream_blocks(tokens * (C / 8))), dim3(NT), 0, st, ids, wte, wpe, (bf16*)x, tokens,
+             S, C);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int embedding_bwd(const void* dx, const int32_t* ids, const int32_t* order, const int32_t* seg, int n_unique, float* dwte,
+                  float* dwpe, int B, int S, int C, cudaStream_t st) {
+  launch_pdl(embedding_bwd_pos_kernel, dim3(stream_blocks((int64_t)S * C)), dim3(NT), 0, st, (const bf16*)dx, dwpe, B, S,
+             C);
+  SRT_LAUNCH_CHECK();
+  launch_pdl(embedding_bwd_tok_kernel, dim3(n_unique), dim3(NT), 0, st, (const bf16*)dx, ids, order, seg, n_unique, dwte,
+             C);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale, float* row_loss,
+                     cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && ld % 8 == 0 && V <= ld, "lm_cross_entropy: ld (%d) must be a multiple of 8 and >= V", ld);
+  launch_pdl(lm_cross_entropy_kernel, dim3((unsigned)rows), dim3(NT), 0, st, (bf16*)logits, labels, V, ld, grad_scale,
+             row_loss);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+}  // namespace srt

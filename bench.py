@@ -316,6 +316,137 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---- second workload: GPT-2 small (BASELINE config 4), selected with --workload gpt2 -----------------
+GPT2 = dict(n_layer=12, n_head=12, d_model=768, vocab=50257, ctx=1024)
+GPT2_BATCH, GPT2_SEQ = 8, 1024
+GPT2_FLOP_PER_TOKEN = 0.854e9  # forward + backward (torch.utils.flop_counter on the CPU model, 2 FLOP per MAC)
+
+
+def run_gpt2(args):
+    """GPT-2 small causal-LM training step, bf16, batch 8 x 1024 tokens per GPU, AdamW lr 3e-4; tokens/s."""
+    import torch
+    import torch.distributed as dist
+    from sirius_b200 import _lib, ops
+    from sirius_b200.gpt2_step import Gpt2Step
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
+    from transformers import GPT2Config, GPT2LMHeadModel
+    torch.manual_seed(0)
+    model = GPT2LMHeadModel(GPT2Config(vocab_size=GPT2["vocab"], n_positions=GPT2["ctx"], n_embd=GPT2["d_model"],
+                                       n_layer=GPT2["n_layer"], n_head=GPT2["n_head"], resid_pdrop=0.0, embd_pdrop=0.0,
+                                       attn_pdrop=0.0))
+    sd = {k: v for k, v in model.state_dict().items() if k.startswith("transformer.") and not k.endswith(".attn.bias")
+          and not k.endswith(".masked_bias")}
+    del model
+    step = Gpt2Step(**GPT2, max_batch=GPT2_BATCH, seq=GPT2_SEQ)
+    step.load_state_dict(sd)
+    stream = torch.cuda.ExternalStream(step.stream)
+    g = torch.Generator().manual_seed(1000 + rank)
+    host = [torch.randint(0, GPT2["vocab"], (GPT2_BATCH, GPT2_SEQ), generator=g, dtype=torch.int32) for _ in range(2)]
+    global_bs = GPT2_BATCH * world
+    grad_t = None
+    if world > 1:
+        ptr, n = step.grad_buffer()
+        grad_t = torch.as_tensor(_DevBuf(ptr, n), device=f"cuda:{local}")
+        with torch.cuda.stream(stream):
+            dist.all_reduce(grad_t)
+        torch.cuda.synchronize()
+
+    def one(i, upload):
+        if upload:
+            step.upload_tokens(host[i % 2])
+        step.forward_backward(global_bs)
+        if grad_t is not None:
+            with torch.cuda.stream(stream):
+                dist.all_reduce(grad_t)
+        step.optimizer_step()
+        return step.loss() if upload else None
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(upload, k):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(k):
+            one(i, upload)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    step.upload_tokens(host[0])
+    for i in range(max(args.warmup, 3)):
+        one(i, False)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.lib().srt_launch_count()
+    ms = timed(False, args.steps)
+    launches = _lib.lib().srt_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    tokens = global_bs * GPT2_SEQ * args.steps
+    value = tokens / (ms / 1e3)
+    ms_e2e = timed(True, args.steps)
+    e2e = tokens / (ms_e2e / 1e3)
+    peaks = load_peaks()
+    ach = value / world * GPT2_FLOP_PER_TOKEN / 1e12
+    out = {
+        "metric": "train tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "GPT-2 small causal-LM train step (fwd+bwd+AdamW), bf16, batch 8 x 1024 tokens per GPU, "
+                               "token ids uniform in [0, 50257)", "global_batch": global_bs, "seq_len": GPT2_SEQ,
+                   "parallelism": f"dp{world}", "optimizer": "AdamW lr 3e-4 wd 0.01", "init": "seeded (no pretrained weights)",
+                   "l2": "working set per step (GBs of activations and 0.8 GB of logits) exceeds the 126 MB L2"},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": GPT2_BATCH * GPT2_SEQ * 4 * 4,
+                "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e / args.steps, 3)},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": round(ach, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": round(ach / peaks["tflops"], 4), "kernel": "whole step (model FLOPs of all GEMMs)",
+                     "traffic": None, "peak_source": f"of {peaks['source']}"},
+        "tc_status": ops.tc_status(), "memory_gib": round(step.memory_bytes() / 2 ** 30, 2),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import gpt2_oracle as GO
+        torch.set_num_threads(os.cpu_count() or 1)
+        m = GO.build_model(**GPT2, seed=0)
+        ids = GO.make_tokens(1, GPT2_SEQ, GPT2["vocab"], 2)
+        opt = torch.optim.AdamW(m.parameters(), lr=3e-4)
+        secs = []
+        for b in ids:
+            t0 = time.perf_counter()
+            opt.zero_grad(set_to_none=True)
+            m(b, labels=b).loss.backward()
+            opt.step()
+            secs.append(time.perf_counter() - t0)
+        out["cpu_baseline"] = {"value": round(GPT2_SEQ / secs[-1], 1), "unit": "tokens/s", "cores": os.cpu_count(),
+                               "kind": "port", "sample": "1 timed step after 1 warm-up of batch 1 x 1024 tokens (fp32, "
+                               "same model and optimizer; the full workload is batch 8)", "sec_per_step": round(secs[-1], 3)}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    step.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def cpu_baseline(sample_batch, steps, warmup):
     """The reference's arithmetic path (stock torchvision ResNet-152 + PyTorch CPU fp32, SGD) timed
     on this box's host cores on a bounded sample of the workload."""
@@ -356,11 +487,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2"],
+                    help="resnet152 is the headline (BASELINE config 2); gpt2 reports tokens/s for config 4")
     ap.add_argument("--colocate-seconds", type=float, default=8.0,
                     help="length of the colocated training+inference window at N=1 (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "gpt2":
+        run_gpt2(args)
     else:
         run_ours(args)
 

@@ -325,6 +325,7 @@ int srt_gpt2_optimizer(srt_gpt2* g);
 int srt_gpt2_loss(srt_gpt2* g, float* host_loss);        /* synchronises; loss of the last micro-batch */
 int srt_gpt2_logits(srt_gpt2* g, float* host, int B);    /* [B*seq][vocab], after forward_only */
 int srt_gpt2_synchronize(srt_gpt2* g);
+int srt_gpt2_grad_buffer(srt_gpt2* g, void** ptr, int64_t* n); /* flat fp32 gradients, for the data-parallel all-reduce */
 void* srt_gpt2_stream(srt_gpt2* g);
 int64_t srt_gpt2_memory_bytes(srt_gpt2* g);
 int64_t srt_gpt2_num_elements(srt_gpt2* g);

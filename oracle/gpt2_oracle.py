@@ -40,7 +40,7 @@ def first_step_gradients(model, ids, autocast_bf16=False):
         loss = m(ids, labels=ids).loss
     loss.backward()
     grads = {k: p.grad.detach().float().numpy().copy() for k, p in m.named_parameters() if k.startswith("transformer.")}
-    return float(loss), grads
+    return float(loss.detach()), grads
 
 
 def train_steps(model, batches, lr=3e-4, weight_decay=0.01, autocast_bf16=False):
@@ -53,7 +53,7 @@ def train_steps(model, batches, lr=3e-4, weight_decay=0.01, autocast_bf16=False)
             loss = m(ids, labels=ids).loss
         loss.backward()
         opt.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     return losses, state_arrays(m)
 
 

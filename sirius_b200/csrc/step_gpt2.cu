@@ -463,6 +463,14 @@ int srt_gpt2_synchronize(srt_gpt2* h) {
   return SRT_OK;
 }
 
+int srt_gpt2_grad_buffer(srt_gpt2* h, void** ptr, int64_t* n) {
+  Gpt2* g = (Gpt2*)h;
+  SRT_REQUIRE(g && ptr && n, "gpt2_grad_buffer: null argument");
+  *ptr = g->G;
+  *n = (int64_t)g->n_flat;
+  return SRT_OK;
+}
+
 void* srt_gpt2_stream(srt_gpt2* h) { return h ? (void*)((Gpt2*)h)->stream : nullptr; }
 int64_t srt_gpt2_memory_bytes(srt_gpt2* h) { return h ? (int64_t)((Gpt2*)h)->bytes_total : -1; }
 int64_t srt_gpt2_num_elements(srt_gpt2* h) { return h ? (int64_t)((Gpt2*)h)->n_flat : -1; }

@@ -39,6 +39,7 @@ register({
     "srt_gpt2_loss": (None, [_vp, _pf]),
     "srt_gpt2_logits": (None, [_vp, _vp, _i]),
     "srt_gpt2_synchronize": (None, [_vp]),
+    "srt_gpt2_grad_buffer": (None, [_vp, C.POINTER(_vp), C.POINTER(_i64)]),
     "srt_gpt2_stream": (_vp, [_vp]),
     "srt_gpt2_memory_bytes": (_i64, [_vp]),
     "srt_gpt2_num_elements": (_i64, [_vp]),
@@ -133,6 +134,11 @@ class Gpt2Step:
     @property
     def stream(self) -> int:
         return _lib.lib().srt_gpt2_stream(self._h)
+
+    def grad_buffer(self):
+        p, n = _vp(), _i64()
+        call("srt_gpt2_grad_buffer", self._h, C.byref(p), C.byref(n))
+        return p.value, n.value
 
     def memory_bytes(self) -> int:
         return _lib.lib().srt_gpt2_memory_bytes(self._h)

@@ -42,3 +42,20 @@ def test_c1_fixture_is_complete():
     assert len(g["fp32"]["final"]) == 155 + 1 + 155 * 4 + 1
     # the reference's fp32 path is measurably inexact: the fixture records by how much
     assert abs(g["fp32"]["losses"][2] - g["fp64"]["losses"][2]) > 1e-2
+
+
+def test_gpt2_oracle_reproduces_the_committed_fixture():
+    """The GPT-2 oracle is pinned on its own committed output (the reference holds no vectors for this model):
+    same seeds, same losses and parameter digests as tests/golden/gpt2_tiny.json."""
+    import json
+    import pathlib
+    from oracle import gpt2_oracle as G
+    from oracle.resnet_oracle import summarize
+    doc = json.loads((pathlib.Path(__file__).parent / "golden" / "gpt2_tiny.json").read_text())
+    model = G.build_model(**doc["config"], seed=doc["seed"])
+    batches = G.make_tokens(doc["batch"], doc["seq"], doc["config"]["vocab"], doc["steps"], seed=doc["seed"])
+    losses, final = G.train_steps(model, batches)
+    assert np.allclose(losses, doc["fp32"]["losses"], rtol=1e-5)
+    dig = summarize(final, samples=4)
+    for k, d in doc["fp32"]["final"].items():
+        assert abs(dig[k]["l2"] - d["l2"]) <= 1e-5 * d["l2"] + 1e-9, k

@@ -354,6 +354,36 @@ int srt_batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in
 int srt_lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale,
                          float* row_loss, void* stream);
 
+/* ---- Swin transformer step -------------------------------------------------------------------------------
+ * torchvision.models.swin_b as the reference trains it (train/swin_b.py:38,83-95; AdamW in the DDP config).
+ * Parameters carry torchvision's state_dict names and shapes. Same call shape as the steps above. */
+typedef struct srt_swin srt_swin;
+typedef struct srt_swin_config {
+  int image, patch, embed;      /* Swin-B: 224, 4, 128 */
+  int depths[4], heads[4];      /* 2,2,18,2 and 4,8,16,32 */
+  int window, num_classes;      /* 7, 1000 */
+  int max_batch;
+  float lr, beta1, beta2, eps, weight_decay; /* AdamW */
+  float ln_eps;                 /* 1e-5 */
+} srt_swin_config;
+int srt_swin_create(const srt_swin_config* cfg, srt_swin** out);
+int srt_swin_destroy(srt_swin* s);
+int srt_swin_num_params(srt_swin* s);
+int srt_swin_param_info(srt_swin* s, int idx, char* name, int name_cap, int64_t shape[4], int* ndim);
+int srt_swin_set_param(srt_swin* s, int idx, const float* host);
+int srt_swin_get_param(srt_swin* s, int idx, float* host, int which);
+int srt_swin_commit_params(srt_swin* s);
+int srt_swin_upload_batch(srt_swin* s, const float* host_images /* NCHW fp32 */, const int64_t* host_labels, int B);
+int srt_swin_forward_backward(srt_swin* s, int B, int global_batch);
+int srt_swin_forward_only(srt_swin* s, int B);
+int srt_swin_optimizer(srt_swin* s);
+int srt_swin_loss(srt_swin* s, float* host_loss);
+int srt_swin_logits(srt_swin* s, float* host, int B);
+int srt_swin_synchronize(srt_swin* s);
+int srt_swin_grad_buffer(srt_swin* s, void** ptr, int64_t* n);
+void* srt_swin_stream(srt_swin* s);
+int64_t srt_swin_memory_bytes(srt_swin* s);
+
 #ifdef __cplusplus
 }
 #endif

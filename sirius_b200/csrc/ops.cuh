@@ -82,6 +82,21 @@ int embedding_fwd(const int32_t* ids, const float* wte, const float* wpe, void* 
                   cudaStream_t st);
 int embedding_bwd(const void* dx, const int32_t* ids, const int32_t* order, const int32_t* seg, int n_unique, float* dwte,
                   float* dwpe, int B, int S, int C, cudaStream_t st);
+int gelu_erf_fwd(const void* x, void* y, int64_t n, cudaStream_t st);
+int gelu_erf_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st);
+// Shifted-window attention (Swin): tokens in natural [B][Hs][Ws] order, windows of WS x WS, cyclic shift.
+struct WindowShape { int B, Hs, Ws, WS, shift; };
+int window_permute(const void* in, void* out, const WindowShape& w, int C, int to_natural, cudaStream_t st);
+int window_qkv(void* nat, void* qw, void* kw, void* vw, const WindowShape& w, int heads, int D, int to_natural,
+               cudaStream_t st);
+int relbias_build(const float* table, float* relbias, int heads, int WS, cudaStream_t st);
+int window_softmax_fwd(void* scores, const float* relbias, const WindowShape& w, int heads, int ld, cudaStream_t st);
+int window_softmax_bwd(const void* P, void* dP, int64_t Z, int L, int ld, cudaStream_t st);
+int relbias_grad(const void* dS, float* dbias_scratch, float* dtable, int64_t windows, int heads, int WS, int ld,
+                 cudaStream_t st);
+int patch_merge(const void* in, void* out, int B, int Hs, int Ws, int C, int inverse, cudaStream_t st);
+int transpose_pad(const void* in, void* out, int R, int C, int64_t ld_in, int64_t z_in, int64_t Z, int ld_out,
+                  cudaStream_t st);
 int lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale, float* row_loss,
                      cudaStream_t st);
 

@@ -454,6 +454,258 @@ lm_cross_entropy_kernel(bf16* __restrict__ logits, const int32_t* __restrict__ l
   }
 }
 
+// ---- GELU, erf form (torch.nn.GELU default) -------------------------------------------------------------
+__device__ inline float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.7071067811865476f)); }
+__device__ inline float gelu_erf_grad_f(float x) {
+  return 0.5f * (1.f + erff(x * 0.7071067811865476f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+__global__ void __launch_bounds__(NT)
+gelu_erf_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int64_t nvec) {
+  pdl_enter();
+  for (int64_t v = (int64_t)blockIdx.x * NT + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * NT) {
+    Vec16<bf16> a;
+    a.load(x + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = gelu_erf_f(f[e]);
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(y + v * 8);
+  }
+}
+__global__ void __launch_bounds__(NT)
+gelu_erf_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, int64_t nvec) {
+  pdl_enter();
+  for (int64_t v = (int64_t)blockIdx.x * NT + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * NT) {
+    Vec16<bf16> a, b;
+    a.load(dy + v * 8);
+    b.load(x + v * 8);
+    float g[8], f[8];
+    a.unpack(g);
+    b.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] *= gelu_erf_grad_f(f[e]);
+    Vec16<bf16> o;
+    o.pack(g);
+    o.store(dx + v * 8);
+  }
+}
+
+// ---- shifted-window attention helpers (Swin) ------------------------------------------------------------
+// Tokens live in the natural [B][Hs][Ws] order. A window of WS x WS tokens of the cyclically shifted map is
+// window (wy, wx), token (iy, ix): shifted position (wy*WS+iy, wx*WS+ix), natural position that plus `shift`
+// modulo the map size.
+struct WinGeom {
+  int B, Hs, Ws, WS, shift, nWy, nWx;
+};
+__device__ inline int64_t win_token_to_natural(const WinGeom& g, int64_t win, int tok) {
+  const int wx = (int)(win % g.nWx);
+  const int wy = (int)((win / g.nWx) % g.nWy);
+  const int64_t b = win / ((int64_t)g.nWx * g.nWy);
+  const int iy = tok / g.WS, ix = tok - iy * g.WS;
+  int h = wy * g.WS + iy + g.shift, w = wx * g.WS + ix + g.shift;
+  if (h >= g.Hs) h -= g.Hs;
+  if (w >= g.Ws) w -= g.Ws;
+  return (b * g.Hs + h) * g.Ws + w;
+}
+// dir 0: out_win[win][tok][c] = in_nat[natural][c]; dir 1: out_nat[natural][c] = in_win[win][tok][c]. C % 8 == 0.
+__global__ void __launch_bounds__(NT)
+window_permute_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, WinGeom g, int C, int dir) {
+  pdl_enter();
+  const int nv = C / 8, L = g.WS * g.WS;
+  const int64_t total = (int64_t)g.B * g.nWy * g.nWx * L * nv;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    const int v = (int)(i % nv);
+    const int64_t wt = i / nv;
+    const int tok = (int)(wt % L);
+    const int64_t win = wt / L;
+    const int64_t nat = win_token_to_natural(g, win, tok);
+    const int64_t a = wt * C + v * 8, b = nat * C + v * 8;
+    *reinterpret_cast<uint4*>(out + (dir ? b : a)) = *reinterpret_cast<const uint4*>(in + (dir ? a : b));
+  }
+}
+// Fused projection [tokens][3][heads][D] <-> per-head windowed Q, K, V [win][head][tok][D].
+// dir 0: natural -> windowed; dir 1: windowed -> natural (the gradient path).
+__global__ void __launch_bounds__(NT)
+window_qkv_kernel(bf16* __restrict__ nat, bf16* __restrict__ qw, bf16* __restrict__ kw, bf16* __restrict__ vw, WinGeom g,
+                  int heads, int D, int dir, int parts) {
+  pdl_enter();
+  const int dv = D / 8, L = g.WS * g.WS, C = heads * D;
+  const int64_t total = (int64_t)g.B * g.nWy * g.nWx * L * parts * heads * dv;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t r = i;
+    const int v = (int)(r % dv); r /= dv;
+    const int hd = (int)(r % heads); r /= heads;
+    const int part = (int)(r % parts); r /= parts;
+    const int tok = (int)(r % L);
+    const int64_t win = r / L;
+    const int64_t n = win_token_to_natural(g, win, tok);
+    bf16* natp = nat + n * parts * C + (int64_t)part * C + hd * D + v * 8;
+    bf16* w = (part == 0 ? qw : part == 1 ? kw : vw) + ((win * heads + hd) * L + tok) * D + v * 8;
+    if (dir == 0) *reinterpret_cast<uint4*>(w) = *reinterpret_cast<const uint4*>(natp);
+    else *reinterpret_cast<uint4*>(natp) = *reinterpret_cast<const uint4*>(w);
+  }
+}
+// relbias[head][i][j] = table[index(i, j)][head], index = (iy_i - iy_j + WS-1) * (2WS-1) + (ix_i - ix_j + WS-1)
+__device__ inline int relpos_index(int i, int j, int WS) {
+  const int iy = i / WS, ix = i - iy * WS, jy = j / WS, jx = j - jy * WS;
+  return (iy - jy + WS - 1) * (2 * WS - 1) + (ix - jx + WS - 1);
+}
+__global__ void __launch_bounds__(NT)
+relbias_build_kernel(const float* __restrict__ table, float* __restrict__ relbias, int heads, int WS) {
+  pdl_enter();
+  const int L = WS * WS;
+  for (int i = blockIdx.x * NT + threadIdx.x; i < heads * L * L; i += gridDim.x * NT) {
+    const int j = i % L, r = (i / L) % L, hd = i / (L * L);
+    relbias[i] = table[relpos_index(r, j, WS) * heads + hd];
+  }
+}
+__device__ inline int shift_region(int p, int size, int WS, int shift) {  // region of a shifted coordinate
+  return p < size - WS ? 0 : (p < size - shift ? 1 : 2);
+}
+// scores [Z][L][ld] (Z = windows * heads, head fastest): P = softmax(scores + relbias + mask) over the L valid
+// columns, columns L..ld-1 are written as zero. One warp per row.
+__global__ void __launch_bounds__(NT)
+window_softmax_fwd_kernel(bf16* __restrict__ s, const float* __restrict__ relbias, WinGeom g, int heads, int ld,
+                          int64_t total_rows) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31, L = g.WS * g.WS;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= total_rows) return;
+  const int i = (int)(row % L);
+  const int64_t z = row / L;
+  const int hd = (int)(z % heads);
+  const int64_t win = z / heads;
+  bf16* p = s + row * ld;
+  const float* rb = relbias + ((int64_t)hd * L + i) * L;
+  int reg_i = 0;
+  const int wx = (int)(win % g.nWx), wy = (int)((win / g.nWx) % g.nWy);
+  if (g.shift > 0) {
+    const int iy = i / g.WS, ix = i - iy * g.WS;
+    reg_i = shift_region(wy * g.WS + iy, g.Hs, g.WS, g.shift) * 3 + shift_region(wx * g.WS + ix, g.Ws, g.WS, g.shift);
+  }
+  float vals[4];  // L <= 128 columns per warp
+  float mx = -INFINITY;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int j = lane + 32 * t;
+    float v = -INFINITY;
+    if (j < L) {
+      v = __bfloat162float(p[j]) + rb[j];
+      if (g.shift > 0) {
+        const int jy = j / g.WS, jx = j - jy * g.WS;
+        const int reg_j = shift_region(wy * g.WS + jy, g.Hs, g.WS, g.shift) * 3 + shift_region(wx * g.WS + jx, g.Ws, g.WS, g.shift);
+        if (reg_j != reg_i) v += -100.f;
+      }
+      mx = fmaxf(mx, v);
+    }
+    vals[t] = v;
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int j = lane + 32 * t;
+    if (j < L) { vals[t] = __expf(vals[t] - mx); sum += vals[t]; }
+  }
+  const float inv = 1.f / warp_sum(sum);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int j = lane + 32 * t;
+    if (j < ld) p[j] = __float2bfloat16_rn(j < L ? vals[t] * inv : 0.f);
+  }
+}
+__global__ void __launch_bounds__(NT)
+window_softmax_bwd_kernel(const bf16* __restrict__ P, bf16* __restrict__ dP, int L, int ld, int64_t total_rows) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= total_rows) return;
+  const bf16* p = P + row * ld;
+  bf16* d = dP + row * ld;
+  float pv[4], dv[4], dot = 0.f;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int j = lane + 32 * t;
+    pv[t] = j < L ? __bfloat162float(p[j]) : 0.f;
+    dv[t] = j < L ? __bfloat162float(d[j]) : 0.f;
+    dot = fmaf(pv[t], dv[t], dot);
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int j = lane + 32 * t;
+    if (j < ld) d[j] = __float2bfloat16_rn(j < L ? pv[t] * (dv[t] - dot) : 0.f);
+  }
+}
+// Gradient of the relative-position table. Stage 1: sum dS over the windows for every (head, i, j), in window
+// order; stage 2: add the (i, j) pairs that share a table entry, in (i, j) order.
+__global__ void __launch_bounds__(64)
+relbias_grad_sum_kernel(const bf16* __restrict__ dS, float* __restrict__ dbias, int64_t windows, int heads, int L, int ld) {
+  pdl_enter();
+  const int i = blockIdx.x % L, hd = blockIdx.x / L, j = threadIdx.x;
+  if (j >= L) return;
+  float acc = 0.f;
+  for (int64_t w = 0; w < windows; ++w) acc += __bfloat162float(dS[((w * heads + hd) * L + i) * ld + j]);
+  dbias[((int64_t)hd * L + i) * L + j] = acc;
+}
+__global__ void __launch_bounds__(NT)
+relbias_grad_table_kernel(const float* __restrict__ dbias, float* __restrict__ dtable, int heads, int WS) {
+  pdl_enter();
+  const int L = WS * WS, n_entries = (2 * WS - 1) * (2 * WS - 1);
+  const int idx = blockIdx.x * NT + threadIdx.x;
+  if (idx >= n_entries * heads) return;
+  const int hd = idx % heads, t = idx / heads;
+  float acc = 0.f;
+  for (int i = 0; i < L; ++i)
+    for (int j = 0; j < L; ++j)
+      if (relpos_index(i, j, WS) == t) acc += dbias[((int64_t)hd * L + i) * L + j];
+  dtable[idx] = acc;
+}
+
+// Patch merging: out[b][h/2][w/2][part*C + c] = in[b][h][w][c], part = (w odd) * 2 + (h odd). dir 1 is the inverse.
+__global__ void __launch_bounds__(NT)
+patch_merge_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int B, int Hs, int Ws, int C, int dir) {
+  pdl_enter();
+  const int nv = C / 8;
+  const int64_t total = (int64_t)B * Hs * Ws * nv;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t r = i;
+    const int v = (int)(r % nv); r /= nv;
+    const int w = (int)(r % Ws); r /= Ws;
+    const int h = (int)(r % Hs);
+    const int64_t b = r / Hs;
+    const int part = (w & 1) * 2 + (h & 1);
+    const int64_t src = ((b * Hs + h) * Ws + w) * C + v * 8;
+    const int64_t dst = (((b * (Hs / 2) + h / 2) * (Ws / 2) + w / 2) * 4 + part) * (int64_t)C + v * 8;
+    *reinterpret_cast<uint4*>(out + (dir ? src : dst)) = *reinterpret_cast<const uint4*>(in + (dir ? dst : src));
+  }
+}
+
+// out[z][c][r] = in[z][r][c] with output row pitch ld_out >= R; the pad columns are written as zero.
+__global__ void __launch_bounds__(256)
+transpose_pad_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int R, int C, int64_t ld_in, int64_t z_in,
+                     int ld_out) {
+  pdl_enter();
+  __shared__ bf16 tile[32][33];
+  const bf16* src = in + (int64_t)blockIdx.z * z_in;
+  bf16* dst = out + (int64_t)blockIdx.z * C * ld_out;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + ty + i * 8, c = c0 + tx;
+    tile[ty + i * 8][tx] = (r < R && c < C) ? src[(int64_t)r * ld_in + c] : __float2bfloat16_rn(0.f);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty + i * 8, r = r0 + tx;
+    if (c < C && r < ld_out) dst[(int64_t)c * ld_out + r] = tile[tx][ty + i * 8];
+  }
+}
+
 inline unsigned rows_grid(int64_t rows) { return (unsigned)((rows + WARPS - 1) / WARPS); }
 inline unsigned stream_blocks(int64_t work_items) {
   int64_t b = (work_items + NT - 1) / NT;
@@ -555,6 +807,102 @@ int lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, i
   launch_pdl(lm_cross_entropy_kernel, dim3((unsigned)rows), dim3(NT), 0, st, (bf16*)logits, labels, V, ld, grad_scale,
              row_loss);
   SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+
+int gelu_erf_fwd(const void* x, void* y, int64_t n, cudaStream_t st) {
+  SRT_REQUIRE(n > 0 && n % 8 == 0, "gelu: element count must be a multiple of 8");
+  launch_pdl(gelu_erf_fwd_kernel, dim3(stream_blocks(n / 8)), dim3(NT), 0, st, (const bf16*)x, (bf16*)y, n / 8);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int gelu_erf_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st) {
+  SRT_REQUIRE(n > 0 && n % 8 == 0, "gelu: element count must be a multiple of 8");
+  launch_pdl(gelu_erf_bwd_kernel, dim3(stream_blocks(n / 8)), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x,
+             (bf16*)dx, n / 8);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+static WinGeom make_geom(const WindowShape& w) {
+  WinGeom g = {w.B, w.Hs, w.Ws, w.WS, w.shift, w.Hs / w.WS, w.Ws / w.WS};
+  return g;
+}
+static int check_geom(const WindowShape& w) {
+  SRT_REQUIRE(w.B > 0 && w.WS > 0 && w.Hs % w.WS == 0 && w.Ws % w.WS == 0 && w.shift >= 0 && w.shift < w.WS &&
+                  w.WS * w.WS <= 128,
+              "window attention: the map (%d x %d) must be a multiple of the window (%d), window area <= 128", w.Hs, w.Ws, w.WS);
+  return SRT_OK;
+}
+int window_permute(const void* in, void* out, const WindowShape& w, int C, int to_natural, cudaStream_t st) {
+  if (int rc = check_geom(w)) return rc;
+  SRT_REQUIRE(C % 8 == 0, "window_permute: C must be a multiple of 8");
+  const int64_t items = (int64_t)w.B * w.Hs * w.Ws * (C / 8);
+  launch_pdl(window_permute_kernel, dim3(stream_blocks(items)), dim3(NT), 0, st, (const bf16*)in, (bf16*)out, make_geom(w), C,
+             to_natural);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int window_qkv(void* nat, void* qw, void* kw, void* vw, const WindowShape& w, int heads, int D, int to_natural,
+               cudaStream_t st) {
+  if (int rc = check_geom(w)) return rc;
+  SRT_REQUIRE(D % 8 == 0, "window_qkv: head size must be a multiple of 8");
+  const int parts = kw ? 3 : 1;  // one tensor [tokens][heads*D] or the fused [tokens][3][heads*D]
+  const int64_t items = (int64_t)w.B * w.Hs * w.Ws * parts * heads * (D / 8);
+  launch_pdl(window_qkv_kernel, dim3(stream_blocks(items)), dim3(NT), 0, st, (bf16*)nat, (bf16*)qw, (bf16*)kw, (bf16*)vw,
+             make_geom(w), heads, D, to_natural, parts);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int relbias_build(const float* table, float* relbias, int heads, int WS, cudaStream_t st) {
+  launch_pdl(relbias_build_kernel, dim3(ceil_div(heads * WS * WS * WS * WS, NT)), dim3(NT), 0, st, table, relbias, heads, WS);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int window_softmax_fwd(void* scores, const float* relbias, const WindowShape& w, int heads, int ld, cudaStream_t st) {
+  if (int rc = check_geom(w)) return rc;
+  const int64_t rows = (int64_t)w.B * (w.Hs / w.WS) * (w.Ws / w.WS) * heads * w.WS * w.WS;
+  SRT_REQUIRE(ld >= w.WS * w.WS && ld <= 128, "window_softmax: bad row pitch %d", ld);
+  launch_pdl(window_softmax_fwd_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (bf16*)scores, relbias, make_geom(w), heads,
+             ld, rows);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int window_softmax_bwd(const void* P, void* dP, int64_t Z, int L, int ld, cudaStream_t st) {
+  SRT_REQUIRE(Z > 0 && L <= ld && ld <= 128, "window_softmax_bwd: bad shape");
+  launch_pdl(window_softmax_bwd_kernel, dim3(rows_grid(Z * L)), dim3(NT), 0, st, (const bf16*)P, (bf16*)dP, L, ld, Z * L);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int relbias_grad(const void* dS, float* dbias_scratch, float* dtable, int64_t windows, int heads, int WS, int ld,
+                 cudaStream_t st) {
+  const int L = WS * WS;
+  SRT_REQUIRE(L <= 64, "relbias_grad: window area above 64");
+  launch_pdl(relbias_grad_sum_kernel, dim3(heads * L), dim3(64), 0, st, (const bf16*)dS, dbias_scratch, windows, heads, L, ld);
+  SRT_LAUNCH_CHECK();
+  launch_pdl(relbias_grad_table_kernel, dim3(ceil_div((2 * WS - 1) * (2 * WS - 1) * heads, NT)), dim3(NT), 0, st,
+             (const float*)dbias_scratch, dtable, heads, WS);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int patch_merge(const void* in, void* out, int B, int Hs, int Ws, int C, int inverse, cudaStream_t st) {
+  SRT_REQUIRE(Hs % 2 == 0 && Ws % 2 == 0 && C % 8 == 0, "patch_merge: even map and C % 8 == 0 required");
+  launch_pdl(patch_merge_kernel, dim3(stream_blocks((int64_t)B * Hs * Ws * (C / 8))), dim3(NT), 0, st, (const bf16*)in,
+             (bf16*)out, B, Hs, Ws, C, inverse);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int transpose_pad(const void* in, void* out, int R, int C, int64_t ld_in, int64_t z_in, int64_t Z, int ld_out,
+                  cudaStream_t st) {
+  SRT_REQUIRE(R > 0 && C > 0 && Z > 0 && ld_out >= R, "transpose_pad: bad shape");
+  // z is spread over grid.z in chunks (the grid's z extent is limited to 65535)
+  for (int64_t z0 = 0; z0 < Z; z0 += 65535) {
+    const int64_t zn = Z - z0 < 65535 ? Z - z0 : 65535;
+    launch_pdl(transpose_pad_kernel, dim3(ceil_div(C, 32), ceil_div(ld_out, 32), (unsigned)zn), dim3(256), 0, st,
+               (const bf16*)in + z0 * z_in, (bf16*)out + z0 * C * ld_out, R, C, ld_in, z_in, ld_out);
+    SRT_LAUNCH_CHECK();
+  }
   return SRT_OK;
 }
 

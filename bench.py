@@ -447,6 +447,118 @@ def run_gpt2(args):
         dist.destroy_process_group()
 
 
+# ---- third workload: Swin-B (BASELINE config 3), selected with --workload swin_b ---------------------
+SWIN_BATCH = 32
+SWIN_FLOP_PER_SAMPLE = 92.55e9  # forward + backward (torch.utils.flop_counter on the CPU model)
+
+
+def run_swin(args):
+    """Swin-B training step, bf16, 32 images of 224 x 224 per GPU, AdamW lr 1e-3; samples/s."""
+    import torch
+    import torch.distributed as dist
+    from sirius_b200 import _lib, ops
+    from sirius_b200.swin_step import SWIN_B, SwinStep
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
+    from torchvision.models.swin_transformer import SwinTransformer
+    torch.manual_seed(0)
+    model = SwinTransformer(patch_size=[4, 4], embed_dim=128, depths=[2, 2, 18, 2], num_heads=[4, 8, 16, 32],
+                            window_size=[7, 7], stochastic_depth_prob=0.0, num_classes=1000)
+    sd = {k: v for k, v in model.state_dict().items() if not k.endswith("relative_position_index")}
+    del model
+    step = SwinStep(**SWIN_B, max_batch=SWIN_BATCH)
+    step.load_state_dict(sd)
+    stream = torch.cuda.ExternalStream(step.stream)
+    g = torch.Generator().manual_seed(1000 + rank)
+    host = [(torch.randn(SWIN_BATCH, 3, 224, 224, generator=g).pin_memory(),
+             torch.randint(0, 1000, (SWIN_BATCH,), generator=g).pin_memory()) for _ in range(2)]
+    global_bs = SWIN_BATCH * world
+    grad_t = None
+    if world > 1:
+        ptr, n = step.grad_buffer()
+        grad_t = torch.as_tensor(_DevBuf(ptr, n), device=f"cuda:{local}")
+        with torch.cuda.stream(stream):
+            dist.all_reduce(grad_t)
+        torch.cuda.synchronize()
+
+    def one(i, upload):
+        if upload:
+            step.upload_batch(*host[i % 2])
+        step.forward_backward(global_bs)
+        if grad_t is not None:
+            with torch.cuda.stream(stream):
+                dist.all_reduce(grad_t)
+        step.optimizer_step()
+        return step.loss() if upload else None
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(upload, k):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(k):
+            one(i, upload)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    step.upload_batch(*host[0])
+    for i in range(max(args.warmup, 3)):
+        one(i, False)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.lib().srt_launch_count()
+    ms = timed(False, args.steps)
+    launches = _lib.lib().srt_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    value = global_bs * args.steps / (ms / 1e3)
+    ms_e2e = timed(True, args.steps)
+    e2e = global_bs * args.steps / (ms_e2e / 1e3)
+    peaks = load_peaks()
+    ach = value / world * SWIN_FLOP_PER_SAMPLE / 1e12
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "Swin-B train step (fwd+bwd+AdamW), bf16, 32 images of 3x224x224 N(0,1) per GPU",
+                   "global_batch": global_bs, "per_gpu_batch": SWIN_BATCH, "parallelism": f"dp{world}",
+                   "optimizer": "AdamW lr 1e-3 wd 0.01", "init": "seeded (no pretrained weights)",
+                   "l2": "working set per step (GBs of activations) exceeds the 126 MB L2"},
+        "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": SWIN_BATCH * 3 * 224 * 224 * 4 + SWIN_BATCH * 8,
+                "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e / args.steps, 3)},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": round(ach, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": round(ach / peaks["tflops"], 4), "kernel": "whole step (model FLOPs of all GEMMs)",
+                     "traffic": None, "peak_source": f"of {peaks['source']}"},
+        "tc_status": ops.tc_status(), "memory_gib": round(step.memory_bytes() / 2 ** 30, 2),
+    }
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    step.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def cpu_baseline(sample_batch, steps, warmup):
     """The reference's arithmetic path (stock torchvision ResNet-152 + PyTorch CPU fp32, SGD) timed
     on this box's host cores on a bounded sample of the workload."""
@@ -487,8 +599,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2"],
-                    help="resnet152 is the headline (BASELINE config 2); gpt2 reports tokens/s for config 4")
+    ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2", "swin_b"],
+                    help="resnet152 is the headline (BASELINE config 2); gpt2 and swin_b report configs 4 and 3")
     ap.add_argument("--colocate-seconds", type=float, default=8.0,
                     help="length of the colocated training+inference window at N=1 (0 = skip)")
     args = ap.parse_args()
@@ -496,6 +608,8 @@ def main():
         run_reference(args)
     elif args.workload == "gpt2":
         run_gpt2(args)
+    elif args.workload == "swin_b":
+        run_swin(args)
     else:
         run_ours(args)
 

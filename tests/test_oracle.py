@@ -59,3 +59,20 @@ def test_gpt2_oracle_reproduces_the_committed_fixture():
     dig = summarize(final, samples=4)
     for k, d in doc["fp32"]["final"].items():
         assert abs(dig[k]["l2"] - d["l2"]) <= 1e-5 * d["l2"] + 1e-9, k
+
+
+def test_swin_oracle_reproduces_the_committed_fixture():
+    """Same pin for the Swin oracle: seeds in, committed losses and parameter digests out."""
+    import json
+    import pathlib
+    from oracle import swin_oracle as S
+    from oracle.resnet_oracle import summarize
+    doc = json.loads((pathlib.Path(__file__).parent / "golden" / "swin_tiny.json").read_text())
+    cfg = {k: tuple(v) if isinstance(v, list) else v for k, v in doc["config"].items()}
+    model = S.build_model(**cfg, seed=doc["seed"])
+    batches = S.make_batches(doc["batch"], doc["steps"], cfg["image"], cfg["num_classes"], seed=doc["seed"])
+    losses, final = S.train_steps(model, batches)
+    assert np.allclose(losses, doc["fp32"]["losses"], rtol=1e-4)
+    dig = summarize(final, samples=4)
+    for k, d in doc["fp32"]["final"].items():
+        assert abs(dig[k]["l2"] - d["l2"]) <= 1e-4 * d["l2"] + 1e-9, k

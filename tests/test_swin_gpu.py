@@ -67,3 +67,44 @@ def test_three_adamw_steps_track_the_oracle_and_repeat_bit_for_bit():
     losses2, params2 = run()
     assert losses2 == losses and all(np.array_equal(params2[n], params[n]) for n in params)
     assert ops.tc_status() == 0
+
+
+@pytest.mark.parametrize("case", ["swin_tiny", "swin_b_c3"])
+def test_against_the_committed_golden_fixture(case):
+    """Seeded weights and inputs against the digests the CPU oracle wrote (tests/golden/*.json). swin_b_c3 is
+    Swin-B at 32 images of 224 x 224."""
+    doc = json.loads((pathlib.Path(__file__).parent / "golden" / f"{case}.json").read_text())
+    cfg = {k: tuple(v) if isinstance(v, list) else v for k, v in doc["config"].items()}
+    B, steps, ref = doc["batch"], doc["steps"], doc["fp32"]
+    model = O.build_model(**cfg, seed=doc["seed"])
+    batches = O.make_batches(B, steps, cfg["image"], cfg["num_classes"], seed=doc["seed"])
+    step = SwinStep(**cfg, max_batch=B)
+    step.load_state_dict(O.state_arrays(model))
+    del model
+    losses = []
+    for i, (im, lb) in enumerate(batches):
+        step.upload_batch(im.contiguous(), lb.contiguous())
+        step.forward_backward()
+        if i == 0:
+            assert abs(step.loss() - ref["loss0"]) < 2e-2 * abs(ref["loss0"])
+            top = max(d["l2"] for d in ref["grad0"].values())
+            for n, d in ref["grad0"].items():
+                if d["l2"] < 1e-3 * top:
+                    continue
+                g = step.get(n, GET_GRAD).astype(np.float64)
+                assert abs(np.sqrt((g ** 2).sum()) - d["l2"]) < 6e-2 * d["l2"], (n, np.sqrt((g ** 2).sum()), d["l2"])
+        step.optimizer_step()
+        losses.append(step.loss())
+    for a, b in zip(losses, ref["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (losses, ref["losses"])
+    lr = doc["optimizer"]["lr"]
+    for n, d in ref["final"].items():
+        a = step.get(n).astype(np.float64).ravel()
+        l2 = float(np.sqrt((a ** 2).sum()))
+        drift = 2 * lr * steps * np.sqrt(a.size)      # what AdamW's sign-like first steps can add to a norm
+        assert abs(l2 - d["l2"]) <= 2e-2 * d["l2"] + drift, (n, l2, d["l2"])
+        scale = d["l2"] / np.sqrt(a.size)
+        for i, v in zip(d["idx"], d["val"]):
+            assert abs(a[i] - v) <= 2e-2 * max(abs(v), scale) + 2 * lr * steps * 1.01, (n, i, a[i], v)
+    assert ops.tc_status() == 0
+    step.close()

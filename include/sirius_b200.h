@@ -384,6 +384,35 @@ int srt_swin_grad_buffer(srt_swin* s, void** ptr, int64_t* n);
 void* srt_swin_stream(srt_swin* s);
 int64_t srt_swin_memory_bytes(srt_swin* s);
 
+/* ---- Qwen2 style decoder step ---------------------------------------------------------------------------
+ * transformers Qwen2ForCausalLM as the reference trains it (train/qwen.py:35-37,80-91): RMSNorm, rotary
+ * embedding, grouped-query attention, SwiGLU, tied embeddings. Parameters carry the reference's state_dict
+ * names and shapes (`lm_head.weight` is the tied token table). Same call shape as srt_gpt2_*. */
+typedef struct srt_qwen2 srt_qwen2;
+typedef struct srt_qwen2_config {
+  int n_layer, n_head, n_kv_head, hidden, intermediate, vocab; /* Qwen2-0.5B: 24, 14, 2, 896, 4864, 151936 */
+  int max_batch, seq;                                          /* seq a multiple of 128 */
+  float rope_theta, rms_eps;                                   /* 1e6, 1e-6 */
+  float lr, beta1, beta2, eps, weight_decay;                   /* AdamW */
+} srt_qwen2_config;
+int srt_qwen2_create(const srt_qwen2_config* cfg, srt_qwen2** out);
+int srt_qwen2_destroy(srt_qwen2* g);
+int srt_qwen2_num_params(srt_qwen2* g);
+int srt_qwen2_param_info(srt_qwen2* g, int idx, char* name, int name_cap, int64_t shape[2], int* ndim);
+int srt_qwen2_set_param(srt_qwen2* g, int idx, const float* host);
+int srt_qwen2_get_param(srt_qwen2* g, int idx, float* host, int which);
+int srt_qwen2_commit_params(srt_qwen2* g);
+int srt_qwen2_upload_tokens(srt_qwen2* g, const int32_t* host_ids, int B);
+int srt_qwen2_forward_backward(srt_qwen2* g, int B, int global_batch);
+int srt_qwen2_forward_only(srt_qwen2* g, int B);
+int srt_qwen2_optimizer(srt_qwen2* g);
+int srt_qwen2_loss(srt_qwen2* g, float* host_loss);
+int srt_qwen2_logits(srt_qwen2* g, float* host, int B);
+int srt_qwen2_synchronize(srt_qwen2* g);
+int srt_qwen2_grad_buffer(srt_qwen2* g, void** ptr, int64_t* n);
+void* srt_qwen2_stream(srt_qwen2* g);
+int64_t srt_qwen2_memory_bytes(srt_qwen2* g);
+
 #ifdef __cplusplus
 }
 #endif

@@ -762,7 +762,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
 struct BgemmParams {
   bf16* D;
   int M, N, k_blocks;
-  int Z1;
+  int Z1, b_div;  // b_div: the B operand's first batch coordinate is z1 / b_div (grouped KV heads)
   long long ldd, d_s1, d_s2;
   float alpha;
   int causal, k_causal;
@@ -849,7 +849,7 @@ bgemm_kernel(const BgemmParams p, const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t bar = smem_u32(&sm.full[s]);
         mbar_arrive_expect_tx(bar, (uint32_t)(A_STAGE_BYTES + B_STAGE_BYTES));
         tma_load_4d(smem_u32(sm.a + s * A_STAGE_BYTES), &tmap_a, bar, (kb0 + i) * BK, m0, z1, z2);
-        tma_load_4d(smem_u32(sm.b + s * B_STAGE_BYTES), &tmap_b, bar, (kb0 + i) * BK, n0, z1, z2);
+        tma_load_4d(smem_u32(sm.b + s * B_STAGE_BYTES), &tmap_b, bar, (kb0 + i) * BK, n0, z1 / p.b_div, z2);
       }
     }
   } else {
@@ -1077,6 +1077,8 @@ int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaSt
   p.D = (bf16*)D;
   p.M = d.M; p.N = d.N; p.k_blocks = ceil_div(d.K, BK);
   p.Z1 = d.Z1;
+  p.b_div = d.b_div > 1 ? d.b_div : 1;
+  SRT_REQUIRE(d.Z1 % p.b_div == 0, "bgemm: Z1 must be a multiple of b_div");
   p.ldd = d.ldd; p.d_s1 = d.d_s1; p.d_s2 = d.d_s2;
   p.alpha = d.alpha;
   p.causal = d.causal; p.k_causal = d.k_causal;
@@ -1087,7 +1089,7 @@ int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaSt
   int rc = make_tmap_4d(&ta, A, (uint64_t)d.K, (uint64_t)d.M, (uint64_t)d.Z1, (uint64_t)d.Z2, (uint64_t)d.lda,
                         (uint64_t)d.a_s1, (uint64_t)d.a_s2, (uint32_t)BM);
   if (rc) return rc;
-  rc = make_tmap_4d(&tb, B, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)d.Z1, (uint64_t)d.Z2, (uint64_t)d.ldb,
+  rc = make_tmap_4d(&tb, B, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)(d.Z1 / p.b_div), (uint64_t)d.Z2, (uint64_t)d.ldb,
                     (uint64_t)d.b_s1, (uint64_t)d.b_s2, (uint32_t)bn);
   if (rc) return rc;
   if (bn == 64) return launch_bgemm<64, 4>(p, ta, tb, d.Z1 * d.Z2, st);

@@ -63,11 +63,25 @@ struct BgemmDesc {
   float alpha;
   int causal;    // skip output tiles wholly above the diagonal (n > m)
   int k_causal;  // 0 none; 1: A is zero for k > m; 2: A is zero for k < m (trims the reduction range per tile)
+  int b_div = 1; // B's first batch coordinate is z1 / b_div: several A heads share one B head (grouped-query attention)
 };
 int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaStream_t st);
 
 int layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
                   int64_t rows, int C, float eps, cudaStream_t st);
+// RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma. Backward through layernorm_bwd with rms = 1 (mean holds zeros).
+int rmsnorm_fwd(const void* x, const float* gamma, void* y, float* mean, float* rstd, int64_t rows, int C, float eps,
+                cudaStream_t st);
+int rmsnorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, const void* addend,
+                void* dx, float* dgamma, int64_t rows, int C, void* scratch, size_t scratch_bytes, cudaStream_t st);
+// Rotary embedding on the heads of a [tokens][ld] matrix, in place: pairs (d, d + D/2) of every head are rotated by
+// pos * theta^(-2d/D); inverse = 1 applies the transposed rotation (the gradient).
+int rope_apply(void* x, int64_t tokens, int S, int heads, int D, int64_t ld, float theta, int inverse, cudaStream_t st);
+// SwiGLU: y = silu(gate) * up for gu = [tokens][2F] (gate first); backward writes d(gu).
+int swiglu_fwd(const void* gu, void* y, int64_t tokens, int F, cudaStream_t st);
+int swiglu_bwd(const void* dy, const void* gu, void* dgu, int64_t tokens, int F, cudaStream_t st);
+// out[t][g*D + d] = sum over the `group` heads of in[(b, g*group + j)][s][d]; in is [B][heads][S][D], out rows have pitch ld.
+int head_group_sum(const void* in, void* out, int B, int S, int heads, int group, int D, int64_t ld, cudaStream_t st);
 size_t layernorm_bwd_scratch_bytes(int C);
 int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                   const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,

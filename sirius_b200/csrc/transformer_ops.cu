@@ -32,7 +32,7 @@ __device__ inline float warp_max(float v) {
 __global__ void __launch_bounds__(NT)
 layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                      bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t rows, int C,
-                     float eps) {
+                     float eps, int rms) {
   pdl_enter();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
@@ -40,15 +40,17 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma
   const bf16* xr = x + row * C;
   const int nv = C / 8;
   float s = 0.f;
-  for (int v = lane; v < nv; v += 32) {
-    Vec16<bf16> a;
-    a.load(xr + v * 8);
-    float f[8];
-    a.unpack(f);
+  if (!rms) {
+    for (int v = lane; v < nv; v += 32) {
+      Vec16<bf16> a;
+      a.load(xr + v * 8);
+      float f[8];
+      a.unpack(f);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) s += f[e];
+      for (int e = 0; e < 8; ++e) s += f[e];
+    }
   }
-  const float mu = warp_sum(s) / (float)C;
+  const float mu = rms ? 0.f : warp_sum(s) / (float)C;
   float q = 0.f;
   for (int v = lane; v < nv; v += 32) {
     Vec16<bf16> a;
@@ -67,7 +69,7 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma
     float f[8];
     a.unpack(f);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = (f[e] - mu) * rs * gamma[v * 8 + e] + beta[v * 8 + e];
+    for (int e = 0; e < 8; ++e) f[e] = (f[e] - mu) * rs * gamma[v * 8 + e] + (beta ? beta[v * 8 + e] : 0.f);
     Vec16<bf16> o;
     o.pack(f);
     o.store(yr + v * 8);
@@ -79,7 +81,7 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ gamma
 __global__ void __launch_bounds__(NT)
 layernorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ gamma,
                         const float* __restrict__ mean, const float* __restrict__ rstd,
-                        const bf16* __restrict__ addend, bf16* __restrict__ dx, int64_t rows, int C) {
+                        const bf16* __restrict__ addend, bf16* __restrict__ dx, int64_t rows, int C, int rms) {
   pdl_enter();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
@@ -102,7 +104,7 @@ layernorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
       sgx = fmaf(ge, (f[e] - mu) * rs, sgx);
     }
   }
-  const float mg = warp_sum(sg) / (float)C, mgx = warp_sum(sgx) / (float)C;
+  const float mg = rms ? 0.f : warp_sum(sg) / (float)C, mgx = warp_sum(sgx) / (float)C;
   for (int v = lane; v < nv; v += 32) {
     Vec16<bf16> a, b;
     a.load(dr + v * 8);
@@ -348,10 +350,15 @@ embedding_fwd_kernel(const int32_t* __restrict__ ids, const float* __restrict__ 
     const int64_t t = i / nv;
     const int v = (int)(i - t * nv);
     const float* a = wte + (int64_t)ids[t] * C + v * 8;
-    const float* b = wpe + (int64_t)(t % S) * C + v * 8;
     float f[8];
+    if (wpe) {
+      const float* b = wpe + (int64_t)(t % S) * C + v * 8;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = a[e] + b[e];
+      for (int e = 0; e < 8; ++e) f[e] = a[e] + b[e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = a[e];
+    }
     Vec16<bf16> o;
     o.pack(f);
     o.store(x + t * C + v * 8);
@@ -706,6 +713,105 @@ transpose_pad_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int R,
   }
 }
 
+
+// ---- rotary embedding, SwiGLU, grouped-head sums (Qwen2 layout) ----------------------------------------------
+__global__ void __launch_bounds__(NT)
+rope_kernel(bf16* __restrict__ x, int64_t tokens, int S, int heads, int D, int64_t ld, float log_theta, int inverse) {
+  pdl_enter();
+  const int half = D / 2;
+  const int64_t total = tokens * heads * half;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    const int d = (int)(i % half);
+    const int hd = (int)((i / half) % heads);
+    const int64_t t = i / ((int64_t)half * heads);
+    const float ang = (float)(t % S) * __expf(-log_theta * (2.f * (float)d / (float)D));
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    if (inverse) sn = -sn;
+    bf16* p = x + t * ld + (int64_t)hd * D + d;
+    const float a = __bfloat162float(p[0]), b = __bfloat162float(p[half]);
+    p[0] = __float2bfloat16_rn(a * cs - b * sn);
+    p[half] = __float2bfloat16_rn(b * cs + a * sn);
+  }
+}
+__global__ void __launch_bounds__(NT)
+swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y, int64_t tokens, int F) {
+  pdl_enter();
+  const int nv = F / 8;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < tokens * nv; i += (int64_t)gridDim.x * NT) {
+    const int64_t t = i / nv;
+    const int v = (int)(i - t * nv);
+    Vec16<bf16> a, b;
+    a.load(gu + t * 2 * F + v * 8);
+    b.load(gu + t * 2 * F + F + v * 8);
+    float g[8], u[8];
+    a.unpack(g);
+    b.unpack(u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
+    Vec16<bf16> o;
+    o.pack(g);
+    o.store(y + t * F + v * 8);
+  }
+}
+__global__ void __launch_bounds__(NT)
+swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ gu, bf16* __restrict__ dgu, int64_t tokens, int F) {
+  pdl_enter();
+  const int nv = F / 8;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < tokens * nv; i += (int64_t)gridDim.x * NT) {
+    const int64_t t = i / nv;
+    const int v = (int)(i - t * nv);
+    Vec16<bf16> a, b, c;
+    a.load(gu + t * 2 * F + v * 8);
+    b.load(gu + t * 2 * F + F + v * 8);
+    c.load(dy + t * F + v * 8);
+    float g[8], u[8], d[8], dg[8], du[8];
+    a.unpack(g);
+    b.unpack(u);
+    c.unpack(d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sg = 1.f / (1.f + __expf(-g[e]));
+      const float silu = g[e] * sg;
+      du[e] = d[e] * silu;
+      dg[e] = d[e] * u[e] * (sg + silu * (1.f - sg));
+    }
+    Vec16<bf16> o1, o2;
+    o1.pack(dg);
+    o2.pack(du);
+    o1.store(dgu + t * 2 * F + v * 8);
+    o2.store(dgu + t * 2 * F + F + v * 8);
+  }
+}
+__global__ void __launch_bounds__(NT)
+head_group_sum_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int B, int S, int heads, int group, int D,
+                      int64_t ld) {
+  pdl_enter();
+  const int dv = D / 8, kvh = heads / group;
+  const int64_t total = (int64_t)B * S * kvh * dv;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t r = i;
+    const int v = (int)(r % dv); r /= dv;
+    const int g = (int)(r % kvh); r /= kvh;
+    const int s = (int)(r % S);
+    const int64_t b = r / S;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int j = 0; j < group; ++j) {
+      Vec16<bf16> a;
+      a.load(in + (((b * heads + g * group + j) * S + s) * (int64_t)D) + v * 8);
+      float f[8];
+      a.unpack(f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    Vec16<bf16> o;
+    o.pack(acc);
+    o.store(out + (b * S + s) * ld + (int64_t)g * D + v * 8);
+  }
+}
+
 inline unsigned rows_grid(int64_t rows) { return (unsigned)((rows + WARPS - 1) / WARPS); }
 inline unsigned stream_blocks(int64_t work_items) {
   int64_t b = (work_items + NT - 1) / NT;
@@ -719,23 +825,32 @@ int layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y,
                   int64_t rows, int C, float eps, cudaStream_t st) {
   SRT_REQUIRE(rows > 0 && C % 8 == 0, "layernorm: C (%d) must be a multiple of 8", C);
   launch_pdl(layernorm_fwd_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)x, gamma, beta, (bf16*)y, mean,
-             rstd, rows, C, eps);
+             rstd, rows, C, eps, 0);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 
-size_t layernorm_bwd_scratch_bytes(int C) { return (size_t)sm_count() * 2 * 2 * C * sizeof(float) + 256; }
+int rmsnorm_fwd(const void* x, const float* gamma, void* y, float* mean, float* rstd, int64_t rows, int C, float eps,
+                cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && C % 8 == 0, "rmsnorm: C (%d) must be a multiple of 8", C);
+  launch_pdl(layernorm_fwd_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)x, gamma, (const float*)nullptr,
+             (bf16*)y, mean, rstd, rows, C, eps, 1);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
 
-int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
-                  const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
-                  size_t scratch_bytes, cudaStream_t st) {
+size_t layernorm_bwd_scratch_bytes(int C) { return (size_t)sm_count() * 2 * 2 * C * sizeof(float) + (size_t)C * sizeof(float) + 256; }
+
+static int norm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                    const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                    size_t scratch_bytes, int rms, cudaStream_t st) {
   SRT_REQUIRE(rows > 0 && C % 8 == 0 && C <= NT * LN_MAXCOL, "layernorm_bwd: C (%d) must be a multiple of 8, at most %d",
               C, NT * LN_MAXCOL);
   int G = 2 * sm_count();
   if ((int64_t)G > rows) G = (int)rows;
   SRT_REQUIRE(scratch && scratch_bytes >= (size_t)G * 2 * C * sizeof(float), "layernorm_bwd: scratch too small");
   launch_pdl(layernorm_bwd_dx_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, gamma,
-             mean, rstd, (const bf16*)addend, (bf16*)dx, rows, C);
+             mean, rstd, (const bf16*)addend, (bf16*)dx, rows, C, rms);
   SRT_LAUNCH_CHECK();
   launch_pdl(layernorm_bwd_param_partial, dim3(G), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, mean, rstd, rows, C,
              (float*)scratch);
@@ -744,6 +859,20 @@ int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float
              dbeta);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
+}
+
+int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                  const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st) {
+  return norm_bwd(dy, x, gamma, mean, rstd, addend, dx, dgamma, dbeta, rows, C, scratch, scratch_bytes, 0, st);
+}
+// The column sums of dy (what would be d beta) land in the tail of the scratch and are dropped.
+int rmsnorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, const void* addend,
+                void* dx, float* dgamma, int64_t rows, int C, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  const size_t part = (size_t)2 * sm_count() * 2 * C * sizeof(float);
+  SRT_REQUIRE(scratch_bytes >= part + (size_t)C * sizeof(float), "rmsnorm_bwd: scratch too small");
+  float* dummy = (float*)((char*)scratch + part);
+  return norm_bwd(dy, x, gamma, mean, rstd, addend, dx, dgamma, dummy, rows, C, scratch, part, 1, st);
 }
 
 int gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t st) {
@@ -792,9 +921,11 @@ int embedding_fwd(const int32_t* ids, const float* wte, const float* wpe, void* 
 }
 int embedding_bwd(const void* dx, const int32_t* ids, const int32_t* order, const int32_t* seg, int n_unique, float* dwte,
                   float* dwpe, int B, int S, int C, cudaStream_t st) {
-  launch_pdl(embedding_bwd_pos_kernel, dim3(stream_blocks((int64_t)S * C)), dim3(NT), 0, st, (const bf16*)dx, dwpe, B, S,
-             C);
-  SRT_LAUNCH_CHECK();
+  if (dwpe) {  // models with a learned position table
+    launch_pdl(embedding_bwd_pos_kernel, dim3(stream_blocks((int64_t)S * C)), dim3(NT), 0, st, (const bf16*)dx, dwpe, B, S,
+               C);
+    SRT_LAUNCH_CHECK();
+  }
   launch_pdl(embedding_bwd_tok_kernel, dim3(n_unique), dim3(NT), 0, st, (const bf16*)dx, ids, order, seg, n_unique, dwte,
              C);
   SRT_LAUNCH_CHECK();
@@ -903,6 +1034,34 @@ int transpose_pad(const void* in, void* out, int R, int C, int64_t ld_in, int64_
                (const bf16*)in + z0 * z_in, (bf16*)out + z0 * C * ld_out, R, C, ld_in, z_in, ld_out);
     SRT_LAUNCH_CHECK();
   }
+  return SRT_OK;
+}
+
+int rope_apply(void* x, int64_t tokens, int S, int heads, int D, int64_t ld, float theta, int inverse, cudaStream_t st) {
+  SRT_REQUIRE(tokens > 0 && D % 2 == 0 && heads > 0, "rope: head size must be even");
+  launch_pdl(rope_kernel, dim3(stream_blocks(tokens * heads * (D / 2))), dim3(NT), 0, st, (bf16*)x, tokens, S, heads, D, ld,
+             logf(theta), inverse);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int swiglu_fwd(const void* gu, void* y, int64_t tokens, int F, cudaStream_t st) {
+  SRT_REQUIRE(tokens > 0 && F % 8 == 0, "swiglu: F must be a multiple of 8");
+  launch_pdl(swiglu_fwd_kernel, dim3(stream_blocks(tokens * (F / 8))), dim3(NT), 0, st, (const bf16*)gu, (bf16*)y, tokens, F);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int swiglu_bwd(const void* dy, const void* gu, void* dgu, int64_t tokens, int F, cudaStream_t st) {
+  SRT_REQUIRE(tokens > 0 && F % 8 == 0, "swiglu: F must be a multiple of 8");
+  launch_pdl(swiglu_bwd_kernel, dim3(stream_blocks(tokens * (F / 8))), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)gu,
+             (bf16*)dgu, tokens, F);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int head_group_sum(const void* in, void* out, int B, int S, int heads, int group, int D, int64_t ld, cudaStream_t st) {
+  SRT_REQUIRE(heads % group == 0 && D % 8 == 0, "head_group_sum: bad grouping");
+  launch_pdl(head_group_sum_kernel, dim3(stream_blocks((int64_t)B * S * (heads / group) * (D / 8))), dim3(NT), 0, st,
+             (const bf16*)in, (bf16*)out, B, S, heads, group, D, ld);
+  SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 

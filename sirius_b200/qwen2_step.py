@@ -1,0 +1,134 @@
+"""Qwen2 style decoder training step on the CUDA library: the loop body of the reference's `train/qwen.py:80-91`
+(`loss = model(ids, labels=ids).loss; loss.backward(); optimizer.step()`) as calls on one object."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import call, register
+
+_vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+
+class Qwen2ConfigC(C.Structure):
+    _fields_ = [("n_layer", _i), ("n_head", _i), ("n_kv_head", _i), ("hidden", _i), ("intermediate", _i), ("vocab", _i),
+                ("max_batch", _i), ("seq", _i), ("rope_theta", _f), ("rms_eps", _f), ("lr", _f), ("beta1", _f), ("beta2", _f),
+                ("eps", _f), ("weight_decay", _f)]
+
+
+register({
+    "srt_qwen2_create": (None, [C.POINTER(Qwen2ConfigC), C.POINTER(_vp)]),
+    "srt_qwen2_destroy": (None, [_vp]),
+    "srt_qwen2_num_params": (_i, [_vp]),
+    "srt_qwen2_param_info": (None, [_vp, _i, C.c_char_p, _i, C.POINTER(_i64), C.POINTER(_i)]),
+    "srt_qwen2_set_param": (None, [_vp, _i, _vp]),
+    "srt_qwen2_get_param": (None, [_vp, _i, _vp, _i]),
+    "srt_qwen2_commit_params": (None, [_vp]),
+    "srt_qwen2_upload_tokens": (None, [_vp, _vp, _i]),
+    "srt_qwen2_forward_backward": (None, [_vp, _i, _i]),
+    "srt_qwen2_forward_only": (None, [_vp, _i]),
+    "srt_qwen2_optimizer": (None, [_vp]),
+    "srt_qwen2_loss": (None, [_vp, C.POINTER(_f)]),
+    "srt_qwen2_logits": (None, [_vp, _vp, _i]),
+    "srt_qwen2_synchronize": (None, [_vp]),
+    "srt_qwen2_grad_buffer": (None, [_vp, C.POINTER(_vp), C.POINTER(_i64)]),
+    "srt_qwen2_stream": (_vp, [_vp]),
+    "srt_qwen2_memory_bytes": (_i64, [_vp]),
+})
+
+GET_VALUE, GET_GRAD, GET_MOMENTUM = 0, 1, 3
+QWEN2_05B = dict(n_layer=24, n_head=14, n_kv_head=2, hidden=896, intermediate=4864, vocab=151936)
+
+
+class Qwen2Step:
+    """`Qwen2Step(**QWEN2_05B, max_batch=4, seq=2048)`; parameters use the names and shapes of
+    `transformers.Qwen2ForCausalLM.state_dict()` (`lm_head.weight` is the tied token table and is not listed)."""
+
+    def __init__(self, n_layer=24, n_head=14, n_kv_head=2, hidden=896, intermediate=4864, vocab=151936, max_batch=4, seq=2048,
+                 rope_theta=1e6, rms_eps=1e-6, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01):
+        cfg = Qwen2ConfigC(n_layer, n_head, n_kv_head, hidden, intermediate, vocab, max_batch, seq, rope_theta, rms_eps, lr,
+                           betas[0], betas[1], eps, weight_decay)
+        self.cfg, self.seq, self.vocab, self.max_batch = cfg, seq, vocab, max_batch
+        self._h = _vp()
+        call("srt_qwen2_create", C.byref(cfg), C.byref(self._h))
+        self.params = {}
+        name, shape, ndim = C.create_string_buffer(256), (_i64 * 2)(), _i()
+        for i in range(_lib.lib().srt_qwen2_num_params(self._h)):
+            call("srt_qwen2_param_info", self._h, i, name, 256, shape, C.byref(ndim))
+            self.params[name.value.decode()] = (i, tuple(shape[:ndim.value]))
+
+    def close(self):
+        if self._h:
+            call("srt_qwen2_destroy", self._h)
+            self._h = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load_state_dict(self, sd) -> None:
+        for name, (idx, shape) in self.params.items():
+            a = np.ascontiguousarray(np.asarray(sd[name].detach().cpu().numpy() if hasattr(sd[name], "detach") else sd[name],
+                                                dtype=np.float32))
+            assert a.shape == shape, (name, a.shape, shape)
+            call("srt_qwen2_set_param", self._h, idx, a.ctypes.data_as(_vp))
+        call("srt_qwen2_commit_params", self._h)
+
+    def get(self, name, which=GET_VALUE) -> np.ndarray:
+        idx, shape = self.params[name]
+        out = np.empty(shape, dtype=np.float32)
+        call("srt_qwen2_get_param", self._h, idx, out.ctypes.data_as(_vp), which)
+        return out
+
+    def state_dict(self) -> dict:
+        return {n: self.get(n) for n in self.params}
+
+    def upload_tokens(self, ids) -> None:
+        a = np.ascontiguousarray(np.asarray(ids.cpu().numpy() if hasattr(ids, "cpu") else ids, dtype=np.int32))
+        assert a.ndim == 2 and a.shape[1] == self.seq and a.shape[0] <= self.max_batch, a.shape
+        self._B = a.shape[0]
+        call("srt_qwen2_upload_tokens", self._h, a.ctypes.data_as(_vp), self._B)
+
+    def forward_backward(self, global_batch=None) -> None:
+        call("srt_qwen2_forward_backward", self._h, self._B, global_batch or self._B)
+
+    def forward_only(self) -> None:
+        call("srt_qwen2_forward_only", self._h, self._B)
+
+    def optimizer_step(self) -> None:
+        call("srt_qwen2_optimizer", self._h)
+
+    def loss(self) -> float:
+        v = _f()
+        call("srt_qwen2_loss", self._h, C.byref(v))
+        return float(v.value)
+
+    def logits(self) -> np.ndarray:
+        out = np.empty((self._B * self.seq, self.vocab), dtype=np.float32)
+        call("srt_qwen2_logits", self._h, out.ctypes.data_as(_vp), self._B)
+        return out
+
+    def synchronize(self) -> None:
+        call("srt_qwen2_synchronize", self._h)
+
+    @property
+    def stream(self) -> int:
+        return _lib.lib().srt_qwen2_stream(self._h)
+
+    def grad_buffer(self):
+        p, n = _vp(), _i64()
+        call("srt_qwen2_grad_buffer", self._h, C.byref(p), C.byref(n))
+        return p.value, n.value
+
+    def memory_bytes(self) -> int:
+        return _lib.lib().srt_qwen2_memory_bytes(self._h)
+
+    def train_step(self, ids) -> float:
+        self.upload_tokens(ids)
+        self.forward_backward()
+        self.optimizer_step()
+        return self.loss()

@@ -90,8 +90,12 @@ int gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t st);
 int gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st);
 int causal_softmax_fwd(void* scores, int64_t Z, int S, cudaStream_t st);
 int causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, cudaStream_t st);
+// causal = 1: `in` is lower triangular and `out` feeds a GEMM with k_causal = 2; tiles that GEMM never reads are skipped.
 int batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1, int Z2,
-                      cudaStream_t st);
+                      cudaStream_t st, int causal = 0);
+// Column sums of a bf16 matrix, two-stage and deterministic (bias gradients): out[c] = sum_r dy[r][c].
+size_t colsum_scratch_bytes(int C);
+int colsum_bf16(const void* dy, int64_t rows, int C, float* out, void* scratch, size_t scratch_bytes, cudaStream_t st);
 int embedding_fwd(const int32_t* ids, const float* wte, const float* wpe, void* x, int64_t tokens, int S, int C,
                   cudaStream_t st);
 int embedding_bwd(const void* dx, const int32_t* ids, const int32_t* order, const int32_t* seg, int n_unique, float* dwte,

@@ -107,7 +107,7 @@ struct Gpt2 {
   // dx = dy W, dW = dy^T x, db = column sums of dy
   int linear_bwd(const Lin& l, const void* dy, const void* x, void* dx, int64_t T) {
     int rc;
-    if ((rc = colsum(SRT_BF16, dy, T, l.out, gf(l.b), stream))) return rc;
+    if ((rc = colsum_bf16(dy, T, l.out, gf(l.b), scratch, scratch_bytes, stream))) return rc;
     if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, gf(l.w), scratch, scratch_bytes, stream)))
       return rc;
     if (dx) return conv_dgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, WT + l.wt_off, dx, nullptr, stream);
@@ -173,6 +173,7 @@ int Gpt2::build() {
     return rc;
   // scratch: split partials of the largest filter gradient, LayerNorm column partials
   size_t sb = layernorm_bwd_scratch_bytes(C);
+  if (colsum_scratch_bytes(4 * C) > sb) sb = colsum_scratch_bytes(4 * C);
   auto wg = [&](int in, int out) {
     const size_t b = conv_wgrad_scratch_bytes(lin_desc((int64_t)T, in, out), SRT_BF16, SRT_IMPL_AUTO);
     if (b > sb) sb = b;
@@ -263,7 +264,7 @@ int Gpt2::backward(int B, int global_batch) {
                     S, (long long)S * S, (long long)H * S * S, 1.f, 1, 0};
     if ((rc = bgemm_bf16(dp, datt, y.qkv_o + 2 * C, dP, stream))) return rc;
     // dV = P^T dO
-    if ((rc = batched_transpose(y.Pm, Tbig, S, S, S, (long long)S * S, (long long)H * S * S, H, B, stream))) return rc;
+    if ((rc = batched_transpose(y.Pm, Tbig, S, S, S, (long long)S * S, (long long)H * S * S, H, B, stream, 1))) return rc;
     if ((rc = batched_transpose(datt, t1, S, D, C, D, (long long)S * C, H, B, stream))) return rc;
     BgemmDesc dv = {S, D, S, H, B, S, (long long)S * S, (long long)H * S * S, S, (long long)D * S, (long long)H * D * S,
                     3LL * C, D, (long long)S * 3 * C, 1.f, 0, 2};
@@ -276,7 +277,7 @@ int Gpt2::backward(int B, int global_batch) {
                     3LL * C, D, (long long)S * 3 * C, scale, 0, 1};
     if ((rc = bgemm_bf16(dq, dP, t1, dqkv, stream))) return rc;
     // dK = dS^T Q / sqrt(D)
-    if ((rc = batched_transpose(dP, Tbig, S, S, S, (long long)S * S, (long long)H * S * S, H, B, stream))) return rc;
+    if ((rc = batched_transpose(dP, Tbig, S, S, S, (long long)S * S, (long long)H * S * S, H, B, stream, 1))) return rc;
     if ((rc = batched_transpose(y.qkv_o, t2, S, D, 3LL * C, D, (long long)S * 3 * C, H, B, stream))) return rc;
     BgemmDesc dk = dq;
     dk.k_causal = 2;

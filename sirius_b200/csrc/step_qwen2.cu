@@ -99,7 +99,7 @@ struct Qwen2 {
   }
   int linear_bwd(const Lin& l, const void* dy, const void* x, void* dx, int64_t T) {
     int rc;
-    if (l.b_off >= 0 && (rc = colsum(SRT_BF16, dy, T, l.out, G + l.b_off, stream))) return rc;
+    if (l.b_off >= 0 && (rc = colsum_bf16(dy, T, l.out, G + l.b_off, scratch, scratch_bytes, stream))) return rc;
     if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, G + l.w_off, scratch, scratch_bytes, stream)))
       return rc;
     if (dx) return conv_dgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, WT + l.wt_off, dx, nullptr, stream);
@@ -171,6 +171,7 @@ int Qwen2::build() {
       (rc = act(&datt, T * Hq * D)) || (rc = act(&dln, T * C)))
     return rc;
   size_t sb = layernorm_bwd_scratch_bytes(C);
+  if (colsum_scratch_bytes(QKV) > sb) sb = colsum_scratch_bytes(QKV);
   auto wg = [&](int in, int out) {
     const size_t b = conv_wgrad_scratch_bytes(lin_desc((int64_t)T, in, out), SRT_BF16, SRT_IMPL_AUTO);
     if (b > sb) sb = b;
@@ -253,7 +254,7 @@ int Qwen2::backward(int B, int global_batch) {
     BgemmDesc dp = {S, S, D, Hq, B, KO, D, (long long)S * KO, QKV, D, (long long)S * QKV, S, SS, Hq * SS, 1.f, 1, 0, group};
     if ((rc = bgemm_bf16(dp, datt, y.qkv_o + VO, dP, stream))) return rc;
     // dV per query head = P^T dO, then summed over the heads of a group
-    if ((rc = batched_transpose(y.Pm, Tbig, S, S, S, SS, Hq * SS, Hq, B, stream))) return rc;
+    if ((rc = batched_transpose(y.Pm, Tbig, S, S, S, SS, Hq * SS, Hq, B, stream, 1))) return rc;
     if ((rc = batched_transpose(datt, t1, S, D, KO, D, (long long)S * KO, Hq, B, stream))) return rc;       // dO^T [B][Hq][D][S]
     BgemmDesc dv = {S, D, S, Hq, B, S, SS, Hq * SS, S, (long long)D * S, (long long)Hq * D * S, D, (long long)S * D,
                     (long long)Hq * S * D, 1.f, 0, 2, 1};
@@ -266,7 +267,7 @@ int Qwen2::backward(int B, int global_batch) {
                     scale, 0, 1, group};
     if ((rc = bgemm_bf16(dq, dP, t1, dqkv, stream))) return rc;
     // dK per query head = dS^T Q * scale, summed per group
-    if ((rc = batched_transpose(dP, Tbig, S, S, S, SS, Hq * SS, Hq, B, stream))) return rc;
+    if ((rc = batched_transpose(dP, Tbig, S, S, S, SS, Hq * SS, Hq, B, stream, 1))) return rc;
     if ((rc = batched_transpose(y.qkv_o, t2, S, D, QKV, D, (long long)S * QKV, Hq, B, stream))) return rc;        // Q^T [B][Hq][D][S]
     BgemmDesc dk = {S, D, S, Hq, B, S, SS, Hq * SS, S, (long long)D * S, (long long)Hq * D * S, D, (long long)S * D,
                     (long long)Hq * S * D, scale, 0, 2, 1};

@@ -116,7 +116,7 @@ struct Swin {
   }
   int linear_bwd(const Lin& l, const void* dy, const void* x, void* dx, int64_t T) {
     int rc;
-    if (l.b >= 0 && (rc = colsum(SRT_BF16, dy, T, l.out, gf(l.b), stream))) return rc;
+    if (l.b >= 0 && (rc = colsum_bf16(dy, T, l.out, gf(l.b), scratch, scratch_bytes, stream))) return rc;
     if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, gf(l.w), scratch, scratch_bytes, stream)))
       return rc;
     if (dx) return conv_dgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, WT + l.wt_off, dx, nullptr, stream);
@@ -223,6 +223,7 @@ int Swin::build() {
       (rc = act(&dg, 4 * maxTC)) || (rc = act(&datt, maxTC)) || (rc = act(&dln, 4 * maxTC)) || (rc = act(&ow, maxTC)))
     return rc;
   size_t sb = layernorm_bwd_scratch_bytes(4 * Cf);
+  if (colsum_scratch_bytes(4 * Cf) > sb) sb = colsum_scratch_bytes(4 * Cf);
   auto wg = [&](const srt_conv_desc& d) {
     const size_t b = conv_wgrad_scratch_bytes(d, SRT_BF16, SRT_IMPL_AUTO);
     if (b > sb) sb = b;
@@ -388,7 +389,7 @@ int Swin::backward(int B, int global_batch) {
   if ((rc = layernorm_bwd(dx, e0, pf(pe_ng), pe_m, pe_r, nullptr, dx_other, gf(pe_ng), gf(pe_nb), T0, cfg.embed, scratch,
                           scratch_bytes, stream)))
     return rc;
-  if ((rc = colsum(SRT_BF16, dx_other, T0, cfg.embed, gf(pe_b), stream))) return rc;
+  if ((rc = colsum_bf16(dx_other, T0, cfg.embed, gf(pe_b), scratch, scratch_bytes, stream))) return rc;
   return conv_wgrad(pe_desc(B), SRT_BF16, SRT_IMPL_AUTO, dx_other, x_img, gf(pe_w), scratch, scratch_bytes, stream);
 }
 

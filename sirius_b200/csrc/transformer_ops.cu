@@ -131,51 +131,74 @@ layernorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   }
 }
 
-// Column partials of (dy * xhat, dy): block b walks rows b, b + G, ...; thread t owns columns t, t + NT, ...
-// partial[(b * 2 + {0,1}) * C + c]. A second kernel adds the G partials in order.
-constexpr int LN_MAXCOL = 8;  // columns per thread: C <= NT * LN_MAXCOL
+// Column reductions over a [rows][C] bf16 matrix, deterministic and two-stage. MODE 0: sum of dy (bias gradients).
+// MODE 1: (sum of dy * xhat, sum of dy) with xhat = (x - mean[row]) * rstd[row] (LayerNorm / RMSNorm parameter gradients).
+// Stage 1: grid (ceil(C/256), slabs); a block is 32 vector lanes (8 columns each) x 8 row lanes and walks its slab of
+// rows with 16-byte loads; partial[(slab * NOUT + o) * C + c]. Stage 2 adds the slabs in order.
+constexpr int CR_MAX_SLABS = 600;
+template <int MODE>
 __global__ void __launch_bounds__(NT)
-layernorm_bwd_param_partial(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ mean,
-                            const float* __restrict__ rstd, int64_t rows, int C, float* __restrict__ partial) {
+colreduce_partial_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ mean,
+                         const float* __restrict__ rstd, int64_t rows, int C, int64_t rows_per_slab,
+                         float* __restrict__ partial) {
   pdl_enter();
-  float ag[LN_MAXCOL], ab[LN_MAXCOL];
+  constexpr int NOUT = MODE == 0 ? 1 : 2;
+  __shared__ float sh[NOUT][8][256 + 8];
+  const int vl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + vl * 8;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_slab;
+  const int64_t r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+  float a0[8], a1[8];
 #pragma unroll
-  for (int i = 0; i < LN_MAXCOL; ++i) { ag[i] = 0.f; ab[i] = 0.f; }
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float mu = mean[r], rs = rstd[r];
+  for (int e = 0; e < 8; ++e) { a0[e] = 0.f; a1[e] = 0.f; }
+  if (c0 < C) {
+    for (int64_t r = r0 + rl; r < r1; r += 8) {
+      Vec16<bf16> g;
+      g.load(dy + r * C + c0);
+      float gf[8];
+      g.unpack(gf);
+      if (MODE == 0) {
 #pragma unroll
-    for (int i = 0; i < LN_MAXCOL; ++i) {
-      const int c = threadIdx.x + i * NT;
-      if (c < C) {
-        const float g = __bfloat162float(dy[r * C + c]);
-        const float xh = (__bfloat162float(x[r * C + c]) - mu) * rs;
-        ag[i] = fmaf(g, xh, ag[i]);
-        ab[i] += g;
+        for (int e = 0; e < 8; ++e) a0[e] += gf[e];
+      } else {
+        Vec16<bf16> xv;
+        xv.load(x + r * C + c0);
+        float xf[8];
+        xv.unpack(xf);
+        const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { a0[e] = fmaf(gf[e], (xf[e] - mu) * rs, a0[e]); a1[e] += gf[e]; }
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < LN_MAXCOL; ++i) {
-    const int c = threadIdx.x + i * NT;
-    if (c < C) {
-      partial[((size_t)blockIdx.x * 2 + 0) * C + c] = ag[i];
-      partial[((size_t)blockIdx.x * 2 + 1) * C + c] = ab[i];
+  for (int e = 0; e < 8; ++e) {
+    sh[0][rl][vl * 8 + e] = a0[e];
+    if (NOUT == 2) sh[NOUT - 1][rl][vl * 8 + e] = a1[e];
+  }
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;  // one column per thread for the lane sum
+  if (c < C) {
+#pragma unroll
+    for (int o = 0; o < NOUT; ++o) {
+      float t = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t += sh[o][j][threadIdx.x];
+      partial[((size_t)blockIdx.y * NOUT + o) * C + c] = t;
     }
   }
 }
 __global__ void __launch_bounds__(NT)
-layernorm_bwd_param_final(const float* __restrict__ partial, int G, int C, float* __restrict__ dgamma,
-                          float* __restrict__ dbeta) {
+colreduce_final_kernel(const float* __restrict__ partial, int slabs, int nout, int C, float* __restrict__ out0,
+                       float* __restrict__ out1) {
   pdl_enter();
   const int c = blockIdx.x * NT + threadIdx.x;
   if (c >= C) return;
-  float sg = 0.f, sb = 0.f;
-  for (int b = 0; b < G; ++b) {
-    sg += partial[((size_t)b * 2 + 0) * C + c];
-    sb += partial[((size_t)b * 2 + 1) * C + c];
+  for (int o = 0; o < nout; ++o) {
+    float t = 0.f;
+    for (int b = 0; b < slabs; ++b) t += partial[((size_t)b * nout + o) * C + c];
+    (o == 0 ? out0 : out1)[c] = t;
   }
-  dgamma[c] = sg;
-  dbeta[c] = sb;
 }
 
 // ---- GELU, tanh form ("gelu_new") -------------------------------------------------------------------
@@ -319,8 +342,11 @@ causal_softmax_bwd_kernel(const bf16* __restrict__ P, bf16* __restrict__ dP, int
 // in: row stride ld_in, batch strides (s1 for z1, s2 for z2), z = z2 * Z1 + z1; out: contiguous [Z][C][R].
 __global__ void __launch_bounds__(256)
 transpose_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int R, int C, int64_t ld_in, int64_t s1,
-                 int64_t s2, int Z1) {
+                 int64_t s2, int Z1, int causal) {
   pdl_enter();
+  // causal: the input is lower triangular and the consumer of out (a GEMM whose reduction starts at the 128-aligned
+  // row block of each output tile) never reads out[c][r] with r below the 128-row block that holds c
+  if (causal && (int)blockIdx.y * 32 + 32 <= ((int)blockIdx.x * 32 / 128) * 128) return;
   __shared__ bf16 tile[32][33];
   const int z = blockIdx.z, z1 = z % Z1, z2 = z / Z1;
   const bf16* src = in + (int64_t)z1 * s1 + (int64_t)z2 * s2;
@@ -839,28 +865,48 @@ int rmsnorm_fwd(const void* x, const float* gamma, void* y, float* mean, float* 
   return SRT_OK;
 }
 
-size_t layernorm_bwd_scratch_bytes(int C) { return (size_t)sm_count() * 2 * 2 * C * sizeof(float) + (size_t)C * sizeof(float) + 256; }
+size_t layernorm_bwd_scratch_bytes(int C) { return (size_t)CR_MAX_SLABS * 2 * C * sizeof(float) + (size_t)C * sizeof(float) + 256; }
 
-static int norm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
-                    const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
-                    size_t scratch_bytes, int rms, cudaStream_t st) {
-  SRT_REQUIRE(rows > 0 && C % 8 == 0 && C <= NT * LN_MAXCOL, "layernorm_bwd: C (%d) must be a multiple of 8, at most %d",
-              C, NT * LN_MAXCOL);
-  int G = 2 * sm_count();
-  if ((int64_t)G > rows) G = (int)rows;
-  SRT_REQUIRE(scratch && scratch_bytes >= (size_t)G * 2 * C * sizeof(float), "layernorm_bwd: scratch too small");
-  launch_pdl(layernorm_bwd_dx_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, gamma,
-             mean, rstd, (const bf16*)addend, (bf16*)dx, rows, C, rms);
+// Two-stage column reduction front end (see colreduce_partial_kernel). mode 0: out0 = column sums of dy; mode 1: norm
+// parameter gradients (out0 = sum dy * xhat, out1 = sum dy).
+static int colreduce(int mode, const void* dy, const void* x, const float* mean, const float* rstd, int64_t rows, int C,
+                     float* out0, float* out1, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  const int gx = ceil_div(C, 256), nout = mode == 0 ? 1 : 2;
+  int64_t slabs = (int64_t)4 * sm_count() / gx;
+  if (slabs > CR_MAX_SLABS) slabs = CR_MAX_SLABS;
+  if (slabs > (rows + 63) / 64) slabs = (rows + 63) / 64;
+  if (slabs < 1) slabs = 1;
+  const int64_t per = (rows + slabs - 1) / slabs;
+  slabs = (rows + per - 1) / per;
+  SRT_REQUIRE(scratch && scratch_bytes >= (size_t)slabs * nout * C * sizeof(float), "column reduction: scratch too small");
+  if (mode == 0)
+    launch_pdl(colreduce_partial_kernel<0>, dim3(gx, (unsigned)slabs), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)nullptr,
+               (const float*)nullptr, (const float*)nullptr, rows, C, per, (float*)scratch);
+  else
+    launch_pdl(colreduce_partial_kernel<1>, dim3(gx, (unsigned)slabs), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, mean,
+               rstd, rows, C, per, (float*)scratch);
   SRT_LAUNCH_CHECK();
-  launch_pdl(layernorm_bwd_param_partial, dim3(G), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, mean, rstd, rows, C,
-             (float*)scratch);
-  SRT_LAUNCH_CHECK();
-  launch_pdl(layernorm_bwd_param_final, dim3(ceil_div(C, NT)), dim3(NT), 0, st, (const float*)scratch, G, C, dgamma,
-             dbeta);
+  launch_pdl(colreduce_final_kernel, dim3(ceil_div(C, NT)), dim3(NT), 0, st, (const float*)scratch, (int)slabs, nout, C, out0,
+             out1);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
 
+size_t colsum_scratch_bytes(int C) { return (size_t)CR_MAX_SLABS * C * sizeof(float) + 256; }
+int colsum_bf16(const void* dy, int64_t rows, int C, float* out, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && C % 8 == 0, "colsum: C (%d) must be a multiple of 8", C);
+  return colreduce(0, dy, nullptr, nullptr, nullptr, rows, C, out, nullptr, scratch, scratch_bytes, st);
+}
+
+static int norm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                    const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
+                    size_t scratch_bytes, int rms, cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && C % 8 == 0, "layernorm_bwd: C (%d) must be a multiple of 8", C);
+  launch_pdl(layernorm_bwd_dx_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, gamma,
+             mean, rstd, (const bf16*)addend, (bf16*)dx, rows, C, rms);
+  SRT_LAUNCH_CHECK();
+  return colreduce(1, dy, x, mean, rstd, rows, C, dgamma, dbeta, scratch, scratch_bytes, st);
+}
 int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                   const void* addend, void* dx, float* dgamma, float* dbeta, int64_t rows, int C, void* scratch,
                   size_t scratch_bytes, cudaStream_t st) {
@@ -869,7 +915,7 @@ int layernorm_bwd(const void* dy, const void* x, const float* gamma, const float
 // The column sums of dy (what would be d beta) land in the tail of the scratch and are dropped.
 int rmsnorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, const void* addend,
                 void* dx, float* dgamma, int64_t rows, int C, void* scratch, size_t scratch_bytes, cudaStream_t st) {
-  const size_t part = (size_t)2 * sm_count() * 2 * C * sizeof(float);
+  const size_t part = (size_t)CR_MAX_SLABS * 2 * C * sizeof(float);
   SRT_REQUIRE(scratch_bytes >= part + (size_t)C * sizeof(float), "rmsnorm_bwd: scratch too small");
   float* dummy = (float*)((char*)scratch + part);
   return norm_bwd(dy, x, gamma, mean, rstd, addend, dx, dgamma, dummy, rows, C, scratch, part, 1, st);
@@ -903,10 +949,10 @@ int causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, cudaStream_t s
 }
 
 int batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1, int Z2,
-                      cudaStream_t st) {
+                      cudaStream_t st, int causal) {
   SRT_REQUIRE(R > 0 && C > 0 && Z1 > 0 && Z2 > 0 && (int64_t)Z1 * Z2 <= 65535, "transpose: bad shape");
   launch_pdl(transpose_kernel, dim3(ceil_div(C, 32), ceil_div(R, 32), Z1 * Z2), dim3(256), 0, st, (const bf16*)in,
-             (bf16*)out, R, C, ld_in, s1, s2, Z1);
+             (bf16*)out, R, C, ld_in, s1, s2, Z1, causal);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

@@ -322,12 +322,29 @@ GPT2_BATCH, GPT2_SEQ = 8, 1024
 GPT2_FLOP_PER_TOKEN = 0.854e9  # forward + backward (torch.utils.flop_counter on the CPU model, 2 FLOP per MAC)
 
 
+QWEN2 = dict(n_layer=24, n_head=14, n_kv_head=2, hidden=896, intermediate=4864, vocab=151936)
+QWEN2_BATCH, QWEN2_SEQ = 4, 2048
+QWEN2_FLOP_PER_TOKEN = 2.964e9  # at 2048 tokens per sequence
+
+
 def run_gpt2(args):
-    """GPT-2 small causal-LM training step, bf16, batch 8 x 1024 tokens per GPU, AdamW lr 3e-4; tokens/s."""
+    return run_lm(args, "gpt2")
+
+
+def run_lm(args, kind):
+    """Causal-LM training step, bf16, AdamW lr 3e-4; tokens/s. kind: gpt2 (GPT-2 small, 8 x 1024 tokens per GPU) or
+    qwen2 (Qwen2-0.5B shape, 4 x 2048 tokens per GPU)."""
     import torch
     import torch.distributed as dist
     from sirius_b200 import _lib, ops
     from sirius_b200.gpt2_step import Gpt2Step
+    from sirius_b200.qwen2_step import Qwen2Step
+    if kind == "qwen2":
+        GPT2, GPT2_BATCH, GPT2_SEQ, GPT2_FLOP_PER_TOKEN = QWEN2, QWEN2_BATCH, QWEN2_SEQ, QWEN2_FLOP_PER_TOKEN
+        title = "Qwen2-0.5B-shaped decoder train step (fwd+bwd+AdamW), bf16, batch 4 x 2048 tokens per GPU, token ids uniform in [0, 151936)"
+    else:
+        GPT2, GPT2_BATCH, GPT2_SEQ, GPT2_FLOP_PER_TOKEN = globals()["GPT2"], globals()["GPT2_BATCH"], globals()["GPT2_SEQ"], globals()["GPT2_FLOP_PER_TOKEN"]
+        title = "GPT-2 small causal-LM train step (fwd+bwd+AdamW), bf16, batch 8 x 1024 tokens per GPU, token ids uniform in [0, 50257)"
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -338,15 +355,26 @@ def run_gpt2(args):
     if world > 1:
         import datetime
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
-    from transformers import GPT2Config, GPT2LMHeadModel
     torch.manual_seed(0)
-    model = GPT2LMHeadModel(GPT2Config(vocab_size=GPT2["vocab"], n_positions=GPT2["ctx"], n_embd=GPT2["d_model"],
-                                       n_layer=GPT2["n_layer"], n_head=GPT2["n_head"], resid_pdrop=0.0, embd_pdrop=0.0,
-                                       attn_pdrop=0.0))
-    sd = {k: v for k, v in model.state_dict().items() if k.startswith("transformer.") and not k.endswith(".attn.bias")
-          and not k.endswith(".masked_bias")}
-    del model
-    step = Gpt2Step(**GPT2, max_batch=GPT2_BATCH, seq=GPT2_SEQ)
+    if kind == "qwen2":
+        from transformers import Qwen2Config, Qwen2ForCausalLM
+        model = Qwen2ForCausalLM(Qwen2Config(vocab_size=GPT2["vocab"], hidden_size=GPT2["hidden"],
+                                             intermediate_size=GPT2["intermediate"], num_hidden_layers=GPT2["n_layer"],
+                                             num_attention_heads=GPT2["n_head"], num_key_value_heads=GPT2["n_kv_head"],
+                                             max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6,
+                                             tie_word_embeddings=True, use_sliding_window=False))
+        sd = {k: v for k, v in model.state_dict().items() if k.startswith("model.")}
+        del model
+        step = Qwen2Step(**GPT2, max_batch=GPT2_BATCH, seq=GPT2_SEQ)
+    else:
+        from transformers import GPT2Config, GPT2LMHeadModel
+        model = GPT2LMHeadModel(GPT2Config(vocab_size=GPT2["vocab"], n_positions=GPT2["ctx"], n_embd=GPT2["d_model"],
+                                           n_layer=GPT2["n_layer"], n_head=GPT2["n_head"], resid_pdrop=0.0, embd_pdrop=0.0,
+                                           attn_pdrop=0.0))
+        sd = {k: v for k, v in model.state_dict().items() if k.startswith("transformer.") and not k.endswith(".attn.bias")
+              and not k.endswith(".masked_bias")}
+        del model
+        step = Gpt2Step(**GPT2, max_batch=GPT2_BATCH, seq=GPT2_SEQ)
     step.load_state_dict(sd)
     stream = torch.cuda.ExternalStream(step.stream)
     g = torch.Generator().manual_seed(1000 + rank)
@@ -411,8 +439,7 @@ def run_gpt2(args):
         "metric": "train tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "GPT-2 small causal-LM train step (fwd+bwd+AdamW), bf16, batch 8 x 1024 tokens per GPU, "
-                               "token ids uniform in [0, 50257)", "global_batch": global_bs, "seq_len": GPT2_SEQ,
+        "config": {"workload": title, "global_batch": global_bs, "seq_len": GPT2_SEQ,
                    "parallelism": f"dp{world}", "optimizer": "AdamW lr 3e-4 wd 0.01", "init": "seeded (no pretrained weights)",
                    "l2": "working set per step (GBs of activations and 0.8 GB of logits) exceeds the 126 MB L2"},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": GPT2_BATCH * GPT2_SEQ * 4 * 4,
@@ -423,7 +450,7 @@ def run_gpt2(args):
                      "traffic": None, "peak_source": f"of {peaks['source']}"},
         "tc_status": ops.tc_status(), "memory_gib": round(step.memory_bytes() / 2 ** 30, 2),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and kind == "gpt2":
         from oracle import gpt2_oracle as GO
         torch.set_num_threads(os.cpu_count() or 1)
         m = GO.build_model(**GPT2, seed=0)
@@ -599,8 +626,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2", "swin_b"],
-                    help="resnet152 is the headline (BASELINE config 2); gpt2 and swin_b report configs 4 and 3")
+    ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2", "swin_b", "qwen2"],
+                    help="resnet152 is the headline (BASELINE config 2); swin_b, gpt2 and qwen2 report configs 3, 4 and 5")
     ap.add_argument("--colocate-seconds", type=float, default=8.0,
                     help="length of the colocated training+inference window at N=1 (0 = skip)")
     args = ap.parse_args()
@@ -610,6 +637,8 @@ def main():
         run_gpt2(args)
     elif args.workload == "swin_b":
         run_swin(args)
+    elif args.workload == "qwen2":
+        run_lm(args, "qwen2")
     else:
         run_ours(args)
 

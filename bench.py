@@ -345,6 +345,9 @@ def run_lm(args, kind):
     else:
         GPT2, GPT2_BATCH, GPT2_SEQ, GPT2_FLOP_PER_TOKEN = globals()["GPT2"], globals()["GPT2_BATCH"], globals()["GPT2_SEQ"], globals()["GPT2_FLOP_PER_TOKEN"]
         title = "GPT-2 small causal-LM train step (fwd+bwd+AdamW), bf16, batch 8 x 1024 tokens per GPU, token ids uniform in [0, 50257)"
+    if args.lm_batch > 0:
+        title = title.replace(f"batch {GPT2_BATCH} x", f"batch {args.lm_batch} x")
+        GPT2_BATCH = args.lm_batch
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -626,6 +629,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lm-batch", type=int, default=0,
+                    help="sequences per GPU for the gpt2 / qwen2 workloads (0 = the configuration's own; smaller for profiling)")
     ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2", "swin_b", "qwen2"],
                     help="resnet152 is the headline (BASELINE config 2); swin_b, gpt2 and qwen2 report configs 3, 4 and 5")
     ap.add_argument("--colocate-seconds", type=float, default=8.0,

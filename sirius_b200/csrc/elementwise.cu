@@ -384,6 +384,64 @@ __global__ void filter_transpose_kernel(const T* __restrict__ w, T* __restrict__
   }
 }
 
+
+// Stride-2 data gradient by output parity. sub[c][t][k] = wt[c][taps[t]][k]: the filter taps that reach one
+// parity class of output pixels, in the order the class's stride-1 gather walks them.
+struct TapList { int n; int rs[4]; };
+template <typename T>
+__global__ void subfilter_kernel(const T* __restrict__ wt, T* __restrict__ sub, int C, int K, int RS, TapList taps) {
+  pdl_enter();
+  constexpr int V = Vec16<T>::N;
+  const int kv = K / V;
+  const int64_t total = (int64_t)C * taps.n * kv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % kv);
+    const int t = (int)((i / kv) % taps.n);
+    const int64_t c = i / ((int64_t)kv * taps.n);
+    Vec16<T> a;
+    a.load(wt + (c * RS + taps.rs[t]) * K + v * V);
+    a.store(sub + (c * taps.n + t) * K + v * V);
+  }
+}
+// dx[n][h][w][:] = class(h & 1, w & 1)[n][h / 2][w / 2][:] (+ addend); a null class contributes zero.
+template <typename T>
+__global__ void parity_interleave_kernel(const T* __restrict__ c00, const T* __restrict__ c01, const T* __restrict__ c10,
+                                         const T* __restrict__ c11, const T* __restrict__ addend, T* __restrict__ dx, int N,
+                                         int H, int W, int C) {
+  pdl_enter();
+  constexpr int V = Vec16<T>::N;
+  const int cv = C / V;
+  const int64_t total = (int64_t)N * H * W * cv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i;
+    const int v = (int)(r % cv); r /= cv;
+    const int w = (int)(r % W); r /= W;
+    const int h = (int)(r % H);
+    const int64_t n = r / H;
+    const T* src = (h & 1) ? ((w & 1) ? c11 : c10) : ((w & 1) ? c01 : c00);
+    float f[V];
+    if (src) {
+      Vec16<T> a;
+      a.load(src + (((n * (H / 2) + h / 2) * (W / 2) + w / 2) * (int64_t)C) + v * V);
+      a.unpack(f);
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) f[e] = 0.f;
+    }
+    if (addend) {
+      Vec16<T> b;
+      b.load(addend + i * V);
+      float g[V];
+      b.unpack(g);
+#pragma unroll
+      for (int e = 0; e < V; ++e) f[e] += g[e];
+    }
+    Vec16<T> o;
+    o.pack(f);
+    o.store(dx + i * V);
+  }
+}
+
 }  // namespace
 
 #define DISPATCH_T(dtype, ...)                                   \
@@ -516,6 +574,31 @@ int filter_transpose(int dtype, const void* w, void* wt, int K, int RS, int C, c
   dim3 grid(ceil_div(C, 32), ceil_div(K, 32), RS);
   DISPATCH_T(dtype, {
     launch_pdl(filter_transpose_kernel<T>, dim3(grid), dim3(dim3(32, 8)), 0, st, (const T*)w, (T*)wt, K, RS, C);
+  });
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int subfilter(int dtype, const void* wt, void* sub, int C, int K, int RS, const int* taps, int ntaps, cudaStream_t st) {
+  SRT_REQUIRE(ntaps >= 1 && ntaps <= 4 && K % 8 == 0, "subfilter: 1..4 taps, K a multiple of 8");
+  TapList tl;
+  tl.n = ntaps;
+  for (int i = 0; i < 4; ++i) tl.rs[i] = i < ntaps ? taps[i] : 0;
+  const int64_t total = (int64_t)C * ntaps * (K / (dtype == SRT_F32 ? 4 : 8));
+  DISPATCH_T(dtype, {
+    launch_pdl(subfilter_kernel<T>, dim3(stream_grid(total)), dim3(NT), 0, st, (const T*)wt, (T*)sub, C, K, RS, tl);
+  });
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
+int parity_interleave(int dtype, const void* c00, const void* c01, const void* c10, const void* c11, const void* addend,
+                      void* dx, int N, int H, int W, int C, cudaStream_t st) {
+  SRT_REQUIRE(H % 2 == 0 && W % 2 == 0 && C % 8 == 0, "parity_interleave: even map and C % 8 == 0 required");
+  const int64_t total = (int64_t)N * H * W * (C / (dtype == SRT_F32 ? 4 : 8));
+  DISPATCH_T(dtype, {
+    launch_pdl(parity_interleave_kernel<T>, dim3(stream_grid(total)), dim3(NT), 0, st, (const T*)c00, (const T*)c01,
+               (const T*)c10, (const T*)c11, (const T*)addend, (T*)dx, N, H, W, C);
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;

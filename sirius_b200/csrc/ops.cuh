@@ -41,6 +41,10 @@ int nchw_to_nhwc(int dtype, const float* src, void* dst, int N, int C, int H, in
 int cast_f32_to_bf16(const float* s, void* d, int64_t n, cudaStream_t st);
 int cast_bf16_to_f32(const void* s, float* d, int64_t n, cudaStream_t st);
 int filter_transpose(int dtype, const void* w, void* wt, int K, int RS, int C, cudaStream_t st);
+// Stride-2 data gradient by output parity: the filter taps of one parity class, and the merge of the four classes.
+int subfilter(int dtype, const void* wt, void* sub, int C, int K, int RS, const int* taps, int ntaps, cudaStream_t st);
+int parity_interleave(int dtype, const void* c00, const void* c01, const void* c10, const void* c11, const void* addend,
+                      void* dx, int N, int H, int W, int C, cudaStream_t st);
 
 // Convolution front ends: validate, pick the kernel family, launch.
 int conv_fprop(const srt_conv_desc& d, int dtype, int impl, const void* x, const void* w, void* y,

@@ -40,6 +40,7 @@ struct ConvL {
   int C, K, R, S, stride, pad;  // C = internal (padded) channels
   int w;                        // param index
   size_t wt_off;                // element offset of the transposed copy (dgrad operand)
+  size_t s2_off;                // 3x3 stride-2 filters: element offset of the four parity sub-filters in the same arena
 };
 struct BNL {
   int C;
@@ -89,6 +90,7 @@ struct Step {
   void* T[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  void* s2_tmp = nullptr;      // the four parity classes of a stride-2 data gradient before they are interleaved
   void* scratch_wg = nullptr;  // split partials of the filter-gradient kernels (they run beside BatchNorm)
   size_t scratch_wg_bytes = 0;
   // Backward overlap: the filter gradient of a unit depends only on (dz, saved input), not on anything
@@ -320,6 +322,8 @@ struct Step {
     c.w = add_param(name + ".weight", SRT_PARAM_CONV, {K, Cin_real, R, R}, c.C);
     c.wt_off = n_wt;
     n_wt += align_up((size_t)K * R * R * c.C, 64);
+    c.s2_off = n_wt;
+    if (stride == 2 && R == 3) n_wt += align_up((size_t)K * R * R * c.C, 64);  // taps regrouped by output parity
     return c;
   }
   BNL make_bn(const std::string& name, int C) {
@@ -340,6 +344,9 @@ struct Step {
 
   int build();
   int refresh_working_copies();
+  bool s2_fast(const ConvL& c) const { return cfg.dtype == SRT_BF16 && cfg.impl != SRT_IMPL_SIMT && c.stride == 2 && (c.R == 1 || (c.R == 3 && c.pad == 1)); }
+  int build_subfilters(const ConvL& c, cudaStream_t st);
+  int dgrad_s2(const Unit& u, const void* dz, void* dx, const void* addend, int B);
   int forward(int B);
   int backward(int B);
 };
@@ -537,6 +544,7 @@ int Step::alloc_activations(int B) {
     if ((rc = aalloc(&T[i], max_act * esz))) return rc;
   scratch_bytes = max_bn_scratch > max_wg_scratch ? max_bn_scratch : max_wg_scratch;  // the fc wgrad uses it too
   if ((rc = aalloc(&scratch, scratch_bytes))) return rc;
+  if ((rc = aalloc(&s2_tmp, max_act * esz))) return rc;
   scratch_wg_bytes = max_wg_scratch;
   if ((rc = aalloc(&scratch_wg, scratch_wg_bytes))) return rc;
   act_batch = B;
@@ -622,13 +630,66 @@ int Step::shrink_activations(int B, size_t* released_bytes) {
   return SRT_OK;
 }
 
+// Parity sub-filters of a 3x3 stride-2 pad-1 filter from its transposed copy wt[c][rs][k]. Output row h = 2i + a
+// receives tap r only when h + 1 - r is even: a = 0 takes r = 1 (input row i); a = 1 takes r = 2 (row i) and r = 0
+// (row i + 1). Columns alike. Class (a, b) is stored as [c][tr][ts][k] in the order its stride-1 gather walks the taps.
+namespace {
+struct ParityTaps { int n; int r[2]; };
+inline ParityTaps parity_taps(int a) { return a == 0 ? ParityTaps{1, {1, 0}} : ParityTaps{2, {2, 0}}; }
+}  // namespace
+
+int Step::build_subfilters(const ConvL& c, cudaStream_t st) {
+  if (!s2_fast(c) || c.R != 3) return SRT_OK;
+  size_t off = c.s2_off;
+  for (int a = 0; a < 2; ++a)
+    for (int b = 0; b < 2; ++b) {
+      const ParityTaps ta = parity_taps(a), tb = parity_taps(b);
+      int taps[4], n = 0;
+      for (int i = 0; i < ta.n; ++i)
+        for (int j = 0; j < tb.n; ++j) taps[n++] = ta.r[i] * 3 + tb.r[j];
+      int rc = subfilter(cfg.dtype, wt(c), (char*)WT + off * esz, c.C, c.K, 9, taps, n, st);
+      if (rc) return rc;
+      off += (size_t)c.C * n * c.K;
+    }
+  return SRT_OK;
+}
+
+// Data gradient of a stride-2 convolution without multiplying the zeros a strided scatter is made of: each output
+// parity class is a stride-1 gather GEMM over dy with its own taps (1, 2, 2, 4 of the 9; a 1x1 filter only has class
+// (0, 0)), written compactly and interleaved (+ addend) by one pass.
+int Step::dgrad_s2(const Unit& u, const void* dz, void* dx, const void* addend, int B) {
+  const ConvL& c = u.conv;
+  const int Hh = u.H / 2, Wh = u.W / 2;
+  const size_t quarter = (size_t)B * Hh * Wh * c.C;
+  const void* cls[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t off = c.s2_off;
+  int rc;
+  for (int a = 0; a < 2; ++a)
+    for (int b = 0; b < 2; ++b) {
+      if (c.R == 1 && (a || b)) continue;
+      const int nr = c.R == 1 ? 1 : parity_taps(a).n, ns = c.R == 1 ? 1 : parity_taps(b).n;
+      GatherGeom g;
+      g.n_img = B; g.src_h = u.P; g.src_w = u.Q; g.src_c = c.K;
+      g.out_h = Hh; g.out_w = Wh;
+      g.R = nr; g.S = ns; g.stride = 1; g.pad = 0; g.dgrad = 0;
+      g.M = B * Hh * Wh; g.Kg = nr * ns * c.K; g.Nout = c.C;
+      void* out = (char*)s2_tmp + (size_t)(a * 2 + b) * quarter * esz;
+      const void* filt = c.R == 1 ? wt(c) : (const void*)((char*)WT + off * esz);
+      if ((rc = conv_gather_gemm_tc(g, dz, filt, out, nullptr, stream))) return rc;
+      cls[a * 2 + b] = out;
+      off += (size_t)c.C * nr * ns * c.K;
+    }
+  return parity_interleave(cfg.dtype, cls[0], cls[1], cls[2], cls[3], addend, dx, B, u.H, u.W, c.C, stream);
+}
+
 // bf16 working copy of the parameters (bf16 mode) and transposed filters for dgrad.
 int Step::refresh_working_copies() {
   int rc;
   if ((rc = join_side())) return rc;
   if (cfg.dtype == SRT_BF16 && (rc = cast_f32_to_bf16(P, Pw, (int64_t)n_flat, stream))) return rc;
   auto tr = [&](const ConvL& c) -> int {
-    return filter_transpose(cfg.dtype, pw(c.w), wt(c), c.K, c.R * c.S, c.C, stream);
+    int r = filter_transpose(cfg.dtype, pw(c.w), wt(c), c.K, c.R * c.S, c.C, stream);
+    return r ? r : build_subfilters(c, stream);
   };
   if ((rc = tr(stem.conv))) return rc;
   for (auto& k : blocks) {
@@ -761,6 +822,8 @@ int Step::backward(int B) {
     srt_conv_epilogue ep = {nullptr, addend};
     const double flops = 2.0 * B * u.P * u.Q * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
     if (int r = before_write(dx)) return r;
+    if (s2_fast(u.conv) && u.H % 2 == 0 && u.W % 2 == 0)
+      return timed(SRT_PROF_CONV, flops, [&] { return dgrad_s2(u, dz, dx, addend, B); });
     return timed(SRT_PROF_CONV, flops, [&] {
       return conv_dgrad(d, dt, impl, dz, wt(u.conv), dx, addend ? &ep : nullptr, stream); });
   };
@@ -1001,9 +1064,11 @@ int srt_step_optimizer(srt_step* h) {
   }
   PdlOff no_early_launch(ts != s->stream);
   auto tr = [&](const ConvL& c) -> int {
-    if (ts != s->stream) return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, ts);
-    return s->timed(SRT_PROF_OPTIM, 2.0 * c.K * c.R * c.S * c.C * s->esz, [&] {
+    int r;
+    if (ts != s->stream) r = filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, ts);
+    else r = s->timed(SRT_PROF_OPTIM, 2.0 * c.K * c.R * c.S * c.C * s->esz, [&] {
       return filter_transpose(s->cfg.dtype, s->pw(c.w), s->wt(c), c.K, c.R * c.S, c.C, s->stream); });
+    return r ? r : s->build_subfilters(c, ts);
   };
   if ((rc = tr(s->stem.conv))) return rc;
   for (auto& k : s->blocks) {

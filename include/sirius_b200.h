@@ -107,6 +107,17 @@ int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int
                     const float* gamma, const float* mean, const float* invstd, const float* scale,
                     const float* shift, int relu, void* dz, void* dresidual, float* dgamma,
                     float* dbeta, void* scratch, size_t scratch_bytes, void* stream);
+/* The same BatchNorm as ONE kernel per direction for tensors that fit on chip: a cluster of 8 CTAs per group of
+ * 16 or 32 channels keeps its rows in shared memory, combines the sums through distributed shared memory and
+ * writes the result: one read and one write of the tensor, no scratch. srt_bn_fused_fits tells whether a tensor
+ * qualifies (backward keeps two slabs, so it qualifies for half the size). No counterpart in the reference. */
+int srt_bn_fused_fits(int dtype, int64_t rows, int C, int backward);
+int srt_bn_forward_fused(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C, const float* gamma,
+                         const float* beta, float eps, float momentum, float* running_mean, float* running_var, float* mean,
+                         float* invstd, float* scale, float* shift, int relu, void* stream);
+int srt_bn_backward_fused(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C, const float* gamma,
+                          const float* mean, const float* invstd, const float* scale, const float* shift, int relu, void* dz,
+                          void* dresidual, float* dgamma, float* dbeta, void* stream);
 
 /* ---- pooling (replaces nn.MaxPool2d(3,2,1) and nn.AdaptiveAvgPool2d(1) of torchvision
  *      ResNet) ------------------------------------------------------------------------------- */

@@ -50,6 +50,9 @@ _SIGNATURES = {
     "srt_bn_stats_static": (None, [_i, _vp, _i64, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "srt_bn_apply": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _i, _vp]),
     "srt_bn_backward": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "srt_bn_fused_fits": (_i, [_i, _i64, _i, _i]),
+    "srt_bn_forward_fused": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "srt_bn_backward_fused": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "srt_maxpool3x3s2_fwd": (None, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "srt_maxpool3x3s2_bwd": (None, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "srt_avgpool_fwd": (None, [_i, _vp, _vp, _i, _i, _i, _vp]),

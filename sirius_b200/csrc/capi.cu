@@ -192,6 +192,26 @@ int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int
                      dgamma, dbeta, scratch, scratch_bytes, ST(stream));
 }
 
+int srt_bn_fused_fits(int dtype, int64_t rows, int C, int backward) { return bn_fused_fits(dtype, rows, C, backward) ? 1 : 0; }
+int srt_bn_forward_fused(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C, const float* gamma,
+                         const float* beta, float eps, float momentum, float* running_mean, float* running_var, float* mean,
+                         float* invstd, float* scale, float* shift, int relu, void* stream) {
+  SRT_REQUIRE(z && y && mean && invstd && scale && shift, "bn_forward_fused: null argument");
+  CHECK_DTYPE(dtype);
+  SRT_REQUIRE(C % 16 == 0 && rows > 0, "bn_forward_fused: C (%d) must be a multiple of 16", C);
+  return bn_forward_fused(dtype, z, residual, y, rows, C, gamma, beta, eps, momentum, running_mean, running_var, mean, invstd,
+                          scale, shift, relu, ST(stream));
+}
+int srt_bn_backward_fused(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C, const float* gamma,
+                          const float* mean, const float* invstd, const float* scale, const float* shift, int relu, void* dz,
+                          void* dresidual, float* dgamma, float* dbeta, void* stream) {
+  SRT_REQUIRE(dy && z && mean && invstd && dz, "bn_backward_fused: null argument");
+  CHECK_DTYPE(dtype);
+  SRT_REQUIRE(C % 16 == 0 && rows > 0, "bn_backward_fused: C (%d) must be a multiple of 16", C);
+  return bn_backward_fused(dtype, dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz, dresidual, dgamma, dbeta,
+                           ST(stream));
+}
+
 int srt_maxpool3x3s2_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W,
                          int C, void* stream) {
   SRT_REQUIRE(x && y && argmax, "maxpool_fwd: null argument");

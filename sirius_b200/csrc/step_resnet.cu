@@ -105,6 +105,7 @@ struct Step {
   bool side_dirty = false;         // side-stream work queued that the main stream has not waited for
   bool wt_dirty = false;           // ... of which only filter transposes (the forward pass need not wait for those)
   bool overlap_wgrad = true;
+  bool fused_bn = getenv("SIRIUS_B200_NO_FUSED_BN") == nullptr;  // one-kernel BatchNorm where the tensor fits on chip
   // Gradient buckets for the data-parallel all-reduce, in the order backward completes them (fc and the
   // last blocks first). A bucket's event fires when every gradient in its range is final.
   struct GradBucket { size_t off, count; int first_block; cudaEvent_t ev; };
@@ -721,6 +722,12 @@ int Step::forward(int B) {
       if ((r = bn_eval_params(pf(u.bn.gamma), pf(u.bn.beta), bf_(u.bn.rmean), bf_(u.bn.rvar), cfg.bn_eps, u.bn.C,
                               u.bn.scale, u.bn.shift, stream)))
         return r;
+    } else if (fused_bn && !follow_mask && bn_fused_pays(dt, rows, u.bn.C, 0)) {
+      // statistics, finalize and apply in one cluster kernel: the tensor is read once and stays on chip
+      return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2), [&] {
+        return bn_forward_fused(dt, u.z, residual, u.y, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps,
+                                cfg.bn_momentum, bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale,
+                                u.bn.shift, u.relu, stream); });
     } else if ((r = timed(SRT_PROF_NORM, abytes, [&] {
           return bn_stats(dt, u.z, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
                           bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift,
@@ -791,7 +798,12 @@ int Step::backward(int B) {
     // two passes over (dy, z[, y]) plus the dz (and masked-gradient) writes
     const double abytes = (double)rows * u.bn.C * esz;
     const double bn_bytes = abytes * ((dres ? 3 : 2) * 2 + 1 + (dres ? 1 : 0));
-    if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
+    if (fused_bn && !follow_mask && bn_fused_pays(dt, rows, u.bn.C, 1)) {
+      if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
+            return bn_backward_fused(dt, dy, dres ? u.y : nullptr, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean, u.bn.invstd,
+                                     u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma), gf(u.bn.beta), stream); })))
+        return r;
+    } else if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
           // units without a residual recompute the ReLU mask from z instead of reading y
           return bn_backward(dt, dy, dres ? u.y : nullptr, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean,
                              u.bn.invstd, u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma),

@@ -109,6 +109,33 @@ def bn_backward(dy, y, z, gamma, mean, invstd, relu=True, want_dresidual=False, 
     return dz, dres, dgamma, dbeta
 
 
+def bn_fused_fits(z, backward=False) -> bool:
+    Cc = z.shape[-1]
+    return bool(_lib.lib().srt_bn_fused_fits(_dt(z), z.numel() // Cc, Cc, int(backward)))
+
+
+def bn_forward_fused(z, gamma, beta, running_mean, running_var, residual=None, relu=True, eps=1e-5, momentum=0.1):
+    """Statistics + apply in one cluster kernel; returns (y, mean, invstd, scale, shift)."""
+    Cc = z.shape[-1]
+    f = lambda: torch.empty(Cc, dtype=torch.float32, device=z.device)
+    mean, invstd, scale, shift = f(), f(), f(), f()
+    y = torch.empty_like(z)
+    call("srt_bn_forward_fused", _dt(z), _p(z), _p(residual), _p(y), z.numel() // Cc, Cc, _p(gamma), _p(beta), eps, momentum,
+         _p(running_mean), _p(running_var), _p(mean), _p(invstd), _p(scale), _p(shift), int(relu), _stream())
+    return y, mean, invstd, scale, shift
+
+
+def bn_backward_fused(dy, y, z, gamma, mean, invstd, relu=True, want_dresidual=False, scale=None, shift=None):
+    Cc = z.shape[-1]
+    dz = torch.empty_like(z)
+    dres = torch.empty_like(z) if want_dresidual else None
+    dgamma = torch.empty(Cc, dtype=torch.float32, device=z.device)
+    dbeta = torch.empty_like(dgamma)
+    call("srt_bn_backward_fused", _dt(z), _p(dy), _p(y), _p(z), z.numel() // Cc, Cc, _p(gamma), _p(mean), _p(invstd),
+         _p(scale), _p(shift), int(relu), _p(dz), _p(dres), _p(dgamma), _p(dbeta), _stream())
+    return dz, dres, dgamma, dbeta
+
+
 def maxpool_fwd(x):
     N, H, W, Cc = x.shape
     P, Q = (H - 1) // 2 + 1, (W - 1) // 2 + 1

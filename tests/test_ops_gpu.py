@@ -224,6 +224,48 @@ def test_batchnorm_mask_recomputed_from_z_is_identical(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape,residual", [((64, 14, 14, 256), False), ((8, 7, 7, 2048), True), ((3, 5, 5, 48), True),
+                                            ((2, 3, 3, 1024), False)])
+def test_batchnorm_one_kernel_cluster_path_matches_the_three_kernel_path(dtype, shape, residual):
+    """The cluster kernels (one read, one write, sums through distributed shared memory) compute the same BatchNorm
+    as statistics + finalize + apply and partial + finalize + apply; only the order of the sums differs."""
+    g = torch.Generator().manual_seed(11)
+    C = shape[-1]
+    z = (torch.randn(shape, generator=g) * 2 + 0.5).to(DEV, dtype)
+    res = torch.randn(shape, generator=g).to(DEV, dtype) if residual else None
+    dy = torch.randn(shape, generator=g).to(DEV, dtype)
+    gamma, beta = (torch.rand(C, generator=g) + 0.5).to(DEV), torch.randn(C, generator=g).to(DEV)
+    assert ops.bn_fused_fits(z)
+    bwd_fits = ops.bn_fused_fits(z, backward=True)   # two resident slabs: the fp32 14x14x256 case is too large
+    assert bwd_fits or dtype == torch.float32
+    rm1, rv1, rm2, rv2 = (torch.zeros(C, device=DEV), torch.ones(C, device=DEV), torch.zeros(C, device=DEV),
+                          torch.ones(C, device=DEV))
+    mean, invstd, scale, shift = ops.bn_stats(z, gamma, beta, rm1, rv1)
+    y = ops.bn_apply(z, scale, shift, residual=res, relu=True)
+    y2, mean2, invstd2, scale2, shift2 = ops.bn_forward_fused(z, gamma, beta, rm2, rv2, residual=res, relu=True)
+    torch.cuda.synchronize()
+    for a, b in ((mean, mean2), (invstd, invstd2), (scale, scale2), (shift, shift2), (rm1, rm2), (rv1, rv2)):
+        assert _err(b, a.cpu()) < 2e-6
+    assert _err(y2, y.float().cpu()) < (1e-6 if dtype == torch.float32 else 4e-3)
+    # backward from identical saved values, both mask variants
+    if not bwd_fits:
+        return
+    ref = ops.bn_backward(dy, y if residual else None, z, gamma, mean, invstd, relu=True, want_dresidual=residual,
+                          scale=scale, shift=shift)
+    got = ops.bn_backward_fused(dy, y if residual else None, z, gamma, mean, invstd, relu=True, want_dresidual=residual,
+                                scale=scale, shift=shift)
+    torch.cuda.synchronize()
+    tol = 2e-5 if dtype == torch.float32 else 4e-3
+    assert _err(got[0], ref[0].float().cpu()) < tol
+    if residual:
+        assert torch.equal(got[1], ref[1])
+    assert _err(got[2], ref[2].cpu()) < 1e-5 and _err(got[3], ref[3].cpu()) < 1e-5
+    # a tensor too large to stay on chip is refused, not mangled
+    big = torch.empty(64, 56, 56, 64, device=DEV, dtype=dtype)
+    assert not ops.bn_fused_fits(big)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_pools(dtype):
     g = torch.Generator().manual_seed(2)
     x = torch.randn(2, 13, 16, 16, generator=g).clamp_min(0)  # zeros create ties like post-ReLU data

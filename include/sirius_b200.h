@@ -320,6 +320,15 @@ typedef struct srt_gpt2_config {
   float ln_eps;                             /* 1e-5 */
 } srt_gpt2_config;
 int srt_gpt2_create(const srt_gpt2_config* cfg, srt_gpt2** out);
+/* Colocation hooks, as for srt_step_*: batch-sized buffers from the training allocator of a page pool
+ * (sirius_pool.h), release / shrink for the memory handover (ColocateCtrl.adjust_l1), kill batch between layers
+ * (at most 4 layers run ahead of the GPU), gradient accumulation over micro-batches (GradAccumulator). */
+struct srt_pool;
+int srt_gpt2_create_with_pool(const srt_gpt2_config* cfg, struct srt_pool* pool, srt_gpt2** out);
+int srt_gpt2_release_activations(srt_gpt2* g, size_t* released_bytes);
+int srt_gpt2_shrink_activations(srt_gpt2* g, int B, size_t* released_bytes);
+int srt_gpt2_request_abort(srt_gpt2* g, int on);
+int srt_gpt2_accumulate(srt_gpt2* g);
 int srt_gpt2_destroy(srt_gpt2* g);
 int srt_gpt2_num_params(srt_gpt2* g);
 int srt_gpt2_param_info(srt_gpt2* g, int idx, char* name, int name_cap, int64_t shape[2], int* ndim);

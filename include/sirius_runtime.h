@@ -167,6 +167,9 @@ typedef struct srt_stub_config {
  * step the kill raises srt_step_request_abort, with a dist rank 0 redistributes on kInferExit. */
 int srt_stub_create(srt_comm* comm, struct srt_step* step, srt_dist* dist, const srt_stub_config* cfg,
                     srt_stub** out);
+/* Executors other than the ResNet one: what the kill means is fn(arg, 1) and clearing it fn(arg, 0), e.g.
+ * (srt_gpt2_request_abort, handle). Set it right after srt_stub_create with step == NULL. */
+int srt_stub_set_abort_target(srt_stub* s, int (*fn)(void*, int), void* arg);
 int srt_stub_stop(srt_stub* s);       /* StubBase::Stop + destruction */
 int srt_stub_cmd(srt_stub* s);        /* GetCmd: pending CtrlEvent or -1 */
 int srt_stub_set_cmd(srt_stub* s, int cmd);

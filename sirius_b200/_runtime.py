@@ -81,6 +81,7 @@ register({
     "srt_adjuster_predict_train_mem_mb": (None, [_vp, _i, _pd]),
     "srt_adjuster_infer_require_plan": (None, [_vp, _i, _d, _pd, _pi, _pi]),
     "srt_adjuster_infer_release_plan": (None, [_vp, _pd, _pd, _pd, _pi, _pi]),
+    "srt_stub_set_abort_target": (None, [_vp, _vp, _vp]),
     "srt_stub_create": (None, [_vp, _vp, _vp, C.POINTER(StubConfig), C.POINTER(_vp)]),
     "srt_stub_stop": (None, [_vp]),
     "srt_stub_cmd": (_i, [_vp]),

@@ -30,6 +30,13 @@ static int64_t unix_us() {
 struct Stub {
   srt_comm* comm = nullptr;
   srt_step* step = nullptr;
+  // what raising / clearing the kill flag means: by default the ResNet executor's call on `step`
+  int (*abort_fn)(void*, int) = nullptr;
+  void* abort_arg = nullptr;
+  void request_abort(int on) {
+    if (abort_fn) abort_fn(abort_arg, on);
+    else if (step) srt_step_request_abort(step, on);
+  }
   srt_dist* dist = nullptr;
   srt_stub_config cfg;
   std::thread th;
@@ -66,7 +73,7 @@ struct Stub {
         will_killed_batch_reconfig = true;
         if (should_kill) {
           std::unique_lock<std::mutex> step_lock(step_mu);  // never inside the optimizer step
-          if (step) srt_step_request_abort(step, 1);
+          request_abort(1);
         }
         cmd.store(msg.event);
         cmd_id = msg.id;
@@ -172,6 +179,14 @@ int srt_stub_report_batch_size(srt_stub* h, int batch_size) {
   if (s->comm) s->put(0, SRT_EV_REPORT_BATCH_SIZE, batch_size);
   return SRT_OK;
 }
+int srt_stub_set_abort_target(srt_stub* h, int (*fn)(void*, int), void* arg) {
+  Stub* s = (Stub*)h;
+  SRT_REQUIRE(s, "stub_set_abort_target: null handle");
+  s->abort_fn = fn;
+  s->abort_arg = arg;
+  return SRT_OK;
+}
+
 int srt_stub_steps_no_interrupt_begin(srt_stub* h) {
   Stub* s = (Stub*)h;
   SRT_REQUIRE(s, "stub: null handle");
@@ -193,7 +208,7 @@ static int adjust_done(Stub* s, int want_cmd, int done_event) {
   if (s->comm) s->put(s->cmd_id, done_event, 0);
   s->cmd.store(-1);
   s->cmd_id = 0;
-  if (want_cmd == SRT_EV_COLOCATE_ADJUST_L1 && s->step) srt_step_request_abort(s->step, 0);
+  if (want_cmd == SRT_EV_COLOCATE_ADJUST_L1) s->request_abort(0);
   std::lock_guard<std::mutex> pl(s->prof_mu);
   s->done_us.push_back(unix_us());
   return SRT_OK;

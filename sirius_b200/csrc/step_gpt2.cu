@@ -17,6 +17,8 @@
 #include <vector>
 
 #include "../../include/sirius_b200.h"
+#include "../../include/sirius_pool.h"
+#include <atomic>
 #include "common.cuh"
 #include "ops.cuh"
 
@@ -61,10 +63,84 @@ struct Gpt2 {
   int n_unique = 0, cur_B = 0;
   std::vector<void*> allocs;
   size_t bytes_total = 0;
+  // Releasable part (everything sized by the batch): from the training allocator of a page pool when one is
+  // attached, so that shrinking the batch hands whole pages to the inference side (as the ResNet executor does).
+  srt_pool* pool = nullptr;
+  std::vector<void*> act_blocks;
+  size_t act_bytes = 0;
+  int act_batch = 0;
+  float* ACC = nullptr;      // gradients accumulated over the micro-batches of a global batch
+  int accum_pending = 0;
+  std::atomic<int> abort_flag{0};
+  static constexpr int kAhead = 4;  // layers the host may run ahead of the GPU (bounds the drain after a kill)
+  cudaEvent_t ahead_ev[kAhead] = {nullptr};
+  unsigned long long layer_seq = 0;
 
   ~Gpt2() {
+    release_activations(nullptr);
+    for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
     for (void* p : allocs) cudaFree(p);
     if (stream) cudaStreamDestroy(stream);
+  }
+  int aalloc(void** out, size_t bytes) {
+    bytes = up(bytes ? bytes : 256, 256);
+    if (pool) {
+      int rc = srt_pool_alloc(pool, SRT_POOL_TRAIN, bytes, out);
+      if (rc) return rc;
+    } else {
+      SRT_CHECK_CUDA(cudaMalloc(out, bytes));
+    }
+    act_blocks.push_back(*out);
+    act_bytes += bytes;
+    return SRT_OK;
+  }
+  int free_activation_blocks() {
+    if (stream && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
+    for (void* p : act_blocks) {
+      if (pool) { int rc = srt_pool_free(pool, SRT_POOL_TRAIN, p); if (rc) return rc; }
+      else cudaFree(p);
+    }
+    act_blocks.clear();
+    act_bytes = 0;
+    act_batch = 0;
+    return SRT_OK;
+  }
+  int release_activations(size_t* released) {
+    if (released) *released = 0;
+    if (act_blocks.empty()) { act_batch = 0; return SRT_OK; }
+    size_t freed = act_bytes;
+    int rc = free_activation_blocks();
+    if (rc) return rc;
+    if (pool && (rc = srt_pool_empty_cache(pool, SRT_POOL_TRAIN, &freed))) return rc;
+    if (released) *released = freed;
+    return SRT_OK;
+  }
+  int alloc_activations(int B);
+  int shrink_activations(int B, size_t* released) {
+    if (released) *released = 0;
+    if (B <= 0) return release_activations(released);
+    SRT_REQUIRE(B <= cfg.max_batch, "gpt2 shrink_activations: batch %d above max_batch %d", B, cfg.max_batch);
+    const size_t before = act_bytes;
+    int rc = free_activation_blocks();
+    if (rc) return rc;
+    if ((rc = alloc_activations(B))) return rc;
+    size_t freed = before > act_bytes ? before - act_bytes : 0;
+    if (pool && (rc = srt_pool_empty_cache(pool, SRT_POOL_TRAIN, &freed))) return rc;
+    if (released) *released = freed;
+    return SRT_OK;
+  }
+  // Between layers: kill-batch flag and bounded launch-ahead.
+  int checkpoint() {
+    if (abort_flag.load(std::memory_order_acquire)) {
+      set_error("step aborted between layers (kill batch)");
+      return SRT_ERR_ABORTED;
+    }
+    const int slot = (int)(layer_seq % kAhead);
+    if (!ahead_ev[slot]) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ahead_ev[slot], cudaEventDisableTiming));
+    else if (layer_seq >= (unsigned long long)kAhead) SRT_CHECK_CUDA(cudaEventSynchronize(ahead_ev[slot]));
+    SRT_CHECK_CUDA(cudaEventRecord(ahead_ev[slot], stream));
+    ++layer_seq;
+    return SRT_OK;
   }
   template <class T>
   int dalloc(T** out, size_t bytes, bool zero = false) {
@@ -151,40 +227,50 @@ int Gpt2::build() {
   if ((rc = dalloc(&Pw, n_flat * 2, true))) return rc;
   if ((rc = dalloc(&WT, n_wt * 2, true))) return rc;
 
-  const size_t T = (size_t)cfg.max_batch * S, BH = (size_t)cfg.max_batch * H;
-  auto act = [&](__nv_bfloat16** p, size_t elems) { return dalloc(p, elems * 2); };
+  if ((rc = dalloc(&ACC, n_flat * 4, true))) return rc;
+  // scratch: split partials of the largest filter gradient, norm / bias column partials (sized for max_batch)
+  const size_t Tmax = (size_t)cfg.max_batch * S;
+  size_t sb = layernorm_bwd_scratch_bytes(C);
+  if (colsum_scratch_bytes(4 * C) > sb) sb = colsum_scratch_bytes(4 * C);
+  auto wg = [&](int in, int out) {
+    const size_t b = conv_wgrad_scratch_bytes(lin_desc((int64_t)Tmax, in, out), SRT_BF16, SRT_IMPL_AUTO);
+    if (b > sb) sb = b;
+  };
+  wg(C, 3 * C); wg(C, C); wg(C, 4 * C); wg(4 * C, C); wg(C, Vpad);
+  scratch_bytes = sb;
+  if ((rc = dalloc((char**)&scratch, scratch_bytes))) return rc;
+  if ((rc = dalloc(&ids, Tmax * 4)) || (rc = dalloc(&labels, Tmax * 4)) || (rc = dalloc(&order, Tmax * 4)) ||
+      (rc = dalloc(&seg, (Tmax + 1) * 4)) || (rc = dalloc(&loss_acc, 256, true)))
+    return rc;
+  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  return alloc_activations(cfg.max_batch);
+}
+
+// Everything sized by the batch: saved activations of every layer, logits, backward scratch.
+int Gpt2::alloc_activations(int B) {
+  SRT_REQUIRE(B > 0 && B <= cfg.max_batch, "gpt2 activations: batch %d outside 1..%d", B, cfg.max_batch);
+  if (act_batch == B) return SRT_OK;
+  int rc = free_activation_blocks();
+  if (rc) return rc;
+  const size_t T = (size_t)B * S, BH = (size_t)B * H;
+  auto act = [&](__nv_bfloat16** p, size_t elems) { return aalloc((void**)p, elems * 2); };
+  auto actf = [&](float** p, size_t elems) { return aalloc((void**)p, elems * 4); };
   if ((rc = act(&x0, T * C))) return rc;
   for (Layer& y : layers) {
     if ((rc = act(&y.ln1o, T * C)) || (rc = act(&y.qkv_o, T * 3 * C)) || (rc = act(&y.Pm, BH * S * S)) ||
         (rc = act(&y.att, T * C)) || (rc = act(&y.x2, T * C)) || (rc = act(&y.ln2o, T * C)) ||
         (rc = act(&y.h, T * 4 * C)) || (rc = act(&y.g, T * 4 * C)) || (rc = act(&y.xout, T * C)))
       return rc;
-    if ((rc = dalloc(&y.ln1_mean, T * 4)) || (rc = dalloc(&y.ln1_rstd, T * 4)) || (rc = dalloc(&y.ln2_mean, T * 4)) ||
-        (rc = dalloc(&y.ln2_rstd, T * 4)))
+    if ((rc = actf(&y.ln1_mean, T)) || (rc = actf(&y.ln1_rstd, T)) || (rc = actf(&y.ln2_mean, T)) || (rc = actf(&y.ln2_rstd, T)))
       return rc;
   }
   if ((rc = act(&lnfo, T * C)) || (rc = act(&logits, T * Vpad))) return rc;
-  if ((rc = dalloc(&lnf_mean, T * 4)) || (rc = dalloc(&lnf_rstd, T * 4)) || (rc = dalloc(&row_loss, T * 4)) ||
-      (rc = dalloc(&loss_acc, 256, true)))
-    return rc;
+  if ((rc = actf(&lnf_mean, T)) || (rc = actf(&lnf_rstd, T)) || (rc = actf(&row_loss, T))) return rc;
   if ((rc = act(&dxa, T * C)) || (rc = act(&dxb, T * C)) || (rc = act(&dqkv, T * 3 * C)) || (rc = act(&dP, BH * S * S)) ||
       (rc = act(&Tbig, BH * S * S)) || (rc = act(&t1, T * C)) || (rc = act(&t2, T * C)) || (rc = act(&dh, T * 4 * C)) ||
       (rc = act(&dg, T * 4 * C)) || (rc = act(&datt, T * C)) || (rc = act(&dln, T * C)))
     return rc;
-  // scratch: split partials of the largest filter gradient, LayerNorm column partials
-  size_t sb = layernorm_bwd_scratch_bytes(C);
-  if (colsum_scratch_bytes(4 * C) > sb) sb = colsum_scratch_bytes(4 * C);
-  auto wg = [&](int in, int out) {
-    const size_t b = conv_wgrad_scratch_bytes(lin_desc((int64_t)T, in, out), SRT_BF16, SRT_IMPL_AUTO);
-    if (b > sb) sb = b;
-  };
-  wg(C, 3 * C); wg(C, C); wg(C, 4 * C); wg(4 * C, C); wg(C, Vpad);
-  scratch_bytes = sb;
-  if ((rc = dalloc((char**)&scratch, scratch_bytes))) return rc;
-  if ((rc = dalloc(&ids, T * 4)) || (rc = dalloc(&labels, T * 4)) || (rc = dalloc(&order, T * 4)) ||
-      (rc = dalloc(&seg, (T + 1) * 4)))
-    return rc;
-  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  act_batch = B;
   return SRT_OK;
 }
 
@@ -205,6 +291,7 @@ int Gpt2::forward(int B) {
   if ((rc = embedding_fwd(ids, pf(wte), pf(wpe), x0, T, S, C, stream))) return rc;
   const __nv_bfloat16* x = x0;
   for (Layer& y : layers) {
+    if ((rc = checkpoint())) return rc;
     if ((rc = layernorm_fwd(x, pf(y.ln1_g), pf(y.ln1_b), y.ln1o, y.ln1_mean, y.ln1_rstd, T, C, cfg.ln_eps, stream))) return rc;
     if ((rc = linear_fwd(y.qkv, y.ln1o, y.qkv_o, nullptr, T))) return rc;
     // scores = Q K^T / sqrt(D), lower triangle only
@@ -250,6 +337,7 @@ int Gpt2::backward(int B, int global_batch) {
   for (int i = L - 1; i >= 0; --i) {
     Layer& y = layers[i];
     const __nv_bfloat16* xin = i == 0 ? x0 : layers[i - 1].xout;
+    if ((rc = checkpoint())) return rc;
     // MLP
     if ((rc = linear_bwd(y.fc2, dx, y.g, dg, T))) return rc;
     if ((rc = gelu_bwd(dg, y.h, dh, T * 4 * C, stream))) return rc;
@@ -298,10 +386,13 @@ using namespace srt;
 
 extern "C" {
 
-int srt_gpt2_create(const srt_gpt2_config* cfg, srt_gpt2** out) {
+int srt_gpt2_create(const srt_gpt2_config* cfg, srt_gpt2** out) { return srt_gpt2_create_with_pool(cfg, nullptr, out); }
+
+int srt_gpt2_create_with_pool(const srt_gpt2_config* cfg, srt_pool* pool, srt_gpt2** out) {
   SRT_REQUIRE(cfg && out, "gpt2_create: null argument");
   Gpt2* g = new Gpt2();
   g->cfg = *cfg;
+  g->pool = pool;
   int rc = g->build();
   if (rc == SRT_OK) rc = cudaStreamSynchronize(g->stream) == cudaSuccess ? SRT_OK : SRT_ERR_CUDA;
   if (rc != SRT_OK) { delete g; return rc; }
@@ -405,14 +496,16 @@ int srt_gpt2_upload_tokens(srt_gpt2* h, const int32_t* host_ids, int B) {
 int srt_gpt2_forward_backward(srt_gpt2* h, int B, int global_batch) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B && global_batch >= B, "gpt2_forward_backward: upload the tokens of this batch first");
-  int rc = g->forward(B);
-  if (rc) return rc;
+  int rc;
+  if (g->act_batch < B && (rc = g->alloc_activations(B))) return rc;  // regain after a release or a shrink
+  if ((rc = g->forward(B))) return rc;
   return g->backward(B, global_batch);
 }
 
 int srt_gpt2_forward_only(srt_gpt2* h, int B) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B, "gpt2_forward_only: upload the tokens of this batch first");
+  if (g->act_batch < B) { int rc = g->alloc_activations(B); if (rc) return rc; }
   return g->forward(B);
 }
 
@@ -420,9 +513,14 @@ int srt_gpt2_optimizer(srt_gpt2* h) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g, "gpt2_optimizer: null handle");
   g->opt_steps++;
-  int rc = adamw(g->P, g->G, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
+  const float* grad = g->accum_pending > 0 ? g->ACC : g->G;
+  int rc = adamw(g->P, grad, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
                  g->cfg.weight_decay, g->opt_steps, g->stream);
   if (rc) return rc;
+  if (g->accum_pending > 0) {
+    SRT_CHECK_CUDA(cudaMemsetAsync(g->ACC, 0, g->n_flat * 4, g->stream));
+    g->accum_pending = 0;
+  }
   auto tr = [&](const Gpt2::Lin& l) {
     return filter_transpose(SRT_BF16, g->pw(l.w), g->WT + l.wt_off, l.out, 1, l.in, g->stream);
   };
@@ -464,6 +562,32 @@ int srt_gpt2_synchronize(srt_gpt2* h) {
   return SRT_OK;
 }
 
+int srt_gpt2_accumulate(srt_gpt2* h) {
+  Gpt2* g = (Gpt2*)h;
+  SRT_REQUIRE(g, "gpt2_accumulate: null handle");
+  g->accum_pending++;
+  return grad_accumulate(g->ACC, g->G, (int64_t)g->n_flat, g->stream);
+}
+
+int srt_gpt2_release_activations(srt_gpt2* h, size_t* released_bytes) {
+  Gpt2* g = (Gpt2*)h;
+  SRT_REQUIRE(g, "gpt2_release_activations: null handle");
+  return g->release_activations(released_bytes);
+}
+
+int srt_gpt2_shrink_activations(srt_gpt2* h, int B, size_t* released_bytes) {
+  Gpt2* g = (Gpt2*)h;
+  SRT_REQUIRE(g, "gpt2_shrink_activations: null handle");
+  return g->shrink_activations(B, released_bytes);
+}
+
+int srt_gpt2_request_abort(srt_gpt2* h, int on) {
+  Gpt2* g = (Gpt2*)h;
+  SRT_REQUIRE(g, "gpt2_request_abort: null handle");
+  g->abort_flag.store(on ? 1 : 0, std::memory_order_release);
+  return SRT_OK;
+}
+
 int srt_gpt2_grad_buffer(srt_gpt2* h, void** ptr, int64_t* n) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g && ptr && n, "gpt2_grad_buffer: null argument");
@@ -473,7 +597,7 @@ int srt_gpt2_grad_buffer(srt_gpt2* h, void** ptr, int64_t* n) {
 }
 
 void* srt_gpt2_stream(srt_gpt2* h) { return h ? (void*)((Gpt2*)h)->stream : nullptr; }
-int64_t srt_gpt2_memory_bytes(srt_gpt2* h) { return h ? (int64_t)((Gpt2*)h)->bytes_total : -1; }
+int64_t srt_gpt2_memory_bytes(srt_gpt2* h) { return h ? (int64_t)(((Gpt2*)h)->bytes_total + ((Gpt2*)h)->act_bytes) : -1; }
 int64_t srt_gpt2_num_elements(srt_gpt2* h) { return h ? (int64_t)((Gpt2*)h)->n_flat : -1; }
 
 }  // extern "C"

@@ -131,8 +131,17 @@ struct Step {
     return SRT_OK;
   }
   float *row_loss = nullptr, *loss_acc = nullptr;
-  float* stage_images = nullptr;   // device staging of the NCHW fp32 batch
+  float* stage_images = nullptr;   // device staging of the NCHW fp32 batch the next forward reads (one of the two below)
   int64_t* stage_labels = nullptr;
+  // Double-buffered staging: a host batch is copied on its own stream into the buffer the executor is not reading,
+  // so the copy of the next batch runs beside the current step (what pinned memory + non_blocking copies give the
+  // reference's loader). ev_up: copy landed; ev_used: the step has consumed the buffer.
+  float* stage_images_b[2] = {nullptr, nullptr};
+  int64_t* stage_labels_b[2] = {nullptr, nullptr};
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_up[2] = {nullptr, nullptr}, ev_used[2] = {nullptr, nullptr};
+  bool used_pending[2] = {false, false};
+  int up_next = 0, pending_up = -1, cur_buf = 0;
   std::vector<void*> allocs;
 
   int opt_steps = 0;
@@ -164,6 +173,23 @@ struct Step {
     }
     act_blocks.push_back(*out);
     act_bytes += bytes;
+    return SRT_OK;
+  }
+  // The batch uploaded last becomes the one the next forward reads: wait for its copy, switch buffers.
+  int adopt_upload() {
+    if (pending_up < 0) return SRT_OK;
+    const int idx = pending_up;
+    pending_up = -1;
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_up[idx], 0));
+    cur_buf = idx;
+    stage_images = stage_images_b[idx];
+    stage_labels = stage_labels_b[idx];
+    return SRT_OK;
+  }
+  // Called once the step's kernels that read the staging buffer are enqueued: a later upload into it must wait for them.
+  int staging_consumed() {
+    SRT_CHECK_CUDA(cudaEventRecord(ev_used[cur_buf], stream));
+    used_pending[cur_buf] = true;
     return SRT_OK;
   }
   int alloc_activations(int B);
@@ -285,6 +311,8 @@ struct Step {
     release_activations(nullptr);
     for (void* p : allocs) cudaFree(p);
     if (switch_ev) cudaEventDestroy(switch_ev);
+    for (int i = 0; i < 2; ++i) { if (ev_up[i]) cudaEventDestroy(ev_up[i]); if (ev_used[i]) cudaEventDestroy(ev_used[i]); }
+    if (copy_stream) { cudaStreamSynchronize(copy_stream); cudaStreamDestroy(copy_stream); }
     for (auto& b : buckets) if (b.ev) cudaEventDestroy(b.ev);
     if (ev_fork) cudaEventDestroy(ev_fork);
     if (ev_join) cudaEventDestroy(ev_join);
@@ -431,8 +459,15 @@ int Step::build() {
   if ((rc = dalloc(&dlogits, (size_t)B * cfg.num_classes * esz, false))) return rc;
   if ((rc = dalloc((void**)&row_loss, (size_t)B * 4, true))) return rc;
   if ((rc = dalloc((void**)&loss_acc, 256, true))) return rc;
-  if ((rc = dalloc((void**)&stage_images, (size_t)B * 3 * IMG * IMG * 4, false))) return rc;
-  if ((rc = dalloc((void**)&stage_labels, (size_t)B * 8, false))) return rc;
+  for (int i = 0; i < 2; ++i) {
+    if ((rc = dalloc((void**)&stage_images_b[i], (size_t)B * 3 * IMG * IMG * 4, false))) return rc;
+    if ((rc = dalloc((void**)&stage_labels_b[i], (size_t)B * 8, false))) return rc;
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_up[i], cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_used[i], cudaEventDisableTiming));
+  }
+  stage_images = stage_images_b[0];
+  stage_labels = stage_labels_b[0];
+  SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
 
   if (pool_kind == SRT_POOL_INFER) {
     // the inference stand-in runs on the highest-priority stream so its blocks are scheduled ahead of
@@ -992,8 +1027,16 @@ int srt_step_upload_batch(srt_step* h, const float* host_images, const int64_t* 
   Step* s = (Step*)h;
   SRT_REQUIRE(s && host_images && host_labels && B > 0 && B <= s->cfg.max_batch, "upload_batch: bad argument");
   const size_t img = (size_t)B * 3 * s->cfg.image * s->cfg.image * 4;
-  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_images, host_images, img, cudaMemcpyHostToDevice, s->stream));
-  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_labels, host_labels, (size_t)B * 8, cudaMemcpyHostToDevice, s->stream));
+  const int idx = s->up_next;
+  s->up_next ^= 1;
+  if (s->used_pending[idx]) {  // the executor may still be reading this buffer
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(s->copy_stream, s->ev_used[idx], 0));
+    s->used_pending[idx] = false;
+  }
+  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_images_b[idx], host_images, img, cudaMemcpyHostToDevice, s->copy_stream));
+  SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_labels_b[idx], host_labels, (size_t)B * 8, cudaMemcpyHostToDevice, s->copy_stream));
+  SRT_CHECK_CUDA(cudaEventRecord(s->ev_up[idx], s->copy_stream));
+  s->pending_up = idx;
   return SRT_OK;
 }
 
@@ -1001,6 +1044,7 @@ int srt_step_set_batch_device(srt_step* h, const float* dev_images, const int64_
   Step* s = (Step*)h;
   SRT_REQUIRE(s && dev_images && dev_labels && B > 0 && B <= s->cfg.max_batch, "set_batch_device: bad argument");
   const size_t img = (size_t)B * 3 * s->cfg.image * s->cfg.image * 4;
+  s->pending_up = -1;  // a device batch replaces whatever host batch was on its way
   SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_images, dev_images, img, cudaMemcpyDeviceToDevice, s->stream));
   SRT_CHECK_CUDA(cudaMemcpyAsync(s->stage_labels, dev_labels, (size_t)B * 8, cudaMemcpyDeviceToDevice, s->stream));
   return SRT_OK;
@@ -1011,6 +1055,7 @@ int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch && global_batch >= B, "forward_backward: bad batch sizes");
   Step::SmScope sm_scope(s);
   int rc;
+  if ((rc = s->adopt_upload())) return rc;
   if (s->act_batch < B && (rc = s->alloc_activations(B))) return rc;  // regain after a release
   rc = s->forward(B);
   if (rc) return rc;
@@ -1019,6 +1064,7 @@ int srt_step_forward_backward(srt_step* h, int B, int global_batch) {
                        s->dlogits, s->stream)))
     return rc;
   if ((rc = sum_f32(s->row_loss, B, s->loss_acc, 0, s->stream))) return rc;
+  if ((rc = s->staging_consumed())) return rc;
   return s->backward(B);
 }
 
@@ -1026,19 +1072,25 @@ int srt_step_forward_only(srt_step* h, int B) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_only: bad batch size");
   Step::SmScope sm_scope(s);
-  if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
-  return s->forward(B);
+  int rc;
+  if ((rc = s->adopt_upload())) return rc;
+  if (s->act_batch < B && (rc = s->alloc_activations(B))) return rc;
+  if ((rc = s->forward(B))) return rc;
+  return s->staging_consumed();
 }
 
 int srt_step_forward_infer(srt_step* h, int B) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && B > 0 && B <= s->cfg.max_batch, "forward_infer: bad batch size");
   Step::SmScope sm_scope(s);
-  if (s->act_batch < B) { int rc = s->alloc_activations(B); if (rc) return rc; }
+  int rc;
+  if ((rc = s->adopt_upload())) return rc;
+  if (s->act_batch < B && (rc = s->alloc_activations(B))) return rc;
   s->eval_mode = true;
-  const int rc = s->forward(B);
+  rc = s->forward(B);
   s->eval_mode = false;
-  return rc;
+  if (rc) return rc;
+  return s->staging_consumed();
 }
 
 int srt_step_accumulate(srt_step* h) {

@@ -26,6 +26,11 @@ class BgemmDescC(C.Structure):
 _pf = C.POINTER(_f)
 register({
     "srt_gpt2_create": (None, [C.POINTER(Gpt2ConfigC), C.POINTER(_vp)]),
+    "srt_gpt2_create_with_pool": (None, [C.POINTER(Gpt2ConfigC), _vp, C.POINTER(_vp)]),
+    "srt_gpt2_release_activations": (None, [_vp, C.POINTER(C.c_size_t)]),
+    "srt_gpt2_shrink_activations": (None, [_vp, _i, C.POINTER(C.c_size_t)]),
+    "srt_gpt2_request_abort": (None, [_vp, _i]),
+    "srt_gpt2_accumulate": (None, [_vp]),
     "srt_gpt2_destroy": (None, [_vp]),
     "srt_gpt2_num_params": (_i, [_vp]),
     "srt_gpt2_param_info": (None, [_vp, _i, C.c_char_p, _i, C.POINTER(_i64), C.POINTER(_i)]),
@@ -63,12 +68,13 @@ class Gpt2Step:
     `transformers.GPT2LMHeadModel.state_dict()` (`lm_head.weight` is the tied token table and is not listed)."""
 
     def __init__(self, n_layer=12, n_head=12, d_model=768, vocab=50257, ctx=1024, max_batch=8, seq=1024,
-                 lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, ln_eps=1e-5):
+                 lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, ln_eps=1e-5, pool=None):
         cfg = Gpt2ConfigC(n_layer, n_head, d_model, vocab, ctx, max_batch, seq, lr, betas[0], betas[1], eps, weight_decay,
                           ln_eps)
         self.cfg, self.seq, self.vocab, self.max_batch = cfg, seq, vocab, max_batch
         self._h = _vp()
-        call("srt_gpt2_create", C.byref(cfg), C.byref(self._h))
+        self.pool = pool
+        call("srt_gpt2_create_with_pool", C.byref(cfg), pool if pool else None, C.byref(self._h))
         self.params = {}
         name, shape, ndim = C.create_string_buffer(256), (_i64 * 2)(), _i()
         for i in range(_lib.lib().srt_gpt2_num_params(self._h)):
@@ -130,6 +136,27 @@ class Gpt2Step:
 
     def synchronize(self) -> None:
         call("srt_gpt2_synchronize", self._h)
+
+    # ---- colocation hooks (the same surface as ResNetStep) ----
+    def accumulate(self) -> None:
+        call("srt_gpt2_accumulate", self._h)
+
+    def release_activations(self) -> int:
+        n = C.c_size_t()
+        call("srt_gpt2_release_activations", self._h, C.byref(n))
+        return n.value
+
+    def shrink_activations(self, B: int) -> int:
+        n = C.c_size_t()
+        call("srt_gpt2_shrink_activations", self._h, int(B), C.byref(n))
+        return n.value
+
+    def request_abort(self, on: bool = True) -> None:
+        call("srt_gpt2_request_abort", self._h, int(on))
+
+    def abort_target(self):
+        """(function address, handle) for srt_stub_set_abort_target: the control thread raises the kill flag through it."""
+        return C.cast(_lib.lib().srt_gpt2_request_abort, _vp), self._h
 
     @property
     def stream(self) -> int:

@@ -131,7 +131,8 @@ class ResNetStep:
         """images: host float32 [B,3,H,W] (numpy or CPU torch, ideally pinned); labels int64 [B]."""
         B = int(images.shape[0])
         images, labels = _host_contig(images, np.float32), _host_contig(labels, np.int64)
-        self._staged = (images, labels)  # keep the host buffers alive until the copy has run
+        # keep the host buffers of the last two uploads alive: their copies run asynchronously on the copy stream
+        self._staged = (getattr(self, '_staged', ()) + ((images, labels),))[-2:]
         call("srt_step_upload_batch", self._h, _host_ptr(images), _host_ptr(labels), B)
         return B
 

@@ -251,8 +251,12 @@ class _StubBase:
                          int(_Config.kill_batch_on_recv() if kill_batch_on_recv is None else kill_batch_on_recv),
                          int(_Config.train_mode == TrainMode.COLOCATE_L1), batch_size, poll_ms)
         self._h = C.c_void_p()
-        step_h = getattr(_step, '_h', None)
+        # the ResNet executor is known to the stub directly; any other step object names its kill entry point
+        target = _step.abort_target() if hasattr(_step, 'abort_target') else None
+        step_h = None if target else getattr(_step, '_h', None)
         call("srt_stub_create", _comm if _comm else None, step_h, _dist if _dist else None, C.byref(cfg), C.byref(self._h))
+        if target:
+            call("srt_stub_set_abort_target", self._h, target[0], target[1])
 
     @property
     def cmd(self):

@@ -183,3 +183,78 @@ def test_inference_mode_forward_uses_running_statistics():
     step.forward_infer(1)
     got = step.logits(1)
     assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
+
+
+def test_gpt2_batch_size_adjustment_on_inference_arrival():
+    """BASELINE config 4's control path on a small GPT-2: the trainer runs the torch_col loop on a pool-backed
+    Gpt2Step; an L1 adjust that names a smaller batch kills the micro-batch in flight (the control thread raises
+    the executor's flag through srt_stub_set_abort_target), the step keeps an activation set for the new batch size
+    and hands the other pages back, and training goes on with gradient accumulation so that every global batch still
+    sees all of its samples."""
+    from oracle import gpt2_oracle as GO
+    from sirius_b200 import torch_col as tc
+    from sirius_b200.gpt2_step import Gpt2Step
+    tag = f"{os.getpid()}_{uuid.uuid4().hex[:6]}"
+    os.environ.update({"COLTRAIN_MODE": "colocate-l1", "COLTRAIN_HOOK_MODE": "xsched-sync2", "COLTRAIN_USE_XSCHED": "1",
+                       "COLTRAIN_HAS_INFER_SERVER": "1", "COLTRAIN_USE_SHARED_TENSOR": "1", "COLTRAIN_KEEP_TARGET_SET": "1",
+                       "SIRIUS_B200_COMM_NAME": f"srt_gpt_comm_{tag}", "SIRIUS_B200_DIST_NAME": f"srt_gpt_dist_{tag}"})
+    cfg = dict(n_layer=2, n_head=4, d_model=128, vocab=30016, ctx=64)
+    BS, SEQ, DS, EPOCHS = 4, 64, 32, 2
+    model = GO.build_model(**cfg, seed=0)
+    srv = tc.DebugServer(1, os.environ["SIRIUS_B200_COMM_NAME"])
+    pool = PagePool(1.0, page_mb=2)
+    tc.setup_colocate_training(0, 1, False, False)
+    step = Gpt2Step(**cfg, max_batch=BS, seq=SEQ, pool=pool.handle)
+    step.load_state_dict(GO.state_arrays(model))
+    tc.set_train_step(step)
+    tc.set_memory_pool(pool.handle)
+    ctrl = tc.create_colocate_ctrl(tc.get_colocate_train_mode(), tc.get_colocate_ctrl_hook_mode(), EPOCHS, BS, stub_poll_ms=5)
+    ds, mgr = tc.init_dynamic_batch(DS, tc.DatasetType.TEXT_GEN, tc.TextDatasetConfig(SEQ), BS, global_batch_size=BS,
+                                    enable_grad_accumulate=True, checkpoint_micro_batch=True)
+    tc.init_train_info(BS, BS, "gpt2")
+    acc = tc.GradAccumulator(step)
+    state = {"n": 0, "cid": None, "mapped_before": None, "sizes": [], "losses": []}
+
+    def iter_train_fn(batch):
+        state["n"] += 1
+        n = len(batch)
+        step.upload_tokens(batch["input_ids"])
+        if state["n"] == 3 and state["cid"] is None:
+            state["mapped_before"] = pool.stat("train_all")
+            state["cid"] = srv.colocate_l1([2])            # the inference side needs memory: continue at batch 2
+            time.sleep(0.05)                               # the control thread raises the kill flag
+        try:
+            step.forward_backward(BS)
+        except SrtError as e:
+            if "aborted" in str(e):
+                raise tc.ColocateAdjustL1Exception("killed in the executor")
+            raise
+        ctrl.check_kill("after backward")
+        loss = step.loss()
+        mgr.optimizer_step(batch, step, grad_accumulator=acc)
+        state["sizes"].append(n)
+        state["losses"].append(loss)
+        return loss
+
+    trainer = tc.Trainer(step, iter_train_fn)
+    ctrl.train_start()
+    for e in range(EPOCHS):
+        trainer.train_one_epoch(e)
+    ctrl.train_end()
+    step.synchronize()
+    stat = trainer.get_overall_stat()
+    assert stat.killed_batch == 1
+    assert [m.id for _, m in srv.events(tc.CtrlEvent.kColocateAdjustL1Done)] == [state["cid"]]
+    released = ctrl.adjust_log[0][3]
+    assert released > 0 and released % pool.stat("page_nbytes") == 0
+    assert pool.stat("train_all") == state["mapped_before"] - released      # the pages stay with the pool
+    # before the adjust full batches, afterwards micro-batches of at most 2 that add up to every global batch
+    assert state["sizes"][:2] == [BS, BS] and max(state["sizes"][2:]) <= 2
+    assert sum(state["sizes"]) == DS * EPOCHS                               # every sample of every epoch trained once
+    assert [e.finished_sample for e in trainer.epoch_stats] == [DS] * EPOCHS
+    assert all(np.isfinite(state["losses"])) and ops.tc_status() == 0
+    step.close()
+    tc.cleanup_colocate_training(False)
+    tc.set_train_step(None)
+    pool.close()
+    srv.close()

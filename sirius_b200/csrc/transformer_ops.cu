@@ -188,16 +188,31 @@ colreduce_partial_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x
     }
   }
 }
+// Stage 2: block = 32 columns x 8 slab lanes; lane l adds slabs l, l + 8, ... in order, then the eight lane sums are
+// added in lane order (fixed shape: deterministic).
 __global__ void __launch_bounds__(NT)
 colreduce_final_kernel(const float* __restrict__ partial, int slabs, int nout, int C, float* __restrict__ out0,
                        float* __restrict__ out1) {
   pdl_enter();
-  const int c = blockIdx.x * NT + threadIdx.x;
-  if (c >= C) return;
-  for (int o = 0; o < nout; ++o) {
-    float t = 0.f;
-    for (int b = 0; b < slabs; ++b) t += partial[((size_t)b * nout + o) * C + c];
-    (o == 0 ? out0 : out1)[c] = t;
+  __shared__ float sh[2][8][33];
+  const int cl = threadIdx.x & 31, lane = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
+  float t0 = 0.f, t1 = 0.f;
+  if (c < C) {
+    for (int b = lane; b < slabs; b += 8) {
+      t0 += partial[((size_t)b * nout) * C + c];
+      if (nout == 2) t1 += partial[((size_t)b * nout + 1) * C + c];
+    }
+  }
+  sh[0][lane][cl] = t0;
+  sh[1][lane][cl] = t1;
+  __syncthreads();
+  if (lane == 0 && c < C) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) { a += sh[0][l][cl]; b += sh[1][l][cl]; }
+    out0[c] = a;
+    if (nout == 2) out1[c] = b;
   }
 }
 
@@ -674,26 +689,40 @@ window_softmax_bwd_kernel(const bf16* __restrict__ P, bf16* __restrict__ dP, int
 }
 // Gradient of the relative-position table. Stage 1: sum dS over the windows for every (head, i, j), in window
 // order; stage 2: add the (i, j) pairs that share a table entry, in (i, j) order.
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(512)
 relbias_grad_sum_kernel(const bf16* __restrict__ dS, float* __restrict__ dbias, int64_t windows, int heads, int L, int ld) {
   pdl_enter();
-  const int i = blockIdx.x % L, hd = blockIdx.x / L, j = threadIdx.x;
-  if (j >= L) return;
+  // block = (head, i); 64 columns x 8 window lanes; lane l adds windows l, l + 8, ... in order
+  __shared__ float sh[8][65];
+  const int i = blockIdx.x % L, hd = blockIdx.x / L;
+  const int j = threadIdx.x & 63, lane = threadIdx.x >> 6;
   float acc = 0.f;
-  for (int64_t w = 0; w < windows; ++w) acc += __bfloat162float(dS[((w * heads + hd) * L + i) * ld + j]);
-  dbias[((int64_t)hd * L + i) * L + j] = acc;
+  if (j < L)
+    for (int64_t w = lane; w < windows; w += 8) acc += __bfloat162float(dS[((w * heads + hd) * L + i) * ld + j]);
+  sh[lane][j] = acc;
+  __syncthreads();
+  if (lane == 0 && j < L) {
+    float t = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) t += sh[l][j];
+    dbias[((int64_t)hd * L + i) * L + j] = t;
+  }
 }
+// entry t = (dy, dx) of the table collects the pairs (i, j) with i - j = (dy, dx): at most L of them, walked in j order
 __global__ void __launch_bounds__(NT)
 relbias_grad_table_kernel(const float* __restrict__ dbias, float* __restrict__ dtable, int heads, int WS) {
   pdl_enter();
-  const int L = WS * WS, n_entries = (2 * WS - 1) * (2 * WS - 1);
+  const int L = WS * WS, side = 2 * WS - 1;
   const int idx = blockIdx.x * NT + threadIdx.x;
-  if (idx >= n_entries * heads) return;
+  if (idx >= side * side * heads) return;
   const int hd = idx % heads, t = idx / heads;
+  const int dy = t / side - (WS - 1), dx = t % side - (WS - 1);
   float acc = 0.f;
-  for (int i = 0; i < L; ++i)
-    for (int j = 0; j < L; ++j)
-      if (relpos_index(i, j, WS) == t) acc += dbias[((int64_t)hd * L + i) * L + j];
+  for (int jy = max(0, -dy); jy < min(WS, WS - dy); ++jy)
+    for (int jx = max(0, -dx); jx < min(WS, WS - dx); ++jx) {
+      const int j = jy * WS + jx, i = (jy + dy) * WS + jx + dx;
+      acc += dbias[((int64_t)hd * L + i) * L + j];
+    }
   dtable[idx] = acc;
 }
 
@@ -886,7 +915,7 @@ static int colreduce(int mode, const void* dy, const void* x, const float* mean,
     launch_pdl(colreduce_partial_kernel<1>, dim3(gx, (unsigned)slabs), dim3(NT), 0, st, (const bf16*)dy, (const bf16*)x, mean,
                rstd, rows, C, per, (float*)scratch);
   SRT_LAUNCH_CHECK();
-  launch_pdl(colreduce_final_kernel, dim3(ceil_div(C, NT)), dim3(NT), 0, st, (const float*)scratch, (int)slabs, nout, C, out0,
+  launch_pdl(colreduce_final_kernel, dim3(ceil_div(C, 32)), dim3(NT), 0, st, (const float*)scratch, (int)slabs, nout, C, out0,
              out1);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -1056,7 +1085,7 @@ int relbias_grad(const void* dS, float* dbias_scratch, float* dtable, int64_t wi
                  cudaStream_t st) {
   const int L = WS * WS;
   SRT_REQUIRE(L <= 64, "relbias_grad: window area above 64");
-  launch_pdl(relbias_grad_sum_kernel, dim3(heads * L), dim3(64), 0, st, (const bf16*)dS, dbias_scratch, windows, heads, L, ld);
+  launch_pdl(relbias_grad_sum_kernel, dim3(heads * L), dim3(512), 0, st, (const bf16*)dS, dbias_scratch, windows, heads, L, ld);
   SRT_LAUNCH_CHECK();
   launch_pdl(relbias_grad_table_kernel, dim3(ceil_div((2 * WS - 1) * (2 * WS - 1) * heads, NT)), dim3(NT), 0, st,
              (const float*)dbias_scratch, dtable, heads, WS);

@@ -71,6 +71,20 @@ struct Gpt2 {
   int act_batch = 0;
   float* ACC = nullptr;      // gradients accumulated over the micro-batches of a global batch
   int accum_pending = 0;
+  // Weight and bias gradients of a linear layer depend only on (dy, saved input): they run on a second,
+  // lowest-priority stream beside the data gradient and whatever follows it in the layer. The main stream waits for
+  // them before it overwrites a dy buffer they read (once per layer, before the layer's last kernel) and at the end.
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  bool side_dirty = false, overlap_wgrad = true;
+  void* scratch_side = nullptr;
+  int join_side() {
+    if (!side || !side_dirty) return SRT_OK;
+    side_dirty = false;
+    SRT_CHECK_CUDA(cudaEventRecord(ev_join, side));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
+    return SRT_OK;
+  }
   std::atomic<int> abort_flag{0};
   static constexpr int kAhead = 4;  // layers the host may run ahead of the GPU (bounds the drain after a kill)
   cudaEvent_t ahead_ev[kAhead] = {nullptr};
@@ -79,6 +93,9 @@ struct Gpt2 {
   ~Gpt2() {
     release_activations(nullptr);
     for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+    if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
     for (void* p : allocs) cudaFree(p);
     if (stream) cudaStreamDestroy(stream);
   }
@@ -96,6 +113,8 @@ struct Gpt2 {
   }
   int free_activation_blocks() {
     if (stream && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
+    if (side && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(side));  // an aborted backward never joined
+    side_dirty = false;
     for (void* p : act_blocks) {
       if (pool) { int rc = srt_pool_free(pool, SRT_POOL_TRAIN, p); if (rc) return rc; }
       else cudaFree(p);
@@ -183,9 +202,21 @@ struct Gpt2 {
   // dx = dy W, dW = dy^T x, db = column sums of dy
   int linear_bwd(const Lin& l, const void* dy, const void* x, void* dx, int64_t T) {
     int rc;
-    if ((rc = colsum_bf16(dy, T, l.out, gf(l.b), scratch, scratch_bytes, stream))) return rc;
-    if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, gf(l.w), scratch, scratch_bytes, stream)))
-      return rc;
+    cudaStream_t ws = stream;
+    void* wscratch = scratch;
+    if (side && overlap_wgrad) {
+      SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+      SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+      side_dirty = true;
+      ws = side;
+      wscratch = scratch_side;
+    }
+    {
+      PdlOff no_early_launch(ws != stream);
+      if ((rc = colsum_bf16(dy, T, l.out, gf(l.b), wscratch, scratch_bytes, ws))) return rc;
+      if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, gf(l.w), wscratch, scratch_bytes, ws)))
+        return rc;
+    }
     if (dx) return conv_dgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, WT + l.wt_off, dx, nullptr, stream);
     return SRT_OK;
   }
@@ -239,10 +270,18 @@ int Gpt2::build() {
   wg(C, 3 * C); wg(C, C); wg(C, 4 * C); wg(4 * C, C); wg(C, Vpad);
   scratch_bytes = sb;
   if ((rc = dalloc((char**)&scratch, scratch_bytes))) return rc;
+  if ((rc = dalloc((char**)&scratch_side, scratch_bytes))) return rc;
   if ((rc = dalloc(&ids, Tmax * 4)) || (rc = dalloc(&labels, Tmax * 4)) || (rc = dalloc(&order, Tmax * 4)) ||
       (rc = dalloc(&seg, (Tmax + 1) * 4)) || (rc = dalloc(&loss_acc, 256, true)))
     return rc;
   SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  {
+    int lo = 0, hi = 0;
+    SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    SRT_CHECK_CUDA(cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, lo));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+  }
   return alloc_activations(cfg.max_batch);
 }
 
@@ -288,6 +327,7 @@ int Gpt2::forward(int B) {
   const int64_t T = (int64_t)B * S;
   const float scale = 1.f / sqrtf((float)D);
   int rc;
+  if ((rc = join_side())) return rc;  // an aborted backward may have left weight-gradient kernels in flight
   if ((rc = embedding_fwd(ids, pf(wte), pf(wpe), x0, T, S, C, stream))) return rc;
   const __nv_bfloat16* x = x0;
   for (Layer& y : layers) {
@@ -326,8 +366,17 @@ int Gpt2::backward(int B, int global_batch) {
   // loss of this micro-batch: sum of the rows times gscale, done by summing then scaling on read
   if ((rc = sum_f32(row_loss, (int)T, loss_acc, 0, stream))) return rc;
   // tied projection: dwte = dlogits^T lnf(x); d lnf(x) = dlogits wte
-  if ((rc = conv_wgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, lnfo, gf(wte), scratch, scratch_bytes, stream)))
+  if (side && overlap_wgrad) {
+    SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+    side_dirty = true;
+    PdlOff no_early_launch(true);
+    if ((rc = conv_wgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, lnfo, gf(wte), scratch_side, scratch_bytes, side)))
+      return rc;
+  } else if ((rc = conv_wgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, lnfo, gf(wte), scratch, scratch_bytes,
+                              stream))) {
     return rc;
+  }
   if ((rc = conv_dgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, WT + wte_wt_off, dln, nullptr, stream))) return rc;
   const __nv_bfloat16* x_last = L > 0 ? layers[L - 1].xout : x0;
   if ((rc = layernorm_bwd(dln, x_last, pf(lnf_g), lnf_mean, lnf_rstd, nullptr, dxa, gf(lnf_g), gf(lnf_b), T, C, scratch,
@@ -372,11 +421,13 @@ int Gpt2::backward(int B, int global_batch) {
     if ((rc = bgemm_bf16(dk, Tbig, t2, dqkv + C, stream))) return rc;
     // fused projection and the first LayerNorm; dx becomes the gradient w.r.t. the layer's input
     if ((rc = linear_bwd(y.qkv, dqkv, y.ln1o, dln, T))) return rc;
+    if ((rc = join_side())) return rc;  // the next kernel overwrites dx, which this layer's first weight gradient read
     if ((rc = layernorm_bwd(dln, xin, pf(y.ln1_g), y.ln1_mean, y.ln1_rstd, dx_other, dx, gf(y.ln1_g), gf(y.ln1_b), T, C,
                             scratch, scratch_bytes, stream)))
       return rc;
   }
   // embedding tables (the token table already holds the output projection's share)
+  if ((rc = join_side())) return rc;
   return embedding_bwd(dx, ids, order, seg, n_unique, gf(wte), gf(wpe), B, S, C, stream);
 }
 

@@ -54,12 +54,29 @@ struct Qwen2 {
                 *dkv_h = nullptr, *dgu = nullptr, *dact = nullptr, *datt = nullptr, *dln = nullptr;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  // Weight and bias gradients of a linear layer depend only on (dy, saved input): they run on a second,
+  // lowest-priority stream beside the data gradient and whatever follows it in the layer. The main stream waits for
+  // them before it overwrites a dy buffer they read (once per layer, before the layer's last kernel) and at the end.
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  bool side_dirty = false, overlap_wgrad = true;
+  void* scratch_side = nullptr;
+  int join_side() {
+    if (!side || !side_dirty) return SRT_OK;
+    side_dirty = false;
+    SRT_CHECK_CUDA(cudaEventRecord(ev_join, side));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
+    return SRT_OK;
+  }
   int32_t *ids = nullptr, *labels = nullptr, *order = nullptr, *seg = nullptr;
   int n_unique = 0, cur_B = 0;
   std::vector<void*> allocs;
   size_t bytes_total = 0;
 
   ~Qwen2() {
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+    if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
     for (void* p : allocs) cudaFree(p);
     if (stream) cudaStreamDestroy(stream);
   }
@@ -99,9 +116,21 @@ struct Qwen2 {
   }
   int linear_bwd(const Lin& l, const void* dy, const void* x, void* dx, int64_t T) {
     int rc;
-    if (l.b_off >= 0 && (rc = colsum_bf16(dy, T, l.out, G + l.b_off, scratch, scratch_bytes, stream))) return rc;
-    if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, G + l.w_off, scratch, scratch_bytes, stream)))
-      return rc;
+    cudaStream_t ws = stream;
+    void* wscratch = scratch;
+    if (side && overlap_wgrad) {
+      SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+      SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+      side_dirty = true;
+      ws = side;
+      wscratch = scratch_side;
+    }
+    {
+      PdlOff no_early_launch(ws != stream);
+      if (l.b_off >= 0 && (rc = colsum_bf16(dy, T, l.out, G + l.b_off, wscratch, scratch_bytes, ws))) return rc;
+      if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, G + l.w_off, wscratch, scratch_bytes, ws)))
+        return rc;
+    }
     if (dx) return conv_dgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, WT + l.wt_off, dx, nullptr, stream);
     return SRT_OK;
   }
@@ -179,10 +208,18 @@ int Qwen2::build() {
   wg(C, QKV); wg(Hq * D, C); wg(C, 2 * F); wg(F, C); wg(C, Vpad);
   scratch_bytes = sb;
   if ((rc = dalloc((char**)&scratch, scratch_bytes))) return rc;
+  if ((rc = dalloc((char**)&scratch_side, scratch_bytes))) return rc;
   if ((rc = dalloc(&ids, T * 4)) || (rc = dalloc(&labels, T * 4)) || (rc = dalloc(&order, T * 4)) ||
       (rc = dalloc(&seg, (T + 1) * 4)))
     return rc;
   SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  {
+    int lo = 0, hi = 0;
+    SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    SRT_CHECK_CUDA(cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, lo));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+  }
   return SRT_OK;
 }
 
@@ -200,6 +237,7 @@ int Qwen2::forward(int B) {
   const int KO = Hq * D, VO = (Hq + Hkv) * D;  // column offsets of K and V inside the fused projection
   const long long SS = (long long)S * S;
   int rc;
+  if ((rc = join_side())) return rc;
   if ((rc = embedding_fwd(ids, pf(emb), nullptr, x0, T, S, C, stream))) return rc;
   const __nv_bfloat16* x = x0;
   for (Layer& y : layers) {
@@ -234,8 +272,17 @@ int Qwen2::backward(int B, int global_batch) {
   const float gscale = 1.f / ((float)global_batch * (float)(S - 1));
   if ((rc = lm_cross_entropy(logits, labels, T, V, Vpad, gscale, row_loss, stream))) return rc;
   if ((rc = sum_f32(row_loss, (int)T, loss_acc, 0, stream))) return rc;
-  if ((rc = conv_wgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, nfo, gf(emb), scratch, scratch_bytes, stream)))
+  if (side && overlap_wgrad) {
+    SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+    side_dirty = true;
+    PdlOff no_early_launch(true);
+    if ((rc = conv_wgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, nfo, gf(emb), scratch_side, scratch_bytes, side)))
+      return rc;
+  } else if ((rc = conv_wgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, nfo, gf(emb), scratch, scratch_bytes,
+                              stream))) {
     return rc;
+  }
   if ((rc = conv_dgrad(lin_desc(T, C, Vpad), SRT_BF16, SRT_IMPL_AUTO, logits, WT + emb_wt_off, dln, nullptr, stream))) return rc;
   const __nv_bfloat16* x_last = L > 0 ? layers[L - 1].xout : x0;
   if ((rc = rmsnorm_bwd(dln, x_last, pf(nf), zf, rf, nullptr, dxa, gf(nf), T, C, scratch, scratch_bytes, stream))) return rc;
@@ -277,9 +324,11 @@ int Qwen2::backward(int B, int global_batch) {
     if ((rc = rope_apply(dqkv, T, S, Hq, D, QKV, cfg.rope_theta, 1, stream))) return rc;
     if ((rc = rope_apply(dqkv + KO, T, S, Hkv, D, QKV, cfg.rope_theta, 1, stream))) return rc;
     if ((rc = linear_bwd(y.qkv, dqkv, y.n1o, dln, T))) return rc;
+    if ((rc = join_side())) return rc;  // the next kernel overwrites dx, which this layer's first weight gradient read
     if ((rc = rmsnorm_bwd(dln, xin, pf(y.n1), y.z1, y.r1, dx_other, dx, gf(y.n1), T, C, scratch, scratch_bytes, stream)))
       return rc;
   }
+  if ((rc = join_side())) return rc;
   return embedding_bwd(dx, ids, order, seg, n_unique, gf(emb), nullptr, B, S, C, stream);
 }
 

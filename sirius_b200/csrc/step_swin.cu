@@ -67,6 +67,20 @@ struct Swin {
   __nv_bfloat16 *dxa = nullptr, *dxb = nullptr, *dqkv = nullptr, *dP = nullptr, *tP = nullptr, *tA = nullptr, *tB = nullptr,
                 *dOh = nullptr, *dqw = nullptr, *dkw = nullptr, *dvw = nullptr, *dh = nullptr, *dg = nullptr, *datt = nullptr,
                 *dln = nullptr, *ow = nullptr, *dpool = nullptr;
+  // Weight and bias gradients of a linear layer depend only on (dy, saved input): they run on a second,
+  // lowest-priority stream beside the data gradient and whatever follows it in the layer. The main stream waits for
+  // them before it overwrites a dy buffer they read (once per layer, before the layer's last kernel) and at the end.
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  bool side_dirty = false, overlap_wgrad = true;
+  void* scratch_side = nullptr;
+  int join_side() {
+    if (!side || !side_dirty) return SRT_OK;
+    side_dirty = false;
+    SRT_CHECK_CUDA(cudaEventRecord(ev_join, side));
+    SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
+    return SRT_OK;
+  }
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   std::vector<void*> allocs;
@@ -74,6 +88,9 @@ struct Swin {
   int cur_B = 0, last_global = 0;
 
   ~Swin() {
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+    if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
     for (void* p : allocs) cudaFree(p);
     if (stream) cudaStreamDestroy(stream);
   }
@@ -116,9 +133,21 @@ struct Swin {
   }
   int linear_bwd(const Lin& l, const void* dy, const void* x, void* dx, int64_t T) {
     int rc;
-    if (l.b >= 0 && (rc = colsum_bf16(dy, T, l.out, gf(l.b), scratch, scratch_bytes, stream))) return rc;
-    if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, gf(l.w), scratch, scratch_bytes, stream)))
-      return rc;
+    cudaStream_t ws = stream;
+    void* wscratch = scratch;
+    if (side && overlap_wgrad) {
+      SRT_CHECK_CUDA(cudaEventRecord(ev_fork, stream));
+      SRT_CHECK_CUDA(cudaStreamWaitEvent(side, ev_fork, 0));
+      side_dirty = true;
+      ws = side;
+      wscratch = scratch_side;
+    }
+    {
+      PdlOff no_early_launch(ws != stream);
+      if (l.b >= 0 && (rc = colsum_bf16(dy, T, l.out, gf(l.b), wscratch, scratch_bytes, ws))) return rc;
+      if ((rc = conv_wgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, x, gf(l.w), wscratch, scratch_bytes, ws)))
+        return rc;
+    }
     if (dx) return conv_dgrad(lin_desc(T, l.in, l.out), SRT_BF16, SRT_IMPL_AUTO, dy, WT + l.wt_off, dx, nullptr, stream);
     return SRT_OK;
   }
@@ -237,7 +266,15 @@ int Swin::build() {
   wg(lin_desc((int64_t)B, Cf, cfg.num_classes));
   scratch_bytes = sb;
   if ((rc = dalloc((char**)&scratch, scratch_bytes))) return rc;
+  if ((rc = dalloc((char**)&scratch_side, scratch_bytes))) return rc;
   SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  {
+    int lo = 0, hi = 0;
+    SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    SRT_CHECK_CUDA(cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, lo));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+    SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+  }
   return SRT_OK;
 }
 
@@ -318,6 +355,7 @@ int Swin::block_bwd(Blk& k, const __nv_bfloat16* xin, __nv_bfloat16*& dx, __nv_b
   if ((rc = bgemm_bf16(dq, tP, tB, dkw, stream))) return rc;
   if ((rc = window_qkv(dqkv, dqw, dkw, dvw, w, Hh, D, 1, stream))) return rc;
   if ((rc = linear_bwd(k.qkv, dqkv, k.ln1o, dln, T))) return rc;
+  if ((rc = join_side())) return rc;  // the next kernel overwrites dx, which this block's first weight gradient read
   return layernorm_bwd(dln, xin, pf(k.n1g), k.m1, k.r1, dx_other, dx, gf(k.n1g), gf(k.n1b), T, C, scratch, scratch_bytes,
                        stream);
 }
@@ -325,6 +363,7 @@ int Swin::block_bwd(Blk& k, const __nv_bfloat16* xin, __nv_bfloat16*& dx, __nv_b
 int Swin::forward(int B) {
   const int S0 = cfg.image / cfg.patch;
   int rc;
+  if ((rc = join_side())) return rc;
   if ((rc = nchw_to_nhwc(SRT_BF16, stage_images, x_img, B, 3, cfg.image, cfg.image, 8, stream))) return rc;
   srt_conv_epilogue ep = {pf(pe_b), nullptr};
   if ((rc = conv_fprop(pe_desc(B), SRT_BF16, SRT_IMPL_AUTO, x_img, pw(pe_w), e0, &ep, stream))) return rc;
@@ -380,10 +419,12 @@ int Swin::backward(int B, int global_batch) {
       if ((rc = layernorm_bwd(dln, m.merged, pf(m.ng), m.m, m.r, nullptr, dh, gf(m.ng), gf(m.nb), T, 4 * m.C, scratch,
                               scratch_bytes, stream)))
         return rc;
+      if ((rc = join_side())) return rc;  // dx was read by the reduction's weight gradient
       if ((rc = patch_merge(dh, dx, B, m.Hs, m.Hs, m.C, 1, stream))) return rc;   // back to the finer map
     }
   }
   // patch embedding: LayerNorm, then the convolution's filter and bias gradients
+  if ((rc = join_side())) return rc;
   const int S0 = cfg.image / cfg.patch;
   const int64_t T0 = (int64_t)B * S0 * S0;
   if ((rc = layernorm_bwd(dx, e0, pf(pe_ng), pe_m, pe_r, nullptr, dx_other, gf(pe_ng), gf(pe_nb), T0, cfg.embed, scratch,

@@ -228,3 +228,27 @@ def test_against_the_committed_golden_fixture(case):
             assert abs(a[i] - v) <= 2e-2 * max(abs(v), scale) + 2 * lr * steps * 1.01, (n, i, a[i], v)
     assert ops.tc_status() == 0
     step.close()
+
+
+@pytest.mark.parametrize("B,S,max_batch", [(1, 72, 3), (3, 40, 3)])
+def test_ragged_sizes_partial_batches_and_short_sequences(B, S, max_batch):
+    """Fewer sequences than the step was created for, sequence lengths that are not a multiple of the 128-row tile
+    (so every GEMM has a ragged last tile and attention a partial diagonal block), a vocabulary that is not a
+    multiple of 64: same parity as the regular case."""
+    cfg = dict(n_layer=2, n_head=2, d_model=64, vocab=333, ctx=80)
+    model = O.build_model(**cfg, seed=3)
+    ids = O.make_tokens(B, S, cfg["vocab"], 1, seed=5)[0]
+    step = Gpt2Step(**cfg, max_batch=max_batch, seq=S)
+    step.load_state_dict(O.state_arrays(model))
+    step.upload_tokens(ids)
+    step.forward_only()
+    assert rel(step.logits(), O.forward_logits(model, ids).reshape(B * S, -1)) < 2e-2
+    loss_ref, grads = O.first_step_gradients(model, ids)
+    step.forward_backward()
+    assert abs(step.loss() - loss_ref) < 2e-2 * abs(loss_ref)
+    top = max(float(np.linalg.norm(g)) for g in grads.values())
+    bad = [(round(rel(step.get(n, GET_GRAD), g), 4), n) for n, g in grads.items()
+           if np.linalg.norm(g) > 1e-3 * top and rel(step.get(n, GET_GRAD), g) >= 5e-2]
+    assert not bad, sorted(bad)[-8:]
+    assert ops.tc_status() == 0
+    step.close()

@@ -108,3 +108,24 @@ def test_against_the_committed_golden_fixture(case):
             assert abs(a[i] - v) <= 2e-2 * max(abs(v), scale) + 2 * lr * steps * 1.01, (n, i, a[i], v)
     assert ops.tc_status() == 0
     step.close()
+
+
+def test_partial_batch_on_a_larger_step_object():
+    """A micro-batch smaller than max_batch (what the dynamic batch manager hands out after an adjust)."""
+    B = 1
+    model = O.build_model(**TINY, seed=0)
+    batch = O.make_batches(B, 1, TINY["image"], TINY["num_classes"], seed=7)[0]
+    step = SwinStep(**TINY, max_batch=3)
+    step.load_state_dict(O.state_arrays(model))
+    step.upload_batch(batch[0].contiguous(), batch[1].contiguous())
+    step.forward_only()
+    assert rel(step.logits(), O.forward_logits(model, batch[0])) < 3e-2
+    loss_ref, grads = O.first_step_gradients(model, batch)
+    step.forward_backward()
+    assert abs(step.loss() - loss_ref) < 2e-2 * abs(loss_ref)
+    top = max(float(np.linalg.norm(g)) for g in grads.values())
+    bad = [(round(rel(step.get(n, GET_GRAD), g), 4), n) for n, g in grads.items()
+           if np.linalg.norm(g) > 1e-3 * top and rel(step.get(n, GET_GRAD), g) >= 6e-2]
+    assert not bad, sorted(bad)[-8:]
+    assert ops.tc_status() == 0
+    step.close()

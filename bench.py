@@ -319,6 +319,23 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def make_overlapped_allreduce(step, grad_t, torch, dist):
+    """All-reduce of the flat gradient buffer bucket by bucket on a communication stream that waits for each bucket's
+    ready event (recorded by the executor during backward); the executor's stream waits for the last one."""
+    comm_stream = torch.cuda.Stream()
+    buckets = step.grad_buckets()
+    done_ev = torch.cuda.Event()
+
+    def allreduce():
+        for b, (off, cnt) in enumerate(buckets):
+            step.wait_grad_bucket(b, comm_stream.cuda_stream)
+            with torch.cuda.stream(comm_stream):
+                dist.all_reduce(grad_t[off:off + cnt])
+        done_ev.record(comm_stream)
+        step.wait_event(done_ev.cuda_event)
+    return allreduce
+
+
 # ---- second workload: GPT-2 small (BASELINE config 4), selected with --workload gpt2 -----------------
 GPT2 = dict(n_layer=12, n_head=12, d_model=768, vocab=50257, ctx=1024)
 GPT2_BATCH, GPT2_SEQ = 8, 1024
@@ -393,14 +410,14 @@ def run_lm(args, kind):
         with torch.cuda.stream(stream):
             dist.all_reduce(grad_t)
         torch.cuda.synchronize()
+    allreduce = make_overlapped_allreduce(step, grad_t, torch, dist) if grad_t is not None else None
 
     def one(i, upload):
         if upload:
             step.upload_tokens(host[i % 2])
         step.forward_backward(global_bs)
-        if grad_t is not None:
-            with torch.cuda.stream(stream):
-                dist.all_reduce(grad_t)
+        if allreduce is not None:
+            allreduce()
         step.optimizer_step()
         return step.loss() if upload else None
 
@@ -521,14 +538,14 @@ def run_swin(args):
         with torch.cuda.stream(stream):
             dist.all_reduce(grad_t)
         torch.cuda.synchronize()
+    allreduce = make_overlapped_allreduce(step, grad_t, torch, dist) if grad_t is not None else None
 
     def one(i, upload):
         if upload:
             step.upload_batch(*host[i % 2])
         step.forward_backward(global_bs)
-        if grad_t is not None:
-            with torch.cuda.stream(stream):
-                dist.all_reduce(grad_t)
+        if allreduce is not None:
+            allreduce()
         step.optimizer_step()
         return step.loss() if upload else None
 

@@ -433,6 +433,19 @@ int srt_qwen2_grad_buffer(srt_qwen2* g, void** ptr, int64_t* n);
 void* srt_qwen2_stream(srt_qwen2* g);
 int64_t srt_qwen2_memory_bytes(srt_qwen2* g);
 
+/* Gradient buckets of the transformer executors, for an all-reduce overlapped with backward (as srt_step_grad_bucket
+ * and friends do for the ResNet executor): srt_<model>_grad_buckets returns the executor's bucket list; buckets are
+ * ranges of its flat gradient buffer in the order backward completes them. After forward_backward has returned, make
+ * the communication stream wait for bucket i (srt_gb_wait), enqueue its all-reduce there, and finally make the
+ * executor's stream (srt_<model>_stream) wait for an event recorded behind the last one (srt_stream_wait_event). */
+void* srt_gpt2_grad_buckets(srt_gpt2* g);
+void* srt_swin_grad_buckets(srt_swin* s);
+void* srt_qwen2_grad_buckets(srt_qwen2* g);
+int srt_gb_count(void* buckets);
+int srt_gb_get(void* buckets, int i, int64_t* offset, int64_t* count);
+int srt_gb_wait(void* buckets, int i, void* stream);
+int srt_stream_wait_event(void* stream, void* cuda_event);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "conv_geom.cuh"
+#include "grad_buckets.cuh"
 #include "ops.cuh"
 
 namespace srt {
@@ -360,6 +361,26 @@ int srt_lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int 
                          float* row_loss, void* stream) {
   SRT_REQUIRE(logits && labels && row_loss, "lm_cross_entropy: null argument");
   return lm_cross_entropy(logits, labels, rows, V, ld, grad_scale, row_loss, (cudaStream_t)stream);
+}
+
+int srt_gb_count(void* gb) { return gb ? (int)((GradBuckets*)gb)->list.size() : -1; }
+int srt_gb_get(void* gb, int i, int64_t* offset, int64_t* count) {
+  GradBuckets* b = (GradBuckets*)gb;
+  SRT_REQUIRE(b && offset && count && i >= 0 && i < (int)b->list.size(), "gb_get: bad argument");
+  *offset = (int64_t)b->list[i].off;
+  *count = (int64_t)b->list[i].count;
+  return SRT_OK;
+}
+int srt_gb_wait(void* gb, int i, void* stream) {
+  GradBuckets* b = (GradBuckets*)gb;
+  SRT_REQUIRE(b && i >= 0 && i < (int)b->list.size(), "gb_wait: bad argument");
+  SRT_CHECK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, b->list[i].ev, 0));
+  return SRT_OK;
+}
+int srt_stream_wait_event(void* stream, void* event) {
+  SRT_REQUIRE(event, "stream_wait_event: null event");
+  SRT_CHECK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+  return SRT_OK;
 }
 
 }  // extern "C"

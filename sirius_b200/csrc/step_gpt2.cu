@@ -20,6 +20,7 @@
 #include "../../include/sirius_pool.h"
 #include <atomic>
 #include "common.cuh"
+#include "grad_buckets.cuh"
 #include "ops.cuh"
 
 namespace srt {
@@ -85,6 +86,7 @@ struct Gpt2 {
     SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
     return SRT_OK;
   }
+  GradBuckets buckets;
   std::atomic<int> abort_flag{0};
   static constexpr int kAhead = 4;  // layers the host may run ahead of the GPU (bounds the drain after a kill)
   cudaEvent_t ahead_ev[kAhead] = {nullptr};
@@ -274,6 +276,11 @@ int Gpt2::build() {
   if ((rc = dalloc(&ids, Tmax * 4)) || (rc = dalloc(&labels, Tmax * 4)) || (rc = dalloc(&order, Tmax * 4)) ||
       (rc = dalloc(&seg, (Tmax + 1) * 4)) || (rc = dalloc(&loss_acc, 256, true)))
     return rc;
+  {
+    std::vector<size_t> starts;
+    for (Layer& y : layers) starts.push_back(params[y.ln1_g].off);
+    if ((rc = buckets.build(starts, n_flat, (size_t)25 << 18))) return rc;  // 25 MiB of fp32 gradients per bucket
+  }
   SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   {
     int lo = 0, hi = 0;
@@ -360,6 +367,7 @@ int Gpt2::backward(int B, int global_batch) {
   const int64_t T = (int64_t)B * S;
   const float scale = 1.f / sqrtf((float)D);
   int rc;
+  buckets.begin_backward();
   // mean over the (S - 1) targets of every sequence of the global batch (micro-batches add up to it)
   const float gscale = 1.f / ((float)global_batch * (float)(S - 1));
   if ((rc = lm_cross_entropy(logits, labels, T, V, Vpad, gscale, row_loss, stream))) return rc;
@@ -425,10 +433,12 @@ int Gpt2::backward(int B, int global_batch) {
     if ((rc = layernorm_bwd(dln, xin, pf(y.ln1_g), y.ln1_mean, y.ln1_rstd, dx_other, dx, gf(y.ln1_g), gf(y.ln1_b), T, C,
                             scratch, scratch_bytes, stream)))
       return rc;
+    if ((rc = buckets.unit_done(i, stream))) return rc;
   }
   // embedding tables (the token table already holds the output projection's share)
   if ((rc = join_side())) return rc;
-  return embedding_bwd(dx, ids, order, seg, n_unique, gf(wte), gf(wpe), B, S, C, stream);
+  if ((rc = embedding_bwd(dx, ids, order, seg, n_unique, gf(wte), gf(wpe), B, S, C, stream))) return rc;
+  return buckets.all_done(stream);
 }
 
 }  // namespace srt
@@ -638,6 +648,8 @@ int srt_gpt2_request_abort(srt_gpt2* h, int on) {
   g->abort_flag.store(on ? 1 : 0, std::memory_order_release);
   return SRT_OK;
 }
+
+void* srt_gpt2_grad_buckets(srt_gpt2* h) { return h ? (void*)&((Gpt2*)h)->buckets : nullptr; }
 
 int srt_gpt2_grad_buffer(srt_gpt2* h, void** ptr, int64_t* n) {
   Gpt2* g = (Gpt2*)h;

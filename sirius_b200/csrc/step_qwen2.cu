@@ -17,6 +17,7 @@
 
 #include "../../include/sirius_b200.h"
 #include "common.cuh"
+#include "grad_buckets.cuh"
 #include "ops.cuh"
 
 namespace srt {
@@ -68,6 +69,7 @@ struct Qwen2 {
     SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
     return SRT_OK;
   }
+  GradBuckets buckets;
   int32_t *ids = nullptr, *labels = nullptr, *order = nullptr, *seg = nullptr;
   int n_unique = 0, cur_B = 0;
   std::vector<void*> allocs;
@@ -212,6 +214,11 @@ int Qwen2::build() {
   if ((rc = dalloc(&ids, T * 4)) || (rc = dalloc(&labels, T * 4)) || (rc = dalloc(&order, T * 4)) ||
       (rc = dalloc(&seg, (T + 1) * 4)))
     return rc;
+  {
+    std::vector<size_t> starts;
+    for (Layer& y : layers) starts.push_back(params[y.n1].off);
+    if ((rc = buckets.build(starts, n_flat, (size_t)25 << 18))) return rc;
+  }
   SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   {
     int lo = 0, hi = 0;
@@ -269,6 +276,7 @@ int Qwen2::backward(int B, int global_batch) {
   const int KO = Hq * D, VO = (Hq + Hkv) * D;
   const long long SS = (long long)S * S;
   int rc;
+  buckets.begin_backward();
   const float gscale = 1.f / ((float)global_batch * (float)(S - 1));
   if ((rc = lm_cross_entropy(logits, labels, T, V, Vpad, gscale, row_loss, stream))) return rc;
   if ((rc = sum_f32(row_loss, (int)T, loss_acc, 0, stream))) return rc;
@@ -327,9 +335,11 @@ int Qwen2::backward(int B, int global_batch) {
     if ((rc = join_side())) return rc;  // the next kernel overwrites dx, which this layer's first weight gradient read
     if ((rc = rmsnorm_bwd(dln, xin, pf(y.n1), y.z1, y.r1, dx_other, dx, gf(y.n1), T, C, scratch, scratch_bytes, stream)))
       return rc;
+    if ((rc = buckets.unit_done(i, stream))) return rc;
   }
   if ((rc = join_side())) return rc;
-  return embedding_bwd(dx, ids, order, seg, n_unique, gf(emb), nullptr, B, S, C, stream);
+  if ((rc = embedding_bwd(dx, ids, order, seg, n_unique, gf(emb), nullptr, B, S, C, stream))) return rc;
+  return buckets.all_done(stream);
 }
 
 }  // namespace srt
@@ -480,6 +490,8 @@ int srt_qwen2_synchronize(srt_qwen2* h) {
   SRT_CHECK_CUDA(cudaStreamSynchronize(g->stream));
   return SRT_OK;
 }
+
+void* srt_qwen2_grad_buckets(srt_qwen2* h) { return h ? (void*)&((Qwen2*)h)->buckets : nullptr; }
 
 int srt_qwen2_grad_buffer(srt_qwen2* h, void** ptr, int64_t* n) {
   Qwen2* g = (Qwen2*)h;

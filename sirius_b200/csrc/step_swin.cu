@@ -16,6 +16,7 @@
 
 #include "../../include/sirius_b200.h"
 #include "common.cuh"
+#include "grad_buckets.cuh"
 #include "ops.cuh"
 
 namespace srt {
@@ -81,6 +82,7 @@ struct Swin {
     SRT_CHECK_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
     return SRT_OK;
   }
+  GradBuckets buckets;      // units: the blocks in forward order, each stage's patch merging counted with its last block
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   std::vector<void*> allocs;
@@ -267,6 +269,11 @@ int Swin::build() {
   scratch_bytes = sb;
   if ((rc = dalloc((char**)&scratch, scratch_bytes))) return rc;
   if ((rc = dalloc((char**)&scratch_side, scratch_bytes))) return rc;
+  {
+    std::vector<size_t> starts;
+    for (Blk& k : blocks) starts.push_back(params[k.n1g].off);
+    if ((rc = buckets.build(starts, n_flat, (size_t)25 << 18))) return rc;
+  }
   SRT_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   {
     int lo = 0, hi = 0;
@@ -395,6 +402,7 @@ int Swin::forward(int B) {
 int Swin::backward(int B, int global_batch) {
   int rc;
   last_global = global_batch;
+  buckets.begin_backward();
   if ((rc = softmax_ce(SRT_BF16, logits, stage_labels, B, cfg.num_classes, 1.f / (float)global_batch, row_loss, dlogits, stream)))
     return rc;
   if ((rc = sum_f32(row_loss, B, loss_acc, 0, stream))) return rc;
@@ -411,6 +419,7 @@ int Swin::backward(int B, int global_batch) {
     for (int i = stage_end[s] - 1; i >= first; --i) {
       const __nv_bfloat16* xin = i > first ? blocks[i - 1].xout : (s == 0 ? x0 : merges[s - 1].out);
       if ((rc = block_bwd(blocks[i], xin, dx, dx_other, B))) return rc;
+      if ((rc = buckets.unit_done(i, stream))) return rc;
     }
     if (s > 0) {
       Merge& m = merges[s - 1];
@@ -431,7 +440,8 @@ int Swin::backward(int B, int global_batch) {
                           scratch_bytes, stream)))
     return rc;
   if ((rc = colsum_bf16(dx_other, T0, cfg.embed, gf(pe_b), scratch, scratch_bytes, stream))) return rc;
-  return conv_wgrad(pe_desc(B), SRT_BF16, SRT_IMPL_AUTO, dx_other, x_img, gf(pe_w), scratch, scratch_bytes, stream);
+  if ((rc = conv_wgrad(pe_desc(B), SRT_BF16, SRT_IMPL_AUTO, dx_other, x_img, gf(pe_w), scratch, scratch_bytes, stream))) return rc;
+  return buckets.all_done(stream);
 }
 
 }  // namespace srt
@@ -588,6 +598,8 @@ int srt_swin_synchronize(srt_swin* h) {
   SRT_CHECK_CUDA(cudaStreamSynchronize(g->stream));
   return SRT_OK;
 }
+
+void* srt_swin_grad_buckets(srt_swin* h) { return h ? (void*)&((Swin*)h)->buckets : nullptr; }
 
 int srt_swin_grad_buffer(srt_swin* h, void** ptr, int64_t* n) {
   Swin* g = (Swin*)h;

@@ -62,8 +62,43 @@ register({
 
 GET_VALUE, GET_GRAD, GET_MOMENTUM = 0, 1, 3
 
+register({
+    "srt_gpt2_grad_buckets": (_vp, [_vp]),
+    "srt_swin_grad_buckets": (_vp, [_vp]),
+    "srt_qwen2_grad_buckets": (_vp, [_vp]),
+    "srt_gb_count": (_i, [_vp]),
+    "srt_gb_get": (None, [_vp, _i, C.POINTER(_i64), C.POINTER(_i64)]),
+    "srt_gb_wait": (None, [_vp, _i, _vp]),
+    "srt_stream_wait_event": (None, [_vp, _vp]),
+})
 
-class Gpt2Step:
+
+class GradBucketsMixin:
+    """Bucketed gradient exchange overlapped with backward; `_buckets_fn` names the C accessor of the executor."""
+    _buckets_fn = None
+
+    def _gb(self):
+        return getattr(_lib.lib(), self._buckets_fn)(self._h)
+
+    def grad_buckets(self):
+        gb = self._gb()
+        out = []
+        for i in range(_lib.lib().srt_gb_count(gb)):
+            off, cnt = _i64(), _i64()
+            call("srt_gb_get", gb, i, C.byref(off), C.byref(cnt))
+            out.append((off.value, cnt.value))
+        return out
+
+    def wait_grad_bucket(self, i: int, cuda_stream: int) -> None:
+        call("srt_gb_wait", self._gb(), i, C.c_void_p(cuda_stream))
+
+    def wait_event(self, cuda_event: int) -> None:
+        call("srt_stream_wait_event", C.c_void_p(self.stream), C.c_void_p(cuda_event))
+
+
+class Gpt2Step(GradBucketsMixin):
+    _buckets_fn = "srt_gpt2_grad_buckets"
+
     """`Gpt2Step(n_layer, n_head, d_model, vocab, ctx, max_batch, seq)`; parameters use the names and shapes of
     `transformers.GPT2LMHeadModel.state_dict()` (`lm_head.weight` is the tied token table and is not listed)."""
 

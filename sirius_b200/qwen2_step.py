@@ -8,6 +8,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import call, register
+from .gpt2_step import GradBucketsMixin
 
 _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
@@ -42,7 +43,9 @@ GET_VALUE, GET_GRAD, GET_MOMENTUM = 0, 1, 3
 QWEN2_05B = dict(n_layer=24, n_head=14, n_kv_head=2, hidden=896, intermediate=4864, vocab=151936)
 
 
-class Qwen2Step:
+class Qwen2Step(GradBucketsMixin):
+    _buckets_fn = "srt_qwen2_grad_buckets"
+
     """`Qwen2Step(**QWEN2_05B, max_batch=4, seq=2048)`; parameters use the names and shapes of
     `transformers.Qwen2ForCausalLM.state_dict()` (`lm_head.weight` is the tied token table and is not listed)."""
 

@@ -8,6 +8,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import call, register
+from .gpt2_step import GradBucketsMixin
 
 _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
@@ -42,7 +43,9 @@ GET_VALUE, GET_GRAD, GET_MOMENTUM = 0, 1, 3
 SWIN_B = dict(image=224, patch=4, embed=128, depths=(2, 2, 18, 2), heads=(4, 8, 16, 32), window=7, num_classes=1000)
 
 
-class SwinStep:
+class SwinStep(GradBucketsMixin):
+    _buckets_fn = "srt_swin_grad_buckets"
+
     """`SwinStep(**SWIN_B, max_batch=32)`; parameters use the names and shapes of torchvision's `swin_b().state_dict()`
     (the `relative_position_index` buffers are derived, not parameters)."""
 

@@ -252,3 +252,43 @@ def test_ragged_sizes_partial_batches_and_short_sequences(B, S, max_batch):
     assert not bad, sorted(bad)[-8:]
     assert ops.tc_status() == 0
     step.close()
+
+
+def test_gradient_buckets_tile_the_buffer_and_fire_when_final():
+    """As for the ResNet executor: the buckets cover the flat gradient buffer once, last layers first, and a stream
+    that waits for a bucket's event copies that bucket's final values while backward is still running."""
+    cfg = dict(n_layer=6, n_head=4, d_model=512, vocab=5000, ctx=128)      # ~3 M gradients per layer: several buckets
+    B, S = 2, 128
+    model = O.build_model(**cfg, seed=0)
+    ids = O.make_tokens(B, S, cfg["vocab"], 1)[0]
+    step = Gpt2Step(**cfg, max_batch=B, seq=S)
+    step.load_state_dict(O.state_arrays(model))
+    ptr, n = step.grad_buffer()
+    buckets = step.grad_buckets()
+    assert len(buckets) >= 2 and buckets[0][0] + buckets[0][1] == n and buckets[-1][0] == 0
+    for (o0, c0), (o1, c1) in zip(buckets, buckets[1:]):
+        assert o1 + c1 == o0
+
+    class Buf:
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+    grad = torch.as_tensor(Buf(), device="cuda:0")
+    comm = torch.cuda.Stream()
+    step.upload_tokens(ids)
+    for _ in range(2):
+        grad.zero_()
+        torch.cuda.synchronize()
+        step.forward_backward()
+        copies = []
+        for b, (off, cnt) in enumerate(buckets):
+            step.wait_grad_bucket(b, comm.cuda_stream)
+            with torch.cuda.stream(comm):
+                copies.append(grad[off:off + cnt].clone())
+        done = torch.cuda.Event()
+        done.record(comm)
+        step.wait_event(done.cuda_event)
+        step.synchronize()
+        torch.cuda.synchronize()
+        for (off, cnt), c in zip(buckets, copies):
+            assert torch.equal(c, grad[off:off + cnt])
+        assert float(grad.abs().sum()) > 0
+    step.close()

@@ -52,6 +52,7 @@ int sm_limit();                  // 0 = none
 void set_sm_limit(int n);        // per thread: a step that runs inside an SM partition sets its width
 // Stream of the widest green-context partition with at most `allowed` SMs (nullptr = whole device).
 int partition_stream(int device, int allowed, cudaStream_t* stream, int* sms);
+int partition_streams(int device, int allowed, cudaStream_t* stream, cudaStream_t* side, int* sms);
 
 // ---- element type traits ---------------------------------------------------------------
 template <typename T> struct ElemTraits;

@@ -4,7 +4,7 @@
 // stream before every launch (common/sm_partition.cu:316-336, SetStreamTpcMask), so that inference
 // kernels always find idle SMs. Here the same effect comes from CUDA green contexts: for a ladder of
 // SM counts the device's SM resource is split once (cuDevSmResourceSplitByCount), a green context is
-// created on each group and one stream on each green context. A kernel launched on such a stream can
+// created on each group and two streams (a main one and a low-priority companion) on each green context. A kernel launched on such a stream can
 // only be scheduled on the SMs of its group. Following the mask then means: between two launches,
 // move to the stream of the widest group that does not exceed the allowed SM count (an event orders
 // the new stream after the old one). Nothing is poked, no kernel has to cooperate.
@@ -34,6 +34,7 @@ struct Rung {
   int sms = 0;
   CUgreenCtx ctx = nullptr;
   cudaStream_t stream = nullptr;
+  cudaStream_t side = nullptr;  // second stream on the same SMs, lowest priority (overlapped weight gradients)
 };
 
 struct Ladder {
@@ -90,6 +91,10 @@ int build_ladder(int device, int stride, Ladder& L) {
     CUstream st;
     CU_TRY(f_stream(&st, r.ctx, CU_STREAM_NON_BLOCKING, 0));
     r.stream = (cudaStream_t)st;
+    int lo = 0, hi = 0;
+    SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CU_TRY(f_stream(&st, r.ctx, CU_STREAM_NON_BLOCKING, lo));
+    r.side = (cudaStream_t)st;
     L.rungs.push_back(r);
     last = got;
   }
@@ -103,7 +108,13 @@ void set_sm_limit(int n) { tl_sm_limit = n; }
 
 // Stream of the widest rung with at most `allowed` SMs; *stream = nullptr when the whole device is
 // allowed (the caller keeps its own stream). *sms = SM count of the choice.
+int partition_streams(int device, int allowed, cudaStream_t* stream, cudaStream_t* side, int* sms);
 int partition_stream(int device, int allowed, cudaStream_t* stream, int* sms) {
+  cudaStream_t side = nullptr;
+  return partition_streams(device, allowed, stream, &side, sms);
+}
+// Same, also returning the low-priority companion stream of the partition.
+int partition_streams(int device, int allowed, cudaStream_t* stream, cudaStream_t* side, int* sms) {
   SRT_REQUIRE(device >= 0 && device < 16, "sm partition: device %d out of range", device);
   std::lock_guard<std::mutex> lk(g_mu);
   Ladder& L = g_ladder[device];
@@ -113,12 +124,14 @@ int partition_stream(int device, int allowed, cudaStream_t* stream, int* sms) {
   }
   if (L.status != SRT_OK) return L.status;
   *stream = nullptr;
+  *side = nullptr;
   *sms = L.total;
   if (allowed >= L.total || L.rungs.empty()) return SRT_OK;
   const Rung* pick = &L.rungs.back();  // never below the narrowest rung
   for (const Rung& r : L.rungs)
     if (r.sms <= allowed) { pick = &r; break; }
   *stream = pick->stream;
+  *side = pick->side;
   *sms = pick->sms;
   return SRT_OK;
 }

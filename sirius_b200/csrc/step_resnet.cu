@@ -112,7 +112,7 @@ struct Step {
   std::vector<GradBucket> buckets;
   int build_buckets(size_t bucket_elems);
   int bucket_ready(int b, bool on_side);
-  bool use_side() const { return side && overlap_wgrad && !follow_mask && !prof_on; }
+  bool use_side() const { return side && overlap_wgrad && !prof_on; }
   int t_slot(const void* p) const { for (int i = 0; i < 6; ++i) if (T[i] == p) return i; return -1; }
   int before_write(const void* buf) {   // main stream is about to overwrite buf
     const int i = t_slot(buf);
@@ -200,6 +200,7 @@ struct Step {
   // on as many SMs as the process-wide allowed-SM mask has bits (see sm_partition.cu).
   bool follow_mask = false;
   cudaStream_t home_stream = nullptr;  // the stream the step was created with (whole device)
+  cudaStream_t home_side = nullptr;    // ... and its low-priority companion
   int cur_sms = 0;                     // 0 = whole device
   cudaEvent_t switch_ev = nullptr;
   // Source of the allowed SM count: the inference side's required-TPC counter on the information
@@ -218,15 +219,20 @@ struct Step {
       const SmMask m = current_sm_mask();
       for (int i = 0; i < total; ++i) allowed += (int)((m.w[i >> 6] >> (i & 63)) & 1ull);
     }
-    cudaStream_t want = nullptr;
+    cudaStream_t want = nullptr, want_side = nullptr;
     int sms = total;
-    int rc = partition_stream(cfg_device, allowed, &want, &sms);
+    int rc = partition_streams(cfg_device, allowed, &want, &want_side, &sms);
     if (rc) return rc;
-    if (!want) { want = home_stream; sms = 0; }
+    if (!want) { want = home_stream; want_side = home_side; sms = 0; }
     if (want == stream) return SRT_OK;
     if (!switch_ev) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&switch_ev, cudaEventDisableTiming));
     SRT_CHECK_CUDA(cudaEventRecord(switch_ev, stream));   // the new stream continues after everything queued so far
     SRT_CHECK_CUDA(cudaStreamWaitEvent(want, switch_ev, 0));
+    if (side && want_side && want_side != side) {           // the companion stream moves with it, in order
+      SRT_CHECK_CUDA(cudaEventRecord(switch_ev, side));
+      SRT_CHECK_CUDA(cudaStreamWaitEvent(want_side, switch_ev, 0));
+      side = want_side;
+    }
     stream = want;
     cur_sms = sms;
     return SRT_OK;
@@ -317,7 +323,7 @@ struct Step {
     if (ev_fork) cudaEventDestroy(ev_fork);
     if (ev_join) cudaEventDestroy(ev_join);
     for (auto e : ev_read) if (e) cudaEventDestroy(e);
-    if (side) cudaStreamDestroy(side);
+    if (home_side) cudaStreamDestroy(home_side);  // partition streams belong to the ladder
     if (own_stream && home_stream) cudaStreamDestroy(home_stream);  // partition streams belong to the ladder
   }
   int dalloc(void** out, size_t bytes, bool zero) {
@@ -484,6 +490,7 @@ int Step::build() {
     int lo = 0, hi = 0;
     SRT_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     SRT_CHECK_CUDA(cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, lo));
+    home_side = side;
     SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
     SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
     for (auto& e : ev_read) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -1170,6 +1177,11 @@ int srt_step_follow_sm_mask(srt_step* h, int on) {
     if (!s->switch_ev) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&s->switch_ev, cudaEventDisableTiming));
     SRT_CHECK_CUDA(cudaEventRecord(s->switch_ev, s->stream));
     SRT_CHECK_CUDA(cudaStreamWaitEvent(s->home_stream, s->switch_ev, 0));
+    if (s->side && s->home_side && s->side != s->home_side) {
+      SRT_CHECK_CUDA(cudaEventRecord(s->switch_ev, s->side));
+      SRT_CHECK_CUDA(cudaStreamWaitEvent(s->home_side, s->switch_ev, 0));
+      s->side = s->home_side;
+    }
     s->stream = s->home_stream;
     s->cur_sms = 0;
   }

@@ -107,10 +107,16 @@ int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int
                     const float* gamma, const float* mean, const float* invstd, const float* scale,
                     const float* shift, int relu, void* dz, void* dresidual, float* dgamma,
                     float* dbeta, void* scratch, size_t scratch_bytes, void* stream);
-/* The same BatchNorm as ONE kernel per direction for tensors that fit on chip: a cluster of 8 CTAs per group of
- * 16 or 32 channels keeps its rows in shared memory, combines the sums through distributed shared memory and
- * writes the result: one read and one write of the tensor, no scratch. srt_bn_fused_fits tells whether a tensor
- * qualifies (backward keeps two slabs, so it qualifies for half the size). No counterpart in the reference. */
+/* The same BatchNorm as ONE launch per direction: a cooperative grid of at most one block per SM sums its work
+ * items, meets at a grid-wide barrier, finalizes the channels (dealt to the warps of the grid), meets again and
+ * applies the coefficients to the same items. Pays where the three launches of the path above cost more than the
+ * passes themselves (tensors that sit in L2). The split into work items depends on the shape only, so the result
+ * has the same bits on any number of SMs. Partial sums and barrier words live in a 2.4 MB workspace that the
+ * library keeps per (device, stream) and allocates on the first call on that stream; every barrier wait is
+ * bounded and reports through srt_tc_status (code 0xB1). srt_bn_fused_fits tells whether a shape qualifies
+ * (C a multiple of 16 bytes of elements, at most 75 776 channels). When dresidual is given, the masked
+ * gradient is written there first and read back for dz (dresidual may alias dy). No counterpart in the
+ * reference. */
 int srt_bn_fused_fits(int dtype, int64_t rows, int C, int backward);
 int srt_bn_forward_fused(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C, const float* gamma,
                          const float* beta, float eps, float momentum, float* running_mean, float* running_var, float* mean,

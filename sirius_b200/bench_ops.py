@@ -1,7 +1,7 @@
 """Per-layer micro-benchmark of the convolution kernels on the ResNet-152 layer shapes.
 
 
-    python -m sirius_b200.bench_ops [--batch 64] [--case NAME] [--pass fprop|dgrad|wgrad|all] [--iters 20]
+    python -m sirius_b200.bench_ops [--batch 64] [--case NAME] [--pass fprop|dgrad|wgrad|all|bn] [--iters 20]
 
 Each case is timed with CUDA events on the launching stream after warm-up; between timed launches a
 buffer larger than L2 is rewritten so every launch starts cold. Prints one JSON line per case/pass.
@@ -91,14 +91,96 @@ def run_case(name, batch, which, iters, flush):
     return out
 
 
+# BatchNorm shapes of ResNet-152: name -> (H, W, C, residual unit)
+BN_CASES = {
+    "bn_stem_c64": (112, 112, 64, False),
+    "bn_l1_c64": (56, 56, 64, False),
+    "bn_l1_c256_res": (56, 56, 256, True),
+    "bn_l2_c128": (28, 28, 128, False),
+    "bn_l2_c512_res": (28, 28, 512, True),
+    "bn_l3_c256": (14, 14, 256, False),
+    "bn_l3_c1024_res": (14, 14, 1024, True),
+    "bn_l4_c512": (7, 7, 512, False),
+    "bn_l4_c2048_res": (7, 7, 2048, True),
+}
+
+
+def run_bn_case(name, batch, iters, flush, one_launch=False):
+    """Forward (statistics + apply) and backward of one BatchNorm(+residual)+ReLU layer. The byte
+    counts are the tensors each pass has to move once: forward reads z twice (statistics, apply),
+    reads the residual and writes y; backward reads dy and z twice (sums, apply), the stored y twice
+    in a residual unit (ReLU mask), and writes dz (and the gradient of the residual branch)."""
+    from ._lib import call, lib
+    H, W, C, res = BN_CASES[name]
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    rows = batch * H * W
+    z = torch.randn(rows, C, device=dev, generator=g).to(torch.bfloat16)
+    r = torch.randn(rows, C, device=dev, generator=g).to(torch.bfloat16) if res else None
+    dy = torch.randn(rows, C, device=dev, generator=g).to(torch.bfloat16)
+    y = torch.empty_like(z)
+    dz = torch.empty_like(z)
+    dres = torch.empty_like(z) if res else None
+    f32 = lambda v: torch.full((C,), v, dtype=torch.float32, device=dev)
+    gamma, beta, rm, rv = f32(1.0), f32(0.0), f32(0.0), f32(1.0)
+    mean, invstd, scale, shift, dgamma, dbeta = (f32(0.0) for _ in range(6))
+    scratch, nscr = ops.bn_scratch(rows, C, dev)
+    P, st, dt = ops._p, ops._stream, ops._dt(z)
+
+    def fwd():
+        call("srt_bn_stats", dt, P(z), rows, C, P(gamma), P(beta), 1e-5, 0.1, P(rm), P(rv), P(mean), P(invstd),
+             P(scale), P(shift), P(scratch), nscr, st())
+        call("srt_bn_apply", dt, P(z), P(r), P(y), rows, C, P(scale), P(shift), 1, st())
+
+    def bwd():
+        call("srt_bn_backward", dt, P(dy), P(y if res else None), P(z), rows, C, P(gamma), P(mean), P(invstd),
+             P(scale), P(shift), 1, P(dz), P(dres), P(dgamma), P(dbeta), P(scratch), nscr, st())
+
+    if one_launch:
+        def fwd():
+            call("srt_bn_forward_fused", dt, P(z), P(r), P(y), rows, C, P(gamma), P(beta), 1e-5, 0.1, P(rm), P(rv), P(mean),
+                 P(invstd), P(scale), P(shift), 1, st())
+
+        def bwd():
+            call("srt_bn_backward_fused", dt, P(dy), P(y if res else None), P(z), rows, C, P(gamma), P(mean), P(invstd),
+                 P(scale), P(shift), 1, P(dz), P(dres), P(dgamma), P(dbeta), st())
+
+    t = z.numel() * 2
+    io = {"bn_fwd": t * (4 if res else 3), "bn_bwd": t * (8 if res else 5)}
+    scrub = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev) if flush else None
+    fwd()
+    for p, fn in (("bn_fwd", fwd), ("bn_bwd", bwd)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        evs = []
+        for _ in range(iters):
+            if scrub is not None:
+                scrub.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        us = sum(a.elapsed_time(b) for a, b in evs) / iters * 1e3
+        print(json.dumps({"case": name, "pass": p, "one_launch": one_launch, "batch": batch, "us": round(us, 2),
+                          "gbytes_per_s": round(io[p] / us / 1e3, 1), "mbytes": round(io[p] / 1e6, 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--case", default="all")
-    ap.add_argument("--pass", dest="which", default="all", choices=["fprop", "dgrad", "wgrad", "all"])
+    ap.add_argument("--pass", dest="which", default="all", choices=["fprop", "dgrad", "wgrad", "all", "bn"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--one-launch", action="store_true", help="BatchNorm cases: the one-launch kernels")
     a = ap.parse_args()
+    if a.which == "bn":
+        for name in (BN_CASES if a.case == "all" else [a.case]):
+            run_bn_case(name, a.batch, a.iters, not a.no_flush, a.one_launch)
+        return
     for name in (CASES if a.case == "all" else [a.case]):
         run_case(name, a.batch, a.which, a.iters, not a.no_flush)
 

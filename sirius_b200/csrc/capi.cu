@@ -199,7 +199,7 @@ int srt_bn_forward_fused(int dtype, const void* z, const void* residual, void* y
                          float* invstd, float* scale, float* shift, int relu, void* stream) {
   SRT_REQUIRE(z && y && mean && invstd && scale && shift, "bn_forward_fused: null argument");
   CHECK_DTYPE(dtype);
-  SRT_REQUIRE(C % 16 == 0 && rows > 0, "bn_forward_fused: C (%d) must be a multiple of 16", C);
+  SRT_REQUIRE(C % 8 == 0 && rows > 0, "bn_forward_fused: C (%d) must be a multiple of 8", C);
   return bn_forward_fused(dtype, z, residual, y, rows, C, gamma, beta, eps, momentum, running_mean, running_var, mean, invstd,
                           scale, shift, relu, ST(stream));
 }
@@ -208,7 +208,7 @@ int srt_bn_backward_fused(int dtype, const void* dy, const void* y, const void* 
                           void* dresidual, float* dgamma, float* dbeta, void* stream) {
   SRT_REQUIRE(dy && z && mean && invstd && dz, "bn_backward_fused: null argument");
   CHECK_DTYPE(dtype);
-  SRT_REQUIRE(C % 16 == 0 && rows > 0, "bn_backward_fused: C (%d) must be a multiple of 16", C);
+  SRT_REQUIRE(C % 8 == 0 && rows > 0, "bn_backward_fused: C (%d) must be a multiple of 8", C);
   return bn_backward_fused(dtype, dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz, dresidual, dgamma, dbeta,
                            ST(stream));
 }

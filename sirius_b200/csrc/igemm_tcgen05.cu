@@ -1097,6 +1097,8 @@ int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaSt
 }
 
 
+int* tc_status_device_ptr() { return status_ptr(); }
+
 // Reads and clears the device status word of the tcgen05 kernels (synchronises the device).
 int tc_status_fetch(int* out) {
   int* sp = status_ptr();

@@ -4,6 +4,7 @@
 // contiguous one), fp32 per-thread accumulation over a short run of rows, double-precision
 // combination of the per-thread and per-slab partial sums in a fixed order (deterministic, and
 // accurate enough for the fp32 parity mode).
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -15,26 +16,59 @@ namespace {
 constexpr int NT = 256;
 constexpr int ROWS_PER_THREAD = 8;   // loads in flight per thread
 constexpr int FIN_CH = 8;            // channels per finalize block (8 x 16 B = one 128-byte line)
-constexpr int FIN_LANES = 128;       // slab lanes per channel in the finalize kernels
+constexpr int FIN_LANES = 32;        // slab lanes per channel in the finalize kernels
+constexpr int TARGET_BLOCKS = 4 * 148;  // blocks a streaming pass wants in flight (4 per SM)
 
+// How a partial-sum kernel covers the rows x C matrix. A block owns `slab` consecutive rows of one
+// chunk of TC channel vectors and writes one partial per channel, so the partial-sum traffic is
+// 16 bytes per channel per slab: tall slabs keep it small against the rows*C input (a 16-row slab of
+// a 1024-channel bf16 tensor would write half as many bytes as it reads). Narrow channel chunks
+// (down to one 128-byte line per row) buy the height without starving the device of blocks.
 struct RowMap {
-  int CV;    // 16-byte vectors per row
-  int TC;    // threads across channel vectors in a block
-  int RL;    // row lanes in a block
-  int slab;  // rows per block
-  int S;     // number of slabs (grid.x)
-  int GY;    // channel chunks (grid.y)
+  int CV;     // 16-byte vectors per row
+  int TC;     // threads across channel vectors in a block
+  int RL;     // row lanes in a block
+  int iters;  // batches of ROWS_PER_THREAD rows per thread
+  int slab;   // rows per block = RL * ROWS_PER_THREAD * iters
+  int S;      // number of slabs (grid.x)
+  int GY;     // channel chunks (grid.y)
 };
 
-inline RowMap make_row_map(int64_t rows, int C, int V) {
+inline RowMap row_map_for(int64_t rows, int CV, int TC, int iters) {
   RowMap m;
-  m.CV = C / V;
-  m.TC = m.CV < NT ? m.CV : NT;
-  m.RL = NT / m.TC;
-  m.slab = m.RL * ROWS_PER_THREAD;
+  m.CV = CV;
+  m.TC = TC;
+  m.RL = NT / TC;
+  m.iters = iters;
+  m.slab = m.RL * ROWS_PER_THREAD * iters;
   m.S = (int)((rows + m.slab - 1) / m.slab);
-  m.GY = (m.CV + m.TC - 1) / m.TC;
+  m.GY = (CV + TC - 1) / TC;
   return m;
+}
+
+// Tallest slab that still gives TARGET_BLOCKS blocks; when no shape reaches that many, the shape
+// with the most blocks. Ties go to the wider channel chunk (longer contiguous runs per row).
+inline RowMap make_row_map(int64_t rows, int C, int V) {
+  const int CV = C / V;
+  const int widest = CV < NT ? CV : NT;
+  RowMap best = row_map_for(rows, CV, widest, 1);
+  constexpr int min_tc = 8;  // one 128-byte line per row and block
+  auto blocks = [](const RowMap& m) { return (int64_t)m.S * m.GY; };
+  auto better = [&](const RowMap& a, const RowMap& b) {  // is a better than b
+    const bool fa = blocks(a) >= TARGET_BLOCKS, fb = blocks(b) >= TARGET_BLOCKS;
+    if (fa != fb) return fa;
+    if (fa) return a.slab != b.slab ? a.slab > b.slab : a.TC > b.TC;
+    if (blocks(a) != blocks(b)) return blocks(a) > blocks(b);
+    return a.slab != b.slab ? a.slab > b.slab : a.TC > b.TC;
+  };
+  for (int tc = widest; tc >= 1; tc = (tc > min_tc ? (tc % 2 == 0 ? tc / 2 : min_tc) : 0)) {
+    for (int iters = 1; iters <= 4; iters *= 2) {
+      const RowMap m = row_map_for(rows, CV, tc, iters);
+      if (better(m, best)) best = m;
+    }
+    if (tc <= min_tc) break;
+  }
+  return best;
 }
 
 // Reduce per-thread accumulators a[V], b[V] over the block's row lanes; lane 0 of each channel
@@ -48,18 +82,43 @@ __device__ inline void block_reduce_store(const float (&a)[V], const float (&b)[
 #pragma unroll
   for (int v = 0; v < V; ++v) { sh_a[t * V + v] = a[v]; sh_b[t * V + v] = b[v]; }
   __syncthreads();
-  // one thread per channel of this block's chunk; row lanes are summed in a fixed order
+  // Row lanes are summed in a fixed order. A narrow chunk leaves most threads without a channel of
+  // their own, so the lanes of a channel are dealt to NT/chunk threads first and those sums combined.
   const int chunk = m.TC * V;
-  for (int ch = t; ch < chunk; ch += NT) {
-    const int c = blockIdx.y * chunk + ch;
-    if (c >= C) break;
+  const int nparts = chunk < NT ? NT / chunk : 1;
+  if (nparts == 1) {
+    for (int ch = t; ch < chunk; ch += NT) {
+      const int c = blockIdx.y * chunk + ch;
+      if (c >= C) break;
+      double sa = 0.0, sb = 0.0;
+      for (int r = 0; r < m.RL; ++r) {
+        sa += (double)sh_a[r * chunk + ch];
+        sb += (double)sh_b[r * chunk + ch];
+      }
+      double2* out = reinterpret_cast<double2*>(partial) + (size_t)blockIdx.x * C + c;
+      *out = make_double2(sa, sb);
+    }
+    return;
+  }
+  __shared__ double2 sh_d[NT];
+  const int ch = t % chunk, part = t / chunk;
+  if (part < nparts) {
     double sa = 0.0, sb = 0.0;
-    for (int r = 0; r < m.RL; ++r) {
+    for (int r = part; r < m.RL; r += nparts) {
       sa += (double)sh_a[r * chunk + ch];
       sb += (double)sh_b[r * chunk + ch];
     }
-    double2* out = reinterpret_cast<double2*>(partial) + (size_t)blockIdx.x * C + c;
-    *out = make_double2(sa, sb);
+    sh_d[part * chunk + ch] = make_double2(sa, sb);
+  }
+  __syncthreads();
+  const int c = blockIdx.y * chunk + ch;
+  if (part == 0 && c < C) {
+    double2 tot = sh_d[ch];
+    for (int q = 1; q < nparts; ++q) {
+      tot.x += sh_d[q * chunk + ch].x;
+      tot.y += sh_d[q * chunk + ch].y;
+    }
+    reinterpret_cast<double2*>(partial)[(size_t)blockIdx.x * C + c] = tot;
   }
 }
 
@@ -105,21 +164,23 @@ bn_stats_partial(const T* __restrict__ z, int64_t rows, int C, RowMap m, double*
 #pragma unroll
   for (int v = 0; v < V; ++v) { s[v] = 0.f; q[v] = 0.f; }
   if (rl < m.RL && cv < m.CV) {
-    const int64_t r0 = (int64_t)blockIdx.x * m.slab + rl;
-    Vec16<T> x[ROWS_PER_THREAD];
+    for (int it = 0; it < m.iters; ++it) {
+      const int64_t r0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * ROWS_PER_THREAD * m.RL + rl;
+      Vec16<T> x[ROWS_PER_THREAD];
 #pragma unroll
-    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-      const int64_t r = r0 + (int64_t)i * m.RL;
-      if (r < rows) x[i].load(z + r * C + (int64_t)cv * V);
-    }
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+        const int64_t r = r0 + (int64_t)i * m.RL;
+        if (r < rows) x[i].load(z + r * C + (int64_t)cv * V);
+      }
 #pragma unroll
-    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-      const int64_t r = r0 + (int64_t)i * m.RL;
-      if (r < rows) {
-        float f[V];
-        x[i].unpack(f);
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+        const int64_t r = r0 + (int64_t)i * m.RL;
+        if (r < rows) {
+          float f[V];
+          x[i].unpack(f);
 #pragma unroll
-        for (int v = 0; v < V; ++v) { s[v] += f[v]; q[v] = fmaf(f[v], f[v], q[v]); }
+          for (int v = 0; v < V; ++v) { s[v] += f[v]; q[v] = fmaf(f[v], f[v], q[v]); }
+        }
       }
     }
   }
@@ -245,29 +306,31 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
     float mu[V], is[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) { mu[v] = mean[cv * V + v]; is[v] = invstd[cv * V + v]; }
-    const int64_t r0 = (int64_t)blockIdx.x * m.slab + rl;
-    Vec16<T> a[ROWS_PER_THREAD], b[ROWS_PER_THREAD];
+    for (int it = 0; it < m.iters; ++it) {
+      const int64_t r0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * ROWS_PER_THREAD * m.RL + rl;
+      Vec16<T> a[ROWS_PER_THREAD], b[ROWS_PER_THREAD];
 #pragma unroll
-    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-      const int64_t r = r0 + (int64_t)i * m.RL;
-      if (r < rows) {
-        const int64_t o = r * C + (int64_t)cv * V;
-        a[i].load(dy + o);
-        b[i].load(z + o);
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+        const int64_t r = r0 + (int64_t)i * m.RL;
+        if (r < rows) {
+          const int64_t o = r * C + (int64_t)cv * V;
+          a[i].load(dy + o);
+          b[i].load(z + o);
+        }
       }
-    }
 #pragma unroll
-    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-      const int64_t r = r0 + (int64_t)i * m.RL;
-      if (r >= rows) continue;
-      float g[V], x[V];
-      a[i].unpack(g);
-      b[i].unpack(x);
-      if (relu) apply_relu_mask<T, V>(g, x, y ? y + r * C + (int64_t)cv * V : nullptr, scale, shift, cv * V);
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+        const int64_t r = r0 + (int64_t)i * m.RL;
+        if (r >= rows) continue;
+        float g[V], x[V];
+        a[i].unpack(g);
+        b[i].unpack(x);
+        if (relu) apply_relu_mask<T, V>(g, x, y ? y + r * C + (int64_t)cv * V : nullptr, scale, shift, cv * V);
 #pragma unroll
-      for (int v = 0; v < V; ++v) {
-        sg[v] += g[v];
-        sgx[v] = fmaf(g[v], (x[v] - mu[v]) * is[v], sgx[v]);
+        for (int v = 0; v < V; ++v) {
+          sg[v] += g[v];
+          sgx[v] = fmaf(g[v], (x[v] - mu[v]) * is[v], sgx[v]);
+        }
       }
     }
   }

@@ -21,10 +21,10 @@ int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t
                 const float* shift, int relu, void* dz, void* dres, float* dgamma, float* dbeta,
                 void* scratch, size_t scratch_bytes, cudaStream_t st);
 
-// One-kernel BatchNorm for tensors whose slabs fit in shared memory (cluster of 8 CTAs per channel group, see
-// norm_cluster.cu); bn_fused_fits says whether a tensor qualifies.
+// One-launch BatchNorm (cooperative grid with two grid-wide barriers, see norm_grid.cu); bn_fused_fits says
+// whether a shape qualifies.
 bool bn_fused_fits(int dtype, int64_t rows, int C, int backward);
-bool bn_fused_pays(int dtype, int64_t rows, int C, int backward);  // fits and is wide enough to beat the three-kernel path
+bool bn_fused_pays(int dtype, int64_t rows, int C, int backward);  // fits and is small enough to beat the three-kernel path
 int bn_forward_fused(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C, const float* gamma,
                      const float* beta, float eps, float momentum, float* rm, float* rv, float* mean, float* invstd,
                      float* scale, float* shift, int relu, cudaStream_t st);

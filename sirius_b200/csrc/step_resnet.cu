@@ -104,8 +104,8 @@ struct Step {
                                    // stream, and those never take part in the T[0]/T[4] swap
   bool side_dirty = false;         // side-stream work queued that the main stream has not waited for
   bool wt_dirty = false;           // ... of which only filter transposes (the forward pass need not wait for those)
-  bool overlap_wgrad = true;
-  bool fused_bn = getenv("SIRIUS_B200_NO_FUSED_BN") == nullptr;  // one-kernel BatchNorm where the tensor fits on chip
+  bool overlap_wgrad = getenv("SIRIUS_B200_NO_OVERLAP") == nullptr;  // weight gradients on the second stream
+  bool fused_bn = getenv("SIRIUS_B200_NO_FUSED_BN") == nullptr;  // one-launch BatchNorm for the tensors that sit in L2
   // Gradient buckets for the data-parallel all-reduce, in the order backward completes them (fc and the
   // last blocks first). A bucket's event fires when every gradient in its range is final.
   struct GradBucket { size_t off, count; int first_block; cudaEvent_t ev; };
@@ -764,8 +764,8 @@ int Step::forward(int B) {
       if ((r = bn_eval_params(pf(u.bn.gamma), pf(u.bn.beta), bf_(u.bn.rmean), bf_(u.bn.rvar), cfg.bn_eps, u.bn.C,
                               u.bn.scale, u.bn.shift, stream)))
         return r;
-    } else if (fused_bn && !follow_mask && bn_fused_pays(dt, rows, u.bn.C, 0)) {
-      // statistics, finalize and apply in one cluster kernel: the tensor is read once and stays on chip
+    } else if (fused_bn && bn_fused_pays(dt, rows, u.bn.C, 0)) {
+      // statistics, finalize and apply in one cooperative launch
       return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2), [&] {
         return bn_forward_fused(dt, u.z, residual, u.y, rows, u.bn.C, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps,
                                 cfg.bn_momentum, bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale,
@@ -840,7 +840,7 @@ int Step::backward(int B) {
     // two passes over (dy, z[, y]) plus the dz (and masked-gradient) writes
     const double abytes = (double)rows * u.bn.C * esz;
     const double bn_bytes = abytes * ((dres ? 3 : 2) * 2 + 1 + (dres ? 1 : 0));
-    if (fused_bn && !follow_mask && bn_fused_pays(dt, rows, u.bn.C, 1)) {
+    if (fused_bn && bn_fused_pays(dt, rows, u.bn.C, 1)) {
       if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
             return bn_backward_fused(dt, dy, dres ? u.y : nullptr, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean, u.bn.invstd,
                                      u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma), gf(u.bn.beta), stream); })))

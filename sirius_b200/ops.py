@@ -115,7 +115,7 @@ def bn_fused_fits(z, backward=False) -> bool:
 
 
 def bn_forward_fused(z, gamma, beta, running_mean, running_var, residual=None, relu=True, eps=1e-5, momentum=0.1):
-    """Statistics + apply in one cluster kernel; returns (y, mean, invstd, scale, shift)."""
+    """Statistics + apply in one cooperative launch; returns (y, mean, invstd, scale, shift)."""
     Cc = z.shape[-1]
     f = lambda: torch.empty(Cc, dtype=torch.float32, device=z.device)
     mean, invstd, scale, shift = f(), f(), f(), f()

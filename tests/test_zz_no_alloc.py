@@ -62,9 +62,12 @@ def test_static_scratch_matches_caller_scratch_on_consecutive_calls(dtype):
 
 
 def test_static_scratch_rejects_oversized_problem():
-    Cc, rows = 2048, 4096  # needs far more than 4 MiB of slab partials
+    # the smallest power-of-two row count of a 32768-channel tensor whose slab partials exceed the 4 MiB
+    Cc, rows = 32768, 1024
+    while _lib.lib().srt_bn_scratch_bytes(rows, Cc) <= (4 << 20) and rows < (1 << 16):
+        rows *= 2
     assert _lib.lib().srt_bn_scratch_bytes(rows, Cc) > (4 << 20)
-    z = torch.zeros(rows, Cc, device=DEV)
+    z = torch.empty(rows, Cc, device=DEV)
     o = [torch.empty(Cc, dtype=torch.float32, device=DEV) for _ in range(4)]
     status = _lib.lib().srt_bn_stats_static(SRT_F32, z.data_ptr(), rows, Cc, None, None, 1e-5, 0.1, None, None,
                                             *(t.data_ptr() for t in o), torch.cuda.current_stream().cuda_stream)

@@ -1097,6 +1097,7 @@ int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaSt
 }
 
 
+void bn_grid_reset_barriers();  // norm_grid.cu
 int* tc_status_device_ptr() { return status_ptr(); }
 
 // Reads and clears the device status word of the tcgen05 kernels (synchronises the device).
@@ -1108,6 +1109,7 @@ int tc_status_fetch(int* out) {
   if (*out != 0) {
     int zero = 0;
     SRT_CHECK_CUDA(cudaMemcpy(sp, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    bn_grid_reset_barriers();
   }
   return SRT_OK;
 }

@@ -123,16 +123,23 @@ __device__ inline unsigned long long global_ns() {
 // wait for the generation to change. The words end every barrier as they began it (count 0), so launches
 // that follow on the same stream need no reset. Global writes made before the barrier by any thread of any
 // block are visible after it to loads that bypass L1 (__ldcg).
-__device__ inline void grid_barrier(unsigned* bar, int* status) {
+//
+// One round trip to L2 per arrival: the arrival is an acq_rel atomic (releases this block's writes, which
+// thread 0 has observed through __syncthreads; the last arriver acquires everybody's), the generation a block
+// waits on is read once when the kernel starts (`gen`, thread 0 only) and counted up locally.
+__device__ inline unsigned barrier_generation(const unsigned* bar) {
+  unsigned v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar + 1) : "memory");
+  return v;
+}
+__device__ inline void grid_barrier(unsigned* bar, unsigned& gen, int* status) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned gen = ld_acquire_u32(bar + 1);
-    __threadfence();
-    const unsigned arrived = atomicAdd(bar, 1u);
+    unsigned arrived;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(bar) : "memory");
     if (arrived == gridDim.x - 1) {
-      atomicExch(bar, 0u);
-      __threadfence();
-      atomicAdd(bar + 1, 1u);
+      asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(bar), "r"(0u) : "memory");
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bar + 1) : "memory");
     } else {
       const unsigned long long t0 = global_ns();
       unsigned spins = 0;
@@ -143,7 +150,7 @@ __device__ inline void grid_barrier(unsigned* bar, int* status) {
         }
       }
     }
-    __threadfence();
+    ++gen;
   }
   __syncthreads();
 }
@@ -243,6 +250,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_fwd_grid(const FwdArgs p) {
   const int t = threadIdx.x;
   const int tc = t % m.TC, rl = t / m.TC;
   const int n_items = m.NS * m.GY;
+  unsigned gen = t == 0 ? barrier_generation(p.ws.bar) : 0u;
 
   // phase 1: per-item sums of z and z*z
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -275,7 +283,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_fwd_grid(const FwdArgs p) {
     }
     item_reduce_store<V>(sa, sq, m, gy, C, p.ws.partial + (size_t)s * C, sh_a, sh_b, sh_d);
   }
-  grid_barrier(p.ws.bar, p.status);
+  grid_barrier(p.ws.bar, gen, p.status);
 
   // finalize: one warp per channel
   {
@@ -301,7 +309,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_fwd_grid(const FwdArgs p) {
       }
     }
   }
-  grid_barrier(p.ws.bar, p.status);
+  grid_barrier(p.ws.bar, gen, p.status);
 
   // phase 2: y = relu(z*scale + shift + residual) over the same items
   const T* res = (const T*)p.residual;
@@ -410,6 +418,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
   const int tc = t % m.TC, rl = t / m.TC;
   const int n_items = m.NS * m.GY;
   const bool recompute_mask = p.relu && !yk;
+  unsigned gen = t == 0 ? barrier_generation(p.ws.bar) : 0u;
 
   // phase 1: sums of g and g*xhat per item, g = dy under the ReLU mask; g is also what the residual branch gets
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -466,7 +475,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
     }
     item_reduce_store<V>(sg, sgx, m, gy, C, p.ws.partial + (size_t)s * C, sh_a, sh_b, sh_d);
   }
-  grid_barrier(p.ws.bar, p.status);
+  grid_barrier(p.ws.bar, gen, p.status);
 
   // finalize: dgamma, dbeta and the coefficients of dz = ka*g + kb*(x - mean) + kd
   {
@@ -486,7 +495,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
       coef[2 * C + c] = -k0 * mg;
     }
   }
-  grid_barrier(p.ws.bar, p.status);
+  grid_barrier(p.ws.bar, gen, p.status);
 
   // phase 2: dz over the same items; the masked gradient comes back from dres where phase 1 stored it
   T* dz = (T*)p.dz;
@@ -585,6 +594,16 @@ inline size_t env_mb(const char* name, long dflt) {
 
 // Any tensor whose channel count is a multiple of the 16-byte vector and small enough for the partial-sum
 // workspace qualifies.
+// After a barrier wait has given up, arrival counts may be left non-zero; with the device idle (the caller
+// has synchronised) put the barrier words of every workspace of the current device back to zero.
+void bn_grid_reset_barriers() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  for (auto& kv : g_ws)
+    if (kv.first.first == dev) (void)cudaMemset(kv.second, 0, WS_BAR_BYTES);
+}
+
 bool bn_fused_fits(int dtype, int64_t rows, int C, int backward) {
   (void)backward;
   const int V = dtype == SRT_F32 ? 4 : 8;

@@ -439,6 +439,33 @@ int srt_qwen2_grad_buffer(srt_qwen2* g, void** ptr, int64_t* n);
 void* srt_qwen2_stream(srt_qwen2* g);
 int64_t srt_qwen2_memory_bytes(srt_qwen2* g);
 
+/* ---- DistilBERT-style encoder, forward only: the second model of the stand-in inference worker (the reference
+ *      serves "distilbert_base" through TVM, server/model_store/infer_model.cc:46-58,394-523; arithmetic of
+ *      transformers.DistilBertModel: embeddings + LayerNorm, n_layer x [Q/K/V, bidirectional attention, out
+ *      projection, residual + LayerNorm, erf-GELU MLP, residual + LayerNorm]). Parameters carry the state_dict
+ *      names and shapes of DistilBertModel. With a pool, activations come from its INFERENCE allocator
+ *      (MemType::kInfer): reserve maps them (after a handover from the trainer), release gives the pages back. */
+typedef struct srt_bert srt_bert;
+typedef struct srt_bert_config {
+  int n_layer, n_head, dim, hidden_dim, vocab, max_pos; /* DistilBERT-base: 6, 12, 768, 3072, 30522, 512 */
+  int max_batch, seq;                                   /* seq a multiple of 8 */
+  float ln_eps;                                         /* 1e-12 */
+} srt_bert_config;
+int srt_bert_create(const srt_bert_config* cfg, struct srt_pool* pool /* may be NULL */, srt_bert** out);
+int srt_bert_destroy(srt_bert* b);
+int srt_bert_num_params(srt_bert* b);
+int srt_bert_param_info(srt_bert* b, int idx, char* name, int name_cap, int64_t shape[2], int* ndim);
+int srt_bert_set_param(srt_bert* b, int idx, const float* host);
+int srt_bert_commit_params(srt_bert* b);
+int srt_bert_upload_tokens(srt_bert* b, const int32_t* host_ids, int B);
+int srt_bert_forward(srt_bert* b, int B);
+int srt_bert_output(srt_bert* b, float* host /* [B][seq][dim] */, int B);
+int srt_bert_synchronize(srt_bert* b);
+int srt_bert_stream(srt_bert* b, void** stream);
+int srt_bert_release_activations(srt_bert* b, size_t* released_bytes);
+int srt_bert_reserve_activations(srt_bert* b);
+int srt_bert_memory_bytes(srt_bert* b, size_t* weights, size_t* activations);
+
 /* Gradient buckets of the transformer executors, for an all-reduce overlapped with backward (as srt_step_grad_bucket
  * and friends do for the ResNet executor): srt_<model>_grad_buckets returns the executor's bucket list; buckets are
  * ranges of its flat gradient buffer in the order backward completes them. After forward_backward has returned, make

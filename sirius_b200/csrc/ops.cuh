@@ -105,6 +105,7 @@ int gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t st);
 int gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st);
 int causal_softmax_fwd(void* scores, int64_t Z, int S, cudaStream_t st);
 int causal_softmax_bwd(const void* P, void* dP, int64_t Z, int S, cudaStream_t st);
+int softmax_rows_fwd(void* scores, int64_t rows, int S, cudaStream_t st);  // whole rows, in place
 // causal = 1: `in` is lower triangular and `out` feeds a GEMM with k_causal = 2; tiles that GEMM never reads are skipped.
 int batched_transpose(const void* in, void* out, int R, int C, int64_t ld_in, int64_t s1, int64_t s2, int Z1, int Z2,
                       cudaStream_t st, int causal = 0);

@@ -309,6 +309,47 @@ causal_softmax_fwd_kernel(bf16* __restrict__ s, int64_t total_rows, int S) {
     o.store(p + v * 8);
   }
 }
+// Softmax over whole rows of S columns, in place (bidirectional attention without a padding mask). One warp per row.
+__global__ void __launch_bounds__(NT)
+softmax_rows_kernel(bf16* __restrict__ s, int64_t total_rows, int S) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (row >= total_rows) return;
+  bf16* p = s + row * S;
+  const int nv = S / 8;
+  float mx = -INFINITY;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a;
+    a.load(p + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) mx = fmaxf(mx, f[e]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a;
+    a.load(p + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum += __expf(f[e] - mx);
+  }
+  const float inv = 1.f / warp_sum(sum);
+  for (int v = lane; v < nv; v += 32) {
+    Vec16<bf16> a;
+    a.load(p + v * 8);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __expf(f[e] - mx) * inv;
+    Vec16<bf16> o;
+    o.pack(f);
+    o.store(p + v * 8);
+  }
+}
 // dS = P * (dP - sum_j P_j dP_j) on the valid part of each row, zero elsewhere; in place over dP.
 __global__ void __launch_bounds__(NT)
 causal_softmax_bwd_kernel(const bf16* __restrict__ P, bf16* __restrict__ dP, int64_t total_rows, int S) {
@@ -967,6 +1008,12 @@ int gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t st
 int causal_softmax_fwd(void* scores, int64_t Z, int S, cudaStream_t st) {
   SRT_REQUIRE(Z > 0 && S % 8 == 0, "causal_softmax: S (%d) must be a multiple of 8", S);
   launch_pdl(causal_softmax_fwd_kernel, dim3(rows_grid(Z * S)), dim3(NT), 0, st, (bf16*)scores, Z * S, S);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+int softmax_rows_fwd(void* scores, int64_t rows, int S, cudaStream_t st) {
+  SRT_REQUIRE(rows > 0 && S % 8 == 0, "softmax_rows: S (%d) must be a multiple of 8", S);
+  launch_pdl(softmax_rows_kernel, dim3(rows_grid(rows)), dim3(NT), 0, st, (bf16*)scores, rows, S);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

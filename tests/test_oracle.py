@@ -76,3 +76,19 @@ def test_swin_oracle_reproduces_the_committed_fixture():
     dig = summarize(final, samples=4)
     for k, d in doc["fp32"]["final"].items():
         assert abs(dig[k]["l2"] - d["l2"]) <= 1e-4 * d["l2"] + 1e-9, k
+
+
+def test_distilbert_oracle_reproduces_the_committed_fixture():
+    """Same pin for the DistilBERT forward oracle: seeds in, committed digest of the last hidden state out."""
+    import json
+    import pathlib
+    from oracle import distilbert_oracle as D
+    doc = json.loads((pathlib.Path(__file__).parent / "golden" / "distilbert_tiny.json").read_text())
+    model = D.build_model(**doc["config"], seed=doc["seed"])
+    ids = D.make_tokens(doc["batch"], doc["seq"], doc["config"]["vocab"], seed=doc["seed"])
+    h = D.last_hidden_state(model, ids)
+    d = doc["fp32"]["last_hidden_state"]
+    assert list(h.shape) == d["shape"]
+    assert abs(float(np.sqrt((h.astype(np.float64) ** 2).sum())) - d["l2"]) <= 1e-5 * d["l2"]
+    assert np.allclose(h.reshape(-1)[d["idx"]], d["val"], rtol=1e-4, atol=1e-5)
+    assert np.allclose(h[:, 0, :], np.array(d["first_token"]), rtol=1e-4, atol=1e-5)

@@ -422,6 +422,15 @@ typedef struct srt_qwen2_config {
   float lr, beta1, beta2, eps, weight_decay;                   /* AdamW */
 } srt_qwen2_config;
 int srt_qwen2_create(const srt_qwen2_config* cfg, srt_qwen2** out);
+/* Colocation hooks, as srt_gpt2_*: activations from the pool's training allocator, kept for the largest batch run
+ * so far; shrink keeps a set for batch B and returns the other pages; request_abort makes forward_backward return
+ * SRT_ERR_ABORTED at the next layer boundary (kill batch); accumulate adds the micro-batch gradients to the
+ * global-batch sum that the optimizer then consumes (pytorch/torch_col/accumulate.py:7-49). */
+int srt_qwen2_create_with_pool(const srt_qwen2_config* cfg, struct srt_pool* pool, srt_qwen2** out);
+int srt_qwen2_accumulate(srt_qwen2* g);
+int srt_qwen2_release_activations(srt_qwen2* g, size_t* released_bytes);
+int srt_qwen2_shrink_activations(srt_qwen2* g, int B, size_t* released_bytes);
+int srt_qwen2_request_abort(srt_qwen2* g, int on);
 int srt_qwen2_destroy(srt_qwen2* g);
 int srt_qwen2_num_params(srt_qwen2* g);
 int srt_qwen2_param_info(srt_qwen2* g, int idx, char* name, int name_cap, int64_t shape[2], int* ndim);

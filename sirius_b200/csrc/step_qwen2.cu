@@ -16,6 +16,8 @@
 #include <vector>
 
 #include "../../include/sirius_b200.h"
+#include "../../include/sirius_pool.h"
+#include <atomic>
 #include "common.cuh"
 #include "grad_buckets.cuh"
 #include "ops.cuh"
@@ -74,8 +76,85 @@ struct Qwen2 {
   int n_unique = 0, cur_B = 0;
   std::vector<void*> allocs;
   size_t bytes_total = 0;
+  // Releasable part (everything sized by the batch): from the training allocator of a page pool when one is
+  // attached, so that shrinking the batch hands whole pages to the inference side (as the other executors do).
+  srt_pool* pool = nullptr;
+  std::vector<void*> act_blocks;
+  size_t act_bytes = 0;
+  int act_batch = 0;
+  float* ACC = nullptr;      // gradients accumulated over the micro-batches of a global batch
+  int accum_pending = 0;
+  std::atomic<int> abort_flag{0};
+  static constexpr int kAhead = 4;  // layers the host may run ahead of the GPU (bounds the drain after a kill)
+  cudaEvent_t ahead_ev[kAhead] = {nullptr};
+  unsigned long long layer_seq = 0;
+
+  int aalloc(void** out, size_t bytes) {
+    bytes = upq(bytes ? bytes : 256, 256);
+    if (pool) {
+      int rc = srt_pool_alloc(pool, SRT_POOL_TRAIN, bytes, out);
+      if (rc) return rc;
+    } else {
+      SRT_CHECK_CUDA(cudaMalloc(out, bytes));
+    }
+    act_blocks.push_back(*out);
+    act_bytes += bytes;
+    return SRT_OK;
+  }
+  int free_activation_blocks() {
+    if (stream && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(stream));
+    if (side && !act_blocks.empty()) SRT_CHECK_CUDA(cudaStreamSynchronize(side));  // an aborted backward never joined
+    side_dirty = false;
+    for (void* p : act_blocks) {
+      if (pool) { int rc = srt_pool_free(pool, SRT_POOL_TRAIN, p); if (rc) return rc; }
+      else cudaFree(p);
+    }
+    act_blocks.clear();
+    act_bytes = 0;
+    act_batch = 0;
+    return SRT_OK;
+  }
+  int release_activations(size_t* released) {
+    if (released) *released = 0;
+    if (act_blocks.empty()) { act_batch = 0; return SRT_OK; }
+    size_t freed = act_bytes;
+    int rc = free_activation_blocks();
+    if (rc) return rc;
+    if (pool && (rc = srt_pool_empty_cache(pool, SRT_POOL_TRAIN, &freed))) return rc;
+    if (released) *released = freed;
+    return SRT_OK;
+  }
+  int alloc_activations(int B);
+  int shrink_activations(int B, size_t* released) {
+    if (released) *released = 0;
+    if (B <= 0) return release_activations(released);
+    SRT_REQUIRE(B <= cfg.max_batch, "qwen2 shrink_activations: batch %d above max_batch %d", B, cfg.max_batch);
+    const size_t before = act_bytes;
+    int rc = free_activation_blocks();
+    if (rc) return rc;
+    if ((rc = alloc_activations(B))) return rc;
+    size_t freed = before > act_bytes ? before - act_bytes : 0;
+    if (pool && (rc = srt_pool_empty_cache(pool, SRT_POOL_TRAIN, &freed))) return rc;
+    if (released) *released = freed;
+    return SRT_OK;
+  }
+  // Between layers: kill-batch flag and bounded launch-ahead.
+  int checkpoint() {
+    if (abort_flag.load(std::memory_order_acquire)) {
+      set_error("step aborted between layers (kill batch)");
+      return SRT_ERR_ABORTED;
+    }
+    const int slot = (int)(layer_seq % kAhead);
+    if (!ahead_ev[slot]) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ahead_ev[slot], cudaEventDisableTiming));
+    else if (layer_seq >= (unsigned long long)kAhead) SRT_CHECK_CUDA(cudaEventSynchronize(ahead_ev[slot]));
+    SRT_CHECK_CUDA(cudaEventRecord(ahead_ev[slot], stream));
+    ++layer_seq;
+    return SRT_OK;
+  }
 
   ~Qwen2() {
+    release_activations(nullptr);
+    for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
     if (ev_fork) cudaEventDestroy(ev_fork);
     if (ev_join) cudaEventDestroy(ev_join);
     if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
@@ -180,27 +259,8 @@ int Qwen2::build() {
   if ((rc = dalloc(&P, n_flat * 4, true)) || (rc = dalloc(&G, n_flat * 4, true)) || (rc = dalloc(&M1, n_flat * 4, true)) ||
       (rc = dalloc(&M2, n_flat * 4, true)) || (rc = dalloc(&Pw, n_flat * 2, true)) || (rc = dalloc(&WT, n_wt * 2, true)))
     return rc;
-  const size_t T = (size_t)cfg.max_batch * S, BH = (size_t)cfg.max_batch * Hq;
-  auto act = [&](__nv_bfloat16** p, size_t elems) { return dalloc(p, elems * 2); };
-  if ((rc = act(&x0, T * C))) return rc;
-  for (Layer& y : layers) {
-    if ((rc = act(&y.n1o, T * C)) || (rc = act(&y.qkv_o, T * QKV)) || (rc = act(&y.Pm, BH * S * S)) ||
-        (rc = act(&y.att, T * Hq * D)) || (rc = act(&y.x2, T * C)) || (rc = act(&y.n2o, T * C)) ||
-        (rc = act(&y.gu_o, T * 2 * F)) || (rc = act(&y.act, T * F)) || (rc = act(&y.xout, T * C)))
-      return rc;
-    if ((rc = dalloc(&y.z1, T * 4, true)) || (rc = dalloc(&y.r1, T * 4)) || (rc = dalloc(&y.z2, T * 4, true)) ||
-        (rc = dalloc(&y.r2, T * 4)))
-      return rc;
-  }
-  if ((rc = act(&nfo, T * C)) || (rc = act(&logits, T * Vpad))) return rc;
-  if ((rc = dalloc(&zf, T * 4, true)) || (rc = dalloc(&rf, T * 4)) || (rc = dalloc(&row_loss, T * 4)) ||
-      (rc = dalloc(&loss_acc, 256, true)))
-    return rc;
-  if ((rc = act(&dxa, T * C)) || (rc = act(&dxb, T * C)) || (rc = act(&dqkv, T * QKV)) || (rc = act(&dP, BH * S * S)) ||
-      (rc = act(&Tbig, BH * S * S)) || (rc = act(&t1, T * Hq * D)) || (rc = act(&t2, T * Hq * D)) ||
-      (rc = act(&dkv_h, T * Hq * D)) || (rc = act(&dgu, T * 2 * F)) || (rc = act(&dact, T * F)) ||
-      (rc = act(&datt, T * Hq * D)) || (rc = act(&dln, T * C)))
-    return rc;
+  if ((rc = dalloc(&ACC, n_flat * 4, true)) || (rc = dalloc(&loss_acc, 256, true))) return rc;
+  const size_t T = (size_t)cfg.max_batch * S;
   size_t sb = layernorm_bwd_scratch_bytes(C);
   if (colsum_scratch_bytes(QKV) > sb) sb = colsum_scratch_bytes(QKV);
   auto wg = [&](int in, int out) {
@@ -227,6 +287,40 @@ int Qwen2::build() {
     SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
     SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
   }
+  return alloc_activations(cfg.max_batch);
+}
+
+// Everything sized by the batch: saved activations of every layer, logits, backward scratch.
+int Qwen2::alloc_activations(int B) {
+  SRT_REQUIRE(B > 0 && B <= cfg.max_batch, "qwen2 activations: batch %d outside 1..%d", B, cfg.max_batch);
+  if (act_batch == B) return SRT_OK;
+  int rc = free_activation_blocks();
+  if (rc) return rc;
+  const size_t T = (size_t)B * S, BH = (size_t)B * Hq;
+  auto act = [&](__nv_bfloat16** p, size_t elems) { return aalloc((void**)p, elems * 2); };
+  auto actf = [&](float** p, size_t elems) { return aalloc((void**)p, elems * 4); };
+  auto zeros = [&](float** p, size_t elems) -> int {  // the "mean" of an RMSNorm: zeros
+    int r = aalloc((void**)p, elems * 4);
+    if (r) return r;
+    SRT_CHECK_CUDA(cudaMemsetAsync(*p, 0, elems * 4, stream));
+    return (int)SRT_OK;
+  };
+  if ((rc = act(&x0, T * C))) return rc;
+  for (Layer& y : layers) {
+    if ((rc = act(&y.n1o, T * C)) || (rc = act(&y.qkv_o, T * QKV)) || (rc = act(&y.Pm, BH * S * S)) ||
+        (rc = act(&y.att, T * Hq * D)) || (rc = act(&y.x2, T * C)) || (rc = act(&y.n2o, T * C)) ||
+        (rc = act(&y.gu_o, T * 2 * F)) || (rc = act(&y.act, T * F)) || (rc = act(&y.xout, T * C)))
+      return rc;
+    if ((rc = zeros(&y.z1, T)) || (rc = actf(&y.r1, T)) || (rc = zeros(&y.z2, T)) || (rc = actf(&y.r2, T))) return rc;
+  }
+  if ((rc = act(&nfo, T * C)) || (rc = act(&logits, T * Vpad))) return rc;
+  if ((rc = zeros(&zf, T)) || (rc = actf(&rf, T)) || (rc = actf(&row_loss, T))) return rc;
+  if ((rc = act(&dxa, T * C)) || (rc = act(&dxb, T * C)) || (rc = act(&dqkv, T * QKV)) || (rc = act(&dP, BH * S * S)) ||
+      (rc = act(&Tbig, BH * S * S)) || (rc = act(&t1, T * Hq * D)) || (rc = act(&t2, T * Hq * D)) ||
+      (rc = act(&dkv_h, T * Hq * D)) || (rc = act(&dgu, T * 2 * F)) || (rc = act(&dact, T * F)) ||
+      (rc = act(&datt, T * Hq * D)) || (rc = act(&dln, T * C)))
+    return rc;
+  act_batch = B;
   return SRT_OK;
 }
 
@@ -248,6 +342,7 @@ int Qwen2::forward(int B) {
   if ((rc = embedding_fwd(ids, pf(emb), nullptr, x0, T, S, C, stream))) return rc;
   const __nv_bfloat16* x = x0;
   for (Layer& y : layers) {
+    if ((rc = checkpoint())) return rc;
     if ((rc = rmsnorm_fwd(x, pf(y.n1), y.n1o, y.z1, y.r1, T, C, cfg.rms_eps, stream))) return rc;
     if ((rc = linear_fwd(y.qkv, y.n1o, y.qkv_o, nullptr, T))) return rc;
     if ((rc = rope_apply(y.qkv_o, T, S, Hq, D, QKV, cfg.rope_theta, 0, stream))) return rc;
@@ -298,6 +393,7 @@ int Qwen2::backward(int B, int global_batch) {
   for (int i = L - 1; i >= 0; --i) {
     Layer& y = layers[i];
     const __nv_bfloat16* xin = i == 0 ? x0 : layers[i - 1].xout;
+    if ((rc = checkpoint())) return rc;
     // MLP
     if ((rc = linear_bwd(y.down, dx, y.act, dact, T))) return rc;
     if ((rc = swiglu_bwd(dact, y.gu_o, dgu, T, F, stream))) return rc;
@@ -348,10 +444,13 @@ using namespace srt;
 
 extern "C" {
 
-int srt_qwen2_create(const srt_qwen2_config* cfg, srt_qwen2** out) {
+int srt_qwen2_create(const srt_qwen2_config* cfg, srt_qwen2** out) { return srt_qwen2_create_with_pool(cfg, nullptr, out); }
+
+int srt_qwen2_create_with_pool(const srt_qwen2_config* cfg, srt_pool* pool, srt_qwen2** out) {
   SRT_REQUIRE(cfg && out, "qwen2_create: null argument");
   Qwen2* g = new Qwen2();
   g->cfg = *cfg;
+  g->pool = pool;
   int rc = g->build();
   if (rc == SRT_OK) rc = cudaStreamSynchronize(g->stream) == cudaSuccess ? SRT_OK : SRT_ERR_CUDA;
   if (rc != SRT_OK) { delete g; return rc; }
@@ -438,14 +537,16 @@ int srt_qwen2_upload_tokens(srt_qwen2* h, const int32_t* host_ids, int B) {
 int srt_qwen2_forward_backward(srt_qwen2* h, int B, int global_batch) {
   Qwen2* g = (Qwen2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B && global_batch >= B, "qwen2_forward_backward: upload the tokens of this batch first");
-  int rc = g->forward(B);
-  if (rc) return rc;
+  int rc;
+  if (g->act_batch < B && (rc = g->alloc_activations(B))) return rc;  // regain after a release or a shrink
+  if ((rc = g->forward(B))) return rc;
   return g->backward(B, global_batch);
 }
 
 int srt_qwen2_forward_only(srt_qwen2* h, int B) {
   Qwen2* g = (Qwen2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B, "qwen2_forward_only: upload the tokens of this batch first");
+  if (g->act_batch < B) { int rc = g->alloc_activations(B); if (rc) return rc; }
   return g->forward(B);
 }
 
@@ -453,9 +554,14 @@ int srt_qwen2_optimizer(srt_qwen2* h) {
   Qwen2* g = (Qwen2*)h;
   SRT_REQUIRE(g, "qwen2_optimizer: null handle");
   g->opt_steps++;
-  int rc = adamw(g->P, g->G, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
+  const float* grad = g->accum_pending > 0 ? g->ACC : g->G;
+  int rc = adamw(g->P, grad, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
                  g->cfg.weight_decay, g->opt_steps, g->stream);
   if (rc) return rc;
+  if (g->accum_pending > 0) {
+    SRT_CHECK_CUDA(cudaMemsetAsync(g->ACC, 0, g->n_flat * 4, g->stream));
+    g->accum_pending = 0;
+  }
   return g->transposes();
 }
 
@@ -502,6 +608,32 @@ int srt_qwen2_grad_buffer(srt_qwen2* h, void** ptr, int64_t* n) {
 }
 
 void* srt_qwen2_stream(srt_qwen2* h) { return h ? (void*)((Qwen2*)h)->stream : nullptr; }
-int64_t srt_qwen2_memory_bytes(srt_qwen2* h) { return h ? (int64_t)((Qwen2*)h)->bytes_total : -1; }
+int64_t srt_qwen2_memory_bytes(srt_qwen2* h) { return h ? (int64_t)(((Qwen2*)h)->bytes_total + ((Qwen2*)h)->act_bytes) : -1; }
+
+int srt_qwen2_accumulate(srt_qwen2* h) {
+  Qwen2* g = (Qwen2*)h;
+  SRT_REQUIRE(g, "qwen2_accumulate: null handle");
+  g->accum_pending++;
+  return grad_accumulate(g->ACC, g->G, (int64_t)g->n_flat, g->stream);
+}
+
+int srt_qwen2_release_activations(srt_qwen2* h, size_t* released_bytes) {
+  Qwen2* g = (Qwen2*)h;
+  SRT_REQUIRE(g, "qwen2_release_activations: null handle");
+  return g->release_activations(released_bytes);
+}
+
+int srt_qwen2_shrink_activations(srt_qwen2* h, int B, size_t* released_bytes) {
+  Qwen2* g = (Qwen2*)h;
+  SRT_REQUIRE(g, "qwen2_shrink_activations: null handle");
+  return g->shrink_activations(B, released_bytes);
+}
+
+int srt_qwen2_request_abort(srt_qwen2* h, int on) {
+  Qwen2* g = (Qwen2*)h;
+  SRT_REQUIRE(g, "qwen2_request_abort: null handle");
+  g->abort_flag.store(on ? 1 : 0, std::memory_order_release);
+  return SRT_OK;
+}
 
 }  // extern "C"

@@ -21,6 +21,11 @@ class Qwen2ConfigC(C.Structure):
 
 register({
     "srt_qwen2_create": (None, [C.POINTER(Qwen2ConfigC), C.POINTER(_vp)]),
+    "srt_qwen2_create_with_pool": (None, [C.POINTER(Qwen2ConfigC), _vp, C.POINTER(_vp)]),
+    "srt_qwen2_accumulate": (None, [_vp]),
+    "srt_qwen2_release_activations": (None, [_vp, C.POINTER(C.c_size_t)]),
+    "srt_qwen2_shrink_activations": (None, [_vp, _i, C.POINTER(C.c_size_t)]),
+    "srt_qwen2_request_abort": (None, [_vp, _i]),
     "srt_qwen2_destroy": (None, [_vp]),
     "srt_qwen2_num_params": (_i, [_vp]),
     "srt_qwen2_param_info": (None, [_vp, _i, C.c_char_p, _i, C.POINTER(_i64), C.POINTER(_i)]),
@@ -50,12 +55,13 @@ class Qwen2Step(GradBucketsMixin):
     `transformers.Qwen2ForCausalLM.state_dict()` (`lm_head.weight` is the tied token table and is not listed)."""
 
     def __init__(self, n_layer=24, n_head=14, n_kv_head=2, hidden=896, intermediate=4864, vocab=151936, max_batch=4, seq=2048,
-                 rope_theta=1e6, rms_eps=1e-6, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01):
+                 rope_theta=1e6, rms_eps=1e-6, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, pool=None):
         cfg = Qwen2ConfigC(n_layer, n_head, n_kv_head, hidden, intermediate, vocab, max_batch, seq, rope_theta, rms_eps, lr,
                            betas[0], betas[1], eps, weight_decay)
         self.cfg, self.seq, self.vocab, self.max_batch = cfg, seq, vocab, max_batch
         self._h = _vp()
-        call("srt_qwen2_create", C.byref(cfg), C.byref(self._h))
+        self.pool = pool
+        call("srt_qwen2_create_with_pool", C.byref(cfg), pool if pool else None, C.byref(self._h))
         self.params = {}
         name, shape, ndim = C.create_string_buffer(256), (_i64 * 2)(), _i()
         for i in range(_lib.lib().srt_qwen2_num_params(self._h)):
@@ -117,6 +123,27 @@ class Qwen2Step(GradBucketsMixin):
 
     def synchronize(self) -> None:
         call("srt_qwen2_synchronize", self._h)
+
+    # ---- colocation hooks (the same surface as ResNetStep and Gpt2Step) ----
+    def accumulate(self) -> None:
+        call("srt_qwen2_accumulate", self._h)
+
+    def release_activations(self) -> int:
+        n = C.c_size_t()
+        call("srt_qwen2_release_activations", self._h, C.byref(n))
+        return n.value
+
+    def shrink_activations(self, B: int) -> int:
+        n = C.c_size_t()
+        call("srt_qwen2_shrink_activations", self._h, int(B), C.byref(n))
+        return n.value
+
+    def request_abort(self, on: bool = True) -> None:
+        call("srt_qwen2_request_abort", self._h, int(on))
+
+    def abort_target(self):
+        """(function address, handle) for srt_stub_set_abort_target: the control thread raises the kill flag through it."""
+        return C.cast(_lib.lib().srt_qwen2_request_abort, _vp), self._h
 
     @property
     def stream(self) -> int:

@@ -258,3 +258,18 @@ def test_gpt2_batch_size_adjustment_on_inference_arrival():
     tc.set_train_step(None)
     pool.close()
     srv.close()
+
+
+def test_lm_colocation_experiment_runs_on_small_models():
+    """The Qwen2 + DistilBERT colocation experiment (BASELINE config 5's shape of work) on small models: requests on
+    the gamma trace are served, cold ones trigger a handover that shrinks the training batch, every global batch is
+    still trained in full, and training returns to the full batch after the idle give-back."""
+    from sirius_b200.colocate_bench_lm import run
+    out = run(duration_s=2.0, rate=100.0, cv=4.0, idle_ms=150.0, batch=4, seq=128, infer_seq=32,
+              train_cfg=dict(n_layer=2, n_head=4, n_kv_head=2, hidden=128, intermediate=256, vocab=30016),
+              infer_cfg=dict(n_layer=2, n_head=4, dim=128, hidden_dim=256, vocab=500, max_pos=64), pool_page_mb=2)
+    assert out["requests"] > 20 and out["handovers"] >= 1 and out["final_loss_finite"]
+    assert out["train_sequences"] > 0 and out["train_sequences"] % 4 == 0 or out["killed_micro_batches"] > 0
+    assert min(out["micro_batch_sizes_seen"]) < 4 <= max(out["micro_batch_sizes_seen"])
+    assert out["infer_p99_ms"] < 2000 and out["handover_gib_median"] > 0
+    assert ops.tc_status() == 0

@@ -489,9 +489,16 @@ def run_lm(args, kind):
         out["cpu_baseline"] = {"value": round(GPT2_SEQ / secs[-1], 1), "unit": "tokens/s", "cores": os.cpu_count(),
                                "kind": "port", "sample": "1 timed step after 1 warm-up of batch 1 x 1024 tokens (fp32, "
                                "same model and optimizer; the full workload is batch 8)", "sec_per_step": round(secs[-1], 3)}
+    if rank == 0 and world == 1 and kind == "qwen2" and args.colocate_seconds > 0:
+        # the same training step next to batch-1 DistilBERT-base requests on a bursty (gamma, CV 4) trace
+        step.close()
+        step = None
+        from sirius_b200 import colocate_bench_lm
+        out["colocated"] = colocate_bench_lm.run(duration_s=args.colocate_seconds)
     if rank == 0:
         print(json.dumps(out), flush=True)
-    step.close()
+    if step is not None:
+        step.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

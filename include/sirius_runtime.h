@@ -102,6 +102,9 @@ int srt_dist_close(srt_dist* d);
 int srt_dist_barrier(srt_dist* d, int timeout_ms);                       /* WaitBarrier */
 int srt_dist_send(srt_dist* d, int dst, const char* data, int nbytes);    /* Send */
 int srt_dist_recv(srt_dist* d, int src, char* buf, int cap, int timeout_ms, int* nbytes);
+/* Task-switch flags shared by the ranks of a job (SwitchStub's shared data, control_stub.cc:186-200):
+ * which 0 = global interrupt flag, 1 = a batch has been killed. set != 0 stores value; *out gets the flag. */
+int srt_dist_switch_flag(srt_dist* d, int which, int set, int value, int* out);
 
 enum { SRT_DBD_FIX = 0, SRT_DBD_SIMPLE = 1, SRT_DBD_BY_PERFORMANCE = 2 };
 int srt_dbd_init(srt_dist* d, int dataset_size, int input_batch_size, int global_batch_size,
@@ -162,6 +165,7 @@ typedef struct srt_stub_config {
   int is_colocate_l1;
   int input_batch_size;     /* used when there is no inference server */
   int poll_ms;              /* timed get of the control thread; 0 = 1000 as in control_stub.cc:67-70 */
+  int task_switch;          /* 1 = SwitchStub (kInterruptTrain / kResumeTrain), 0 = ColocateStub */
 } srt_stub_config;
 /* comm == NULL: no colocated inference server (no thread is started). step/dist may be NULL; with a
  * step the kill raises srt_step_request_abort, with a dist rank 0 redistributes on kInferExit. */
@@ -186,6 +190,15 @@ int srt_stub_set_killed_batch_recover(srt_stub* s);
 int srt_stub_set_train_first_epoch_done(srt_stub* s);
 int srt_stub_can_exit_after_infer_workload_done(srt_stub* s);
 double srt_stub_passed_ms_from_set_cmd(srt_stub* s);
+/* SwitchStub (task-switch mode, control_stub.cc:186-400). kInterruptTrain raises the global interrupt flag, kills the
+ * batch in flight and becomes the pending command; the trainer releases its memory and calls
+ * try_interrupt_train_done (replies kInterruptTrainDone once per command; *done = 1 when it replied). The trainer
+ * then polls prepare_resume until kResumeTrain has arrived on every rank (two barriers over the shared flag; a new
+ * interrupt in between is answered at once); the master replies kResumeTrainDone. switch_flag reads or writes the
+ * shared flags (which as srt_dist_switch_flag). */
+int srt_stub_try_interrupt_train_done(srt_stub* s, int barrier, int* done);
+int srt_stub_prepare_resume(srt_stub* s, int* resumed);
+int srt_stub_switch_flag(srt_stub* s, int which, int set, int value, int* out);
 /* StubProfiler: microsecond unix timestamps of adjust requests / replies; returns how many exist. */
 int srt_stub_adjust_timestamps(srt_stub* s, int done, int64_t* out, int cap);
 

@@ -26,7 +26,7 @@ class AdjusterConfig(C.Structure):
 
 class StubConfig(C.Structure):
     _fields_ = [("rank", _i), ("world_size", _i), ("kill_batch_on_recv", _i), ("is_colocate_l1", _i),
-                ("input_batch_size", _i), ("poll_ms", _i)]
+                ("input_batch_size", _i), ("poll_ms", _i), ("task_switch", _i)]
 
 
 class PoolConfig(C.Structure):
@@ -59,6 +59,7 @@ register({
     "srt_dist_barrier": (None, [_vp, _i]),
     "srt_dist_send": (None, [_vp, _i, C.c_char_p, _i]),
     "srt_dist_recv": (None, [_vp, _i, C.c_char_p, _i, _i, _pi]),
+    "srt_dist_switch_flag": (None, [_vp, _i, _i, _i, _pi]),
     "srt_dbd_init": (None, [_vp, _i, _i, _i, _i, _i]),
     "srt_dbd_distribute_batch": (None, [_vp, _vp, _i, _i, _i]),
     "srt_dbd_get_batch": (None, [_vp, _i, _pi, _i, _pi, _pi]),
@@ -99,6 +100,9 @@ register({
     "srt_stub_set_train_first_epoch_done": (None, [_vp]),
     "srt_stub_can_exit_after_infer_workload_done": (_i, [_vp]),
     "srt_stub_passed_ms_from_set_cmd": (_d, [_vp]),
+    "srt_stub_try_interrupt_train_done": (None, [_vp, _i, _pi]),
+    "srt_stub_prepare_resume": (None, [_vp, _pi]),
+    "srt_stub_switch_flag": (None, [_vp, _i, _i, _i, _pi]),
     "srt_stub_adjust_timestamps": (_i, [_vp, _i, C.POINTER(_i64), _i]),
     "srt_pool_create": (None, [C.POINTER(PoolConfig), C.POINTER(_vp)]),
     "srt_pool_destroy": (None, [_vp]),

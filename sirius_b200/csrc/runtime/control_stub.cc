@@ -7,6 +7,9 @@
 // and StubProfiler (:642-652). The reference kills a batch by rejecting CUDA calls and dropping the
 // launches queued in its libcuda shim; here the step executor is told to stop between units
 // (srt_step_request_abort), which bounds the drain to the units already in flight.
+//
+// With cfg.task_switch the same object is the SwitchStub (:186-400): kInterruptTrain / kResumeTrain, the
+// interrupt flag shared by the ranks, TryInterruptTrainDone and PrepareResume.
 #include <sys/time.h>
 
 #include <atomic>
@@ -50,6 +53,68 @@ struct Stub {
   std::chrono::steady_clock::time_point set_cmd_time = std::chrono::steady_clock::now();
   std::vector<int64_t> req_us, done_us;
   int current_bs = 0;
+  // task switch
+  uint64_t last_reply_cmd_id = 0;
+  int local_flag[2] = {0, 0};  // stand-in for the shared flags when there is no dist segment (one rank)
+
+  int flag(int which, int set, int value) {
+    int out = 0;
+    if (dist) { srt_dist_switch_flag(dist, which, set, value, &out); return out; }
+    if (set) local_flag[which] = value ? 1 : 0;
+    return local_flag[which];
+  }
+  void barrier() { if (dist && cfg.world_size > 1) srt_dist_barrier(dist, 30000); }
+
+  // caller holds mu
+  bool try_interrupt_done_locked(bool with_barrier) {
+    if (cmd_id > last_reply_cmd_id) {
+      const uint64_t id = cmd_id;
+      last_reply_cmd_id = cmd_id;
+      cmd_id = 0;
+      request_abort(0);
+      if (with_barrier) barrier();
+      if (cfg.rank == 0 && comm) put(id, SRT_EV_INTERRUPT_TRAIN_DONE, 0);
+      return true;
+    }
+    return false;
+  }
+
+  void process_switch(const srt_ctrl_msg& msg) {
+    std::unique_lock<std::mutex> lk(mu);
+    switch (msg.event) {
+      case SRT_EV_INTERRUPT_TRAIN:
+        if (cmd.load() == SRT_EV_INTERRUPT_TRAIN && cmd_id == 0) {
+          // already interrupted and answered: the memory is free, reply at once
+          last_reply_cmd_id = msg.id;
+          if (cfg.rank == 0 && comm) put(msg.id, SRT_EV_INTERRUPT_TRAIN_DONE, 0);
+        } else {
+          if (cfg.rank == 0) { flag(0, 1, 1); flag(1, 1, 0); }
+          if (cfg.kill_batch_on_recv && has_killed_batch_recover.load(std::memory_order_acquire)) {
+            std::unique_lock<std::mutex> step_lock(step_mu);  // never inside the optimizer step
+            request_abort(1);
+            has_killed_batch_recover = false;
+          }
+          cmd_id = msg.id;
+          cmd.store(SRT_EV_INTERRUPT_TRAIN);
+          set_cmd_time = std::chrono::steady_clock::now();
+          std::lock_guard<std::mutex> pl(prof_mu);
+          req_us.push_back(unix_us());
+        }
+        break;
+      case SRT_EV_RESUME_TRAIN:
+        if (cmd.load() == SRT_EV_INTERRUPT_TRAIN && cmd_id == 0) {
+          cmd.store(SRT_EV_RESUME_TRAIN);
+          flag(0, 1, 0);
+        }  // otherwise ignored, as in the reference: the interrupt has not been answered yet
+        break;
+      case SRT_EV_INFERENCE_WORKLOAD_DONE:
+        infer_workload_done_ms = unix_us() / 1000;
+        break;
+      default:
+        set_error("SwitchStub: unknown command %d", msg.event);
+        break;
+    }
+  }
 
   void put(uint64_t id, int event, int value) {
     srt_ctrl_msg m = {id, event, value};
@@ -57,6 +122,7 @@ struct Stub {
   }
 
   void process(const srt_ctrl_msg& msg) {
+    if (cfg.task_switch) return process_switch(msg);
     std::unique_lock<std::mutex> lk(mu);
     switch (msg.event) {
       case SRT_EV_COLOCATE_ADJUST_L1:
@@ -250,6 +316,50 @@ int srt_stub_can_exit_after_infer_workload_done(srt_stub* h) {
   if (s->infer_workload_done_ms == 0) return 0;
   return unix_us() / 1000 - s->infer_workload_done_ms > 30 * 1000 ? 1 : 0;
 }
+int srt_stub_try_interrupt_train_done(srt_stub* h, int barrier, int* done) {
+  Stub* s = (Stub*)h;
+  SRT_REQUIRE(s, "stub: null handle");
+  std::unique_lock<std::mutex> lk(s->mu);
+  const bool ok = s->try_interrupt_done_locked(barrier != 0);
+  if (ok) {
+    std::lock_guard<std::mutex> pl(s->prof_mu);
+    s->done_us.push_back(unix_us());
+  }
+  if (done) *done = ok ? 1 : 0;
+  return SRT_OK;
+}
+
+// PrepareResume (control_stub.cc:339-392): every rank calls it in the same loop iteration.
+int srt_stub_prepare_resume(srt_stub* h, int* resumed) {
+  Stub* s = (Stub*)h;
+  SRT_REQUIRE(s && resumed, "stub: null argument");
+  std::unique_lock<std::mutex> lk(s->mu);
+  if (s->cmd.load() == SRT_EV_INTERRUPT_TRAIN && s->cmd_id != 0) s->flag(0, 1, 1);  // a new interrupt came in
+  s->barrier();
+  const bool resume = s->flag(0, 0, 0) == 0;  // cleared by the master when kResumeTrain arrived
+  s->barrier();
+  if (!resume) {
+    s->try_interrupt_done_locked(false);
+    s->barrier();
+    *resumed = 0;
+    return SRT_OK;
+  }
+  s->cmd.store(SRT_EV_RESUME_TRAIN);
+  s->has_killed_batch_recover = true;
+  s->barrier();
+  if (s->cfg.rank == 0 && s->comm) s->put(0, SRT_EV_RESUME_TRAIN_DONE, 0);
+  *resumed = 1;
+  return SRT_OK;
+}
+
+int srt_stub_switch_flag(srt_stub* h, int which, int set, int value, int* out) {
+  Stub* s = (Stub*)h;
+  SRT_REQUIRE(s && (which == 0 || which == 1), "stub_switch_flag: bad argument");
+  const int v = s->flag(which, set, value);
+  if (out) *out = v;
+  return SRT_OK;
+}
+
 double srt_stub_passed_ms_from_set_cmd(srt_stub* h) {
   Stub* s = (Stub*)h;
   if (!s) return 0;

@@ -87,6 +87,10 @@ struct DistLayout {
   shm::Mutex perf_mu;
   int perf_n;
   PerfEntry perf[kPerfCap];
+  // task-switch flags shared by the ranks of one job (SwitchStub's "switch_stub" shared data,
+  // pytorch/torch_col/csrc/control_stub.cc:186-200): [0] global interrupt flag, [1] has a batch been killed
+  shm::Mutex sw_mu;
+  int sw_flag[2];
 };
 
 }  // namespace
@@ -240,6 +244,7 @@ int srt_dist_open(const char* name, int rank, int world_size, int timeout_ms, sr
         for (int j = 0; j < SRT_MAX_DEVICE_NUM; ++j) { l->mail[i][j].mu.init(); l->mail[i][j].cond.init(); }
       l->mu.init(); l->vote_cv.init(); l->vote_cnt.store(0);
       l->perf_mu.init();
+      l->sw_mu.init(); l->sw_flag[0] = l->sw_flag[1] = 0;
     }, &err);
   } else {
     ok = d->seg.open(nm, kDistMagic, timeout_ms, &err);
@@ -565,6 +570,16 @@ int srt_dbd_info(srt_dist* h, int which, int rank, int* out) {
     case SRT_DBD_RANK_PROCED: *out = l->proced_per_train[rank]; break;
     default: set_error("dbd_info: unknown item %d", which); return SRT_ERR_INVALID;
   }
+  return SRT_OK;
+}
+
+int srt_dist_switch_flag(srt_dist* h, int which, int set, int value, int* out) {
+  DIST_CHECK(h);
+  SRT_REQUIRE(which == 0 || which == 1, "dist_switch_flag: unknown flag %d", which);
+  DistLayout* l = ((Dist*)h)->L();
+  shm::Guard g(l->sw_mu);
+  if (set) l->sw_flag[which] = value ? 1 : 0;
+  if (out) *out = l->sw_flag[which];
   return SRT_OK;
 }
 

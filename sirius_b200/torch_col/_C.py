@@ -246,10 +246,10 @@ def rearrange_memory(): raise RuntimeError('rearrange_memory is deprecated in th
 
 # ---- stubs ------------------------------------------------------------------------------------
 class _StubBase:
-    def __init__(self, batch_size: int, kill_batch_on_recv=None, poll_ms=0):
+    def __init__(self, batch_size: int, kill_batch_on_recv=None, poll_ms=0, task_switch=False):
         cfg = StubConfig(_Config.rank, _Config.world_size,
                          int(_Config.kill_batch_on_recv() if kill_batch_on_recv is None else kill_batch_on_recv),
-                         int(_Config.train_mode == TrainMode.COLOCATE_L1), batch_size, poll_ms)
+                         int(_Config.train_mode == TrainMode.COLOCATE_L1), batch_size, poll_ms, int(task_switch))
         self._h = C.c_void_p()
         # the ResNet executor is known to the stub directly; any other step object names its kill entry point
         target = _step.abort_target() if hasattr(_step, 'abort_target') else None
@@ -304,6 +304,41 @@ class PyColocateStub(_StubBase):
 
     @property
     def unpub_target_batch_size(self): return self._bs(True)
+
+    def _stamps(self, done):
+        n = _lib.lib().srt_stub_adjust_timestamps(self._h, done, None, 0)
+        buf = (C.c_int64 * max(n, 1))()
+        n = _lib.lib().srt_stub_adjust_timestamps(self._h, done, buf, n)
+        return list(buf[:n])
+
+
+class PySwitchStub(_StubBase):
+    """SwitchStub of the reference (cython/ctrl_stub.pxi, csrc/control_stub.cc:186-400): interrupt / resume of the
+    whole training job for the task-switch modes."""
+
+    def __init__(self, batch_size: int = 0, poll_ms: int = 0):
+        super().__init__(batch_size, poll_ms=poll_ms, task_switch=True)
+
+    def try_interrupt_train_done(self, barrier: bool = False) -> bool:
+        v = C.c_int()
+        call("srt_stub_try_interrupt_train_done", self._h, int(barrier), C.byref(v))
+        return bool(v.value)
+
+    def prepare_resume(self) -> bool:
+        v = C.c_int()
+        call("srt_stub_prepare_resume", self._h, C.byref(v))
+        return bool(v.value)
+
+    def _flag(self, which, set_, value=0):
+        v = C.c_int()
+        call("srt_stub_switch_flag", self._h, which, int(set_), int(value), C.byref(v))
+        return bool(v.value)
+
+    def get_global_interrupt_flag(self) -> bool: return self._flag(0, False)
+    def set_global_interrupt_flag(self, flag: bool): self._flag(0, True, flag)
+    def get_global_has_batch_killed(self) -> bool: return self._flag(1, False)
+    def set_global_has_batch_killed(self, flag: bool): self._flag(1, True, flag)
+    def set_killed_batch_recover(self): call("srt_stub_set_killed_batch_recover", self._h)
 
     def _stamps(self, done):
         n = _lib.lib().srt_stub_adjust_timestamps(self._h, done, None, 0)

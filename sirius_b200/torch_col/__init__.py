@@ -3,7 +3,7 @@
 from . import xsched  # noqa: F401
 from ._C import *  # noqa: F401,F403
 from ._C import (CtrlEvent, ColocateCtrlHookMode, TrainMode, PyCtrlMsgEntry, PyInfTraCommunicator, PyColocateStub,  # noqa: F401
-                 PyDummyStub, dist, torch_col_init, torch_col_shutdown, set_train_step, get_train_step,
+                 PyDummyStub, PySwitchStub, dist, torch_col_init, torch_col_shutdown, set_train_step, get_train_step,
                  set_memory_pool, init_train_info, update_current_batch_size, get_train_rank, get_train_world_size,
                  is_train_master, is_configured, get_colocate_train_mode, get_colocate_ctrl_hook_mode,
                  is_enable_shared_tensor, is_enable_xsched, has_colocated_infer_server, get_unix_timestamp,

@@ -55,7 +55,7 @@ class CtrlBase(abc.ABC):
         if self.train_mode.is_colocate():
             return self.adjust()
         if self.train_mode.is_taskswitch():
-            raise NotImplementedError("task-switch mode is not built")
+            return self.switch(bool(barrier))
 
     def register_pytorch_hook(self, module_list: List = ()):  # the executor polls the kill flag itself
         pass
@@ -179,9 +179,81 @@ class DummyCtrl(CtrlBase):
 
 
 class SwitchCtrl(CtrlBase):
-    """Task-switch controller (colocate_ctrl.py:117-301): not built (interrupt/resume of the whole job)."""
-    def __init__(self, *a, **k):
-        raise NotImplementedError("task-switch mode is not built; use colocate-l1 / colocate-l2 / normal")
+    """Task-switch controller (colocate_ctrl.py:117-301): on kInterruptTrain the batch in flight is killed, the
+    trainer drops its whole activation set, returns the pages and replies kInterruptTrainDone; it then waits in
+    `Trainer` until kResumeTrain arrives (`PySwitchStub.prepare_resume`). taskswitch-l0 never interrupts."""
+
+    def __init__(self, train_mode, hook_mode, num_epoch, batch_size, stub_poll_ms: int = 0):
+        assert train_mode in (TrainMode.TASKSWITCH_L1, TrainMode.TASKSWITCH_L0)
+        super().__init__(train_mode, hook_mode, num_epoch, batch_size)
+        self._stub = _C.PySwitchStub(batch_size, poll_ms=stub_poll_ms)
+        self.switch_log = []  # (release_ms, empty_cache_ms, reply_ms, released_bytes, start time.time())
+
+    def check_kill(self, where: str):
+        """What the reference's forward/backward hooks do (colocate_ctrl.py:183-245)."""
+        if self.train_mode == TrainMode.TASKSWITCH_L1 and self._stub.cmd == CtrlEvent.kInterruptTrain:
+            xsched.kill_batch()
+            raise SwitchL1Exception(where)
+
+    @contextlib.contextmanager
+    def steps_no_interrupt(self):
+        if self.train_mode == TrainMode.TASKSWITCH_L0:
+            yield
+            return
+        step = _C.get_train_step()
+        if step is not None and hasattr(step, 'synchronize'):
+            step.synchronize()  # SyncAllStreams
+        if self._stub.cmd == CtrlEvent.kInterruptTrain:
+            raise SwitchL1Exception('before_critical_section')
+        self._stub.StepsNoInteruptBegin()
+        if self._stub.cmd == CtrlEvent.kInterruptTrain:
+            self._stub.StepsNoInteruptEnd()
+            raise SwitchL1Exception('before_critical_section')
+        try:
+            yield
+            if step is not None and hasattr(step, 'synchronize'):
+                step.synchronize()
+        finally:
+            self._stub.StepsNoInteruptEnd()
+        # an interrupt may have arrived during the critical section: nothing is executing now
+        if _C.get_train_world_size() == 1 and self._stub.cmd == CtrlEvent.kInterruptTrain:
+            self.switch(barrier=False)
+
+    def switch(self, barrier: bool):
+        if self.train_mode != TrainMode.TASKSWITCH_L1:
+            raise RuntimeError(f"Unsupported train_mode: {self.train_mode.name}")
+        return self.switch_l1(barrier)
+
+    def switch_l1(self, barrier: bool):
+        t0 = time.time()
+        with EventManager.record_duration_event('switch_l1'):
+            released = _C.release_interm_memory()
+            t1 = time.time()
+            released = max(int(released or 0), int(MemoryPool.empty_cache() or 0))
+            t2 = time.time()
+            succ = self.try_reply_interrupt(barrier)
+            t3 = time.time()
+        if succ:
+            self.switch_log.append(((t1 - t0) * 1e3, (t2 - t1) * 1e3, (t3 - t2) * 1e3, released, t0))
+        return succ
+
+    def try_reply_interrupt(self, barrier): return self._stub.try_interrupt_train_done(barrier)
+
+    @property
+    def target_batch_size(self): return self.input_batch_size
+
+    @property
+    def unpub_target_batch_size(self): return self.input_batch_size
+
+    def report_batch_size(self, batch_size): self._stub.report_batch_size(batch_size)
+
+    def train_end(self):
+        if _C.is_enable_shared_tensor():
+            MemoryPool.empty_cache()
+        self._stub.train_end()
+
+    def set_killed_batch_recover(self): self._stub.set_killed_batch_recover()
+    def set_killed_batch_reconfiged(self): pass
 
 
 def create_colocate_ctrl(train_mode: TrainMode, hook_mode: ColocateCtrlHookMode, num_epoch: int, batch_size: int,
@@ -190,7 +262,7 @@ def create_colocate_ctrl(train_mode: TrainMode, hook_mode: ColocateCtrlHookMode,
         return DummyCtrl(train_mode, hook_mode, num_epoch, batch_size)
     if train_mode.is_colocate():
         return ColocateCtrl(train_mode, hook_mode, num_epoch, batch_size, **kw)
-    return SwitchCtrl(train_mode, hook_mode, num_epoch, batch_size)
+    return SwitchCtrl(train_mode, hook_mode, num_epoch, batch_size, **kw)
 
 
 def get_colocate_ctrl() -> Union[DummyCtrl, ColocateCtrl]:

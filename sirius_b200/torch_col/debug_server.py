@@ -45,6 +45,31 @@ class DebugServer:
             self.comm.update_field(r, 6, bs)
         self.comm.put_all_inf2tra(CtrlEvent.kInferExit, 0, [0] * self.world)
 
+    def interrupt_train(self) -> int:
+        """Controller::InterruptTrain (controller.cc:152-170): kInterruptTrain to every rank."""
+        cid = self.cmd_id
+        self.cmd_id += 1
+        self.comm.put_all_inf2tra(CtrlEvent.kInterruptTrain, cid, [0] * self.world)
+        return cid
+
+    def resume_train(self) -> int:
+        """Controller::ResumeTrain (controller.cc:190-206): kResumeTrain to rank 0 only."""
+        cid = self.cmd_id
+        self.cmd_id += 1
+        self.comm.put_inf2tra(CtrlEvent.kResumeTrain, cid, 0, 0)
+        return cid
+
+    def wait_event(self, event: CtrlEvent, cmd_id: Optional[int] = None, count: int = 1, timeout_s: float = 30.0) -> float:
+        """Seconds until `count` status messages of `event` (with this command id, when given) have arrived."""
+        t0 = time.time()
+        while time.time() - t0 < timeout_s:
+            with self._lock:
+                n = sum(1 for _, m in self.status if m.event == event and (cmd_id is None or m.id == cmd_id))
+            if n >= count:
+                return time.time() - t0
+            time.sleep(0.0005)
+        raise TimeoutError(f"{event.name} (id {cmd_id}) not received {count} time(s)")
+
     def inference_workload_done(self):
         self.comm.put_all_inf2tra(CtrlEvent.kInferenceWorkloadDone, 0, [0] * self.world)
 

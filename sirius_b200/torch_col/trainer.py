@@ -102,6 +102,11 @@ class Trainer:
         _C.dist.wait_barrier()
         xsched.kill_batch()  # the in-flight units drain; nothing of the batch is executing afterwards
         self.batch_manager.abort_batch(epoch_idx, batch_idx, batch)
+        from .colocate_ctrl import SwitchCtrl
+        if isinstance(self.dynamic_dataset.col_ctrl, SwitchCtrl):
+            if _C.is_train_master():
+                self.dynamic_dataset.col_ctrl._stub.set_global_has_batch_killed(True)
+            _C.dist.wait_barrier()
         bs = self.dynamic_dataset.get_batch_size(batch)
         with EventManager.record_duration_event(f'batch_exception_{epoch_idx:02d}_{batch_idx:03d}_{bs:02d}'):
             self.dynamic_dataset.col_ctrl.release_and_reply(True)
@@ -118,6 +123,12 @@ class Trainer:
                 if _C.get_colocate_train_mode().is_colocate():
                     self.dynamic_dataset.col_ctrl.set_killed_batch_reconfiged()
             _C.dist.wait_barrier()
+        # task switch: the job stays off the GPU until the server sends kResumeTrain (trainer.py:243-248)
+        if _C.get_colocate_train_mode().is_taskswitch():
+            with EventManager.record_duration_event(f'wait_resume_{epoch_idx:02d}_{batch_idx:03d}'):
+                while not self.dynamic_dataset.col_ctrl._stub.prepare_resume():
+                    time.sleep(1e-3)
+                _C.dist.wait_barrier()
         self._last_max_batch_size_from_last_kill = None
 
     def _is_ddp_training(self):

@@ -273,3 +273,84 @@ def test_lm_colocation_experiment_runs_on_small_models():
     assert min(out["micro_batch_sizes_seen"]) < 4 <= max(out["micro_batch_sizes_seen"])
     assert out["infer_p99_ms"] < 2000 and out["handover_gib_median"] > 0
     assert ops.tc_status() == 0
+
+
+def test_gpt2_task_switch_releases_everything_and_resumes():
+    """taskswitch-l1 on a pool-backed Gpt2Step: kInterruptTrain kills the micro-batch in flight, the trainer returns
+    its whole activation set to the pool and the master replies kInterruptTrainDone; it stays off the GPU until
+    kResumeTrain, then maps its pages again and trains every sample of every epoch."""
+    import threading
+    from oracle import gpt2_oracle as GO
+    from sirius_b200 import torch_col as tc
+    from sirius_b200.gpt2_step import Gpt2Step
+    tag = f"{os.getpid()}_{uuid.uuid4().hex[:6]}"
+    os.environ.update({"COLTRAIN_MODE": "taskswitch-l1", "COLTRAIN_HOOK_MODE": "xsched-sync2", "COLTRAIN_USE_XSCHED": "1",
+                       "COLTRAIN_HAS_INFER_SERVER": "1", "COLTRAIN_USE_SHARED_TENSOR": "1",
+                       "SIRIUS_B200_COMM_NAME": f"srt_ts_comm_{tag}", "SIRIUS_B200_DIST_NAME": f"srt_ts_dist_{tag}"})
+    cfg = dict(n_layer=2, n_head=4, d_model=128, vocab=30016, ctx=64)
+    BS, SEQ, DS, EPOCHS = 4, 64, 32, 2
+    model = GO.build_model(**cfg, seed=0)
+    srv = tc.DebugServer(1, os.environ["SIRIUS_B200_COMM_NAME"])
+    pool = PagePool(1.0, page_mb=2)
+    tc.setup_colocate_training(0, 1, False, False)
+    step = Gpt2Step(**cfg, max_batch=BS, seq=SEQ, pool=pool.handle)
+    step.load_state_dict(GO.state_arrays(model))
+    tc.set_train_step(step)
+    tc.set_memory_pool(pool.handle)
+    ctrl = tc.create_colocate_ctrl(tc.get_colocate_train_mode(), tc.get_colocate_ctrl_hook_mode(), EPOCHS, BS, stub_poll_ms=5)
+    assert isinstance(ctrl, tc.SwitchCtrl)
+    ds, mgr = tc.init_dynamic_batch(DS, tc.DatasetType.TEXT_GEN, tc.TextDatasetConfig(SEQ), BS, global_batch_size=BS,
+                                    enable_grad_accumulate=True, checkpoint_micro_batch=True)
+    tc.init_train_info(BS, BS, "gpt2")
+    acc = tc.GradAccumulator(step)
+    state = {"n": 0, "cid": None, "usage_interrupted": None, "sizes": [], "losses": [], "free_before": None}
+
+    def server():                                              # answers the interrupt reply with a resume, later
+        srv.wait_event(tc.CtrlEvent.kInterruptTrainDone, None, 1, 60)
+        state["usage_interrupted"] = (pool.stat("train_usage"), pool.stat("free_pages"))
+        time.sleep(0.2)
+        srv.resume_train()
+
+    th = threading.Thread(target=server, daemon=True)
+    th.start()
+
+    def iter_train_fn(batch):
+        state["n"] += 1
+        step.upload_tokens(batch["input_ids"])
+        if state["n"] == 3 and state["cid"] is None:
+            state["free_before"] = pool.stat("free_pages")
+            state["cid"] = srv.interrupt_train()
+            time.sleep(0.05)                                   # the control thread raises the kill flag
+        try:
+            step.forward_backward(BS)
+        except SrtError as e:
+            if "aborted" in str(e):
+                raise tc.SwitchL1Exception("killed in the executor")
+            raise
+        ctrl.check_kill("after backward")
+        loss = step.loss()
+        mgr.optimizer_step(batch, step, grad_accumulator=acc)
+        state["sizes"].append(len(batch))
+        state["losses"].append(loss)
+        return loss
+
+    trainer = tc.Trainer(step, iter_train_fn)
+    ctrl.train_start()
+    for e in range(EPOCHS):
+        trainer.train_one_epoch(e)
+    ctrl.train_end()
+    step.synchronize()
+    th.join(30)
+    assert trainer.get_overall_stat().killed_batch == 1
+    assert [m.id for _, m in srv.events(tc.CtrlEvent.kInterruptTrainDone)] == [state["cid"]]
+    assert len(srv.events(tc.CtrlEvent.kResumeTrainDone)) == 1
+    usage, free_pages = state["usage_interrupted"]
+    assert usage == 0 and free_pages > state["free_before"]    # the whole activation set went back to the pool
+    assert len(ctrl.switch_log) == 1 and ctrl.switch_log[0][3] > 0
+    assert sum(state["sizes"]) == DS * EPOCHS and set(state["sizes"]) == {BS}
+    assert all(np.isfinite(state["losses"])) and ops.tc_status() == 0
+    step.close()
+    tc.cleanup_colocate_training(False)
+    tc.set_train_step(None)
+    pool.close()
+    srv.close()

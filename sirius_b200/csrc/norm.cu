@@ -14,7 +14,8 @@ namespace srt {
 namespace {
 
 constexpr int NT = 256;
-constexpr int ROWS_PER_THREAD = 8;   // loads in flight per thread
+constexpr int ROWS_PER_THREAD = 8;   // rows per thread and batch
+constexpr int BWD_ROWS = 4;          // rows in flight per thread in the backward sums (two or three tensors per row)
 constexpr int FIN_CH = 8;            // channels per finalize block (8 x 16 B = one 128-byte line)
 constexpr int FIN_LANES = 32;        // slab lanes per channel in the finalize kernels
 constexpr int TARGET_BLOCKS = 4 * 148;  // blocks a streaming pass wants in flight (4 per SM)
@@ -265,12 +266,11 @@ bn_apply_kernel(const T* __restrict__ z, const T* __restrict__ residual, T* __re
 // otherwise recomputed from z with the same fused multiply-add the forward pass used, which has
 // the same sign as the stored (rounded) y.
 template <typename T, int V>
-__device__ __forceinline__ void apply_relu_mask(float (&g)[V], const float (&x)[V], const T* y_ptr,
+__device__ __forceinline__ void apply_relu_mask(float (&g)[V], const float (&x)[V], const Vec16<T>* y_vec,
                                                 const float* __restrict__ scale,
                                                 const float* __restrict__ shift, int c0) {
-  if (y_ptr) {
-    Vec16<T> yv;
-    yv.load(y_ptr);
+  if (y_vec) {
+    const Vec16<T>& yv = *y_vec;
     float yy[V];
     yv.unpack(yy);
 #pragma unroll
@@ -288,8 +288,10 @@ __device__ __forceinline__ void apply_relu_mask(float (&g)[V], const float (&x)[
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(NT)
+// MASK: 0 no ReLU, 1 mask from the stored output y, 2 mask recomputed from z (a compile-time choice, so the
+// per-channel vectors and loads of the unused variant take no registers)
+template <typename T, int MASK>
+__global__ void __launch_bounds__(NT, 3)
 bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z,
                int64_t rows, int C, RowMap m, const float* __restrict__ mean,
                const float* __restrict__ invstd, const float* __restrict__ scale,
@@ -306,26 +308,27 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
     float mu[V], is[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) { mu[v] = mean[cv * V + v]; is[v] = invstd[cv * V + v]; }
-    for (int it = 0; it < m.iters; ++it) {
-      const int64_t r0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * ROWS_PER_THREAD * m.RL + rl;
-      Vec16<T> a[ROWS_PER_THREAD], b[ROWS_PER_THREAD];
+    for (int it = 0; it < m.iters * (ROWS_PER_THREAD / BWD_ROWS); ++it) {
+      const int64_t r0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * BWD_ROWS * m.RL + rl;
+      Vec16<T> a[BWD_ROWS], b[BWD_ROWS], yv[BWD_ROWS];  // the stored output travels with the other two loads
 #pragma unroll
-      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      for (int i = 0; i < BWD_ROWS; ++i) {
         const int64_t r = r0 + (int64_t)i * m.RL;
         if (r < rows) {
           const int64_t o = r * C + (int64_t)cv * V;
           a[i].load(dy + o);
           b[i].load(z + o);
+          if (MASK == 1) yv[i].load(y + o);
         }
       }
 #pragma unroll
-      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      for (int i = 0; i < BWD_ROWS; ++i) {
         const int64_t r = r0 + (int64_t)i * m.RL;
         if (r >= rows) continue;
         float g[V], x[V];
         a[i].unpack(g);
         b[i].unpack(x);
-        if (relu) apply_relu_mask<T, V>(g, x, y ? y + r * C + (int64_t)cv * V : nullptr, scale, shift, cv * V);
+        if (MASK != 0) apply_relu_mask<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, scale, shift, cv * V);
 #pragma unroll
         for (int v = 0; v < V; ++v) {
           sg[v] += g[v];
@@ -357,8 +360,8 @@ bn_bwd_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
   coef[2 * C + c] = -k0 * mg;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(NT)
+template <typename T, int MASK>
+__global__ void __launch_bounds__(NT, 4)
 bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z, T* __restrict__ dz,
              T* __restrict__ dres, int64_t nvec, int CV, int C, const float* __restrict__ mean,
              const float* __restrict__ coef,
@@ -366,11 +369,15 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
   pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
-  Vec16<T> a[UNR], b[UNR];
+  Vec16<T> a[UNR], b[UNR], yv[UNR];
 #pragma unroll
   for (int u = 0; u < UNR; ++u) {
     const int64_t i = base + (int64_t)u * NT;
-    if (i < nvec) { a[u].load(dy + i * V); b[u].load(z + i * V); }
+    if (i < nvec) {
+      a[u].load(dy + i * V);
+      b[u].load(z + i * V);
+      if (MASK == 1) yv[u].load(y + i * V);
+    }
   }
 #pragma unroll
   for (int u = 0; u < UNR; ++u) {
@@ -380,7 +387,7 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
     float g[V], x[V];
     a[u].unpack(g);
     b[u].unpack(x);
-    if (relu) apply_relu_mask<T, V>(g, x, y ? y + i * V : nullptr, scale, shift, cv * V);
+    if (MASK != 0) apply_relu_mask<T, V>(g, x, MASK == 1 ? &yv[u] : nullptr, scale, shift, cv * V);
     if (dres) {
       Vec16<T> o;
       o.pack(g);
@@ -538,15 +545,19 @@ static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t r
   RowMap m = make_row_map(rows, C, V);
   double* partial = (double*)scratch;
   float* coef = (float*)((char*)scratch + (size_t)m.S * C * 2 * sizeof(double));
-  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_bwd_partial<T>, dim3(m.S, m.GY), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z, rows, C,
-             m, mean, invstd, scale, shift, relu, partial);
+  const int mask = !relu ? 0 : (y ? 1 : 2);
+  const bool early = (pdl_classes() & PDL_NORM) != 0;
+  auto partial_k = mask == 0 ? bn_bwd_partial<T, 0> : mask == 1 ? bn_bwd_partial<T, 1> : bn_bwd_partial<T, 2>;
+  launch_pdl_if(early, partial_k, dim3(m.S, m.GY), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z, rows, C, m, mean,
+                invstd, scale, shift, relu, partial);
   SRT_LAUNCH_CHECK();
-  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_bwd_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st, partial, m.S, C, rows,
-             gamma, invstd, dgamma, dbeta, coef);
+  launch_pdl_if(early, bn_bwd_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st, partial, m.S, C, rows,
+                gamma, invstd, dgamma, dbeta, coef);
   SRT_LAUNCH_CHECK();
   const int64_t nvec = rows * C / V;
-  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_bwd_apply<T>, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z,
-             (T*)dz, (T*)dres, nvec, C / V, C, mean, (const float*)coef, scale, shift, relu);
+  auto apply_k = mask == 0 ? bn_bwd_apply<T, 0> : mask == 1 ? bn_bwd_apply<T, 1> : bn_bwd_apply<T, 2>;
+  launch_pdl_if(early, apply_k, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z, (T*)dz,
+                (T*)dres, nvec, C / V, C, mean, (const float*)coef, scale, shift, relu);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

@@ -385,11 +385,10 @@ struct BwdArgs {
 // ReLU mask of y = relu(z*scale + shift [+ residual]): from the stored y when given, otherwise recomputed
 // from z with the fused multiply-add of the forward pass (same sign as the stored, rounded y).
 template <typename T, int V>
-__device__ __forceinline__ void mask_gradient(float (&g)[V], const float (&x)[V], const T* y_ptr,
+__device__ __forceinline__ void mask_gradient(float (&g)[V], const float (&x)[V], const Vec16<T>* y_vec,
                                               const float (&sc)[V], const float (&sf)[V]) {
-  if (y_ptr) {
-    Vec16<T> yv;
-    yv.load(y_ptr);
+  if (y_vec) {
+    const Vec16<T>& yv = *y_vec;
     float yy[V];
     yv.unpack(yy);
 #pragma unroll
@@ -400,7 +399,9 @@ __device__ __forceinline__ void mask_gradient(float (&g)[V], const float (&x)[V]
   }
 }
 
-template <typename T>
+// MASK: 0 no ReLU, 1 mask from the stored output y, 2 mask recomputed from z (compile-time, so the vectors and
+// loads of the unused variants take no registers)
+template <typename T, int MASK>
 __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
   pdl_enter();
   constexpr int V = Vec16<T>::N;
@@ -417,7 +418,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
   const int t = threadIdx.x;
   const int tc = t % m.TC, rl = t / m.TC;
   const int n_items = m.NS * m.GY;
-  const bool recompute_mask = p.relu && !yk;
+  constexpr bool recompute_mask = MASK == 2;
   unsigned gen = t == 0 ? barrier_generation(p.ws.bar) : 0u;
 
   // phase 1: sums of g and g*xhat per item, g = dy under the ReLU mask; g is also what the residual branch gets
@@ -441,7 +442,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
       const int64_t r_begin = (int64_t)s * m.R;
       const int64_t r_end = r_begin + m.R < rows ? r_begin + m.R : rows;
       for (int64_t r0 = r_begin + rl; r0 < r_end; r0 += (int64_t)RPT_B * m.RL) {
-        Vec16<T> a[RPT_B], b[RPT_B];
+        Vec16<T> a[RPT_B], b[RPT_B], yv[RPT_B];  // the stored output travels with the other two loads
 #pragma unroll
         for (int i = 0; i < RPT_B; ++i) {
           const int64_t r = r0 + (int64_t)i * m.RL;
@@ -449,6 +450,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
             const int64_t o = r * C + (int64_t)cv * V;
             a[i].load(dy + o);
             b[i].load(z + o);
+            if (MASK == 1) yv[i].load(yk + o);
           }
         }
 #pragma unroll
@@ -459,7 +461,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
           float g[V], x[V];
           a[i].unpack(g);
           b[i].unpack(x);
-          if (p.relu) mask_gradient<T, V>(g, x, yk ? yk + o : nullptr, sc, sf);
+          if (MASK != 0) mask_gradient<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, sc, sf);
           if (dres) {
             Vec16<T> w;
             w.pack(g);
@@ -500,7 +502,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
   // phase 2: dz over the same items; the masked gradient comes back from dres where phase 1 stored it
   T* dz = (T*)p.dz;
   const T* gsrc = dres ? (const T*)dres : dy;
-  const bool mask_again = p.relu && !dres;
+  const bool mask_again = MASK != 0 && !dres;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int s = item / m.GY, gy = item % m.GY;
     const int cv = gy * m.TC + tc;
@@ -510,7 +512,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
     load_vec_f32<V>(kb, p.ws.coef + C + cv * V);
     load_vec_f32<V>(kd, p.ws.coef + 2 * C + cv * V);
     load_vec_f32<V>(mu, p.mean + cv * V);
-    if (mask_again && !yk) {
+    if (MASK == 2 && mask_again) {
       load_vec_f32<V>(sc, p.scale + cv * V);
       load_vec_f32<V>(sf, p.shift + cv * V);
     } else {
@@ -520,7 +522,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
     const int64_t r_begin = (int64_t)s * m.R;
     const int64_t r_end = r_begin + m.R < rows ? r_begin + m.R : rows;
     for (int64_t r0 = r_begin + rl; r0 < r_end; r0 += (int64_t)UNR * m.RL) {
-      Vec16<T> a[UNR], b[UNR];
+      Vec16<T> a[UNR], b[UNR], yv[UNR];
 #pragma unroll
       for (int i = 0; i < UNR; ++i) {
         const int64_t r = r0 + (int64_t)i * m.RL;
@@ -528,6 +530,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
           const int64_t o = r * C + (int64_t)cv * V;
           a[i].load(gsrc + o);
           b[i].load(z + o);
+          if (MASK == 1 && mask_again) yv[i].load(yk + o);
         }
       }
 #pragma unroll
@@ -538,7 +541,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
         float g[V], x[V];
         a[i].unpack(g);
         b[i].unpack(x);
-        if (mask_again) mask_gradient<T, V>(g, x, yk ? yk + o : nullptr, sc, sf);
+        if (mask_again) mask_gradient<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, sc, sf);
         float out[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) out[v] = fmaf(ka[v], g[v], fmaf(kb[v], x[v] - mu[v], kd[v]));
@@ -653,8 +656,11 @@ int bn_backward_fused(int dtype, const void* dy, const void* y, const void* z, i
   a.status = tc_status_device_ptr();
   if (int rc = workspace_for(st, &a.ws)) return rc;
   const int blocks = grid_blocks(a.m);
-  if (dtype == SRT_F32) return launch_grid(bn_bwd_grid<float>, blocks, st, a);
-  return launch_grid(bn_bwd_grid<__nv_bfloat16>, blocks, st, a);
+  const int mask = !relu ? 0 : (y ? 1 : 2);
+  if (dtype == SRT_F32)
+    return launch_grid(mask == 0 ? bn_bwd_grid<float, 0> : mask == 1 ? bn_bwd_grid<float, 1> : bn_bwd_grid<float, 2>, blocks, st, a);
+  return launch_grid(mask == 0 ? bn_bwd_grid<__nv_bfloat16, 0> : mask == 1 ? bn_bwd_grid<__nv_bfloat16, 1>
+                                                                            : bn_bwd_grid<__nv_bfloat16, 2>, blocks, st, a);
 }
 
 }  // namespace srt

@@ -18,7 +18,8 @@ constexpr int ROWS_PER_THREAD = 8;   // rows per thread and batch
 constexpr int BWD_ROWS = 4;          // rows in flight per thread in the backward sums (two or three tensors per row)
 constexpr int FIN_CH = 8;            // channels per finalize block (8 x 16 B = one 128-byte line)
 constexpr int FIN_LANES = 32;        // slab lanes per channel in the finalize kernels
-constexpr int TARGET_BLOCKS = 4 * 148;  // blocks a streaming pass wants in flight (4 per SM)
+constexpr int RESIDENT_BLOCKS = 3 * 148;  // blocks of the partial-sum kernels the device holds at once (80 registers)
+constexpr int MAX_ITERS = 16;
 
 // How a partial-sum kernel covers the rows x C matrix. A block owns `slab` consecutive rows of one
 // chunk of TC channel vectors and writes one partial per channel, so the partial-sum traffic is
@@ -47,23 +48,24 @@ inline RowMap row_map_for(int64_t rows, int CV, int TC, int iters) {
   return m;
 }
 
-// Tallest slab that still gives TARGET_BLOCKS blocks; when no shape reaches that many, the shape
-// with the most blocks. Ties go to the wider channel chunk (longer contiguous runs per row).
+// One wave of long-lived blocks: the shape with the most blocks among those the device holds at once (a block
+// that loops over several batches of rows keeps loads in flight while earlier ones are summed, and no second,
+// partly filled wave follows); a tensor too large for that gets the fewest blocks possible. Ties go to the
+// taller slab (fewer partial sums).
 inline RowMap make_row_map(int64_t rows, int C, int V) {
   const int CV = C / V;
   const int widest = CV < NT ? CV : NT;
-  RowMap best = row_map_for(rows, CV, widest, 1);
   constexpr int min_tc = 8;  // one 128-byte line per row and block
+  RowMap best = row_map_for(rows, CV, widest, 1);
   auto blocks = [](const RowMap& m) { return (int64_t)m.S * m.GY; };
   auto better = [&](const RowMap& a, const RowMap& b) {  // is a better than b
-    const bool fa = blocks(a) >= TARGET_BLOCKS, fb = blocks(b) >= TARGET_BLOCKS;
+    const bool fa = blocks(a) <= RESIDENT_BLOCKS, fb = blocks(b) <= RESIDENT_BLOCKS;
     if (fa != fb) return fa;
-    if (fa) return a.slab != b.slab ? a.slab > b.slab : a.TC > b.TC;
-    if (blocks(a) != blocks(b)) return blocks(a) > blocks(b);
+    if (blocks(a) != blocks(b)) return fa ? blocks(a) > blocks(b) : blocks(a) < blocks(b);
     return a.slab != b.slab ? a.slab > b.slab : a.TC > b.TC;
   };
   for (int tc = widest; tc >= 1; tc = (tc > min_tc ? (tc % 2 == 0 ? tc / 2 : min_tc) : 0)) {
-    for (int iters = 1; iters <= 4; iters *= 2) {
+    for (int iters = 1; iters <= MAX_ITERS; iters *= 2) {
       const RowMap m = row_map_for(rows, CV, tc, iters);
       if (better(m, best)) best = m;
     }
@@ -166,7 +168,9 @@ bn_stats_partial(const T* __restrict__ z, int64_t rows, int C, RowMap m, double*
   for (int v = 0; v < V; ++v) { s[v] = 0.f; q[v] = 0.f; }
   if (rl < m.RL && cv < m.CV) {
     for (int it = 0; it < m.iters; ++it) {
-      const int64_t r0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * ROWS_PER_THREAD * m.RL + rl;
+      const int64_t batch0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * ROWS_PER_THREAD * m.RL;
+      if (batch0 >= rows) break;  // the last slab may be short
+      const int64_t r0 = batch0 + rl;
       Vec16<T> x[ROWS_PER_THREAD];
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) {
@@ -309,7 +313,9 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
 #pragma unroll
     for (int v = 0; v < V; ++v) { mu[v] = mean[cv * V + v]; is[v] = invstd[cv * V + v]; }
     for (int it = 0; it < m.iters * (ROWS_PER_THREAD / BWD_ROWS); ++it) {
-      const int64_t r0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * BWD_ROWS * m.RL + rl;
+      const int64_t batch0 = (int64_t)blockIdx.x * m.slab + (int64_t)it * BWD_ROWS * m.RL;
+      if (batch0 >= rows) break;  // the last slab may be short
+      const int64_t r0 = batch0 + rl;
       Vec16<T> a[BWD_ROWS], b[BWD_ROWS], yv[BWD_ROWS];  // the stored output travels with the other two loads
 #pragma unroll
       for (int i = 0; i < BWD_ROWS; ++i) {

@@ -465,15 +465,16 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
 
 // ------------------------------------------------------------------------------------------
 // Persistent fprop/dgrad kernel: one CTA per SM walks the output tiles t = blockIdx.x, +gridDim.x,
-// ... (t = m_tile * n_tiles + n_tile). 320 threads:
-//   warp 0      TMA producer: B tile every stage, A tile too when it is a plain matrix block
-//   warp 1      tensor-memory allocation, tcgen05.mma issue (lane 0)
-//   warps 2-5   epilogue: TMEM -> registers -> (+bias, +addend) -> bf16 -> swizzled smem -> TMA store
-//   warps 6-9   A gather producers (cp.async), idle when A comes by TMA
+// ... (t = m_tile * n_tiles + n_tile). 448 threads:
+//   warp 0        TMA producer: B tile every stage, A tile too when it is a plain matrix block
+//   warp 1        tensor-memory allocation, tcgen05.mma issue (lane 0)
+//   warps 2-5     epilogue group 0: TMEM -> registers -> (+bias, +addend) -> bf16 -> swizzled smem -> TMA store
+//   warps 6-9     A gather producers (cp.async), idle when A comes by TMA
+//   warps 10-13   epilogue group 1 (takes every other 64-column slab of a tile)
 // The shared-memory stage ring runs across tile boundaries, and the accumulator is double-buffered
 // in tensor memory (2 x BN columns), so the loads of tile i+1 and the MMAs of tile i+1 overlap the
 // epilogue of tile i.
-constexpr int P_THREADS = 320;
+constexpr int P_THREADS = 448;
 constexpr int OUT_SLAB_BYTES = BM * 128;  // 128 rows x 64 bf16
 
 struct PersistParams {
@@ -503,6 +504,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
   pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int PLAG = NS - 2;  // cp.async groups in flight per gather thread
+  constexpr int EPI_GROUPS = BN >= 128 ? 2 : 1;  // epilogue warp groups at work (see the epilogue branch)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = base;
@@ -527,7 +529,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tmem_full[b]), 1);
-      mbar_init(smem_u32(&tmem_empty[b]), NPROD);
+      mbar_init(smem_u32(&tmem_empty[b]), (uint32_t)(NPROD * EPI_GROUPS));
     }
     mbar_fence_init();
   }
@@ -558,7 +560,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           const uint32_t ph = (uint32_t)(it / NS) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) { ok = false; break; }
           const uint32_t bar = smem_u32(&full[s]);
-          if (p.no_load) { mbar_arrive(bar); continue; }
+          if (p.no_load & 1) { mbar_arrive(bar); continue; }
           mbar_arrive_expect_tx(bar, bytes);
           tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
           if (p.a_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
@@ -595,82 +597,90 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
         umma_commit(smem_u32(&tmem_full[b]));
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 6 || warp >= 10) {
     // ---------------- epilogue ----------------
-    const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const int row = q * 32 + lane;          // row of the tile held by this thread
-    const int et = tid - 64;                // 0..127
-    const bool issuer = et == 0;
-    const uint32_t swz_row = (uint32_t)row * 128u;
-    int tc = 0, slab_count = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tc) {
-      const int m0 = (t / p.n_tiles) * BM, n0 = (t % p.n_tiles) * BN;
-      const int b = tc & 1;
-      if (ok) ok = mbar_wait(smem_u32(&tmem_full[b]), (uint32_t)(tc >> 1) & 1u, p.status, W_EPI_TMEM);
-      tc_fence_after_sync();
-      const int m = m0 + row;
-      constexpr int NSLAB = BN / 64;
+    // Two groups of four warps (warps 2-5 and 10-13; the four warps of a group cover the four TMEM lane
+    // quarters). The 64-column slabs of a tile are dealt to the groups in turn, each group has its own staging
+    // slab, named barrier and store issuer, so the two halves of a tile's epilogue run side by side: a single warp
+    // per scheduler issues the conversion code at a fraction of the issue rate, and that code, not the memory
+    // system, bounds the epilogue. A 64-column tile has one slab and uses one group.
+    constexpr int NSLAB = BN / 64;
+    const int grp = warp >= 10 ? 1 : 0;
+    if (grp < EPI_GROUPS) {
+      const int q = warp & 3;                 // TMEM lane quarter this warp may read
+      const int row = q * 32 + lane;          // row of the tile held by this thread
+      const int et = (warp - (grp ? 10 : 2)) * 32 + lane;  // 0..127 within the group
+      const bool issuer = et == 0;
+      const uint32_t swz_row = (uint32_t)row * 128u;
+      uint8_t* stage = sOut + grp * OUT_SLAB_BYTES;
+      const uint32_t bar_id = 1u + (uint32_t)grp;
+      constexpr int LAST_SLAB_BASE = NSLAB - EPI_GROUPS;  // this group's last slab is LAST_SLAB_BASE + grp
+      int tc = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tc) {
+        const int m0 = (t / p.n_tiles) * BM, n0 = (t % p.n_tiles) * BN;
+        const int b = tc & 1;
+        if (ok) ok = mbar_wait(smem_u32(&tmem_full[b]), (uint32_t)(tc >> 1) & 1u, p.status, W_EPI_TMEM);
+        tc_fence_after_sync();
+        const int m = m0 + row;
 #pragma unroll 1
-      for (int c = 0; c < NSLAB; ++c) {
-        const int col0 = n0 + c * 64;
-        const bool live = col0 < g.Nout;  // uniform across the epilogue threads
-        const int buf = slab_count & 1;
-        uint8_t* stage = sOut + buf * OUT_SLAB_BYTES;
-        if (live) {
-          // the store that read this staging buffer two slabs ago must be done with it
-          if (issuer) bulk_wait_group_read<1>();
-          named_bar_sync(1, NPROD);
-        }
+        for (int c = grp; c < NSLAB; c += EPI_GROUPS) {
+          const int col0 = n0 + c * 64;
+          const bool live = col0 < g.Nout;  // uniform across the epilogue threads
+          uint4 packed[8];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t acc[32];
-          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c * 64 + h * 32), acc);
-          tmem_ld_wait();
-          if (c == NSLAB - 1 && h == 1) {
-            // last read of this accumulator: hand it back to the MMA warp
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&tmem_empty[b]));
-          }
-          if (!live) continue;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = col0 + h * 32 + v * 8;
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
-            if (col < g.Nout) {
-              if (p.bias) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
-              }
-              if (p.addend && m < g.M) {
-                Vec16<bf16> av;
-                av.load(p.addend + (size_t)m * g.Nout + col);
-                float af[8];
-                av.unpack(af);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] += af[e];
-              }
+          for (int h = 0; h < 2; ++h) {
+            uint32_t acc[32];
+            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c * 64 + h * 32), acc);
+            tmem_ld_wait();
+            if (c == LAST_SLAB_BASE + grp && h == 1) {
+              // this group's last read of the accumulator: hand it back to the MMA warp
+              tc_fence_before_sync();
+              mbar_arrive(smem_u32(&tmem_empty[b]));
             }
-            Vec16<bf16> ov;
-            ov.pack(f);
-            const int chunk = h * 4 + v;
-            *reinterpret_cast<uint4*>(stage + swz_row + (uint32_t)((chunk ^ (row & 7)) << 4)) = ov.raw;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = col0 + h * 32 + v * 8;
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
+              if (live && col < g.Nout) {
+                if (p.bias) {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
+                }
+                if (p.addend && m < g.M) {
+                  Vec16<bf16> av;
+                  av.load(p.addend + (size_t)m * g.Nout + col);
+                  float af[8];
+                  av.unpack(af);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) f[e] += af[e];
+                }
+              }
+              Vec16<bf16> ov;
+              ov.pack(f);
+              packed[h * 4 + v] = ov.raw;
+            }
           }
-        }
-        if (live) {
-          fence_proxy_async_smem();
-          named_bar_sync(1, NPROD);
-          if (issuer) {
-            tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
-            bulk_commit_group();
+          if (live) {
+            // the store that read this group's staging slab last must be done with it
+            if (issuer) bulk_wait_group_read<0>();
+            named_bar_sync(bar_id, NPROD);
+#pragma unroll
+            for (int chunk = 0; chunk < 8; ++chunk)
+              *reinterpret_cast<uint4*>(stage + swz_row + (uint32_t)((chunk ^ (row & 7)) << 4)) = packed[chunk];
+            fence_proxy_async_smem();
+            named_bar_sync(bar_id, NPROD);
+            if (issuer) {
+              tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
+              bulk_commit_group();
+            }
           }
-          ++slab_count;
         }
       }
+      if (issuer) bulk_wait_group<0>();
     }
-    if (issuer) bulk_wait_group<0>();
   } else {
     // ---------------- A gather producers ----------------
     if (!p.a_tma) {
@@ -726,7 +736,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
             }
             v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
             const bf16* ptr = v ? p.src + ((size_t)(pixb[i] + ih * g.src_w + iw) * g.src_c + c) : p.src;
-            if (!p.no_load) cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
+            if (!(p.no_load & 1)) cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
           }
           cp_async_commit();
           if (it >= PLAG) {
@@ -1117,7 +1127,7 @@ int tc_status_fetch(int* out) {
 void tc_set_force_gather(int v) { g_force_gather = v; }
 static int g_fwd_variant = 0;   // 0: persistent kernel, 1: one tile per CTA (kept for comparison)
 static int g_force_bn = 0;      // 0: heuristic, else 64/128/256
-static int g_no_load = 0;       // timing experiment, see PersistParams::no_load
+static int g_no_load = getenv("SIRIUS_B200_DEBUG_NO_LOAD") ? atoi(getenv("SIRIUS_B200_DEBUG_NO_LOAD")) : 0;  // timing experiments, see PersistParams::no_load
 void tc_set_no_load(int v) { g_no_load = v; }
 void tc_set_fwd_variant(int variant, int bn) { g_fwd_variant = variant; g_force_bn = bn; }
 

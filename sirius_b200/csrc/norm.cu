@@ -57,6 +57,9 @@ inline RowMap make_row_map(int64_t rows, int C, int V) {
   const int widest = CV < NT ? CV : NT;
   constexpr int min_tc = 8;  // one 128-byte line per row and block
   RowMap best = row_map_for(rows, CV, widest, 1);
+  // fp32 is the parity mode: whole rows per block and eight rows per thread keep the fp32 part of every sum short
+  // (three SGD steps at lr 0.1 amplify rounding differences of the statistics into percent of the loss)
+  if (V == 4) return best;
   auto blocks = [](const RowMap& m) { return (int64_t)m.S * m.GY; };
   auto better = [&](const RowMap& a, const RowMap& b) {  // is a better than b
     const bool fa = blocks(a) <= RESIDENT_BLOCKS, fb = blocks(b) <= RESIDENT_BLOCKS;

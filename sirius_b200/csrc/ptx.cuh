@@ -41,10 +41,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Every wait in the kernels is bounded: after kWaitLimitCycles the waiter records `code` in the
 // status word and gives up, so a protocol bug surfaces as an error status instead of a hang.
 constexpr long long kWaitLimitCycles = 2000000000ll;  // about one second at B200 clocks
+#ifndef SRT_POLL_SLEEP_NS
+#define SRT_POLL_SLEEP_NS 40
+#endif
+constexpr unsigned kPollSleepNs = SRT_POLL_SLEEP_NS;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  // A waiting role (one lane of the producer or MMA warp) shares its scheduler and the shared-memory pipe with an
+  // epilogue warp: polling back to back slows that warp several times over, so the poll sleeps between tries.
   while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(kPollSleepNs);
     if (clock64() - t0 > kWaitLimitCycles) {
       atomicCAS(status, 0, code);
       return false;

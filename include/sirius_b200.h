@@ -96,6 +96,21 @@ int srt_bn_stats_static(int dtype, const void* z, int64_t rows, int C, const flo
                         const float* beta, float eps, float momentum, float* running_mean,
                         float* running_var, float* mean, float* invstd, float* scale, float* shift,
                         void* stream);
+/* Convolution followed by BatchNorm without the statistics pass over y (every conv + bn pair of
+ * torchvision's Bottleneck, train/resnet152.py:86): the bf16 tensor-core fprop writes, besides
+ * y, the sum and the sum of squares of the stored y values per 128-row tile and output channel
+ * (`partial`, double2 [*slabs][K], srt_conv_fprop_bn_stats_bytes(d) bytes, 16-byte aligned), and
+ * srt_bn_finalize turns partial sums of that layout into what srt_bn_stats returns. Only the
+ * bf16 tensor-core path has this epilogue: srt_conv_fprop_bn_stats_supported says whether a
+ * (dtype, impl) pair may use it; otherwise call srt_conv_fprop and srt_bn_stats. */
+int srt_conv_fprop_bn_stats(const srt_conv_desc* d, int dtype, int impl, const void* x, const void* w,
+                            void* y, const srt_conv_epilogue* ep, void* partial, size_t partial_bytes,
+                            int* slabs, void* stream);
+size_t srt_conv_fprop_bn_stats_bytes(const srt_conv_desc* d);
+int srt_conv_fprop_bn_stats_supported(const srt_conv_desc* d, int dtype, int impl);
+int srt_bn_finalize(const void* partial, int slabs, int C, int64_t rows, const float* gamma, const float* beta,
+                    float eps, float momentum, float* running_mean, float* running_var, float* mean,
+                    float* invstd, float* scale, float* shift, void* stream);
 /* y = act(z*scale + shift (+ residual)); relu != 0 applies max(.,0). */
 int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
                  const float* scale, const float* shift, int relu, void* stream);

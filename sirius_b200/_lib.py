@@ -41,6 +41,10 @@ _SIGNATURES = {
     "srt_last_error": (C.c_char_p, []),
     "srt_version": (C.c_char_p, []),
     "srt_conv_fprop": (None, [_PD, _i, _i, _vp, _vp, _vp, _PE, _vp]),
+    "srt_conv_fprop_bn_stats": (None, [_PD, _i, _i, _vp, _vp, _vp, _PE, _vp, _sz, C.POINTER(C.c_int), _vp]),
+    "srt_conv_fprop_bn_stats_bytes": (_sz, [_PD]),
+    "srt_conv_fprop_bn_stats_supported": (_i, [_PD, _i, _i]),
+    "srt_bn_finalize": (None, [_vp, _i, _i, _i64, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "srt_conv_dgrad": (None, [_PD, _i, _i, _vp, _vp, _vp, _PE, _vp]),
     "srt_conv_wgrad": (None, [_PD, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "srt_conv_wgrad_scratch_bytes": (_sz, [_PD, _i, _i]),

@@ -92,6 +92,24 @@ int conv_fprop(const srt_conv_desc& d, int dtype, int impl, const void* x, const
   return conv_gather_gemm_simt(g, dtype, x, w, y, ep, st);
 }
 
+bool conv_fprop_stats_supported(const srt_conv_desc& d, int dtype, int impl) {
+  return use_tc(dtype, impl) && conv_col_stats_available() && d.C % 8 == 0 && d.K % 8 == 0;
+}
+
+size_t conv_fprop_stats_bytes(const srt_conv_desc& d) {
+  return conv_col_stats_bytes((int64_t)d.N * d.P * d.Q, d.K);
+}
+
+int conv_fprop_stats(const srt_conv_desc& d, int dtype, int impl, const void* x, const void* w, void* y,
+                     const srt_conv_epilogue* ep, void* partial, size_t partial_bytes, int* slabs, cudaStream_t st) {
+  int rc = check_desc(d);
+  if (rc) return rc;
+  SRT_REQUIRE(conv_fprop_stats_supported(d, dtype, impl),
+              "conv_fprop_bn_stats: only the bf16 tensor-core path computes the column sums");
+  GatherGeom g = make_fprop_geom(d);
+  return conv_gather_gemm_tc_stats(g, x, w, y, ep, (double*)partial, partial_bytes, slabs, st);
+}
+
 int conv_dgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* wt,
                void* dx, const srt_conv_epilogue* ep, cudaStream_t st) {
   int rc = check_desc(d);
@@ -135,6 +153,17 @@ int srt_conv_fprop(const srt_conv_desc* d, int dtype, int impl, const void* x, c
   CHECK_DTYPE(dtype);
   return conv_fprop(*d, dtype, impl, x, w, y, ep, ST(stream));
 }
+int srt_conv_fprop_bn_stats(const srt_conv_desc* d, int dtype, int impl, const void* x, const void* w,
+                            void* y, const srt_conv_epilogue* ep, void* partial, size_t partial_bytes,
+                            int* slabs, void* stream) {
+  SRT_REQUIRE(d && x && w && y && partial && slabs, "conv_fprop_bn_stats: null argument");
+  CHECK_DTYPE(dtype);
+  return conv_fprop_stats(*d, dtype, impl, x, w, y, ep, partial, partial_bytes, slabs, ST(stream));
+}
+size_t srt_conv_fprop_bn_stats_bytes(const srt_conv_desc* d) { return d ? conv_fprop_stats_bytes(*d) : 0; }
+int srt_conv_fprop_bn_stats_supported(const srt_conv_desc* d, int dtype, int impl) {
+  return d && conv_fprop_stats_supported(*d, dtype, impl) ? 1 : 0;
+}
 int srt_conv_dgrad(const srt_conv_desc* d, int dtype, int impl, const void* dy, const void* wt,
                    void* dx, const srt_conv_epilogue* ep, void* stream) {
   SRT_REQUIRE(d && dy && wt && dx, "conv_dgrad: null argument");
@@ -168,6 +197,13 @@ int srt_bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gam
                   invstd, scale, shift, scratch, scratch_bytes, ST(stream));
 }
 size_t srt_bn_scratch_bytes(int64_t rows, int C) { return bn_scratch_bytes(rows, C); }
+int srt_bn_finalize(const void* partial, int slabs, int C, int64_t rows, const float* gamma, const float* beta,
+                    float eps, float momentum, float* running_mean, float* running_var, float* mean,
+                    float* invstd, float* scale, float* shift, void* stream) {
+  SRT_REQUIRE(partial && mean && invstd && scale && shift, "bn_finalize: null argument");
+  return bn_finalize(partial, slabs, C, rows, gamma, beta, eps, momentum, running_mean, running_var, mean, invstd,
+                     scale, shift, ST(stream));
+}
 int srt_bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
                         const float* beta, float eps, float momentum, float* running_mean,
                         float* running_var, float* mean, float* invstd, float* scale, float* shift,

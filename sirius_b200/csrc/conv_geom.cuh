@@ -86,6 +86,12 @@ int launch_split_reduce(const float* partial, float* out, long long n, int split
 
 int conv_gather_gemm_tc(const GatherGeom& g, const void* src, const void* Bm, void* D,
                         const srt_conv_epilogue* ep, cudaStream_t st);
+// The same kernel, whose epilogue also writes per 128-row tile and output column the sum and the sum of squares
+// of the stored values (double2 [slabs][Nout]) for the BatchNorm that follows.
+bool conv_col_stats_available();
+size_t conv_col_stats_bytes(int64_t M, int Nout);
+int conv_gather_gemm_tc_stats(const GatherGeom& g, const void* src, const void* Bm, void* D, const srt_conv_epilogue* ep,
+                              double* col_partial, size_t col_partial_bytes, int* slabs, cudaStream_t st);
 int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw, void* scratch,
                   size_t scratch_bytes, cudaStream_t st);
 size_t conv_wgrad_tc_scratch_bytes(const GatherGeom& g);

@@ -487,6 +487,10 @@ struct PersistParams {
   int m_tiles, n_tiles;
   int no_load;  // timing experiment: hand stages over without loading them (results are garbage)
   int* status;
+  // Optional: per 128-row tile and output column, the sum and the sum of squares of the stored (rounded) values,
+  // as double2 [m_tiles][Nout]. The BatchNorm that follows a convolution finalizes its statistics from these and
+  // never reads the tensor for them.
+  double* col_partial;
 };
 
 enum WaitCode2 { W_MMA_TMEM_EMPTY = 5 };
@@ -675,6 +679,51 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
             if (issuer) {
               tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
               bulk_commit_group();
+            }
+            if (p.col_partial != nullptr) {
+              // Column sums of the slab as it sits in the staging buffer. Warp w of the group takes columns
+              // 16w..16w+15; a lane owns one column pair and a quarter of the rows, picked so that the 32 words
+              // a warp reads at once fall into 32 different banks of the swizzled slab (the four row classes
+              // differ in bits 1-2 of the row, which the swizzle turns into different 16-byte chunks).
+              const int wg = et >> 5, cpl = lane & 7, rgl = lane >> 3;
+              const int cp = wg * 8 + cpl;
+              const uint32_t chunk = (uint32_t)(cp >> 2), within = (uint32_t)(cp & 3) * 4u;
+              const int nvalid = g.M - m0;  // rows of this tile that exist
+              // both columns of the pair ride in one packed fp32x2 add and one packed fma per row
+              uint64_t s01 = 0ull, q01 = 0ull;
+              const uint8_t* rp0 = stage + (uint32_t)(rgl * 2) * 128u + ((chunk ^ (uint32_t)(rgl * 2)) << 4) + within;
+              const uint8_t* rp1 = stage + (uint32_t)(rgl * 2 + 1) * 128u + ((chunk ^ (uint32_t)(rgl * 2 + 1)) << 4) + within;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int r = (i >> 1) * 8 + rgl * 2 + (i & 1);
+                uint32_t wv = *reinterpret_cast<const uint32_t*>(((i & 1) ? rp1 : rp0) + (i >> 1) * 1024);
+                if (r >= nvalid) wv = 0u;
+                uint64_t x01;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(x01) : "r"(wv << 16), "r"(wv & 0xffff0000u));
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(s01) : "l"(x01));
+                asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(q01) : "l"(x01));
+              }
+              float s0, s1, q0, q1;
+              {
+                uint32_t a, b, c, d;
+                asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(s01));
+                asm("mov.b64 {%0, %1}, %2;" : "=r"(c), "=r"(d) : "l"(q01));
+                s0 = __uint_as_float(a); s1 = __uint_as_float(b);
+                q0 = __uint_as_float(c); q1 = __uint_as_float(d);
+              }
+#pragma unroll
+              for (int o = 8; o <= 16; o <<= 1) {
+                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                q0 += __shfl_xor_sync(0xffffffffu, q0, o);
+                q1 += __shfl_xor_sync(0xffffffffu, q1, o);
+              }
+              const int col = col0 + 2 * cp;
+              if (rgl == 0 && col < g.Nout) {
+                double2* out = reinterpret_cast<double2*>(p.col_partial) + (size_t)(t / p.n_tiles) * g.Nout + col;
+                out[0] = make_double2((double)s0, (double)q0);
+                out[1] = make_double2((double)s1, (double)q1);
+              }
             }
           }
         }
@@ -1132,9 +1181,10 @@ void tc_set_no_load(int v) { g_no_load = v; }
 void tc_set_fwd_variant(int variant, int bn) { g_fwd_variant = variant; g_force_bn = bn; }
 
 static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, const void* Bm, void* D,
-                                          const srt_conv_epilogue* ep, cudaStream_t st) {
+                                          const srt_conv_epilogue* ep, cudaStream_t st, double* col_partial = nullptr) {
   PersistParams p;
   p.g = g;
+  p.col_partial = col_partial;
   p.src = (const bf16*)src;
   p.bias = ep ? ep->bias : nullptr;
   p.addend = ep ? (const bf16*)ep->addend : nullptr;
@@ -1193,6 +1243,23 @@ int conv_gather_gemm_tc(const GatherGeom& g, const void* src, const void* Bm, vo
   }
   if (bn == 64) return launch_fwd<64, 4>(p, tb, ta, st);
   return launch_fwd<128, 3>(p, tb, ta, st);
+}
+
+// Convolution whose epilogue also leaves the per-tile column sums for the BatchNorm that follows
+// (double2 [ceil(M/128)][Nout]: sum, sum of squares). Only the persistent kernel has that epilogue.
+bool conv_col_stats_available() { return g_fwd_variant == 0; }
+size_t conv_col_stats_bytes(int64_t M, int Nout) { return (size_t)ceil_div_ll(M, BM) * Nout * 2 * sizeof(double); }
+int conv_gather_gemm_tc_stats(const GatherGeom& g, const void* src, const void* Bm, void* D, const srt_conv_epilogue* ep,
+                              double* col_partial, size_t col_partial_bytes, int* slabs, cudaStream_t st) {
+  SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
+              "tcgen05 conv: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
+  SRT_REQUIRE(((uintptr_t)src & 15) == 0 && ((uintptr_t)D & 15) == 0, "tcgen05 conv: unaligned tensor");
+  SRT_REQUIRE(conv_col_stats_available(), "tcgen05 conv: column sums need the persistent kernel");
+  SRT_REQUIRE(col_partial && ((uintptr_t)col_partial & 15) == 0 && col_partial_bytes >= conv_col_stats_bytes(g.M, g.Nout),
+              "tcgen05 conv: column-sum buffer missing, unaligned or too small (%zu < %zu)", col_partial_bytes,
+              conv_col_stats_bytes(g.M, g.Nout));
+  if (slabs) *slabs = ceil_div(g.M, BM);
+  return conv_gather_gemm_tc_persistent(g, src, Bm, D, ep, st, col_partial);
 }
 
 size_t conv_wgrad_tc_scratch_bytes(const GatherGeom& g) {

@@ -462,6 +462,17 @@ int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, 
                                    scale, shift, scratch, st);
 }
 
+int bn_finalize(const void* partial, int slabs, int C, int64_t rows, const float* gamma, const float* beta, float eps,
+                float momentum, float* rm, float* rv, float* mean, float* invstd, float* scale, float* shift,
+                cudaStream_t st) {
+  SRT_REQUIRE(partial && slabs > 0 && C > 0 && rows > 0, "bn_finalize: empty input");
+  SRT_REQUIRE(((uintptr_t)partial & 15) == 0, "bn_finalize: partial sums must be 16-byte aligned");
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st,
+      (const double*)partial, slabs, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
+  SRT_LAUNCH_CHECK();
+  return SRT_OK;
+}
+
 template <typename T>
 static void bn_apply_t(const void* z, const void* residual, void* y, int64_t rows, int C,
                        const float* scale, const float* shift, int relu, cudaStream_t st) {

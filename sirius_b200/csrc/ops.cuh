@@ -6,6 +6,10 @@
 namespace srt {
 
 size_t bn_scratch_bytes(int64_t rows, int C);
+// Second half of bn_stats for partial sums somebody else produced (double2 [slabs][C]: sum, sum of squares).
+int bn_finalize(const void* partial, int slabs, int C, int64_t rows, const float* gamma, const float* beta, float eps,
+                float momentum, float* rm, float* rv, float* mean, float* invstd, float* scale, float* shift,
+                cudaStream_t st);
 int bn_stats(int dtype, const void* z, int64_t rows, int C, const float* gamma, const float* beta,
              float eps, float momentum, float* rm, float* rv, float* mean, float* invstd,
              float* scale, float* shift, void* scratch, size_t scratch_bytes, cudaStream_t st);
@@ -62,6 +66,13 @@ int conv_fprop(const srt_conv_desc& d, int dtype, int impl, const void* x, const
                const srt_conv_epilogue* ep, cudaStream_t st);
 int conv_dgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* wt,
                void* dx, const srt_conv_epilogue* ep, cudaStream_t st);
+// fprop that also leaves the column sums of y for bn_finalize (bf16 tensor-core path only; ask
+// conv_fprop_stats_supported first). `partial` needs conv_fprop_stats_bytes(d) bytes; *slabs receives the number
+// of partial rows written.
+bool conv_fprop_stats_supported(const srt_conv_desc& d, int dtype, int impl);
+size_t conv_fprop_stats_bytes(const srt_conv_desc& d);
+int conv_fprop_stats(const srt_conv_desc& d, int dtype, int impl, const void* x, const void* w, void* y,
+                     const srt_conv_epilogue* ep, void* partial, size_t partial_bytes, int* slabs, cudaStream_t st);
 int conv_wgrad(const srt_conv_desc& d, int dtype, int impl, const void* dy, const void* x,
                float* dw, void* scratch, size_t scratch_bytes, cudaStream_t st);
 size_t conv_wgrad_scratch_bytes(const srt_conv_desc& d, int dtype, int impl);

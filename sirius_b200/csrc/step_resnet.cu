@@ -106,6 +106,7 @@ struct Step {
   bool wt_dirty = false;           // ... of which only filter transposes (the forward pass need not wait for those)
   bool overlap_wgrad = getenv("SIRIUS_B200_NO_OVERLAP") == nullptr;  // weight gradients on the second stream
   bool fused_bn = getenv("SIRIUS_B200_NO_FUSED_BN") == nullptr;  // one-launch BatchNorm for the tensors that sit in L2
+  bool conv_stats = getenv("SIRIUS_B200_NO_CONV_STATS") == nullptr;  // BatchNorm sums taken in the convolution's epilogue
   // Gradient buckets for the data-parallel all-reduce, in the order backward completes them (fc and the
   // last blocks first). A bucket's event fires when every gradient in its range is final.
   struct GradBucket { size_t off, count; int first_block; cudaEvent_t ev; };
@@ -563,6 +564,10 @@ int Step::alloc_activations(int B) {
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     const size_t ws = conv_wgrad_scratch_bytes(d, dtype, cfg.impl);
     if (ws > max_wg_scratch) max_wg_scratch = ws;
+    if (conv_stats && conv_fprop_stats_supported(d, dtype, cfg.impl)) {
+      const size_t cs = conv_fprop_stats_bytes(d);
+      if (cs > max_bn_scratch) max_bn_scratch = cs;
+    }
     return SRT_OK;
   };
   if ((rc = alloc_unit(stem))) return rc;
@@ -757,6 +762,19 @@ int Step::forward(int B) {
     const int64_t rows = (int64_t)B * u.P * u.Q;
     const double flops = 2.0 * rows * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
     const double abytes = (double)rows * u.bn.C * esz;
+    if (!eval_mode && conv_stats && conv_fprop_stats_supported(d, dt, impl)) {
+      // the convolution's epilogue leaves the column sums of z; BatchNorm finalizes them and goes straight to apply
+      int slabs = 0;
+      if ((r = timed(SRT_PROF_CONV, flops, [&] {
+            return conv_fprop_stats(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, scratch, scratch_bytes, &slabs, stream); })))
+        return r;
+      if ((r = timed(SRT_PROF_NORM, 0.0, [&] {
+            return bn_finalize(scratch, slabs, u.bn.C, rows, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
+                               bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift, stream); })))
+        return r;
+      return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2), [&] {
+        return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream); });
+    }
     if ((r = timed(SRT_PROF_CONV, flops, [&] { return conv_fprop(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, stream); })))
       return r;
     if (eval_mode) {

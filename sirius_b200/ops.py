@@ -44,6 +44,28 @@ def conv_fprop(x, w, stride, pad, bias=None, addend=None, impl=IMPL_AUTO, out=No
     return y
 
 
+def conv_fprop_bn_stats(x, w, stride, pad, gamma, beta, running_mean, running_var, eps=1e-5, momentum=0.1,
+                        bias=None, addend=None, impl=IMPL_AUTO):
+    """Convolution whose epilogue takes the BatchNorm sums of its output, then the finalize step:
+    returns (y, mean, invstd, scale, shift) like conv_fprop followed by bn_stats."""
+    N, H, W, Cin = x.shape
+    K, R, S, _ = w.shape
+    d = ConvDesc.make(N, H, W, Cin, K, R, S, stride, pad)
+    if not _lib.lib().srt_conv_fprop_bn_stats_supported(C.byref(d), _dt(x), impl):
+        raise RuntimeError("conv_fprop_bn_stats: this dtype/impl has no statistics epilogue")
+    y = torch.empty((N, d.P, d.Q, K), dtype=x.dtype, device=x.device)
+    nbytes = _lib.lib().srt_conv_fprop_bn_stats_bytes(C.byref(d))
+    partial = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    slabs = C.c_int(0)
+    call("srt_conv_fprop_bn_stats", C.byref(d), _dt(x), impl, _p(x), _p(w), _p(y), _ep(bias, addend), _p(partial),
+         nbytes, C.byref(slabs), _stream())
+    f = lambda: torch.empty(K, dtype=torch.float32, device=x.device)
+    mean, invstd, scale, shift = f(), f(), f(), f()
+    call("srt_bn_finalize", _p(partial), slabs.value, K, N * d.P * d.Q, _p(gamma), _p(beta), eps, momentum,
+         _p(running_mean), _p(running_var), _p(mean), _p(invstd), _p(scale), _p(shift), _stream())
+    return y, mean, invstd, scale, shift
+
+
 def filter_transpose(w):
     K, R, S, Cin = w.shape
     d = ConvDesc.make(1, R, S, Cin, K, R, S, 1, 0)

@@ -162,6 +162,52 @@ def test_conv_epilogue_bias_addend():
         assert _err(y, ref) < tol
 
 
+STATS_CASES = CONV_CASES + [
+    ("1x1_c64_k256_98tiles", 4, 56, 56, 64, 256, 1, 1, 1, 0),
+    ("3x3_c64_k64_multi_tile_per_cta", 6, 56, 56, 64, 64, 3, 3, 1, 1),
+    ("1x1_c128_k72_ragged_slab", 3, 10, 10, 128, 72, 1, 1, 1, 0),
+]
+
+
+@pytest.mark.parametrize("case", STATS_CASES, ids=[c[0] for c in STATS_CASES])
+@pytest.mark.parametrize("with_terms", [False, True], ids=["plain", "bias_addend"])
+def test_conv_fprop_bn_stats_matches_separate_passes(case, with_terms):
+    """The convolution that takes the BatchNorm sums in its epilogue: same y bit for bit as srt_conv_fprop, and the
+    finalized statistics equal those srt_bn_stats computes from that y (both sum the rounded bf16 values; only the
+    order of the fp32/fp64 additions differs)."""
+    _, N, H, W, Cc, K, R, S, stride, pad = case
+    x, w, dy = _mk(case, torch.bfloat16)
+    g = torch.Generator().manual_seed(11)
+    xd, wd = x.to(DEV, torch.bfloat16), w.to(DEV, torch.bfloat16)
+    bias = (torch.randn(K, generator=g) * 3).to(DEV) if with_terms else None
+    addend = torch.randn(dy.shape, generator=g).to(DEV, torch.bfloat16) if with_terms else None
+    gamma = (torch.rand(K, generator=g) + 0.5).to(DEV)
+    beta = torch.randn(K, generator=g).to(DEV)
+    rm1, rv1 = torch.zeros(K, device=DEV), torch.ones(K, device=DEV)
+    rm2, rv2 = torch.zeros(K, device=DEV), torch.ones(K, device=DEV)
+    y_ref = ops.conv_fprop(xd, wd, stride, pad, bias=bias, addend=addend, impl=IMPL_TCGEN05)
+    want = ops.bn_stats(y_ref, gamma, beta, rm1, rv1)
+    y, *got = ops.conv_fprop_bn_stats(xd, wd, stride, pad, gamma, beta, rm2, rv2, bias=bias, addend=addend,
+                                      impl=IMPL_TCGEN05)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_ref)
+    for name, a, b in zip(("mean", "invstd", "scale", "shift"), got, want):
+        assert torch.allclose(a, b, rtol=2e-5, atol=2e-6), (name, (a - b).abs().max().item())
+    assert torch.allclose(rm2, rm1, rtol=2e-5, atol=2e-6) and torch.allclose(rv2, rv1, rtol=2e-5, atol=2e-6)
+    # and against the definition, in fp64 on the host
+    yf = y.double().cpu().reshape(-1, K)
+    assert torch.allclose(got[0].cpu().double(), yf.mean(0), rtol=1e-4, atol=1e-5)
+    assert torch.allclose(got[1].cpu().double(), 1.0 / torch.sqrt(yf.var(0, unbiased=False) + 1e-5), rtol=1e-4)
+
+
+def test_conv_fprop_bn_stats_rejects_what_it_cannot_do():
+    x = torch.randn(1, 4, 4, 8, device=DEV)
+    w = torch.randn(8, 1, 1, 8, device=DEV)
+    one = torch.ones(8, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.conv_fprop_bn_stats(x, w, 1, 0, one, one, one.clone(), one.clone())  # fp32 has no statistics epilogue
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("shape", [(2, 14, 14, 64), (3, 7, 7, 2048), (2, 5, 5, 24)], ids=str)
 def test_batchnorm_fwd_bwd(dtype, shape):

@@ -1,7 +1,7 @@
 """Per-layer micro-benchmark of the convolution kernels on the ResNet-152 layer shapes.
 
 
-    python -m sirius_b200.bench_ops [--batch 64] [--case NAME] [--pass fprop|dgrad|wgrad|all|bn] [--iters 20]
+    python -m sirius_b200.bench_ops [--batch 64] [--case NAME] [--pass fprop|fprop_stats|dgrad|wgrad|all|bn] [--iters 20]
 
 Each case is timed with CUDA events on the launching stream after warm-up; between timed launches a
 buffer larger than L2 is rewritten so every launch starts cold. Prints one JSON line per case/pass.
@@ -10,12 +10,13 @@ Used for the per-shape roofline table and as the small, self-terminating command
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 
 import torch
 
-from . import ops
-from ._lib import IMPL_AUTO
+from . import _lib, ops
+from ._lib import IMPL_AUTO, SRT_BF16, ConvDesc
 
 # name: (H, W, C, K, R, stride, pad)  -- activations are batch x H x W x C
 CASES = {
@@ -51,13 +52,26 @@ def run_case(name, batch, which, iters, flush):
     dy = torch.randn(batch, P, P, K, device=dev, generator=g).to(torch.bfloat16)
     wt = ops.filter_transpose(w)
     flops = 2.0 * batch * P * P * K * R * R * C
+    # fprop whose epilogue also takes the BatchNorm column sums (the convolution launch alone, no finalize)
+    d = ConvDesc.make(batch, H, W, C, K, R, R, stride, pad)
+    y_st = torch.empty_like(dy)
+    nb = _lib.lib().srt_conv_fprop_bn_stats_bytes(ctypes.byref(d))
+    partial = torch.empty(nb, dtype=torch.uint8, device=dev)
+    slabs = ctypes.c_int(0)
+
+    def fprop_stats():
+        _lib.call("srt_conv_fprop_bn_stats", ctypes.byref(d), SRT_BF16, IMPL_AUTO, x.data_ptr(), w.data_ptr(), y_st.data_ptr(),
+                  None, partial.data_ptr(), nb, ctypes.byref(slabs), torch.cuda.current_stream().cuda_stream)
+
     fns = {
+        "fprop_stats": fprop_stats,
         "fprop": lambda: ops.conv_fprop(x, w, stride, pad, impl=IMPL_AUTO),
         "dgrad": lambda: ops.conv_dgrad(dy, wt, x.shape, stride, pad, impl=IMPL_AUTO),
         "wgrad": lambda: ops.conv_wgrad(dy, x, R, R, stride, pad, impl=IMPL_AUTO),
     }
     # bytes every launch must move at least once: both operands read, result written
     io = {
+        "fprop_stats": (x.numel() + w.numel() + dy.numel()) * 2 + nb,
         "fprop": (x.numel() + w.numel() + dy.numel()) * 2,
         "dgrad": (x.numel() + w.numel() + dy.numel()) * 2,
         "wgrad": (x.numel() + dy.numel()) * 2 + w.numel() * 4,
@@ -174,7 +188,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--case", default="all")
-    ap.add_argument("--pass", dest="which", default="all", choices=["fprop", "dgrad", "wgrad", "all", "bn"])
+    ap.add_argument("--pass", dest="which", default="all", choices=["fprop", "fprop_stats", "dgrad", "wgrad", "all", "bn"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--one-launch", action="store_true", help="BatchNorm cases: the one-launch kernels")

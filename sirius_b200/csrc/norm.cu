@@ -129,14 +129,18 @@ __device__ inline void block_reduce_store(const float (&a)[V], const float (&b)[
 }
 
 // Sum of the S slab partials of channel c: FIN_LANES lanes stride over the slabs, then a fixed-shape
-// tree through shared memory (deterministic). Call with blockDim = (FIN_CH channels, FIN_LANES).
+// tree through shared memory (deterministic). Call with blockDim = (FIN_CH channels, LANES). The partial sums a
+// convolution epilogue leaves come one row per 128-row tile (up to 1568 rows for the layer1 tensors): those get
+// FIN_LANES_TALL lanes, so that a lane still has only a dozen loads in a row.
+constexpr int FIN_LANES_TALL = 128;
+template <int LANES = FIN_LANES>
 __device__ inline double2 reduce_partials(const double* __restrict__ partial, int S, int C, int c) {
-  __shared__ double2 sh[FIN_LANES][FIN_CH];
+  __shared__ double2 sh[LANES][FIN_CH];
   double2 acc = make_double2(0.0, 0.0);
   if (c < C) {
     const double2* p = reinterpret_cast<const double2*>(partial);
 #pragma unroll 4
-    for (int i = threadIdx.y; i < S; i += FIN_LANES) {
+    for (int i = threadIdx.y; i < S; i += LANES) {
       const double2 v = p[(size_t)i * C + c];
       acc.x += v.x;
       acc.y += v.y;
@@ -145,7 +149,7 @@ __device__ inline double2 reduce_partials(const double* __restrict__ partial, in
   sh[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
 #pragma unroll
-  for (int o = FIN_LANES / 2; o > 0; o >>= 1) {
+  for (int o = LANES / 2; o > 0; o >>= 1) {
     if ((int)threadIdx.y < o) {
       double2 a = sh[threadIdx.y][threadIdx.x];
       const double2 b = sh[threadIdx.y + o][threadIdx.x];
@@ -195,14 +199,15 @@ bn_stats_partial(const T* __restrict__ z, int64_t rows, int C, RowMap m, double*
   block_reduce_store<V>(s, q, m, C, partial);
 }
 
-__global__ void __launch_bounds__(FIN_CH * FIN_LANES)
+template <int LANES>
+__global__ void __launch_bounds__(FIN_CH * LANES)
 bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
                   const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                   float momentum, float* running_mean, float* running_var, float* mean, float* invstd,
                   float* scale, float* shift) {
   pdl_enter();
   const int c = blockIdx.x * FIN_CH + threadIdx.x;
-  const double2 tot = reduce_partials(partial, S, C, c);
+  const double2 tot = reduce_partials<LANES>(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
   const double mu = tot.x / (double)rows;
   double var = tot.y / (double)rows - mu * mu;
@@ -444,7 +449,7 @@ static int bn_stats_t(const void* z, int64_t rows, int C, const float* gamma, co
   double* partial = (double*)scratch;
   launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_partial<T>, dim3(m.S, m.GY), dim3(NT), 0, st, (const T*)z, rows, C, m, partial);
   SRT_LAUNCH_CHECK();
-  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st,
+  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_finalize<FIN_LANES>, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st,
       partial, m.S, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
@@ -467,8 +472,13 @@ int bn_finalize(const void* partial, int slabs, int C, int64_t rows, const float
                 cudaStream_t st) {
   SRT_REQUIRE(partial && slabs > 0 && C > 0 && rows > 0, "bn_finalize: empty input");
   SRT_REQUIRE(((uintptr_t)partial & 15) == 0, "bn_finalize: partial sums must be 16-byte aligned");
-  launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_stats_finalize, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st,
-      (const double*)partial, slabs, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
+  const bool early = (pdl_classes() & PDL_NORM) != 0;
+  if (slabs > 8 * FIN_LANES)
+    launch_pdl_if(early, bn_stats_finalize<FIN_LANES_TALL>, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES_TALL), 0, st,
+        (const double*)partial, slabs, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
+  else
+    launch_pdl_if(early, bn_stats_finalize<FIN_LANES>, dim3(ceil_div(C, FIN_CH)), dim3(FIN_CH, FIN_LANES), 0, st,
+        (const double*)partial, slabs, C, rows, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

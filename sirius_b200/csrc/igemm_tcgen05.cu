@@ -500,6 +500,26 @@ constexpr size_t persist_smem_bytes() {
   return 1024 + (size_t)NS * (A_STAGE_BYTES + BN * BK * 2) + 2 * OUT_SLAB_BYTES + (2 * NS + 4) * 8 + 16;
 }
 
+// One lane's share of a staged 128 x 64 bf16 slab for the column sums: 32 rows (rp0/rp1 point at the lane's even
+// and odd row of the first group of eight, later groups lie 1024 bytes apart) of one column pair, summed and
+// square-summed as packed fp32 pairs. MASKED zeroes the rows at and beyond nvalid (the ragged last tile).
+template <bool MASKED>
+__device__ inline void slab_col_sums(const uint8_t* rp0, const uint8_t* rp1, int rgl, int nvalid, uint64_t& s01,
+                                     uint64_t& q01) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    uint32_t wv = *reinterpret_cast<const uint32_t*>(((i & 1) ? rp1 : rp0) + (i >> 1) * 1024);
+    if (MASKED) {
+      const int r = (i >> 1) * 8 + rgl * 2 + (i & 1);
+      if (r >= nvalid) wv = 0u;
+    }
+    uint64_t x01;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(x01) : "r"(wv << 16), "r"(wv & 0xffff0000u));
+    asm("add.rn.f32x2 %0, %0, %1;" : "+l"(s01) : "l"(x01));
+    asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(q01) : "l"(x01));
+  }
+}
+
 template <int BN, int NS>
 __global__ void __launch_bounds__(P_THREADS, 1)
 igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap tmap_b,
@@ -693,16 +713,8 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
               uint64_t s01 = 0ull, q01 = 0ull;
               const uint8_t* rp0 = stage + (uint32_t)(rgl * 2) * 128u + ((chunk ^ (uint32_t)(rgl * 2)) << 4) + within;
               const uint8_t* rp1 = stage + (uint32_t)(rgl * 2 + 1) * 128u + ((chunk ^ (uint32_t)(rgl * 2 + 1)) << 4) + within;
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int r = (i >> 1) * 8 + rgl * 2 + (i & 1);
-                uint32_t wv = *reinterpret_cast<const uint32_t*>(((i & 1) ? rp1 : rp0) + (i >> 1) * 1024);
-                if (r >= nvalid) wv = 0u;
-                uint64_t x01;
-                asm("mov.b64 %0, {%1, %2};" : "=l"(x01) : "r"(wv << 16), "r"(wv & 0xffff0000u));
-                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(s01) : "l"(x01));
-                asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(q01) : "l"(x01));
-              }
+              if (nvalid >= BM) slab_col_sums<false>(rp0, rp1, rgl, nvalid, s01, q01);  // every tile but the last
+              else slab_col_sums<true>(rp0, rp1, rgl, nvalid, s01, q01);
               float s0, s1, q0, q1;
               {
                 uint32_t a, b, c, d;

@@ -207,22 +207,29 @@ bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows
                   float* scale, float* shift) {
   pdl_enter();
   const int c = blockIdx.x * FIN_CH + threadIdx.x;
+  // the channel's parameters are fetched before the reduction, so their latency hides behind its loads
+  float g = 1.f, b = 0.f, rm0 = 0.f, rv0 = 0.f;
+  if (threadIdx.y == 0 && c < C) {
+    if (gamma) g = gamma[c];
+    if (beta) b = beta[c];
+    if (running_mean) rm0 = running_mean[c];
+    if (running_var) rv0 = running_var[c];
+  }
   const double2 tot = reduce_partials<LANES>(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
   const double mu = tot.x / (double)rows;
   double var = tot.y / (double)rows - mu * mu;
   if (var < 0.0) var = 0.0;
   const float is = (float)(1.0 / sqrt(var + (double)eps));
-  const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
   mean[c] = (float)mu;
   invstd[c] = is;
   const float sc = g * is;
   scale[c] = sc;
   shift[c] = b - (float)mu * sc;
-  if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * (float)mu;
+  if (running_mean) running_mean[c] = (1.f - momentum) * rm0 + momentum * (float)mu;
   if (running_var) {
     const double unbiased = rows > 1 ? var * (double)rows / (double)(rows - 1) : var;
-    running_var[c] = (1.f - momentum) * running_var[c] + momentum * (float)unbiased;
+    running_var[c] = (1.f - momentum) * rv0 + momentum * (float)unbiased;
   }
 }
 
@@ -360,17 +367,21 @@ bn_bwd_finalize(const double* __restrict__ partial, int S, int C, int64_t rows,
                 float* dbeta, float* coef) {
   pdl_enter();
   const int c = blockIdx.x * FIN_CH + threadIdx.x;
+  float g = 1.f, is = 0.f;  // fetched before the reduction, so their latency hides behind its loads
+  if (threadIdx.y == 0 && c < C) {
+    if (gamma) g = gamma[c];
+    is = invstd[c];
+  }
   const double2 tot = reduce_partials(partial, S, C, c);
   if (threadIdx.y != 0 || c >= C) return;
   if (dbeta) dbeta[c] = (float)tot.x;
   if (dgamma) dgamma[c] = (float)tot.y;
   // dz = k0*(g - mean_g - xhat*mean_gx), xhat = (x - mean)*invstd, stored as three per-channel
   // vectors so the elementwise pass reads them with 16-byte loads: dz = ka*g + kb*(x - mean) + kd
-  const float g = gamma ? gamma[c] : 1.f;
-  const float k0 = g * invstd[c];
+  const float k0 = g * is;
   const float mg = (float)(tot.x / (double)rows), mgx = (float)(tot.y / (double)rows);
   coef[c] = k0;
-  coef[C + c] = -k0 * mgx * invstd[c];
+  coef[C + c] = -k0 * mgx * is;
   coef[2 * C + c] = -k0 * mg;
 }
 

@@ -133,7 +133,6 @@ template <int BN, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 igemm_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a) {
-  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   extern __shared__ uint8_t smem_raw[];
   SmemLayout sm = carve_smem<NS, B_STAGE_BYTES>(smem_raw);
@@ -163,6 +162,9 @@ igemm_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tmap_b,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  // Everything above touches only shared memory, tensor memory and the kernel parameters, so under an early
+  // (programmatic dependent) launch it runs beside the predecessor's tail; global memory is first touched below.
+  pdl_enter();
 
   if (warp < 4) {
     // ---------------- gather producers ----------------
@@ -313,7 +315,6 @@ template <int BN, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap_dy,
                    const __grid_constant__ CUtensorMap tmap_x) {
-  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;  // BN/64 blocks of [64 pixels][128 bytes]
   constexpr int CPR = BN / 8;                 // 16-byte chunks per pixel row
   constexpr int RSTEP = NPROD / CPR;          // pixel rows covered per pass
@@ -349,6 +350,9 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  // Everything above touches only shared memory, tensor memory and the kernel parameters, so under an early
+  // (programmatic dependent) launch it runs beside the predecessor's tail; global memory is first touched below.
+  pdl_enter();
 
   if (warp < 4) {
     // ---------------- gather producers: x(pix, j) for 64 pixels x BN columns ----------------
@@ -525,7 +529,6 @@ __global__ void __launch_bounds__(P_THREADS, 1)
 igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_d) {
-  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int PLAG = NS - 2;  // cp.async groups in flight per gather thread
   constexpr int EPI_GROUPS = BN >= 128 ? 2 : 1;  // epilogue warp groups at work (see the epilogue branch)
@@ -570,6 +573,9 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  // Everything above touches only shared memory, tensor memory and the kernel parameters, so under an early
+  // (programmatic dependent) launch it runs beside the predecessor's tail; global memory is first touched below.
+  pdl_enter();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -844,7 +850,6 @@ template <int BN, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 bgemm_kernel(const BgemmParams p, const __grid_constant__ CUtensorMap tmap_a,
              const __grid_constant__ CUtensorMap tmap_b) {
-  pdl_enter();
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
   if (p.causal && n0 >= m0 + BM) return;  // wholly above the diagonal: never read by the consumer
@@ -877,6 +882,9 @@ bgemm_kernel(const BgemmParams p, const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  // Everything above touches only shared memory, tensor memory and the kernel parameters, so under an early
+  // (programmatic dependent) launch it runs beside the predecessor's tail; global memory is first touched below.
+  pdl_enter();
 
   if (warp < 4) {
     bool ready = true;

@@ -756,7 +756,59 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
       const uint32_t swz = (uint32_t)((j ^ (r0 & 7)) << 4);
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      // Channel counts that are multiples of BK (every 3x3 layer of the step) keep a k-block inside one filter tap, and
+      // without a dgrad stride the source pixel of a row is its tap-(0,0) pixel plus a per-k-block offset: one element
+      // offset per row and tile, one per k-block, an add, two unsigned bounds checks and a select per copy, no
+      // division in the loop. Everything else (stem: 8 channels; strided dgrad) takes the general loop below.
+      const bool fast = (g.src_c % BK) == 0 && (!g.dgrad || g.stride == 1);
+      if (fast) {
+        const int sgn = g.dgrad ? -1 : 1;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+          const int m0 = (t / p.n_tiles) * BM;
+          int rowoff[8], ih0[8], iw0[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = m0 + r0 + 16 * i;
+            if (m < g.M) {
+              RowCoord rc = decode_row(g, m);
+              ih0[i] = g.dgrad ? rc.oh + g.pad : rc.oh * g.stride - g.pad;
+              iw0[i] = g.dgrad ? rc.ow + g.pad : rc.ow * g.stride - g.pad;
+              rowoff[i] = ((rc.n * g.src_h + ih0[i]) * g.src_w + iw0[i]) * g.src_c;
+            } else {
+              ih0[i] = -(1 << 20);
+              iw0[i] = 0;
+              rowoff[i] = 0;
+            }
+          }
+          int r = 0, sf = 0, c0 = 0;  // filter tap and first channel of the k-block
+          for (int kb = 0; kb < nkb; ++kb, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) { ok = false; break; }
+            const int dr = sgn * r, ds = sgn * sf;
+            const int tapoff = (dr * g.src_w + ds) * g.src_c + c0 + j * 8;
+            const uint32_t dst0 = smem_u32(sA + s * A_STAGE_BYTES) + (uint32_t)r0 * 128u + swz;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const bool v = (unsigned)(ih0[i] + dr) < (unsigned)g.src_h && (unsigned)(iw0[i] + ds) < (unsigned)g.src_w;
+              const int off = v ? rowoff[i] + tapoff : 0;
+              if (!(p.no_load & 1)) cp_async_16(dst0 + (uint32_t)i * (16u * 128u), p.src + off, v ? 16u : 0u);
+            }
+            cp_async_commit();
+            if (it >= PLAG) {
+              cp_async_wait<PLAG>();
+              fence_proxy_async_smem();
+              mbar_arrive(smem_u32(&full[(it - PLAG) % NS]));
+            }
+            c0 += BK;
+            if (c0 == g.src_c) {
+              c0 = 0;
+              if (++sf == g.S) { sf = 0; ++r; }
+            }
+          }
+        }
+      }
+      for (int t = blockIdx.x; !fast && t < total_tiles && ok; t += gridDim.x) {
         const int m0 = (t / p.n_tiles) * BM;
         int pixb[8], ih0[8], iw0[8];
 #pragma unroll

@@ -49,3 +49,20 @@ def test_error_string_and_version_calls_need_no_gpu():
     lib = _lib.lib()
     lib.srt_last_error.restype = C.c_char_p
     assert isinstance(lib.srt_last_error(), bytes)
+
+
+def test_conv_bn_stats_sizing_and_support_are_host_side():
+    """srt_conv_fprop_bn_stats_bytes / _supported do no device work: one double2 per 128-row tile and output
+    channel, and only the bf16 tensor-core path has the statistics epilogue."""
+    from sirius_b200 import _lib
+    from sirius_b200._lib import IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05, SRT_BF16, SRT_F32, ConvDesc
+    lib = _lib.lib()
+    for (N, H, W, Cin, K, R, stride, pad) in ((64, 56, 56, 64, 256, 1, 1, 0), (3, 9, 11, 24, 40, 3, 1, 1), (2, 28, 28, 128, 128, 3, 2, 1)):
+        d = ConvDesc.make(N, H, W, Cin, K, R, R, stride, pad)
+        rows = N * d.P * d.Q
+        assert lib.srt_conv_fprop_bn_stats_bytes(C.byref(d)) == -(-rows // 128) * K * 16
+        assert lib.srt_conv_fprop_bn_stats_supported(C.byref(d), SRT_BF16, IMPL_AUTO) == 1
+        assert lib.srt_conv_fprop_bn_stats_supported(C.byref(d), SRT_BF16, IMPL_TCGEN05) == 1
+        assert lib.srt_conv_fprop_bn_stats_supported(C.byref(d), SRT_BF16, IMPL_SIMT) == 0
+        assert lib.srt_conv_fprop_bn_stats_supported(C.byref(d), SRT_F32, IMPL_AUTO) == 0
+    assert lib.srt_conv_fprop_bn_stats_bytes(None) == 0

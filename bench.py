@@ -144,31 +144,22 @@ def run_ours(args):
     torch.cuda.synchronize()
     global_bs = BATCH * world
 
-    grad_t = None
+    # Gradient exchange overlapped with backward, inside the library: forward_backward returns once everything is
+    # enqueued (the GPU is then still early in backward); begin() enqueues one NCCL all-reduce per gradient bucket
+    # on the library's communication stream, each behind the event the executor records when that bucket's
+    # gradients are final; wait() puts the optimizer behind the last one. bf16 on the wire (2 bytes per parameter).
+    exchange = None
     if world > 1:
-        ptr, n = step.grad_buffer()
-        grad_t = torch.as_tensor(_DevBuf(ptr, n), device=f"cuda:{local}")
-        with torch.cuda.stream(stream):
-            dist.all_reduce(grad_t)  # communicator warm-up (pytorch/torch_col/__init__.py:61-64)
-        grad_t.zero_()
-        torch.cuda.synchronize()
-
-    # Gradient exchange overlapped with backward: forward_backward returns once everything is enqueued
-    # (the GPU is then still early in backward), so the all-reduce of each bucket is enqueued right away on
-    # a communication stream that waits for that bucket's ready event; the optimizer waits for the last one.
-    comm_stream = torch.cuda.Stream() if world > 1 else None
-    buckets = step.grad_buckets() if world > 1 else []
-    done_ev = torch.cuda.Event() if world > 1 else None
+        from sirius_b200.ddp import GradExchange
+        exchange = GradExchange(rank, world, device=local, wire=args.wire, max_ctas=args.nccl_max_ctas)
+        step.forward_backward(BATCH, BATCH * world)   # communicator warm-up (pytorch/torch_col/__init__.py:61-64)
+        exchange.allreduce(step)
+        step.synchronize()
 
     def allreduce():
-        if grad_t is None:
-            return
-        for b, (off, cnt) in enumerate(buckets):
-            step.wait_grad_bucket(b, comm_stream.cuda_stream)
-            with torch.cuda.stream(comm_stream):
-                dist.all_reduce(grad_t[off:off + cnt])
-        done_ev.record(comm_stream)
-        step.wait_event(done_ev.cuda_event)
+        if exchange is not None:
+            exchange.begin(step)
+            exchange.wait(step)
 
     def step_resident(i):
         im, lb = dev[i % nbuf]
@@ -319,20 +310,16 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def make_overlapped_allreduce(step, grad_t, torch, dist):
-    """All-reduce of the flat gradient buffer bucket by bucket on a communication stream that waits for each bucket's
-    ready event (recorded by the executor during backward); the executor's stream waits for the last one."""
-    comm_stream = torch.cuda.Stream()
-    buckets = step.grad_buckets()
-    done_ev = torch.cuda.Event()
+def make_overlapped_allreduce(step, rank, world, local, args):
+    """Gradient exchange of a transformer step through the library's NCCL communicator: one all-reduce per gradient
+    bucket on the library's communication stream, each behind the bucket's ready event (recorded by the executor
+    during backward); the executor's stream waits for the last one."""
+    from sirius_b200.ddp import GradExchange
+    ex = GradExchange(rank, world, device=local, wire=args.wire, max_ctas=args.nccl_max_ctas)
 
     def allreduce():
-        for b, (off, cnt) in enumerate(buckets):
-            step.wait_grad_bucket(b, comm_stream.cuda_stream)
-            with torch.cuda.stream(comm_stream):
-                dist.all_reduce(grad_t[off:off + cnt])
-        done_ev.record(comm_stream)
-        step.wait_event(done_ev.cuda_event)
+        ex.begin(step)
+        ex.wait(step)
     return allreduce
 
 
@@ -403,14 +390,7 @@ def run_lm(args, kind):
     g = torch.Generator().manual_seed(1000 + rank)
     host = [torch.randint(0, GPT2["vocab"], (GPT2_BATCH, GPT2_SEQ), generator=g, dtype=torch.int32) for _ in range(2)]
     global_bs = GPT2_BATCH * world
-    grad_t = None
-    if world > 1:
-        ptr, n = step.grad_buffer()
-        grad_t = torch.as_tensor(_DevBuf(ptr, n), device=f"cuda:{local}")
-        with torch.cuda.stream(stream):
-            dist.all_reduce(grad_t)
-        torch.cuda.synchronize()
-    allreduce = make_overlapped_allreduce(step, grad_t, torch, dist) if grad_t is not None else None
+    allreduce = make_overlapped_allreduce(step, rank, world, local, args) if world > 1 else None
 
     def one(i, upload):
         if upload:
@@ -538,14 +518,7 @@ def run_swin(args):
     host = [(torch.randn(SWIN_BATCH, 3, 224, 224, generator=g).pin_memory(),
              torch.randint(0, 1000, (SWIN_BATCH,), generator=g).pin_memory()) for _ in range(2)]
     global_bs = SWIN_BATCH * world
-    grad_t = None
-    if world > 1:
-        ptr, n = step.grad_buffer()
-        grad_t = torch.as_tensor(_DevBuf(ptr, n), device=f"cuda:{local}")
-        with torch.cuda.stream(stream):
-            dist.all_reduce(grad_t)
-        torch.cuda.synchronize()
-    allreduce = make_overlapped_allreduce(step, grad_t, torch, dist) if grad_t is not None else None
+    allreduce = make_overlapped_allreduce(step, rank, world, local, args) if world > 1 else None
 
     def one(i, upload):
         if upload:
@@ -660,6 +633,10 @@ def main():
                     help="sequences per GPU for the gpt2 / qwen2 workloads (0 = the configuration's own; smaller for profiling)")
     ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2", "swin_b", "qwen2"],
                     help="resnet152 is the headline (BASELINE config 2); swin_b, gpt2 and qwen2 report configs 3, 4 and 5")
+    ap.add_argument("--wire", default="bf16", choices=["bf16", "f32"],
+                    help="gradient format on NVLink for N > 1: bf16 (2 bytes per parameter) or f32")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0,
+                    help="cap on the CTAs NCCL's kernels occupy beside the training kernels (0 = NCCL's default)")
     ap.add_argument("--colocate-seconds", type=float, default=8.0,
                     help="length of the colocated training+inference window at N=1 (0 = skip)")
     args = ap.parse_args()

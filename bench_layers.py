@@ -1,7 +1,8 @@
-"""Per-layer micro-benchmark of the convolution kernels on the ResNet-152 layer shapes.
+"""Per-layer micro-benchmark of the convolution and BatchNorm kernels on the ResNet-152 layer shapes
+(a measurement tool beside bench.py; nothing in the library imports it).
 
-
-    python -m sirius_b200.bench_ops [--batch 64] [--case NAME] [--pass fprop|fprop_stats|dgrad|wgrad|all|bn] [--iters 20]
+    python bench_layers.py [--batch 64] [--case NAME] [--pass fprop|fprop_stats|dgrad|wgrad|all|bn] [--iters 20]
+                           [--plan gather,tile_n,pair]
 
 Each case is timed with CUDA events on the launching stream after warm-up; between timed launches a
 buffer larger than L2 is rewritten so every launch starts cold. Prints one JSON line per case/pass.
@@ -15,8 +16,8 @@ import json
 
 import torch
 
-from . import _lib, ops
-from ._lib import IMPL_AUTO, SRT_BF16, ConvDesc
+from sirius_b200 import _lib, ops
+from sirius_b200._lib import IMPL_AUTO, SRT_BF16, ConvDesc
 
 # name: (H, W, C, K, R, stride, pad)  -- activations are batch x H x W x C
 CASES = {
@@ -40,6 +41,9 @@ CASES = {
     "syn_1x1_k4096_n128": (14, 14, 4096, 128, 1, 1, 0),
     "syn_1x1_k4096_n64": (14, 14, 4096, 64, 1, 1, 0),
 }
+
+
+PLAN = ""
 
 
 def run_case(name, batch, which, iters, flush):
@@ -97,7 +101,7 @@ def run_case(name, batch, which, iters, flush):
         torch.cuda.synchronize()
         total = sum(a.elapsed_time(b) for a, b in evs)
         us = total / iters * 1e3
-        rec = {"case": name, "pass": p, "batch": batch, "us": round(us, 2),
+        rec = {"case": name, "pass": p, "batch": batch, "plan": PLAN, "us": round(us, 2),
                "tflops": round(flops / us / 1e6, 1), "min_gbytes_per_s": round(io[p] / us / 1e3, 1),
                "gflop": round(flops / 1e9, 2), "mbytes": round(io[p] / 1e6, 1), "tc_status": ops.tc_status()}
         print(json.dumps(rec), flush=True)
@@ -126,7 +130,7 @@ def run_bn_case(name, batch, iters, flush, one_launch=False):
     counts are the tensors each pass has to move once: forward reads z twice (statistics, apply),
     reads the residual and writes y; backward reads dy and z twice (sums, apply), the stored y twice
     in a residual unit (ReLU mask), and writes dz (and the gradient of the residual branch)."""
-    from ._lib import call, lib
+    from sirius_b200._lib import call
     H, W, C, res = BN_CASES[name]
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
@@ -192,7 +196,12 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--one-launch", action="store_true", help="BatchNorm cases: the one-launch kernels")
+    ap.add_argument("--plan", default="", help="fprop/dgrad plan override 'gather,tile_n,pair' (srt_conv_plan_override)")
     a = ap.parse_args()
+    global PLAN
+    PLAN = a.plan
+    if a.plan:
+        _lib.lib().srt_conv_plan_override(*[int(v) for v in a.plan.split(",")])
     if a.which == "bn":
         for name in (BN_CASES if a.case == "all" else [a.case]):
             run_bn_case(name, a.batch, a.iters, not a.no_flush, a.one_launch)

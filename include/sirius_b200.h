@@ -204,11 +204,13 @@ int srt_debug_smid_probe(void* device_mask3, void* stream);
  * Every wait inside the tensor-core kernels is bounded; a wait that gives up records a non-zero
  * code here instead of hanging the GPU. Synchronises the device, returns and clears the word. */
 int srt_tc_status(int* status);
-/* Test hook: route 1x1 stride-1 convolutions through the gather path instead of TMA for A. */
-int srt_debug_force_gather(int on);
-/* Test hook: fprop/dgrad kernel variant (0 = persistent CTA per SM, 1 = one output tile per CTA)
- * and tile width (0 = heuristic, else 64, 128 or 256 output channels per tile). */
-int srt_debug_fwd_variant(int variant, int bn);
+/* Plan override of the tensor-core fprop/dgrad kernel for tuning and for tests that must reach every
+ * code path with small problems (process-wide; 0, 0, -1 restores the heuristics):
+ *   gather  1 = fetch the A operand of 1x1 stride-1 problems with the gather threads instead of TMA
+ *   tile_n  output-tile width: 64, 128 or 256 filters (0 = heuristic)
+ *   pair    1 = two CTAs per 256-row tile (tcgen05 cta_group::2) wherever the output is wider than 64
+ *           filters, 0 = always one CTA per 128-row tile, -1 = heuristic. */
+int srt_conv_plan_override(int gather, int tile_n, int pair);
 
 /* ---- training-step executor (replaces the body of the reference's training loop:
  *      model(images) / criterion / backward / optimizer stage, train/resnet152.py:84-91, with
@@ -277,6 +279,46 @@ int srt_step_num_grad_buckets(srt_step* s);
 int srt_step_grad_bucket(srt_step* s, int i, int64_t* offset, int64_t* count);
 int srt_step_wait_grad_bucket(srt_step* s, int i, void* stream);
 int srt_step_wait_event(srt_step* s, void* cuda_event);
+/* ---- gradient exchange between data-parallel ranks (replaces the reference's c10d Reducer and ProcessGroupNCCL
+ *      extension: pytorch/torch_col/csrc/dist_ext.h:109-243, dist_ext.cc:59-123; abort / restart of the communicator:
+ *      dist_ext.cc:673-784 _set_nccl_comm_abort_flag, _restart_nccl_comm) ---------------------------------------
+ * One NCCL communicator and one communication stream per rank, owned by the library (NCCL is loaded at run time;
+ * srt_ddp_available() is 0 where it cannot be). Rank 0 obtains SRT_DDP_ID_BYTES of unique id and hands it to
+ * the other ranks by any channel (the mailboxes of srt_dist_*, torch.distributed, a file); every rank then calls
+ * srt_ddp_create with the same id, which blocks until all ranks have joined. max_ctas > 0 caps the CTAs NCCL's
+ * kernels may occupy beside the training kernels (0 = NCCL's default).
+ *
+ * srt_allreduce_begin enqueues, on the communication stream, one sum all-reduce per bucket
+ * [offsets[i], offsets[i] + counts[i]) of the fp32 buffer `grad`, bucket i behind the CUDA event ready_events[i]
+ * (NULL entries or a NULL array: no wait), and returns at once. wire_dtype SRT_F32 reduces the values in place;
+ * SRT_BF16 rounds each bucket to bf16 into a staging buffer of the communicator (allocated at the first such call,
+ * grown when a larger buffer comes), reduces half the bytes and widens the sums back into `grad` (bucket offsets
+ * must then be multiples of 8). srt_allreduce_wait makes `stream` wait for the exchange begun last. The buffer
+ * must not be written between begin and the moment the waiting stream proceeds.
+ * srt_step_allreduce_begin / srt_gb_allreduce_begin take buckets and events from a step executor
+ * (srt_step_num_grad_buckets ..., srt_<model>_grad_buckets); srt_step_allreduce_wait orders the ResNet executor's
+ * stream behind the exchange (the transformer executors: srt_allreduce_wait on srt_<model>_stream).
+ * srt_ddp_abort tears the communicator down without waiting for collectives in flight (after a killed batch left
+ * ranks with different numbers of collectives issued); srt_ddp_restart joins a new communicator under a new id. */
+typedef struct srt_ddp srt_ddp;
+#define SRT_DDP_ID_BYTES 128
+int srt_ddp_available(void);
+int srt_ddp_nccl_version(int* version);
+int srt_ddp_unique_id(void* id);
+int srt_ddp_create(const void* id, int rank, int world, int device, int max_ctas, srt_ddp** out);
+int srt_ddp_destroy(srt_ddp* c);
+int srt_ddp_abort(srt_ddp* c);
+int srt_ddp_restart(srt_ddp* c, const void* id);
+void* srt_ddp_stream(srt_ddp* c);
+int srt_ddp_stats(srt_ddp* c, int64_t* exchanges, int64_t* bytes_on_wire);
+int srt_allreduce_begin(srt_ddp* c, float* grad, int nbuckets, const int64_t* offsets, const int64_t* counts,
+                        void* const* ready_events, int wire_dtype);
+int srt_allreduce_wait(srt_ddp* c, void* stream);
+/* Plain in-place sum all-reduce of `count` elements on `stream` (accumulated gradients before an update, scalars). */
+int srt_ddp_allreduce(srt_ddp* c, void* buf, int64_t count, int dtype, void* stream);
+int srt_step_allreduce_begin(srt_step* s, srt_ddp* c, int accumulated, int wire_dtype);
+int srt_step_allreduce_wait(srt_step* s, srt_ddp* c);
+int srt_gb_allreduce_begin(void* buckets, float* grad, srt_ddp* c, int wire_dtype);
 int srt_step_current_sms(srt_step* s, int* sms);
 int srt_step_destroy(srt_step* s);
 /* Parameter registry under torchvision state_dict names ("layer1.0.conv1.weight", ...). Shapes and
@@ -286,6 +328,11 @@ int srt_step_param_info(srt_step* s, int idx, char* name, int name_cap, int64_t 
                         int* kind);
 int srt_step_set_param(srt_step* s, int idx, const float* host);
 int srt_step_get_param(srt_step* s, int idx, float* host, int which);
+/* Resume support (what loading a torch.optim.SGD state_dict does, pytorch/torch_col/util.py:182-190 pre-allocates
+ * the same buffers): sets the value (which = SRT_GET_VALUE), the momentum buffer (SRT_GET_MOMENTUM; the next
+ * optimizer step then continues the run instead of initialising the momentum from the gradient) or the
+ * accumulated gradient (SRT_GET_ACCUM) of one parameter from host data in the torch layout. */
+int srt_step_set_state(srt_step* s, int idx, const float* host, int which);
 /* Rebuild the derived copies (bf16 working weights, transposed filters) after set_param. */
 int srt_step_commit_params(srt_step* s);
 void* srt_step_stream(srt_step* s);

@@ -43,22 +43,31 @@ def forward_logits(model, ids):
         return model(ids).logits.float().numpy()
 
 
-def first_step_gradients(model, ids):
+def _loss_backward(m, ids, micro_batches):
+    """Mean next-token loss over the batch, back-propagated. micro_batches > 1 runs the sequences in equal groups
+    and scales each group's mean loss by 1 / micro_batches before backward: every sequence holds the same number
+    of predicted tokens, so the accumulated gradient is that of the whole batch (up to fp32 summation order)
+    while the activations of one group at a time fit the host's memory."""
+    total = 0.0
+    for chunk in ids.chunk(micro_batches):
+        loss = m(chunk, labels=chunk).loss / micro_batches
+        loss.backward()
+        total += float(loss.detach())
+    return total
+
+
+def first_step_gradients(model, ids, micro_batches=1):
     m = copy.deepcopy(model)
-    loss = m(ids, labels=ids).loss
-    loss.backward()
-    return float(loss.detach()), {k: p.grad.detach().float().numpy().copy() for k, p in m.named_parameters()
-                                  if k.startswith("model.")}
+    loss = _loss_backward(m, ids, micro_batches)
+    return loss, {k: p.grad.detach().float().numpy().copy() for k, p in m.named_parameters() if k.startswith("model.")}
 
 
-def train_steps(model, batches, lr=3e-4, weight_decay=0.01):
+def train_steps(model, batches, lr=3e-4, weight_decay=0.01, micro_batches=1):
     m = copy.deepcopy(model)
     opt = torch.optim.AdamW(m.parameters(), lr=lr, weight_decay=weight_decay)
     losses = []
     for ids in batches:
         opt.zero_grad(set_to_none=True)
-        loss = m(ids, labels=ids).loss
-        loss.backward()
+        losses.append(_loss_backward(m, ids, micro_batches))
         opt.step()
-        losses.append(float(loss.detach()))
     return losses, state_arrays(m)

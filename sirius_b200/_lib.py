@@ -73,8 +73,7 @@ _SIGNATURES = {
     "srt_set_sm_mask": (None, [C.POINTER(C.c_uint64)]),
     "srt_get_sm_mask": (None, [C.POINTER(C.c_uint64)]),
     "srt_tc_status": (None, [C.POINTER(C.c_int)]),
-    "srt_debug_force_gather": (None, [_i]),
-    "srt_debug_fwd_variant": (None, [_i, _i]),
+    "srt_conv_plan_override": (None, [_i, _i, _i]),
 }
 
 _lib = None

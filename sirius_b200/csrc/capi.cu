@@ -60,9 +60,7 @@ void set_current_sm_mask(const SmMask& m) {
 }
 
 int tc_status_fetch(int* out);
-void tc_set_force_gather(int v);
-void tc_set_fwd_variant(int variant, int bn);
-void tc_set_no_load(int v);
+void tc_set_conv_plan(int gather, int tile_n, int pair);
 
 static int check_desc(const srt_conv_desc& d) {
   SRT_REQUIRE(d.N > 0 && d.H > 0 && d.W > 0 && d.C > 0 && d.K > 0 && d.R > 0 && d.S > 0 &&
@@ -338,18 +336,12 @@ int srt_tc_status(int* status) {
   SRT_REQUIRE(status != nullptr, "tc_status: null argument");
   return tc_status_fetch(status);
 }
-int srt_debug_force_gather(int on) {
-  tc_set_force_gather(on);
-  return SRT_OK;
-}
-int srt_debug_no_load(int on) {
-  tc_set_no_load(on);
-  return SRT_OK;
-}
-int srt_debug_fwd_variant(int variant, int bn) {
-  SRT_REQUIRE(variant == 0 || variant == 1, "fwd_variant: 0 (persistent) or 1 (tile per CTA)");
-  SRT_REQUIRE(bn == 0 || bn == 64 || bn == 128 || bn == 256, "fwd_variant: bn must be 0, 64, 128 or 256");
-  tc_set_fwd_variant(variant, bn);
+int srt_conv_plan_override(int gather, int tile_n, int pair) {
+  SRT_REQUIRE(gather == 0 || gather == 1, "conv_plan_override: gather must be 0 or 1");
+  SRT_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256,
+              "conv_plan_override: tile_n must be 0, 64, 128 or 256");
+  SRT_REQUIRE(pair >= -1 && pair <= 1, "conv_plan_override: pair must be -1, 0 or 1");
+  tc_set_conv_plan(gather, tile_n, pair);
   return SRT_OK;
 }
 
@@ -412,6 +404,18 @@ int srt_gb_wait(void* gb, int i, void* stream) {
   SRT_REQUIRE(b && i >= 0 && i < (int)b->list.size(), "gb_wait: bad argument");
   SRT_CHECK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, b->list[i].ev, 0));
   return SRT_OK;
+}
+int srt_gb_allreduce_begin(void* gb, float* grad, srt_ddp* c, int wire_dtype) {
+  GradBuckets* b = (GradBuckets*)gb;
+  SRT_REQUIRE(b && grad && c, "gb_allreduce_begin: null argument");
+  std::vector<int64_t> off, cnt;
+  std::vector<cudaEvent_t> ev;
+  for (auto& k : b->list) {
+    off.push_back((int64_t)k.off);
+    cnt.push_back((int64_t)k.count);
+    ev.push_back(k.ev);
+  }
+  return grad_exchange_begin((Comm*)c, grad, (int)off.size(), off.data(), cnt.data(), ev.data(), wire_dtype);
 }
 int srt_stream_wait_event(void* stream, void* event) {
   SRT_REQUIRE(event, "stream_wait_event: null event");

@@ -5,6 +5,8 @@
 
 namespace srt {
 
+int* tc_status_device_ptr();  // igemm_tcgen05.cu: the status word srt_tc_status() reads
+
 namespace {
 constexpr int NT = 256;
 
@@ -190,20 +192,36 @@ __device__ inline float block_reduce(float v, bool is_max) {
   return r;
 }
 
+constexpr int kStatusBadLabel = 0xCE;  // status code: a label outside [0, classes) was skipped
+
 template <typename T>
 __global__ void softmax_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels,
                                   int classes, float grad_scale, float* __restrict__ row_loss,
-                                  T* __restrict__ dlogits) {
+                                  T* __restrict__ dlogits, int* __restrict__ status) {
   pdl_enter();
   const int row = blockIdx.x;
   const T* l = logits + (size_t)row * classes;
+  // A label outside [0, classes) (an ignore index, a data set with more classes than the head) must not index
+  // the row: such a row contributes no loss and no gradient, and the status word reports it.
+  const int64_t lab64 = labels[row];
+  if (lab64 < 0 || lab64 >= (int64_t)classes) {
+    if (dlogits) {
+      T* d = dlogits + (size_t)row * classes;
+      for (int c = threadIdx.x; c < classes; c += blockDim.x) d[c] = ElemTraits<T>::from_f(0.f);
+    }
+    if (threadIdx.x == 0) {
+      if (row_loss) row_loss[row] = 0.f;
+      if (status) atomicCAS(status, 0, kStatusBadLabel);
+    }
+    return;
+  }
   float mx = -INFINITY;
   for (int c = threadIdx.x; c < classes; c += blockDim.x) mx = fmaxf(mx, ElemTraits<T>::to_f(l[c]));
   mx = block_reduce(mx, true);
   float se = 0.f;
   for (int c = threadIdx.x; c < classes; c += blockDim.x) se += expf(ElemTraits<T>::to_f(l[c]) - mx);
   se = block_reduce(se, false);
-  const int lab = (int)labels[row];
+  const int lab = (int)lab64;
   const float inv = 1.f / se;
   if (dlogits) {
     T* d = dlogits + (size_t)row * classes;
@@ -496,7 +514,8 @@ int softmax_ce(int dtype, const void* logits, const int64_t* labels, int B, int 
                float grad_scale, float* row_loss, void* dlogits, cudaStream_t st) {
   SRT_REQUIRE(B > 0 && classes > 0, "softmax_ce: empty input");
   DISPATCH_T(dtype, {
-    launch_pdl(softmax_ce_kernel<T>, dim3(B), dim3(NT), 0, st, (const T*)logits, labels, classes, grad_scale, row_loss, (T*)dlogits);
+    launch_pdl(softmax_ce_kernel<T>, dim3(B), dim3(NT), 0, st, (const T*)logits, labels, classes, grad_scale, row_loss, (T*)dlogits,
+               tc_status_device_ptr());
   });
   SRT_LAUNCH_CHECK();
   return SRT_OK;

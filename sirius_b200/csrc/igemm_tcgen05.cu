@@ -30,7 +30,7 @@
 
 namespace srt {
 
-static int g_force_gather = 0;  // test hook: route plain-matrix operands through the gather path
+static int g_force_gather = 0;  // plan override: fetch plain-matrix operands with the gather threads
 
 namespace {
 
@@ -48,6 +48,22 @@ __device__ int g_tc_status;  // 0 = ok; otherwise the code of the first wait tha
 
 enum WaitCode { W_PROD_EMPTY = 1, W_TMA_EMPTY = 2, W_MMA_FULL = 3, W_EPI_TMEM = 4 };
 
+// Phase time stamps of the persistent kernel, compiled in only for timing studies (-DSRT_PHASE_STAMPS; the shipped
+// library does not define it): slot i of CTA b is written to stamps[b * 16 + i] as a %globaltimer reading.
+#ifdef SRT_PHASE_STAMPS
+__device__ unsigned long long* g_phase_stamps;
+__device__ __forceinline__ void phase_stamp(int i) {
+  if (g_phase_stamps) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_phase_stamps[blockIdx.x * 16 + i] = t;
+  }
+}
+#define SRT_STAMP(i) phase_stamp(i)
+#else
+#define SRT_STAMP(i)
+#endif
+
 // n / d for 0 <= n < 2^31 with a precomputed multiplier and shift (d >= 1).
 __host__ inline void fastdiv_make(uint32_t d, uint32_t* mul, uint32_t* shr) {
   uint32_t p = 0;
@@ -60,16 +76,6 @@ __device__ __forceinline__ int fastdiv(int n, int d, uint32_t mul, uint32_t shr)
   return d == 1 ? n : (int)(__umulhi((uint32_t)n, mul) >> shr);
 }
 
-struct FwdParams {
-  GatherGeom g;
-  const bf16* src;
-  bf16* D;
-  const float* bias;
-  const bf16* addend;
-  int k_blocks;
-  int a_tma;
-  int* status;
-};
 
 struct WgradParams {
   GatherGeom g;  // fprop geometry: rows = output pixels, gather from x
@@ -129,186 +135,6 @@ __device__ __forceinline__ void producer_drain(int issued, uint64_t* full) {
 }
 
 // ------------------------------------------------------------------------------------------
-template <int BN, int NS>
-__global__ void __launch_bounds__(NTHREADS)
-igemm_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_a) {
-  constexpr int B_STAGE_BYTES = BN * BK * 2;
-  extern __shared__ uint8_t smem_raw[];
-  SmemLayout sm = carve_smem<NS, B_STAGE_BYTES>(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const GatherGeom& g = p.g;
-  const int nkb = p.k_blocks;
-
-  if (tid == 0) {
-    const uint32_t full_count = p.a_tma ? 1u : (uint32_t)(NPROD + 1);
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(smem_u32(&sm.full[s]), full_count);
-      mbar_init(smem_u32(&sm.empty[s]), 1);
-    }
-    mbar_init(smem_u32(sm.tmem_full), 1);
-    mbar_fence_init();
-  }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&tmap_b);
-    if (p.a_tma) tma_prefetch_desc(&tmap_a);
-  }
-  if (warp == 5) {
-    tmem_alloc(smem_u32(sm.tmem_ptr), BN);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *sm.tmem_ptr;
-  // Everything above touches only shared memory, tensor memory and the kernel parameters, so under an early
-  // (programmatic dependent) launch it runs beside the predecessor's tail; global memory is first touched below.
-  pdl_enter();
-
-  if (warp < 4) {
-    // ---------------- gather producers ----------------
-    if (!p.a_tma) {
-      const int j = tid & 7, r0 = tid >> 3;
-      const uint32_t swz = (uint32_t)((j ^ (r0 & 7)) << 4);
-      int pixb[8], ih0[8], iw0[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int m = m0 + r0 + 16 * i;
-        if (m < g.M) {
-          RowCoord rc = decode_row(g, m);
-          pixb[i] = rc.n * g.src_h * g.src_w;
-          ih0[i] = g.dgrad ? rc.oh + g.pad : rc.oh * g.stride - g.pad;
-          iw0[i] = g.dgrad ? rc.ow + g.pad : rc.ow * g.stride - g.pad;
-        } else {
-          pixb[i] = 0;
-          ih0[i] = g.dgrad ? -(1 << 20) : -(1 << 20);
-          iw0[i] = 0;
-        }
-      }
-      int issued = 0;
-      bool ok = true;
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % NS;
-        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
-        if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) { ok = false; break; }
-        const int kk = kb * BK + j * 8;
-        const bool k_ok = kk < g.Kg;
-        const int tap = kk / g.src_c, c = kk - tap * g.src_c;
-        const int r = tap / g.S, sf = tap - r * g.S;
-        const uint32_t dst0 = smem_u32(sm.a + s * A_STAGE_BYTES) + (uint32_t)r0 * 128u + swz;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          int ih, iw;
-          bool v = k_ok;
-          if (!g.dgrad) {
-            ih = ih0[i] + r;
-            iw = iw0[i] + sf;
-          } else {
-            const int th = ih0[i] - r, tw = iw0[i] - sf;
-            v = v && th >= 0 && tw >= 0;
-            if (g.stride > 1) {
-              v = v && (th % g.stride == 0) && (tw % g.stride == 0);
-              ih = th / g.stride;
-              iw = tw / g.stride;
-            } else {
-              ih = th;
-              iw = tw;
-            }
-          }
-          v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
-          const bf16* ptr = v ? p.src + ((size_t)(pixb[i] + ih * g.src_w + iw) * g.src_c + c) : p.src;
-          cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
-        }
-        producer_handover<NS>(kb, sm.full);
-        issued = kb + 1;
-      }
-      (void)ok;
-      producer_drain<NS>(issued, sm.full);
-    }
-    // ---------------- epilogue ----------------
-    const bool ready = mbar_wait(smem_u32(sm.tmem_full), 0u, p.status, W_EPI_TMEM);
-    tc_fence_after_sync();
-    const int m = m0 + warp * 32 + lane;
-#pragma unroll 1
-    for (int cb = 0; cb < BN / 32; ++cb) {
-      uint32_t acc[32];
-      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 32), acc);
-      tmem_ld_wait();
-      if (ready && m < g.M) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const int col = n0 + cb * 32 + v * 8;
-          if (col < g.Nout) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
-            if (p.bias) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
-            }
-            const size_t o = (size_t)m * g.Nout + col;
-            if (p.addend) {
-              Vec16<bf16> av;
-              av.load(p.addend + o);
-              float af[8];
-              av.unpack(af);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] += af[e];
-            }
-            Vec16<bf16> ov;
-            ov.pack(f);
-            ov.store(p.D + o);
-          }
-        }
-      }
-    }
-  } else if (warp == 4) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      const uint32_t bytes = (uint32_t)B_STAGE_BYTES + (p.a_tma ? (uint32_t)A_STAGE_BYTES : 0u);
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % NS;
-        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
-        if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
-        const uint32_t bar = smem_u32(&sm.full[s]);
-        mbar_arrive_expect_tx(bar, bytes);
-        tma_load_2d(smem_u32(sm.b + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
-        if (p.a_tma) tma_load_2d(smem_u32(sm.a + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
-      }
-    }
-  } else {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
-      bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % NS;
-        const uint32_t ph = (uint32_t)(kb / NS) & 1u;
-        if (!mbar_wait(smem_u32(&sm.full[s]), ph, p.status, W_MMA_FULL)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t a0 = smem_u32(sm.a + s * A_STAGE_BYTES);
-        const uint32_t b0 = smem_u32(sm.b + s * B_STAGE_BYTES);
-#pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          const uint64_t ad = make_smem_desc_sw128(a0 + k * 32, 0, 1024);
-          const uint64_t bd = make_smem_desc_sw128(b0 + k * 32, 0, 1024);
-          umma_bf16(tmem_base, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&sm.empty[s]));
-      }
-      umma_commit(smem_u32(sm.tmem_full));
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 5) {
-    __syncwarp();
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, BN);
-  }
-}
 
 // ------------------------------------------------------------------------------------------
 template <int BN, int NS>
@@ -469,16 +295,28 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
 
 // ------------------------------------------------------------------------------------------
 // Persistent fprop/dgrad kernel: one CTA per SM walks the output tiles t = blockIdx.x, +gridDim.x,
-// ... (t = m_tile * n_tiles + n_tile). 448 threads:
+// ... (t = m_tile * n_tiles + n_tile). 704 threads:
 //   warp 0        TMA producer: B tile every stage, A tile too when it is a plain matrix block
 //   warp 1        tensor-memory allocation, tcgen05.mma issue (lane 0)
-//   warps 2-5     epilogue group 0: TMEM -> registers -> (+bias, +addend) -> bf16 -> swizzled smem -> TMA store
-//   warps 6-9     A gather producers (cp.async), idle when A comes by TMA
-//   warps 10-13   epilogue group 1 (takes every other 64-column slab of a tile)
+//   warps 2-3, 20-21   A gather producers (cp.async), idle when A comes by TMA
+//   warps 4-19    four epilogue groups of four warps: TMEM -> registers -> (+bias, +addend) -> bf16 -> swizzled
+//                 smem -> TMA store, one 64-column slab of a tile at a time, slabs dealt round-robin
 // The shared-memory stage ring runs across tile boundaries, and the accumulator is double-buffered
 // in tensor memory (2 x BN columns), so the loads of tile i+1 and the MMAs of tile i+1 overlap the
 // epilogue of tile i.
-constexpr int P_THREADS = 448;
+//
+// PAIR = true runs two CTAs (a cluster of two, on the two SMs of one TPC) as one unit on a 256 x BN tile:
+// CTA r of the pair loads rows [128r, 128r+128) of A and filters [BN/2 * r, BN/2 * (r+1)) of B, the
+// leader (rank 0) issues tcgen05.mma.cta_group::2 over both CTAs' shared memory, and each CTA finds its 128
+// output rows in its own tensor memory and runs its own epilogue. An SM then stages 16 KB + BN x 64 bytes
+// per k-block instead of 16 KB + BN x 128 bytes for the same 128 x BN outputs: the L2-to-SM operand stream,
+// which bounds these main loops, shrinks by a quarter (BN = 128) to a third (BN = 256), and the smaller stages
+// allow a deeper ring. Every load is a plain per-CTA TMA load (none is multicast); what crosses the pair is
+// barrier traffic only: both CTAs' loads and gather threads signal the leader's "full" barriers, the MMA's
+// commits signal the "empty" and "accumulator ready" barriers of both CTAs, and the peer's epilogue
+// releases the accumulator on the leader's barrier.
+constexpr int P_THREADS = 704;
+constexpr int EPI_GROUPS = 4;            // epilogue warp groups (a power of two)
 constexpr int OUT_SLAB_BYTES = BM * 128;  // 128 rows x 64 bf16
 
 struct PersistParams {
@@ -488,8 +326,8 @@ struct PersistParams {
   const bf16* addend;
   int k_blocks;
   int a_tma;
-  int m_tiles, n_tiles;
-  int no_load;  // timing experiment: hand stages over without loading them (results are garbage)
+  int m_tiles, n_tiles;  // 128-row tiles and BN-column tiles of the output
+  int gather_lag;        // cp.async groups a gather thread keeps in flight before it hands a stage over (1..NS-2)
   int* status;
   // Optional: per 128-row tile and output column, the sum and the sum of squares of the stored (rounded) values,
   // as double2 [m_tiles][Nout]. The BatchNorm that follows a convolution finalizes its statistics from these and
@@ -499,9 +337,9 @@ struct PersistParams {
 
 enum WaitCode2 { W_MMA_TMEM_EMPTY = 5 };
 
-template <int BN, int NS>
+template <int BN, int NS, bool PAIR>
 constexpr size_t persist_smem_bytes() {
-  return 1024 + (size_t)NS * (A_STAGE_BYTES + BN * BK * 2) + 2 * OUT_SLAB_BYTES + (2 * NS + 4) * 8 + 16;
+  return 1024 + (size_t)NS * (A_STAGE_BYTES + (PAIR ? BN / 2 : BN) * BK * 2) + EPI_GROUPS * OUT_SLAB_BYTES + (2 * NS + 4) * 8 + 16;
 }
 
 // One lane's share of a staged 128 x 64 bf16 slab for the column sums: 32 rows (rp0/rp1 point at the lane's even
@@ -524,20 +362,30 @@ __device__ inline void slab_col_sums(const uint8_t* rp0, const uint8_t* rp1, int
   }
 }
 
-template <int BN, int NS>
+// cp.async.wait_group takes an immediate: wait until at most `lag` of this thread's groups are pending.
+__device__ __forceinline__ void cp_async_wait_lag(int lag) {
+  switch (lag) {
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    default: cp_async_wait<4>(); break;
+  }
+}
+
+template <int BN, int NS, bool PAIR>
 __global__ void __launch_bounds__(P_THREADS, 1)
 igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_d) {
-  constexpr int B_STAGE_BYTES = BN * BK * 2;
-  constexpr int PLAG = NS - 2;  // cp.async groups in flight per gather thread
-  constexpr int EPI_GROUPS = BN >= 128 ? 2 : 1;  // epilogue warp groups at work (see the epilogue branch)
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;    // filters this CTA stages per k-block
+  constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+  constexpr int NCTA = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = base;
   uint8_t* sB = sA + NS * A_STAGE_BYTES;
   uint8_t* sOut = sB + NS * B_STAGE_BYTES;
-  uint64_t* full = (uint64_t*)(sOut + 2 * OUT_SLAB_BYTES);
+  uint64_t* full = (uint64_t*)(sOut + EPI_GROUPS * OUT_SLAB_BYTES);
   uint64_t* empty = full + NS;
   uint64_t* tmem_full = empty + NS;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;  // [2]
@@ -546,17 +394,26 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const GatherGeom& g = p.g;
   const int nkb = p.k_blocks;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  if (tid == 0) SRT_STAMP(0);
+  // In a pair the unit of work is a 256-row tile; rank r owns its rows 128r..128r+127.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int nunits = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int total_tiles = (PAIR ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;
 
   if (tid == 0) {
-    const uint32_t full_count = p.a_tma ? 1u : (uint32_t)(NPROD + 1);
+    // "full" is waited on by the MMA thread (the leader's, in a pair): one arrival from the TMA thread that
+    // announces the bytes, plus one per gather warp of every CTA of the unit when A is gathered (lane 0 arrives
+    // for its warp: an arrival on the other CTA's barrier is a remote transaction, and 128 of them per stage
+    // cost more than the loads).
+    const uint32_t full_count = p.a_tma ? 1u : (uint32_t)(NCTA * (NPROD / 32) + 1);
     for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&full[s]), full_count);
       mbar_init(smem_u32(&empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tmem_full[b]), 1);
-      mbar_init(smem_u32(&tmem_empty[b]), (uint32_t)(NPROD * EPI_GROUPS));
+      mbar_init(smem_u32(&tmem_empty[b]), (uint32_t)(NCTA * (NPROD / 32) * (BN / 64)));  // one arrival per warp and slab
     }
     mbar_fence_init();
   }
@@ -566,53 +423,74 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
     if (p.a_tma) tma_prefetch_desc(&tmap_a);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_ptr), 2 * BN);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_ptr), 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_ptr), 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers and tensor memory exist before anything refers to them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  if (tid == 0) SRT_STAMP(1);
   // Everything above touches only shared memory, tensor memory and the kernel parameters, so under an early
   // (programmatic dependent) launch it runs beside the predecessor's tail; global memory is first touched below.
   pdl_enter();
+  if (tid == 0) SRT_STAMP(2);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const uint32_t bytes = (uint32_t)B_STAGE_BYTES + (p.a_tma ? (uint32_t)A_STAGE_BYTES : 0u);
+      // bytes that land on one "full" barrier per stage: from both CTAs of a pair
+      const uint32_t bytes = (uint32_t)NCTA * ((uint32_t)B_STAGE_BYTES + (p.a_tma ? (uint32_t)A_STAGE_BYTES : 0u));
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / p.n_tiles) * BM, n0 = (t % p.n_tiles) * BN;
+      for (int t = unit; t < total_tiles && ok; t += nunits) {
+        const int m0 = ((t / p.n_tiles) * NCTA + (int)rank) * BM;
+        const int n0 = (t % p.n_tiles) * BN + (int)rank * B_ROWS;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % NS;
           const uint32_t ph = (uint32_t)(it / NS) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) { ok = false; break; }
-          const uint32_t bar = smem_u32(&full[s]);
-          if (p.no_load & 1) { mbar_arrive(bar); continue; }
-          mbar_arrive_expect_tx(bar, bytes);
-          tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
-          if (p.a_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
+          if (PAIR) {
+            const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0u);
+            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full[s]), bytes);
+            tma_load_2d_pair(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, lbar, kb * BK, n0);
+            if (p.a_tma) tma_load_2d_pair(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, lbar, kb * BK, m0);
+          } else {
+            const uint32_t bar = smem_u32(&full[s]);
+            mbar_arrive_expect_tx(bar, bytes);
+            tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
+            if (p.a_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+    // ---------------- MMA issuer (the leader's, in a pair) ----------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM * NCTA, BN, 0, 0);
       int it = 0, tc = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tc) {
+      for (int t = unit; t < total_tiles && ok; t += nunits, ++tc) {
         const int b = tc & 1;
         const uint32_t aph = (uint32_t)(tc >> 1) & 1u;
-        if (!mbar_wait(smem_u32(&tmem_empty[b]), aph ^ 1u, p.status, W_MMA_TMEM_EMPTY)) { ok = false; break; }
+        const bool got = PAIR ? mbar_wait_cluster(smem_u32(&tmem_empty[b]), aph ^ 1u, p.status, W_MMA_TMEM_EMPTY)
+                              : mbar_wait(smem_u32(&tmem_empty[b]), aph ^ 1u, p.status, W_MMA_TMEM_EMPTY);
+        if (!got) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t acc = tmem_base + (uint32_t)(b * BN);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % NS;
           const uint32_t ph = (uint32_t)(it / NS) & 1u;
-          if (!mbar_wait(smem_u32(&full[s]), ph, p.status, W_MMA_FULL)) { ok = false; break; }
+          const bool fl = PAIR ? mbar_wait_cluster(smem_u32(&full[s]), ph, p.status, W_MMA_FULL)
+                               : mbar_wait(smem_u32(&full[s]), ph, p.status, W_MMA_FULL);
+          if (!fl) { ok = false; break; }
+          if (it == 0) SRT_STAMP(3);
           tc_fence_after_sync();
           const uint32_t a0 = smem_u32(sA + s * A_STAGE_BYTES);
           const uint32_t b0 = smem_u32(sB + s * B_STAGE_BYTES);
@@ -620,142 +498,172 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = make_smem_desc_sw128(a0 + k * 32, 0, 1024);
             const uint64_t bd = make_smem_desc_sw128(b0 + k * 32, 0, 1024);
-            umma_bf16(acc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) umma_bf16_pair(acc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_bf16(acc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&empty[s]));
+          if (PAIR) umma_commit_pair(smem_u32(&empty[s]), (uint16_t)3);
+          else umma_commit(smem_u32(&empty[s]));
         }
-        umma_commit(smem_u32(&tmem_full[b]));
+        if (PAIR) umma_commit_pair(smem_u32(&tmem_full[b]), (uint16_t)3);
+        else umma_commit(smem_u32(&tmem_full[b]));
+        SRT_STAMP(4);  // last write wins: the issue of the last tile's last MMA
       }
     }
-  } else if (warp < 6 || warp >= 10) {
+  } else if (warp >= 4 && warp < 4 + 4 * EPI_GROUPS) {
     // ---------------- epilogue ----------------
-    // Two groups of four warps (warps 2-5 and 10-13; the four warps of a group cover the four TMEM lane
-    // quarters). The 64-column slabs of a tile are dealt to the groups in turn, each group has its own staging
-    // slab, named barrier and store issuer, so the two halves of a tile's epilogue run side by side: a single warp
-    // per scheduler issues the conversion code at a fraction of the issue rate, and that code, not the memory
-    // system, bounds the epilogue. A 64-column tile has one slab and uses one group.
+    // Four groups of four warps (warps 4-19; the four warps of a group cover the four TMEM lane quarters, which a
+    // warp can only read by its index modulo 4). The unit of epilogue work is one 64-column slab of one tile; the
+    // slabs are dealt to the groups round-robin across tiles, so a 256-column tile has its four slabs converted
+    // side by side and narrower tiles keep groups busy with consecutive tiles (both accumulator buffers are then
+    // being read while the MMA warp waits for the first to come back). Each group has its own staging slab,
+    // named barrier and store issuer. Per slab a warp waits for tensor memory, converts and stages 32 columns
+    // at a time; with one or two such warps per scheduler (the earlier layout) those dependent chains, not the
+    // memory system, bounded the epilogue: 2.05 us per slab, 4.1 us per 128 x 256 tile, a third of a
+    // layer-3 reduce convolution and most of an expand one.
     constexpr int NSLAB = BN / 64;
-    const int grp = warp >= 10 ? 1 : 0;
-    if (grp < EPI_GROUPS) {
-      const int q = warp & 3;                 // TMEM lane quarter this warp may read
-      const int row = q * 32 + lane;          // row of the tile held by this thread
-      const int et = (warp - (grp ? 10 : 2)) * 32 + lane;  // 0..127 within the group
-      const bool issuer = et == 0;
-      const uint32_t swz_row = (uint32_t)row * 128u;
-      uint8_t* stage = sOut + grp * OUT_SLAB_BYTES;
-      const uint32_t bar_id = 1u + (uint32_t)grp;
-      constexpr int LAST_SLAB_BASE = NSLAB - EPI_GROUPS;  // this group's last slab is LAST_SLAB_BASE + grp
-      int tc = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tc) {
-        const int m0 = (t / p.n_tiles) * BM, n0 = (t % p.n_tiles) * BN;
-        const int b = tc & 1;
-        if (ok) ok = mbar_wait(smem_u32(&tmem_full[b]), (uint32_t)(tc >> 1) & 1u, p.status, W_EPI_TMEM);
-        tc_fence_after_sync();
-        const int m = m0 + row;
+    const int grp = (warp - 4) >> 2;
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;          // row of the tile held by this thread
+    const int et = ((warp - 4) & 3) * 32 + lane;  // 0..127 within the group
+    const bool issuer = et == 0;
+    const uint32_t swz_row = (uint32_t)row * 128u;
+    uint8_t* stage = sOut + grp * OUT_SLAB_BYTES;
+    const uint32_t bar_id = 1u + (uint32_t)grp;
+    int tc = 0;
+    bool ok = true;
+    for (int t = unit; t < total_tiles; t += nunits, ++tc) {
+      const int m_tile = (t / p.n_tiles) * NCTA + (int)rank;
+      const int m0 = m_tile * BM, n0 = (t % p.n_tiles) * BN;
+      const int b = tc & 1;
+      // every group passes every tile's barrier, with or without a slab of its own in the tile: a waiter that
+      // skipped a phase could take the completion of an earlier one for the one it waits for
+      if (ok) ok = mbar_wait(smem_u32(&tmem_full[b]), (uint32_t)(tc >> 1) & 1u, p.status, W_EPI_TMEM);
+      if (issuer && grp == 0) SRT_STAMP(5);  // last write wins: the last tile's accumulator is complete
+      tc_fence_after_sync();
+      const int m = m0 + row;
+      const bool tile_live = m0 < g.M;  // false only for the second half of a pair's last, odd row tile
 #pragma unroll 1
-        for (int c = grp; c < NSLAB; c += EPI_GROUPS) {
-          const int col0 = n0 + c * 64;
-          const bool live = col0 < g.Nout;  // uniform across the epilogue threads
-          uint4 packed[8];
+      for (int c = 0; c < NSLAB; ++c) {
+        if (((tc * NSLAB + c) & (EPI_GROUPS - 1)) != grp) continue;
+        const int col0 = n0 + c * 64;
+        const bool live = tile_live && col0 < g.Nout;  // uniform across the group
+        if (live) {
+          // the store that read this group's staging slab last must be done with it
+          if (issuer) bulk_wait_group_read<0>();
+          named_bar_sync(bar_id, NPROD);
+        }
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t acc[32];
+        for (int h = 0; h < 2; ++h) {
+          uint32_t acc[32];
+          if (live) {
             tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c * 64 + h * 32), acc);
             tmem_ld_wait();
-            if (c == LAST_SLAB_BASE + grp && h == 1) {
-              // this group's last read of the accumulator: hand it back to the MMA warp
-              tc_fence_before_sync();
-              mbar_arrive(smem_u32(&tmem_empty[b]));
-            }
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int col = col0 + h * 32 + v * 8;
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
-              if (live && col < g.Nout) {
-                if (p.bias) {
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
-                }
-                if (p.addend && m < g.M) {
-                  Vec16<bf16> av;
-                  av.load(p.addend + (size_t)m * g.Nout + col);
-                  float af[8];
-                  av.unpack(af);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) f[e] += af[e];
-                }
-              }
-              Vec16<bf16> ov;
-              ov.pack(f);
-              packed[h * 4 + v] = ov.raw;
+          }
+          if (h == 1) {
+            // this slab has been read: one arrival per warp and slab hands the accumulator back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[b]), 0u));
+              else mbar_arrive(smem_u32(&tmem_empty[b]));
             }
           }
-          if (live) {
-            // the store that read this group's staging slab last must be done with it
-            if (issuer) bulk_wait_group_read<0>();
-            named_bar_sync(bar_id, NPROD);
+          if (!live) continue;
 #pragma unroll
-            for (int chunk = 0; chunk < 8; ++chunk)
-              *reinterpret_cast<uint4*>(stage + swz_row + (uint32_t)((chunk ^ (row & 7)) << 4)) = packed[chunk];
-            fence_proxy_async_smem();
-            named_bar_sync(bar_id, NPROD);
-            if (issuer) {
-              tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
-              bulk_commit_group();
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + h * 32 + v * 8;
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[v * 8 + e]);
+            if (col < g.Nout) {
+              if (p.bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
+              }
+              if (p.addend && m < g.M) {
+                Vec16<bf16> av;
+                av.load(p.addend + (size_t)m * g.Nout + col);
+                float af[8];
+                av.unpack(af);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] += af[e];
+              }
             }
-            if (p.col_partial != nullptr) {
-              // Column sums of the slab as it sits in the staging buffer. Warp w of the group takes columns
-              // 16w..16w+15; a lane owns one column pair and a quarter of the rows, picked so that the 32 words
-              // a warp reads at once fall into 32 different banks of the swizzled slab (the four row classes
-              // differ in bits 1-2 of the row, which the swizzle turns into different 16-byte chunks).
-              const int wg = et >> 5, cpl = lane & 7, rgl = lane >> 3;
-              const int cp = wg * 8 + cpl;
-              const uint32_t chunk = (uint32_t)(cp >> 2), within = (uint32_t)(cp & 3) * 4u;
-              const int nvalid = g.M - m0;  // rows of this tile that exist
-              // both columns of the pair ride in one packed fp32x2 add and one packed fma per row
-              uint64_t s01 = 0ull, q01 = 0ull;
-              const uint8_t* rp0 = stage + (uint32_t)(rgl * 2) * 128u + ((chunk ^ (uint32_t)(rgl * 2)) << 4) + within;
-              const uint8_t* rp1 = stage + (uint32_t)(rgl * 2 + 1) * 128u + ((chunk ^ (uint32_t)(rgl * 2 + 1)) << 4) + within;
-              if (nvalid >= BM) slab_col_sums<false>(rp0, rp1, rgl, nvalid, s01, q01);  // every tile but the last
-              else slab_col_sums<true>(rp0, rp1, rgl, nvalid, s01, q01);
-              float s0, s1, q0, q1;
-              {
-                uint32_t a, b, c, d;
-                asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(s01));
-                asm("mov.b64 {%0, %1}, %2;" : "=r"(c), "=r"(d) : "l"(q01));
-                s0 = __uint_as_float(a); s1 = __uint_as_float(b);
-                q0 = __uint_as_float(c); q1 = __uint_as_float(d);
-              }
+            Vec16<bf16> ov;
+            ov.pack(f);
+            const int chunk = h * 4 + v;
+            *reinterpret_cast<uint4*>(stage + swz_row + (uint32_t)((chunk ^ (row & 7)) << 4)) = ov.raw;
+          }
+        }
+        if (live) {
+          fence_proxy_async_smem();
+          named_bar_sync(bar_id, NPROD);
+          if (issuer) {
+            tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
+            bulk_commit_group();
+          }
+          if (p.col_partial != nullptr) {
+            // Column sums of the slab as it sits in the staging buffer. Warp w of the group takes columns
+            // 16w..16w+15; a lane owns one column pair and a quarter of the rows, picked so that the 32 words
+            // a warp reads at once fall into 32 different banks of the swizzled slab (the four row classes
+            // differ in bits 1-2 of the row, which the swizzle turns into different 16-byte chunks).
+            const int wg = et >> 5, cpl = lane & 7, rgl = lane >> 3;
+            const int cp = wg * 8 + cpl;
+            const uint32_t chunk = (uint32_t)(cp >> 2), within = (uint32_t)(cp & 3) * 4u;
+            const int nvalid = g.M - m0;  // rows of this tile that exist
+            // both columns of the pair ride in one packed fp32x2 add and one packed fma per row
+            uint64_t s01 = 0ull, q01 = 0ull;
+            const uint8_t* rp0 = stage + (uint32_t)(rgl * 2) * 128u + ((chunk ^ (uint32_t)(rgl * 2)) << 4) + within;
+            const uint8_t* rp1 = stage + (uint32_t)(rgl * 2 + 1) * 128u + ((chunk ^ (uint32_t)(rgl * 2 + 1)) << 4) + within;
+            if (nvalid >= BM) slab_col_sums<false>(rp0, rp1, rgl, nvalid, s01, q01);  // every tile but the last
+            else slab_col_sums<true>(rp0, rp1, rgl, nvalid, s01, q01);
+            float s0, s1, q0, q1;
+            {
+              uint32_t a, b2, c2, d;
+              asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b2) : "l"(s01));
+              asm("mov.b64 {%0, %1}, %2;" : "=r"(c2), "=r"(d) : "l"(q01));
+              s0 = __uint_as_float(a); s1 = __uint_as_float(b2);
+              q0 = __uint_as_float(c2); q1 = __uint_as_float(d);
+            }
 #pragma unroll
-              for (int o = 8; o <= 16; o <<= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-                q0 += __shfl_xor_sync(0xffffffffu, q0, o);
-                q1 += __shfl_xor_sync(0xffffffffu, q1, o);
-              }
-              const int col = col0 + 2 * cp;
-              if (rgl == 0 && col < g.Nout) {
-                double2* out = reinterpret_cast<double2*>(p.col_partial) + (size_t)(t / p.n_tiles) * g.Nout + col;
-                out[0] = make_double2((double)s0, (double)q0);
-                out[1] = make_double2((double)s1, (double)q1);
-              }
+            for (int o = 8; o <= 16; o <<= 1) {
+              s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+              s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+              q0 += __shfl_xor_sync(0xffffffffu, q0, o);
+              q1 += __shfl_xor_sync(0xffffffffu, q1, o);
+            }
+            const int col = col0 + 2 * cp;
+            if (rgl == 0 && col < g.Nout) {
+              double2* out = reinterpret_cast<double2*>(p.col_partial) + (size_t)m_tile * g.Nout + col;
+              out[0] = make_double2((double)s0, (double)q0);
+              out[1] = make_double2((double)s1, (double)q1);
             }
           }
         }
       }
-      if (issuer) bulk_wait_group<0>();
     }
+    if (issuer && grp == 0) SRT_STAMP(6);
+    // the staging slab must outlive the last store's read of it; the data reaches memory before the grid ends
+    if (issuer) bulk_wait_group_read<0>();
+    if (issuer && grp == 0) SRT_STAMP(7);
   } else {
     // ---------------- A gather producers ----------------
     if (!p.a_tma) {
-      const int pt = tid - 192;  // 0..127
+      const int pt = (warp < 4 ? warp - 2 : warp - 18) * 32 + lane;  // 0..127 over warps 2, 3, 20, 21
       const int j = pt & 7, r0 = pt >> 3;
+      const int PLAG = p.gather_lag;
       const uint32_t swz = (uint32_t)((j ^ (r0 & 7)) << 4);
       int it = 0;
       bool ok = true;
+      // A stage is complete when every gather warp of the unit has arrived on the MMA thread's barrier. Each
+      // thread has waited for its own copies and fenced them towards the async proxy before the warp meets.
+      auto stage_done = [&](int k) {
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&full[k % NS]), 0u));
+          else mbar_arrive(smem_u32(&full[k % NS]));
+        }
+      };
       // Channel counts that are multiples of BK (every 3x3 layer of the step) keep a k-block inside one filter tap, and
       // without a dgrad stride the source pixel of a row is its tap-(0,0) pixel plus a per-k-block offset: one element
       // offset per row and tile, one per k-block, an add, two unsigned bounds checks and a select per copy, no
@@ -763,8 +671,8 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
       const bool fast = (g.src_c % BK) == 0 && (!g.dgrad || g.stride == 1);
       if (fast) {
         const int sgn = g.dgrad ? -1 : 1;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-          const int m0 = (t / p.n_tiles) * BM;
+        for (int t = unit; t < total_tiles && ok; t += nunits) {
+          const int m0 = ((t / p.n_tiles) * NCTA + (int)rank) * BM;
           int rowoff[8], ih0[8], iw0[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -784,7 +692,8 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           for (int kb = 0; kb < nkb; ++kb, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
-            if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) { ok = false; break; }
+            // warp-uniform outcome: the warp leaves the loop together (its lanes meet in stage_done)
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY))) { ok = false; break; }
             const int dr = sgn * r, ds = sgn * sf;
             const int tapoff = (dr * g.src_w + ds) * g.src_c + c0 + j * 8;
             const uint32_t dst0 = smem_u32(sA + s * A_STAGE_BYTES) + (uint32_t)r0 * 128u + swz;
@@ -792,13 +701,13 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
             for (int i = 0; i < 8; ++i) {
               const bool v = (unsigned)(ih0[i] + dr) < (unsigned)g.src_h && (unsigned)(iw0[i] + ds) < (unsigned)g.src_w;
               const int off = v ? rowoff[i] + tapoff : 0;
-              if (!(p.no_load & 1)) cp_async_16(dst0 + (uint32_t)i * (16u * 128u), p.src + off, v ? 16u : 0u);
+              cp_async_16(dst0 + (uint32_t)i * (16u * 128u), p.src + off, v ? 16u : 0u);
             }
             cp_async_commit();
             if (it >= PLAG) {
-              cp_async_wait<PLAG>();
+              cp_async_wait_lag(PLAG);
               fence_proxy_async_smem();
-              mbar_arrive(smem_u32(&full[(it - PLAG) % NS]));
+              stage_done(it - PLAG);
             }
             c0 += BK;
             if (c0 == g.src_c) {
@@ -808,8 +717,8 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           }
         }
       }
-      for (int t = blockIdx.x; !fast && t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / p.n_tiles) * BM;
+      for (int t = unit; !fast && t < total_tiles && ok; t += nunits) {
+        const int m0 = ((t / p.n_tiles) * NCTA + (int)rank) * BM;
         int pixb[8], ih0[8], iw0[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -828,7 +737,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % NS;
           const uint32_t ph = (uint32_t)(it / NS) & 1u;
-          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY))) { ok = false; break; }
           const int kk = kb * BK + j * 8;
           const bool k_ok = kk < g.Kg;
           const int tap = kk / g.src_c, c = kk - tap * g.src_c;
@@ -855,29 +764,35 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
             }
             v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
             const bf16* ptr = v ? p.src + ((size_t)(pixb[i] + ih * g.src_w + iw) * g.src_c + c) : p.src;
-            if (!(p.no_load & 1)) cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
+            cp_async_16(dst0 + (uint32_t)i * (16u * 128u), ptr, v ? 16u : 0u);
           }
           cp_async_commit();
           if (it >= PLAG) {
-            cp_async_wait<PLAG>();
+            cp_async_wait_lag(PLAG);
             fence_proxy_async_smem();
-            mbar_arrive(smem_u32(&full[(it - PLAG) % NS]));
+            stage_done(it - PLAG);
           }
         }
       }
       // drain: every stage issued but not yet handed over
       cp_async_wait<0>();
       fence_proxy_async_smem();
-      for (int k = it > PLAG ? it - PLAG : 0; k < it; ++k) mbar_arrive(smem_u32(&full[k % NS]));
+      for (int k = it > PLAG ? it - PLAG : 0; k < it; ++k) stage_done(k);
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (tid == 0) SRT_STAMP(8);
+  // Neither CTA of a pair may retire while the other can still signal its barriers or have its shared and
+  // tensor memory read by an MMA in flight.
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
+    if (lane == 0) SRT_STAMP(9);
   }
 }
 
@@ -1074,21 +989,6 @@ int* status_ptr() {
 }
 
 template <int BN, int NS>
-int launch_fwd(const FwdParams& p, const CUtensorMap& tb, const CUtensorMap& ta, cudaStream_t st) {
-  constexpr size_t smem = smem_bytes<NS, BN * BK * 2>();
-  static bool configured = false;
-  if (!configured) {
-    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_fwd_kernel<BN, NS>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
-  dim3 grid(ceil_div(p.g.M, BM), ceil_div(p.g.Nout, BN));
-  launch_pdl_if(pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0, igemm_fwd_kernel<BN, NS>, dim3(grid), dim3(NTHREADS), smem, st, p, tb, ta);
-  SRT_LAUNCH_CHECK();
-  return SRT_OK;
-}
-
-template <int BN, int NS>
 int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, const CUtensorMap& tx, int splits,
                  cudaStream_t st) {
   constexpr size_t smem = smem_bytes<NS, BN * BK * 2>();
@@ -1104,20 +1004,42 @@ int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, const CUtensorMap
   return SRT_OK;
 }
 
-template <int BN, int NS>
+template <int BN, int NS, bool PAIR>
 int launch_persistent(const PersistParams& p, const CUtensorMap& tb, const CUtensorMap& ta,
                       const CUtensorMap& td, cudaStream_t st) {
-  constexpr size_t smem = persist_smem_bytes<BN, NS>();
+  constexpr size_t smem = persist_smem_bytes<BN, NS, PAIR>();
   static_assert(smem <= 232448, "persistent igemm: shared memory budget exceeded");
   static bool configured = false;
   if (!configured) {
-    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_fwd_persistent<BN, NS>,
+    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_fwd_persistent<BN, NS, PAIR>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  launch_pdl_if(pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0, igemm_fwd_persistent<BN, NS>, dim3(grid), dim3(P_THREADS), smem, st, p, tb, ta, td);
+  const bool early = pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(P_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = early ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (PAIR) {
+    // one unit = two CTAs on the two SMs of a TPC, working on a 256-row tile
+    const int units = ceil_div(p.m_tiles, 2) * p.n_tiles;
+    const int room = sm_count() / 2;
+    cfg.gridDim = dim3(2 * (units < room ? units : room));
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  } else {
+    const int tiles = p.m_tiles * p.n_tiles;
+    cfg.gridDim = dim3(tiles < sm_count() ? tiles : sm_count());
+  }
+  cudaLaunchKernelEx(&cfg, igemm_fwd_persistent<BN, NS, PAIR>, p, tb, ta, td);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -1228,6 +1150,14 @@ int bgemm_bf16(const BgemmDesc& d, const void* A, const void* B, void* D, cudaSt
 }
 
 
+#ifdef SRT_PHASE_STAMPS
+extern "C" int srt_dbg_set_phase_stamps(void* device_buffer) {
+  unsigned long long* p = (unsigned long long*)device_buffer;
+  SRT_CHECK_CUDA(cudaMemcpyToSymbol(g_phase_stamps, &p, sizeof(p)));
+  return SRT_OK;
+}
+#endif
+
 void bn_grid_reset_barriers();  // norm_grid.cu
 int* tc_status_device_ptr() { return status_ptr(); }
 
@@ -1245,12 +1175,18 @@ int tc_status_fetch(int* out) {
   return SRT_OK;
 }
 
-void tc_set_force_gather(int v) { g_force_gather = v; }
-static int g_fwd_variant = 0;   // 0: persistent kernel, 1: one tile per CTA (kept for comparison)
-static int g_force_bn = 0;      // 0: heuristic, else 64/128/256
-static int g_no_load = getenv("SIRIUS_B200_DEBUG_NO_LOAD") ? atoi(getenv("SIRIUS_B200_DEBUG_NO_LOAD")) : 0;  // timing experiments, see PersistParams::no_load
-void tc_set_no_load(int v) { g_no_load = v; }
-void tc_set_fwd_variant(int variant, int bn) { g_fwd_variant = variant; g_force_bn = bn; }
+// Plan override of the fprop/dgrad kernel (a tuning and test aid; 0 / 0 / -1 restores the heuristics):
+//   gather  1: fetch plain-matrix (1x1, stride 1) operands with the gather threads instead of TMA
+//   tile_n  64, 128 or 256: output-tile width
+//   pair    0: one CTA per tile, 1: CTA pairs wherever the shape allows, -1: heuristic
+static int g_force_bn = 0;
+static int g_gather_lag = getenv("SIRIUS_B200_GATHER_LAG") ? atoi(getenv("SIRIUS_B200_GATHER_LAG")) : 0;  // 0 = stage count - 2
+static int g_force_pair = getenv("SIRIUS_B200_CONV_PAIR") ? atoi(getenv("SIRIUS_B200_CONV_PAIR")) : -1;
+void tc_set_conv_plan(int gather, int tile_n, int pair) {
+  g_force_gather = gather;
+  g_force_bn = tile_n;
+  g_force_pair = pair;
+}
 
 static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, const void* Bm, void* D,
                                           const srt_conv_epilogue* ep, cudaStream_t st, double* col_partial = nullptr) {
@@ -1261,16 +1197,28 @@ static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, 
   p.bias = ep ? ep->bias : nullptr;
   p.addend = ep ? (const bf16*)ep->addend : nullptr;
   p.k_blocks = ceil_div(g.Kg, BK);
-  p.no_load = g_no_load;
   p.status = status_ptr();
   SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
   const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
   p.a_tma = (plain && !g_force_gather) ? 1 : 0;
-  const int bn = pick_bn(g.M, g.Nout, g_force_bn);
+  p.gather_lag = 0;  // set with the stage count below
+  // CTA pairs: the unit is a 256 x tile_n tile of which each CTA stages half the filters, so the operand stream
+  // per SM shrinks by a quarter to a third. Measured on the ResNet shapes (16-36 k-blocks per tile) that gain is
+  // eaten by the pair's cross-SM signalling (+-5 %); on long reductions it is 13 % (64 k-blocks: 47.3 -> 41.3 us).
+  // The heuristic therefore pairs plain-matrix (TMA-fed) problems from 32 k-blocks up whose output is at least
+  // 128 columns wide (a 64-column tile would leave each CTA 32 filters per k-block): the MLP down-projections and
+  // the data gradients of the wide layers of the transformer steps.
+  bool pair = p.a_tma && p.k_blocks >= 32 && g.Nout >= 128 && g_force_bn != 64;
+  if (g_force_pair == 0) pair = false;
+  if (g_force_pair == 1) pair = g.Nout > 64 && g_force_bn != 64;
+  if (sm_count() < 2) pair = false;
+  int bn;
+  if (pair) bn = g_force_bn ? g_force_bn : (g.Nout > 128 ? 256 : 128);
+  else bn = pick_bn(g.M, g.Nout, g_force_bn);
   p.m_tiles = ceil_div(g.M, BM);
   p.n_tiles = ceil_div(g.Nout, bn);
   CUtensorMap tb, ta, td;
-  int rc = make_tmap_2d(&tb, Bm, (uint64_t)g.Nout, (uint64_t)g.Kg, (uint32_t)bn);
+  int rc = make_tmap_2d(&tb, Bm, (uint64_t)g.Nout, (uint64_t)g.Kg, (uint32_t)(pair ? bn / 2 : bn));
   if (rc != SRT_OK) return rc;
   if (p.a_tma) {
     rc = make_tmap_2d(&ta, src, (uint64_t)g.M, (uint64_t)g.Kg, (uint32_t)BM);
@@ -1280,9 +1228,21 @@ static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, 
   }
   rc = make_tmap_store(&td, D, (uint64_t)g.M, (uint64_t)g.Nout);
   if (rc != SRT_OK) return rc;
-  if (bn == 64) return launch_persistent<64, 6>(p, tb, ta, td, st);
-  if (bn == 128) return launch_persistent<128, 5>(p, tb, ta, td, st);
-  return launch_persistent<256, 4>(p, tb, ta, td, st);
+  auto lag = [&](int ns) {
+    int l = g_gather_lag > 0 ? g_gather_lag : ns - 2;
+    if (l > ns - 2) l = ns - 2;
+    if (l > 4) l = 4;
+    return l < 1 ? 1 : l;
+  };
+  if (pair) {
+    if (bn == 128) { p.gather_lag = lag(6); return launch_persistent<128, 6, true>(p, tb, ta, td, st); }
+    p.gather_lag = lag(5);
+    return launch_persistent<256, 5, true>(p, tb, ta, td, st);
+  }
+  if (bn == 64) { p.gather_lag = lag(6); return launch_persistent<64, 6, false>(p, tb, ta, td, st); }
+  if (bn == 128) { p.gather_lag = lag(5); return launch_persistent<128, 5, false>(p, tb, ta, td, st); }
+  p.gather_lag = lag(3);
+  return launch_persistent<256, 3, false>(p, tb, ta, td, st);
 }
 
 int conv_gather_gemm_tc(const GatherGeom& g, const void* src, const void* Bm, void* D,
@@ -1290,43 +1250,18 @@ int conv_gather_gemm_tc(const GatherGeom& g, const void* src, const void* Bm, vo
   SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
               "tcgen05 conv: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
   SRT_REQUIRE(((uintptr_t)src & 15) == 0 && ((uintptr_t)D & 15) == 0, "tcgen05 conv: unaligned tensor");
-  if (g_fwd_variant == 0) return conv_gather_gemm_tc_persistent(g, src, Bm, D, ep, st);
-  FwdParams p;
-  p.g = g;
-  p.src = (const bf16*)src;
-  p.D = (bf16*)D;
-  p.bias = ep ? ep->bias : nullptr;
-  p.addend = ep ? (const bf16*)ep->addend : nullptr;
-  p.k_blocks = ceil_div(g.Kg, BK);
-  p.status = status_ptr();
-  SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
-  const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-  p.a_tma = (plain && !g_force_gather) ? 1 : 0;
-
-  const int bn = g.Nout <= 64 ? 64 : 128;
-  CUtensorMap tb, ta;
-  int rc = make_tmap_2d(&tb, Bm, (uint64_t)g.Nout, (uint64_t)g.Kg, (uint32_t)bn);
-  if (rc != SRT_OK) return rc;
-  if (p.a_tma) {
-    rc = make_tmap_2d(&ta, src, (uint64_t)g.M, (uint64_t)g.Kg, (uint32_t)BM);
-    if (rc != SRT_OK) return rc;
-  } else {
-    ta = tb;
-  }
-  if (bn == 64) return launch_fwd<64, 4>(p, tb, ta, st);
-  return launch_fwd<128, 3>(p, tb, ta, st);
+  return conv_gather_gemm_tc_persistent(g, src, Bm, D, ep, st);
 }
 
 // Convolution whose epilogue also leaves the per-tile column sums for the BatchNorm that follows
-// (double2 [ceil(M/128)][Nout]: sum, sum of squares). Only the persistent kernel has that epilogue.
-bool conv_col_stats_available() { return g_fwd_variant == 0; }
+// (double2 [ceil(M/128)][Nout]: sum, sum of squares).
+bool conv_col_stats_available() { return true; }
 size_t conv_col_stats_bytes(int64_t M, int Nout) { return (size_t)ceil_div_ll(M, BM) * Nout * 2 * sizeof(double); }
 int conv_gather_gemm_tc_stats(const GatherGeom& g, const void* src, const void* Bm, void* D, const srt_conv_epilogue* ep,
                               double* col_partial, size_t col_partial_bytes, int* slabs, cudaStream_t st) {
   SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
               "tcgen05 conv: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
   SRT_REQUIRE(((uintptr_t)src & 15) == 0 && ((uintptr_t)D & 15) == 0, "tcgen05 conv: unaligned tensor");
-  SRT_REQUIRE(conv_col_stats_available(), "tcgen05 conv: column sums need the persistent kernel");
   SRT_REQUIRE(col_partial && ((uintptr_t)col_partial & 15) == 0 && col_partial_bytes >= conv_col_stats_bytes(g.M, g.Nout),
               "tcgen05 conv: column-sum buffer missing, unaligned or too small (%zu < %zu)", col_partial_bytes,
               conv_col_stats_bytes(g.M, g.Nout));

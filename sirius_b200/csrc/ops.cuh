@@ -145,4 +145,12 @@ int transpose_pad(const void* in, void* out, int R, int C, int64_t ld_in, int64_
 int lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, int ld, float grad_scale, float* row_loss,
                      cudaStream_t st);
 
+
+// Gradient exchange between data-parallel ranks (grad_exchange.cu): one all-reduce per bucket on the
+// communicator's stream, bucket i behind ready[i]; the consumer stream then waits for the whole exchange.
+struct Comm;
+int grad_exchange_begin(Comm* c, float* grad, int nbuckets, const int64_t* offsets, const int64_t* counts,
+                        const cudaEvent_t* ready, int wire_dtype);
+int grad_exchange_wait(Comm* c, cudaStream_t consumer);
+
 }  // namespace srt

@@ -1,6 +1,7 @@
 // Thin inline-PTX wrappers for the sm_100a primitives the tensor-core kernels use: mbarrier,
-// TMA (cp.async.bulk.tensor, no cluster multicast anywhere), cp.async, tcgen05 (tensor memory
-// allocation, MMA, commit, load) and the shared-memory / instruction descriptors of tcgen05.mma.
+// TMA (cp.async.bulk.tensor; every CTA loads its own tiles, no load is multicast), cp.async, tcgen05
+// (tensor memory allocation, MMA, commit, load; the cta_group::2 forms drive the tensor cores of a
+// CTA pair as one 256-row unit) and the shared-memory / instruction descriptors of tcgen05.mma.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -60,6 +61,54 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   return true;
 }
 
+// ---- CTA pairs (clusters of two) ------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Cluster-wide barrier: every thread of every CTA of the cluster arrives, then waits.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// Arrive on an mbarrier that may live in the other CTA of the pair (address from map_to_cta). Default
+// semantics (release at CTA scope): what crosses the pair is the signal only, the data a stage holds is read by
+// the tensor core of the CTA that wrote it. A cluster-scope release here was measured to cost a factor of two on
+// the gathered main loop (it also orders the thread's copies still in flight).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// The same bounded wait with cluster-scope acquire, for barriers the other CTA of a pair arrives on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    __nanosleep(kPollSleepNs);
+    if (clock64() - t0 > kWaitLimitCycles) {
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
 // ---- proxy fences -----------------------------------------------------------------------------
 // Makes generic-proxy shared-memory writes (st.shared, completed cp.async) visible to the async
 // proxy that tcgen05.mma and TMA use.
@@ -78,6 +127,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
       "%4}], [%2];" ::"r"(dst),
       "l"((uint64_t)tmap), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// The same load issued by either CTA of a pair: the data lands in the issuing CTA's shared memory, the
+// transaction bytes are counted on `cluster_bar`, which may be the pair leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t cluster_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4}], [%2];" ::"r"(dst),
+      "l"((uint64_t)tmap), "r"(cluster_bar), "r"(x), "r"(y)
       : "memory");
 }
 
@@ -139,6 +199,19 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
                : "memory");
 }
+// Pair forms: issued by the same warp of both CTAs; the columns are allocated in both tensor memories.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -161,6 +234,28 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
+}
+// Pair MMA, issued by one thread of the leader CTA: D is 256 x N, rows 0-127 accumulate in the leader's
+// tensor memory and rows 128-255 in the peer's; each CTA supplies its 128 rows of A and its half of the
+// N rows of B from the same shared-memory offsets.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in every CTA of `cta_mask` once the pair MMAs this
+// thread issued so far have completed (a barrier signal sent to both CTAs; no data is multicast).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
 }
 // Load 32 consecutive fp32 columns of this thread's TMEM lane (lane = 32*(warp%4) + laneid).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -1011,6 +1011,32 @@ int srt_step_set_param(srt_step* h, int idx, const float* host) {
   return SRT_OK;
 }
 
+int srt_step_set_state(srt_step* h, int idx, const float* host, int which) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && host && idx >= 0 && idx < (int)s->params.size(), "set_state: bad argument");
+  SRT_REQUIRE(which == SRT_GET_VALUE || which == SRT_GET_MOMENTUM || which == SRT_GET_ACCUM,
+              "set_state: only the value, the momentum and the accumulated gradient can be set");
+  const ParamRec& r = s->params[idx];
+  if (which == SRT_GET_VALUE || r.kind == SRT_PARAM_BUFFER) return srt_step_set_param(h, idx, host);
+  float* dst = (which == SRT_GET_MOMENTUM ? s->M : s->ACC) + r.off;
+  SRT_CHECK_CUDA(cudaStreamSynchronize(s->stream));
+  if (r.kind == SRT_PARAM_CONV) {
+    const int K = (int)r.shape[0], C = (int)r.shape[1], R = (int)r.shape[2], S = (int)r.shape[3];
+    std::vector<float> tmp((size_t)K * R * S * r.cpad, 0.f);
+    for (int k = 0; k < K; ++k)
+      for (int c = 0; c < C; ++c)
+        for (int a = 0; a < R; ++a)
+          for (int b = 0; b < S; ++b)
+            tmp[(((size_t)k * R + a) * S + b) * r.cpad + c] = host[(((size_t)k * C + c) * R + a) * S + b];
+    SRT_CHECK_CUDA(cudaMemcpy(dst, tmp.data(), tmp.size() * 4, cudaMemcpyHostToDevice));
+  } else {
+    SRT_CHECK_CUDA(cudaMemcpy(dst, host, r.count * 4, cudaMemcpyHostToDevice));
+  }
+  // a loaded momentum continues a run: the next update is m = mu*m + g, not the first step's m = g
+  if (which == SRT_GET_MOMENTUM && s->opt_steps == 0) s->opt_steps = 1;
+  return SRT_OK;
+}
+
 int srt_step_get_param(srt_step* h, int idx, float* host, int which) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && host && idx >= 0 && idx < (int)s->params.size(), "get_param: bad argument");
@@ -1051,6 +1077,9 @@ void* srt_step_stream(srt_step* h) { return h ? (void*)((Step*)h)->stream : null
 int srt_step_upload_batch(srt_step* h, const float* host_images, const int64_t* host_labels, int B) {
   Step* s = (Step*)h;
   SRT_REQUIRE(s && host_images && host_labels && B > 0 && B <= s->cfg.max_batch, "upload_batch: bad argument");
+  for (int i = 0; i < B; ++i)
+    SRT_REQUIRE(host_labels[i] >= 0 && host_labels[i] < (int64_t)s->cfg.num_classes,
+                "upload_batch: label %lld of sample %d is outside [0, %d)", (long long)host_labels[i], i, s->cfg.num_classes);
   const size_t img = (size_t)B * 3 * s->cfg.image * s->cfg.image * 4;
   const int idx = s->up_next;
   s->up_next ^= 1;
@@ -1232,6 +1261,34 @@ int srt_step_wait_grad_bucket(srt_step* h, int i, void* stream) {
   SRT_REQUIRE(s && i >= 0 && i < (int)s->buckets.size(), "wait_grad_bucket: bad argument");
   SRT_CHECK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, s->buckets[i].ev, 0));
   return SRT_OK;
+}
+
+// accumulated = 0: the gradients of the backward pass just enqueued, bucket by bucket behind their ready events;
+// accumulated = 1: the accumulated-gradient buffer (srt_step_accumulate) as one range behind the executor's stream,
+// which is what ranks exchange when they ran different numbers of micro-batches.
+int srt_step_allreduce_begin(srt_step* h, srt_ddp* c, int accumulated, int wire_dtype) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && c, "step_allreduce_begin: null argument");
+  if (accumulated) {
+    SRT_CHECK_CUDA(cudaEventRecord(s->ev_fork, s->stream));
+    const int64_t off = 0, cnt = (int64_t)s->n_flat;
+    const cudaEvent_t ev = s->ev_fork;
+    return grad_exchange_begin((Comm*)c, s->ACC, 1, &off, &cnt, &ev, wire_dtype);
+  }
+  std::vector<int64_t> off, cnt;
+  std::vector<cudaEvent_t> ev;
+  for (auto& b : s->buckets) {
+    off.push_back((int64_t)b.off);
+    cnt.push_back((int64_t)b.count);
+    ev.push_back(b.ev);
+  }
+  return grad_exchange_begin((Comm*)c, s->G, (int)off.size(), off.data(), cnt.data(), ev.data(), wire_dtype);
+}
+
+int srt_step_allreduce_wait(srt_step* h, srt_ddp* c) {
+  Step* s = (Step*)h;
+  SRT_REQUIRE(s && c, "step_allreduce_wait: null argument");
+  return grad_exchange_wait((Comm*)c, s->stream);
 }
 
 int srt_step_wait_event(srt_step* h, void* event) {

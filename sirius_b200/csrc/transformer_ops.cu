@@ -10,6 +10,8 @@
 
 namespace srt {
 
+int* tc_status_device_ptr();  // igemm_tcgen05.cu: the status word srt_tc_status() reads
+
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -480,7 +482,7 @@ embedding_bwd_tok_kernel(const bf16* __restrict__ dx, const int32_t* __restrict_
 // zero in rows without a target and in the padding columns. One block per row.
 __global__ void __launch_bounds__(NT)
 lm_cross_entropy_kernel(bf16* __restrict__ logits, const int32_t* __restrict__ labels, int V, int ld, float grad_scale,
-                        float* __restrict__ row_loss) {
+                        float* __restrict__ row_loss, int* __restrict__ status) {
   pdl_enter();
   __shared__ float red[WARPS];
   __shared__ float bcast;
@@ -488,9 +490,15 @@ lm_cross_entropy_kernel(bf16* __restrict__ logits, const int32_t* __restrict__ l
   bf16* z = logits + row * ld;
   const int label = labels[row];
   const int nv = ld / 8, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  if (label < 0) {
+  // label < 0 marks a position without a target (the last token of a sequence); a label at or beyond the
+  // vocabulary is a caller error: neither may index the row, both give no loss and no gradient, the second is
+  // reported through the status word.
+  if (label < 0 || label >= V) {
     for (int v = threadIdx.x; v < nv; v += NT) *reinterpret_cast<uint4*>(z + v * 8) = make_uint4(0, 0, 0, 0);
-    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    if (threadIdx.x == 0) {
+      row_loss[row] = 0.f;
+      if (label >= V && status) atomicCAS(status, 0, 0xCE);
+    }
     return;
   }
   float mx = -INFINITY;
@@ -1058,7 +1066,7 @@ int lm_cross_entropy(void* logits, const int32_t* labels, int64_t rows, int V, i
                      cudaStream_t st) {
   SRT_REQUIRE(rows > 0 && ld % 8 == 0 && V <= ld, "lm_cross_entropy: ld (%d) must be a multiple of 8 and >= V", ld);
   launch_pdl(lm_cross_entropy_kernel, dim3((unsigned)rows), dim3(NT), 0, st, (bf16*)logits, labels, V, ld, grad_scale,
-             row_loss);
+             row_loss, tc_status_device_ptr());
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

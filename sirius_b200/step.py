@@ -26,6 +26,7 @@ register({
     "srt_step_param_info": (None, [_vp, _i, C.c_char_p, _i, C.POINTER(_i64), C.POINTER(_i), C.POINTER(_i)]),
     "srt_step_set_param": (None, [_vp, _i, _vp]),
     "srt_step_get_param": (None, [_vp, _i, _vp, _i]),
+    "srt_step_set_state": (None, [_vp, _i, _vp, _i]),
     "srt_step_commit_params": (None, [_vp]),
     "srt_step_stream": (_vp, [_vp]),
     "srt_step_upload_batch": (None, [_vp, _vp, _vp, _i]),
@@ -112,6 +113,16 @@ class ResNetStep:
                 raise ValueError(f"{name}: shape {a.shape} != {info.shape}")
             call("srt_step_set_param", self._h, info.index, a.ctypes.data)
         call("srt_step_commit_params", self._h)
+
+    def load_momentum(self, momentum: dict) -> None:
+        """Momentum buffers of torch.optim.SGD (mapping parameter name -> array, torch layouts), to continue a
+        run from a saved optimizer state."""
+        for name, v in momentum.items():
+            info = self.params[name]
+            a = np.ascontiguousarray(_to_numpy(v), dtype=np.float32)
+            if tuple(a.shape) != info.shape:
+                raise ValueError(f"{name}: shape {a.shape} != {info.shape}")
+            call("srt_step_set_state", self._h, info.index, a.ctypes.data, GET_MOMENTUM)
 
     def get(self, name, which=GET_VALUE) -> np.ndarray:
         info = self.params[name]

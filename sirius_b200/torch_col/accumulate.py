@@ -10,8 +10,15 @@ from collections import defaultdict
 
 
 class GradAccumulator:
-    def __init__(self, model):
+    def __init__(self, model, exchange=None):
+        """exchange: a sirius_b200.ddp.GradExchange for data-parallel training with a step object. The ranks of a
+        job may run different numbers of micro-batches per global batch, so what they exchange is the accumulated
+        gradient, once, right before the update (DDP's no_sync on every micro-batch but the last,
+        pytorch/torch_col/dynamic_batch.py:155-167)."""
         self._step = model if hasattr(model, 'optimizer_step') and hasattr(model, 'accumulate') else None
+        self._exchange = exchange
+        if exchange is not None and self._step is None:
+            raise ValueError("a GradExchange works on a step object; torch modules bring their own all-reduce")
         if self._step is None:
             import torch
             self.param_list = [p for p in model.parameters() if p.requires_grad]
@@ -29,6 +36,8 @@ class GradAccumulator:
 
     def step(self, optimizer=None, scaler=None, do_zero_grad=True):
         if self._step is not None:
+            if self._exchange is not None:
+                self._exchange.allreduce(self._step, accumulated=True)   # sum over ranks, on the library's NCCL stream
             return self._step.optimizer_step()  # uses and then clears the accumulated gradient
         for p in self.param_list:
             self.param_grads[p]['local'] = p.grad

@@ -13,7 +13,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import swin_oracle as O  # noqa: E402
-from oracle.resnet_oracle import summarize  # noqa: E402
+from oracle.digest import digest  # noqa: E402
 
 CASES = {
     # name: (config, batch, steps)
@@ -30,10 +30,12 @@ def run(name):
     batches = O.make_batches(batch, steps, cfg["image"], cfg["num_classes"], seed=0)
     loss0, grads = O.first_step_gradients(model, batches[0])
     losses, final = O.train_steps(model, batches)
+    init = O.state_arrays(model)
     doc = {"case": name, "config": {k: list(v) if isinstance(v, tuple) else v for k, v in cfg.items()}, "batch": batch,
            "steps": steps, "seed": 0, "torch": torch.__version__,
            "optimizer": {"kind": "AdamW", "lr": 1e-3, "betas": [0.9, 0.999], "eps": 1e-8, "weight_decay": 0.01},
-           "fp32": {"loss0": loss0, "losses": losses, "grad0": summarize(grads, samples=4), "final": summarize(final, samples=4)}}
+           "fp32": {"loss0": loss0, "losses": losses, "grad0": digest(grads), "final": digest(final),
+                    "delta": digest({k: final[k] - init[k] for k in final})}}
     with open(os.path.join(HERE, name + ".json"), "w") as f:
         json.dump(doc, f)
     print(name, "losses", losses)

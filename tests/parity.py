@@ -64,3 +64,63 @@ def check_digest(get_ours, dig32: dict, dig64: dict, factor=3.0, floor=1e-4, wha
           f"{rms(n_r):.3e}; sampled entries ours {rms(s_o):.3e} / reference {rms(s_r):.3e}")
     assert rms(n_o) <= factor * rms(n_r) + floor, what
     assert rms(s_o) <= factor * rms(s_r) + floor, what
+
+
+# ---- committed digests of full-size runs (oracle/digest.py) -------------------------------------------------
+def check_gradient_digests(get_grad, dig: dict, tol=5e-2, what=""):
+    """First-step gradients against the oracle's digests, per tensor: the relative L2 distance estimated from the
+    +-1 sketch, and the root-mean-square deviation of the fixed entries relative to the tensor's rms entry, must
+    both stay within `tol` times 1.6 (the sketch estimate of a distance has a relative standard error of 18 %,
+    the 32-entry one of 13 %; 1.6 is three of the former). Tensors whose gradient is zero up to rounding (a bias
+    softmax cannot see, and the like: norm below 1e-3 of the largest) are skipped. Unlike a norm, both
+    quantities are sensitive to direction: a sign error reads 2, an unrelated tensor 1.4."""
+    from oracle.digest import sample_distance, sketch_distance
+    top = max(d["l2"] for d in dig.values())
+    worst = (0.0, None, None)
+    for n, d in dig.items():
+        if d["l2"] < 1e-3 * top:
+            continue
+        g = get_grad(n)
+        l2 = float(np.sqrt((np.asarray(g, np.float64) ** 2).sum()))
+        assert abs(l2 - d["l2"]) < tol * d["l2"], (what, n, "norm", l2, d["l2"])
+        ds, de = sketch_distance(g, d), sample_distance(g, d)
+        worst = max(worst, (ds, n, "sketch"), (de, n, "entries"))
+        assert ds < 1.6 * tol, (what, n, "sketch distance", ds)
+        assert de < 1.6 * tol, (what, n, "sampled entries", de)
+    print(f"{what}: worst relative distance to the oracle's gradient digests {worst}")
+
+
+def check_update_digests(get_param, init: dict, dig_delta: dict, dig_final: dict, lr, steps, what=""):
+    """The update p_final - p_init after `steps` AdamW steps against the oracle's.
+
+    AdamW's first steps move every entry by about lr * sign(gradient), so where rounding makes a small gradient
+    entry change sign the update differs by 2 lr however good the arithmetic is; with gradient errors of a few
+    percent that is a few percent of the entries and a relative L2 distance of 0.2-0.35 between two correct
+    runs (measured between the oracle's fp32 and bf16-autocast runs of the small configurations), while a wrong
+    gradient direction gives 1.4 and a sign error 2. Weight tensors (two or more dimensions in the model, i.e.
+    not a bias or a norm scale) therefore must stay below 0.3 in estimated relative L2 distance (measured on a
+    B200: 0.06 on the small configurations, 0.09 on GPT-2 small at 8 x 1024) and within 10 %
+    in norm; every tensor's final value must match the oracle's in norm (2e-2 plus the drift bound
+    2 * lr * steps * sqrt(n) for the vectors) and no sampled entry may be farther than 2 * lr * steps from the
+    oracle's beyond 2e-2 of its size."""
+    from oracle.digest import sketch_distance
+    worst = (0.0, None)
+    for n, d in dig_delta.items():
+        p = np.asarray(get_param(n), np.float64)
+        delta = p - np.asarray(init[n], np.float64)
+        is_matrix = np.asarray(init[n]).ndim >= 2
+        if is_matrix and d["l2"] > 0:
+            dist = sketch_distance(delta, d)
+            worst = max(worst, (dist, n))
+            assert dist < 0.3, (what, n, "update direction", dist)
+            l2 = float(np.sqrt((delta ** 2).sum()))
+            assert abs(l2 - d["l2"]) < 0.1 * d["l2"], (what, n, "update norm", l2, d["l2"])
+        f = dig_final[n]
+        flat = p.ravel()
+        l2 = float(np.sqrt((flat ** 2).sum()))
+        drift = 0.0 if is_matrix else 2 * lr * steps * np.sqrt(flat.size)
+        assert abs(l2 - f["l2"]) <= 2e-2 * f["l2"] + drift, (what, n, "final norm", l2, f["l2"])
+        got = flat[np.asarray(f["idx"], dtype=np.int64)]
+        lim = 2e-2 * np.abs(np.asarray(f["val"])) + 2 * lr * steps * 1.01
+        assert np.all(np.abs(got - np.asarray(f["val"])) <= lim), (what, n, "final entries")
+    print(f"{what}: worst estimated relative distance of a weight update to the oracle's {worst}")

@@ -36,7 +36,7 @@ def test_library_exports_every_declared_function():
 
 
 def test_every_declared_function_has_a_python_signature():
-    from sirius_b200 import _lib, _runtime, bert_infer, gpt2_step, ops, pool, qwen2_step, step, swin_step  # noqa: F401  (each registers its signatures)
+    from sirius_b200 import _lib, _runtime, bert_infer, ddp, gpt2_step, ops, pool, qwen2_step, step, swin_step  # noqa: F401  (each registers its signatures)
     bound = set(_lib.declared_symbols())
     unbound = sorted(set(header_functions()) - bound)
     assert not unbound, unbound
@@ -66,3 +66,18 @@ def test_conv_bn_stats_sizing_and_support_are_host_side():
         assert lib.srt_conv_fprop_bn_stats_supported(C.byref(d), SRT_BF16, IMPL_SIMT) == 0
         assert lib.srt_conv_fprop_bn_stats_supported(C.byref(d), SRT_F32, IMPL_AUTO) == 0
     assert lib.srt_conv_fprop_bn_stats_bytes(None) == 0
+
+
+def test_gradient_exchange_entry_points_fail_cleanly_without_a_communicator():
+    """The NCCL-backed exchange is resolved at run time: loading the library needs neither NCCL nor a GPU, and
+    calls with a missing communicator or arguments return an error status with a message instead of crashing."""
+    from sirius_b200 import _lib, ddp
+    lib = _lib.lib()
+    assert lib.srt_ddp_available() in (0, 1)
+    off, cnt = (C.c_int64 * 1)(0), (C.c_int64 * 1)(8)
+    assert lib.srt_allreduce_begin(None, None, 1, off, cnt, None, _lib.SRT_F32) != 0
+    assert b"allreduce_begin" in lib.srt_last_error()
+    assert lib.srt_allreduce_wait(None, None) != 0
+    assert lib.srt_ddp_allreduce(None, None, 0, _lib.SRT_F32, None) != 0
+    assert lib.srt_ddp_destroy(None) == 0
+    assert ddp.WIRE["bf16"] == _lib.SRT_BF16

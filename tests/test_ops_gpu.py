@@ -95,34 +95,59 @@ def test_conv_bf16_simt(case):
     _run_bf16(case, IMPL_SIMT)
 
 
-# fprop/dgrad kernel variants: persistent CTA per SM (default) with the tile width chosen by the
-# heuristic or forced, and the one-tile-per-CTA kernel
-VARIANTS = {"persistent": (0, 0), "persistent_bn64": (0, 64), "persistent_bn128": (0, 128),
-            "persistent_bn256": (0, 256), "tile_per_cta": (1, 0)}
+# fprop/dgrad kernel plans (gather, tile width, CTA pair): the heuristic, every forced tile width with one CTA
+# per 128-row tile, and two CTAs per 256-row tile (tcgen05 cta_group::2) with each of its tile widths
+PLANS = {"auto": (0, 0, -1), "single_bn64": (0, 64, 0), "single_bn128": (0, 128, 0), "single_bn256": (0, 256, 0),
+         "pair_bn128": (0, 128, 1), "pair_bn256": (0, 256, 1)}
 
 
-@pytest.mark.parametrize("variant", list(VARIANTS), ids=list(VARIANTS))
-@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
-def test_conv_bf16_tcgen05(case, variant):
-    lib().srt_debug_fwd_variant(*VARIANTS[variant])
+def _with_plan(plan, fn):
+    lib().srt_conv_plan_override(*plan)
     try:
-        _run_bf16(case, IMPL_TCGEN05)
+        return fn()
     finally:
-        lib().srt_debug_fwd_variant(0, 0)
+        lib().srt_conv_plan_override(0, 0, -1)
+
+
+@pytest.mark.parametrize("plan", list(PLANS), ids=list(PLANS))
+@pytest.mark.parametrize("case", CONV_CASES, ids=IDS)
+def test_conv_bf16_tcgen05(case, plan):
+    _with_plan(PLANS[plan], lambda: _run_bf16(case, IMPL_TCGEN05))
 
 
 def test_conv_tcgen05_many_tiles_per_cta():
     """More tiles than SMs with a short reduction: the persistent kernel's stage ring and the two
-    accumulator buffers wrap many times per CTA."""
-    case = ("many_tiles", 40, 28, 28, 64, 128, 1, 1, 1, 0)  # M = 31360 -> 245 row tiles
-    for bn in (64, 128):
-        lib().srt_debug_fwd_variant(0, bn)
-        try:
-            _run_bf16(case, IMPL_TCGEN05)
-        finally:
-            lib().srt_debug_fwd_variant(0, 0)
+    accumulator buffers wrap many times per CTA (and per CTA pair)."""
+    case = ("many_tiles", 40, 28, 28, 64, 128, 1, 1, 1, 0)  # M = 31360 -> 245 row tiles (odd: a pair's last half is empty)
+    for plan in ((0, 64, 0), (0, 128, 0), (0, 128, 1)):
+        _with_plan(plan, lambda: _run_bf16(case, IMPL_TCGEN05))
+    case = ("many_tiles_wide", 40, 28, 28, 64, 512, 1, 1, 1, 0)  # two 256-wide tiles per row tile
+    for plan in ((0, 256, 0), (0, 256, 1)):
+        _with_plan(plan, lambda: _run_bf16(case, IMPL_TCGEN05))
     case = ("many_tiles_3x3", 24, 28, 28, 64, 64, 3, 3, 1, 1)  # gathered A, 147 row tiles
     _run_bf16(case, IMPL_TCGEN05)
+    case = ("many_tiles_3x3_pair", 24, 28, 28, 64, 128, 3, 3, 1, 1)  # gathered A through CTA pairs
+    _with_plan((0, 128, 1), lambda: _run_bf16(case, IMPL_TCGEN05))
+
+
+def test_conv_pair_equals_single_bitwise():
+    """Two CTAs per 256-row tile accumulate every output in the same k order as one CTA per 128-row tile:
+    fprop and dgrad of a 1x1 (TMA-fed) and a 3x3 (gathered) problem must agree bit for bit, ragged last tile
+    included."""
+    bf = torch.bfloat16
+    for case in (("p1x1", 9, 14, 14, 256, 320, 1, 1, 1, 0), ("p3x3", 5, 14, 14, 128, 192, 3, 3, 1, 1)):
+        x, w, dy = _mk(case, bf)
+        xd, wd, dyd = x.to(DEV, bf), w.to(DEV, bf), dy.to(DEV, bf)
+        stride, pad = case[8], case[9]
+        wt = ops.filter_transpose(wd)
+        run = lambda: (ops.conv_fprop(xd, wd, stride, pad, impl=IMPL_TCGEN05),
+                       ops.conv_dgrad(dyd, wt, x.shape, stride, pad, impl=IMPL_TCGEN05))
+        single = _with_plan((0, 0, 0), run)
+        pair = _with_plan((0, 0, 1), run)
+        torch.cuda.synchronize()
+        assert ops.tc_status() == 0
+        assert torch.equal(single[0], pair[0]), case[0]
+        assert torch.equal(single[1], pair[1]), case[0]
 
 
 def test_conv_tcgen05_gather_equals_tma():
@@ -134,12 +159,8 @@ def test_conv_tcgen05_gather_equals_tma():
     dyd = dy.to(DEV, bf)
     y_tma = ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05)
     dw_tma = ops.conv_wgrad(dyd, xd, 1, 1, 1, 0, impl=IMPL_TCGEN05)
-    lib().srt_debug_force_gather(1)
-    try:
-        y_g = ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05)
-        dw_g = ops.conv_wgrad(dyd, xd, 1, 1, 1, 0, impl=IMPL_TCGEN05)
-    finally:
-        lib().srt_debug_force_gather(0)
+    y_g, dw_g = _with_plan((1, 0, -1), lambda: (ops.conv_fprop(xd, wd, 1, 0, impl=IMPL_TCGEN05),
+                                                 ops.conv_wgrad(dyd, xd, 1, 1, 1, 0, impl=IMPL_TCGEN05)))
     torch.cuda.synchronize()
     assert ops.tc_status() == 0
     assert torch.equal(y_tma, y_g)

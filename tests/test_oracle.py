@@ -92,3 +92,62 @@ def test_distilbert_oracle_reproduces_the_committed_fixture():
     assert abs(float(np.sqrt((h.astype(np.float64) ** 2).sum())) - d["l2"]) <= 1e-5 * d["l2"]
     assert np.allclose(h.reshape(-1)[d["idx"]], d["val"], rtol=1e-4, atol=1e-5)
     assert np.allclose(h[:, 0, :], np.array(d["first_token"]), rtol=1e-4, atol=1e-5)
+
+
+def test_digest_sketch_measures_distance_and_direction():
+    """The +-1 sketch of oracle/digest.py estimates |a - b| / |b| from 16 numbers per tensor: zero for the same
+    tensor, the noise level for a perturbed one (within the estimator's 18 % standard error, three sigma here),
+    above 1 for an unrelated tensor or a sign error; the sampled entries agree."""
+    from oracle import digest as D
+    rng = np.random.default_rng(1)
+    b = rng.standard_normal(300_000).astype(np.float32)
+    d = D.digest({"t": b})["t"]
+    assert d["n"] == b.size and len(d["proj"]) == D.NPROJ and len(d["idx"]) == D.NSAMPLES
+    assert D.sketch_distance(b, d) == 0.0 and D.sample_distance(b, d) == 0.0
+    for eps in (1e-3, 3e-2, 0.3):
+        a = b + eps * rng.standard_normal(b.size).astype(np.float32)
+        assert 0.45 * eps < D.sketch_distance(a, d) < 1.55 * eps
+        assert 0.5 * eps < D.sample_distance(a, d) < 1.5 * eps
+    assert D.sketch_distance(-b, d) > 1.0
+    assert D.sketch_distance(rng.standard_normal(b.size), d) > 0.7
+    # a permutation keeps the norm and the mean, but not the sketch
+    assert D.sketch_distance(b[::-1].copy(), d) > 0.7
+
+
+def test_gpt2_fixture_digests_are_the_oracles():
+    """The committed GPT-2 fixture's gradient, final-parameter and update digests are reproduced by the oracle in
+    this container (sketch distance and sampled entries at fp32 round-off)."""
+    import json
+    import pathlib
+    from oracle import digest as D
+    from oracle import gpt2_oracle as G
+    doc = json.loads((pathlib.Path(__file__).parent / "golden" / "gpt2_tiny.json").read_text())
+    model = G.build_model(**doc["config"], seed=doc["seed"])
+    batches = G.make_tokens(doc["batch"], doc["seq"], doc["config"]["vocab"], doc["steps"], seed=doc["seed"])
+    _, grads = G.first_step_gradients(model, batches[0])
+    _, final = G.train_steps(model, batches)
+    init = G.state_arrays(model)
+    for k, d in doc["fp32"]["grad0"].items():
+        if d["l2"] > 1e-6:
+            assert D.sketch_distance(grads[k], d) < 1e-3 and D.sample_distance(grads[k], d) < 1e-3, k
+    for k, d in doc["fp32"]["delta"].items():
+        if init[k].ndim >= 2:
+            assert D.sketch_distance(final[k] - init[k], d) < 5e-2, k   # AdamW amplifies round-off where g ~ 0
+
+
+def test_qwen2_oracle_micro_batches_equal_the_whole_batch():
+    """The full-size Qwen2 fixture is generated one sequence at a time (host memory); on the tiny configuration
+    the accumulated gradient and the losses equal those of the whole batch up to fp32 summation order."""
+    import json
+    import pathlib
+    from oracle import qwen2_oracle as Q
+    doc = json.loads((pathlib.Path(__file__).parent / "golden" / "qwen2_tiny.json").read_text())
+    model = Q.build_model(**doc["config"], seed=doc["seed"])
+    ids = Q.make_tokens(doc["batch"], doc["seq"], doc["config"]["vocab"], 1, seed=doc["seed"])[0]
+    l1, g1 = Q.first_step_gradients(model, ids)
+    l2, g2 = Q.first_step_gradients(model, ids, micro_batches=doc["batch"])
+    assert abs(l1 - l2) < 1e-5 * abs(l1) and abs(l1 - doc["fp32"]["loss0"]) < 1e-5 * abs(l1)
+    for k in g1:
+        n = np.linalg.norm(g1[k])
+        if n > 1e-6:
+            assert np.linalg.norm(g1[k] - g2[k]) < 1e-4 * n, k

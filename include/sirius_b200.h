@@ -85,13 +85,18 @@ size_t srt_bn_scratch_bytes(int64_t rows, int C);
  * the input and all outputs. Limits and rules:
  *  - problems with srt_bn_scratch_bytes(rows, C) > SRT_BN_STATIC_SCRATCH_BYTES are rejected with
  *    SRT_ERR_INVALID and a message; use srt_bn_stats for those;
- *  - the first call on each device looks up the array's device address (with that device current);
- *    make that first call before any stream capture is begun;
+ *  - the array's device address is looked up once per device, with that device current: by
+ *    srt_bn_static_prepare(), or else by the first srt_bn_stats_static call on the device. That first look-up
+ *    is also when the CUDA runtime may load the module that holds the array (lazy module loading), so it can
+ *    touch the driver's allocator: call srt_bn_static_prepare() at start-up, on every device to be used and
+ *    before any stream capture is begun, and the later calls touch no allocator at all. Call it again after a
+ *    cudaDeviceReset (an address looked up before the reset is stale);
  *  - all calls share the one array, which keeps whatever the previous call left in it (nothing in
  *    it needs clearing: each call writes every partial before reading it), so two calls whose
  *    kernels can overlap on the GPU (different streams, no ordering) race and must be serialised;
  *  - it calls neither cudaMalloc nor cudaFree nor any allocating library routine. */
 #define SRT_BN_STATIC_SCRATCH_BYTES (4u << 20)
+int srt_bn_static_prepare(void);
 int srt_bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
                         const float* beta, float eps, float momentum, float* running_mean,
                         float* running_var, float* mean, float* invstd, float* scale, float* shift,

@@ -186,7 +186,8 @@ int srt_stub_steps_no_interrupt_end(srt_stub* s);
 int srt_stub_adjust_l1_done(srt_stub* s);
 int srt_stub_adjust_l2_done(srt_stub* s);
 int srt_stub_target_batch_size(srt_stub* s, int unpublished, int* out);
-int srt_stub_set_killed_batch_recover(srt_stub* s);
+int srt_stub_set_killed_batch_recover(srt_stub* s);     /* SetKilledBatchRecover: the next adjust may kill again */
+int srt_stub_set_killed_batch_reconfiged(srt_stub* s);  /* SetKilledBatchReconfiged: redistribution after the kill is done */
 int srt_stub_set_train_first_epoch_done(srt_stub* s);
 int srt_stub_can_exit_after_infer_workload_done(srt_stub* s);
 double srt_stub_passed_ms_from_set_cmd(srt_stub* s);

@@ -97,6 +97,7 @@ register({
     "srt_stub_adjust_l2_done": (None, [_vp]),
     "srt_stub_target_batch_size": (None, [_vp, _i, _pi]),
     "srt_stub_set_killed_batch_recover": (None, [_vp]),
+    "srt_stub_set_killed_batch_reconfiged": (None, [_vp]),
     "srt_stub_set_train_first_epoch_done": (None, [_vp]),
     "srt_stub_can_exit_after_infer_workload_done": (_i, [_vp]),
     "srt_stub_passed_ms_from_set_cmd": (_d, [_vp]),
@@ -105,9 +106,26 @@ register({
     "srt_stub_switch_flag": (None, [_vp, _i, _i, _i, _pi]),
     "srt_stub_adjust_timestamps": (_i, [_vp, _i, C.POINTER(_i64), _i]),
     "srt_pool_create": (None, [C.POINTER(PoolConfig), C.POINTER(_vp)]),
+    "srt_pool_create_shared": (None, [C.POINTER(PoolConfig), C.c_char_p, C.POINTER(_vp)]),
+    "srt_pool_attach": (None, [C.c_char_p, _i, _i, C.POINTER(_vp)]),
     "srt_pool_destroy": (None, [_vp]),
+    "srt_pool_init": (None, [_i, _sz, _i]),
+    "srt_pool_shutdown": (None, [_i]),
+    "srt_pool_default": (None, [_i, C.POINTER(_vp)]),
+    "srt_alloc": (_vp, [_sz, _i, _vp]),
+    "srt_free": (C.c_void_p, [_vp, _sz, _i, _vp]),
+    "srt_record_stream": (None, [_vp, _i, _vp]),
+    "srt_empty_cache": (None, [_i, C.POINTER(_sz)]),
+    "srt_tag_model_begin": (None, []),
+    "srt_tag_model_end": (None, []),
+    "srt_tag_interm": (None, [_vp, _i]),
+    "srt_untag_interm": (None, [_i]),
+    "srt_release_interm": (None, [_i, C.POINTER(_sz)]),
+    "srt_pool_stat_dev": (_i64, [_i, _i]),
+    "srt_alloc_counters": (None, [_i, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "srt_pool_alloc": (None, [_vp, _i, _sz, C.POINTER(_vp)]),
     "srt_pool_free": (None, [_vp, _i, _vp]),
+    "srt_pool_hollow": (None, [_vp, _i, _vp]),
     "srt_pool_empty_cache": (None, [_vp, _i, C.POINTER(_sz)]),
     "srt_pool_stat": (_i64, [_vp, _i]),
     "srt_pool_set_oom_handler": (None, [_vp, _vp, _vp]),

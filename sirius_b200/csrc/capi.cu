@@ -211,6 +211,7 @@ int srt_bn_stats_static(int dtype, const void* z, int64_t rows, int C, const flo
   return bn_stats_static(dtype, z, rows, C, gamma, beta, eps, momentum, running_mean, running_var,
                          mean, invstd, scale, shift, ST(stream));
 }
+int srt_bn_static_prepare(void) { return bn_static_prepare(true, nullptr); }
 int srt_bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
                  const float* scale, const float* shift, int relu, void* stream) {
   SRT_REQUIRE(z && y && scale && shift, "bn_apply: null argument");

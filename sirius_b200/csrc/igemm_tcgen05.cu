@@ -339,7 +339,7 @@ enum WaitCode2 { W_MMA_TMEM_EMPTY = 5 };
 
 template <int BN, int NS, bool PAIR>
 constexpr size_t persist_smem_bytes() {
-  return 1024 + (size_t)NS * (A_STAGE_BYTES + (PAIR ? BN / 2 : BN) * BK * 2) + EPI_GROUPS * OUT_SLAB_BYTES + (2 * NS + 4) * 8 + 16;
+  return 1024 + (size_t)NS * (A_STAGE_BYTES + (PAIR ? BN / 2 : BN) * BK * 2) + EPI_GROUPS * OUT_SLAB_BYTES + (2 * NS + 2 * EPI_GROUPS + 2) * 8 + 16;
 }
 
 // One lane's share of a staged 128 x 64 bf16 slab for the column sums: 32 rows (rp0/rp1 point at the lane's even
@@ -387,8 +387,8 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
   uint8_t* sOut = sB + NS * B_STAGE_BYTES;
   uint64_t* full = (uint64_t*)(sOut + EPI_GROUPS * OUT_SLAB_BYTES);
   uint64_t* empty = full + NS;
-  uint64_t* tmem_full = empty + NS;   // [2]
-  uint64_t* tmem_empty = tmem_full + 2;  // [2]
+  uint64_t* acc_ready = empty + NS;      // [EPI_GROUPS][2]: per epilogue group and accumulator buffer, see the MMA branch
+  uint64_t* tmem_empty = acc_ready + 2 * EPI_GROUPS;  // [2]: one per accumulator buffer
   uint32_t* tmem_ptr = (uint32_t*)(tmem_empty + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -411,10 +411,9 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
       mbar_init(smem_u32(&full[s]), full_count);
       mbar_init(smem_u32(&empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&tmem_full[b]), 1);
+    for (int gi = 0; gi < 2 * EPI_GROUPS; ++gi) mbar_init(smem_u32(&acc_ready[gi]), 1);
+    for (int b = 0; b < 2; ++b)
       mbar_init(smem_u32(&tmem_empty[b]), (uint32_t)(NCTA * (NPROD / 32) * (BN / 64)));  // one arrival per warp and slab
-    }
     mbar_fence_init();
   }
   if (warp == 0 && lane == 0) {
@@ -504,8 +503,19 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           if (PAIR) umma_commit_pair(smem_u32(&empty[s]), (uint16_t)3);
           else umma_commit(smem_u32(&empty[s]));
         }
-        if (PAIR) umma_commit_pair(smem_u32(&tmem_full[b]), (uint16_t)3);
-        else umma_commit(smem_u32(&tmem_full[b]));
+        // The tile is announced to the epilogue groups that own one of its slabs, each on its own barrier for
+        // this accumulator buffer. A parity wait cannot tell phase n from phase n + 2, so a waiter must never
+        // fall two completions behind its barrier: with one barrier per buffer polled by every group, a group
+        // that owns no slab of a tile (or is still busy with an earlier one) can; with one barrier per group
+        // across both buffers, the MMA warp can complete tiles t + 1 and t + 2 while the group still works on
+        // tile t. On a barrier of its own per buffer a group sees exactly the tiles it owns there, and the
+        // next completion after one it has not consumed needs that very accumulator handed back first.
+#pragma unroll
+        for (int c = 0; c < BN / 64; ++c) {
+          const uint32_t gbar = smem_u32(&acc_ready[2 * ((tc * (BN / 64) + c) & (EPI_GROUPS - 1)) + b]);
+          if (PAIR) umma_commit_pair(gbar, (uint16_t)3);
+          else umma_commit(gbar);
+        }
         SRT_STAMP(4);  // last write wins: the issue of the last tile's last MMA
       }
     }
@@ -530,21 +540,22 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
     uint8_t* stage = sOut + grp * OUT_SLAB_BYTES;
     const uint32_t bar_id = 1u + (uint32_t)grp;
     int tc = 0;
+    uint32_t owned[2] = {0u, 0u};  // tiles of this group seen so far, per accumulator buffer
     bool ok = true;
     for (int t = unit; t < total_tiles; t += nunits, ++tc) {
+      // the slab of this tile that falls to this group, if any (at most one: a tile has at most EPI_GROUPS slabs)
+      const int c = (grp - tc * NSLAB) & (EPI_GROUPS - 1);
+      if (c >= NSLAB) continue;
       const int m_tile = (t / p.n_tiles) * NCTA + (int)rank;
       const int m0 = m_tile * BM, n0 = (t % p.n_tiles) * BN;
       const int b = tc & 1;
-      // every group passes every tile's barrier, with or without a slab of its own in the tile: a waiter that
-      // skipped a phase could take the completion of an earlier one for the one it waits for
-      if (ok) ok = mbar_wait(smem_u32(&tmem_full[b]), (uint32_t)(tc >> 1) & 1u, p.status, W_EPI_TMEM);
+      if (ok) ok = mbar_wait(smem_u32(&acc_ready[2 * grp + b]), owned[b] & 1u, p.status, W_EPI_TMEM);
+      ++owned[b];
       if (issuer && grp == 0) SRT_STAMP(5);  // last write wins: the last tile's accumulator is complete
       tc_fence_after_sync();
       const int m = m0 + row;
       const bool tile_live = m0 < g.M;  // false only for the second half of a pair's last, odd row tile
-#pragma unroll 1
-      for (int c = 0; c < NSLAB; ++c) {
-        if (((tc * NSLAB + c) & (EPI_GROUPS - 1)) != grp) continue;
+      {
         const int col0 = n0 + c * 64;
         const bool live = tile_live && col0 < g.Nout;  // uniform across the group
         if (live) {
@@ -558,6 +569,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           if (live) {
             tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c * 64 + h * 32), acc);
             tmem_ld_wait();
+            if (issuer && grp == 0) SRT_STAMP(10 + h);
           }
           if (h == 1) {
             // this slab has been read: one arrival per warp and slab hands the accumulator back to the MMA warp
@@ -596,12 +608,15 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           }
         }
         if (live) {
+          if (issuer && grp == 0) SRT_STAMP(12);
           fence_proxy_async_smem();
+          if (issuer && grp == 0) SRT_STAMP(13);
           named_bar_sync(bar_id, NPROD);
           if (issuer) {
             tma_store_2d(&tmap_d, smem_u32(stage), col0, m0);
             bulk_commit_group();
           }
+          if (issuer && grp == 0) SRT_STAMP(14);
           if (p.col_partial != nullptr) {
             // Column sums of the slab as it sits in the staging buffer. Warp w of the group takes columns
             // 16w..16w+15; a lane owns one column pair and a quarter of the rows, picked so that the 32 words
@@ -638,6 +653,7 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
               out[0] = make_double2((double)s0, (double)q0);
               out[1] = make_double2((double)s1, (double)q1);
             }
+            if (issuer && grp == 0) SRT_STAMP(15);
           }
         }
       }

@@ -522,6 +522,24 @@ static __device__ __align__(256) unsigned char g_bn_static_scratch[SRT_BN_STATIC
 static std::mutex g_static_mu;
 static void* g_static_ptr[64] = {nullptr};
 
+// Looks the array's device address up for the current device (again, if asked to: a cudaDeviceReset
+// invalidates an address looked up before it). The first look-up on a device may be the moment the CUDA
+// runtime loads this file's module and backs the array (lazy module loading), so a caller who must not touch
+// the allocator later does it here, at start-up.
+int bn_static_prepare(bool refresh, void** out) {
+  int dev = -1;
+  SRT_CHECK_CUDA(cudaGetDevice(&dev));
+  SRT_REQUIRE(dev >= 0 && dev < 64, "bn_stats_static: unsupported device ordinal %d", dev);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (refresh || g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    SRT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_bn_static_scratch));
+    g_static_ptr[dev] = p;
+  }
+  if (out) *out = g_static_ptr[dev];
+  return SRT_OK;
+}
+
 int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
                     const float* beta, float eps, float momentum, float* rm, float* rv, float* mean,
                     float* invstd, float* scale, float* shift, cudaStream_t st) {
@@ -531,19 +549,8 @@ int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* 
               "bn_stats_static: rows=%lld, C=%d needs %zu bytes of partial sums, the built-in scratch "
               "holds %zu; use srt_bn_stats with caller-provided scratch",
               (long long)rows, C, need, (size_t)SRT_BN_STATIC_SCRATCH_BYTES);
-  int dev = -1;
-  SRT_CHECK_CUDA(cudaGetDevice(&dev));
-  SRT_REQUIRE(dev >= 0 && dev < 64, "bn_stats_static: unsupported device ordinal %d", dev);
   void* ptr = nullptr;
-  {
-    std::lock_guard<std::mutex> lk(g_static_mu);
-    if (g_static_ptr[dev] == nullptr) {
-      void* p = nullptr;
-      SRT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_bn_static_scratch));
-      g_static_ptr[dev] = p;
-    }
-    ptr = g_static_ptr[dev];
-  }
+  if (int rc = bn_static_prepare(false, &ptr)) return rc;
   // Nothing in the array has to start at zero: every slab partial that the finalize kernel reads
   // is written by the partial kernel of the same call first.
   return bn_stats(dtype, z, rows, C, gamma, beta, eps, momentum, rm, rv, mean, invstd, scale, shift,

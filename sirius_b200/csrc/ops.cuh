@@ -18,6 +18,7 @@ int bn_eval_params(const float* gamma, const float* beta, const float* rmean, co
 int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* gamma,
                     const float* beta, float eps, float momentum, float* rm, float* rv, float* mean,
                     float* invstd, float* scale, float* shift, cudaStream_t st);
+int bn_static_prepare(bool refresh, void** out);
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
              const float* scale, const float* shift, int relu, cudaStream_t st);
 int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,

@@ -300,6 +300,15 @@ int srt_stub_set_killed_batch_recover(srt_stub* h) {
   Stub* s = (Stub*)h;
   SRT_REQUIRE(s, "stub: null handle");
   s->has_killed_batch_recover.store(true, std::memory_order_release);
+  return SRT_OK;
+}
+
+// ColocateStub::SetKilledBatchReconfiged (control_stub.h:114-116): rank 0 calls it once the remaining samples of
+// the killed global batch have been redistributed. Until then a kInferExit must not redistribute concurrently
+// (control_stub.cc:544), which is why this flag is separate from the "may be killed again" flag above.
+int srt_stub_set_killed_batch_reconfiged(srt_stub* h) {
+  Stub* s = (Stub*)h;
+  SRT_REQUIRE(s, "stub: null handle");
   s->will_killed_batch_reconfig.store(false, std::memory_order_release);
   return SRT_OK;
 }

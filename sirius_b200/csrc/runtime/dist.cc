@@ -161,6 +161,15 @@ static void distribute_impl(Dist* d, const std::vector<int>& workers, const std:
     shm::Guard g(l->perf_mu);
     for (int i = 0; i < nw; ++i) { perf[i] = perf_get_locked(l, target_bs[i]); sum += perf[i]; }
   }
+  // Fewer samples left than ranks that could take them (the tail of a global batch after aborts): "at least one
+  // each" cannot hold. The first num_unproc ranks get one sample, the others none and leave the distribution.
+  if (num_unproc < nw) {
+    for (int i = 0; i < nw; ++i) {
+      l->unproc_per_train[workers[i]] = i < num_unproc ? 1 : 0;
+      if (i >= num_unproc) l->has_unproc_batches[workers[i]] = 0;
+    }
+    return;
+  }
   int distributed = 0;
   for (int i = 0; i < nw; ++i) {
     const double ratio = sum == 0 ? 1.0 / nw : perf[i] / sum;
@@ -168,9 +177,10 @@ static void distribute_impl(Dist* d, const std::vector<int>& workers, const std:
     l->unproc_per_train[workers[i]] = ns;
     distributed += ns;
   }
+  // round-off: hand the difference out (or take it back, never below one sample) one by one; with
+  // num_unproc >= nw this ends after at most |diff| + nw visits
   int diff = num_unproc - distributed;
-  int guard = 0;
-  for (int i = 0; diff != 0 && guard < 1 << 22; ++i, ++guard) {
+  for (int i = 0, visits = 0; diff != 0 && visits < 4 * (nw + std::abs(num_unproc - distributed)); ++i, ++visits) {
     if (i >= nw) i = 0;
     int& v = l->unproc_per_train[workers[i]];
     if (diff > 0) { v += 1; diff--; }

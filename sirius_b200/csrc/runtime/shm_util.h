@@ -6,6 +6,9 @@
 #include <errno.h>
 #include <fcntl.h>
 #include <pthread.h>
+#include <signal.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <stdint.h>
 #include <string.h>
 #include <sys/mman.h>
@@ -80,7 +83,41 @@ struct SegHeader {
   uint32_t magic;
   uint32_t bytes;
   std::atomic<int> ready;
+  // Who made this incarnation of the segment. A segment outlives a creator that crashed or was killed, and a
+  // process of the next job that opens the name before the new creator has replaced it would map the orphan
+  // (and then run on different barriers and ledgers than its peers). Openers therefore only accept a segment
+  // whose creator is alive: the creator always unlinks and recreates the name when it starts, so an orphan is
+  // by definition one whose creator is gone.
+  int32_t owner_pid;
+  uint64_t owner_start;  // the creator's start time (clock ticks since boot, /proc/<pid>/stat field 22): pids are reused
 };
+
+// Start time of a process in clock ticks since boot, 0 if it cannot be read.
+inline uint64_t process_start_ticks(int pid) {
+  char path[64], buf[1024];
+  snprintf(path, sizeof(path), "/proc/%d/stat", pid);
+  int fd = ::open(path, O_RDONLY | O_CLOEXEC);
+  if (fd < 0) return 0;
+  ssize_t n = ::read(fd, buf, sizeof(buf) - 1);
+  ::close(fd);
+  if (n <= 0) return 0;
+  buf[n] = 0;
+  const char* p = strrchr(buf, ')');  // the command name may contain spaces and parentheses
+  if (!p) return 0;
+  int field = 2;
+  for (++p; *p; ++p) {
+    if (*p != ' ') continue;
+    if (++field == 22) return strtoull(p + 1, nullptr, 10);
+  }
+  return 0;
+}
+
+inline bool owner_alive(const SegHeader& h) {
+  if (h.owner_pid <= 0) return false;
+  if (kill(h.owner_pid, 0) != 0 && errno == ESRCH) return false;
+  const uint64_t st = process_start_ticks(h.owner_pid);
+  return st == 0 || h.owner_start == 0 || st == h.owner_start;  // unreadable /proc: the pid check has to do
+}
 
 // Maps a named segment holding a T (T begins with a SegHeader named `hdr`). The creator
 // zero-fills it and runs init(T*) before publishing; openers wait up to timeout_ms for it.
@@ -104,10 +141,16 @@ class Segment {
     if (p == MAP_FAILED) { *err = std::string("mmap: ") + strerror(errno); return false; }
     ptr_ = static_cast<T*>(p);
     owner_ = true;
-    if (ptr_->hdr.ready.load(std::memory_order_acquire) == 1 && ptr_->hdr.magic == magic) return true;  // reuse
+    if (ptr_->hdr.ready.load(std::memory_order_acquire) == 1 && ptr_->hdr.magic == magic) {  // reuse: now this process vouches for it
+      ptr_->hdr.owner_pid = (int32_t)getpid();
+      ptr_->hdr.owner_start = process_start_ticks((int)getpid());
+      return true;
+    }
     memset(p, 0, sizeof(T));
     ptr_->hdr.magic = magic;
     ptr_->hdr.bytes = (uint32_t)sizeof(T);
+    ptr_->hdr.owner_pid = (int32_t)getpid();
+    ptr_->hdr.owner_start = process_start_ticks((int)getpid());
     init(ptr_);
     ptr_->hdr.ready.store(1, std::memory_order_release);
     return true;
@@ -125,17 +168,28 @@ class Segment {
           ::close(fd);
           if (p == MAP_FAILED) { *err = std::string("mmap: ") + strerror(errno); return false; }
           ptr_ = static_cast<T*>(p);
+          bool orphan = false;
           for (;;) {
             if (ptr_->hdr.ready.load(std::memory_order_acquire) == 1) {
               if (ptr_->hdr.magic != magic || ptr_->hdr.bytes != sizeof(T)) {
                 *err = "segment " + name_ + " has a different layout";
                 return false;
               }
-              return true;
+              if (owner_alive(ptr_->hdr)) return true;
+              orphan = true;  // left by a creator that is gone: wait for this job's creator to replace it
+              break;
             }
             if (expired(dl)) { *err = "segment " + name_ + " never became ready"; return false; }
             usleep(1000);
           }
+          munmap(ptr_, sizeof(T));
+          ptr_ = nullptr;
+          if (orphan && expired(dl)) {
+            *err = "segment " + name_ + " was left by a process that no longer runs, and nobody replaced it";
+            return false;
+          }
+          usleep(2000);
+          continue;
         }
         ::close(fd);
       }

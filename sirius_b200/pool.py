@@ -17,11 +17,25 @@ class PagePool:
     (colserve::sta::CUDAMemPool, common/cuda_allocator.h:61-150)."""
 
     def __init__(self, pool_gb: float, device: int = 0, page_mb: int = 32, host_backend: bool = False,
-                 unmap_on_release: bool = False):
+                 unmap_on_release: bool = False, shared_name: str | None = None):
+        """shared_name: create the pool for other processes to attach to (PagePool.attach), as the reference's
+        inference server does for its trainers."""
         cfg = PoolConfig(device, 1 if host_backend else 0, page_mb << 20, int(pool_gb * (1 << 30)), 0, 0,
                          int(unmap_on_release))
         self._h = C.c_void_p()
-        call("srt_pool_create", C.byref(cfg), C.byref(self._h))
+        if shared_name is None:
+            call("srt_pool_create", C.byref(cfg), C.byref(self._h))
+        else:
+            call("srt_pool_create_shared", C.byref(cfg), shared_name.encode(), C.byref(self._h))
+
+    @classmethod
+    def attach(cls, shared_name: str, device: int = 0, timeout_ms: int = 10000) -> "PagePool":
+        """Open a pool another process created with shared_name: same physical pages, this process's own
+        allocators and virtual ranges."""
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        call("srt_pool_attach", shared_name.encode(), device, timeout_ms, C.byref(self._h))
+        return self
 
     @property
     def handle(self): return self._h

@@ -130,6 +130,18 @@ def test_conv_tcgen05_many_tiles_per_cta():
     _with_plan((0, 128, 1), lambda: _run_bf16(case, IMPL_TCGEN05))
 
 
+@pytest.mark.parametrize("K", [64, 128, 256])
+def test_conv_tcgen05_ten_tiles_per_cta(K):
+    """1568 row tiles over 148 SMs: every CTA walks ten or more tiles, so the epilogue groups fall behind the MMA
+    warp and catch up again, the accumulator buffers and the per-group barriers wrap many times, and a 64-, 128-
+    and 256-column tile deal their slabs to the groups in all three patterns."""
+    case = (f"ten_tiles_k{K}", 64, 56, 56, 64, K, 1, 1, 1, 0)
+    _run_bf16(case, IMPL_TCGEN05)
+    if K > 64:
+        _with_plan((0, 0, 1), lambda: _run_bf16(case, IMPL_TCGEN05))
+        _with_plan((1, 0, -1), lambda: _run_bf16(case, IMPL_TCGEN05))   # the same through the gather path
+
+
 def test_conv_pair_equals_single_bitwise():
     """Two CTAs per 256-row tile accumulate every output in the same k order as one CTA per 128-row tile:
     fprop and dgrad of a 1x1 (TMA-fed) and a 3x3 (gathered) problem must agree bit for bit, ragged last tile

@@ -212,6 +212,52 @@ def test_ledger_two_ranks_split_every_global_batch(policy):
     assert out[0][3] + out[1][3] == 32                                # shares of a global batch add up
 
 
+def _tail_worker(rank, world, dist_name, policy, q):
+    os.environ["SIRIUS_B200_DIST_NAME"] = dist_name
+    TC.torch_col_init(rank, world)
+    D = TC._DynamicBatchDistirbutor
+    TC.dist.init_dynamic_batch_distributor(34, 8, 32, False, policy)     # second global batch: 2 samples for 4 ranks
+    if rank == 0:
+        TC._PerfModel.record_thpt(8, 10.0)
+    TC.dist.wait_barrier()
+    D.next_epoch()
+    mine, shares = [], []
+    for gb in range(2):
+        D.next_global_batch()
+        shares.append(D._info(6, rank))
+        while True:
+            rng, last = D.get_batch(D.query_next_batch_size(8))
+            mine += rng
+            if last:
+                D.vote_finish_last_micro_batch()
+            D.finish_batch(rng, last)
+            if last:
+                break
+    q.put((rank, mine, shares))
+    TC.dist.wait_barrier()
+    TC.torch_col_shutdown()
+
+
+@pytest.mark.parametrize("policy", ["simple", "by_performance"])
+def test_fewer_samples_than_ranks_at_the_tail_of_an_epoch(policy):
+    """34 samples, global batch 32, four ranks: the last global batch has two samples. Two ranks get one each,
+    the other two get none, the shares add up to what the ledger holds (throughput-proportional splitting used to
+    hand every rank at least one sample and over-commit the ledger), and every sample is trained once."""
+    ctx = mp.get_context("spawn")
+    q, nm = ctx.Queue(), _name("tail")
+    ps = [ctx.Process(target=_tail_worker, args=(r, 4, nm, policy, q)) for r in range(4)]
+    for p in ps:
+        p.start()
+    out = sorted(q.get(timeout=90) for _ in range(4))
+    for p in ps:
+        p.join(30)
+        assert p.exitcode == 0
+    assert sum(o[2][0] for o in out) == 32 and sum(o[2][1] for o in out) == 2
+    assert sorted(o[2][1] for o in out) == [0, 0, 1, 1]
+    ranges = sorted(r for o in out for r in o[1] if r[1] > r[0])
+    assert ranges[0][0] == 0 and ranges[-1][1] == 34 and all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+
+
 def test_distribute_batch_matches_reference_for_every_policy():
     rnd = random.Random(2)
     for _ in range(300):
@@ -428,3 +474,59 @@ def test_pool_random_workload_keeps_invariants():
         assert _stat(h, 4) == 64
     finally:
         call("srt_pool_destroy", h)
+
+
+# ---------------------------------------------------------------- orphaned segments
+def _orphan_maker(name):
+    """Rank 0 of an earlier job: creates the segment, then dies without cleaning up."""
+    h = C.c_void_p()
+    call("srt_dist_open", name.encode(), 0, 2, 2000, C.byref(h))
+    os._exit(0)
+
+
+def _late_rank(rank, name, delay, q):
+    import time
+    time.sleep(delay)
+    h = C.c_void_p()
+    t0 = time.time()
+    call("srt_dist_open", name.encode(), rank, 2, 20000, C.byref(h))
+    waited = time.time() - t0
+    call("srt_dist_barrier", h, 20000)                       # both ranks are on the SAME segment: the barrier opens
+    if rank == 1:
+        call("srt_dist_send", h, 0, b"same job", 8)
+    else:
+        buf, n = C.create_string_buffer(64), C.c_int()
+        call("srt_dist_recv", h, 1, buf, 64, 20000, C.byref(n))
+        assert buf.raw[:n.value] == b"same job"
+    call("srt_dist_barrier", h, 20000)
+    q.put((rank, waited))
+    call("srt_dist_close", h)
+
+
+def test_a_rank_that_starts_first_does_not_attach_to_the_segment_of_a_dead_job():
+    """A ready dist_train_sync segment left in /dev/shm by a killed job, and rank 1 of the next job starting
+    before its rank 0: rank 1 must not map the orphan (the two ranks would then wait on different barriers);
+    it waits until this job's rank 0 has replaced the segment."""
+    ctx = mp.get_context("spawn")
+    nm = _name("orphan")
+    maker = ctx.Process(target=_orphan_maker, args=(nm,))
+    maker.start()
+    maker.join(30)
+    assert maker.exitcode == 0 and os.path.exists("/dev/shm/" + nm)     # the orphan is there, ready, and ownerless
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_late_rank, args=(1, nm, 0.0, q)), ctx.Process(target=_late_rank, args=(0, nm, 1.0, q))]
+    for p in ps:
+        p.start()
+    out = dict(q.get(timeout=60) for _ in range(2))
+    for p in ps:
+        p.join(30)
+        assert p.exitcode == 0
+    assert out[1] >= 0.8            # rank 1 waited for rank 0 instead of taking the orphan at once
+    # and with nobody to replace it, opening fails with a message instead of succeeding on the orphan
+    maker = ctx.Process(target=_orphan_maker, args=(nm,))
+    maker.start()
+    maker.join(30)
+    h = C.c_void_p()
+    with pytest.raises(SrtError, match="no longer runs"):
+        call("srt_dist_open", nm.encode(), 1, 2, 300, C.byref(h))
+    os.unlink("/dev/shm/" + nm)

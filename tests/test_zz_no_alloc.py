@@ -61,6 +61,34 @@ def test_static_scratch_matches_caller_scratch_on_consecutive_calls(dtype):
             assert torch.equal(a, b)
 
 
+def test_calls_after_the_prepared_one_leave_free_device_memory_unchanged():
+    """After srt_bn_static_prepare() and one warm call, further calls (here on a non-default stream, back to back,
+    which is how a handover would issue them) change the free device memory by not one byte: neither the entry
+    point nor anything under it allocates."""
+    call("srt_bn_static_prepare")
+    g = torch.Generator().manual_seed(5)
+    Cc, shape = 128, (8, 28, 28, 128)
+    z = (torch.randn(shape, generator=g) * 2).to(DEV, torch.bfloat16)
+    rows = z.numel() // Cc
+    gamma, beta = torch.ones(Cc, device=DEV), torch.zeros(Cc, device=DEV)
+    rm, rv = torch.zeros(Cc, device=DEV), torch.ones(Cc, device=DEV)
+    o = [torch.empty(Cc, dtype=torch.float32, device=DEV) for _ in range(4)]
+    side = torch.cuda.Stream()
+    args = (SRT_BF16, z.data_ptr(), rows, Cc, gamma.data_ptr(), beta.data_ptr(), 1e-5, 0.1, rm.data_ptr(), rv.data_ptr(),
+            *(t.data_ptr() for t in o))
+    call("srt_bn_stats_static", *args, side.cuda_stream)          # warm call
+    torch.cuda.synchronize()
+    first = [t.clone() for t in o]
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(6):                                            # consecutive calls on the same stream: ordered, no race
+        call("srt_bn_stats_static", *args, side.cuda_stream)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    for a, b in zip(first, o):                                    # mean / invstd / scale / shift do not depend on the running stats
+        assert torch.equal(a, b)
+
+
 def test_static_scratch_rejects_oversized_problem():
     # the smallest power-of-two row count of a 32768-channel tensor whose slab partials exceed the 4 MiB
     Cc, rows = 32768, 1024

@@ -156,6 +156,15 @@ int srt_adjuster_infer_require_plan(srt_adjuster* a, int device_id, double requi
 int srt_adjuster_infer_release_plan(srt_adjuster* a, const double* train_avail_mb, const double* free_mb,
                                     const double* reserve_mb, int* plan_bs, int* n);
 
+/* PredictTrainMemUsageMB (train_adjuster.cc:55-83): base + slope * the planned target batch of `device_id`. */
+int srt_adjuster_predict_train_mem_usage_mb(srt_adjuster* a, int device_id, double* mem_mb);
+/* The KV-cache pool's plans (train_adjuster.cc:343-520): the caller derives the memory figures from the page
+ * pool (see srt_kvpool_*). *n = 0 when there is nothing to adjust. */
+int srt_adjuster_llm_require_plan(srt_adjuster* a, int device_id, double required_mem_mb, double train_avail_mem_mb,
+                                  const double* train_avail_mb_minus_reserve, int* plan_bs, int* n);
+int srt_adjuster_llm_release_plan(srt_adjuster* a, const double* train_avail_mb, const double* free_mb, int* plan_bs,
+                                  int* n);
+
 /* ---- ColocateStub: the trainer's control thread (pytorch/torch_col/csrc/control_stub.{h,cc}) ------ */
 typedef struct srt_stub srt_stub;
 struct srt_step;

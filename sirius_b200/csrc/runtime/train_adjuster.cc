@@ -200,4 +200,84 @@ int srt_adjuster_infer_release_plan(srt_adjuster* h, const double* train_avail_m
   return a->publish(plan_bs);
 }
 
+// TrainAdjuster::PredictTrainMemUsageMB (train_adjuster.cc:55-83): what the trainer on `device_id` will use once
+// it runs at the target batch size the server has planned for it.
+int srt_adjuster_predict_train_mem_usage_mb(srt_adjuster* h, int device_id, double* mem_mb) {
+  Adjuster* a = (Adjuster*)h;
+  SRT_REQUIRE(a && mem_mb, "adjuster: null argument");
+  std::lock_guard<std::mutex> lk(a->mu);
+  *mem_mb = 0.0;
+  if (a->cached_world <= 0 || device_id < 0 || device_id >= a->cached_world) return SRT_OK;  // no trainer: no usage
+  int rc = a->ensure_param();
+  if (rc) return rc;
+  const int bs = a->cached_target[device_id];
+  *mem_mb = bs == std::numeric_limits<int>::min() ? 0.0 : a->predict_mem(bs);
+  return SRT_OK;
+}
+
+// TrainAdjuster::GetLLMInferRequireMemAdjustPlan (train_adjuster.cc:436-520): the KV-cache pool needs
+// required_mem_mb more; train_avail_mem_mb is what training could still use afterwards (free pages + its own
+// pages - margin - the requirement), computed by the caller from the pool.
+int srt_adjuster_llm_require_plan(srt_adjuster* h, int device_id, double required_mem_mb, double train_avail_mem_mb,
+                                  const double* avail_minus_reserve, int* plan_bs, int* n) {
+  Adjuster* a = (Adjuster*)h;
+  SRT_REQUIRE(a && plan_bs && n, "adjuster: null argument");
+  std::lock_guard<std::mutex> lk(a->mu);
+  *n = 0;
+  if (a->cached_world <= 0) return SRT_OK;  // no trainer to adjust
+  SRT_REQUIRE(device_id >= 0 && device_id < a->cached_world, "adjuster: bad device %d", device_id);
+  int rc = a->ensure_param();
+  if (rc) return rc;
+  const int world = a->cached_world, cur = a->cached_target[device_id];
+  if (cur <= 0 || required_mem_mb <= 0) return SRT_OK;
+  int init_bs = 0;
+  rc = srt_comm_get_train_field(a->comm, 0, SRT_TI_INIT_BS, &init_bs);
+  if (rc) return rc;
+  const int by_avail = a->predict_target_bs(std::max(train_avail_mem_mb, 0.0), init_bs);
+  const int by_required = cur - a->delta_bs(required_mem_mb);
+  const int target = std::max(0, std::min(by_avail, by_required));
+  for (int r = 0; r < world; ++r)
+    SRT_REQUIRE(a->cached_target[r] == cur, "adjuster: ranks with different target batch sizes are not supported "
+                "by the LLM require plan (as in the reference)");
+  if (target > 0 && a->imbalance(target, avail_minus_reserve))
+    for (int r = 0; r < world; ++r) plan_bs[r] = r == device_id ? target : a->cached_target[r];
+  else
+    for (int r = 0; r < world; ++r) plan_bs[r] = target;
+  *n = world;
+  return a->publish(plan_bs);
+}
+
+// TrainAdjuster::GetLLMInferReleaseMemAdjustPlan (train_adjuster.cc:343-434): the KV-cache pool gave pages back.
+int srt_adjuster_llm_release_plan(srt_adjuster* h, const double* train_avail_mb, const double* free_mb, int* plan_bs,
+                                  int* n) {
+  Adjuster* a = (Adjuster*)h;
+  SRT_REQUIRE(a && train_avail_mb && free_mb && plan_bs && n, "adjuster: null argument");
+  std::lock_guard<std::mutex> lk(a->mu);
+  *n = 0;
+  if (a->cached_world <= 0) return SRT_OK;
+  int rc = a->ensure_param();
+  if (rc) return rc;
+  const int world = a->cached_world;
+  int init_bs = 0;
+  rc = srt_comm_get_train_field(a->comm, 0, SRT_TI_INIT_BS, &init_bs);
+  if (rc) return rc;
+  std::vector<int> target(world);
+  std::vector<double> avail(world);
+  for (int r = 0; r < world; ++r) {
+    const int cur = a->cached_target[r];
+    avail[r] = std::max(train_avail_mb[r], 0.0);
+    const int by_avail = a->predict_target_bs(avail[r], init_bs);
+    const int by_delta = cur + a->delta_bs(std::max(free_mb[r], 0.0));
+    target[r] = std::max(cur, std::min(by_avail, by_delta));
+  }
+  const int mn = *std::min_element(target.begin(), target.end());
+  if (mn <= 0 || !a->imbalance(mn, avail.data())) {
+    for (int r = 0; r < world; ++r) plan_bs[r] = mn;
+  } else {
+    for (int r = 0; r < world; ++r) plan_bs[r] = target[r];
+  }
+  *n = world;
+  return a->publish(plan_bs);
+}
+
 }  // extern "C"

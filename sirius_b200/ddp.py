@@ -12,7 +12,10 @@ The all-reduce is a sum: the loss is scaled by micro_batch / global_batch (Micro
 pytorch/torch_col/dynamic_batch.py:112-120), so the sum over ranks is the global-batch mean."""
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
+import os
+import sys
 from typing import Callable, Optional
 
 from . import _lib
@@ -60,6 +63,20 @@ def _torch_broadcast(payload: Optional[bytes]) -> bytes:
     return box[0]
 
 
+@contextlib.contextmanager
+def _stdout_to_stderr():
+    """Route file descriptor 1 to stderr for the duration (native libraries write there directly)."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    try:
+        os.dup2(2, 1)
+        yield
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 class GradExchange:
     """One NCCL communicator + communication stream owned by the library.
 
@@ -79,7 +96,9 @@ class GradExchange:
             device = torch.cuda.current_device()
         self.device = device
         self._h = _vp()
-        call("srt_ddp_create", self._new_id(), rank, world, device, max_ctas, C.byref(self._h))
+        uid = self._new_id()
+        with _stdout_to_stderr():   # NCCL announces its version on stdout; callers may own that stream (one JSON line)
+            call("srt_ddp_create", uid, rank, world, device, max_ctas, C.byref(self._h))
 
     def _new_id(self) -> bytes:
         buf = None
@@ -122,7 +141,9 @@ class GradExchange:
         call("srt_ddp_abort", self._h)
 
     def restart(self) -> None:
-        call("srt_ddp_restart", self._h, self._new_id())
+        uid = self._new_id()
+        with _stdout_to_stderr():
+            call("srt_ddp_restart", self._h, uid)
 
     @property
     def stream(self) -> int:

@@ -36,7 +36,7 @@ def test_library_exports_every_declared_function():
 
 
 def test_every_declared_function_has_a_python_signature():
-    from sirius_b200 import _lib, _runtime, bert_infer, ddp, gpt2_step, ops, pool, qwen2_step, step, swin_step  # noqa: F401  (each registers its signatures)
+    from sirius_b200 import _lib, _runtime, bert_infer, ddp, gpt2_step, ops, pool, qwen2_step, server, step, swin_step  # noqa: F401  (each registers its signatures)
     bound = set(_lib.declared_symbols())
     unbound = sorted(set(header_functions()) - bound)
     assert not unbound, unbound

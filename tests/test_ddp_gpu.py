@@ -67,9 +67,6 @@ def _exchange_rank(rank, port, q):
             assert float(err) < 2 ** -8, float(err)
         st = ex.stats()
         assert st["exchanges"] == 1 and st["bytes_on_wire"] == n * (4 if wire == "f32" else 2)
-        step.optimizer_step()
-        step.synchronize()
-        out[wire] = float(torch.as_tensor(step.get("layer2.0.conv2.weight")).double().sum())
         # abort and rejoin under a new id (what the reference does after a killed batch left ranks out of step)
         if wire == "f32":
             ex.abort()
@@ -78,6 +75,9 @@ def _exchange_rank(rank, port, q):
             ex.allreduce(step)
             step.synchronize()
             assert torch.equal(grad.cpu(), want)
+        step.optimizer_step()
+        step.synchronize()
+        out[wire] = float(torch.as_tensor(step.get("layer2.0.conv2.weight")).double().sum())
         ex.close()
     assert ops.tc_status() == 0
     q.put((rank, out))

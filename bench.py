@@ -29,6 +29,7 @@ ARCH, BATCH, IMAGE, CLASSES = "resnet152", 64, 224, 1000
 POOL_GB = 12.0            # COLTRAIN_SHARED_TENSOR_POOL_GB default of the reference (config.cc:57-69)
 FLOP_PER_SAMPLE = 68.85e9  # forward + backward, 2 FLOP per MAC (torch.utils.flop_counter on the CPU model)
 METRIC, UNIT = "train samples/s", "samples/s"
+REGIONS = 3               # timed regions per number; the median is reported
 WORKLOAD = "ResNet-152 train step (fwd+bwd+SGD-momentum), bf16, batch 64 per GPU, 3x224x224 N(0,1)"
 
 
@@ -204,15 +205,19 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    # Three timed regions of exactly `steps` steps each; the reported one is the median (a single region of a
+    # few tenths of a second is at the mercy of one slow collective or one host hiccup).
     launches0 = _lib.lib().srt_launch_count()
-    ms = timed(step_resident, args.steps)
-    launches = _lib.lib().srt_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else {}
+    regions = [timed(step_resident, args.steps) for _ in range(REGIONS)]
+    launches = (_lib.lib().srt_launch_count() - launches0) // REGIONS
+    ms = sorted(regions)[REGIONS // 2]
     value = global_bs * args.steps / (ms / 1e3)
 
     step.upload_batch(*host[0])
     step_e2e(0)
-    ms_e2e = timed(step_e2e, args.steps)
+    regions_e2e = [timed(step_e2e, args.steps) for _ in range(REGIONS)]
+    clocks = sampler.stop() if rank == 0 else {}
+    ms_e2e = sorted(regions_e2e)[REGIONS // 2]
     e2e = global_bs * args.steps / (ms_e2e / 1e3)
 
     # ---- per-kernel-family device time (separate profiled pass, not part of `value`) ----
@@ -290,6 +295,8 @@ def run_ours(args):
                 "h2d_bytes_per_step": BATCH * 3 * IMAGE * IMAGE * 4 + BATCH * 8, "d2h_bytes_per_step": 4,
                 "ms_per_step": round(ms_e2e / args.steps, 3)},
         "gpu_launches": int(launches),
+        "timed_regions_ms": {"resident": [round(x, 3) for x in regions], "e2e": [round(x, 3) for x in regions_e2e],
+                             "reported": "median"},
         "clocks": clocks,
         "roofline": roofline,
         "kernel_families": fam,
@@ -297,10 +304,31 @@ def run_ours(args):
         "tc_status": status,
         "handover": handover,
     }
+    if args.other_workloads:
+        # the other configurations the metric is defined on, at the same number of GPUs, a few steps each
+        short = argparse.Namespace(**{**vars(args), "steps": max(3, min(args.steps, 10)), "warmup": 3})
+        wl = {}
+        for name, fn in (("swin_b", lambda: run_swin(short, embedded=True)), ("gpt2", lambda: run_lm(short, "gpt2", embedded=True))):
+            try:
+                wl[name] = fn()
+            except Exception as e:  # noqa: BLE001  (the headline number stands on its own)
+                wl[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        out["workloads"] = wl
     if rank == 0 and world == 1 and args.colocate_seconds > 0:
-        # training next to a stand-in inference worker on the same GPU: request latency, handover latency
-        from sirius_b200 import colocate_bench
-        out["colocated"] = colocate_bench.run(duration_s=args.colocate_seconds)
+        # Training next to an inference server in a second process that owns the page pool and the control channel:
+        # request latency, training throughput, protocol-level handover latency per GiB. "per_request" is the
+        # configuration as stated (every request triggers a memory handover and an SM-mask shrink, continuous
+        # Poisson arrivals); "cold_request" keeps the pages until the server has been idle (the reference server's
+        # own policy) and runs for a shorter window.
+        from sirius_b200 import colocate_proc
+        col = {}
+        for key, policy, secs in (("per_request", "per-request", args.colocate_seconds),
+                                  ("cold_request", "cold-request", max(8.0, args.colocate_seconds / 3))):
+            try:
+                col[key] = colocate_proc.run(duration_s=secs, policy=policy)
+            except Exception as e:  # noqa: BLE001
+                col[key] = {"error": f"{type(e).__name__}: {e}"[:500]}
+        out["colocated"] = col
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(sample_batch=16, steps=1, warmup=1)
     if rank == 0:
@@ -323,7 +351,7 @@ def make_overlapped_allreduce(step, rank, world, local, args):
     return allreduce
 
 
-# ---- second workload: GPT-2 small (BASELINE config 4), selected with --workload gpt2 -----------------
+# ---- second workload: GPT-2 small (batch 8 x 1024 tokens per GPU), selected with --workload gpt2 -----------------
 GPT2 = dict(n_layer=12, n_head=12, d_model=768, vocab=50257, ctx=1024)
 GPT2_BATCH, GPT2_SEQ = 8, 1024
 GPT2_FLOP_PER_TOKEN = 0.854e9  # forward + backward (torch.utils.flop_counter on the CPU model, 2 FLOP per MAC)
@@ -338,7 +366,15 @@ def run_gpt2(args):
     return run_lm(args, "gpt2")
 
 
-def run_lm(args, kind):
+def compact(out):
+    """The figures of a workload that the headline line carries for the other configurations."""
+    return {"metric": out["metric"], "value": out["value"], "unit": out["unit"], "ms_per_step": out["ms_per_step"],
+            "steps": out["steps"], "e2e": out["e2e"]["value"], "model_flops_frac": out["roofline"]["frac"],
+            "workload": out["config"]["workload"], "global_batch": out["config"]["global_batch"],
+            "gpu_launches": out["gpu_launches"], "clocks": out["clocks"], "tc_status": out["tc_status"]}
+
+
+def run_lm(args, kind, embedded=False):
     """Causal-LM training step, bf16, AdamW lr 3e-4; tokens/s. kind: gpt2 (GPT-2 small, 8 x 1024 tokens per GPU) or
     qwen2 (Qwen2-0.5B shape, 4 x 2048 tokens per GPU)."""
     import torch
@@ -362,7 +398,7 @@ def run_lm(args, kind):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not embedded:
         import datetime
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     torch.manual_seed(0)
@@ -453,6 +489,9 @@ def run_lm(args, kind):
                      "traffic": None, "peak_source": f"of {peaks['source']}"},
         "tc_status": ops.tc_status(), "memory_gib": round(step.memory_bytes() / 2 ** 30, 2),
     }
+    if embedded:
+        step.close()
+        return compact(out)
     if rank == 0 and world == 1 and not args.no_cpu_baseline and kind == "gpt2":
         from oracle import gpt2_oracle as GO
         torch.set_num_threads(os.cpu_count() or 1)
@@ -484,12 +523,12 @@ def run_lm(args, kind):
         dist.destroy_process_group()
 
 
-# ---- third workload: Swin-B (BASELINE config 3), selected with --workload swin_b ---------------------
+# ---- third workload: Swin-B (batch 32 per GPU), selected with --workload swin_b ---------------------
 SWIN_BATCH = 32
 SWIN_FLOP_PER_SAMPLE = 92.55e9  # forward + backward (torch.utils.flop_counter on the CPU model)
 
 
-def run_swin(args):
+def run_swin(args, embedded=False):
     """Swin-B training step, bf16, 32 images of 224 x 224 per GPU, AdamW lr 1e-3; samples/s."""
     import torch
     import torch.distributed as dist
@@ -502,7 +541,7 @@ def run_swin(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not embedded:
         import datetime
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     from torchvision.models.swin_transformer import SwinTransformer
@@ -581,6 +620,9 @@ def run_swin(args):
                      "traffic": None, "peak_source": f"of {peaks['source']}"},
         "tc_status": ops.tc_status(), "memory_gib": round(step.memory_bytes() / 2 ** 30, 2),
     }
+    if embedded:
+        step.close()
+        return compact(out)
     if rank == 0:
         print(json.dumps(out), flush=True)
     step.close()
@@ -632,13 +674,15 @@ def main():
     ap.add_argument("--lm-batch", type=int, default=0,
                     help="sequences per GPU for the gpt2 / qwen2 workloads (0 = the configuration's own; smaller for profiling)")
     ap.add_argument("--workload", default="resnet152", choices=["resnet152", "gpt2", "swin_b", "qwen2"],
-                    help="resnet152 is the headline (BASELINE config 2); swin_b, gpt2 and qwen2 report configs 3, 4 and 5")
+                    help="resnet152 (batch 64 per GPU) is the headline; swin_b, gpt2 and qwen2 time the other training workloads of the reference's evaluation")
     ap.add_argument("--wire", default="bf16", choices=["bf16", "f32"],
                     help="gradient format on NVLink for N > 1: bf16 (2 bytes per parameter) or f32")
     ap.add_argument("--nccl-max-ctas", type=int, default=0,
                     help="cap on the CTAs NCCL's kernels occupy beside the training kernels (0 = NCCL's default)")
-    ap.add_argument("--colocate-seconds", type=float, default=8.0,
+    ap.add_argument("--colocate-seconds", type=float, default=30.0,
                     help="length of the colocated training+inference window at N=1 (0 = skip)")
+    ap.add_argument("--no-other-workloads", dest="other_workloads", action="store_false",
+                    help="skip the compact Swin-B and GPT-2 results appended to the headline line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -218,7 +218,9 @@ def run(duration_s=10.0, rate=50.0, idle_ms=500.0, burst_s=1.0, gap_s=1.0, batch
                                 if np.any(ho_gib > 0) else None),
         "worker_phase_ms": {k: {"p50": pct(v, 0.5), "p99": pct(v, 0.99), "max": pct(v, 1.0)} for k, v in phase.items()},
         "trainer_adjust_ms": [[round(x, 2) for x in a[:3]] for a in ctrl.adjust_log][:8],
-        "kill_seen_after_ms": [round((k - s0) * 1e3, 2) for k, s0 in zip(kill_seen, sent_at)][:8],
+        # each kill is paired with the latest adjust sent before it (not every adjust kills a micro-batch)
+        "kill_seen_after_ms": [round((k - max(s0 for s0 in sent_at if s0 <= k)) * 1e3, 2)
+                               for k in kill_seen if any(s0 <= k for s0 in sent_at)][:8],
         "adjust_start_after_ms": [round((a[4] - s0) * 1e3, 2) for a, s0 in zip(ctrl.adjust_log, sent_at)][:8],
         "pool_gib": round(pool.stat("pool_nbytes") / 2 ** 30, 2), "train_activation_gib": round(train_bytes / 2 ** 30, 2),
         "infer_activation_mib": round(infer_bytes / 2 ** 20, 1), "idle_ms": idle_ms,

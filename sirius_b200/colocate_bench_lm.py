@@ -218,7 +218,9 @@ def run(duration_s=10.0, rate=100.0, cv=4.0, idle_ms=500.0, batch=4, seq=2048, i
         "handover_ms_per_gib": (round(float(np.median(ho_ms[ho_gib > 0] / ho_gib[ho_gib > 0])), 3)
                                 if np.any(ho_gib > 0) else None),
         "worker_phase_ms": {k: {"p50": pct(v, 0.5), "p99": pct(v, 0.99), "max": pct(v, 1.0)} for k, v in phase.items()},
-        "kill_seen_after_ms": [round((k - s0) * 1e3, 2) for k, s0 in zip(kill_seen, sent_at)][:8],
+        # each kill is paired with the latest adjust sent before it (not every adjust kills a micro-batch)
+        "kill_seen_after_ms": [round((k - max(s0 for s0 in sent_at if s0 <= k)) * 1e3, 2)
+                               for k in kill_seen if any(s0 <= k for s0 in sent_at)][:8],
         "pool_gib": round(pool.stat("pool_nbytes") / 2 ** 30, 2), "train_pages": int(train_pages),
         "infer_activation_mib": round(infer_bytes / 2 ** 20, 1), "idle_ms": idle_ms,
         "arrivals": f"gamma inter-arrival times, mean rate {rate}/s, CV {cv}, MT19937 seed {seed}",

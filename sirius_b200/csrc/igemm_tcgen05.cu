@@ -1,24 +1,32 @@
 // bf16 implicit-GEMM convolution on the sm_100a tensor cores.
 //
-// Two warp-specialised kernels, both 192 threads per CTA and one 128-row output tile per CTA:
+// Two warp-specialised kernels:
 //
-//   igemm_fwd_kernel   fprop and dgrad.  D[m][n] = sum_k A(m,k) B[n][k]
-//       A: 128 output positions x 64 reduction elements per stage, gathered from the NHWC source
-//          with 16-byte cp.async (zero-fill outside the image) straight into the 128-byte-swizzled
-//          K-major layout tcgen05.mma reads; for 1x1 stride-1 filters the tile is a plain matrix
-//          block and comes by TMA instead.
-//       B: BN filters x 64 reduction elements per stage by TMA (K-major, 128-byte swizzle).
-//   igemm_wgrad_kernel  filter gradient.  dW[k][j] = sum_pix dy[pix][k] X(pix,j)
+//   igemm_fwd_persistent<BN, NS, PAIR>   fprop and dgrad.  D[m][n] = sum_k A(m,k) B[n][k]
+//       Persistent: one CTA (or one CTA pair, cta_group::2) per SM walks output tiles of 128 (256 for a pair)
+//       rows x BN filters; 704 threads.
+//       A: 128 output positions x 64 reduction elements per stage, gathered from the NHWC source with 16-byte
+//          cp.async (zero-fill outside the image) straight into the 128-byte-swizzled K-major layout
+//          tcgen05.mma reads; for 1x1 stride-1 filters the tile is a plain matrix block and comes by TMA.
+//       B: BN filters x 64 reduction elements per stage by TMA (K-major, 128-byte swizzle); in a pair each CTA
+//          loads its half of the filters and the leader's MMA reads both halves.
+//       Warps: 0 TMA producer, 1 MMA issuer (allocates tensor memory), 2-3 and 20-21 gather producers, 4-19
+//       four epilogue groups of four warps (warp w of a group owns TMEM lanes 32w..32w+31). The accumulator is
+//       double-buffered in tensor memory (2 x BN columns) so the epilogue of tile t overlaps the main loop of
+//       tile t+1; 64-column slabs of a tile are dealt round-robin to the epilogue groups, each slab announced
+//       on its own mbarrier per (group, accumulator buffer) so that a waiter never falls two phases behind.
+//       The epilogue converts to bf16, adds bias / residual, optionally accumulates per-channel sums for
+//       BatchNorm, stages the slab in shared memory and stores it with TMA.
+//   igemm_wgrad_kernel                   filter gradient.  dW[k][j] = sum_pix dy[pix][k] X(pix,j)
+//       192 threads, one 128-filter tile per CTA.
 //       A: dy block, 64 pixels x 128 filters per stage by TMA (MN-major, two 64-wide boxes).
 //       B: 64 pixels x BN gathered input channels per stage by cp.async (MN-major).
-//       The pixel range is split across blockIdx.z; partial sums go to scratch and are reduced
-//       in a fixed order afterwards.
+//       The pixel range is split across blockIdx.z; partial sums go to scratch and are reduced in a fixed
+//       order afterwards.
 //
-// Warp roles: warps 0-3 gather during the main loop and then run the epilogue (warp w owns TMEM
-// lanes 32w..32w+31), warp 4 lane 0 issues TMA, warp 5 allocates tensor memory and its lane 0
-// issues tcgen05.mma. A ring of NS shared-memory stages is handed over with mbarriers; the fp32
-// accumulator lives in BN columns of tensor memory. No cluster launch and no multicast: every
-// CTA loads its own tiles. Every wait is bounded and reports through a status word.
+// A ring of NS shared-memory stages is handed over with mbarriers. No load uses cluster multicast: every CTA
+// loads its own tiles (the pair's commit is the only cluster-scope signal). Every wait is bounded and reports
+// through a status word.
 #include <cuda.h>
 
 #include <mutex>

@@ -186,7 +186,7 @@ def test_inference_mode_forward_uses_running_statistics():
 
 
 def test_gpt2_batch_size_adjustment_on_inference_arrival():
-    """BASELINE config 4's control path on a small GPT-2: the trainer runs the torch_col loop on a pool-backed
+    """The GPT-2 colocation workload's control path on a small GPT-2: the trainer runs the torch_col loop on a pool-backed
     Gpt2Step; an L1 adjust that names a smaller batch kills the micro-batch in flight (the control thread raises
     the executor's flag through srt_stub_set_abort_target), the step keeps an activation set for the new batch size
     and hands the other pages back, and training goes on with gradient accumulation so that every global batch still
@@ -261,7 +261,7 @@ def test_gpt2_batch_size_adjustment_on_inference_arrival():
 
 
 def test_lm_colocation_experiment_runs_on_small_models():
-    """The Qwen2 + DistilBERT colocation experiment (BASELINE config 5's shape of work) on small models: requests on
+    """The Qwen2 + DistilBERT colocation experiment (the reference's LLM colocation workload) on small models: requests on
     the gamma trace are served, cold ones trigger a handover that shrinks the training batch, every global batch is
     still trained in full, and training returns to the full batch after the idle give-back."""
     from sirius_b200.colocate_bench_lm import run

@@ -490,7 +490,7 @@ def _late_rank(rank, name, delay, q):
     h = C.c_void_p()
     t0 = time.time()
     call("srt_dist_open", name.encode(), rank, 2, 20000, C.byref(h))
-    waited = time.time() - t0
+    opened = time.time()
     call("srt_dist_barrier", h, 20000)                       # both ranks are on the SAME segment: the barrier opens
     if rank == 1:
         call("srt_dist_send", h, 0, b"same job", 8)
@@ -499,7 +499,7 @@ def _late_rank(rank, name, delay, q):
         call("srt_dist_recv", h, 1, buf, 64, 20000, C.byref(n))
         assert buf.raw[:n.value] == b"same job"
     call("srt_dist_barrier", h, 20000)
-    q.put((rank, waited))
+    q.put((rank, (t0, opened)))
     call("srt_dist_close", h)
 
 
@@ -514,14 +514,15 @@ def test_a_rank_that_starts_first_does_not_attach_to_the_segment_of_a_dead_job()
     maker.join(30)
     assert maker.exitcode == 0 and os.path.exists("/dev/shm/" + nm)     # the orphan is there, ready, and ownerless
     q = ctx.Queue()
-    ps = [ctx.Process(target=_late_rank, args=(1, nm, 0.0, q)), ctx.Process(target=_late_rank, args=(0, nm, 1.0, q))]
+    ps = [ctx.Process(target=_late_rank, args=(1, nm, 0.0, q)), ctx.Process(target=_late_rank, args=(0, nm, 2.0, q))]
     for p in ps:
         p.start()
     out = dict(q.get(timeout=60) for _ in range(2))
     for p in ps:
         p.join(30)
         assert p.exitcode == 0
-    assert out[1] >= 0.8            # rank 1 waited for rank 0 instead of taking the orphan at once
+    # rank 1 waited for rank 0 instead of taking the orphan at once: its open returned after rank 0 had begun its own
+    assert out[1][0] < out[0][0] and out[1][1] >= out[0][0]
     # and with nobody to replace it, opening fails with a message instead of succeeding on the orphan
     maker = ctx.Process(target=_orphan_maker, args=(nm,))
     maker.start()

@@ -133,7 +133,7 @@ def test_bf16_step_tracks_oracle(arch, batch, image):
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_resnet152_c1_against_golden(dtype):
-    """BASELINE config 1: ResNet-152, batch 16, 224x224, 3 SGD steps, against the fixture."""
+    """The reference's CPU-runnable case: ResNet-152, batch 16, 224x224, 3 SGD steps, against the fixture."""
     arch, batch, image, steps = "resnet152", 16, 224, 3
     g = _gold("resnet152_c1")
     step = _new_step(arch, batch, image, dtype)

@@ -91,6 +91,19 @@ int srt_smp_allowed_sm_mask(int infer_required_tpc, int gpu_sm_num, int min_trai
  * The comm handle must outlive the step or be detached first. */
 struct srt_step;
 int srt_step_follow_infer_tpc(struct srt_step* s, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc);
+/* The same hook for the transformer executors, checked between layers (GPT-2, Qwen2) or blocks (Swin): the
+ * executor moves its main stream and the low-priority stream of its weight gradients to the partition that fits.
+ * enable = 0 brings it back to its whole-device streams; enable = 1 with comm == NULL follows the process-wide
+ * allowed-SM mask instead of a board. *_current_sms: width of the partition in use, 0 = whole device. */
+struct srt_gpt2;
+struct srt_qwen2;
+struct srt_swin;
+int srt_gpt2_follow_infer_tpc(struct srt_gpt2* g, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc, int enable);
+int srt_qwen2_follow_infer_tpc(struct srt_qwen2* g, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc, int enable);
+int srt_swin_follow_infer_tpc(struct srt_swin* g, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc, int enable);
+int srt_gpt2_current_sms(struct srt_gpt2* g);
+int srt_qwen2_current_sms(struct srt_qwen2* g);
+int srt_swin_current_sms(struct srt_swin* g);
 
 /* ---- DistTrainSync, DynamicBatchDistirbutor, PerfModel ----------------------------------------
  * (pytorch/torch_col/csrc/dist_train_sync.{h,cc}, dynamic_batch.{h,cc}, perf_model.{h,cc}) */
@@ -146,7 +159,11 @@ int srt_adjuster_create(srt_comm* comm, const srt_adjuster_config* cfg, srt_adju
 int srt_adjuster_destroy(srt_adjuster* a);
 int srt_adjuster_load_train_info(srt_adjuster* a);
 int srt_adjuster_reset_train_info(srt_adjuster* a);
+/* GetModelMemParam (server/train_adjuster.cc:642-698): the reference's hand-fit constants for its PyTorch models. */
 int srt_adjuster_model_mem_param(const char* model_name, double* base_mb, double* slope_mb);
+/* The line measured for this library's executors on a B200; what the adjuster uses when the configuration gives no
+ * slope, unless SIRIUS_B200_ADJUSTER_FIT=reference. */
+int srt_adjuster_model_mem_param_measured(const char* model_name, double* base_mb, double* slope_mb);
 int srt_adjuster_predict_train_mem_mb(srt_adjuster* a, int batch_size, double* mem_mb);
 /* plan_bs[world]: target batch size per rank; *n = 0 when no adjustment is needed. Also writes
  * target_batch_size_unpublished of every rank (UpdateCachedTrainInfoByAdjustPlan).

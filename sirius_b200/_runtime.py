@@ -79,6 +79,7 @@ register({
     "srt_adjuster_load_train_info": (None, [_vp]),
     "srt_adjuster_reset_train_info": (None, [_vp]),
     "srt_adjuster_model_mem_param": (None, [C.c_char_p, _pd, _pd]),
+    "srt_adjuster_model_mem_param_measured": (None, [C.c_char_p, _pd, _pd]),
     "srt_adjuster_predict_train_mem_mb": (None, [_vp, _i, _pd]),
     "srt_adjuster_infer_require_plan": (None, [_vp, _i, _d, _pd, _pi, _pi]),
     "srt_adjuster_infer_release_plan": (None, [_vp, _pd, _pd, _pd, _pi, _pi]),
@@ -143,6 +144,12 @@ register({
     "srt_step_wait_event": (None, [_vp, _vp]),
     "srt_step_current_sms": (None, [_vp, C.POINTER(_i)]),
     "srt_step_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i]),
+    "srt_gpt2_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i, _i]),
+    "srt_qwen2_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i, _i]),
+    "srt_swin_follow_infer_tpc": (None, [_vp, _vp, _i, _i, _i, _i]),
+    "srt_gpt2_current_sms": (_i, [_vp]),
+    "srt_qwen2_current_sms": (_i, [_vp]),
+    "srt_swin_current_sms": (_i, [_vp]),
     "srt_smp_partition_levels": (None, [_i, C.POINTER(_i), _i, C.POINTER(_i)]),
     "srt_smp_partition_stream": (None, [_i, _i, C.POINTER(_vp), C.POINTER(_i)]),
     "srt_debug_smid_probe": (None, [_vp, _vp]),

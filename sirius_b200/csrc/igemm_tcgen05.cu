@@ -90,7 +90,8 @@ struct WgradParams {
   const bf16* x;
   float* out;          // [splits][Kout][J] partials, or dW itself when splits == 1
   int pix_per_split;   // multiple of 64
-  int b_tma;           // 1x1 stride-1 filters: X is a plain [pixels][C] matrix and comes by TMA
+  int b_tma;           // how X arrives: 0 gathered with cp.async, 1 plain [pixels][C] matrix by TMA (1x1 stride-1
+                       // filters), 2 im2col TMA (one 64-pixel x 64-channel block per filter tap and channel chunk)
   uint32_t hw_mul, hw_shr, w_mul, w_shr;  // fast division by out_h*out_w and out_w
   int* status;
 };
@@ -200,25 +201,29 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
     // destination of row r0 in block cj/8; later rows step RSTEP*128 bytes (RSTEP % 8 == 0)
     const uint32_t dst_off = (uint32_t)(cj >> 3) * 8192u + (uint32_t)r0 * 128u +
                              (uint32_t)(((cj & 7) ^ (r0 & 7)) << 4);
+    // This thread's pixels are pbeg + r0, + RSTEP, + 2 RSTEP, ... through all k-blocks (NI * RSTEP = BK): decoded
+    // once, then advanced with carries; the tap's source position follows from (oh, ow) with two multiply-adds.
+    int pix = pbeg + r0;
+    int n = fastdiv(pix, hw, p.hw_mul, p.hw_shr);
+    int oh = fastdiv(pix - n * hw, g.out_w, p.w_mul, p.w_shr), ow = pix - n * hw - oh * g.out_w;
     int issued = 0;
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % NS;
       const uint32_t ph = (uint32_t)(kb / NS) & 1u;
       if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY)) break;
       const uint32_t dst0 = smem_u32(sm.b + s * B_STAGE_BYTES) + dst_off;
-      const int pix0 = pbeg + kb * BK + r0;
 #pragma unroll
       for (int i = 0; i < NI; ++i) {
-        const int pix = pix0 + i * RSTEP;
-        bool v = j_ok && pix < pend;
-        const int n = fastdiv(pix, hw, p.hw_mul, p.hw_shr);
-        const int rem = pix - n * hw;
-        const int oh = fastdiv(rem, g.out_w, p.w_mul, p.w_shr), ow = rem - oh * g.out_w;
         const int ih = oh * g.stride - g.pad + r, iw = ow * g.stride - g.pad + sf;
-        v = v && ih >= 0 && iw >= 0 && ih < g.src_h && iw < g.src_w;
-        const bf16* ptr =
-            v ? p.x + (((size_t)n * g.src_h + ih) * g.src_w + iw) * g.src_c + c : p.x;
-        cp_async_16(dst0 + (uint32_t)i * (uint32_t)(RSTEP * 128), ptr, v ? 16u : 0u);
+        const bool v = j_ok && pix < pend && (unsigned)ih < (unsigned)g.src_h && (unsigned)iw < (unsigned)g.src_w;
+        const int off = v ? ((n * g.src_h + ih) * g.src_w + iw) * g.src_c + c : 0;
+        cp_async_16(dst0 + (uint32_t)i * (uint32_t)(RSTEP * 128), p.x + off, v ? 16u : 0u);
+        pix += RSTEP;
+        ow += RSTEP;
+        while (ow >= g.out_w) {
+          ow -= g.out_w;
+          if (++oh == g.out_h) { oh = 0; ++n; }
+        }
       }
       producer_handover<NS>(kb, sm.full);
       issued = kb + 1;
@@ -250,21 +255,46 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
     }
   } else if (warp == 4) {
     if (lane == 0) {
+      // im2col: 64-column block blk of the tile is one filter tap and one 64-channel chunk of it; blocks at and
+      // beyond the last column are not loaded (their products land in columns the epilogue does not store)
+      int blk_c[BN / 64], blk_live = 0;
+      uint16_t blk_r[BN / 64], blk_s[BN / 64];
+#pragma unroll
+      for (int blk = 0; blk < BN / 64; ++blk) {
+        const int j = j0 + blk * 64;
+        const int tap = j / g.src_c;
+        blk_c[blk] = j - tap * g.src_c;
+        blk_r[blk] = (uint16_t)(tap / g.S);
+        blk_s[blk] = (uint16_t)(tap - (tap / g.S) * g.S);
+        if (j < J) ++blk_live;
+      }
+      const int hw = g.out_h * g.out_w;
+      const uint32_t b_bytes = p.b_tma == 1 ? (uint32_t)B_STAGE_BYTES : p.b_tma == 2 ? (uint32_t)blk_live * 8192u : 0u;
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % NS;
         const uint32_t ph = (uint32_t)(kb / NS) & 1u;
         if (!mbar_wait(smem_u32(&sm.empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
         const uint32_t bar = smem_u32(&sm.full[s]);
-        mbar_arrive_expect_tx(bar, (uint32_t)A_STAGE_BYTES + (p.b_tma ? (uint32_t)B_STAGE_BYTES : 0u));
+        mbar_arrive_expect_tx(bar, (uint32_t)A_STAGE_BYTES + b_bytes);
         const uint32_t dst = smem_u32(sm.a + s * A_STAGE_BYTES);
         const int pix0 = pbeg + kb * BK;
         tma_load_2d(dst, &tmap_dy, bar, ko0, pix0);
         tma_load_2d(dst + 8192u, &tmap_dy, bar, ko0 + 64, pix0);
-        if (p.b_tma) {
-          const uint32_t dstb = smem_u32(sm.b + s * B_STAGE_BYTES);
+        const uint32_t dstb = smem_u32(sm.b + s * B_STAGE_BYTES);
+        if (p.b_tma == 1) {
 #pragma unroll
           for (int blk = 0; blk < BN / 64; ++blk)
             tma_load_2d(dstb + (uint32_t)blk * 8192u, &tmap_x, bar, j0 + blk * 64, pix0);
+        } else if (p.b_tma == 2) {
+          // base pixel of the k-block's first output position; the 64 positions are consecutive base pixels
+          const int n = fastdiv(pix0, hw, p.hw_mul, p.hw_shr);
+          const int rem = pix0 - n * hw;
+          const int oh = fastdiv(rem, g.out_w, p.w_mul, p.w_shr), ow = rem - oh * g.out_w;
+          const int bw = ow * g.stride - g.pad, bh = oh * g.stride - g.pad;
+#pragma unroll
+          for (int blk = 0; blk < BN / 64; ++blk)
+            if (blk < blk_live)
+              tma_load_im2col_4d(dstb + (uint32_t)blk * 8192u, &tmap_x, bar, blk_c[blk], bw, bh, n, blk_s[blk], blk_r[blk]);
         }
       }
     }
@@ -333,7 +363,11 @@ struct PersistParams {
   const float* bias;
   const bf16* addend;
   int k_blocks;
-  int a_tma;
+  int a_tma;             // how the A operand arrives: 0 gathered with cp.async, 1 plain matrix by TMA, 2 im2col TMA
+  int im_lower_w, im_lower_h;  // im2col: base pixel of output position (oh, ow) = (oh, ow) * im_stride + lower
+  int im_stride;
+  int im_cpt;            // im2col: 64-channel chunks per filter tap (k-block kb = tap * im_cpt + chunk)
+  int im_flip;           // im2col: taps run backwards (data gradient)
   int m_tiles, n_tiles;  // 128-row tiles and BN-column tiles of the output
   int gather_lag;        // cp.async groups a gather thread keeps in flight before it hands a stage over (1..NS-2)
   int* status;
@@ -459,20 +493,40 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
       for (int t = unit; t < total_tiles && ok; t += nunits) {
         const int m0 = ((t / p.n_tiles) * NCTA + (int)rank) * BM;
         const int n0 = (t % p.n_tiles) * BN + (int)rank * B_ROWS;
+        // im2col: the tile's 128 output positions are consecutive base pixels from that of row m0 (the walk wraps
+        // rows and images inside the tensor map's bounding box; positions past the last image read as zero). A
+        // half-tile without rows (a pair's odd last tile) loads the first tile's pixels, which nobody stores.
+        int iw0 = 0, ih0 = 0, in0 = 0, tap_r = 0, tap_s = 0, chunk = 0;
+        if (p.a_tma == 2) {
+          const RowCoord rc = decode_row(g, m0 < g.M ? m0 : 0);
+          iw0 = rc.ow * p.im_stride + p.im_lower_w;
+          ih0 = rc.oh * p.im_stride + p.im_lower_h;
+          in0 = rc.n;
+        }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % NS;
           const uint32_t ph = (uint32_t)(it / NS) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) { ok = false; break; }
+          const uint16_t off_w = (uint16_t)(p.im_flip ? g.S - 1 - tap_s : tap_s);
+          const uint16_t off_h = (uint16_t)(p.im_flip ? g.R - 1 - tap_r : tap_r);
           if (PAIR) {
             const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0u);
             if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full[s]), bytes);
             tma_load_2d_pair(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, lbar, kb * BK, n0);
-            if (p.a_tma) tma_load_2d_pair(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, lbar, kb * BK, m0);
+            if (p.a_tma == 1) tma_load_2d_pair(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, lbar, kb * BK, m0);
+            else if (p.a_tma == 2)
+              tma_load_im2col_4d_pair(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, lbar, chunk * BK, iw0, ih0, in0, off_w, off_h);
           } else {
             const uint32_t bar = smem_u32(&full[s]);
             mbar_arrive_expect_tx(bar, bytes);
             tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmap_b, bar, kb * BK, n0);
-            if (p.a_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
+            if (p.a_tma == 1) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, kb * BK, m0);
+            else if (p.a_tma == 2)
+              tma_load_im2col_4d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_a, bar, chunk * BK, iw0, ih0, in0, off_w, off_h);
+          }
+          if (p.a_tma == 2 && ++chunk == p.im_cpt) {
+            chunk = 0;
+            if (++tap_s == g.S) { tap_s = 0; ++tap_r; }
           }
         }
       }
@@ -688,11 +742,13 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           else mbar_arrive(smem_u32(&full[k % NS]));
         }
       };
-      // Channel counts that are multiples of BK (every 3x3 layer of the step) keep a k-block inside one filter tap, and
-      // without a dgrad stride the source pixel of a row is its tap-(0,0) pixel plus a per-k-block offset: one element
-      // offset per row and tile, one per k-block, an add, two unsigned bounds checks and a select per copy, no
-      // division in the loop. Everything else (stem: 8 channels; strided dgrad) takes the general loop below.
-      const bool fast = (g.src_c % BK) == 0 && (!g.dgrad || g.stride == 1);
+      // A thread copies the same 16-byte chunk j of every row, so within a k-block it stays inside one filter tap when
+      // the channel count is a multiple of BK (one tap per k-block) or divides BK (several taps per k-block, one per
+      // chunk: the 8-channel stem). Without a dgrad stride the source pixel of a row is then its tap-(0,0) pixel plus
+      // a per-thread, per-k-block offset: one element offset per row and tile, one per k-block, an add, two unsigned
+      // bounds checks and a select per copy, no division in the loop. Everything else (channel counts like 24, strided
+      // dgrad) takes the general loop below.
+      const bool fast = ((g.src_c % BK) == 0 || (BK % g.src_c) == 0) && (!g.dgrad || g.stride == 1);
       if (fast) {
         const int sgn = g.dgrad ? -1 : 1;
         for (int t = unit; t < total_tiles && ok; t += nunits) {
@@ -712,18 +768,25 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
               rowoff[i] = 0;
             }
           }
-          int r = 0, sf = 0, c0 = 0;  // filter tap and first channel of the k-block
+          // filter tap and first channel of this thread's chunk in the k-block (taps beyond the filter: zero rows of
+          // the padded reduction)
+          int c0 = j * 8, r = 0, sf = 0;
+          while (c0 >= g.src_c) {
+            c0 -= g.src_c;
+            if (++sf == g.S) { sf = 0; ++r; }
+          }
           for (int kb = 0; kb < nkb; ++kb, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             // warp-uniform outcome: the warp leaves the loop together (its lanes meet in stage_done)
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_PROD_EMPTY))) { ok = false; break; }
             const int dr = sgn * r, ds = sgn * sf;
-            const int tapoff = (dr * g.src_w + ds) * g.src_c + c0 + j * 8;
+            const int tapoff = (dr * g.src_w + ds) * g.src_c + c0;
+            const bool tap_ok = r < g.R;
             const uint32_t dst0 = smem_u32(sA + s * A_STAGE_BYTES) + (uint32_t)r0 * 128u + swz;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const bool v = (unsigned)(ih0[i] + dr) < (unsigned)g.src_h && (unsigned)(iw0[i] + ds) < (unsigned)g.src_w;
+              const bool v = tap_ok && (unsigned)(ih0[i] + dr) < (unsigned)g.src_h && (unsigned)(iw0[i] + ds) < (unsigned)g.src_w;
               const int off = v ? rowoff[i] + tapoff : 0;
               cp_async_16(dst0 + (uint32_t)i * (16u * 128u), p.src + off, v ? 16u : 0u);
             }
@@ -734,8 +797,8 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
               stage_done(it - PLAG);
             }
             c0 += BK;
-            if (c0 == g.src_c) {
-              c0 = 0;
+            while (c0 >= g.src_c) {
+              c0 -= g.src_c;
               if (++sf == g.S) { sf = 0; ++r; }
             }
           }
@@ -974,6 +1037,78 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeIm2colFn get_encode_im2col_fn() {
+  static EncodeIm2colFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeIm2colFn)sym;
+  });
+  return fn;
+}
+
+// The corners of the im2col bounding box (the range of base pixels) for a gather geometry: a convolution reads
+// output position o at o * stride - pad + tap, a stride-1 data gradient at o - (R - 1 - pad) + (R - 1 - tap).
+struct Im2colBox {
+  int lower_w, lower_h, upper_w, upper_h, stride;
+};
+inline Im2colBox im2col_box(const GatherGeom& g) {
+  Im2colBox b;
+  if (!g.dgrad) {
+    b.lower_w = -g.pad; b.lower_h = -g.pad;
+    b.upper_w = g.pad - (g.S - 1); b.upper_h = g.pad - (g.R - 1);
+    b.stride = g.stride;
+  } else {
+    b.lower_w = -(g.S - 1 - g.pad); b.lower_h = -(g.R - 1 - g.pad);
+    b.upper_w = -g.pad; b.upper_h = -g.pad;
+    b.stride = 1;
+  }
+  return b;
+}
+// Whether the source of a gather geometry can be fetched by im2col TMA loads of 64-channel chunks: a k-block must
+// not straddle a filter tap, a strided data gradient has holes no box describes, and the corner fields are 8 bits.
+inline bool im2col_ok(const GatherGeom& g) {
+  if (g.src_c % 64 != 0 || (g.dgrad && g.stride != 1) || g.stride > 8) return false;
+  if (g.pad > g.R - 1 || g.pad > g.S - 1 || g.R > 16 || g.S > 16) return false;
+  const Im2colBox b = im2col_box(g);
+  // the bounding box must hold exactly out_w x out_h base pixels per image
+  const int cw = (g.src_w - 1 + b.upper_w - b.lower_w) / b.stride + 1, ch = (g.src_h - 1 + b.upper_h - b.lower_h) / b.stride + 1;
+  return cw == g.out_w && ch == g.out_h && g.src_w + b.upper_w - b.lower_w > 0 && g.src_h + b.upper_h - b.lower_h > 0;
+}
+
+// NHWC bf16 tensor [n][h][w][c] for im2col loads of `pixels` base pixels x 64 channels, 128B swizzle.
+int make_tmap_im2col(CUtensorMap* tm, const void* base, const GatherGeom& g, uint32_t pixels) {
+  EncodeIm2colFn fn = get_encode_im2col_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeIm2col is not available from the CUDA driver");
+    return SRT_ERR_CUDA;
+  }
+  SRT_REQUIRE(((uintptr_t)base & 15) == 0 && g.src_c % 64 == 0, "im2col TMA operand must be 16-byte aligned with 64-channel chunks");
+  const Im2colBox b = im2col_box(g);
+  cuuint64_t dims[4] = {(cuuint64_t)g.src_c, (cuuint64_t)g.src_w, (cuuint64_t)g.src_h, (cuuint64_t)g.n_img};
+  cuuint64_t strides[3] = {(cuuint64_t)g.src_c * 2, (cuuint64_t)g.src_w * g.src_c * 2,
+                           (cuuint64_t)g.src_h * g.src_w * g.src_c * 2};
+  int lower[2] = {b.lower_w, b.lower_h};
+  int upper[2] = {b.upper_w, b.upper_h};
+  cuuint32_t estr[4] = {1, (cuuint32_t)b.stride, (cuuint32_t)b.stride, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, lower, upper, 64,
+                  pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeIm2col failed with CUresult %d", (int)r);
+    return SRT_ERR_CUDA;
+  }
+  return SRT_OK;
+}
+
 // 2-D bf16 row-major matrix [rows][cols] (cols contiguous), box = 64 cols x box_rows, 128B swizzle.
 int make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
@@ -1205,6 +1340,7 @@ int tc_status_fetch(int* out) {
 //   pair    0: one CTA per tile, 1: CTA pairs wherever the shape allows, -1: heuristic
 static int g_force_bn = 0;
 static int g_gather_lag = getenv("SIRIUS_B200_GATHER_LAG") ? atoi(getenv("SIRIUS_B200_GATHER_LAG")) : 0;  // 0 = stage count - 2
+static int g_im2col = getenv("SIRIUS_B200_CONV_IM2COL") ? atoi(getenv("SIRIUS_B200_CONV_IM2COL")) : 1;  // 0: gather filters wider than 1x1
 static int g_force_pair = getenv("SIRIUS_B200_CONV_PAIR") ? atoi(getenv("SIRIUS_B200_CONV_PAIR")) : -1;
 void tc_set_conv_plan(int gather, int tile_n, int pair) {
   g_force_gather = gather;
@@ -1224,7 +1360,15 @@ static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, 
   p.status = status_ptr();
   SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
   const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-  p.a_tma = (plain && !g_force_gather) ? 1 : 0;
+  p.a_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col) ? 2 : 0;
+  p.im_lower_w = p.im_lower_h = p.im_flip = 0;
+  p.im_stride = p.im_cpt = 1;
+  if (p.a_tma == 2) {
+    const Im2colBox b = im2col_box(g);
+    p.im_lower_w = b.lower_w; p.im_lower_h = b.lower_h; p.im_stride = b.stride;
+    p.im_cpt = g.src_c / BK;
+    p.im_flip = g.dgrad;
+  }
   p.gather_lag = 0;  // set with the stage count below
   // CTA pairs: the unit is a 256 x tile_n tile of which each CTA stages half the filters, so the operand stream
   // per SM shrinks by a quarter to a third. Measured on the ResNet shapes (16-36 k-blocks per tile) that gain is
@@ -1244,8 +1388,11 @@ static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, 
   CUtensorMap tb, ta, td;
   int rc = make_tmap_2d(&tb, Bm, (uint64_t)g.Nout, (uint64_t)g.Kg, (uint32_t)(pair ? bn / 2 : bn));
   if (rc != SRT_OK) return rc;
-  if (p.a_tma) {
+  if (p.a_tma == 1) {
     rc = make_tmap_2d(&ta, src, (uint64_t)g.M, (uint64_t)g.Kg, (uint32_t)BM);
+    if (rc != SRT_OK) return rc;
+  } else if (p.a_tma == 2) {
+    rc = make_tmap_im2col(&ta, src, g, (uint32_t)BM);
     if (rc != SRT_OK) return rc;
   } else {
     ta = tb;
@@ -1316,12 +1463,15 @@ int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw,
   fastdiv_make((uint32_t)(g.out_h * g.out_w), &p.hw_mul, &p.hw_shr);
   fastdiv_make((uint32_t)g.out_w, &p.w_mul, &p.w_shr);
   const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-  p.b_tma = (plain && !g_force_gather) ? 1 : 0;
+  p.b_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col) ? 2 : 0;
   CUtensorMap tdy, tx;
   int rc = make_tmap_2d(&tdy, dy, (uint64_t)g.M, (uint64_t)g.Nout, 64);
   if (rc != SRT_OK) return rc;
-  if (p.b_tma) {
+  if (p.b_tma == 1) {
     rc = make_tmap_2d(&tx, x, (uint64_t)g.M, (uint64_t)g.src_c, 64);
+    if (rc != SRT_OK) return rc;
+  } else if (p.b_tma == 2) {
+    rc = make_tmap_im2col(&tx, x, g, 64);
     if (rc != SRT_OK) return rc;
   } else {
     tx = tdy;

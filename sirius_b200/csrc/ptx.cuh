@@ -141,6 +141,29 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
       : "memory");
 }
 
+// 4-D im2col load of an NHWC tensor (tensor map from cuTensorMapEncodeIm2col): `pixels per column` consecutive
+// base pixels starting at (w, h, n), walked w fastest through the map's bounding box with the map's traversal
+// stride, each read at base + (off_w, off_h); 64 channels from c. Pixels outside the tensor read as zero. The
+// rows land 128 bytes apart in the 128-byte-swizzled layout, like a 2-D tiled load of a [pixels][64] block.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tmap, uint32_t bar, int c, int w, int h,
+                                                   int n, uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+      "%5, %6}], [%2], {%7, %8};" ::"r"(dst),
+      "l"((uint64_t)tmap), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
+// The same load issued by either CTA of a pair (see tma_load_2d_pair).
+__device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst, const void* tmap, uint32_t cluster_bar, int c,
+                                                        int w, int h, int n, uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+      "l"((uint64_t)tmap), "r"(cluster_bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
 // 4-D tiled load (innermost coordinate first): used for batched operands, (k, row, batch1, batch2).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1,
                                             int c2, int c3) {

@@ -6,6 +6,7 @@
 // imbalance check (:552-584) and the per-model constants (:642-698, hand-fit on V100/A100; callers
 // on B200 pass their own base/slope, measured with srt_step_memory_bytes).
 #include <math.h>
+#include <stdlib.h>
 
 #include <algorithm>
 #include <limits>
@@ -48,7 +49,10 @@ struct Adjuster {
     int rc = srt_comm_get_train_info(comm, 0, &ti);
     if (rc) return rc;
     SRT_REQUIRE(ti.train_pid != -1, "train adjuster: train info of rank 0 is not valid");
-    rc = srt_adjuster_model_mem_param(ti.model_name, &base, &slope);
+    // the trainer is one of this library's executors unless told otherwise: use the line measured for it
+    const char* fit = getenv("SIRIUS_B200_ADJUSTER_FIT");
+    rc = (fit && std::string(fit) == "reference") ? srt_adjuster_model_mem_param(ti.model_name, &base, &slope)
+                                                  : srt_adjuster_model_mem_param_measured(ti.model_name, &base, &slope);
     if (rc) return rc;
     have_param = true;
     return SRT_OK;
@@ -77,6 +81,20 @@ int srt_adjuster_model_mem_param(const char* model_name, double* base_mb, double
   for (const auto& e : kTable)
     if (std::string(model_name) == e.name) { *base_mb = e.base; *slope_mb = e.slope; return SRT_OK; }
   set_error("train adjuster: unsupported model '%s'", model_name);
+  return SRT_ERR_UNSUPPORTED;
+}
+
+// The same line for this library's bf16 executors on a B200, measured with `python -m sirius_b200.mem_model`
+// (device memory taken by the executor at two batch sizes; resnet152 at 224x224, gpt2 at 1024 tokens, qwen = the
+// 0.5B shape at 2048 tokens). The swin_b_ddp entry adds the gradient buckets' bf16 wire buffer to swin_b.
+int srt_adjuster_model_mem_param_measured(const char* model_name, double* base_mb, double* slope_mb) {
+  SRT_REQUIRE(model_name && base_mb && slope_mb, "model_mem_param_measured: null argument");
+  static const struct { const char* name; double base, slope; } kTable[] = {
+      {"resnet152", 1475, 103}, {"swin_b", 1920, 143}, {"swin_b_ddp", 2090, 143}, {"gpt2", 3000, 737},
+      {"qwen", 11530, 5453}};
+  for (const auto& e : kTable)
+    if (std::string(model_name) == e.name) { *base_mb = e.base; *slope_mb = e.slope; return SRT_OK; }
+  set_error("train adjuster: no measured memory line for model '%s'", model_name);
   return SRT_ERR_UNSUPPORTED;
 }
 

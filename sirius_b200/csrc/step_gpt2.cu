@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "grad_buckets.cuh"
 #include "ops.cuh"
+#include "partition_follow.cuh"
 
 namespace srt {
 
@@ -76,6 +77,7 @@ struct Gpt2 {
   // lowest-priority stream beside the data gradient and whatever follows it in the layer. The main stream waits for
   // them before it overwrites a dy buffer they read (once per layer, before the layer's last kernel) and at the end.
   cudaStream_t side = nullptr;
+  PartitionFollower part;   // SM-partition following between layers (off by default)
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool side_dirty = false, overlap_wgrad = true;
   void* scratch_side = nullptr;
@@ -93,6 +95,7 @@ struct Gpt2 {
   unsigned long long layer_seq = 0;
 
   ~Gpt2() {
+    if (part.home_stream) { stream = part.home_stream; side = part.home_side; }  // partition streams belong to the ladder
     release_activations(nullptr);
     for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
     if (ev_fork) cudaEventDestroy(ev_fork);
@@ -156,6 +159,7 @@ struct Gpt2 {
       set_error("step aborted between layers (kill batch)");
       return SRT_ERR_ABORTED;
     }
+    if (int rc = part.follow(stream, side)) return rc;
     const int slot = (int)(layer_seq % kAhead);
     if (!ahead_ev[slot]) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ahead_ev[slot], cudaEventDisableTiming));
     else if (layer_seq >= (unsigned long long)kAhead) SRT_CHECK_CUDA(cudaEventSynchronize(ahead_ev[slot]));
@@ -557,6 +561,7 @@ int srt_gpt2_upload_tokens(srt_gpt2* h, const int32_t* host_ids, int B) {
 int srt_gpt2_forward_backward(srt_gpt2* h, int B, int global_batch) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B && global_batch >= B, "gpt2_forward_backward: upload the tokens of this batch first");
+  PartitionFollower::Scope sm_scope(g->part);
   int rc;
   if (g->act_batch < B && (rc = g->alloc_activations(B))) return rc;  // regain after a release or a shrink
   if ((rc = g->forward(B))) return rc;
@@ -566,6 +571,7 @@ int srt_gpt2_forward_backward(srt_gpt2* h, int B, int global_batch) {
 int srt_gpt2_forward_only(srt_gpt2* h, int B) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B, "gpt2_forward_only: upload the tokens of this batch first");
+  PartitionFollower::Scope sm_scope(g->part);
   if (g->act_batch < B) { int rc = g->alloc_activations(B); if (rc) return rc; }
   return g->forward(B);
 }
@@ -573,6 +579,7 @@ int srt_gpt2_forward_only(srt_gpt2* h, int B) {
 int srt_gpt2_optimizer(srt_gpt2* h) {
   Gpt2* g = (Gpt2*)h;
   SRT_REQUIRE(g, "gpt2_optimizer: null handle");
+  PartitionFollower::Scope sm_scope(g->part);
   g->opt_steps++;
   const float* grad = g->accum_pending > 0 ? g->ACC : g->G;
   int rc = adamw(g->P, grad, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
@@ -615,6 +622,15 @@ int srt_gpt2_logits(srt_gpt2* h, float* host, int B) {
     }
   return SRT_OK;
 }
+
+int srt_gpt2_follow_infer_tpc(srt_gpt2* h, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc, int enable) {
+  Gpt2* g = (Gpt2*)h;
+  SRT_REQUIRE(g, "gpt2_follow_infer_tpc: null handle");
+  { int dev = 0; SRT_CHECK_CUDA(cudaGetDevice(&dev)); g->part.device = dev; }
+  return g->part.configure(g->stream, g->side, comm, device, min_train_tpc, max_train_tpc, enable != 0);
+}
+
+int srt_gpt2_current_sms(srt_gpt2* h) { return h ? ((Gpt2*)h)->part.cur_sms : -1; }
 
 int srt_gpt2_synchronize(srt_gpt2* h) {
   Gpt2* g = (Gpt2*)h;

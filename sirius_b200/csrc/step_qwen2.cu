@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "grad_buckets.cuh"
 #include "ops.cuh"
+#include "partition_follow.cuh"
 
 namespace srt {
 
@@ -61,6 +62,7 @@ struct Qwen2 {
   // lowest-priority stream beside the data gradient and whatever follows it in the layer. The main stream waits for
   // them before it overwrites a dy buffer they read (once per layer, before the layer's last kernel) and at the end.
   cudaStream_t side = nullptr;
+  PartitionFollower part;   // SM-partition following between layers (off by default)
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool side_dirty = false, overlap_wgrad = true;
   void* scratch_side = nullptr;
@@ -144,6 +146,7 @@ struct Qwen2 {
       set_error("step aborted between layers (kill batch)");
       return SRT_ERR_ABORTED;
     }
+    if (int rc = part.follow(stream, side)) return rc;
     const int slot = (int)(layer_seq % kAhead);
     if (!ahead_ev[slot]) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&ahead_ev[slot], cudaEventDisableTiming));
     else if (layer_seq >= (unsigned long long)kAhead) SRT_CHECK_CUDA(cudaEventSynchronize(ahead_ev[slot]));
@@ -153,6 +156,7 @@ struct Qwen2 {
   }
 
   ~Qwen2() {
+    if (part.home_stream) { stream = part.home_stream; side = part.home_side; }  // partition streams belong to the ladder
     release_activations(nullptr);
     for (auto e : ahead_ev) if (e) cudaEventDestroy(e);
     if (ev_fork) cudaEventDestroy(ev_fork);
@@ -537,6 +541,7 @@ int srt_qwen2_upload_tokens(srt_qwen2* h, const int32_t* host_ids, int B) {
 int srt_qwen2_forward_backward(srt_qwen2* h, int B, int global_batch) {
   Qwen2* g = (Qwen2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B && global_batch >= B, "qwen2_forward_backward: upload the tokens of this batch first");
+  PartitionFollower::Scope sm_scope(g->part);
   int rc;
   if (g->act_batch < B && (rc = g->alloc_activations(B))) return rc;  // regain after a release or a shrink
   if ((rc = g->forward(B))) return rc;
@@ -546,6 +551,7 @@ int srt_qwen2_forward_backward(srt_qwen2* h, int B, int global_batch) {
 int srt_qwen2_forward_only(srt_qwen2* h, int B) {
   Qwen2* g = (Qwen2*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B, "qwen2_forward_only: upload the tokens of this batch first");
+  PartitionFollower::Scope sm_scope(g->part);
   if (g->act_batch < B) { int rc = g->alloc_activations(B); if (rc) return rc; }
   return g->forward(B);
 }
@@ -553,6 +559,7 @@ int srt_qwen2_forward_only(srt_qwen2* h, int B) {
 int srt_qwen2_optimizer(srt_qwen2* h) {
   Qwen2* g = (Qwen2*)h;
   SRT_REQUIRE(g, "qwen2_optimizer: null handle");
+  PartitionFollower::Scope sm_scope(g->part);
   g->opt_steps++;
   const float* grad = g->accum_pending > 0 ? g->ACC : g->G;
   int rc = adamw(g->P, grad, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
@@ -589,6 +596,15 @@ int srt_qwen2_logits(srt_qwen2* h, float* host, int B) {
     }
   return SRT_OK;
 }
+
+int srt_qwen2_follow_infer_tpc(srt_qwen2* h, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc, int enable) {
+  Qwen2* g = (Qwen2*)h;
+  SRT_REQUIRE(g, "qwen2_follow_infer_tpc: null handle");
+  { int dev = 0; SRT_CHECK_CUDA(cudaGetDevice(&dev)); g->part.device = dev; }
+  return g->part.configure(g->stream, g->side, comm, device, min_train_tpc, max_train_tpc, enable != 0);
+}
+
+int srt_qwen2_current_sms(srt_qwen2* h) { return h ? ((Qwen2*)h)->part.cur_sms : -1; }
 
 int srt_qwen2_synchronize(srt_qwen2* h) {
   Qwen2* g = (Qwen2*)h;

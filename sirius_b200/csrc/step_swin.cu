@@ -18,6 +18,7 @@
 #include "common.cuh"
 #include "grad_buckets.cuh"
 #include "ops.cuh"
+#include "partition_follow.cuh"
 
 namespace srt {
 
@@ -72,6 +73,7 @@ struct Swin {
   // lowest-priority stream beside the data gradient and whatever follows it in the layer. The main stream waits for
   // them before it overwrites a dy buffer they read (once per layer, before the layer's last kernel) and at the end.
   cudaStream_t side = nullptr;
+  PartitionFollower part;   // SM-partition following between layers (off by default)
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool side_dirty = false, overlap_wgrad = true;
   void* scratch_side = nullptr;
@@ -90,6 +92,7 @@ struct Swin {
   int cur_B = 0, last_global = 0;
 
   ~Swin() {
+    if (part.home_stream) { stream = part.home_stream; side = part.home_side; }  // partition streams belong to the ladder
     if (ev_fork) cudaEventDestroy(ev_fork);
     if (ev_join) cudaEventDestroy(ev_join);
     if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
@@ -380,6 +383,7 @@ int Swin::forward(int B) {
   int b0 = 0;
   for (int s = 0; s < 4; ++s) {
     for (int i = b0; i < stage_end[s]; ++i) {
+      if ((rc = part.follow(stream, side))) return rc;
       if ((rc = block_fwd(blocks[i], x, B))) return rc;
       x = blocks[i].xout;
     }
@@ -418,6 +422,7 @@ int Swin::backward(int B, int global_batch) {
     const int first = s == 0 ? 0 : stage_end[s - 1];
     for (int i = stage_end[s] - 1; i >= first; --i) {
       const __nv_bfloat16* xin = i > first ? blocks[i - 1].xout : (s == 0 ? x0 : merges[s - 1].out);
+      if ((rc = part.follow(stream, side))) return rc;
       if ((rc = block_bwd(blocks[i], xin, dx, dx_other, B))) return rc;
       if ((rc = buckets.unit_done(i, stream))) return rc;
     }
@@ -546,6 +551,7 @@ int srt_swin_upload_batch(srt_swin* h, const float* host_images, const int64_t* 
 int srt_swin_forward_backward(srt_swin* h, int B, int global_batch) {
   Swin* g = (Swin*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B && global_batch >= B, "swin_forward_backward: upload this batch first");
+  PartitionFollower::Scope sm_scope(g->part);
   int rc = g->forward(B);
   if (rc) return rc;
   return g->backward(B, global_batch);
@@ -554,12 +560,14 @@ int srt_swin_forward_backward(srt_swin* h, int B, int global_batch) {
 int srt_swin_forward_only(srt_swin* h, int B) {
   Swin* g = (Swin*)h;
   SRT_REQUIRE(g && B > 0 && B == g->cur_B, "swin_forward_only: upload this batch first");
+  PartitionFollower::Scope sm_scope(g->part);
   return g->forward(B);
 }
 
 int srt_swin_optimizer(srt_swin* h) {
   Swin* g = (Swin*)h;
   SRT_REQUIRE(g, "swin_optimizer: null handle");
+  PartitionFollower::Scope sm_scope(g->part);
   g->opt_steps++;
   int rc = adamw(g->P, g->G, g->M1, g->M2, g->Pw, (int64_t)g->n_flat, g->cfg.lr, g->cfg.beta1, g->cfg.beta2, g->cfg.eps,
                  g->cfg.weight_decay, g->opt_steps, g->stream);
@@ -591,6 +599,15 @@ int srt_swin_logits(srt_swin* h, float* host, int B) {
   }
   return SRT_OK;
 }
+
+int srt_swin_follow_infer_tpc(srt_swin* h, srt_comm* comm, int device, int min_train_tpc, int max_train_tpc, int enable) {
+  Swin* g = (Swin*)h;
+  SRT_REQUIRE(g, "swin_follow_infer_tpc: null handle");
+  { int dev = 0; SRT_CHECK_CUDA(cudaGetDevice(&dev)); g->part.device = dev; }
+  return g->part.configure(g->stream, g->side, comm, device, min_train_tpc, max_train_tpc, enable != 0);
+}
+
+int srt_swin_current_sms(srt_swin* h) { return h ? ((Swin*)h)->part.cur_sms : -1; }
 
 int srt_swin_synchronize(srt_swin* h) {
   Swin* g = (Swin*)h;

@@ -202,6 +202,21 @@ class Gpt2Step(GradBucketsMixin):
         call("srt_gpt2_grad_buffer", self._h, C.byref(p), C.byref(n))
         return p.value, n.value
 
+    def follow_infer_tpc(self, comm_handle, device: int = 0, min_train_tpc: int = 5, max_train_tpc: int = 0) -> None:
+        """Between layers, move to the SM partition that the inference side's required-TPC counter on the
+        information board leaves to training (pytorch/torch_col/csrc/init.cc:56-62); None detaches."""
+        from . import _runtime  # noqa: F401  (registers the entry points)
+        call("srt_gpt2_follow_infer_tpc", self._h, comm_handle, device, min_train_tpc, max_train_tpc, 0 if comm_handle is None else 1)
+
+    def follow_sm_mask(self, on: bool = True) -> None:
+        """Follow the process-wide allowed-SM mask instead of a board."""
+        from . import _runtime  # noqa: F401
+        call("srt_gpt2_follow_infer_tpc", self._h, None, 0, 0, 0, int(on))
+
+    def current_sms(self) -> int:
+        from . import _runtime  # noqa: F401
+        return _lib.lib().srt_gpt2_current_sms(self._h)
+
     def memory_bytes(self) -> int:
         return _lib.lib().srt_gpt2_memory_bytes(self._h)
 

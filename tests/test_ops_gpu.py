@@ -98,7 +98,7 @@ def test_conv_bf16_simt(case):
 # fprop/dgrad kernel plans (gather, tile width, CTA pair): the heuristic, every forced tile width with one CTA
 # per 128-row tile, and two CTAs per 256-row tile (tcgen05 cta_group::2) with each of its tile widths
 PLANS = {"auto": (0, 0, -1), "single_bn64": (0, 64, 0), "single_bn128": (0, 128, 0), "single_bn256": (0, 256, 0),
-         "pair_bn128": (0, 128, 1), "pair_bn256": (0, 256, 1)}
+         "pair_bn128": (0, 128, 1), "pair_bn256": (0, 256, 1), "gather": (1, 0, -1), "gather_pair": (1, 0, 1)}
 
 
 def _with_plan(plan, fn):
@@ -177,6 +177,45 @@ def test_conv_tcgen05_gather_equals_tma():
     assert ops.tc_status() == 0
     assert torch.equal(y_tma, y_g)
     assert torch.equal(dw_tma, dw_g)
+
+
+IM2COL_CASES = [
+    ("i3x3_tail", 5, 14, 14, 128, 192, 3, 3, 1, 1),          # 980 rows: tiles cross image borders, ragged last tile
+    ("i3x3_c64_two_taps_per_tile", 3, 28, 28, 64, 64, 3, 3, 1, 1),
+    ("i3x3_s2", 3, 28, 28, 128, 128, 3, 3, 2, 1),
+    ("i1x1_s2", 3, 28, 28, 256, 512, 1, 1, 2, 0),
+    ("i5x5_pad2", 2, 12, 10, 64, 72, 5, 5, 1, 2),
+    ("i3x3_pad0", 2, 16, 16, 64, 64, 3, 3, 1, 0),
+    ("i3x3_7x7_image", 67, 7, 7, 128, 256, 3, 3, 1, 1),      # 49-pixel images: a tile spans three of them
+]
+
+
+@pytest.mark.parametrize("case", IM2COL_CASES, ids=[c[0] for c in IM2COL_CASES])
+def test_conv_im2col_tma_equals_gather_bitwise(case):
+    """Filters wider than 1x1 (and strided 1x1 filters) fetch their activation operand with im2col TMA loads when
+    the channel count is a multiple of 64; the cp.async gather delivers the same tiles, so fprop, dgrad (stride 1)
+    and wgrad agree bit for bit with it, through single CTAs and CTA pairs, and match the fp32 reference."""
+    bf = torch.bfloat16
+    _, N, H, W, C, K, R, S, stride, pad = case
+    x, w, dy = _mk(case, bf)
+    xd, wd, dyd = x.to(DEV, bf), w.to(DEV, bf), dy.to(DEV, bf)
+    wt = ops.filter_transpose(wd)
+
+    def run():
+        y = ops.conv_fprop(xd, wd, stride, pad, impl=IMPL_TCGEN05)
+        dx = ops.conv_dgrad(dyd, wt, x.shape, stride, pad, impl=IMPL_TCGEN05)
+        dw = ops.conv_wgrad(dyd, xd, R, S, stride, pad, impl=IMPL_TCGEN05)
+        return y, dx, dw
+    ref = _ref(x, w, dy, stride, pad)
+    base = _with_plan((1, 0, 0), run)                     # everything gathered, one CTA per tile
+    for plan in ((0, 0, 0), (0, 0, 1), (0, 64, 0)):
+        got = _with_plan(plan, run)
+        torch.cuda.synchronize()
+        assert ops.tc_status() == 0
+        for name, a, b in zip(("fprop", "dgrad", "wgrad"), got, base):
+            assert torch.equal(a, b), (case[0], plan, name)
+    for name, a, r in zip(("fprop", "dgrad", "wgrad"), base, ref):
+        assert _err(a, r) < 2e-2, (case[0], name)
 
 
 def test_conv_epilogue_bias_addend():

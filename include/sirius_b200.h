@@ -43,10 +43,14 @@ typedef struct srt_conv_desc {
 } srt_conv_desc;
 
 /* Fused epilogue of fprop/dgrad: y = acc (+ bias[k]) (+ addend[m][k]).  Null pointers disable a
- * term. addend may alias y. */
+ * term. addend may alias y. addend_bits (optional, with addend): one bit per element of addend, bit e of
+ * byte i for element 8i + e in row-major order; an element whose bit is 0 is not added. This is how the
+ * data gradient of the first convolution of a residual block receives the block's output gradient under
+ * the ReLU mask of the block's output (srt_bn_apply_bits) without a masked copy of it in memory. */
 typedef struct srt_conv_epilogue {
   const float* bias;     /* [K] fp32, or NULL            */
   const void*  addend;   /* same shape/dtype as y, or NULL */
+  const unsigned char* addend_bits;  /* [M*K/8] or NULL */
 } srt_conv_epilogue;
 
 /* y[N,P,Q,K] = conv(x[N,H,W,C], w[K,R,S,C]). */
@@ -127,6 +131,17 @@ int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int
                     const float* gamma, const float* mean, const float* invstd, const float* scale,
                     const float* shift, int relu, void* dz, void* dresidual, float* dgamma,
                     float* dbeta, void* scratch, size_t scratch_bytes, void* stream);
+/* The ReLU mask of a bf16 unit as one bit per element instead of the stored output: srt_bn_apply_bits is
+ * srt_bn_apply with relu = 1 that also writes relu_bits[rows*C/8] (bit e of byte i: element 8i + e of y is
+ * positive); srt_bn_backward_bits is srt_bn_backward (one_launch = 0, needs scratch) or srt_bn_backward_fused
+ * (one_launch = 1) reading those bits where the other two read y: a sixteenth of the bytes in both of their
+ * passes. Together with srt_conv_epilogue.addend_bits a residual block's backward needs neither the stored
+ * output nor a masked copy of its gradient. No counterpart in the reference (autograd keeps the output). */
+int srt_bn_apply_bits(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
+                      const float* scale, const float* shift, unsigned char* relu_bits, void* stream);
+int srt_bn_backward_bits(int dtype, const void* dy, const unsigned char* relu_bits, const void* z, int64_t rows, int C,
+                         const float* gamma, const float* mean, const float* invstd, void* dz, void* dresidual,
+                         float* dgamma, float* dbeta, void* scratch, size_t scratch_bytes, int one_launch, void* stream);
 /* The same BatchNorm as ONE launch per direction: a cooperative grid of at most one block per SM sums its work
  * items, meets at a grid-wide barrier, finalizes the channels (dealt to the warps of the grid), meets again and
  * applies the coefficients to the same items. Pays where the three launches of the path above cost more than the

@@ -94,7 +94,7 @@ int srt_step_follow_infer_tpc(struct srt_step* s, srt_comm* comm, int device, in
 /* The same hook for the transformer executors, checked between layers (GPT-2, Qwen2) or blocks (Swin): the
  * executor moves its main stream and the low-priority stream of its weight gradients to the partition that fits.
  * enable = 0 brings it back to its whole-device streams; enable = 1 with comm == NULL follows the process-wide
- * allowed-SM mask instead of a board. *_current_sms: width of the partition in use, 0 = whole device. */
+ * allowed-SM mask instead of a board. *_current_sms: SMs of the partition in use (the device's SM count when none is). */
 struct srt_gpt2;
 struct srt_qwen2;
 struct srt_swin;

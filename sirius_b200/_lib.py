@@ -29,7 +29,7 @@ class ConvDesc(C.Structure):
 
 
 class ConvEpilogue(C.Structure):
-    _fields_ = [("bias", C.c_void_p), ("addend", C.c_void_p)]
+    _fields_ = [("bias", C.c_void_p), ("addend", C.c_void_p), ("addend_bits", C.c_void_p)]
 
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -53,6 +53,8 @@ _SIGNATURES = {
     "srt_bn_scratch_bytes": (_sz, [_i64, _i]),
     "srt_bn_stats_static": (None, [_i, _vp, _i64, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "srt_bn_apply": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _i, _vp]),
+    "srt_bn_apply_bits": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _vp]),
+    "srt_bn_backward_bits": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "srt_bn_backward": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "srt_bn_fused_fits": (_i, [_i, _i64, _i, _i]),
     "srt_bn_forward_fused": (None, [_i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),

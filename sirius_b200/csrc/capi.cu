@@ -228,6 +228,26 @@ int srt_bn_backward(int dtype, const void* dy, const void* y, const void* z, int
                      dgamma, dbeta, scratch, scratch_bytes, ST(stream));
 }
 
+int srt_bn_apply_bits(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
+                      const float* scale, const float* shift, uint8_t* relu_bits, void* stream) {
+  SRT_REQUIRE(z && y && scale && shift && relu_bits, "bn_apply_bits: null argument");
+  CHECK_DTYPE(dtype);
+  return bn_apply(dtype, z, residual, y, rows, C, scale, shift, 1, ST(stream), relu_bits);
+}
+int srt_bn_backward_bits(int dtype, const void* dy, const uint8_t* relu_bits, const void* z, int64_t rows, int C,
+                         const float* gamma, const float* mean, const float* invstd, void* dz, void* dresidual,
+                         float* dgamma, float* dbeta, void* scratch, size_t scratch_bytes, int one_launch, void* stream) {
+  SRT_REQUIRE(dy && relu_bits && z && mean && invstd && dz, "bn_backward_bits: null argument");
+  CHECK_DTYPE(dtype);
+  if (one_launch) {
+    SRT_REQUIRE(C % 8 == 0 && rows > 0, "bn_backward_bits: C (%d) must be a multiple of 8", C);
+    return bn_backward_fused(dtype, dy, nullptr, z, rows, C, gamma, mean, invstd, nullptr, nullptr, 1, dz, dresidual, dgamma,
+                             dbeta, ST(stream), relu_bits);
+  }
+  return bn_backward(dtype, dy, nullptr, z, rows, C, gamma, mean, invstd, nullptr, nullptr, 1, dz, dresidual, dgamma, dbeta,
+                     scratch, scratch_bytes, ST(stream), relu_bits);
+}
+
 int srt_bn_fused_fits(int dtype, int64_t rows, int C, int backward) { return bn_fused_fits(dtype, rows, C, backward) ? 1 : 0; }
 int srt_bn_forward_fused(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C, const float* gamma,
                          const float* beta, float eps, float momentum, float* running_mean, float* running_var, float* mean,

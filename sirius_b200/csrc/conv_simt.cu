@@ -32,7 +32,7 @@ template <> struct Ld4<__nv_bfloat16> {
 template <typename T>
 __global__ void __launch_bounds__(NT)
 gather_gemm_simt(GatherGeom g, const T* __restrict__ src, const T* __restrict__ Bm,
-                 T* __restrict__ D, const float* __restrict__ bias, const T* addend) {
+                 T* __restrict__ D, const float* __restrict__ bias, const T* addend, const uint8_t* __restrict__ addend_bits) {
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Bs[BK][BN + 4];
   const int t = threadIdx.x;
@@ -88,7 +88,7 @@ gather_gemm_simt(GatherGeom g, const T* __restrict__ src, const T* __restrict__ 
       float v = acc[i][j];
       if (bias) v += bias[nn];
       const size_t o = (size_t)mm * g.Nout + nn;
-      if (addend) v += ElemTraits<T>::to_f(addend[o]);
+      if (addend && (!addend_bits || ((addend_bits[o >> 3] >> (o & 7)) & 1))) v += ElemTraits<T>::to_f(addend[o]);
       D[o] = ElemTraits<T>::from_f(v);
     }
   }
@@ -192,7 +192,7 @@ static int gather_gemm_simt_launch(const GatherGeom& g, const void* src, const v
   dim3 grid(ceil_div(g.M, BM), ceil_div(g.Nout, BN));
   gather_gemm_simt<T><<<grid, NT, 0, st>>>(g, (const T*)src, (const T*)Bm, (T*)D,
                                           ep ? ep->bias : nullptr,
-                                          ep ? (const T*)ep->addend : nullptr);
+                                          ep ? (const T*)ep->addend : nullptr, ep ? ep->addend_bits : nullptr);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }

@@ -39,6 +39,8 @@
 namespace srt {
 
 static int g_force_gather = 0;  // plan override: fetch plain-matrix operands with the gather threads
+static int g_force_pair = getenv("SIRIUS_B200_CONV_PAIR") ? atoi(getenv("SIRIUS_B200_CONV_PAIR")) : -1;  // plan override: 0 never pairs CTAs
+static int g_im2col_enabled = getenv("SIRIUS_B200_CONV_IM2COL") ? atoi(getenv("SIRIUS_B200_CONV_IM2COL")) : 1;  // 0: gather filters wider than 1x1
 
 namespace {
 
@@ -332,6 +334,165 @@ igemm_wgrad_kernel(const WgradParams p, const __grid_constant__ CUtensorMap tmap
 
 
 // ------------------------------------------------------------------------------------------
+// Filter gradient on CTA pairs (tcgen05 cta_group::2): a pair owns a 256-filter x 256-column tile of dW for one
+// split of the pixel range. CTA r of the pair stages, per k-block of 64 pixels, its 128 filters of dy (two
+// 64-filter boxes) and its 128 of the tile's columns of X (two 64-channel blocks, plain or im2col TMA), the
+// leader issues 256 x 256 x 16 MMAs over both CTAs' shared memory, and each CTA finds its 128 filter rows x 256
+// columns in its own tensor memory. Per k-block an SM then receives 32 KB for 128 x 256 x 64 multiply-adds, half of
+// what the single-CTA kernel's 128 x 128 tile needs, and one CTA per SM with a six-stage ring covers the load
+// latency. The fp32 tile leaves through shared memory (the ring's stages, free by then) and TMA stores of
+// 128 rows x 32 columns, which write whole lines where a store per thread and row would write 16-byte pieces.
+// Both operands must come by TMA (the gather path stays with the single-CTA kernel). No load is multicast.
+constexpr int WP_NS = 6;
+constexpr int WP_STAGE_BYTES = 32768;  // 16 KB of dy + 16 KB of X per CTA and k-block
+constexpr size_t wgrad_pair_smem_bytes() { return 1024 + (size_t)WP_NS * WP_STAGE_BYTES + (2 * WP_NS + 1) * 8 + 16; }
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+igemm_wgrad_pair(const WgradParams p, const __grid_constant__ CUtensorMap tmap_dy,
+                 const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_out) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(base + WP_NS * WP_STAGE_BYTES);
+  uint64_t* empty = full + WP_NS;
+  uint64_t* tmem_full = empty + WP_NS;
+  uint32_t* tmem_ptr = (uint32_t*)(tmem_full + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const GatherGeom& g = p.g;
+  const int Kout = g.Nout, J = g.Kg;
+  const uint32_t rank = cluster_ctarank();
+  const int j0 = (int)(blockIdx.x >> 1) * 256 + (int)rank * 128;   // this CTA's 128 columns
+  const int ko0 = (int)blockIdx.y * 256 + (int)rank * 128;         // ... and its 128 filters
+  const int pbeg = blockIdx.z * p.pix_per_split;
+  const int pend = min(g.M, pbeg + p.pix_per_split);
+  const int nkb = (pend - pbeg + BK - 1) / BK;
+
+  if (tid == 0) {
+    for (int s = 0; s < WP_NS; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    mbar_init(smem_u32(tmem_full), 1);
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmap_dy);
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_out);
+  }
+  if (warp == 5) {
+    tmem_alloc_pair(smem_u32(tmem_ptr), 256);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers and tensor memory exist before anything refers to them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+  pdl_enter();
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // live 64-column blocks of either CTA (a block at or beyond the last column is not loaded)
+      auto live_blocks = [&](int jbase) { return jbase >= J ? 0 : (jbase + 64 >= J ? 1 : 2); };
+      const int my_live = live_blocks(j0);
+      const int pair_j0 = (int)(blockIdx.x >> 1) * 256;
+      const uint32_t pair_bytes = 2u * 16384u + (uint32_t)(live_blocks(pair_j0) + live_blocks(pair_j0 + 128)) * 8192u;
+      int blk_c[2];
+      uint16_t blk_r[2], blk_s[2];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        const int j = j0 + blk * 64;
+        const int tap = j / g.src_c;
+        blk_c[blk] = j - tap * g.src_c;
+        blk_r[blk] = (uint16_t)(tap / g.S);
+        blk_s[blk] = (uint16_t)(tap - (tap / g.S) * g.S);
+      }
+      const int hw = g.out_h * g.out_w;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % WP_NS;
+        const uint32_t ph = (uint32_t)(kb / WP_NS) & 1u;
+        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, p.status, W_TMA_EMPTY)) break;
+        const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0u);
+        if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full[s]), pair_bytes);
+        const uint32_t dst = smem_u32(base + s * WP_STAGE_BYTES);
+        const int pix0 = pbeg + kb * BK;
+        tma_load_2d_pair(dst, &tmap_dy, lbar, ko0, pix0);
+        tma_load_2d_pair(dst + 8192u, &tmap_dy, lbar, ko0 + 64, pix0);
+        const uint32_t dstb = dst + 16384u;
+        if (p.b_tma == 1) {
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk)
+            if (blk < my_live) tma_load_2d_pair(dstb + (uint32_t)blk * 8192u, &tmap_x, lbar, j0 + blk * 64, pix0);
+        } else {
+          const int n = fastdiv(pix0, hw, p.hw_mul, p.hw_shr);
+          const int rem = pix0 - n * hw;
+          const int oh = fastdiv(rem, g.out_w, p.w_mul, p.w_shr), ow = rem - oh * g.out_w;
+          const int bw = ow * g.stride - g.pad, bh = oh * g.stride - g.pad;
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk)
+            if (blk < my_live)
+              tma_load_im2col_4d_pair(dstb + (uint32_t)blk * 8192u, &tmap_x, lbar, blk_c[blk], bw, bh, n, blk_s[blk], blk_r[blk]);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, 256, 1, 1);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % WP_NS;
+        const uint32_t ph = (uint32_t)(kb / WP_NS) & 1u;
+        if (!mbar_wait_cluster(smem_u32(&full[s]), ph, p.status, W_MMA_FULL)) break;
+        tc_fence_after_sync();
+        const uint32_t a0 = smem_u32(base + s * WP_STAGE_BYTES);
+        const uint32_t b0 = a0 + 16384u;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t ad = make_smem_desc_sw128(a0 + k * 2048, 8192, 1024);
+          const uint64_t bd = make_smem_desc_sw128(b0 + k * 2048, 8192, 1024);
+          umma_bf16_pair(tmem_base, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit_pair(smem_u32(&empty[s]), (uint16_t)3);
+      }
+      umma_commit_pair(smem_u32(tmem_full), (uint16_t)3);
+    }
+  } else {
+    // ---------------- epilogue: this CTA's 128 filter rows x 256 columns, fp32, through shared memory ----------------
+    const bool ready = mbar_wait(smem_u32(tmem_full), 0u, p.status, W_EPI_TMEM);
+    tc_fence_after_sync();
+    // every MMA has completed, so every stage has been consumed: the ring is free for staging
+    const int row = warp * 32 + lane;
+    const int pair_j0 = (int)(blockIdx.x >> 1) * 256;
+#pragma unroll 1
+    for (int cb = 0; cb < 8; ++cb) {
+      uint32_t acc[32];
+      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 32), acc);
+      tmem_ld_wait();
+      uint8_t* stage = base + cb * 16384;  // [128 rows][128 bytes], 16-byte chunks swizzled by the row
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        *reinterpret_cast<uint4*>(stage + (uint32_t)row * 128u + (uint32_t)((v ^ (row & 7)) << 4)) =
+            make_uint4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
+      fence_proxy_async_smem();
+      named_bar_sync(1, NPROD);
+      if (tid == 0 && ready && pair_j0 + cb * 32 < J) {
+        tma_store_3d(&tmap_out, smem_u32(stage), pair_j0 + cb * 32, ko0, (int)blockIdx.z);
+        bulk_commit_group();
+      }
+    }
+    if (tid == 0) bulk_wait_group_read<0>();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers or read its operands
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // Persistent fprop/dgrad kernel: one CTA per SM walks the output tiles t = blockIdx.x, +gridDim.x,
 // ... (t = m_tile * n_tiles + n_tile). 704 threads:
 //   warp 0        TMA producer: B tile every stage, A tile too when it is a plain matrix block
@@ -362,6 +523,7 @@ struct PersistParams {
   const bf16* src;
   const float* bias;
   const bf16* addend;
+  const uint8_t* addend_bits;  // optional: one bit per element of addend; a cleared bit leaves the element out
   int k_blocks;
   int a_tma;             // how the A operand arrives: 0 gathered with cp.async, 1 plain matrix by TMA, 2 im2col TMA
   int im_lower_w, im_lower_h;  // im2col: base pixel of output position (oh, ow) = (oh, ow) * im_stride + lower
@@ -625,6 +787,11 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
           if (issuer) bulk_wait_group_read<0>();
           named_bar_sync(bar_id, NPROD);
         }
+        // the addend's mask bits of this thread's 64 columns: one 8-byte load when rows are whole 8-byte groups
+        uint2 abits = make_uint2(0u, 0u);
+        const bool abits_wide = p.addend_bits != nullptr && (g.Nout & 63) == 0;
+        if (abits_wide && live && m < g.M)
+          abits = *reinterpret_cast<const uint2*>(p.addend_bits + (((size_t)m * g.Nout + col0) >> 3));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t acc[32];
@@ -659,6 +826,12 @@ igemm_fwd_persistent(const PersistParams p, const __grid_constant__ CUtensorMap 
                 av.load(p.addend + (size_t)m * g.Nout + col);
                 float af[8];
                 av.unpack(af);
+                if (p.addend_bits) {
+                  const unsigned bits = abits_wide ? ((h ? abits.y : abits.x) >> (v * 8))
+                                                   : (unsigned)p.addend_bits[((size_t)m * g.Nout + col) >> 3];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) af[e] = ((bits >> e) & 1u) ? af[e] : 0.f;
+                }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] += af[e];
               }
@@ -1075,7 +1248,7 @@ inline Im2colBox im2col_box(const GatherGeom& g) {
 }
 // Whether the source of a gather geometry can be fetched by im2col TMA loads of 64-channel chunks: a k-block must
 // not straddle a filter tap, a strided data gradient has holes no box describes, and the corner fields are 8 bits.
-inline bool im2col_ok(const GatherGeom& g) {
+bool im2col_ok(const GatherGeom& g) {
   if (g.src_c % 64 != 0 || (g.dgrad && g.stride != 1) || g.stride > 8) return false;
   if (g.pad > g.R - 1 || g.pad > g.S - 1 || g.R > 16 || g.S > 16) return false;
   const Im2colBox b = im2col_box(g);
@@ -1163,6 +1336,54 @@ int launch_wgrad(const WgradParams& p, const CUtensorMap& tdy, const CUtensorMap
   return SRT_OK;
 }
 
+// fp32 partial sums [splits][filters][columns] for TMA stores of 128 rows x 32 columns, 128B swizzle.
+int make_tmap_wgrad_out(CUtensorMap* tm, float* base, uint64_t J, uint64_t Kout, uint64_t splits) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return SRT_ERR_CUDA;
+  }
+  SRT_REQUIRE(((uintptr_t)base & 15) == 0 && (J * 4) % 16 == 0, "wgrad output must be 16-byte aligned with a 16-byte multiple row pitch");
+  cuuint64_t dims[3] = {J, Kout, splits};
+  cuuint64_t strides[2] = {J * 4, Kout * J * 4};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (wgrad output) failed with CUresult %d", (int)r);
+    return SRT_ERR_CUDA;
+  }
+  return SRT_OK;
+}
+
+int launch_wgrad_pair(const WgradParams& p, const CUtensorMap& tdy, const CUtensorMap& tx, const CUtensorMap& tout,
+                      int splits, cudaStream_t st) {
+  constexpr size_t smem = wgrad_pair_smem_bytes();
+  static_assert(smem <= 232448, "pair wgrad: shared memory budget exceeded");
+  static bool configured = false;
+  if (!configured) {
+    SRT_CHECK_CUDA(cudaFuncSetAttribute(igemm_wgrad_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * ceil_div(p.g.Kg, 256), ceil_div(p.g.Nout, 256), splits);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = (pdl_big_kernels() && (pdl_classes() & PDL_GEMM) != 0) ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  SRT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, igemm_wgrad_pair, p, tdy, tx, tout));
+  return SRT_OK;
+}
+
 template <int BN, int NS, bool PAIR>
 int launch_persistent(const PersistParams& p, const CUtensorMap& tb, const CUtensorMap& ta,
                       const CUtensorMap& td, cudaStream_t st) {
@@ -1221,10 +1442,31 @@ int pick_bn(int M, int N, int forced) {
 
 struct WgradPlan {
   int bn, splits, pix_per_split;
+  int b_tma;  // how X arrives: 0 gathered, 1 plain matrix by TMA, 2 im2col TMA
+  bool pair;  // 256 x 256 tiles on CTA pairs
 };
+
+static int g_wgrad_pair = getenv("SIRIUS_B200_WGRAD_PAIR") ? atoi(getenv("SIRIUS_B200_WGRAD_PAIR")) : 1;
 
 WgradPlan plan_wgrad(const GatherGeom& g) {
   WgradPlan w;
+  const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
+  w.b_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col_enabled) ? 2 : 0;
+  // CTA pairs where both operands come by TMA and the tile is not mostly padding: at least 256 filters (ragged
+  // beyond that is fine) and 192 columns
+  w.pair = g_wgrad_pair && g_force_pair != 0 && w.b_tma != 0 && g.Nout >= 256 && g.Kg >= 192 && g.src_c % 64 == 0 && sm_count() >= 2;
+  if (w.pair) {
+    w.bn = 256;
+    const int tiles = ceil_div(g.Kg, 256) * ceil_div(g.Nout, 256);
+    int want = (sm_count() / 2) / tiles;
+    const int max_by_pix = ceil_div(g.M, 4 * BK);
+    int splits = want < max_by_pix ? want : max_by_pix;
+    if (splits < 1) splits = 1;
+    if (splits > 128) splits = 128;
+    w.pix_per_split = ceil_div(ceil_div(g.M, splits), BK) * BK;
+    w.splits = ceil_div(g.M, w.pix_per_split);
+    return w;
+  }
   w.bn = g.Kg <= 64 ? 64 : 128;
   // as many splits as fit the machine in one wave (two CTAs per SM), never less than 4 k-blocks each
   const int tiles = ceil_div(g.Kg, w.bn) * ceil_div(g.Nout, BM);
@@ -1340,8 +1582,6 @@ int tc_status_fetch(int* out) {
 //   pair    0: one CTA per tile, 1: CTA pairs wherever the shape allows, -1: heuristic
 static int g_force_bn = 0;
 static int g_gather_lag = getenv("SIRIUS_B200_GATHER_LAG") ? atoi(getenv("SIRIUS_B200_GATHER_LAG")) : 0;  // 0 = stage count - 2
-static int g_im2col = getenv("SIRIUS_B200_CONV_IM2COL") ? atoi(getenv("SIRIUS_B200_CONV_IM2COL")) : 1;  // 0: gather filters wider than 1x1
-static int g_force_pair = getenv("SIRIUS_B200_CONV_PAIR") ? atoi(getenv("SIRIUS_B200_CONV_PAIR")) : -1;
 void tc_set_conv_plan(int gather, int tile_n, int pair) {
   g_force_gather = gather;
   g_force_bn = tile_n;
@@ -1356,11 +1596,12 @@ static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, 
   p.src = (const bf16*)src;
   p.bias = ep ? ep->bias : nullptr;
   p.addend = ep ? (const bf16*)ep->addend : nullptr;
+  p.addend_bits = ep && ep->addend ? ep->addend_bits : nullptr;
   p.k_blocks = ceil_div(g.Kg, BK);
   p.status = status_ptr();
   SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
   const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-  p.a_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col) ? 2 : 0;
+  p.a_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col_enabled) ? 2 : 0;
   p.im_lower_w = p.im_lower_h = p.im_flip = 0;
   p.im_stride = p.im_cpt = 1;
   if (p.a_tma == 2) {
@@ -1462,8 +1703,7 @@ int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw,
   SRT_REQUIRE(p.status != nullptr, "tcgen05 status word unavailable");
   fastdiv_make((uint32_t)(g.out_h * g.out_w), &p.hw_mul, &p.hw_shr);
   fastdiv_make((uint32_t)g.out_w, &p.w_mul, &p.w_shr);
-  const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-  p.b_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col) ? 2 : 0;
+  p.b_tma = w.b_tma;
   CUtensorMap tdy, tx;
   int rc = make_tmap_2d(&tdy, dy, (uint64_t)g.M, (uint64_t)g.Nout, 64);
   if (rc != SRT_OK) return rc;
@@ -1476,8 +1716,21 @@ int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw,
   } else {
     tx = tdy;
   }
+  if (w.pair) {
+    CUtensorMap tout;
+    rc = make_tmap_wgrad_out(&tout, p.out, (uint64_t)g.Kg, (uint64_t)g.Nout, (uint64_t)w.splits);
+    if (rc != SRT_OK) return rc;
+    rc = launch_wgrad_pair(p, tdy, tx, tout, w.splits, st);
+    if (rc != SRT_OK) return rc;
+    if (w.splits > 1) return launch_split_reduce(p.out, dw, (long long)g.Nout * g.Kg, w.splits, st);
+    return SRT_OK;
+  }
+  // Three stages of 32 KB leave room for two CTAs per SM (the split count assumes them): one CTA's prologue and
+  // its fp32 epilogue then run beside the other's main loop. Four stages (one CTA per SM) remain selectable.
+  static const int stages = getenv("SIRIUS_B200_WGRAD_STAGES") ? atoi(getenv("SIRIUS_B200_WGRAD_STAGES")) : 3;
   rc = w.bn == 64 ? launch_wgrad<64, 4>(p, tdy, tx, w.splits, st)
-                  : launch_wgrad<128, 4>(p, tdy, tx, w.splits, st);
+       : stages == 4 ? launch_wgrad<128, 4>(p, tdy, tx, w.splits, st)
+                     : launch_wgrad<128, 3>(p, tdy, tx, w.splits, st);
   if (rc != SRT_OK) return rc;
   if (w.splits > 1) return launch_split_reduce(p.out, dw, (long long)g.Nout * g.Kg, w.splits, st);
   return SRT_OK;

@@ -235,10 +235,13 @@ bn_stats_finalize(const double* __restrict__ partial, int S, int C, int64_t rows
 
 constexpr int UNR = 4;  // independent 16-byte vectors per thread in the elementwise kernels
 
+// relu_bits (optional, 8-element vectors only): byte i receives the ReLU mask of vector i of y, bit e set when
+// element e came out positive. The backward pass of a residual unit reads those bits instead of the stored y.
 template <typename T, bool HAS_RES>
 __global__ void __launch_bounds__(NT)
 bn_apply_kernel(const T* __restrict__ z, const T* __restrict__ residual, T* __restrict__ y, int64_t nvec,
-                int CV, const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
+                int CV, const float* __restrict__ scale, const float* __restrict__ shift, int relu,
+                uint8_t* __restrict__ relu_bits) {
   pdl_enter();
   constexpr int V = Vec16<T>::N;
   const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
@@ -278,6 +281,15 @@ bn_apply_kernel(const T* __restrict__ z, const T* __restrict__ residual, T* __re
     Vec16<T> o;
     o.pack(f);
     o.store(y + i * V);
+    if (V == 8 && relu_bits) {
+      // the mask of the value as stored (after rounding): what a reader of y would see
+      float r[V];
+      o.unpack(r);
+      unsigned bits = 0u;
+#pragma unroll
+      for (int v = 0; v < V; ++v) bits |= (r[v] > 0.f ? 1u : 0u) << v;
+      relu_bits[i] = (uint8_t)bits;
+    }
   }
 }
 
@@ -307,8 +319,15 @@ __device__ __forceinline__ void apply_relu_mask(float (&g)[V], const float (&x)[
   }
 }
 
-// MASK: 0 no ReLU, 1 mask from the stored output y, 2 mask recomputed from z (a compile-time choice, so the
-// per-channel vectors and loads of the unused variant take no registers)
+template <int V>
+__device__ __forceinline__ void apply_relu_bits(float (&g)[V], unsigned bits) {
+#pragma unroll
+  for (int v = 0; v < V; ++v) g[v] = ((bits >> v) & 1u) ? g[v] : 0.f;
+}
+
+// MASK: 0 no ReLU, 1 mask from the stored output y, 2 mask recomputed from z, 3 mask from one bit per element
+// (the y pointer then holds the bytes bn_apply_kernel wrote; 8-element vectors only). A compile-time choice, so
+// the per-channel vectors and loads of the unused variants take no registers.
 template <typename T, int MASK>
 __global__ void __launch_bounds__(NT, 3)
 bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __restrict__ z,
@@ -332,6 +351,7 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
       if (batch0 >= rows) break;  // the last slab may be short
       const int64_t r0 = batch0 + rl;
       Vec16<T> a[BWD_ROWS], b[BWD_ROWS], yv[BWD_ROWS];  // the stored output travels with the other two loads
+      unsigned mb[BWD_ROWS];
 #pragma unroll
       for (int i = 0; i < BWD_ROWS; ++i) {
         const int64_t r = r0 + (int64_t)i * m.RL;
@@ -340,6 +360,7 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
           a[i].load(dy + o);
           b[i].load(z + o);
           if (MASK == 1) yv[i].load(y + o);
+          if (MASK == 3) mb[i] = reinterpret_cast<const uint8_t*>(y)[o / V];
         }
       }
 #pragma unroll
@@ -349,7 +370,8 @@ bn_bwd_partial(const T* __restrict__ dy, const T* __restrict__ y, const T* __res
         float g[V], x[V];
         a[i].unpack(g);
         b[i].unpack(x);
-        if (MASK != 0) apply_relu_mask<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, scale, shift, cv * V);
+        if (MASK == 3) apply_relu_bits<V>(g, mb[i]);
+        else if (MASK != 0) apply_relu_mask<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, scale, shift, cv * V);
 #pragma unroll
         for (int v = 0; v < V; ++v) {
           sg[v] += g[v];
@@ -395,6 +417,7 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
   constexpr int V = Vec16<T>::N;
   const int64_t base = (int64_t)blockIdx.x * (NT * UNR) + threadIdx.x;
   Vec16<T> a[UNR], b[UNR], yv[UNR];
+  unsigned mb[UNR];
 #pragma unroll
   for (int u = 0; u < UNR; ++u) {
     const int64_t i = base + (int64_t)u * NT;
@@ -402,6 +425,7 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
       a[u].load(dy + i * V);
       b[u].load(z + i * V);
       if (MASK == 1) yv[u].load(y + i * V);
+      if (MASK == 3) mb[u] = reinterpret_cast<const uint8_t*>(y)[i];
     }
   }
 #pragma unroll
@@ -412,7 +436,8 @@ bn_bwd_apply(const T* __restrict__ dy, const T* __restrict__ y, const T* __restr
     float g[V], x[V];
     a[u].unpack(g);
     b[u].unpack(x);
-    if (MASK != 0) apply_relu_mask<T, V>(g, x, MASK == 1 ? &yv[u] : nullptr, scale, shift, cv * V);
+    if (MASK == 3) apply_relu_bits<V>(g, mb[u]);
+    else if (MASK != 0) apply_relu_mask<T, V>(g, x, MASK == 1 ? &yv[u] : nullptr, scale, shift, cv * V);
     if (dres) {
       Vec16<T> o;
       o.pack(g);
@@ -496,15 +521,15 @@ int bn_finalize(const void* partial, int slabs, int C, int64_t rows, const float
 
 template <typename T>
 static void bn_apply_t(const void* z, const void* residual, void* y, int64_t rows, int C,
-                       const float* scale, const float* shift, int relu, cudaStream_t st) {
+                       const float* scale, const float* shift, int relu, uint8_t* relu_bits, cudaStream_t st) {
   constexpr int V = Vec16<T>::N;
   const int64_t nvec = rows * C / V;
   if (residual)
     launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_apply_kernel<T, true>, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)z,
-               (const T*)residual, (T*)y, nvec, C / V, scale, shift, relu);
+               (const T*)residual, (T*)y, nvec, C / V, scale, shift, relu, relu_bits);
   else
     launch_pdl_if((pdl_classes() & PDL_NORM) != 0, bn_apply_kernel<T, false>, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)z,
-               (const T*)nullptr, (T*)y, nvec, C / V, scale, shift, relu);
+               (const T*)nullptr, (T*)y, nvec, C / V, scale, shift, relu, relu_bits);
 }
 
 // ---- allocation-free variant of bn_stats ----------------------------------------------------
@@ -576,10 +601,11 @@ int bn_eval_params(const float* gamma, const float* beta, const float* rmean, co
 }
 
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
-             const float* scale, const float* shift, int relu, cudaStream_t st) {
+             const float* scale, const float* shift, int relu, cudaStream_t st, uint8_t* relu_bits) {
   SRT_REQUIRE(C % 8 == 0, "bn_apply: C (%d) must be a multiple of 8", C);
-  if (dtype == SRT_F32) bn_apply_t<float>(z, residual, y, rows, C, scale, shift, relu, st);
-  else bn_apply_t<__nv_bfloat16>(z, residual, y, rows, C, scale, shift, relu, st);
+  SRT_REQUIRE(!relu_bits || (dtype == SRT_BF16 && relu), "bn_apply: the ReLU bit mask is written for bf16 tensors under a ReLU");
+  if (dtype == SRT_F32) bn_apply_t<float>(z, residual, y, rows, C, scale, shift, relu, nullptr, st);
+  else bn_apply_t<__nv_bfloat16>(z, residual, y, rows, C, scale, shift, relu, relu_bits, st);
   SRT_LAUNCH_CHECK();
   return SRT_OK;
 }
@@ -588,14 +614,16 @@ template <typename T>
 static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t rows, int C,
                          const float* gamma, const float* mean, const float* invstd,
                          const float* scale, const float* shift, int relu, void* dz, void* dres,
-                         float* dgamma, float* dbeta, void* scratch, cudaStream_t st) {
+                         float* dgamma, float* dbeta, void* scratch, cudaStream_t st, const uint8_t* relu_bits) {
   constexpr int V = Vec16<T>::N;
   RowMap m = make_row_map(rows, C, V);
   double* partial = (double*)scratch;
   float* coef = (float*)((char*)scratch + (size_t)m.S * C * 2 * sizeof(double));
-  const int mask = !relu ? 0 : (y ? 1 : 2);
+  const int mask = !relu ? 0 : relu_bits ? 3 : (y ? 1 : 2);
+  if (mask == 3) y = relu_bits;  // the kernels find the bytes where the stored output would be
   const bool early = (pdl_classes() & PDL_NORM) != 0;
-  auto partial_k = mask == 0 ? bn_bwd_partial<T, 0> : mask == 1 ? bn_bwd_partial<T, 1> : bn_bwd_partial<T, 2>;
+  auto partial_k = mask == 0 ? bn_bwd_partial<T, 0> : mask == 1 ? bn_bwd_partial<T, 1> : mask == 2 ? bn_bwd_partial<T, 2>
+                                                                                               : bn_bwd_partial<T, 3>;
   launch_pdl_if(early, partial_k, dim3(m.S, m.GY), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z, rows, C, m, mean,
                 invstd, scale, shift, relu, partial);
   SRT_LAUNCH_CHECK();
@@ -603,7 +631,7 @@ static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t r
                 gamma, invstd, dgamma, dbeta, coef);
   SRT_LAUNCH_CHECK();
   const int64_t nvec = rows * C / V;
-  auto apply_k = mask == 0 ? bn_bwd_apply<T, 0> : mask == 1 ? bn_bwd_apply<T, 1> : bn_bwd_apply<T, 2>;
+  auto apply_k = mask == 0 ? bn_bwd_apply<T, 0> : mask == 1 ? bn_bwd_apply<T, 1> : mask == 2 ? bn_bwd_apply<T, 2> : bn_bwd_apply<T, 3>;
   launch_pdl_if(early, apply_k, dim3(unrolled_grid(nvec)), dim3(NT), 0, st, (const T*)dy, (const T*)y, (const T*)z, (T*)dz,
                 (T*)dres, nvec, C / V, C, mean, (const float*)coef, scale, shift, relu);
   SRT_LAUNCH_CHECK();
@@ -613,16 +641,17 @@ static int bn_backward_t(const void* dy, const void* y, const void* z, int64_t r
 int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
                 const float* gamma, const float* mean, const float* invstd, const float* scale,
                 const float* shift, int relu, void* dz, void* dres, float* dgamma, float* dbeta,
-                void* scratch, size_t scratch_bytes, cudaStream_t st) {
+                void* scratch, size_t scratch_bytes, cudaStream_t st, const uint8_t* relu_bits) {
   SRT_REQUIRE(C % 8 == 0 && rows > 0, "bn_backward: C (%d) must be a multiple of 8", C);
   SRT_REQUIRE(scratch && scratch_bytes >= bn_scratch_bytes(rows, C),
               "bn_backward: scratch too small");
-  SRT_REQUIRE(!relu || y || (scale && shift), "bn_backward: the ReLU mask needs y or scale/shift");
+  SRT_REQUIRE(!relu || y || relu_bits || (scale && shift), "bn_backward: the ReLU mask needs y, its bits or scale/shift");
+  SRT_REQUIRE(!relu_bits || (dtype == SRT_BF16 && relu), "bn_backward: the ReLU bit mask goes with bf16 tensors under a ReLU");
   if (dtype == SRT_F32)
     return bn_backward_t<float>(dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz, dres,
-                                dgamma, dbeta, scratch, st);
+                                dgamma, dbeta, scratch, st, nullptr);
   return bn_backward_t<__nv_bfloat16>(dy, y, z, rows, C, gamma, mean, invstd, scale, shift, relu, dz,
-                                      dres, dgamma, dbeta, scratch, st);
+                                      dres, dgamma, dbeta, scratch, st, relu_bits);
 }
 
 }  // namespace srt

@@ -399,7 +399,14 @@ __device__ __forceinline__ void mask_gradient(float (&g)[V], const float (&x)[V]
   }
 }
 
-// MASK: 0 no ReLU, 1 mask from the stored output y, 2 mask recomputed from z (compile-time, so the vectors and
+template <int V>
+__device__ __forceinline__ void mask_gradient_bits(float (&g)[V], unsigned bits) {
+#pragma unroll
+  for (int v = 0; v < V; ++v) g[v] = ((bits >> v) & 1u) ? g[v] : 0.f;
+}
+
+// MASK: 0 no ReLU, 1 mask from the stored output y, 2 mask recomputed from z, 3 mask from one bit per element (the
+// y pointer then holds the bytes the forward apply kernel wrote; 8-element vectors) (compile-time, so the vectors and
 // loads of the unused variants take no registers)
 template <typename T, int MASK>
 __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
@@ -443,6 +450,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
       const int64_t r_end = r_begin + m.R < rows ? r_begin + m.R : rows;
       for (int64_t r0 = r_begin + rl; r0 < r_end; r0 += (int64_t)RPT_B * m.RL) {
         Vec16<T> a[RPT_B], b[RPT_B], yv[RPT_B];  // the stored output travels with the other two loads
+        unsigned mb[RPT_B];
 #pragma unroll
         for (int i = 0; i < RPT_B; ++i) {
           const int64_t r = r0 + (int64_t)i * m.RL;
@@ -451,6 +459,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
             a[i].load(dy + o);
             b[i].load(z + o);
             if (MASK == 1) yv[i].load(yk + o);
+            if (MASK == 3) mb[i] = reinterpret_cast<const uint8_t*>(p.y)[o / V];
           }
         }
 #pragma unroll
@@ -461,7 +470,8 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
           float g[V], x[V];
           a[i].unpack(g);
           b[i].unpack(x);
-          if (MASK != 0) mask_gradient<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, sc, sf);
+          if (MASK == 3) mask_gradient_bits<V>(g, mb[i]);
+          else if (MASK != 0) mask_gradient<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, sc, sf);
           if (dres) {
             Vec16<T> w;
             w.pack(g);
@@ -523,6 +533,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
     const int64_t r_end = r_begin + m.R < rows ? r_begin + m.R : rows;
     for (int64_t r0 = r_begin + rl; r0 < r_end; r0 += (int64_t)UNR * m.RL) {
       Vec16<T> a[UNR], b[UNR], yv[UNR];
+      unsigned mb[UNR];
 #pragma unroll
       for (int i = 0; i < UNR; ++i) {
         const int64_t r = r0 + (int64_t)i * m.RL;
@@ -531,6 +542,7 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
           a[i].load(gsrc + o);
           b[i].load(z + o);
           if (MASK == 1 && mask_again) yv[i].load(yk + o);
+          if (MASK == 3 && mask_again) mb[i] = reinterpret_cast<const uint8_t*>(p.y)[o / V];
         }
       }
 #pragma unroll
@@ -541,7 +553,8 @@ __global__ void __maxnreg__(MAX_REGS) bn_bwd_grid(const BwdArgs p) {
         float g[V], x[V];
         a[i].unpack(g);
         b[i].unpack(x);
-        if (mask_again) mask_gradient<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, sc, sf);
+        if (MASK == 3 && mask_again) mask_gradient_bits<V>(g, mb[i]);
+        else if (mask_again) mask_gradient<T, V>(g, x, MASK == 1 ? &yv[i] : nullptr, sc, sf);
         float out[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) out[v] = fmaf(ka[v], g[v], fmaf(kb[v], x[v] - mu[v], kd[v]));
@@ -645,22 +658,23 @@ int bn_forward_fused(int dtype, const void* z, const void* residual, void* y, in
 
 int bn_backward_fused(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C, const float* gamma,
                       const float* mean, const float* invstd, const float* scale, const float* shift, int relu, void* dz,
-                      void* dres, float* dgamma, float* dbeta, cudaStream_t st) {
+                      void* dres, float* dgamma, float* dbeta, cudaStream_t st, const uint8_t* relu_bits) {
   SRT_REQUIRE(bn_fused_fits(dtype, rows, C, 1), "bn_backward_fused: unsupported shape (rows %lld, C %d)", (long long)rows, C);
-  SRT_REQUIRE(!relu || y || (scale && shift), "bn_backward_fused: the ReLU mask needs y or scale/shift");
+  SRT_REQUIRE(!relu || y || relu_bits || (scale && shift), "bn_backward_fused: the ReLU mask needs y, its bits or scale/shift");
+  SRT_REQUIRE(!relu_bits || (dtype == SRT_BF16 && relu), "bn_backward_fused: the ReLU bit mask goes with bf16 tensors under a ReLU");
   BwdArgs a;
-  a.dy = dy; a.y = y; a.z = z; a.dz = dz; a.dres = dres; a.rows = rows; a.C = C;
+  a.dy = dy; a.y = relu_bits ? (const void*)relu_bits : y; a.z = z; a.dz = dz; a.dres = dres; a.rows = rows; a.C = C;
   a.m = make_grid_map(rows, C, dtype == SRT_F32 ? 4 : 8);
   a.gamma = gamma; a.mean = mean; a.invstd = invstd; a.scale = scale; a.shift = shift; a.relu = relu;
   a.dgamma = dgamma; a.dbeta = dbeta;
   a.status = tc_status_device_ptr();
   if (int rc = workspace_for(st, &a.ws)) return rc;
   const int blocks = grid_blocks(a.m);
-  const int mask = !relu ? 0 : (y ? 1 : 2);
+  const int mask = !relu ? 0 : relu_bits ? 3 : (y ? 1 : 2);
   if (dtype == SRT_F32)
     return launch_grid(mask == 0 ? bn_bwd_grid<float, 0> : mask == 1 ? bn_bwd_grid<float, 1> : bn_bwd_grid<float, 2>, blocks, st, a);
   return launch_grid(mask == 0 ? bn_bwd_grid<__nv_bfloat16, 0> : mask == 1 ? bn_bwd_grid<__nv_bfloat16, 1>
-                                                                            : bn_bwd_grid<__nv_bfloat16, 2>, blocks, st, a);
+                     : mask == 2 ? bn_bwd_grid<__nv_bfloat16, 2> : bn_bwd_grid<__nv_bfloat16, 3>, blocks, st, a);
 }
 
 }  // namespace srt

@@ -19,12 +19,15 @@ int bn_stats_static(int dtype, const void* z, int64_t rows, int C, const float* 
                     const float* beta, float eps, float momentum, float* rm, float* rv, float* mean,
                     float* invstd, float* scale, float* shift, cudaStream_t st);
 int bn_static_prepare(bool refresh, void** out);
+// relu_bits: one bit per element of a bf16 tensor under a ReLU (bit e of byte i = element 8i + e came out positive).
+// bn_apply writes them when given a buffer of rows * C / 8 bytes; the backward functions read them instead of the
+// stored output y (a sixteenth of its bytes).
 int bn_apply(int dtype, const void* z, const void* residual, void* y, int64_t rows, int C,
-             const float* scale, const float* shift, int relu, cudaStream_t st);
+             const float* scale, const float* shift, int relu, cudaStream_t st, uint8_t* relu_bits = nullptr);
 int bn_backward(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C,
                 const float* gamma, const float* mean, const float* invstd, const float* scale,
                 const float* shift, int relu, void* dz, void* dres, float* dgamma, float* dbeta,
-                void* scratch, size_t scratch_bytes, cudaStream_t st);
+                void* scratch, size_t scratch_bytes, cudaStream_t st, const uint8_t* relu_bits = nullptr);
 
 // One-launch BatchNorm (cooperative grid with two grid-wide barriers, see norm_grid.cu); bn_fused_fits says
 // whether a shape qualifies.
@@ -35,7 +38,7 @@ int bn_forward_fused(int dtype, const void* z, const void* residual, void* y, in
                      float* scale, float* shift, int relu, cudaStream_t st);
 int bn_backward_fused(int dtype, const void* dy, const void* y, const void* z, int64_t rows, int C, const float* gamma,
                       const float* mean, const float* invstd, const float* scale, const float* shift, int relu, void* dz,
-                      void* dres, float* dgamma, float* dbeta, cudaStream_t st);
+                      void* dres, float* dgamma, float* dbeta, cudaStream_t st, const uint8_t* relu_bits = nullptr);
 
 int maxpool_fwd(int dtype, const void* x, void* y, uint8_t* argmax, int N, int H, int W, int C,
                 cudaStream_t st);

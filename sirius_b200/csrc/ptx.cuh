@@ -181,6 +181,14 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
                "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+// 3-D tiled store (innermost coordinate first).
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   (uint64_t)tmap),
+               "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -630,7 +630,9 @@ int srt_gpt2_follow_infer_tpc(srt_gpt2* h, srt_comm* comm, int device, int min_t
   return g->part.configure(g->stream, g->side, comm, device, min_train_tpc, max_train_tpc, enable != 0);
 }
 
-int srt_gpt2_current_sms(srt_gpt2* h) { return h ? ((Gpt2*)h)->part.cur_sms : -1; }
+int srt_gpt2_current_sms(srt_gpt2* h) { if (!h) return -1;
+  const int w = ((Gpt2*)h)->part.cur_sms;
+  return w ? w : PartitionFollower::device_sm_count(); }
 
 int srt_gpt2_synchronize(srt_gpt2* h) {
   Gpt2* g = (Gpt2*)h;

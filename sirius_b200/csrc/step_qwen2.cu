@@ -604,7 +604,9 @@ int srt_qwen2_follow_infer_tpc(srt_qwen2* h, srt_comm* comm, int device, int min
   return g->part.configure(g->stream, g->side, comm, device, min_train_tpc, max_train_tpc, enable != 0);
 }
 
-int srt_qwen2_current_sms(srt_qwen2* h) { return h ? ((Qwen2*)h)->part.cur_sms : -1; }
+int srt_qwen2_current_sms(srt_qwen2* h) { if (!h) return -1;
+  const int w = ((Qwen2*)h)->part.cur_sms;
+  return w ? w : PartitionFollower::device_sm_count(); }
 
 int srt_qwen2_synchronize(srt_qwen2* h) {
   Qwen2* g = (Qwen2*)h;

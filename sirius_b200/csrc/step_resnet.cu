@@ -54,6 +54,11 @@ struct Unit {
   void* z;  // conv output (pre-BN)
   void* y;  // post BN (+residual) (+ReLU)
   int H, W, P, Q;  // input and output spatial size
+  // Residual units in bf16: the ReLU mask of y as one bit per element, written by the forward apply pass. The
+  // backward pass reads it instead of y (twice), and the first convolution's data gradient adds the block's output
+  // gradient under it, so no masked copy of that gradient is written either.
+  uint8_t* bits = nullptr;
+  bool bits_valid = false;  // the bits belong to the last forward pass
 };
 struct Block {
   Unit u1, u2, u3, ds;
@@ -107,6 +112,7 @@ struct Step {
   bool overlap_wgrad = getenv("SIRIUS_B200_NO_OVERLAP") == nullptr;  // weight gradients on the second stream
   bool fused_bn = getenv("SIRIUS_B200_NO_FUSED_BN") == nullptr;  // one-launch BatchNorm for the tensors that sit in L2
   bool conv_stats = getenv("SIRIUS_B200_NO_CONV_STATS") == nullptr;  // BatchNorm sums taken in the convolution's epilogue
+  bool relu_bits = getenv("SIRIUS_B200_NO_RELU_BITS") == nullptr;    // residual units keep their ReLU mask as bits (bf16)
   // Gradient buckets for the data-parallel all-reduce, in the order backward completes them (fc and the
   // last blocks first). A bucket's event fires when every gradient in its range is final.
   struct GradBucket { size_t off, count; int first_block; cudaEvent_t ev; };
@@ -553,12 +559,15 @@ int Step::alloc_activations(int B) {
   if (rc) return rc;
   const int dtype = cfg.dtype, IMG = cfg.image;
   size_t max_act = 0, max_bn_scratch = 0, max_wg_scratch = 0;
-  auto alloc_unit = [&](Unit& u) -> int {
+  auto alloc_unit = [&](Unit& u, bool with_bits = false) -> int {
     const size_t elems = (size_t)B * u.P * u.Q * u.conv.K;
     if (elems > max_act) max_act = elems;
     int r;
     if ((r = aalloc(&u.z, elems * esz))) return r;
     if ((r = aalloc(&u.y, elems * esz))) return r;
+    u.bits = nullptr;
+    u.bits_valid = false;
+    if (with_bits && relu_bits && dtype == SRT_BF16 && u.relu && (r = aalloc((void**)&u.bits, elems / 8))) return r;
     const size_t bs = bn_scratch_bytes((int64_t)B * u.P * u.Q, u.conv.K);
     if (bs > max_bn_scratch) max_bn_scratch = bs;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
@@ -574,7 +583,7 @@ int Step::alloc_activations(int B) {
   for (auto& k : blocks) {
     if ((rc = alloc_unit(k.u1))) return rc;
     if ((rc = alloc_unit(k.u2))) return rc;
-    if ((rc = alloc_unit(k.u3))) return rc;
+    if ((rc = alloc_unit(k.u3, true))) return rc;
     if (k.has_ds && (rc = alloc_unit(k.ds))) return rc;
   }
   {
@@ -762,6 +771,8 @@ int Step::forward(int B) {
     const int64_t rows = (int64_t)B * u.P * u.Q;
     const double flops = 2.0 * rows * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
     const double abytes = (double)rows * u.bn.C * esz;
+    uint8_t* bits = (residual && u.relu && !eval_mode) ? u.bits : nullptr;
+    u.bits_valid = false;
     if (!eval_mode && conv_stats && conv_fprop_stats_supported(d, dt, impl)) {
       // the convolution's epilogue leaves the column sums of z; BatchNorm finalizes them and goes straight to apply
       int slabs = 0;
@@ -772,8 +783,9 @@ int Step::forward(int B) {
             return bn_finalize(scratch, slabs, u.bn.C, rows, pf(u.bn.gamma), pf(u.bn.beta), cfg.bn_eps, cfg.bn_momentum,
                                bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift, stream); })))
         return r;
-      return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2), [&] {
-        return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream); });
+      u.bits_valid = bits != nullptr;
+      return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2) + (bits ? abytes / 16 : 0), [&] {
+        return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream, bits); });
     }
     if ((r = timed(SRT_PROF_CONV, flops, [&] { return conv_fprop(d, dt, impl, in, pw(u.conv.w), u.z, nullptr, stream); })))
       return r;
@@ -793,8 +805,9 @@ int Step::forward(int B) {
                           bf_(u.bn.rmean), bf_(u.bn.rvar), u.bn.mean, u.bn.invstd, u.bn.scale, u.bn.shift,
                           scratch, scratch_bytes, stream); })))
       return r;
-    return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2), [&] {
-      return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream); });
+    u.bits_valid = bits != nullptr;
+    return timed(SRT_PROF_NORM, abytes * (residual ? 3 : 2) + (bits ? abytes / 16 : 0), [&] {
+      return bn_apply(dt, u.z, residual, u.y, rows, u.bn.C, u.bn.scale, u.bn.shift, u.relu, stream, bits); });
   };
   const double img_px = (double)B * cfg.image * cfg.image;
   if ((rc = timed(SRT_PROF_OTHER, img_px * (3 * 4 + kStemCpad * esz), [&] {
@@ -849,25 +862,29 @@ int Step::backward(int B) {
 
   // gradient through conv+BN(+ReLU): dy (w.r.t. u.y) -> dz, filter gradient into G
   const bool fork = use_side();
-  auto unit_bwd = [&](Unit& u, const void* dy, const void* in, void* dz, void* dres) -> int {
+  // res_unit: the unit's output had the residual added before its ReLU, so the mask cannot be recomputed from z:
+  // it comes from the bits the forward pass left, or from the stored y. dres (optional) receives the masked gradient.
+  auto unit_bwd = [&](Unit& u, const void* dy, const void* in, void* dz, void* dres, bool res_unit) -> int {
     if (int c = checkpoint()) return c;
     const int64_t rows = (int64_t)B * u.P * u.Q;
     int r;
     if ((r = before_write(dz))) return r;
     if (dres && (r = before_write(dres))) return r;
-    // two passes over (dy, z[, y]) plus the dz (and masked-gradient) writes
+    const uint8_t* bits = res_unit && u.bits_valid ? u.bits : nullptr;
+    const void* ymask = res_unit && !bits ? u.y : nullptr;
+    // two passes over (dy, z[, y or its bits]) plus the dz (and masked-gradient) writes
     const double abytes = (double)rows * u.bn.C * esz;
-    const double bn_bytes = abytes * ((dres ? 3 : 2) * 2 + 1 + (dres ? 1 : 0));
+    const double bn_bytes = abytes * ((2.0 + (ymask ? 1.0 : bits ? 1.0 / 16 : 0.0)) * 2 + 1 + (dres ? 1 : 0));
     if (fused_bn && bn_fused_pays(dt, rows, u.bn.C, 1)) {
       if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
-            return bn_backward_fused(dt, dy, dres ? u.y : nullptr, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean, u.bn.invstd,
-                                     u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma), gf(u.bn.beta), stream); })))
+            return bn_backward_fused(dt, dy, ymask, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean, u.bn.invstd,
+                                     u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma), gf(u.bn.beta), stream, bits); })))
         return r;
     } else if ((r = timed(SRT_PROF_NORM, bn_bytes, [&] {
           // units without a residual recompute the ReLU mask from z instead of reading y
-          return bn_backward(dt, dy, dres ? u.y : nullptr, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean,
+          return bn_backward(dt, dy, ymask, u.z, rows, u.bn.C, pf(u.bn.gamma), u.bn.mean,
                              u.bn.invstd, u.bn.scale, u.bn.shift, u.relu, dz, dres, gf(u.bn.gamma),
-                             gf(u.bn.beta), scratch, scratch_bytes, stream); })))
+                             gf(u.bn.beta), scratch, scratch_bytes, stream, bits); })))
       return r;
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
     const double flops = 2.0 * rows * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
@@ -889,9 +906,9 @@ int Step::backward(int B) {
     }
     return SRT_OK;
   };
-  auto unit_dgrad = [&](Unit& u, const void* dz, void* dx, const void* addend) -> int {
+  auto unit_dgrad = [&](Unit& u, const void* dz, void* dx, const void* addend, const uint8_t* addend_bits = nullptr) -> int {
     srt_conv_desc d = {B, u.H, u.W, u.conv.C, u.conv.K, u.conv.R, u.conv.S, u.conv.stride, u.conv.pad, u.P, u.Q};
-    srt_conv_epilogue ep = {nullptr, addend};
+    srt_conv_epilogue ep = {nullptr, addend, addend_bits};
     const double flops = 2.0 * B * u.P * u.Q * u.conv.K * u.conv.R * u.conv.S * u.conv.C;
     if (int r = before_write(dx)) return r;
     if (s2_fast(u.conv) && u.H % 2 == 0 && u.W % 2 == 0)
@@ -907,17 +924,22 @@ int Step::backward(int B) {
     const void* x_in = i == 0 ? pool_y : blocks[i - 1].u3.y;
     // T0 = dout. u3: dz3 -> D, masked dout -> T2
     void* D = next_dz();
-    if ((rc = unit_bwd(k.u3, T[0], k.u2.y, D, T[2]))) return rc;
+    // With the mask bits of the block's output at hand (bf16), a block without a downsample branch needs no masked
+    // copy of dout: the first convolution's data gradient adds dout under the bits in its epilogue.
+    const bool masked_add = !k.has_ds && k.u3.bits_valid && !s2_fast(k.u1.conv);
+    if ((rc = unit_bwd(k.u3, T[0], k.u2.y, D, masked_add ? nullptr : T[2], true))) return rc;
     if ((rc = unit_dgrad(k.u3, D, T[3], nullptr))) return rc;        // dy2 -> T3
     D = next_dz();
-    if ((rc = unit_bwd(k.u2, T[3], k.u1.y, D, nullptr))) return rc;   // dz2 -> D
+    if ((rc = unit_bwd(k.u2, T[3], k.u1.y, D, nullptr, false))) return rc;   // dz2 -> D
     if ((rc = unit_dgrad(k.u2, D, T[3], nullptr))) return rc;        // dy1 -> T3
     D = next_dz();
-    if ((rc = unit_bwd(k.u1, T[3], x_in, D, nullptr))) return rc;     // dz1 -> D
+    if ((rc = unit_bwd(k.u1, T[3], x_in, D, nullptr, false))) return rc;     // dz1 -> D
     if (k.has_ds) {
-      if ((rc = unit_bwd(k.ds, T[2], x_in, T[3], nullptr))) return rc;   // dz_ds -> T3
+      if ((rc = unit_bwd(k.ds, T[2], x_in, T[3], nullptr, false))) return rc;   // dz_ds -> T3
       if ((rc = unit_dgrad(k.ds, T[3], T[4], nullptr))) return rc;     // dx_ds -> T4
       if ((rc = unit_dgrad(k.u1, D, T[4], T[4]))) return rc;           // dx = dgrad(dz1) + dx_ds
+    } else if (masked_add) {
+      if ((rc = unit_dgrad(k.u1, D, T[4], T[0], k.u3.bits))) return rc;  // dx = dgrad(dz1) + dout under the ReLU mask
     } else {
       if ((rc = unit_dgrad(k.u1, D, T[4], T[2]))) return rc;           // dx = dgrad(dz1) + masked dout
     }
@@ -933,7 +955,7 @@ int Step::backward(int B) {
   if ((rc = timed(SRT_PROF_OTHER, pool_in * 1.25 + pool_in / 4 / esz, [&] {
         return maxpool_bwd(dt, T[0], pool_arg, T[3], B, stem.P, stem.Q, 64, stream); })))
     return rc;
-  if ((rc = unit_bwd(stem, T[3], x0, next_dz(), nullptr))) return rc;
+  if ((rc = unit_bwd(stem, T[3], x0, next_dz(), nullptr, false))) return rc;
   if ((rc = join_side())) return rc;
   return bucket_ready((int)buckets.size() - 1, false);
 }

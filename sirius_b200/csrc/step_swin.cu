@@ -607,7 +607,9 @@ int srt_swin_follow_infer_tpc(srt_swin* h, srt_comm* comm, int device, int min_t
   return g->part.configure(g->stream, g->side, comm, device, min_train_tpc, max_train_tpc, enable != 0);
 }
 
-int srt_swin_current_sms(srt_swin* h) { return h ? ((Swin*)h)->part.cur_sms : -1; }
+int srt_swin_current_sms(srt_swin* h) { if (!h) return -1;
+  const int w = ((Swin*)h)->part.cur_sms;
+  return w ? w : PartitionFollower::device_sm_count(); }
 
 int srt_swin_synchronize(srt_swin* h) {
   Swin* g = (Swin*)h;

@@ -29,10 +29,10 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _ep(bias, addend):
+def _ep(bias, addend, addend_bits=None):
     if bias is None and addend is None:
         return None
-    return C.byref(ConvEpilogue(_p(bias), _p(addend)))
+    return C.byref(ConvEpilogue(_p(bias), _p(addend), _p(addend_bits)))
 
 
 def conv_fprop(x, w, stride, pad, bias=None, addend=None, impl=IMPL_AUTO, out=None):
@@ -74,12 +74,12 @@ def filter_transpose(w):
     return wt
 
 
-def conv_dgrad(dy, wt, x_shape, stride, pad, addend=None, impl=IMPL_AUTO):
+def conv_dgrad(dy, wt, x_shape, stride, pad, addend=None, impl=IMPL_AUTO, addend_bits=None):
     N, H, W, Cin = x_shape
     _, R, S, K = wt.shape
     d = ConvDesc.make(N, H, W, Cin, K, R, S, stride, pad)
     dx = torch.empty((N, H, W, Cin), dtype=dy.dtype, device=dy.device)
-    call("srt_conv_dgrad", C.byref(d), _dt(dy), impl, _p(dy), _p(wt), _p(dx), _ep(None, addend), _stream())
+    call("srt_conv_dgrad", C.byref(d), _dt(dy), impl, _p(dy), _p(wt), _p(dx), _ep(None, addend, addend_bits), _stream())
     return dx
 
 
@@ -116,6 +116,28 @@ def bn_apply(z, scale, shift, residual=None, relu=True):
     call("srt_bn_apply", _dt(z), _p(z), _p(residual), _p(y), z.numel() // Cc, Cc, _p(scale), _p(shift),
          int(relu), _stream())
     return y
+
+
+def bn_apply_bits(z, scale, shift, residual=None):
+    """bn_apply under a ReLU that also returns the mask as one bit per element (uint8 [numel / 8])."""
+    Cc = z.shape[-1]
+    y = torch.empty_like(z)
+    bits = torch.empty(z.numel() // 8, dtype=torch.uint8, device=z.device)
+    call("srt_bn_apply_bits", _dt(z), _p(z), _p(residual), _p(y), z.numel() // Cc, Cc, _p(scale), _p(shift), _p(bits), _stream())
+    return y, bits
+
+
+def bn_backward_bits(dy, bits, z, gamma, mean, invstd, want_dresidual=False, one_launch=False):
+    Cc = z.shape[-1]
+    rows = z.numel() // Cc
+    dz = torch.empty_like(z)
+    dres = torch.empty_like(z) if want_dresidual else None
+    dgamma = torch.empty(Cc, dtype=torch.float32, device=z.device)
+    dbeta = torch.empty_like(dgamma)
+    scratch, n = bn_scratch(rows, Cc, z.device)
+    call("srt_bn_backward_bits", _dt(z), _p(dy), _p(bits), _p(z), rows, Cc, _p(gamma), _p(mean), _p(invstd), _p(dz), _p(dres),
+         _p(dgamma), _p(dbeta), _p(scratch), n, int(one_launch), _stream())
+    return dz, dres, dgamma, dbeta
 
 
 def bn_backward(dy, y, z, gamma, mean, invstd, relu=True, want_dresidual=False, scale=None, shift=None):

@@ -213,7 +213,11 @@ def test_conv_im2col_tma_equals_gather_bitwise(case):
         torch.cuda.synchronize()
         assert ops.tc_status() == 0
         for name, a, b in zip(("fprop", "dgrad", "wgrad"), got, base):
-            assert torch.equal(a, b), (case[0], plan, name)
+            if name == "wgrad" and plan[2] == 1:
+                # CTA pairs split the pixel range differently: the same sums in another fp32 order
+                assert _err(a, b.float().cpu()) < 1e-5, (case[0], plan, name)
+            else:
+                assert torch.equal(a, b), (case[0], plan, name)
     for name, a, r in zip(("fprop", "dgrad", "wgrad"), base, ref):
         assert _err(a, r) < 2e-2, (case[0], name)
 
@@ -339,6 +343,47 @@ def test_batchnorm_mask_recomputed_from_z_is_identical(dtype):
     b = ops.bn_backward(dy, None, z, gamma, mean, invstd, relu=True, scale=scale, shift=shift)
     torch.cuda.synchronize()
     assert torch.equal(a[0], b[0]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+
+
+@pytest.mark.parametrize("shape", [(16, 14, 14, 256), (3, 7, 7, 2048), (5, 9, 11, 48), (64, 28, 28, 128)], ids=str)
+def test_relu_bit_mask_replaces_the_stored_output_bit_for_bit(shape):
+    """A residual unit's ReLU mask as one bit per element: the forward apply pass writes it next to y, both backward
+    paths (three kernels, one launch) read it where they would read y and give the same bits, and a data gradient
+    that adds dout under the bits equals one that adds the masked copy."""
+    bf = torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    C = shape[-1]
+    z = (torch.randn(shape, generator=g) * 2 + 0.3).to(DEV, bf)
+    res = torch.randn(shape, generator=g).to(DEV, bf)
+    dy = torch.randn(shape, generator=g).to(DEV, bf)
+    gamma, beta = (torch.rand(C, generator=g) + 0.5).to(DEV), torch.randn(C, generator=g).to(DEV)
+    mean, invstd, scale, shift = ops.bn_stats(z, gamma, beta, None, None)
+    y = ops.bn_apply(z, scale, shift, residual=res, relu=True)
+    y2, bits = ops.bn_apply_bits(z, scale, shift, residual=res)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    want = ((y.reshape(-1, 8) > 0).to(torch.int32) << torch.arange(8, device=DEV, dtype=torch.int32)).sum(1).to(torch.uint8)
+    assert torch.equal(bits, want)
+    for one_launch in (False, True):
+        for want_dres in (True, False):
+            ref = (ops.bn_backward_fused if one_launch else ops.bn_backward)(dy, y, z, gamma, mean, invstd, relu=True,
+                                                                             want_dresidual=want_dres)
+            got = ops.bn_backward_bits(dy, bits, z, gamma, mean, invstd, want_dresidual=want_dres, one_launch=one_launch)
+            torch.cuda.synchronize()
+            for name, a, b in zip(("dz", "dres", "dgamma", "dbeta"), got, ref):
+                assert (a is None and b is None) or torch.equal(a, b), (name, one_launch, want_dres)
+    # dx = dgrad(dz) + dout under the mask, against dx = dgrad(dz) + (masked copy of dout)
+    K = 64
+    w = (torch.randn(K, 1, 1, C, generator=g) * C ** -0.5).to(DEV, bf)
+    dz1 = torch.randn(*shape[:3], K, generator=g).to(DEV, bf)
+    wt = ops.filter_transpose(w)
+    masked = torch.where(y > 0, dy, torch.zeros_like(dy))
+    for impl in (IMPL_TCGEN05, IMPL_SIMT):
+        a = ops.conv_dgrad(dz1, wt, shape, 1, 0, addend=masked, impl=impl)
+        b = ops.conv_dgrad(dz1, wt, shape, 1, 0, addend=dy, addend_bits=bits, impl=impl)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b), impl
+    assert ops.tc_status() == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])

@@ -125,7 +125,7 @@ BN_CASES = {
 }
 
 
-def run_bn_case(name, batch, iters, flush, one_launch=False):
+def run_bn_case(name, batch, iters, flush, one_launch=False, bits=False):
     """Forward (statistics + apply) and backward of one BatchNorm(+residual)+ReLU layer. The byte
     counts are the tensors each pass has to move once: forward reads z twice (statistics, apply),
     reads the residual and writes y; backward reads dy and z twice (sums, apply), the stored y twice
@@ -165,8 +165,24 @@ def run_bn_case(name, batch, iters, flush, one_launch=False):
             call("srt_bn_backward_fused", dt, P(dy), P(y if res else None), P(z), rows, C, P(gamma), P(mean), P(invstd),
                  P(scale), P(shift), 1, P(dz), P(dres), P(dgamma), P(dbeta), st())
 
+    if bits and res:
+        # residual unit as the training step runs it: the forward apply leaves the ReLU mask as one bit per element,
+        # the backward reads the bits instead of y and writes no masked copy of dy
+        mask = torch.empty(z.numel() // 8, dtype=torch.uint8, device=dev)
+
+        def fwd():
+            call("srt_bn_stats", dt, P(z), rows, C, P(gamma), P(beta), 1e-5, 0.1, P(rm), P(rv), P(mean), P(invstd),
+                 P(scale), P(shift), P(scratch), nscr, st())
+            call("srt_bn_apply_bits", dt, P(z), P(r), P(y), rows, C, P(scale), P(shift), P(mask), st())
+
+        def bwd():
+            call("srt_bn_backward_bits", dt, P(dy), P(mask), P(z), rows, C, P(gamma), P(mean), P(invstd), P(dz), None,
+                 P(dgamma), P(dbeta), P(scratch), nscr, int(one_launch), st())
+
     t = z.numel() * 2
     io = {"bn_fwd": t * (4 if res else 3), "bn_bwd": t * (8 if res else 5)}
+    if bits and res:
+        io = {"bn_fwd": t * (4 + 1 / 16), "bn_bwd": t * (5 + 2 / 16)}
     scrub = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev) if flush else None
     fwd()
     for p, fn in (("bn_fwd", fwd), ("bn_bwd", bwd)):
@@ -184,7 +200,7 @@ def run_bn_case(name, batch, iters, flush, one_launch=False):
             evs.append((e0, e1))
         torch.cuda.synchronize()
         us = sum(a.elapsed_time(b) for a, b in evs) / iters * 1e3
-        print(json.dumps({"case": name, "pass": p, "one_launch": one_launch, "batch": batch, "us": round(us, 2),
+        print(json.dumps({"case": name, "pass": p, "one_launch": one_launch, "relu_bits": bool(bits and res), "batch": batch, "us": round(us, 2),
                           "gbytes_per_s": round(io[p] / us / 1e3, 1), "mbytes": round(io[p] / 1e6, 1)}), flush=True)
 
 
@@ -196,6 +212,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--one-launch", action="store_true", help="BatchNorm cases: the one-launch kernels")
+    ap.add_argument("--relu-bits", action="store_true", help="BatchNorm residual cases: mask bits instead of the stored output")
     ap.add_argument("--plan", default="", help="fprop/dgrad plan override 'gather,tile_n,pair' (srt_conv_plan_override)")
     a = ap.parse_args()
     global PLAN
@@ -204,7 +221,7 @@ def main():
         _lib.lib().srt_conv_plan_override(*[int(v) for v in a.plan.split(",")])
     if a.which == "bn":
         for name in (BN_CASES if a.case == "all" else [a.case]):
-            run_bn_case(name, a.batch, a.iters, not a.no_flush, a.one_launch)
+            run_bn_case(name, a.batch, a.iters, not a.no_flush, a.one_launch, a.relu_bits)
         return
     for name in (CASES if a.case == "all" else [a.case]):
         run_case(name, a.batch, a.which, a.iters, not a.no_flush)

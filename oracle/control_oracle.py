@@ -3,8 +3,8 @@ INFRASTRUCTURE ONLY: never imported by the product.
 
 Each function follows the cited reference code literally (plain Python ints / floats), so the C++
 runtime can be compared with it on random inputs. The reference has no tests or golden vectors for
-these functions, so parity here is "restatement vs. restatement by independent
-code paths", pinned on the reference's source text.
+these functions, so PARITY IS UNPINNED here: the comparison is restatement against restatement
+by independent code paths, anchored on the reference's source text only.
 """
 from __future__ import annotations
 

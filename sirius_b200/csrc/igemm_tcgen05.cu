@@ -1618,6 +1618,8 @@ static int conv_gather_gemm_tc_persistent(const GatherGeom& g, const void* src, 
   // 128 columns wide (a 64-column tile would leave each CTA 32 filters per k-block): the MLP down-projections and
   // the data gradients of the wide layers of the transformer steps.
   bool pair = p.a_tma && p.k_blocks >= 32 && g.Nout >= 128 && g_force_bn != 64;
+  static const int fwd_pair_env = getenv("SIRIUS_B200_FWD_PAIR") ? atoi(getenv("SIRIUS_B200_FWD_PAIR")) : -1;
+  if (fwd_pair_env == 0) pair = false;
   if (g_force_pair == 0) pair = false;
   if (g_force_pair == 1) pair = g.Nout > 64 && g_force_bn != 64;
   if (sm_count() < 2) pair = false;

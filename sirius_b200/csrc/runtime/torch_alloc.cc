@@ -108,6 +108,7 @@ int srt_pool_init(int device, size_t nbytes, int cleanup) {
     cfg.backend = getenv("SIRIUS_B200_POOL_HOST_BACKEND") ? SRT_POOL_BACKEND_HOST : SRT_POOL_BACKEND_CUDA_VMM;
     cfg.pool_nbytes = nbytes;
     if (const char* pg = getenv("SIRIUS_B200_POOL_PAGE_MB")) cfg.page_nbytes = (size_t)atoi(pg) << 20;
+    if (const char* um = getenv("SIRIUS_B200_POOL_UNMAP_ON_RELEASE")) cfg.unmap_on_release = atoi(um) != 0;  // the reference's unmap-at-release
     int rc = srt_pool_create_shared(&cfg, name.c_str(), &d.pool);
     if (rc) return rc;
   }

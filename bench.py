@@ -29,6 +29,13 @@ ARCH, BATCH, IMAGE, CLASSES = "resnet152", 64, 224, 1000
 POOL_GB = 12.0            # COLTRAIN_SHARED_TENSOR_POOL_GB default of the reference (config.cc:57-69)
 FLOP_PER_SAMPLE = 68.85e9  # forward + backward, 2 FLOP per MAC (torch.utils.flop_counter on the CPU model)
 METRIC, UNIT = "train samples/s", "samples/s"
+# DRAM bytes per launch by kernel family (dram__bytes_read.sum + dram__bytes_write.sum of every kernel of the family in
+# one training step, divided by the family's launches): the one-pass ncu capture of a whole step summarised in
+# profiles/resnet152_bf16_b64_step_launch_list.md. A benchmark run cannot be profiled while it is timed, so these are
+# constants of that capture; they change when the kernels do.
+DRAM_BYTES_PER_LAUNCH = {"batchnorm": 23500512, "conv_fprop_dgrad": 24757257, "conv_wgrad": 27412543,
+                         "optimizer": 8842468, "other": 32372448}
+KERNEL_LAUNCHES_PER_STEP = {"batchnorm": 609, "conv_fprop_dgrad": 310, "conv_wgrad": 266, "optimizer": 157, "other": 8}
 REGIONS = 3               # timed regions per number; the median is reported
 WORKLOAD = "ResNet-152 train step (fwd+bwd+SGD-momentum), bf16, batch 64 per GPU, 3x224x224 N(0,1)"
 
@@ -276,12 +283,19 @@ def run_ours(args):
         peak = peaks["tflops"] if tensor else peaks["hbm_gbs"]
         fam[name] = {"bound": "tensor" if tensor else "hbm", "achieved": round(ach, 2), "peak": peak,
                      "unit": "TFLOP/s" if tensor else "GB/s", "frac": round(ach / peak, 4),
-                     "ms_per_step": round(d["ms"] / prof_steps, 3), "launches_per_step": d["launches"] // prof_steps}
+                     "ms_per_step": round(d["ms"] / prof_steps, 3), "launches_per_step": d["launches"] // prof_steps,
+                     # per kernel launch of the family (an operator call of the profiled pass may be two or three
+                     # kernels), so that both figures have the unit of the ncu capture
+                     "algorithmic_per_launch": round(d["work"] / prof_steps / KERNEL_LAUNCHES_PER_STEP.get(name, d["launches"] // prof_steps)),
+                     "traffic": DRAM_BYTES_PER_LAUNCH.get(name)}
     top = max(fam, key=lambda k: fam[k]["ms_per_step"]) if fam else None
     roofline = None
     if top:
         roofline = {k: fam[top][k] for k in ("bound", "achieved", "peak", "unit", "frac")}
-        roofline.update({"kernel": top, "traffic": None, "peak_source": f"of {peaks['source']}"})
+        roofline.update({"kernel": top, "traffic": fam[top]["traffic"],
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, whole-step capture "
+                                           "(profiles/resnet152_bf16_b64_step_launch_list.md)",
+                         "peak_source": f"of {peaks['source']}"})
 
     out = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,

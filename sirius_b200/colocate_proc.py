@@ -40,6 +40,18 @@ if __name__ == "__main__" and __package__ in (None, ""):
     __package__ = "sirius_b200"
 
 ARCH, IMAGE = "resnet152", 224
+_CHILDREN = []   # launchers of training processes this module has started and not yet seen exit
+
+
+def kill_children():
+    """Ends training processes still running (for a caller that has to leave early)."""
+    for launcher in list(_CHILDREN):
+        try:
+            if launcher.wait(0) is None:
+                launcher.kill()
+        except Exception:  # noqa: BLE001
+            pass
+        _CHILDREN.remove(launcher)
 
 
 def _seeded_state(arch):
@@ -177,6 +189,7 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
     args = f"role=trainer batch={batch} result={result} max-seconds={duration_s + 120}" + ("" if sm_partition else " no-sm-partition")
     launcher.launch(os.path.abspath(__file__), args, interpreter=sys.executable,
                     log_path=os.path.join(tempfile.gettempdir(), f"srt_colocate_{port}.log"))
+    _CHILDREN.append(launcher)
     ctl.set_train_pid(launcher.pid)
     t0 = time.time()
     while not os.path.exists(result + ".ready"):
@@ -258,6 +271,10 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
     with open(result + ".stop", "w") as f:
         f.write("stop")
     status = launcher.wait(120000)
+    if status is None:
+        launcher.kill()
+    if launcher in _CHILDREN:
+        _CHILDREN.remove(launcher)
     tr = json.load(open(result)) if os.path.exists(result) else {}
     for f in (result, result + ".ready", result + ".stop"):
         if os.path.exists(f):

@@ -362,9 +362,13 @@ def run_ours(args):
             extras()
         except Exception as e:  # noqa: BLE001
             failure.append(f"{type(e).__name__}: {e}"[:300])
+    import faulthandler
+    # shortly before the budget runs out, every thread's Python stack goes to stderr: says which leg and call is stuck
+    faulthandler.dump_traceback_later(max(1.0, args.extras_budget - 3.0), exit=False)
     worker = threading.Thread(target=guarded, daemon=True)
     worker.start()
     worker.join(args.extras_budget)
+    faulthandler.cancel_dump_traceback_later()
     unfinished = worker.is_alive()
     if unfinished:
         out["extras"] = f"stopped after {args.extras_budget:.0f} s: the legs that had not finished are missing from this line"

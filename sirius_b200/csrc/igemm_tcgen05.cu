@@ -362,6 +362,11 @@ igemm_wgrad_pair(const WgradParams p, const __grid_constant__ CUtensorMap tmap_d
   const uint32_t rank = cluster_ctarank();
   const int j0 = (int)(blockIdx.x >> 1) * 256 + (int)rank * 128;   // this CTA's 128 columns
   const int ko0 = (int)blockIdx.y * 256 + (int)rank * 128;         // ... and its 128 filters
+  // A CTA whose 128 filters all lie beyond the last one (the second half of a ragged last tile) still takes part in
+  // the pair's protocol, but no box of its loads or stores may lie wholly outside the tensor: it loads the first
+  // filters instead and stores nothing.
+  const bool rows_live = ko0 < Kout;
+  const int ko_load = rows_live ? ko0 : 0;
   const int pbeg = blockIdx.z * p.pix_per_split;
   const int pend = min(g.M, pbeg + p.pix_per_split);
   const int nkb = (pend - pbeg + BK - 1) / BK;
@@ -416,8 +421,8 @@ igemm_wgrad_pair(const WgradParams p, const __grid_constant__ CUtensorMap tmap_d
         if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full[s]), pair_bytes);
         const uint32_t dst = smem_u32(base + s * WP_STAGE_BYTES);
         const int pix0 = pbeg + kb * BK;
-        tma_load_2d_pair(dst, &tmap_dy, lbar, ko0, pix0);
-        tma_load_2d_pair(dst + 8192u, &tmap_dy, lbar, ko0 + 64, pix0);
+        tma_load_2d_pair(dst, &tmap_dy, lbar, ko_load, pix0);
+        tma_load_2d_pair(dst + 8192u, &tmap_dy, lbar, ko_load + 64 < Kout ? ko_load + 64 : ko_load, pix0);
         const uint32_t dstb = dst + 16384u;
         if (p.b_tma == 1) {
 #pragma unroll
@@ -474,7 +479,7 @@ igemm_wgrad_pair(const WgradParams p, const __grid_constant__ CUtensorMap tmap_d
             make_uint4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
       fence_proxy_async_smem();
       named_bar_sync(1, NPROD);
-      if (tid == 0 && ready && pair_j0 + cb * 32 < J) {
+      if (tid == 0 && ready && rows_live && pair_j0 + cb * 32 < J) {
         tma_store_3d(&tmap_out, smem_u32(stage), pair_j0 + cb * 32, ko0, (int)blockIdx.z);
         bulk_commit_group();
       }
@@ -1455,6 +1460,11 @@ WgradPlan plan_wgrad(const GatherGeom& g) {
   // CTA pairs where both operands come by TMA and the tile is not mostly padding: at least 256 filters (ragged
   // beyond that is fine) and 192 columns
   w.pair = g_wgrad_pair && g_force_pair != 0 && w.b_tma != 0 && g.Nout >= 256 && g.Kg >= 192 && g.src_c % 64 == 0 && sm_count() >= 2;
+  // ... and only grids of a single wave (every pair resident at once). A grid of several waves of clusters on the
+  // low-priority stream, beside the main stream's kernels, stopped making progress in about one process out of
+  // three (GPT-2's tied embedding, 591 tiles); the cause was not found by reading, single-wave grids ran 10^4 steps
+  // without it, so larger problems stay on the single-CTA kernel.
+  if (w.pair && ceil_div(g.Kg, 256) * ceil_div(g.Nout, 256) > sm_count() / 2) w.pair = false;
   if (w.pair) {
     w.bn = 256;
     const int tiles = ceil_div(g.Kg, 256) * ceil_div(g.Nout, 256);

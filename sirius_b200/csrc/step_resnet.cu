@@ -532,6 +532,21 @@ int Step::build_buckets(size_t bucket_elems) {
       end = start;
     }
   }
+  // The last bucket is ready only when backward ends, so its exchange is the part that cannot hide behind compute:
+  // keep it small. When "the rest" is large, cut it once more at the first block that starts at least 1 MiB into the
+  // buffer (the stem, layer1 and the head of layer2 stay: a couple of megabytes whose all-reduce is latency-bound).
+  constexpr size_t kTailElems = (size_t)1 << 18;
+  if (end > 4 * kTailElems) {
+    for (int i = 1; i < (int)blocks.size(); ++i) {
+      const size_t start = params[blocks[i].u1.conv.w].off;
+      if (start >= end) break;
+      if (start >= kTailElems) {
+        buckets.push_back({start, end - start, i, nullptr});
+        end = start;
+        break;
+      }
+    }
+  }
   buckets.push_back({0, end, -1, nullptr});  // the rest, stem included: ready when backward is
   for (auto& b : buckets) SRT_CHECK_CUDA(cudaEventCreateWithFlags(&b.ev, cudaEventDisableTiming));
   return SRT_OK;

@@ -359,6 +359,7 @@ def run_ours(args):
 
     def guarded():
         try:
+            torch.cuda.set_device(local)   # the current device is per thread
             extras()
         except Exception as e:  # noqa: BLE001
             failure.append(f"{type(e).__name__}: {e}"[:300])
@@ -734,7 +735,7 @@ def main():
                     help="cap on the CTAs NCCL's kernels occupy beside the training kernels (0 = NCCL's default)")
     ap.add_argument("--colocate-seconds", type=float, default=30.0,
                     help="length of the colocated training+inference window at N=1 (0 = skip)")
-    ap.add_argument("--extras-budget", type=float, default=420.0,
+    ap.add_argument("--extras-budget", type=float, default=300.0,
                     help="seconds the additions to the headline line (other workloads, colocation, reference-style handover, "
                          "CPU baseline) may take in total before the line is printed without the unfinished ones")
     ap.add_argument("--no-other-workloads", dest="other_workloads", action="store_false",

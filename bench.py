@@ -6,10 +6,20 @@
 
 One JSON line on stdout (rank 0). `value` is samples/s with the batch already in HBM; `e2e` is the
 same step driven through the public API from pinned host buffers (H2D of the batch and D2H of the
-loss inside the timed region). `roofline` describes the kernel family that takes the most device
-time, timed with CUDA events on the step's stream in a separate profiled pass. `cpu_baseline` is
-the CPU oracle (stock torchvision/PyTorch fp32, the reference's arithmetic path) timed on this
-box's host cores on a bounded sample.
+loss inside the timed region). Both are the median of three timed regions of exactly K steps each
+(`timed_regions_ms`), CUDA events on the step's stream, max over ranks. `roofline` describes the
+kernel family that takes the most device time, timed with CUDA events on the step's stream in a
+separate profiled pass; its `traffic` is that family's DRAM bytes per kernel launch from an ncu
+capture of a whole step. `kernel_families` carries the same for every family.
+
+Additions to the line, run after the headline numbers exist and under a time budget
+(`--extras-budget`; a leg that has not finished by then is left out and the line is printed anyway):
+`handover.unmap_on_release` (release / regain of the activation pages with the reference's
+unmap-at-release, beside the kept-mapping default), `workloads` (Swin-B batch 32 and GPT-2 small
+8 x 1024 at the same number of GPUs), `colocated` (N = 1: training next to an inference server in a
+second process, every request a memory handover and an SM-mask shrink for 30 s at 50 req/s, and the
+same with pages kept until the server idles), `cpu_baseline` (the CPU oracle: stock torchvision /
+PyTorch fp32, the reference's arithmetic path, timed on this box's host cores on a bounded sample).
 """
 from __future__ import annotations
 

@@ -374,15 +374,19 @@ def run_ours(args):
         except Exception as e:  # noqa: BLE001
             failure.append(f"{type(e).__name__}: {e}"[:300])
     import faulthandler
+    if exchange is not None:
+        exchange.close()     # the other workloads bring their own communicator
+    # with several ranks the only additions are the two other workloads (tens of seconds): a shorter leash
+    budget = args.extras_budget if world == 1 else min(args.extras_budget, 150.0)
     # shortly before the budget runs out, every thread's Python stack goes to stderr: says which leg and call is stuck
-    faulthandler.dump_traceback_later(max(1.0, args.extras_budget - 3.0), exit=False)
+    faulthandler.dump_traceback_later(max(1.0, budget - 3.0), exit=False)
     worker = threading.Thread(target=guarded, daemon=True)
     worker.start()
-    worker.join(args.extras_budget)
+    worker.join(budget)
     faulthandler.cancel_dump_traceback_later()
     unfinished = worker.is_alive()
     if unfinished:
-        out["extras"] = f"stopped after {args.extras_budget:.0f} s: the legs that had not finished are missing from this line"
+        out["extras"] = f"stopped after {budget:.0f} s: the legs that had not finished are missing from this line"
     elif failure:
         out["extras"] = "failed: " + failure[0]
     if rank == 0:

@@ -231,6 +231,11 @@ int srt_tc_status(int* status);
  *   pair    1 = two CTAs per 256-row tile (tcgen05 cta_group::2) wherever the output is wider than 64
  *           filters, 0 = always one CTA per 128-row tile, -1 = heuristic. */
 int srt_conv_plan_override(int gather, int tile_n, int pair);
+/* Process-wide: whether filter gradients may use the CTA-pair kernel (256 x 256 tiles, clusters of two) where the
+ * shape allows, or always the single-CTA kernel. on = 1 / 0 sets it, -1 only reads; returns the previous setting.
+ * srt_conv_wgrad_scratch_bytes covers both, so the switch may change between sizing and launch. Default 1; the
+ * gradient exchange (srt_ddp_create through sirius_b200.ddp) turns it off for data-parallel runs. */
+int srt_conv_wgrad_pairs(int on);
 
 /* ---- training-step executor (replaces the body of the reference's training loop:
  *      model(images) / criterion / backward / optimizer stage, train/resnet152.py:84-91, with

@@ -76,6 +76,7 @@ _SIGNATURES = {
     "srt_get_sm_mask": (None, [C.POINTER(C.c_uint64)]),
     "srt_tc_status": (None, [C.POINTER(C.c_int)]),
     "srt_conv_plan_override": (None, [_i, _i, _i]),
+    "srt_conv_wgrad_pairs": (_i, [_i]),
     "srt_bn_static_prepare": (None, []),
 }
 

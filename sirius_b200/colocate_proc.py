@@ -267,6 +267,25 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
     t_stop = time.time()
     if have_mem:
         give_back()
+    # One multi-GiB handover across the process boundary: ask training to continue at an eighth of its batch (the
+    # adjust names the batch size, as every kColocateAdjustL1 does), from the Controller call to the Done reply,
+    # per GiB of pages that became free in between; then let it grow back.
+    big = None
+    try:
+        small = max(1, batch // 8)
+        free_before = stat(FREE_PAGES)
+        t1 = time.perf_counter()
+        cid = ctl.colocate_infer_require_adjust(0, [small])
+        ctl.wait_colocate_adjust_done(0, cid, 30000)
+        dt = (time.perf_counter() - t1) * 1e3
+        freed = (stat(FREE_PAGES) - free_before) * page
+        if freed > 0:
+            big = {"target_batch": small, "freed_gib": round(freed / 2 ** 30, 3), "ms": round(dt, 3),
+                   "ms_per_gib": round(dt / (freed / 2 ** 30), 3)}
+        ctl.colocate_infer_release_adjust([batch])
+        time.sleep(0.2)                                  # a few training steps at the full batch again
+    except Exception as e:  # noqa: BLE001  (the per-request figures stand without it)
+        big = {"error": f"{type(e).__name__}: {e}"[:200]}
     ctl.inference_workload_done()
     with open(result + ".stop", "w") as f:
         f.write("stop")
@@ -301,6 +320,7 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
         "handover_ms_p99": pct(list(ho[:, 0]), 0.99) if len(ho) else None,
         "handover_gib_median": round(float(np.median(ho[:, 1])) / 2 ** 30, 3) if len(ho) else None,
         "handover_ms_per_gib": round(float(np.median(ho[:, 0] / (ho[:, 1] / 2 ** 30))), 3) if len(ho) else None,
+        "handover_multi_gib": big,
         "server_phase_ms": {k: {"p50": pct(v, 0.5), "p99": pct(v, 0.99), "max": pct(v, 1.0)} for k, v in phase.items()},
         "trainer_adjust_ms_first": [[round(x, 2) for x in a[:3]] for a in tr.get("adjust_log", [])][:4],
         "pool_gib": round(pool_bytes / 2 ** 30, 2), "train_activation_gib": round(train_bytes / 2 ** 30, 2),

@@ -61,6 +61,8 @@ void set_current_sm_mask(const SmMask& m) {
 
 int tc_status_fetch(int* out);
 void tc_set_conv_plan(int gather, int tile_n, int pair);
+void tc_set_wgrad_pairs(bool on);
+bool tc_wgrad_pairs();
 
 static int check_desc(const srt_conv_desc& d) {
   SRT_REQUIRE(d.N > 0 && d.H > 0 && d.W > 0 && d.C > 0 && d.K > 0 && d.R > 0 && d.S > 0 &&
@@ -357,6 +359,12 @@ int srt_tc_status(int* status) {
   SRT_REQUIRE(status != nullptr, "tc_status: null argument");
   return tc_status_fetch(status);
 }
+int srt_conv_wgrad_pairs(int on) {
+  const int was = tc_wgrad_pairs() ? 1 : 0;
+  if (on >= 0) tc_set_wgrad_pairs(on != 0);
+  return was;
+}
+
 int srt_conv_plan_override(int gather, int tile_n, int pair) {
   SRT_REQUIRE(gather == 0 || gather == 1, "conv_plan_override: gather must be 0 or 1");
   SRT_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256,

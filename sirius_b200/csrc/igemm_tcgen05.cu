@@ -1453,13 +1453,13 @@ struct WgradPlan {
 
 static int g_wgrad_pair = getenv("SIRIUS_B200_WGRAD_PAIR") ? atoi(getenv("SIRIUS_B200_WGRAD_PAIR")) : 1;
 
-WgradPlan plan_wgrad(const GatherGeom& g) {
+WgradPlan plan_wgrad(const GatherGeom& g, bool allow_pair = true) {
   WgradPlan w;
   const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
   w.b_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col_enabled) ? 2 : 0;
   // CTA pairs where both operands come by TMA and the tile is not mostly padding: at least 256 filters (ragged
   // beyond that is fine) and 192 columns
-  w.pair = g_wgrad_pair && g_force_pair != 0 && w.b_tma != 0 && g.Nout >= 256 && g.Kg >= 192 && g.src_c % 64 == 0 && sm_count() >= 2;
+  w.pair = allow_pair && g_wgrad_pair && g_force_pair != 0 && w.b_tma != 0 && g.Nout >= 256 && g.Kg >= 192 && g.src_c % 64 == 0 && sm_count() >= 2;
   // ... and only grids of a single wave (every pair resident at once). A grid of several waves of clusters on the
   // low-priority stream, beside the main stream's kernels, stopped making progress in about one process out of
   // three (GPT-2's tied embedding, 591 tiles); the cause was not found by reading, single-wave grids ran 10^4 steps
@@ -1592,6 +1592,9 @@ int tc_status_fetch(int* out) {
 //   pair    0: one CTA per tile, 1: CTA pairs wherever the shape allows, -1: heuristic
 static int g_force_bn = 0;
 static int g_gather_lag = getenv("SIRIUS_B200_GATHER_LAG") ? atoi(getenv("SIRIUS_B200_GATHER_LAG")) : 0;  // 0 = stage count - 2
+void tc_set_wgrad_pairs(bool on) { g_wgrad_pair = on ? 1 : 0; }
+bool tc_wgrad_pairs() { return g_wgrad_pair != 0; }
+
 void tc_set_conv_plan(int gather, int tile_n, int pair) {
   g_force_gather = gather;
   g_force_bn = tile_n;
@@ -1693,9 +1696,14 @@ int conv_gather_gemm_tc_stats(const GatherGeom& g, const void* src, const void* 
   return conv_gather_gemm_tc_persistent(g, src, Bm, D, ep, st, col_partial);
 }
 
-size_t conv_wgrad_tc_scratch_bytes(const GatherGeom& g) {
-  WgradPlan w = plan_wgrad(g);
+static size_t wgrad_plan_bytes(const GatherGeom& g, const WgradPlan& w) {
   return w.splits > 1 ? (size_t)w.splits * g.Nout * g.Kg * sizeof(float) : 0;
+}
+// Enough for either kernel: a caller sizes its scratch once, and which kernel a launch takes can change afterwards
+// (srt_conv_wgrad_pairs, a plan override).
+size_t conv_wgrad_tc_scratch_bytes(const GatherGeom& g) {
+  const size_t a = wgrad_plan_bytes(g, plan_wgrad(g, true)), b = wgrad_plan_bytes(g, plan_wgrad(g, false));
+  return a > b ? a : b;
 }
 
 int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw, void* scratch,
@@ -1703,7 +1711,7 @@ int conv_wgrad_tc(const GatherGeom& g, const void* dy, const void* x, float* dw,
   SRT_REQUIRE(g.src_c % 8 == 0 && g.Nout % 8 == 0,
               "tcgen05 wgrad: channel counts (%d, %d) must be multiples of 8", g.src_c, g.Nout);
   WgradPlan w = plan_wgrad(g);
-  const size_t need = conv_wgrad_tc_scratch_bytes(g);
+  const size_t need = wgrad_plan_bytes(g, w);
   SRT_REQUIRE(scratch_bytes >= need && (need == 0 || scratch != nullptr),
               "tcgen05 wgrad: scratch too small (%zu < %zu)", scratch_bytes, need);
   WgradParams p;

@@ -81,3 +81,27 @@ def test_gradient_exchange_entry_points_fail_cleanly_without_a_communicator():
     assert lib.srt_ddp_allreduce(None, None, 0, _lib.SRT_F32, None) != 0
     assert lib.srt_ddp_destroy(None) == 0
     assert ddp.WIRE["bf16"] == _lib.SRT_BF16
+
+
+def test_filter_gradient_pair_switch_does_not_change_the_scratch_a_caller_sized():
+    """srt_conv_wgrad_pairs flips which kernel a filter gradient takes, process-wide, at any time (the gradient
+    exchange turns the pairs off); the scratch size reported for a problem covers both kernels, so scratch sized
+    before the flip is still enough after it. The call returns the previous setting; -1 only reads."""
+    import ctypes as C
+    from sirius_b200 import _lib
+    from sirius_b200._lib import ConvDesc, IMPL_AUTO, SRT_BF16
+    lib = _lib.lib()
+    lib.srt_conv_wgrad_scratch_bytes.restype = C.c_size_t
+    start = lib.srt_conv_wgrad_pairs(-1)
+    try:
+        for shape in ((64, 14, 14, 256, 256, 3, 3, 1, 1), (64, 14, 14, 1024, 256, 1, 1, 1, 0), (64, 56, 56, 64, 64, 3, 3, 1, 1),
+                      (8192, 1, 1, 768, 50304, 1, 1, 1, 0), (64, 7, 7, 512, 2048, 1, 1, 1, 0), (5, 9, 11, 24, 40, 3, 3, 1, 1)):
+            d = ConvDesc.make(*shape)
+            assert lib.srt_conv_wgrad_pairs(1) in (0, 1)
+            on = lib.srt_conv_wgrad_scratch_bytes(C.byref(d), SRT_BF16, IMPL_AUTO)
+            assert lib.srt_conv_wgrad_pairs(0) == 1
+            off = lib.srt_conv_wgrad_scratch_bytes(C.byref(d), SRT_BF16, IMPL_AUTO)
+            assert lib.srt_conv_wgrad_pairs(-1) == 0
+            assert on == off, shape
+    finally:
+        lib.srt_conv_wgrad_pairs(start)

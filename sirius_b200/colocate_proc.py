@@ -137,7 +137,8 @@ def trainer_main(a):
 
 
 # ------------------------------------------------------------------------------------------------------ server
-def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=64, seed=0, sm_partition=True):
+def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=64, seed=0, sm_partition=True,
+        multi_gib=False):
     import torch
     from . import _lib
     from ._lib import call
@@ -272,6 +273,8 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
     # per GiB of pages that became free in between; then let it grow back.
     big = None
     try:
+        if not multi_gib:
+            raise StopIteration
         small = max(1, batch // 8)
         free_before = stat(FREE_PAGES)
         t1 = time.perf_counter()
@@ -284,6 +287,8 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
                    "ms_per_gib": round(dt / (freed / 2 ** 30), 3)}
         ctl.colocate_infer_release_adjust([batch])
         time.sleep(0.2)                                  # a few training steps at the full batch again
+    except StopIteration:
+        pass
     except Exception as e:  # noqa: BLE001  (the per-request figures stand without it)
         big = {"error": f"{type(e).__name__}: {e}"[:200]}
     ctl.inference_workload_done()
@@ -349,13 +354,16 @@ def main():
     ap.add_argument("--idle-ms", type=float, default=500.0)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--no-sm-partition", action="store_true")
+    ap.add_argument("--multi-gib", action="store_true",
+                    help="after the window, one adjust to an eighth of the batch: handover of several GiB across the processes")
     ap.add_argument("--result", default="")
     ap.add_argument("--max-seconds", type=float, default=300.0)
     a = ap.parse_args()
     if a.role == "trainer":
         trainer_main(a)
     else:
-        print(json.dumps(run(a.duration, a.rate, a.policy, a.idle_ms, a.batch, sm_partition=not a.no_sm_partition)), flush=True)
+        print(json.dumps(run(a.duration, a.rate, a.policy, a.idle_ms, a.batch, sm_partition=not a.no_sm_partition,
+                             multi_gib=a.multi_gib)), flush=True)
 
 
 if __name__ == "__main__":

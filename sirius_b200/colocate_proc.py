@@ -345,7 +345,7 @@ def run(duration_s=30.0, rate=50.0, policy="per-request", idle_ms=500.0, batch=6
     return out
 
 
-def main():
+def make_parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("--role", default="server", choices=["server", "trainer"])
     ap.add_argument("--duration", type=float, default=30.0)
@@ -358,7 +358,11 @@ def main():
                     help="after the window, one adjust to an eighth of the batch: handover of several GiB across the processes")
     ap.add_argument("--result", default="")
     ap.add_argument("--max-seconds", type=float, default=300.0)
-    a = ap.parse_args()
+    return ap
+
+
+def main():
+    a = make_parser().parse_args()
     if a.role == "trainer":
         trainer_main(a)
     else:

@@ -305,3 +305,17 @@ def test_kv_cache_pool_trades_pages_with_a_trainer():
         call("srt_adjuster_destroy", adj)
         tra.close()
         srv.close()
+
+
+def test_the_colocation_trainer_understands_the_command_line_the_launcher_builds():
+    """The two-process colocation experiment starts its trainer through TrainLauncher: the "key=value" argument string
+    the server side writes must expand (server/train_launcher.cc:213-238: "--key value", a bare key is a flag) into
+    what the trainer's own parser accepts, with and without the SM partition."""
+    from sirius_b200.colocate_proc import make_parser
+    from sirius_b200.server import ServeMode, TrainLauncher
+    launcher = TrainLauncher(ServeMode.COLOCATE_L1)
+    for extra, flag in (("", False), (" no-sm-partition", True)):
+        argv = launcher.argv("/tmp/train.py", "role=trainer batch=64 result=/tmp/r.json max-seconds=150.0" + extra)
+        assert argv[:2] == ["python", "/tmp/train.py"]
+        a = make_parser().parse_args(argv[2:])
+        assert (a.role, a.batch, a.result, a.max_seconds, a.no_sm_partition) == ("trainer", 64, "/tmp/r.json", 150.0, flag)

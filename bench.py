@@ -404,8 +404,13 @@ def run_ours(args):
         sys.stdout.flush()
         os._exit(0)
     if world > 1:
+        # a rank whose additions ran out of time has left without this barrier: do not wait for it for ever
+        leave = threading.Timer(30.0, lambda: os._exit(0))
+        leave.daemon = True
+        leave.start()
         dist.barrier()
         dist.destroy_process_group()
+        leave.cancel()
 
 
 def make_overlapped_allreduce(step, rank, world, local, args):

@@ -1453,13 +1453,17 @@ struct WgradPlan {
 
 static int g_wgrad_pair = getenv("SIRIUS_B200_WGRAD_PAIR") ? atoi(getenv("SIRIUS_B200_WGRAD_PAIR")) : 1;
 
-WgradPlan plan_wgrad(const GatherGeom& g, bool allow_pair = true) {
+// sizing = true asks what the plan would be with every process-wide switch (pair kernel, plan override, im2col) in
+// the position that allows the pair kernel: scratch sized from it stays large enough whichever way they are set later.
+WgradPlan plan_wgrad(const GatherGeom& g, bool allow_pair = true, bool sizing = false) {
   WgradPlan w;
   const bool plain = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
   w.b_tma = g_force_gather ? 0 : plain ? 1 : (im2col_ok(g) && g_im2col_enabled) ? 2 : 0;
+  const bool by_tma = sizing ? (plain || im2col_ok(g)) : w.b_tma != 0;
+  const bool switched_on = sizing || (g_wgrad_pair && g_force_pair != 0);
   // CTA pairs where both operands come by TMA and the tile is not mostly padding: at least 256 filters (ragged
   // beyond that is fine) and 192 columns
-  w.pair = allow_pair && g_wgrad_pair && g_force_pair != 0 && w.b_tma != 0 && g.Nout >= 256 && g.Kg >= 192 && g.src_c % 64 == 0 && sm_count() >= 2;
+  w.pair = allow_pair && switched_on && by_tma && g.Nout >= 256 && g.Kg >= 192 && g.src_c % 64 == 0 && sm_count() >= 2;
   // ... and only grids of a single wave (every pair resident at once). A grid of several waves of clusters on the
   // low-priority stream, beside the main stream's kernels, stopped making progress in about one process out of
   // three (GPT-2's tied embedding, 591 tiles); the cause was not found by reading, single-wave grids ran 10^4 steps
@@ -1702,7 +1706,7 @@ static size_t wgrad_plan_bytes(const GatherGeom& g, const WgradPlan& w) {
 // Enough for either kernel: a caller sizes its scratch once, and which kernel a launch takes can change afterwards
 // (srt_conv_wgrad_pairs, a plan override).
 size_t conv_wgrad_tc_scratch_bytes(const GatherGeom& g) {
-  const size_t a = wgrad_plan_bytes(g, plan_wgrad(g, true)), b = wgrad_plan_bytes(g, plan_wgrad(g, false));
+  const size_t a = wgrad_plan_bytes(g, plan_wgrad(g, true, true)), b = wgrad_plan_bytes(g, plan_wgrad(g, false));
   return a > b ? a : b;
 }
 

@@ -234,7 +234,7 @@ int srt_conv_plan_override(int gather, int tile_n, int pair);
 /* Process-wide: whether filter gradients may use the CTA-pair kernel (256 x 256 tiles, clusters of two) where the
  * shape allows, or always the single-CTA kernel. on = 1 / 0 sets it, -1 only reads; returns the previous setting.
  * srt_conv_wgrad_scratch_bytes covers both, so the switch may change between sizing and launch. Default 1; the
- * gradient exchange (srt_ddp_create through sirius_b200.ddp) turns it off for data-parallel runs. */
+ * gradient exchange (srt_ddp_create) turns it off for data-parallel runs. */
 int srt_conv_wgrad_pairs(int on);
 
 /* ---- training-step executor (replaces the body of the reference's training loop:
@@ -311,7 +311,8 @@ int srt_step_wait_event(srt_step* s, void* cuda_event);
  * srt_ddp_available() is 0 where it cannot be). Rank 0 obtains SRT_DDP_ID_BYTES of unique id and hands it to
  * the other ranks by any channel (the mailboxes of srt_dist_*, torch.distributed, a file); every rank then calls
  * srt_ddp_create with the same id, which blocks until all ranks have joined. max_ctas > 0 caps the CTAs NCCL's
- * kernels may occupy beside the training kernels (0 = NCCL's default).
+ * kernels may occupy beside the training kernels (0 = NCCL's default). Creating a communicator of more than one
+ * rank also switches the CTA-pair filter-gradient kernel off for the process (srt_conv_wgrad_pairs).
  *
  * srt_allreduce_begin enqueues, on the communication stream, one sum all-reduce per bucket
  * [offsets[i], offsets[i] + counts[i]) of the fp32 buffer `grad`, bucket i behind the CUDA event ready_events[i]

@@ -192,6 +192,8 @@ int grad_exchange_wait(Comm* c, cudaStream_t consumer) {
   return SRT_OK;
 }
 
+void tc_set_wgrad_pairs(bool on);  // igemm_tcgen05.cu
+
 }  // namespace srt
 
 using namespace srt;
@@ -239,6 +241,10 @@ int srt_ddp_create(const void* id, int rank, int world, int device, int max_ctas
     delete c;
     return rc;
   }
+  // Data-parallel runs keep every filter gradient on the single-CTA kernel: a grid of CTA pairs that is not resident
+  // all at once (NCCL's kernels hold SMs while they wait for their peers) is the one configuration of this library
+  // with an unexplained stall on record, and a stalled rank stalls every rank. srt_conv_wgrad_pairs(1) undoes it.
+  if (world > 1) tc_set_wgrad_pairs(false);
   *out = (srt_ddp*)c;
   return SRT_OK;
 }

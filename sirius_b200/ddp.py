@@ -96,10 +96,7 @@ class GradExchange:
             device = torch.cuda.current_device()
         self.device = device
         self._h = _vp()
-        # Data-parallel runs keep every filter gradient on the single-CTA kernel: a grid of CTA pairs that is not
-        # resident all at once (NCCL's kernels hold SMs while they wait for their peers) is the one configuration of
-        # this library with an unexplained stall on record, and a stalled rank stalls every rank.
-        _lib.lib().srt_conv_wgrad_pairs(0)
+        # (srt_ddp_create also switches the CTA-pair filter-gradient kernel off for the process: srt_conv_wgrad_pairs)
         uid = self._new_id()
         with _stdout_to_stderr():   # NCCL announces its version on stdout; callers may own that stream (one JSON line)
             call("srt_ddp_create", uid, rank, world, device, max_ctas, C.byref(self._h))

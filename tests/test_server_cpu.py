@@ -139,6 +139,28 @@ def test_controller_task_switch_interrupt_and_resume():
         srv.close()
 
 
+def test_controller_task_switch_l3_kills_the_training_process(tmp_path):
+    """taskswitch-l3 (server/control/controller.cc:172-182): InterruptTrain sends no message, it kills the training
+    process the launcher started (SIGKILL); with no training process it does nothing. The command id is 0 either way."""
+    nm = _name("l3")
+    srv = PyInfTraCommunicator(True, True, 1, nm)
+    ctl = Controller(srv, None, ServeMode.TASKSWITCH_L3)
+    tl = TrainLauncher(ServeMode.TASKSWITCH_L3, use_xsched=False, use_shared_tensor_train=False)
+    try:
+        assert ctl.interrupt_train() == 0                                    # no pid known: nothing happens
+        sleeper = tmp_path / "sleep.py"
+        sleeper.write_text("import time\ntime.sleep(60)\n")
+        pid = tl.launch(str(sleeper), "", interpreter=sys.executable)
+        assert tl.wait(50) is None
+        ctl.set_train_pid(pid)
+        assert ctl.interrupt_train() == 0
+        assert tl.wait(5000) == 128 + 9
+    finally:
+        tl.kill()
+        ctl.close()
+        srv.close()
+
+
 def test_resource_manager_figures_follow_the_pool_and_the_memory_model():
     nm = _name("res")
     srv = PyInfTraCommunicator(True, True, 1, nm)

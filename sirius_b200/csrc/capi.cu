@@ -1,5 +1,7 @@
 // extern "C" surface of the kernel library: argument checks, dtype / kernel-family dispatch.
 #include <stdarg.h>
+#include <time.h>
+#include <unistd.h>
 
 #include <atomic>
 #include <stdlib.h>
@@ -19,6 +21,29 @@ void set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
+}
+
+static bool env_is_one(const char* name) {
+  const char* e = getenv(name);
+  return e && e[0] == '1' && e[1] == 0;
+}
+bool log_on(LogKind kind) {
+  static const char* const names[] = {"COLTRAIN_LOG_CONTROL_STUB", "COLTRAIN_LOG_DYNAMIC_BATCH",
+                                      "COLTRAIN_LOG_NCCL_PROCESS_GROUP"};
+  return env_is_one("COLTRAIN_LOG_ALL") || env_is_one(names[kind]);
+}
+void log_line(LogKind kind, const char* fmt, ...) {
+  static const char* const tags[] = {"control_stub", "dynamic_batch", "nccl_process_group"};
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  timespec ts;
+  clock_gettime(CLOCK_REALTIME, &ts);
+  // one write per line, so lines of several ranks do not interleave inside a line
+  fprintf(stderr, "[torch_col %s %lld.%03ld pid %d] %s\n", tags[kind], (long long)ts.tv_sec, ts.tv_nsec / 1000000,
+          (int)getpid(), buf);
 }
 
 static std::atomic<long long> g_launches{0};

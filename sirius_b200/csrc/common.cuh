@@ -33,6 +33,17 @@ void set_error(const char* fmt, ...);
 
 void count_launch();  // bumps the process-wide launch counter
 
+// Diagnostic lines on stderr, silent unless the environment asks for them: the reference's
+// LOG_IF(INFO, TorchColConfig::log_*) with the same variables (pytorch/torch_col/csrc/config.cc:66-69,91-98):
+// COLTRAIN_LOG_ALL=1 or the variable of the kind. Read at every call (the call sites are per command, not per kernel).
+enum LogKind { LOG_CONTROL_STUB = 0, LOG_DYNAMIC_BATCH = 1, LOG_NCCL_PROCESS_GROUP = 2 };
+bool log_on(LogKind kind);
+void log_line(LogKind kind, const char* fmt, ...);
+#define SRT_LOG(kind, ...)                                                          \
+  do {                                                                              \
+    if (::srt::log_on(kind)) ::srt::log_line(kind, __VA_ARGS__);                    \
+  } while (0)
+
 #define SRT_LAUNCH_CHECK()                                                          \
   do {                                                                              \
     ::srt::count_launch();                                                          \

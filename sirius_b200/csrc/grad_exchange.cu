@@ -245,6 +245,8 @@ int srt_ddp_create(const void* id, int rank, int world, int device, int max_ctas
   // all at once (NCCL's kernels hold SMs while they wait for their peers) is the one configuration of this library
   // with an unexplained stall on record, and a stalled rank stalls every rank. srt_conv_wgrad_pairs(1) undoes it.
   if (world > 1) tc_set_wgrad_pairs(false);
+  SRT_LOG(LOG_NCCL_PROCESS_GROUP, "[ProcessGroupNCCL] rank %d of %d created its communicator on device %d (max CTAs %d)", rank,
+          world, device, max_ctas);
   *out = (srt_ddp*)c;
   return SRT_OK;
 }
@@ -265,6 +267,8 @@ int srt_ddp_abort(srt_ddp* h) {
   Comm* c = (Comm*)h;
   SRT_REQUIRE(c, "comm_abort: null communicator");
   if (c->comm) {
+    SRT_LOG(LOG_NCCL_PROCESS_GROUP, "[ProcessGroupNCCL] rank %d aborts its communicator (%lld exchanges so far)", c->rank,
+            (long long)c->exchanges);
     SRT_CHECK_NCCL(nccl()->CommAbort(c->comm));
     c->comm = nullptr;
   }
@@ -279,6 +283,7 @@ int srt_ddp_restart(srt_ddp* h, const void* id) {
     if (int rc = srt_ddp_abort(h)) return rc;
   }
   SRT_CHECK_CUDA(cudaSetDevice(c->device));
+  SRT_LOG(LOG_NCCL_PROCESS_GROUP, "[ProcessGroupNCCL] rank %d of %d restarts its communicator", c->rank, c->world);
   return comm_init(c, id);
 }
 

@@ -81,18 +81,23 @@ struct Stub {
 
   void process_switch(const srt_ctrl_msg& msg) {
     std::unique_lock<std::mutex> lk(mu);
+    SRT_LOG(LOG_CONTROL_STUB, "[SwitchStub] rank %d receives event %d (cmd_id %llu, value %d)", cfg.rank, msg.event,
+            (unsigned long long)msg.id, msg.value);
     switch (msg.event) {
       case SRT_EV_INTERRUPT_TRAIN:
         if (cmd.load() == SRT_EV_INTERRUPT_TRAIN && cmd_id == 0) {
           // already interrupted and answered: the memory is free, reply at once
           last_reply_cmd_id = msg.id;
           if (cfg.rank == 0 && comm) put(msg.id, SRT_EV_INTERRUPT_TRAIN_DONE, 0);
+          SRT_LOG(LOG_CONTROL_STUB, "[SwitchStub] already interrupted: InterruptTrainDone for cmd_id %llu sent at once",
+                  (unsigned long long)msg.id);
         } else {
           if (cfg.rank == 0) { flag(0, 1, 1); flag(1, 1, 0); }
           if (cfg.kill_batch_on_recv && has_killed_batch_recover.load(std::memory_order_acquire)) {
             std::unique_lock<std::mutex> step_lock(step_mu);  // never inside the optimizer step
             request_abort(1);
             has_killed_batch_recover = false;
+            SRT_LOG(LOG_CONTROL_STUB, "[SwitchStub] kill batch on InterruptTrain, cmd_id %llu", (unsigned long long)msg.id);
           }
           cmd_id = msg.id;
           cmd.store(SRT_EV_INTERRUPT_TRAIN);
@@ -124,6 +129,8 @@ struct Stub {
   void process(const srt_ctrl_msg& msg) {
     if (cfg.task_switch) return process_switch(msg);
     std::unique_lock<std::mutex> lk(mu);
+    SRT_LOG(LOG_CONTROL_STUB, "[ColocateStub] rank %d receives event %d (cmd_id %llu, value %d)", cfg.rank, msg.event,
+            (unsigned long long)msg.id, msg.value);
     switch (msg.event) {
       case SRT_EV_COLOCATE_ADJUST_L1:
       case SRT_EV_COLOCATE_ADJUST_L2: {
@@ -133,6 +140,8 @@ struct Stub {
           // the previous killed batch has not been recovered yet: memory is already released
           put(msg.id, msg.event == SRT_EV_COLOCATE_ADJUST_L1 ? SRT_EV_COLOCATE_ADJUST_L1_DONE
                                                              : SRT_EV_COLOCATE_ADJUST_L2_DONE, 0);
+          SRT_LOG(LOG_CONTROL_STUB, "[ColocateStub] killed batch not recovered yet: adjust cmd_id %llu answered at once",
+                  (unsigned long long)msg.id);
           break;
         }
         has_killed_batch_recover = false;
@@ -140,6 +149,8 @@ struct Stub {
         if (should_kill) {
           std::unique_lock<std::mutex> step_lock(step_mu);  // never inside the optimizer step
           request_abort(1);
+          SRT_LOG(LOG_CONTROL_STUB, "[ColocateStub] kill batch on adjust L1, cmd_id %llu, target batch size %d",
+                  (unsigned long long)msg.id, msg.value);
         }
         cmd.store(msg.event);
         cmd_id = msg.id;
@@ -149,7 +160,10 @@ struct Stub {
       } break;
       case SRT_EV_INFER_EXIT: {
         if (cfg.rank != 0) break;
-        if (cfg.is_colocate_l1 && will_killed_batch_reconfig.load(std::memory_order_acquire)) break;
+        if (cfg.is_colocate_l1 && will_killed_batch_reconfig.load(std::memory_order_acquire)) {
+          SRT_LOG(LOG_CONTROL_STUB, "[ColocateStub] InferExit: the killed batch is still being reconfigured, no redistribution");
+          break;
+        }
         bool all_same = true;
         for (int i = 0; i < cfg.world_size; ++i) {
           int t = 0, u = 0;
@@ -159,6 +173,7 @@ struct Stub {
             break;
           }
         }
+        SRT_LOG(LOG_CONTROL_STUB, "[ColocateStub] InferExit: %s", all_same ? "targets already published" : "redistribute the batch");
         if (!all_same && dist) srt_dbd_distribute_batch(dist, comm, 1, 0, 0);
       } break;
       case SRT_EV_INFERENCE_WORKLOAD_DONE:
@@ -272,6 +287,8 @@ static int adjust_done(Stub* s, int want_cmd, int done_event) {
   std::lock_guard<std::mutex> lk(s->mu);
   if (s->cmd.load() != want_cmd) return SRT_OK;
   if (s->comm) s->put(s->cmd_id, done_event, 0);
+  SRT_LOG(LOG_CONTROL_STUB, "[ColocateStub] rank %d replies event %d for cmd_id %llu", s->cfg.rank, done_event,
+          (unsigned long long)s->cmd_id);
   s->cmd.store(-1);
   s->cmd_id = 0;
   if (want_cmd == SRT_EV_COLOCATE_ADJUST_L1) s->request_abort(0);

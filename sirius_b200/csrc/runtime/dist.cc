@@ -217,6 +217,15 @@ static int distribute_locked(Dist* d, srt_comm* comm, bool check, bool to_all, b
     else SRT_REQUIRE(num_unproc == 0, "distribute_batch: %d samples left but no rank can take them", num_unproc);
   }
   SRT_REQUIRE(num_unproc >= 0, "distribute_batch: negative unprocessed count");
+  if (log_on(LOG_DYNAMIC_BATCH)) {
+    std::string per, tgt;
+    for (int i = 0; i < d->world; ++i) {
+      per += (i ? " " : "") + std::to_string(l->unproc_per_train[i]);
+      tgt += (i ? " " : "") + std::to_string(target_unpub[i]);
+    }
+    log_line(LOG_DYNAMIC_BATCH, "[DistributeBatch] %d unprocessed samples -> per rank [%s], target batch sizes [%s]%s",
+             num_unproc, per.c_str(), tgt.c_str(), do_distribute ? "" : " (not redistributed)");
+  }
   if (comm) {  // publish: target_batch_size := target_batch_size_unpublished
     for (int i = 0; i < d->world; ++i) {
       int rc = srt_comm_update_train_field(comm, i, SRT_TI_TARGET_BS, target_unpub[i]);
@@ -442,6 +451,8 @@ int srt_dbd_finish_batch(srt_dist* h, const int* ranges, int n_ranges, int end_o
   if (!d->lazy) { l->procing_per_train[d->rank] -= num; l->proced_per_train[d->rank] += num; }
   l->num_procing -= num;
   l->num_proced += num;
+  SRT_LOG(LOG_DYNAMIC_BATCH, "[FinishBatch] rank %d finished %d samples%s: %d unprocessed, %d processing, %d processed",
+          d->rank, num, end_of_global_batch ? " (end of global batch)" : "", l->num_unproc, l->num_procing, l->num_proced);
   if (end_of_global_batch) {
     SRT_REQUIRE(d->lazy || l->procing_per_train[d->rank] == 0,
                 "finish_batch: end of global batch with %d samples still processing", l->procing_per_train[d->rank]);
@@ -462,6 +473,8 @@ int srt_dbd_abort_batch(srt_dist* h, const int* ranges, int n_ranges, int /*end_
   if (!d->lazy) { l->procing_per_train[d->rank] -= num; l->unproc_per_train[d->rank] += num; }
   l->num_procing -= num;
   l->num_unproc += num;
+  SRT_LOG(LOG_DYNAMIC_BATCH, "[AbortBatch] rank %d gives back %d samples: %d unprocessed, %d processing, %d processed",
+          d->rank, num, l->num_unproc, l->num_procing, l->num_proced);
   return SRT_OK;
 }
 
@@ -496,6 +509,7 @@ int srt_dbd_vote_abort_last_micro_batch(srt_dist* h) {
   shm::Guard g(l->mu);
   l->vote_cnt.store(kAbortVote, std::memory_order_relaxed);
   l->vote_cv.notify_all();
+  SRT_LOG(LOG_DYNAMIC_BATCH, "[VoteAbortLastMicroBatch] rank %d", ((Dist*)h)->rank);
   return SRT_OK;
 }
 

@@ -269,6 +269,70 @@ def test_distribute_batch_matches_reference_for_every_policy():
             assert sum(got) == unproc and (pol == "simple" or min(got) >= 1)
 
 
+# ---------------------------------------------------------------- diagnostic lines
+def test_log_switches_of_the_environment_contract(dist1, capfd, monkeypatch):
+    """COLTRAIN_LOG_CONTROL_STUB / COLTRAIN_LOG_DYNAMIC_BATCH / COLTRAIN_LOG_ALL = "1" turn on the runtime's
+    diagnostic lines on stderr (the reference's LOG_IF(INFO, TorchColConfig::log_*),
+    pytorch/torch_col/csrc/config.cc:66-69,91-98); without them the runtime is silent."""
+    from sirius_b200._runtime import StubConfig
+    nm = _name("log")
+    srv = PyInfTraCommunicator(True, True, 1, nm)
+    tra = PyInfTraCommunicator(False, False, 1, nm)
+    cfg = StubConfig(0, 1, 1, 1, 16, 20, 0)
+    stub = C.c_void_p()
+    call("srt_stub_create", tra._h, None, None, C.byref(cfg), C.byref(stub))
+    D = TC._DynamicBatchDistirbutor
+    dist1.init_dynamic_batch_distributor(512, 16, 32, False, "fix")
+    D.next_epoch()
+
+    def one_adjust_and_one_batch(cmd_id):
+        srv.put_inf2tra(CtrlEvent.kColocateAdjustL1, cmd_id, 8, 0)
+        t0 = time.time()
+        while _lib.lib().srt_stub_cmd(stub) != CtrlEvent.kColocateAdjustL1:
+            assert time.time() - t0 < 5
+            time.sleep(0.005)
+        call("srt_stub_adjust_l1_done", stub)
+        call("srt_stub_set_killed_batch_recover", stub)
+        assert srv.timed_get(1000, 1, 0).event == CtrlEvent.kColocateAdjustL1Done
+        D.next_global_batch()
+        rng, last = D.get_batch(16)
+        D.abort_batch(rng, last)
+        rng, last = D.get_batch(16)
+        D.finish_batch(rng, last)
+        rng, last = D.get_batch(16)
+        D.finish_batch(rng, last)
+
+    try:
+        for v in ("COLTRAIN_LOG_ALL", "COLTRAIN_LOG_CONTROL_STUB", "COLTRAIN_LOG_DYNAMIC_BATCH"):
+            monkeypatch.delenv(v, raising=False)
+        one_adjust_and_one_batch(1)
+        assert "torch_col" not in capfd.readouterr().err
+        monkeypatch.setenv("COLTRAIN_LOG_CONTROL_STUB", "1")
+        one_adjust_and_one_batch(2)
+        err = capfd.readouterr().err
+        assert "[torch_col control_stub" in err and "kill batch on adjust L1, cmd_id 2, target batch size 8" in err
+        assert f"replies event {int(CtrlEvent.kColocateAdjustL1Done)} for cmd_id 2" in err and "dynamic_batch" not in err
+        monkeypatch.delenv("COLTRAIN_LOG_CONTROL_STUB")
+        monkeypatch.setenv("COLTRAIN_LOG_DYNAMIC_BATCH", "1")
+        one_adjust_and_one_batch(3)
+        err = capfd.readouterr().err
+        assert "control_stub" not in err
+        assert "[DistributeBatch] 32 unprocessed samples -> per rank [32]" in err
+        assert "[AbortBatch] rank 0 gives back 16 samples: 32 unprocessed, 0 processing, 0 processed" in err
+        assert "[FinishBatch] rank 0 finished 16 samples (end of global batch): 0 unprocessed, 0 processing, 32 processed" in err
+        monkeypatch.setenv("COLTRAIN_LOG_DYNAMIC_BATCH", "yes")          # only "1" counts, as in the reference
+        one_adjust_and_one_batch(4)
+        assert "torch_col" not in capfd.readouterr().err
+        monkeypatch.setenv("COLTRAIN_LOG_ALL", "1")
+        one_adjust_and_one_batch(5)
+        err = capfd.readouterr().err
+        assert "control_stub" in err and "dynamic_batch" in err
+    finally:
+        call("srt_stub_stop", stub)
+        tra.close()
+        srv.close()
+
+
 # ---------------------------------------------------------------- train adjuster
 def _make_adjuster(world, targets, init_bs, cfg):
     nm = _name("adj")

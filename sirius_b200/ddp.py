@@ -16,6 +16,7 @@ import contextlib
 import ctypes as C
 import os
 import sys
+import weakref
 from typing import Callable, Optional
 
 from . import _lib
@@ -43,6 +44,12 @@ register({
 })
 
 WIRE = {"f32": SRT_F32, "fp32": SRT_F32, "bf16": SRT_BF16}
+_LIVE = weakref.WeakSet()     # the exchanges of this process that have not been closed (torch_col.xsched.get_nccl_streams)
+
+
+def live_streams() -> list:
+    """cudaStream_t values of the communication streams NCCL work of this process is enqueued on."""
+    return [ex.stream for ex in list(_LIVE) if ex._h]
 
 
 def available() -> bool:
@@ -100,6 +107,7 @@ class GradExchange:
         uid = self._new_id()
         with _stdout_to_stderr():   # NCCL announces its version on stdout; callers may own that stream (one JSON line)
             call("srt_ddp_create", uid, rank, world, device, max_ctas, C.byref(self._h))
+        _LIVE.add(self)
 
     def _new_id(self) -> bytes:
         buf = None

@@ -365,7 +365,7 @@ def run_ours(args):
                 except Exception as e:  # noqa: BLE001
                     col[key] = {"error": f"{type(e).__name__}: {e}"[:500]}
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
-            out["cpu_baseline"] = cpu_baseline(sample_batch=16, steps=1, warmup=1)
+            out["cpu_baseline"] = cpu_baseline(sample_batch=16, steps=3, warmup=1)
 
     failure = []
 
@@ -711,7 +711,13 @@ def cpu_baseline(sample_batch, steps, warmup):
     on this box's host cores on a bounded sample of the workload."""
     from oracle import resnet_oracle as O
     sec, threads = O.time_train_step(ARCH, batch=sample_batch, image=IMAGE, steps=steps, warmup=warmup)
-    return {"value": round(sample_batch / sec, 3), "unit": UNIT, "cores": threads, "kind": "port",
+    cpu_model = None
+    try:
+        with open("/proc/cpuinfo") as f:
+            cpu_model = next((ln.split(":", 1)[1].strip() for ln in f if ln.startswith("model name")), None)
+    except OSError:
+        pass
+    return {"value": round(sample_batch / sec, 3), "unit": UNIT, "cores": threads, "cpu_model": cpu_model, "kind": "port",
             "sample": f"{steps} timed step(s) after {warmup} warm-up of batch {sample_batch} (fp32, same model, "
                       f"optimizer and input distribution; the full workload is batch {BATCH})",
             "sec_per_step": round(sec, 3)}

@@ -122,6 +122,27 @@ int srt_launcher_launch(const srt_launcher_config* cfg, const char* interpreter,
 /* *exited = 1 with the wait status in *status once the child is gone; timeout_ms = 0 polls. */
 int srt_launcher_wait(int pid, int timeout_ms, int* exited, int* status);
 int srt_launcher_kill(int pid);
+/* Supervision of a launched job (the tail of LaunchTrain, server/train_launcher.cc:335-381): waits up to timeout_ms
+ * (-1 = for ever) for `pid`. When it has ended, the controller (may be NULL) forgets the pid and is told that training
+ * has ended (Controller::TrainEnd, in case the trainer could not say so), *status gets the exit status (128 + signal
+ * for a signalled child) and *outcome says what the end means:
+ *   SRT_JOB_RUNNING   still running after timeout_ms
+ *   SRT_JOB_FINISHED  it exited by itself
+ *   SRT_JOB_KILLED    SIGKILL (task-switch l3's InterruptTrain, srt_launcher_kill, KillTrain): launch it again
+ *   SRT_JOB_FAILED    any other signal: every rank on the board of `comm` (may be NULL) is killed and the call returns
+ *                     SRT_ERR_STATE, srt_last_error() naming the signal and the batch sizes on the board (the
+ *                     reference ends the server process at this point). */
+enum { SRT_JOB_RUNNING = 0, SRT_JOB_FINISHED = 1, SRT_JOB_KILLED = 2, SRT_JOB_FAILED = 3 };
+int srt_launcher_supervise(srt_controller* c, srt_comm* comm, int pid, int timeout_ms, int* outcome, int* status);
+/* KillTrain (:410-427): SIGKILL to every rank whose TrainInfo on the board is valid; *killed (may be NULL) counts them. */
+int srt_launcher_kill_train(srt_comm* comm, int* killed);
+/* DummyAdjust (:383-408), the reference's fault injector for the adjust protocol (Config::dummy_adjust): blocks for
+ * delay_ms (-1 = the reference's 60 s), then for duration_ms (0 = 60 s) or until training is idle repeats: ColocateAdjust
+ * by one sample, wait for Done, DummyInferExit back to original_target_bs, sleep a uniform random min_gap_ms..max_gap_ms
+ * (0 = 200..1000) drawn from std::mt19937(seed; 0 = 42). *rounds (may be NULL) counts the adjusts. The controller must
+ * have been created with dummy_adjust = 1. Run it on a thread of its own. */
+int srt_launcher_dummy_adjust(srt_controller* c, int original_target_bs, int delay_ms, int duration_ms, unsigned seed,
+                              int min_gap_ms, int max_gap_ms, int* rounds);
 
 /* ---- KVCachePool (server/llm/kv_cache_pool.cc:232-347): the LLM server's KV cache in pool pages ------------
  * KV-cache pages are blocks of page_nbytes from the pool's inference allocator. When the pool cannot supply a

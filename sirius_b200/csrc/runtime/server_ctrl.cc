@@ -6,6 +6,7 @@
 #include <fcntl.h>
 #include <math.h>
 #include <signal.h>
+#include <string.h>
 #include <sys/wait.h>
 #include <unistd.h>
 
@@ -15,6 +16,7 @@
 #include <condition_variable>
 #include <map>
 #include <mutex>
+#include <random>
 #include <sstream>
 #include <string>
 #include <thread>
@@ -654,6 +656,95 @@ int srt_launcher_wait(int pid, int timeout_ms, int* exited, int* status) {
 int srt_launcher_kill(int pid) {
   SRT_REQUIRE(pid > 0, "launcher_kill: bad pid");
   if (kill(pid, SIGKILL) != 0 && errno != ESRCH) { set_error("launcher_kill: cannot signal %d", pid); return SRT_ERR_STATE; }
+  return SRT_OK;
+}
+
+// What LaunchTrain does after the fork (server/train_launcher.cc:335-381): wait for the job, tell the controller that
+// training has ended (the trainer may not have been able to), and decide what the end means.
+int srt_launcher_supervise(srt_controller* ctl, srt_comm* comm, int pid, int timeout_ms, int* outcome, int* status) {
+  SRT_REQUIRE(pid > 0 && outcome, "launcher_supervise: bad argument");
+  *outcome = SRT_JOB_RUNNING;
+  const auto give_up = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
+  int st = 0;
+  for (;;) {
+    const pid_t r = waitpid(pid, &st, WNOHANG);
+    if (r == pid) break;
+    SRT_REQUIRE(r == 0, "launcher_supervise: %d is not a child of this process", pid);
+    if (timeout_ms >= 0 && std::chrono::steady_clock::now() >= give_up) return SRT_OK;
+    std::this_thread::sleep_for(std::chrono::milliseconds(5));
+  }
+  if (status) *status = WIFEXITED(st) ? WEXITSTATUS(st) : 128 + WTERMSIG(st);
+  Controller* c = (Controller*)ctl;
+  if (c) {
+    { std::lock_guard<std::mutex> lk(c->mu); c->train_pid = -1; }
+    srt_ctrl_msg end{0, SRT_EV_TRAIN_END, 0};  // Controller::TrainEnd: the monitor thread sees the trainer's own message
+    srt_comm_put(c->comm, &end, SRT_TRA2INF, 0);
+  }
+  if (!WIFSIGNALED(st)) { *outcome = SRT_JOB_FINISHED; return SRT_OK; }
+  const int sig = WTERMSIG(st);
+  if (sig == SIGKILL) { *outcome = SRT_JOB_KILLED; return SRT_OK; }  // task-switch l3, KillTrain: start it again
+  // Any other signal is a crash. The reference ends the server here (LOG(FATAL)) after killing every rank; this call
+  // kills the ranks, records what the board says about the job and returns an error.
+  *outcome = SRT_JOB_FAILED;
+  int cur = -1, target = -1, unpub = -1, killed = 0;
+  if (comm) {
+    srt_comm_get_train_field(comm, 0, SRT_TI_CURRENT_BS, &cur);
+    srt_comm_get_train_field(comm, 0, SRT_TI_TARGET_BS, &target);
+    srt_comm_get_train_field(comm, 0, SRT_TI_TARGET_BS_UNPUBLISHED, &unpub);
+    srt_launcher_kill_train(comm, &killed);
+  }
+  set_error("training job %d failed, signal is %s; batch size on the board: current %d, target %d, unpublished %d; "
+            "%d other rank(s) killed", pid, strsignal(sig), cur, target, unpub, killed);
+  return SRT_ERR_STATE;
+}
+
+// KillTrain (server/train_launcher.cc:410-427): every rank whose entry on the board is valid gets SIGKILL.
+int srt_launcher_kill_train(srt_comm* comm, int* killed) {
+  SRT_REQUIRE(comm, "launcher_kill_train: null channel");
+  if (killed) *killed = 0;
+  int pid0 = -1, world = 0;
+  if (srt_comm_get_train_field(comm, 0, SRT_TI_PID, &pid0) != SRT_OK || pid0 == -1) return SRT_OK;  // no job on record
+  if (srt_comm_get_train_field(comm, 0, SRT_TI_WORLD_SIZE, &world) != SRT_OK) return SRT_OK;
+  for (int r = 0; r < world && r < SRT_MAX_DEVICE_NUM; ++r) {
+    int pid = -1;
+    if (srt_comm_get_train_field(comm, r, SRT_TI_PID, &pid) != SRT_OK || pid <= 0) continue;
+    if (kill(pid, SIGKILL) == 0) { if (killed) ++*killed; }
+    else SRT_REQUIRE(errno == ESRCH, "launcher_kill_train: cannot signal rank %d (pid %d)", r, pid);
+  }
+  return SRT_OK;
+}
+
+// DummyAdjust (server/train_launcher.cc:383-408): the reference's fault injector for the adjust protocol. After a delay
+// it shrinks training by one sample, waits for Done and lets it grow back, at random intervals, while training runs.
+int srt_launcher_dummy_adjust(srt_controller* ctl, int original_target_bs, int delay_ms, int duration_ms, unsigned seed,
+                              int min_gap_ms, int max_gap_ms, int* rounds) {
+  Controller* c = (Controller*)ctl;
+  SRT_REQUIRE(c && c->cfg.dummy_adjust, "launcher_dummy_adjust: needs a controller created with dummy_adjust = 1");
+  if (rounds) *rounds = 0;
+  if (delay_ms < 0) delay_ms = 60000;
+  if (duration_ms <= 0) duration_ms = 60000;
+  if (min_gap_ms <= 0) min_gap_ms = 200;
+  if (max_gap_ms < min_gap_ms) max_gap_ms = std::max(min_gap_ms, 1000);
+  const auto t_wait = std::chrono::steady_clock::now() + std::chrono::milliseconds(delay_ms);
+  while (c->idle() && std::chrono::steady_clock::now() < t_wait + std::chrono::milliseconds(duration_ms))
+    std::this_thread::sleep_for(std::chrono::milliseconds(10));  // "while train_pid == -1"
+  std::this_thread::sleep_until(t_wait);
+  std::mt19937 gen(seed ? seed : 42);
+  std::uniform_int_distribution<> gap(min_gap_ms, max_gap_ms);
+  const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(duration_ms);
+  while (std::chrono::steady_clock::now() < t_end && !c->idle()) {
+    uint64_t cid = 0, eid = 0;
+    int rc = srt_controller_colocate_adjust(ctl, 0, 1, &cid);
+    if (rc) return rc;
+    if (cid) {
+      rc = srt_controller_wait_colocate_adjust_done(ctl, 0, cid, 60000);
+      if (rc) return rc;
+    }
+    rc = srt_controller_dummy_infer_exit(ctl, 0, original_target_bs, &eid);
+    if (rc) return rc;
+    if (rounds) ++*rounds;
+    std::this_thread::sleep_for(std::chrono::milliseconds(gap(gen)));
+  }
   return SRT_OK;
 }
 

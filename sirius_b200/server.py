@@ -88,6 +88,9 @@ register({
     "srt_launcher_launch": (None, [C.POINTER(LauncherConfig), C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, _pi]),
     "srt_launcher_wait": (None, [_i, _i, _pi, _pi]),
     "srt_launcher_kill": (None, [_i]),
+    "srt_launcher_supervise": (None, [_vp, _vp, _i, _i, _pi, _pi]),
+    "srt_launcher_kill_train": (None, [_vp, _pi]),
+    "srt_launcher_dummy_adjust": (None, [_vp, _i, _i, _i, C.c_uint, _i, _i, _pi]),
     "srt_kvpool_create": (None, [_vp, _vp, _vp, C.POINTER(KvPoolConfig), C.POINTER(_vp)]),
     "srt_kvpool_destroy": (None, [_vp]),
     "srt_kvpool_set_block_shape": (None, [_vp, _i64, _i64, _i64, _i64, _sz]),
@@ -243,6 +246,13 @@ class ColdModelCache:
             self._h = _vp()
 
 
+class JobOutcome(enum.IntEnum):
+    RUNNING = 0
+    FINISHED = 1
+    KILLED = 2
+    FAILED = 3
+
+
 class TrainLauncher:
     """server/train_launcher.cc:88-311: the environment and command line a training job is started with."""
 
@@ -285,6 +295,33 @@ class TrainLauncher:
     def kill(self):
         if self.pid > 0:
             call("srt_launcher_kill", self.pid)
+
+    def supervise(self, controller=None, comm=None, timeout_ms: int = -1):
+        """(outcome, exit status) of the job: JobOutcome.RUNNING after timeout_ms, FINISHED, KILLED (SIGKILL: launch
+        it again, as the reference's Train() loop does). A job that died of another signal raises SrtError after
+        every rank on the board has been killed (server/train_launcher.cc:335-381)."""
+        out, st = _i(), _i()
+        call("srt_launcher_supervise", _h(controller), _h(comm), self.pid, timeout_ms, C.byref(out), C.byref(st))
+        if out.value != JobOutcome.RUNNING:
+            self.pid = -1
+        return JobOutcome(out.value), (st.value if out.value != JobOutcome.RUNNING else None)
+
+    @staticmethod
+    def kill_train(comm) -> int:
+        """KillTrain: SIGKILL to every rank registered on the board; returns how many were signalled."""
+        n = _i()
+        call("srt_launcher_kill_train", _h(comm), C.byref(n))
+        return n.value
+
+    @staticmethod
+    def dummy_adjust(controller, original_target_bs: int, delay_ms: int = -1, duration_ms: int = 0, seed: int = 42,
+                     min_gap_ms: int = 0, max_gap_ms: int = 0) -> int:
+        """DummyAdjust (blocking; run it on a thread): random shrink-by-one / grow-back rounds while training runs.
+        Returns the number of rounds."""
+        n = _i()
+        call("srt_launcher_dummy_adjust", _h(controller), original_target_bs, delay_ms, duration_ms, seed, min_gap_ms,
+             max_gap_ms, C.byref(n))
+        return n.value
 
 
 class KVCachePool:

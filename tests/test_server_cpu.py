@@ -16,8 +16,8 @@ import pytest
 from sirius_b200._lib import SrtError, call
 from sirius_b200._runtime import AdjusterConfig
 from sirius_b200.pool import INFER, TRAIN, PagePool
-from sirius_b200.server import (ColdModelCache, Controller, KVCachePool, ResourceManager, ServeMode, TrainLauncher,
-                                TrainStatus)
+from sirius_b200.server import (ColdModelCache, Controller, JobOutcome, KVCachePool, ResourceManager, ServeMode,
+                                TrainLauncher, TrainStatus)
 from sirius_b200.torch_col._C import CtrlEvent, PyInfTraCommunicator
 
 MB = 1 << 20
@@ -250,6 +250,109 @@ def test_train_launcher_environment_command_line_and_child(tmp_path):
     assert tl.wait(50) is None
     tl.kill()
     assert tl.wait(5000) == 128 + 9
+
+
+def test_launcher_supervises_the_job_it_started(tmp_path):
+    """The tail of LaunchTrain (server/train_launcher.cc:335-381): when the job ends the controller is told that training
+    has ended even if the trainer never said so; a normal exit is FINISHED, SIGKILL means "start it again", any other
+    signal is a crash: the other ranks on the board are killed and the call fails with what the board knew."""
+    nm = _name("sup")
+    srv = PyInfTraCommunicator(True, True, 2, nm)
+    tra = PyInfTraCommunicator(False, False, 2, nm)
+    ctl = Controller(srv, None, ServeMode.TASKSWITCH_L3)
+    tl = TrainLauncher(ServeMode.TASKSWITCH_L3, use_xsched=False, use_shared_tensor_train=False)
+    sleeper = tmp_path / "sleep.py"
+    sleeper.write_text("import time\ntime.sleep(60)\n")
+    quick = tmp_path / "quick.py"
+    quick.write_text("import sys\nsys.exit(3)\n")
+    crash = tmp_path / "crash.py"
+    crash.write_text("import os, signal, time\ntime.sleep(0.3)\nos.kill(os.getpid(), signal.SIGTERM)\ntime.sleep(60)\n")
+    other = None
+    try:
+        # 1. a job that exits by itself, having announced its start but not its end
+        tl.launch(str(quick), "", interpreter=sys.executable)
+        tra.put_tra2inf(CtrlEvent.kTrainStart, 0, 0, 0)
+        _wait(lambda: not ctl.is_train_idle())
+        assert tl.supervise(ctl, srv, 20000) == (JobOutcome.FINISHED, 3)
+        _wait(ctl.is_train_idle)
+        # 2. task-switch l3: the interrupt kills the job, supervision says "launch it again"
+        pid = tl.launch(str(sleeper), "", interpreter=sys.executable)
+        ctl.set_train_pid(pid)
+        tra.put_tra2inf(CtrlEvent.kTrainStart, 0, 0, 0)
+        _wait(lambda: not ctl.is_train_idle())
+        assert tl.supervise(ctl, srv, 50) == (JobOutcome.RUNNING, None)
+        ctl.interrupt_train()
+        assert tl.supervise(ctl, srv, 20000) == (JobOutcome.KILLED, 128 + 9)
+        _wait(ctl.is_train_idle)
+        assert ctl.interrupt_train() == 0                      # the pid is forgotten: nothing left to kill
+        # 3. a crash (SIGTERM) of rank 0 takes the other rank on the board with it
+        other = TrainLauncher(ServeMode.TASKSWITCH_L3, use_xsched=False, use_shared_tensor_train=False)
+        other.launch(str(sleeper), "", interpreter=sys.executable)
+        pid0 = tl.launch(str(crash), "", interpreter=sys.executable)
+        for r, p in enumerate((pid0, other.pid)):
+            srv.set_train_info(r, train_pid=p, train_rank=r, train_world_size=2, init_batch_size=64, current_batch_size=48,
+                               target_batch_size=48, target_batch_size_unpublished=40, model_name="resnet152")
+        with pytest.raises(SrtError, match="signal is Terminated.*current 48, target 48, unpublished 40.*1 other rank"):
+            tl.supervise(ctl, srv, 20000)
+        assert other.wait(5000) == 128 + 9
+        # KillTrain on a board without a job does nothing
+        call("srt_comm_invalidate_train_info", srv._h, 0)
+        assert TrainLauncher.kill_train(srv) == 0
+    finally:
+        tl.kill()
+        if other is not None:
+            other.kill()
+        ctl.close()
+        tra.close()
+        srv.close()
+
+
+def test_dummy_adjust_injects_shrink_and_grow_rounds_while_training_runs():
+    """DummyAdjust (server/train_launcher.cc:383-408): every round is a ColocateAdjust by one sample (sent when a plan
+    of the adjuster is still unpublished, skipped otherwise, as Controller::ColocateAdjust decides), a wait for Done and
+    a kInferExit with the original batch size; the rounds end when training does."""
+    nm = _name("dum")
+    srv = PyInfTraCommunicator(True, True, 1, nm)
+    tra = PyInfTraCommunicator(False, False, 1, nm)
+    _register_trainers(srv, 1, 32)
+    call("srt_comm_update_train_field", srv._h, 0, 6, 31)          # an unpublished plan: target 32 -> 31
+    ctl = Controller(srv, None, ServeMode.COLOCATE_L1, dummy_adjust=True)
+    seen, stop = [], threading.Event()
+
+    def trainer():
+        tra.put_tra2inf(CtrlEvent.kTrainStart, 0, 0, 0)
+        while not stop.is_set():
+            m = tra.timed_get(20, 0, 0)
+            if m is None:
+                continue
+            seen.append((int(m.event), m.value))
+            if m.event == CtrlEvent.kColocateAdjustL1:
+                tra.put_tra2inf(CtrlEvent.kColocateAdjustL1Done, m.id, 0, 0)
+            if len([e for e in seen if e[0] == CtrlEvent.kInferExit]) >= 3:
+                tra.put_tra2inf(CtrlEvent.kTrainEnd, 0, 0, 0)
+                return
+
+    th = threading.Thread(target=trainer)
+    th.start()
+    try:
+        _wait(lambda: not ctl.is_train_idle())
+        rounds = TrainLauncher.dummy_adjust(ctl, 32, delay_ms=0, duration_ms=20000, seed=42, min_gap_ms=5, max_gap_ms=15)
+        th.join(10)
+        assert rounds >= 3 and ctl.is_train_idle()
+        adjusts = [v for e, v in seen if e == CtrlEvent.kColocateAdjustL1]
+        exits = [v for e, v in seen if e == CtrlEvent.kInferExit]
+        assert adjusts[:3] == [30, 30, 30] and exits[:3] == [32, 32, 32]
+        assert [e for e, _ in seen[:4]] == [CtrlEvent.kColocateAdjustL1, CtrlEvent.kInferExit] * 2   # Done awaited in between
+        plain = Controller(srv, None, ServeMode.COLOCATE_L1)
+        with pytest.raises(SrtError, match="dummy_adjust"):
+            TrainLauncher.dummy_adjust(plain, 32, delay_ms=0, duration_ms=10)
+        plain.close()
+    finally:
+        stop.set()
+        th.join(5)
+        ctl.close()
+        tra.close()
+        srv.close()
 
 
 def test_kv_cache_pool_trades_pages_with_a_trainer():

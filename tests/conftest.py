@@ -12,6 +12,9 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 
 
+GPU_TEST_LIMIT_S = 900   # the slowest GPU test takes well under a minute
+
+
 def pytest_collection_modifyitems(config, items):
     try:
         import torch
@@ -19,6 +22,13 @@ def pytest_collection_modifyitems(config, items):
     except Exception:
         has_gpu = False
     if has_gpu:
+        # A GPU test that stops making progress sits inside a CUDA call, where a signal-based limit cannot reach it:
+        # the thread method dumps every stack and ends the run, so the device is released instead of held until
+        # whoever started the run gives up.
+        if config.pluginmanager.hasplugin("timeout"):
+            for item in items:
+                if "gpu" in item.keywords and item.get_closest_marker("timeout") is None:
+                    item.add_marker(pytest.mark.timeout(GPU_TEST_LIMIT_S, method="thread"))
         return
     skip = pytest.mark.skip(reason="no CUDA device")
     for item in items:

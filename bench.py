@@ -140,6 +140,11 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    # The headline part takes well under a minute. If it has not finished after fifteen, something on the device has
+    # stopped making progress: every thread's stack goes to stderr and the process ends, which releases the device
+    # (re-armed with the additions' own limit further down).
+    import faulthandler
+    faulthandler.dump_traceback_later(900.0, exit=True)
     torch.cuda.set_device(local)
     if world > 1:
         import datetime
@@ -375,7 +380,6 @@ def run_ours(args):
             extras()
         except Exception as e:  # noqa: BLE001
             failure.append(f"{type(e).__name__}: {e}"[:300])
-    import faulthandler
     if exchange is not None:
         exchange.close()     # the other workloads bring their own communicator
     # with several ranks the only additions are the two other workloads (tens of seconds): a shorter leash

@@ -71,6 +71,40 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_tsan() -> Path:
+    """The same library with the host runtime (csrc/runtime/*.cc: shared-memory channel, ledger, control stub, page pool,
+    allocator seam, server plane) compiled under ThreadSanitizer; the kernels and executors are the normal objects.
+    Run the CPU suite on it with
+
+        SIRIUS_B200_LIB=<printed path> LD_PRELOAD=$(gcc -print-file-name=libtsan.so) \
+        TSAN_OPTIONS="halt_on_error=0 exitcode=0 log_path=/tmp/tsan" python -m pytest tests -q -m "not gpu"
+
+    and read /tmp/tsan.<pid>; reports inside libtorch (gloo's work objects) are not this library's."""
+    build()
+    out = BUILD / "tsan"
+    out.mkdir(exist_ok=True)
+    objs = []
+    for src in _sources():
+        if src.parent.name != "runtime":
+            objs.append(BUILD / (src.stem + ".o"))
+            continue
+        obj = out / (src.stem + ".o")
+        objs.append(obj)
+        cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O1", "-g", "--expt-relaxed-constexpr",
+               "-Xcompiler", "-fPIC,-fsanitize=thread", "-x", "cu", "-c", str(src), "-o", str(obj)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError(f"nvcc (tsan) failed on {src.name}")
+    lib = out / "libsirius_b200.so"
+    cmd = [NVCC, "-shared", "-o", str(lib), *map(str, objs), "-lpthread", "-lrt", "-ldl", "-Xlinker", "-ltsan"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("link (tsan) failed")
+    return lib
+
+
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose=True)
+    p = build_tsan() if "--tsan" in sys.argv else build(force="--force" in sys.argv, verbose=True)
     print(p)

@@ -5,10 +5,13 @@ There is no fallback: if the shared library is missing or a call fails, an excep
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libsirius_b200.so"
+# SIRIUS_B200_LIB selects another build of the same sources, e.g. the ThreadSanitizer build of the host runtime
+# (`python -m sirius_b200._build --tsan`); unset, the in-tree library is the only one ever loaded.
+LIB_PATH = Path(os.environ.get("SIRIUS_B200_LIB") or _PKG / "libsirius_b200.so")
 
 SRT_F32, SRT_BF16 = 0, 1
 IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2

@@ -38,7 +38,7 @@ struct TpcData {  // SMPartitioner::TpcData
 };
 struct CommLayout {
   shm::SegHeader hdr;
-  int world_size;
+  std::atomic<int> world_size;  // read by every getter and putter while a registering rank may raise it
   shm::Mutex shm_mutex;
   Ring q[2][SRT_MAX_DEVICE_NUM];
   Group group[2];
@@ -119,7 +119,10 @@ int srt_comm_open(const char* name, int is_server, int cleanup, int train_world_
     delete c;
     return SRT_ERR_STATE;
   }
-  if (!is_server && train_world_size > 0 && c->L()->world_size == 0) c->L()->world_size = train_world_size;
+  if (!is_server && train_world_size > 0) {
+    int none = 0;
+    c->L()->world_size.compare_exchange_strong(none, train_world_size, std::memory_order_relaxed);
+  }
   *out = (srt_comm*)c;
   return SRT_OK;
 }
@@ -134,7 +137,7 @@ int srt_comm_close(srt_comm* h) {
 
 int srt_comm_world_size(srt_comm* h) {
   Comm* c = (Comm*)h;
-  return c && c->L() ? c->L()->world_size : -1;
+  return c && c->L() ? c->L()->world_size.load(std::memory_order_relaxed) : -1;
 }
 
 int srt_comm_put(srt_comm* h, const srt_ctrl_msg* msg, int direction, int rank) {
@@ -157,9 +160,9 @@ int srt_comm_put(srt_comm* h, const srt_ctrl_msg* msg, int direction, int rank) 
 int srt_comm_put_all(srt_comm* h, const srt_ctrl_msg* msgs, int n, int direction) {
   COMM_CHECK(h, 0);
   CommLayout* l = ((Comm*)h)->L();
-  SRT_REQUIRE(msgs && (n == 1 || n == l->world_size), "comm_put_all: need 1 or %d messages, got %d",
-              l->world_size, n);
-  for (int i = 0; i < l->world_size; ++i) {
+  const int world = l->world_size.load(std::memory_order_relaxed);
+  SRT_REQUIRE(msgs && (n == 1 || n == world), "comm_put_all: need 1 or %d messages, got %d", world, n);
+  for (int i = 0; i < world; ++i) {
     int rc = srt_comm_put(h, &msgs[n == 1 ? 0 : i], direction, i);
     if (rc) return rc;
   }
@@ -195,7 +198,8 @@ int srt_comm_timed_get_from_any(srt_comm* h, int timeout_ms, int direction, int*
   Group& grp = l->group[direction];
   shm::Guard gg(grp.mu);
   for (;;) {
-    for (int i = 0; i < l->world_size; ++i) {
+    const int world = l->world_size.load(std::memory_order_relaxed);
+    for (int i = 0; i < world; ++i) {
       Ring& r = l->q[direction][i];
       shm::Guard g(r.mu);
       if (ring_pop(r, out)) { *rank = i; *got = 1; return SRT_OK; }
@@ -204,7 +208,7 @@ int srt_comm_timed_get_from_any(srt_comm* h, int timeout_ms, int direction, int*
     if (timeout_ms < 0) grp.cond.wait(grp.mu);
     else if (!grp.cond.wait_until(grp.mu, dl)) {
       // one last look: a put between the scan and the wait only signals the group condition
-      for (int i = 0; i < l->world_size; ++i) {
+      for (int i = 0; i < l->world_size.load(std::memory_order_relaxed); ++i) {
         Ring& r = l->q[direction][i];
         shm::Guard g(r.mu);
         if (ring_pop(r, out)) { *rank = i; *got = 1; return SRT_OK; }
@@ -232,7 +236,9 @@ int srt_comm_set_train_info(srt_comm* h, int rank, const srt_train_info* info) {
   shm::Guard g(l->train_mu[rank]);
   l->train[rank] = *info;
   l->train[rank].model_name[255] = 0;
-  if (info->train_world_size > 0) l->world_size = std::max(l->world_size, info->train_world_size);
+  int cur = l->world_size.load(std::memory_order_relaxed);   // only ever raised
+  while (cur < info->train_world_size &&
+         !l->world_size.compare_exchange_weak(cur, info->train_world_size, std::memory_order_relaxed)) {}
   return SRT_OK;
 }
 

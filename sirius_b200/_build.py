@@ -71,17 +71,27 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
-def build_tsan() -> Path:
-    """The same library with the host runtime (csrc/runtime/*.cc: shared-memory channel, ledger, control stub, page pool,
-    allocator seam, server plane) compiled under ThreadSanitizer; the kernels and executors are the normal objects.
-    Run the CPU suite on it with
+SANITIZERS = {
+    # name: (host compiler flags, runtime libraries to link, libraries to LD_PRELOAD when the tests run under python)
+    "thread": ("-fsanitize=thread", ["-ltsan"], ["libtsan.so"]),
+    "address": ("-fsanitize=address,-fsanitize=undefined,-fno-omit-frame-pointer", ["-lasan", "-lubsan"],
+                ["libasan.so", "libubsan.so"]),
+}
 
-        SIRIUS_B200_LIB=<printed path> LD_PRELOAD=$(gcc -print-file-name=libtsan.so) \
+
+def build_sanitized(kind: str = "thread") -> Path:
+    """The same library with the host runtime (csrc/runtime/*.cc: shared-memory channel, ledger, control stub, page pool,
+    allocator seam, server plane) compiled under ThreadSanitizer ("thread") or AddressSanitizer + UBSan ("address"); the
+    kernels and executors are the normal objects. Run the CPU suite on it with
+
+        SIRIUS_B200_LIB=<printed path> LD_PRELOAD="$(gcc -print-file-name=libtsan.so)" \
         TSAN_OPTIONS="halt_on_error=0 exitcode=0 log_path=/tmp/tsan" python -m pytest tests -q -m "not gpu"
 
-    and read /tmp/tsan.<pid>; reports inside libtorch (gloo's work objects) are not this library's."""
+    (address: libasan.so and libubsan.so preloaded, ASAN_OPTIONS="detect_leaks=0:halt_on_error=0:log_path=/tmp/asan")
+    and read the log files; reports inside libtorch (gloo's work objects, OpenMP loops) are not this library's."""
+    flags, link, _ = SANITIZERS[kind]
     build()
-    out = BUILD / "tsan"
+    out = BUILD / f"sanitize_{kind}"
     out.mkdir(exist_ok=True)
     objs = []
     for src in _sources():
@@ -91,20 +101,27 @@ def build_tsan() -> Path:
         obj = out / (src.stem + ".o")
         objs.append(obj)
         cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O1", "-g", "--expt-relaxed-constexpr",
-               "-Xcompiler", "-fPIC,-fsanitize=thread", "-x", "cu", "-c", str(src), "-o", str(obj)]
+               "-Xcompiler", "-fPIC," + flags, "-x", "cu", "-c", str(src), "-o", str(obj)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)
-            raise RuntimeError(f"nvcc (tsan) failed on {src.name}")
+            raise RuntimeError(f"nvcc ({kind} sanitizer) failed on {src.name}")
     lib = out / "libsirius_b200.so"
-    cmd = [NVCC, "-shared", "-o", str(lib), *map(str, objs), "-lpthread", "-lrt", "-ldl", "-Xlinker", "-ltsan"]
+    cmd = [NVCC, "-shared", "-o", str(lib), *map(str, objs), "-lpthread", "-lrt", "-ldl"]
+    for l in link:
+        cmd += ["-Xlinker", l]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
-        raise RuntimeError("link (tsan) failed")
+        raise RuntimeError(f"link ({kind} sanitizer) failed")
     return lib
 
 
 if __name__ == "__main__":
-    p = build_tsan() if "--tsan" in sys.argv else build(force="--force" in sys.argv, verbose=True)
+    if "--tsan" in sys.argv:
+        p = build_sanitized("thread")
+    elif "--asan" in sys.argv:
+        p = build_sanitized("address")
+    else:
+        p = build(force="--force" in sys.argv, verbose=True)
     print(p)

@@ -540,6 +540,86 @@ def test_pool_random_workload_keeps_invariants():
         call("srt_pool_destroy", h)
 
 
+def test_pool_and_channel_under_several_threads():
+    """Six threads allocate, tag, check and free on both allocators of one pool (with empty_cache calls in between)
+    while four putters and three getters share one channel: no allocation overlaps another live one (every block keeps
+    its tag), the page accounting closes, every message put is received exactly once. The sanitizer builds
+    (`python -m sirius_b200._build --tsan|--asan`) run the same test."""
+    import threading
+    h = _pool(pool_mb=192, page_mb=2)
+    srv = PyInfTraCommunicator(True, True, 4, _name("mt"))
+    stop, errors = threading.Event(), []
+    put, got = [0] * 4, [0] * 3
+
+    def alloc_worker(i):
+        kind, rnd, held = i % 2, random.Random(i), []
+        try:
+            while not stop.is_set():
+                if held and (len(held) > 12 or rnd.random() < 0.45):
+                    ptr, n, tag = held.pop(rnd.randrange(len(held)))
+                    assert C.string_at(ptr.value, 1)[0] == tag and C.string_at(ptr.value + n - 1, 1)[0] == tag
+                    call("srt_pool_free", h, kind, ptr)
+                else:
+                    n, ptr = rnd.choice([512, 4096, 100000, 1 << 20, 3 << 20]), C.c_void_p()
+                    try:
+                        call("srt_pool_alloc", h, kind, n, C.byref(ptr))
+                    except SrtError:
+                        continue                                   # the other side holds the pages right now
+                    tag = (i * 37 + len(held)) % 251
+                    C.memset(ptr.value, tag, n)
+                    held.append((ptr, n, tag))
+                if rnd.random() < 0.02:
+                    call("srt_pool_empty_cache", h, kind, None)
+            for ptr, n, tag in held:
+                assert C.string_at(ptr.value, 1)[0] == tag
+                call("srt_pool_free", h, kind, ptr)
+        except BaseException as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    def putter(i):
+        rnd = random.Random(50 + i)
+        try:
+            while not stop.is_set():
+                try:
+                    srv.put_tra2inf(CtrlEvent.kReportBatchSize, put[i] + 1, i, rnd.randrange(4))
+                    put[i] += 1
+                except SrtError:
+                    time.sleep(0.0005)                             # that ring is full: let the getters catch up
+        except BaseException as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    def getter(i):
+        try:
+            while not stop.is_set():
+                m = srv.timed_get_from_any(5, 1) if i else srv.timed_get(5, 1, 0)
+                if m is not None:
+                    got[i] += 1
+        except BaseException as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    threads = ([threading.Thread(target=alloc_worker, args=(i,)) for i in range(6)]
+               + [threading.Thread(target=putter, args=(i,)) for i in range(4)])
+    getters = [threading.Thread(target=getter, args=(i,)) for i in range(3)]
+    try:
+        for t in threads + getters:
+            t.start()
+        time.sleep(1.5)
+        stop.set()
+        for t in threads + getters:
+            t.join(30)
+        assert not errors, errors[:3]
+        while srv.timed_get_from_any(0, 1) is not None:           # what the getters left behind when they stopped
+            got[0] += 1
+        assert sum(put) == sum(got) and sum(put) > 100
+        call("srt_pool_empty_cache", h, 0, None)
+        call("srt_pool_empty_cache", h, 1, None)
+        assert _stat(h, 4) == 96 and _stat(h, 0) == 0 and _stat(h, 1) == 0
+    finally:
+        stop.set()
+        srv.close()
+        call("srt_pool_destroy", h)
+
+
 # ---------------------------------------------------------------- orphaned segments
 def _orphan_maker(name):
     """Rank 0 of an earlier job: creates the segment, then dies without cleaning up."""

@@ -77,6 +77,8 @@ class Trainer:
                                                 EngineColocateAdjustL1Exception("vote finish failed"))
                         continue
                 self.batch_manager.finish_batch(epoch_idx, batch_idx, batch)
+                if epoch_idx == 0 and batch_idx == 0:
+                    self._default_first_batch_callback()
                 running_loss += float(loss or 0.0)
                 self._cur_epoch_stat.finished_batch += 1
                 self._cur_epoch_stat.finished_sample += self.dynamic_dataset.get_batch_size(batch)
@@ -130,6 +132,26 @@ class Trainer:
                     time.sleep(1e-3)
                 _C.dist.wait_barrier()
         self._last_max_batch_size_from_last_kill = None
+
+    def _default_first_batch_callback(self):
+        """After the first finished micro-batch (trainer.py:252-266): what has been allocated so far is the model, not
+        intermediates; the communication stream of the gradient exchange becomes known to the launch layer."""
+        if _C.is_enable_shared_tensor():
+            _C.tag_model_end()
+        if _C.is_enable_xsched():
+            if xsched.is_guess_nccl_begined():
+                xsched.guess_nccl_end()
+                nccl_streams = xsched.get_nccl_streams()
+                assert len(nccl_streams) <= 1, f"nccl streams {nccl_streams}"
+                if len(nccl_streams) == 1:
+                    xsched.register_stream(nccl_streams[0], False)
+            step = _C.get_train_step()
+            if step is not None and hasattr(step, 'synchronize'):
+                step.synchronize()
+            xsched.initial_kill_batch(0, 0)
+
+    def _default_first_epoch_callback(self):
+        pass
 
     def _is_ddp_training(self):
         return _C.get_train_world_size() > 1

@@ -15,9 +15,27 @@ from ._C import ColocateCtrlHookMode, CtrlEvent, TrainMode
 from .util import EventManager, MemoryPool
 
 
+_saved_tensor_hook_on = False
+
+
 def register_saved_tensor_hook():
-    """The reference tags every saved activation through autograd hooks (colocate_ctrl.py:18-29); the step
-    object knows its activation set, so nothing has to be registered."""
+    """colocate_ctrl.py:18-29: every tensor autograd saves for backward is tagged as an intermediate, so that
+    release_interm_memory() can give its memory back in one call. Only matters when PyTorch itself allocates from the
+    pool (torch_col._C.install_torch_allocator); a step object knows its own activation set."""
+    global _saved_tensor_hook_on
+    if _saved_tensor_hook_on:
+        return
+    try:
+        import torch
+    except ImportError:
+        return
+
+    def pack_hook(x):
+        _C.tag_interm_memory(x)
+        return x
+
+    torch._C._autograd._push_saved_tensors_default_hooks(pack_hook, lambda x: x)
+    _saved_tensor_hook_on = True
 
 
 class ColocateAdjustL1Exception(Exception):
@@ -57,8 +75,53 @@ class CtrlBase(abc.ABC):
         if self.train_mode.is_taskswitch():
             return self.switch(bool(barrier))
 
-    def register_pytorch_hook(self, module_list: List = ()):  # the executor polls the kill flag itself
-        pass
+    # ---- forward / backward hooks for torch modules (colocate_ctrl.py:101-110, 176-260, 355-400) ------------------
+    # A step object polls the kill flag between its units by itself; a torch.nn.Module trained on the allocator seam
+    # gets the reference's hooks: every leaf module checks the command after its forward and before its backward.
+    _kill_event = None         # the command that ends a micro-batch in this mode
+    _kill_exception = None
+
+    @classmethod
+    def register_fbward_hook(cls, module, fwd_hook, bwd_hook):
+        if not _C.is_enable_fbward_hook():
+            return
+        children = list(module.children())
+        if not children:
+            module.register_forward_hook(fwd_hook)
+            module.register_full_backward_hook(bwd_hook)
+        else:
+            for child in children:
+                cls.register_fbward_hook(child, fwd_hook, bwd_hook)
+
+    def _make_hook(self, where: str):
+        sync_first = self.hook_mode == ColocateCtrlHookMode.SYNC
+
+        def hook(module, _in, _out):
+            with EventManager.record_duration_event(where):
+                if sync_first:
+                    import torch
+                    if torch.cuda.is_available():
+                        torch.cuda.current_stream().synchronize()
+                if self._stub.cmd == self._kill_event:
+                    if not sync_first:
+                        xsched.kill_batch()
+                    raise self._kill_exception(f'[{where}]')
+        return hook
+
+    def register_pytorch_hook(self, module_list: List = ()):
+        """Hooks on every leaf of the torch modules in module_list (entries that are not torch modules, such as step
+        objects, are skipped). xsched-sync2 relies on an autograd-engine hook in the reference's PyTorch fork; on stock
+        PyTorch it gets the module-level hooks of xsched-sync."""
+        if self._kill_event is None or self.hook_mode == ColocateCtrlHookMode.NONE:
+            return
+        name = {ColocateCtrlHookMode.SYNC: 'sync'}.get(self.hook_mode, 'xsched_sync')
+        n = 0
+        for module in module_list:
+            if hasattr(module, 'children') and hasattr(module, 'register_forward_hook'):
+                CtrlBase.register_fbward_hook(module, self._make_hook(f'{name}_fwd'), self._make_hook(f'{name}_bwd'))
+                n += 1
+        if n and _C.is_release_interm_memory_v2():
+            register_saved_tensor_hook()
 
     def train_start(self): self._stub.train_start()
     def train_end(self): self._stub.train_end()
@@ -73,6 +136,8 @@ class ColocateCtrl(CtrlBase):
         super().__init__(train_mode, hook_mode, num_epoch, batch_size)
         self._stub = _C.PyColocateStub(batch_size, poll_ms=stub_poll_ms)
         _C._last_colocate_stub = self._stub
+        if train_mode == TrainMode.COLOCATE_L1:
+            self._kill_event, self._kill_exception = CtrlEvent.kColocateAdjustL1, ColocateAdjustL1Exception
         # keep an activation set for the announced batch size through an L1 adjust instead of dropping
         # everything and mapping it again at the next iteration (COLTRAIN_KEEP_TARGET_SET=0 restores that)
         self.keep_target_set = os.environ.get('COLTRAIN_KEEP_TARGET_SET', '1') != '0'
@@ -187,6 +252,8 @@ class SwitchCtrl(CtrlBase):
         assert train_mode in (TrainMode.TASKSWITCH_L1, TrainMode.TASKSWITCH_L0)
         super().__init__(train_mode, hook_mode, num_epoch, batch_size)
         self._stub = _C.PySwitchStub(batch_size, poll_ms=stub_poll_ms)
+        if train_mode == TrainMode.TASKSWITCH_L1:
+            self._kill_event, self._kill_exception = CtrlEvent.kInterruptTrain, SwitchL1Exception
         self.switch_log = []  # (release_ms, empty_cache_ms, reply_ms, released_bytes, start time.time())
 
     def check_kill(self, where: str):

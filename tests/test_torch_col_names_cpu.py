@@ -97,3 +97,61 @@ def test_monitor_sm_partition_prints_the_board(monkeypatch):
     finally:
         _C.torch_col_shutdown()
         srv.close()
+
+
+def test_forward_and_backward_hooks_end_a_micro_batch_of_a_torch_module(monkeypatch):
+    """ColocateCtrl.register_pytorch_hook on a torch.nn.Module (colocate_ctrl.py:101-110, 355-400): every leaf module
+    checks the stub's command after its forward and before its backward; an L1 adjust raises
+    ColocateAdjustL1Exception there, anything else lets the pass run. Step objects in the list are skipped."""
+    import torch
+    from sirius_b200.torch_col.colocate_ctrl import ColocateAdjustL1Exception, CtrlBase
+    name = f"srt_hooks_{os.getpid()}_{uuid.uuid4().hex[:6]}"
+    monkeypatch.setenv("COLTRAIN_HAS_INFER_SERVER", "1")
+    monkeypatch.setenv("SIRIUS_B200_COMM_NAME", name)
+    monkeypatch.setenv("SIRIUS_B200_DIST_NAME", name + "_dist")
+    srv = tc.DebugServer(1, name)
+    ctrl = None
+    try:
+        _C.torch_col_init(0, 1)
+        ctrl = tc.create_colocate_ctrl(tc.TrainMode.COLOCATE_L1, tc.ColocateCtrlHookMode.XSCHED_SYNC, 1, 4)
+        net = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.ReLU(), torch.nn.Sequential(torch.nn.Linear(8, 2)))
+        ctrl.register_pytorch_hook([net, object()])
+        x = torch.randn(4, 8, requires_grad=True)
+        net(x).sum().backward()                                            # no command: nothing happens
+        assert x.grad is not None
+        # a command arriving after the second leaf's forward ends the forward pass there
+        seen = []
+
+        def command_arrives(m, i, o):
+            seen.append("relu")
+            ctrl._stub.cmd = _C.CtrlEvent.kColocateAdjustL1
+
+        def last_layer_ran(m, i, o):
+            seen.append("last")
+
+        net[1].register_forward_hook(command_arrives)
+        net[2][0].register_forward_hook(last_layer_ran)
+        with pytest.raises(ColocateAdjustL1Exception, match="xsched_sync_fwd"):
+            net(x)
+        assert seen == ["relu"]                                            # the last layer's forward is reached, its own
+        #                                                                    hook (registered first) raises before ours
+        ctrl._stub.cmd = None
+        # ... and one arriving between forward and backward ends the backward pass at its first leaf
+        net2 = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 1))
+        ctrl.register_pytorch_hook([net2])
+        y = net2(torch.randn(4, 8, requires_grad=True)).sum()
+        ctrl._stub.cmd = _C.CtrlEvent.kColocateAdjustL1
+        with pytest.raises(ColocateAdjustL1Exception, match="xsched_sync_bwd"):
+            y.backward()
+        ctrl._stub.cmd = _C.CtrlEvent.kColocateAdjustL2                    # not a kill command in this mode
+        net2(torch.randn(4, 8)).sum().backward()
+        _C.disable_fbward_hook()
+        net3 = torch.nn.Linear(2, 2)
+        ctrl.register_pytorch_hook([net3])
+        assert len(net3._forward_hooks) == 0
+    finally:
+        _C._Config.use_fbward_hook = True
+        if ctrl is not None:
+            CtrlBase._reset()
+        _C.torch_col_shutdown()
+        srv.close()

@@ -22,6 +22,15 @@ from sirius_b200.step import ResNetStep
 ARCH, B, IMG = "resnet50", 16, 64
 
 
+def _wait_cmd(ctrl, event, limit_s=5.0):
+    """Until the trainer's control thread has taken the command in (it raises the kill flag before it publishes the
+    command): a fixed sleep would be a guess about the host's load."""
+    t0 = time.time()
+    while ctrl._stub.cmd != event:
+        assert time.time() - t0 < limit_s, f"the control thread never saw {event}"
+        time.sleep(0.002)
+
+
 def _batches(n):
     return O.make_batches(B, n, IMG)
 
@@ -91,7 +100,7 @@ def test_l1_adjust_kills_batch_releases_memory_and_training_reproduces_undisturb
             if inject and state["n"] == 4 and state["cid"] is None:
                 state["free_before"] = pool.stat("free_pages")
                 state["cid"] = srv.colocate_l1([B])        # same target: the batch is redone as it was
-                time.sleep(0.05)                           # the control thread raises the kill flag
+                _wait_cmd(ctrl, tc.CtrlEvent.kColocateAdjustL1)
             try:
                 step.forward_backward(len(batch), GBS)
             except SrtError as e:
@@ -222,7 +231,7 @@ def test_gpt2_batch_size_adjustment_on_inference_arrival():
         if state["n"] == 3 and state["cid"] is None:
             state["mapped_before"] = pool.stat("train_all")
             state["cid"] = srv.colocate_l1([2])            # the inference side needs memory: continue at batch 2
-            time.sleep(0.05)                               # the control thread raises the kill flag
+            _wait_cmd(ctrl, tc.CtrlEvent.kColocateAdjustL1)
         try:
             step.forward_backward(BS)
         except SrtError as e:
@@ -320,7 +329,7 @@ def test_gpt2_task_switch_releases_everything_and_resumes():
         if state["n"] == 3 and state["cid"] is None:
             state["free_before"] = pool.stat("free_pages")
             state["cid"] = srv.interrupt_train()
-            time.sleep(0.05)                                   # the control thread raises the kill flag
+            _wait_cmd(ctrl, tc.CtrlEvent.kInterruptTrain)
         try:
             step.forward_backward(BS)
         except SrtError as e:

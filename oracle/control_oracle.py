@@ -143,3 +143,170 @@ class TrainAdjuster:
         plan = [mn] * world if mn <= 0 or not self.imbalance(mn, amr) else targets
         self.t = list(plan)
         return plan
+
+
+# ---- pytorch/torch_col/csrc/dynamic_batch.cc:144-252, 316-573, 640-733 ---------------------------
+class Ledger:
+    """The DynamicBatchDistirbutor's shared state and the per-rank counters of every rank, in one object (the C++
+    keeps the former in shared memory and the latter in each process). Sample ranges are half-open pairs kept in sets
+    ordered by (first, second), as the reference's boost sets of pairs are. Every CHECK of the reference is an
+    AssertionError here."""
+
+    def __init__(self, world: int, dataset_size: int, input_batch_size: int, global_batch_size: int, lazy: bool,
+                 policy: str, perf: Optional[PerfModel] = None):
+        self.world, self.dataset_size, self.input_bs, self.gbs = world, dataset_size, input_batch_size, global_batch_size
+        self.lazy, self.policy, self.perf = lazy, policy, perf or PerfModel()
+        self.num_gb_per_epoch = (dataset_size + global_batch_size - 1) // global_batch_size       # :80-81
+        init = -1 if lazy else 0                                                                    # :131-141
+        self.unproc_per, self.procing_per, self.proced_per = [init] * world, [init] * world, [init] * world
+        self.has_unproc = [False] * world
+        self.unproc, self.procing, self.proced = [], [], []            # sorted lists of (first, second)
+        self.n_unproc = self.n_procing = self.n_proced = 0
+        # per-process members (:76-79), one entry per rank
+        self.num_proced_gb = [0] * world
+        self.num_proced_sample_of_epoch = [0] * world
+        self.next_epoch_idx = [0] * world
+        self.first_epoch_start = [False] * world
+
+    @staticmethod
+    def _n(r): return r[1] - r[0]
+
+    # DistributeBatchWithoutLock (:157-252); target_unpub = the board's unpublished targets, None without a server
+    def distribute(self, check: bool, to_all: bool, at_begin: bool, target_unpub: Optional[List[int]] = None):
+        do = not (self.lazy or (not at_begin and self.policy == 'fix'))
+        if check and do:
+            n = sum(self.unproc_per)
+            assert n == self.n_unproc, (self.unproc_per, self.n_unproc)
+        else:
+            n = self.n_unproc
+        if to_all:
+            self.has_unproc = [True] * self.world
+        if do:
+            workers = [i for i in range(self.world) if self.has_unproc[i]]
+            if workers:
+                tbs = [target_unpub[i] if target_unpub is not None else self.input_bs for i in workers]
+                if self.policy == 'by_performance' and n < len(workers):
+                    # the reference's round-off loop cannot end here (every worker holds the minimum of one sample);
+                    # the library gives the first n workers one sample each and takes the others out
+                    for k, w in enumerate(workers):
+                        self.unproc_per[w] = 1 if k < n else 0
+                        if k >= n:
+                            self.has_unproc[w] = False
+                else:
+                    share = distribute_batch(self.policy, n, [self.perf.get(b) for b in tbs], len(workers))
+                    for w, s in zip(workers, share):
+                        self.unproc_per[w] = s
+            else:
+                assert n == 0
+        assert n >= 0
+
+    # NextGlobalBatchImpl (:640-716), the master's part; the ranks' counters are read from rank 0's members
+    def next_global_batch(self, target_unpub: Optional[List[int]] = None):
+        cur = self.gbs
+        if self.gbs + self.num_proced_sample_of_epoch[0] > self.dataset_size:
+            cur = self.dataset_size - self.num_proced_sample_of_epoch[0]
+        assert cur >= 0
+        self.n_unproc, self.n_procing, self.n_proced = cur, 0, 0
+        self.unproc, self.procing, self.proced = [], [], []
+        if cur > 0:
+            first = self.num_proced_sample_of_epoch[0]
+            self.unproc = [(first, first + cur)]
+            self.distribute(False, True, True, target_unpub)
+            if not self.lazy:
+                self.procing_per, self.proced_per = [0] * self.world, [0] * self.world
+        elif not self.lazy:
+            self.unproc_per, self.procing_per, self.proced_per = [0] * self.world, [0] * self.world, [0] * self.world
+
+    # LazyDistributingGetBatchSize (:414-436)
+    def _lazy_size(self, batch_size: int):
+        ongoing = sum(self.has_unproc)
+        assert ongoing > 0
+        mx = self.n_unproc - ongoing + 1
+        return (mx, True) if batch_size >= mx else (batch_size, False)
+
+    # GetBatch (:316-412)
+    def get_batch(self, rank: int, batch_size: int):
+        if self.lazy:
+            size, last = self._lazy_size(batch_size)
+        else:
+            size, last = min(batch_size, self.unproc_per[rank]), None
+        got, out, i = 0, [], 0
+        while got < size:
+            assert i < len(self.unproc)
+            r = self.unproc[i]
+            if self._n(r) + got <= size:
+                got += self._n(r)
+                out.append(r)
+                self.procing.append(r)
+                del self.unproc[i]                           # the iterator moves to the next range
+            else:
+                head, rest = (r[0], r[0] + size - got), (r[0] + size - got, r[1])      # SliceBatchRange
+                got += self._n(head)
+                out.append(head)
+                self.procing.append(head)
+                self.unproc[i] = rest
+                self.unproc.sort()
+                i = self.unproc.index(rest)
+        self.procing.sort()
+        if not self.lazy:
+            self.unproc_per[rank] -= got
+            self.procing_per[rank] += got
+            assert self.unproc_per[rank] >= 0
+        self.n_unproc -= got
+        self.n_procing += got
+        assert self.n_unproc >= 0
+        if not self.lazy:
+            last = self.unproc_per[rank] == 0
+        if last:
+            self.has_unproc[rank] = False
+        return out, last
+
+    # QueryNextBatchSize (:438-459)
+    def query_next_batch_size(self, rank: int, batch_size: int) -> int:
+        return min(self.n_unproc if self.lazy else self.unproc_per[rank], batch_size)
+
+    def _move(self, ranges, dst):
+        n = 0
+        for r in ranges:
+            r = tuple(r)
+            assert r in self.procing, r
+            self.procing.remove(r)
+            dst.append(r)
+            n += self._n(r)
+        dst.sort()
+        return n
+
+    # FinishBatch (:461-530)
+    def finish_batch(self, rank: int, ranges, end_of_global_batch: bool):
+        n = self._move(ranges, self.proced)
+        if not self.lazy:
+            self.procing_per[rank] -= n
+            self.proced_per[rank] += n
+        self.n_procing -= n
+        self.n_proced += n
+        if end_of_global_batch:
+            assert self.lazy or self.procing_per[rank] == 0
+            self.num_proced_gb[rank] += 1
+            self.num_proced_sample_of_epoch[rank] = min(self.num_proced_sample_of_epoch[rank] + self.gbs, self.dataset_size)
+
+    # AbortBatch (:532-573)
+    def abort_batch(self, rank: int, ranges):
+        n = self._move(ranges, self.unproc)
+        if not self.lazy:
+            self.procing_per[rank] -= n
+            self.unproc_per[rank] += n
+        self.n_procing -= n
+        self.n_unproc += n
+
+    # NextEpoch (:718-733)
+    def next_epoch(self, rank: int) -> int:
+        if self.first_epoch_start[rank]:
+            assert self.num_proced_sample_of_epoch[rank] == self.dataset_size
+            assert self.num_proced_gb[rank] == self.num_gb_per_epoch
+        else:
+            self.first_epoch_start[rank] = True
+        e = self.next_epoch_idx[rank]
+        self.next_epoch_idx[rank] += 1
+        self.num_proced_gb[rank] = 0
+        self.num_proced_sample_of_epoch[rank] = 0
+        return e

@@ -258,6 +258,166 @@ def test_fewer_samples_than_ranks_at_the_tail_of_an_epoch(policy):
     assert ranges[0][0] == 0 and ranges[-1][1] == 34 and all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
 
 
+def _ledger_ranks(world, ds, bs, gbs, lazy, policy):
+    """`world` handles on one segment, opened and initialised from one thread per rank (the lazy mode's init and every
+    NextGlobalBatch meet at the job's barrier)."""
+    import threading
+    name = _name("led")
+    hs = [C.c_void_p() for _ in range(world)]
+    call("srt_dist_open", name.encode(), 0, world, 5000, C.byref(hs[0]))
+    for r in range(1, world):
+        call("srt_dist_open", name.encode(), r, world, 5000, C.byref(hs[r]))
+
+    def together(fn):
+        errs = []
+
+        def run(r):
+            try:
+                fn(r)
+            except BaseException as e:  # noqa: BLE001
+                errs.append(repr(e))
+        ts = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(30)
+        assert not errs, errs
+
+    together(lambda r: call("srt_dbd_init", hs[r], ds, bs, gbs, int(lazy), {"fix": 0, "simple": 1, "by_performance": 2}[policy]))
+    return hs, together
+
+
+def _ledger_info(h, which, rank=0):
+    v = C.c_int()
+    call("srt_dbd_info", h, which, rank, C.byref(v))
+    return v.value
+
+
+@pytest.mark.parametrize("world,lazy,policy", [(1, False, "fix"), (1, True, "simple"), (2, False, "fix"), (2, False, "simple"),
+                                               (2, False, "by_performance"), (3, False, "by_performance"), (2, True, "simple")])
+def test_ledger_follows_the_restated_reference_on_random_schedules(world, lazy, policy):
+    """Random micro-batch sizes, aborts and finishes over several global batches and two epochs, on `world` ranks of one
+    job: every range handed out, every last-micro-batch flag and every counter equal those of the restated
+    DynamicBatchDistirbutor (oracle/control_oracle.py: Ledger), whose assertions are the reference's CHECKs."""
+    ds, bs, gbs = 150, 16, 64                                   # the last global batch of an epoch is a remainder of 22
+    hs, together = _ledger_ranks(world, ds, bs, gbs, lazy, policy)
+    ref = O.Ledger(world, ds, bs, gbs, lazy, policy)
+    rnd = random.Random(int(os.environ.get("SRT_LEDGER_SEED", "0")) + 100 * world + 10 * int(lazy) + len(policy))
+
+    def same_counters():
+        assert [_ledger_info(hs[0], w) for w in (3, 4, 5)] == [ref.n_unproc, ref.n_procing, ref.n_proced]
+        for r in range(world):
+            assert [_ledger_info(hs[0], w, r) for w in (6, 7, 8)] == [ref.unproc_per[r], ref.procing_per[r], ref.proced_per[r]]
+
+    def get(r, want):
+        buf, n, last = (C.c_int * 128)(), C.c_int(), C.c_int()
+        q = C.c_int()
+        call("srt_dbd_query_next_batch_size", hs[r], want, C.byref(q))
+        assert q.value == ref.query_next_batch_size(r, want)
+        call("srt_dbd_get_batch", hs[r], want, buf, 64, C.byref(n), C.byref(last))
+        got = [(buf[2 * i], buf[2 * i + 1]) for i in range(n.value)]
+        exp, exp_last = ref.get_batch(r, want)
+        assert (got, bool(last.value)) == (exp, bool(exp_last)), (r, want)
+        return got, bool(last.value)
+
+    def flat(ranges):
+        arr = (C.c_int * (2 * max(len(ranges), 1)))()
+        for i, (a, b) in enumerate(ranges):
+            arr[2 * i], arr[2 * i + 1] = a, b
+        return arr
+
+    try:
+        for epoch in range(2):
+            for r in range(world):
+                e = C.c_int()
+                call("srt_dbd_next_epoch", hs[r], C.byref(e))
+                assert e.value == ref.next_epoch(r) == epoch
+            for gb in range(ref.num_gb_per_epoch):
+                together(lambda r: call("srt_dbd_next_global_batch", hs[r], None, 10000))
+                ref.next_global_batch()
+                same_counters()
+                # A rank holds its last micro-batch until every rank has one (the finish vote); a kill anywhere makes
+                # every rank that waits in the vote give its last micro-batch back too, then rank 0 hands the
+                # remainder out again (Trainer.handle_abort_batch).
+                pending, kills = {}, 0
+
+                def abort(r, ranges, last):
+                    call("srt_dbd_abort_batch", hs[r], flat(ranges), len(ranges), int(last))
+                    ref.abort_batch(r, ranges)
+
+                def kill_all(first=None):
+                    if first is not None:
+                        abort(*first)
+                    for q, rg in pending.items():
+                        abort(q, rg, True)
+                    pending.clear()
+                    call("srt_dbd_distribute_batch", hs[0], None, 1, 1, 0)
+                    ref.distribute(True, True, False)
+                    same_counters()
+
+                while True:
+                    free = [i for i in range(world) if i not in pending]
+                    if not free:
+                        if kills < 2 and rnd.random() < 0.3:
+                            kills += 1
+                            kill_all()
+                            continue
+                        for q, rg in pending.items():
+                            call("srt_dbd_finish_batch", hs[q], flat(rg), len(rg), 1)
+                            ref.finish_batch(q, rg, True)
+                        same_counters()
+                        break
+                    r = rnd.choice(free)
+                    ranges, last = get(r, rnd.choice([1, 3, 7, 16, 40]))
+                    same_counters()
+                    if kills < 4 and ranges and rnd.random() < 0.2:
+                        kills += 1
+                        kill_all((r, ranges, last))
+                    elif last:
+                        pending[r] = ranges
+                    else:
+                        call("srt_dbd_finish_batch", hs[r], flat(ranges), len(ranges), 0)
+                        ref.finish_batch(r, ranges, False)
+                        same_counters()
+                assert ref.n_unproc == 0 and ref.n_procing == 0
+                assert [_ledger_info(hs[r], 2) for r in range(world)] == ref.num_proced_gb
+    finally:
+        for h in hs:
+            call("srt_dist_close", h)
+
+
+def test_ledger_splits_by_measured_throughput_at_each_ranks_target_batch_size():
+    """BY_PERFORMANCE with a colocated server: a rank's share of a global batch is proportional to the throughput the
+    performance model holds for that rank's unpublished target batch size (dynamic_batch.cc:254-314,
+    perf_model.cc:65-95), here 16 samples at 1.6 samples/ms against 8 at 1.0, and the targets are published."""
+    world, ds, gbs = 2, 400, 100
+    hs, together = _ledger_ranks(world, ds, 16, gbs, False, "by_performance")
+    nm = _name("ledc")
+    srv = PyInfTraCommunicator(True, True, world, nm)
+    ref = O.Ledger(world, ds, 16, gbs, False, "by_performance")
+    try:
+        for r, tgt in enumerate((16, 8)):
+            srv.set_train_info(r, train_pid=os.getpid(), train_rank=r, train_world_size=world, init_batch_size=16,
+                               current_batch_size=16, target_batch_size=16, target_batch_size_unpublished=tgt,
+                               model_name="resnet152")
+        for bs, ms in ((16, 10.0), (8, 8.0), (16, 10.0)):
+            call("srt_perf_record_thpt", hs[0], bs, C.c_double(ms))
+            ref.perf.record(bs, ms)
+        for r in range(world):
+            e = C.c_int()
+            call("srt_dbd_next_epoch", hs[r], C.byref(e))
+            ref.next_epoch(r)
+        together(lambda r: call("srt_dbd_next_global_batch", hs[r], srv._h, 10000))
+        ref.next_global_batch([16, 8])
+        shares = [_ledger_info(hs[0], 6, r) for r in range(world)]
+        assert shares == ref.unproc_per == [62, 38]       # int(61.5) + int(38.5) = 99: the round-off loop gives rank 0 the last one
+        assert [srv.get_field(r, 5) for r in range(world)] == [16, 8]     # target := unpublished target
+    finally:
+        for h in hs:
+            call("srt_dist_close", h)
+        srv.close()
+
+
 def test_distribute_batch_matches_reference_for_every_policy():
     rnd = random.Random(2)
     for _ in range(300):

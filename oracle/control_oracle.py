@@ -144,6 +144,32 @@ class TrainAdjuster:
         self.t = list(plan)
         return plan
 
+    # GetLLMInferRequireMemAdjustPlan (:435-519). train_avail_mb = what training could still use once the requirement
+    # is met (free pages + its own pages - margin - requirement), as the function computes it from the pool.
+    # With LLM serving the reference's CheckImbalance ends the server, so balance must be off.
+    def llm_require(self, dev: int, required_mb: float, train_avail_mb: float) -> List[int]:
+        cur = self.t[dev]
+        if cur <= 0 or required_mb <= 0:
+            return []
+        by_avail = self.predict_target_bs(max(train_avail_mb, 0.0))
+        by_required = cur - self.delta_bs(required_mb)
+        target = max(0, min(by_avail, by_required))
+        assert all(x == cur for x in self.t), "LOG(FATAL): Not supported"
+        assert not self.balance, "LOG(FATAL): Not supported for LLM"
+        self.t = [target] * len(self.t)
+        return list(self.t)
+
+    # GetLLMInferReleaseMemAdjustPlan (:342-433). free_mb / train_avail_mb per device as computed there from the pool.
+    def llm_release(self, train_avail_mb, free_mb) -> List[int]:
+        assert not self.balance, "LOG(FATAL): Not supported for LLM"
+        targets = []
+        for r, cur in enumerate(self.t):
+            by_avail = self.predict_target_bs(max(train_avail_mb[r], 0.0))
+            by_delta = cur + self.delta_bs(max(free_mb[r], 0.0))
+            targets.append(max(cur, min(by_avail, by_delta)))
+        self.t = [min(targets)] * len(self.t)
+        return list(self.t)
+
 
 # ---- pytorch/torch_col/csrc/dynamic_batch.cc:144-252, 316-573, 640-733 ---------------------------
 class Ledger:

@@ -544,6 +544,39 @@ def test_train_adjuster_plans_match_reference_logic():
             srv.close()
 
 
+def test_llm_adjust_plans_match_reference_logic():
+    """The KV-cache pool's plans (server/train_adjuster.cc:342-519): on a require the target is the smaller of what the
+    memory left for training allows and the current target minus the requirement's worth of samples, never below 0 and
+    the same for every rank; on a release the smaller of what fits and the current target plus the freed memory's
+    worth, never below the current target; both are published as the unpublished target."""
+    rnd = random.Random(11)
+    for trial in range(40):
+        world, init_bs = rnd.choice([1, 2, 4]), rnd.choice([32, 64])
+        t0 = rnd.randint(0, init_bs)
+        cfg = AdjusterConfig(1150.0, 85.0, 0, 0, 1500.0, world, 1)
+        srv, h = _make_adjuster(world, [t0] * world, init_bs, cfg)
+        ref = O.TrainAdjuster(1150.0, 85.0, [t0] * world, init_bs, 0, False, 1500.0, world, True)
+        try:
+            for _ in range(8):
+                plan, n = (C.c_int * 8)(), C.c_int()
+                if rnd.random() < 0.5:
+                    dev, need, avail = rnd.randrange(world), rnd.uniform(-50, 3000), rnd.uniform(-500, 9000)
+                    call("srt_adjuster_llm_require_plan", h, dev, C.c_double(need), C.c_double(avail), None, plan, C.byref(n))
+                    want = ref.llm_require(dev, need, avail)
+                else:
+                    av = [rnd.uniform(-500, 9000) for _ in range(world)]
+                    fr = [rnd.uniform(-500, 4000) for _ in range(world)]
+                    call("srt_adjuster_llm_release_plan", h, (C.c_double * world)(*av), (C.c_double * world)(*fr), plan,
+                         C.byref(n))
+                    want = ref.llm_release(av, fr)
+                assert list(plan[:n.value]) == want, (trial, want, list(plan[:n.value]))
+                if want:
+                    assert [srv.get_field(r, 6) for r in range(world)] == want
+        finally:
+            call("srt_adjuster_destroy", h)
+            srv.close()
+
+
 # ---------------------------------------------------------------- page pool (host backend)
 def _pool(pool_mb=64, page_mb=2, unmap_on_release=0):
     cfg = PoolConfig(0, 1, page_mb << 20, pool_mb << 20, 4, 1, unmap_on_release)
